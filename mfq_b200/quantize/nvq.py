@@ -1,0 +1,143 @@
+"""NVQ quantizer: even-parity sign coding + joint lattice-index / group-scale search.
+
+Steps (same pipeline as the reference, ``mfq/quantize/nvq_quant.py:170-240,453-600``),
+restated as batched torch so the nearest-codeword search is two GEMMs per chunk:
+
+1. signs: 7 free sign bits per 8 weights, the 8th is their parity.  A block whose
+   true signs have odd parity gives up the sign of its cheapest element
+   (smallest ``w*x^2``); the magnitude target of that element becomes ``-|x|``.
+2. per group, ``search_steps`` trial scales ``max|x| / (qmax + offset)``; for each:
+   nearest codeword per vector under the weighted metric
+   ``argmin_c  s^2 * (w . c^2) - 2 s * ((w*x) . c)``, weighted-LS refit of the
+   scale, one more assignment + refit; keep the lowest error.
+3. row anchor ``d = f16(max_g scale / (2^k-1))``, group codes ``rint(scale / d)``;
+   re-assign at the effective scales, refit the anchor in closed form, repeat once.
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from ..formats.nvq import NvqSpec, NvqTensor, codebook as lattice
+
+__all__ = ["quantize_nvq", "encode_even_parity"]
+
+
+def encode_even_parity(rows: torch.Tensor, w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Return (magnitude targets ``[out, K8]``, 7-bit sign masks ``[out, K8/8]``)."""
+    out, n = rows.shape
+    blk = rows.reshape(out, n // 8, 8)
+    neg = blk < 0
+    odd = (neg.sum(-1) & 1).bool()
+    cost = (w.reshape(out, n // 8, 8) * blk * blk)
+    victim = cost.argmin(-1)
+    flip = torch.zeros_like(neg)
+    flip.scatter_(-1, victim[..., None], odd[..., None])
+    stored = neg ^ flip
+    target = torch.where(flip, -blk.abs(), blk.abs())
+    bitw = (1 << torch.arange(7, device=rows.device)).to(torch.int32)
+    masks = (stored[..., :7].to(torch.int32) * bitw).sum(-1).to(torch.uint8)
+    return target.reshape(out, n), masks
+
+
+def _assign(cross: torch.Tensor, quad: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    s = scale[:, None]
+    return (s * s * quad - 2.0 * s * cross).argmin(-1)
+
+
+def _refit(xg, wg, idx, table, vpg):
+    code = table[idx].reshape(xg.shape)
+    num = (wg * xg * code).sum(-1)
+    den = (wg * code * code).sum(-1)
+    return torch.where(den > 0, num / den.clamp_min(1e-30), torch.zeros_like(num)).clamp_min(0.0), code
+
+
+def _search(xg: torch.Tensor, wg: torch.Tensor, table: torch.Tensor, vec: int, steps: int):
+    g, gs = xg.shape
+    vpg = gs // vec
+    xv = xg.reshape(g * vpg, vec)
+    wv = wg.reshape(g * vpg, vec)
+    cross = (wv * xv) @ table.T
+    quad = wv @ (table * table).T
+    qmax = float(table.max())
+    amax = xg.abs().amax(-1)
+    best_err = torch.full((g,), float("inf"), device=xg.device)
+    best_scale = torch.zeros(g, device=xg.device)
+    best_idx = torch.zeros((g, vpg), dtype=torch.long, device=xg.device)
+    for off in torch.linspace(-0.12 * qmax, 0.12 * qmax, steps).tolist():
+        s0 = torch.where(amax > 0, amax / (qmax + off), torch.zeros_like(amax))
+        idx = _assign(cross, quad, s0.repeat_interleave(vpg)).reshape(g, vpg)
+        s1, _ = _refit(xg, wg, idx, table, vpg)
+        idx = _assign(cross, quad, s1.repeat_interleave(vpg)).reshape(g, vpg)
+        s2, code = _refit(xg, wg, idx, table, vpg)
+        diff = s2[:, None] * code - xg
+        err = (wg * diff * diff).sum(-1)
+        take = err < best_err
+        best_err = torch.where(take, err, best_err)
+        best_scale = torch.where(take, s2, best_scale)
+        best_idx[take] = idx[take]
+    return best_scale, best_idx, cross, quad
+
+
+def quantize_nvq(weight, spec: NvqSpec, *, axis: int = 0, importance=None, search_steps: int = 19,
+                 refit_anchor: bool = True, device: str | torch.device = "cpu", row_chunk: int = 256) -> NvqTensor:
+    if spec.sign_mode != "even":
+        raise NotImplementedError("the quantizer emits even-parity signs only")
+    w_full = torch.as_tensor(np.asarray(weight, dtype=np.float32) if not torch.is_tensor(weight) else weight).to(torch.float32)
+    shape = tuple(w_full.shape)
+    axis %= w_full.ndim
+    rows_all = w_full.movedim(axis, 0).reshape(shape[axis], -1)
+    out, n = rows_all.shape
+    gs, vec = spec.groupsize, spec.vector_size
+    ng = math.ceil(n / gs)
+    padded = ng * gs
+    table = torch.as_tensor(lattice(spec).astype(np.float32), device=device)
+    levels = (1 << spec.sub_bits) - 1
+    nvec, nsign = math.ceil(n / vec), math.ceil(n / 8)
+    d_all = np.zeros(out, np.float32)
+    s_all = np.zeros((out, ng), np.uint8)
+    i_all = np.zeros((out, nvec), np.uint16 if spec.index_bits > 8 else np.uint8)
+    m_all = np.zeros((out, nsign), np.uint8)
+    imp = None if importance is None else torch.as_tensor(np.asarray(importance, dtype=np.float32)).reshape(1, n)
+    for r0 in range(0, out, row_chunk):
+        rows = torch.nn.functional.pad(rows_all[r0 : r0 + row_chunk], (0, padded - n)).to(device)
+        o = rows.shape[0]
+        wobj = torch.ones_like(rows) if imp is None else torch.nn.functional.pad(imp.expand(o, n), (0, padded - n)).to(device).clone()
+        if padded > n:
+            wobj[:, n:] = 0.0
+        target, masks = encode_even_parity(rows, torch.where(wobj > 0, wobj, torch.full_like(wobj, 1e-12)))
+        xg = target.reshape(o * ng, gs)
+        wg = wobj.reshape(o * ng, gs)
+        raw, idx, cross, quad = _search(xg, wg, table, vec, search_steps)
+        raw2 = raw.reshape(o, ng)
+        top = raw2.amax(-1)
+        d = torch.where(top > 0, (top / levels).to(torch.float16).to(torch.float32), torch.zeros_like(top))
+        sub = torch.clamp(torch.round(raw2 / torch.where(d > 0, d, torch.ones_like(d))[:, None]), 0, levels)
+        vpg = gs // vec
+
+        def reassign(anchor):
+            eff = (anchor[:, None] * sub).reshape(-1)
+            return _assign(cross, quad, eff.repeat_interleave(vpg)).reshape(o * ng, vpg)
+
+        def refit(index):
+            code = table[index].reshape(o, ng, gs) * sub[:, :, None]
+            num = (wg.reshape(o, ng, gs) * xg.reshape(o, ng, gs) * code).sum((-1, -2))
+            den = (wg.reshape(o, ng, gs) * code * code).sum((-1, -2))
+            a = torch.where(den > 0, num / den.clamp_min(1e-30), torch.zeros_like(num)).clamp_min(0.0)
+            return a.to(torch.float16).to(torch.float32)
+
+        idx = reassign(d)
+        if refit_anchor:
+            d = refit(idx)
+            idx = reassign(d)
+            d = refit(idx)
+        sl = slice(r0, r0 + o)
+        d_all[sl] = d.cpu().numpy()
+        s_all[sl] = sub.to(torch.uint8).cpu().numpy()
+        i_all[sl] = idx.reshape(o, ng * vpg)[:, :nvec].cpu().numpy().astype(i_all.dtype)
+        m_all[sl] = masks[:, :nsign].cpu().numpy()
+    return NvqTensor(spec=spec, shape=shape, axis=axis, neuron_len=n, neuron_scale=d_all, sub_scale=s_all,
+                     indices=i_all, signs=m_all)

@@ -1,0 +1,28 @@
+import os
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: test needs a CUDA device (sm_100a)")
+    config.addinivalue_line("markers", "multigpu: test needs more than one CUDA device")
+
+
+@pytest.fixture(scope="session")
+def reference_pkg():
+    """The unmodified reference package, if it was installed under baseline/_ref (golden cross-checks)."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "mfq").is_dir():
+        pytest.skip("reference package not installed")
+    sys.path.insert(0, str(ref))
+    try:
+        import mfq  # noqa: F401
+    except Exception as exc:  # pragma: no cover
+        pytest.skip(f"reference package not importable: {exc}")
+    return ref
