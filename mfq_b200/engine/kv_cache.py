@@ -1,0 +1,95 @@
+"""Paged KV cache with FP8 pages.
+
+Pool layout per layer (what the CUDA kernels index): ``k, v : [pages, kv_heads, page_size, head_dim]``
+E4M3 and ``k_scale, v_scale : [pages, kv_heads, page_size]`` fp32 (one multiplier per token and head).
+Pages are 16 tokens, like the reference's paged cache (``cpp_runtime/backends/cuda/models/qwen35/paged_kv.h:25-26``),
+whose pages hold fp16/bf16 or TurboQuant codes; FP8 pages halve the decode-attention traffic.  The host
+side keeps a free list and per-sequence page lists; a sequence's block-table row is written to a device
+tensor that the kernels (and the captured decode graph) read.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+PAGE_SIZE = 16
+
+
+@dataclass
+class LayerKV:
+    k: torch.Tensor
+    v: torch.Tensor
+    k_scale: torch.Tensor
+    v_scale: torch.Tensor
+    page_size: int
+
+
+class PageAllocator:
+    """Host-side free list of physical pages (page 0 is reserved as the null page)."""
+
+    def __init__(self, num_pages: int) -> None:
+        self.num_pages = num_pages
+        self.free = list(range(num_pages - 1, 0, -1))
+        self.owned: dict[int, list[int]] = {}
+
+    @property
+    def free_pages(self) -> int:
+        return len(self.free)
+
+    def pages_for(self, tokens: int, page_size: int = PAGE_SIZE) -> int:
+        return (tokens + page_size - 1) // page_size
+
+    def ensure(self, seq_id: int, tokens: int, page_size: int = PAGE_SIZE) -> list[int]:
+        """Grow ``seq_id`` to hold ``tokens`` tokens; raises ``MemoryError`` when the pool is exhausted."""
+        pages = self.owned.setdefault(seq_id, [])
+        need = self.pages_for(tokens, page_size) - len(pages)
+        if need > len(self.free):
+            raise MemoryError(f"KV pool exhausted: need {need} pages, {len(self.free)} free")
+        for _ in range(max(0, need)):
+            pages.append(self.free.pop())
+        return pages
+
+    def release(self, seq_id: int) -> None:
+        for p in self.owned.pop(seq_id, []):
+            self.free.append(p)
+
+
+class PagedKVCache:
+    def __init__(self, *, layers: int, kv_heads: int, head_dim: int, num_pages: int, max_seqs: int,
+                 max_pages_per_seq: int, device: torch.device | str, page_size: int = PAGE_SIZE) -> None:
+        self.page_size = page_size
+        self.num_pages = num_pages
+        self.max_pages_per_seq = max_pages_per_seq
+        dev = torch.device(device)
+        shape = (layers, num_pages, kv_heads, page_size, head_dim)
+        self.k = torch.zeros(shape, dtype=torch.float8_e4m3fn, device=dev)
+        self.v = torch.zeros(shape, dtype=torch.float8_e4m3fn, device=dev)
+        self.k_scale = torch.zeros(shape[:-1], dtype=torch.float32, device=dev)
+        self.v_scale = torch.zeros(shape[:-1], dtype=torch.float32, device=dev)
+        self.block_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, device=dev)
+        self.allocator = PageAllocator(num_pages)
+
+    def layer(self, i: int) -> LayerKV:
+        return LayerKV(self.k[i], self.v[i], self.k_scale[i], self.v_scale[i], self.page_size)
+
+    def bytes_per_token(self) -> int:
+        layers, _, heads, _, dim = self.k.shape
+        return layers * heads * (2 * dim + 8)
+
+    def assign(self, row: int, seq_id: int, tokens: int) -> None:
+        """Make block-table ``row`` cover ``tokens`` tokens of ``seq_id`` (allocating pages as needed)."""
+        pages = self.allocator.ensure(seq_id, tokens, self.page_size)
+        if len(pages) > self.max_pages_per_seq:
+            raise MemoryError("sequence exceeds max_pages_per_seq")
+        self.block_table[row, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
+
+    def slots(self, seq_id: int, start: int, count: int) -> torch.Tensor:
+        pages = self.allocator.owned[seq_id]
+        pos = torch.arange(start, start + count)
+        page_ids = torch.tensor(pages, dtype=torch.int64)[pos // self.page_size]
+        return (page_ids * self.page_size + pos % self.page_size).to(torch.int32)
+
+    def release(self, seq_id: int) -> None:
+        self.allocator.release(seq_id)

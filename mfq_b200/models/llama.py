@@ -1,0 +1,254 @@
+"""Dense Llama-style decoder in block-scaled FP8 (weights E4M3 + 128x128 fp32 multipliers, FP8 paged KV).
+
+One module, two execution paths with identical quantization semantics:
+
+* ``device.type == "cuda"``: the hand-written kernels of :mod:`mfq_b200.ops` (tcgen05 FP8 GEMM with the
+  residual add fused in its epilogue, fused RMSNorm+quant, RoPE+page write, paged decode attention);
+* CPU: the fp32 restatements in :mod:`mfq_b200.ops.reference` (the oracle of the tests).
+
+Projections are stored fused (``qkv``, ``gate_up``) and, under tensor parallelism, pre-sharded per rank:
+column shards for ``qkv``/``gate_up`` (whole heads / whole 128-row blocks per rank), input shards for
+``o_proj``/``down``, so each rank's shard keeps the 128x128 scale grid intact.  The canonical checkpoint names
+(``model.block.N.attention.query.weight`` ...) follow the reference schema
+(``mfq/architectures/tensor_schema.py:551-596``); axis rules follow ``ops/include/cuda_execution.h:179-197``.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import ops
+from ..ops import reference as ref
+from ..quantize.fp8_block import quantize_fp8_block_torch
+
+FP8 = torch.float8_e4m3fn
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 128256
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    rope_theta: float = 5e5
+    rms_eps: float = 1e-5
+    max_position: int = 8192
+    name: str = "llama-8b-fp8"
+
+    @classmethod
+    def llama_8b(cls) -> "LlamaConfig":
+        return cls()
+
+    @classmethod
+    def tiny(cls) -> "LlamaConfig":
+        return cls(vocab_size=1024, hidden_size=256, intermediate_size=512, num_layers=2, num_heads=4, num_kv_heads=2,
+                   head_dim=128, rope_theta=1e4, name="llama-tiny-fp8")
+
+    def param_count(self) -> int:
+        h, i = self.hidden_size, self.intermediate_size
+        per = h * (self.num_heads + 2 * self.num_kv_heads) * self.head_dim + self.num_heads * self.head_dim * h + 3 * h * i
+        return self.num_layers * per + 2 * self.vocab_size * h
+
+
+@dataclass
+class Fp8Linear:
+    """``[out, in]`` E4M3 codes + ``[ceil(out/128), in/128]`` fp32 multipliers."""
+
+    q: torch.Tensor
+    scale: torch.Tensor
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor) -> "Fp8Linear":
+        q, s = quantize_fp8_block_torch(w)
+        return cls(q, s)
+
+    def __call__(self, x_q: torch.Tensor, x_scale: torch.Tensor, residual: torch.Tensor | None = None, out=None):
+        if x_q.is_cuda:
+            return ops.fp8_gemm(x_q, x_scale, self.q, self.scale, residual=residual, out=out)
+        return ref.fp8_gemm(x_q, x_scale, self.q, self.scale, residual=residual)
+
+    def dequant(self) -> torch.Tensor:
+        return ref.dequant_block(self.q, self.scale)
+
+
+@dataclass
+class LlamaLayer:
+    attn_norm: torch.Tensor
+    qkv: Fp8Linear
+    o_proj: Fp8Linear
+    mlp_norm: torch.Tensor
+    gate_up: Fp8Linear
+    down: Fp8Linear
+
+
+@dataclass
+class LlamaWeights:
+    embed: torch.Tensor  # [V, H] bf16
+    layers: list[LlamaLayer]
+    final_norm: torch.Tensor
+    lm_head: Fp8Linear
+    tp_rank: int = 0
+    tp_size: int = 1
+
+    @classmethod
+    def random_init(cls, cfg: LlamaConfig, device, seed: int = 0, std: float = 0.02, tp_rank: int = 0,
+                    tp_size: int = 1) -> "LlamaWeights":
+        """N(0, std) weights, quantized layer by layer on ``device``.  Every rank draws the full matrix from the
+        same seed and keeps its shard, so TP=n and TP=1 hold the same model."""
+        dev = torch.device(device)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed)
+        h, i, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+        hq, hk = cfg.num_heads, cfg.num_kv_heads
+
+        def rnd(rows, cols):
+            return torch.randn((rows, cols), generator=gen, device=dev, dtype=torch.float32).mul_(std).to(torch.bfloat16)
+
+        def rows_shard(w, parts):  # split output rows into tp_size equal shards, keep ours
+            return w.reshape(tp_size, parts // tp_size, -1)[tp_rank] if tp_size > 1 else w
+
+        layers = []
+        for _ in range(cfg.num_layers):
+            wq, wk, wv = rnd(hq * d, h), rnd(hk * d, h), rnd(hk * d, h)
+            wo = rnd(h, hq * d)
+            wg, wu, wd = rnd(i, h), rnd(i, h), rnd(h, i)
+            if tp_size > 1:
+                wq, wk, wv = rows_shard(wq, hq * d), rows_shard(wk, hk * d), rows_shard(wv, hk * d)
+                wg, wu = rows_shard(wg, i), rows_shard(wu, i)
+                wo = wo.reshape(h, tp_size, hq * d // tp_size)[:, tp_rank].contiguous()
+                wd = wd.reshape(h, tp_size, i // tp_size)[:, tp_rank].contiguous()
+            layers.append(LlamaLayer(
+                attn_norm=torch.ones(h, dtype=torch.bfloat16, device=dev),
+                qkv=Fp8Linear.from_float(torch.cat([wq, wk, wv], 0)),
+                o_proj=Fp8Linear.from_float(wo),
+                mlp_norm=torch.ones(h, dtype=torch.bfloat16, device=dev),
+                gate_up=Fp8Linear.from_float(torch.cat([wg, wu], 0)),
+                down=Fp8Linear.from_float(wd),
+            ))
+            del wq, wk, wv, wo, wg, wu, wd
+        embed = rnd(cfg.vocab_size, h)
+        head = rnd(cfg.vocab_size, h)
+        if tp_size > 1:
+            head = rows_shard(head, cfg.vocab_size)
+        return cls(embed, layers, torch.ones(h, dtype=torch.bfloat16, device=dev), Fp8Linear.from_float(head),
+                   tp_rank, tp_size)
+
+    def nbytes(self) -> int:
+        total = self.embed.numel() * 2 + self.lm_head.q.numel()
+        for l in self.layers:
+            for lin in (l.qkv, l.o_proj, l.gate_up, l.down):
+                total += lin.q.numel() + lin.scale.numel() * 4
+        return total
+
+
+@dataclass
+class StepBuffers:
+    """Device tensors describing one forward pass."""
+
+    input_ids: torch.Tensor  # [T] int32
+    positions: torch.Tensor  # [T] int32
+    slots: torch.Tensor  # [T] int32 physical KV slot per token (-1 = do not write)
+    # decode: one row per sequence
+    block_table: torch.Tensor | None = None  # [B, max_pages] int32
+    seq_lens: torch.Tensor | None = None  # [B] int32, length *after* this step's token
+    # prefill: cumulative sequence boundaries (host list) of the packed chunk
+    cu_seqlens: list[int] = field(default_factory=list)
+    q_len: int = 1
+
+
+class LlamaModel:
+    """Stateless forward over :class:`LlamaWeights`; KV state lives in a :class:`PagedKVCache`."""
+
+    def __init__(self, cfg: LlamaConfig, weights: LlamaWeights, collective=None) -> None:
+        self.cfg, self.w = cfg, weights
+        self.tp = weights.tp_size
+        self.collective = collective  # tensor-parallel reducer (None at TP=1)
+        self.hq = cfg.num_heads // self.tp
+        self.hk = max(1, cfg.num_kv_heads // self.tp)
+        self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.attn_splits = 1
+
+    # -- primitive dispatch -------------------------------------------------------------------------------------
+    def _norm_quant(self, x, w):
+        if x.is_cuda:
+            q, s, _, _ = ops.rmsnorm_quant(x, w, self.cfg.rms_eps)
+            return q, s
+        q, s, _, _ = ref.rmsnorm_quant(x, w, self.cfg.rms_eps)
+        return q, s
+
+    def _quant(self, x):
+        return ops.quant_rows(x) if x.is_cuda else ref.quant_rows(x)
+
+    def _silu_quant(self, gu):
+        return ops.silu_mul_quant(gu) if gu.is_cuda else ref.silu_mul_quant(gu)
+
+    def _row_parallel(self, lin: Fp8Linear, xq, xs, h):
+        """Input-sharded projection + residual.  At TP>1 every rank adds its partial; rank 0 carries the residual."""
+        if self.tp == 1:
+            return lin(xq, xs, residual=h, out=h if h.is_cuda else None)
+        return self.collective.row_parallel_linear(lin, xq, xs, h)
+
+    # -- attention ----------------------------------------------------------------------------------------------
+    def _attention(self, qkv, kv, step: StepBuffers, prefill: bool):
+        cfg = self.cfg
+        d = cfg.head_dim
+        t = qkv.shape[0]
+        if qkv.is_cuda:
+            q = ops.rope_kv_write(qkv, step.positions, step.slots, kv, n_q=self.hq, n_kv=self.hk, head_dim=d,
+                                  theta=cfg.rope_theta)
+        else:
+            q3 = qkv.view(t, self.hq + 2 * self.hk, d)
+            q = ref.rope(q3[:, : self.hq], step.positions, cfg.rope_theta)
+            k = ref.rope(q3[:, self.hq : self.hq + self.hk], step.positions, cfg.rope_theta)
+            ref.write_kv(kv, k, q3[:, self.hq + self.hk :], step.slots)
+        if not prefill:
+            if qkv.is_cuda:
+                o = ops.paged_attn_decode(q, kv, step.block_table, step.seq_lens, sm_scale=self.sm_scale,
+                                          splits=self.attn_splits, q_len=step.q_len)
+            else:
+                o = ref.paged_attn_decode(q, kv, step.block_table, step.seq_lens, self.sm_scale, step.q_len)
+            return o.reshape(t, self.hq * d)
+        # prefill over a packed chunk: each sequence attends causally to itself, through the same FP8 rounding
+        # of K/V that later decode steps will read back from the pages
+        if qkv.is_cuda:
+            return ops.attn_prefill(q, kv, step, n_kv=self.hk, sm_scale=self.sm_scale).reshape(t, self.hq * d)
+        outs = []
+        for i in range(len(step.cu_seqlens) - 1):
+            a, b = step.cu_seqlens[i], step.cu_seqlens[i + 1]
+            sl = step.slots[a:b].long()
+            pages, off = sl // kv.page_size, sl % kv.page_size
+            kk = kv.k[pages, :, off].float() * kv.k_scale[pages, :, off][..., None]
+            vv = kv.v[pages, :, off].float() * kv.v_scale[pages, :, off][..., None]
+            outs.append(ref.attention(q[a:b], kk, vv, self.sm_scale, causal_offset=0))
+        return torch.cat(outs, 0).reshape(t, self.hq * d)
+
+    # -- forward ------------------------------------------------------------------------------------------------
+    def forward(self, step: StepBuffers, cache, *, prefill: bool, logits_rows: torch.Tensor | None = None):
+        """Returns bf16 logits ``[rows, vocab]`` (all tokens, or ``logits_rows`` of them)."""
+        w = self.w
+        ids = step.input_ids
+        h = ops.embed(ids, w.embed) if w.embed.is_cuda else w.embed[ids.long()].clone()
+        for li, layer in enumerate(w.layers):
+            kv = cache.layer(li)
+            xq, xs = self._norm_quant(h, layer.attn_norm)
+            qkv = layer.qkv(xq, xs)
+            attn = self._attention(qkv, kv, step, prefill)
+            aq, a_s = self._quant(attn)
+            h = self._row_parallel(layer.o_proj, aq, a_s, h)
+            xq, xs = self._norm_quant(h, layer.mlp_norm)
+            gu = layer.gate_up(xq, xs)
+            hq_, hs = self._silu_quant(gu)
+            h = self._row_parallel(layer.down, hq_, hs, h)
+        if logits_rows is not None:
+            h = h[logits_rows.long()] if not h.is_cuda else h.index_select(0, logits_rows.long())
+        xq, xs = self._norm_quant(h, w.final_norm)
+        logits = w.lm_head(xq, xs)
+        if self.tp > 1:
+            logits = self.collective.gather_columns(logits)
+        return logits

@@ -1,0 +1,124 @@
+"""Per-kernel timings at the Llama-8B shapes: ``python -m mfq_b200.ops.bench_kernels [--json out.json]``.
+
+Each kernel is timed in isolation with CUDA events over ``reps`` launches after a warm-up, rotating through
+enough independent weight copies that every launch reads its weights from HBM (more than 4x the 126 MB L2),
+and reported against the measured roofline denominators (copy bandwidth / cuBLAS bf16 rate) when
+``MEASURED_PEAKS.json`` is present in the working directory.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+from . import kernels as K
+from . import reference as ref
+from ..engine.kv_cache import PagedKVCache
+
+L2_BYTES = 126 << 20
+
+
+def time_ms(fn, reps: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn(0)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(reps):
+        fn(i)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def peaks() -> dict:
+    if os.path.exists("MEASURED_PEAKS.json"):
+        p = json.load(open("MEASURED_PEAKS.json"))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops"], "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "kind": "fallback"}
+
+
+def bench_gemm(m: int, n: int, k: int, reps: int, splits=None, tile=None) -> dict:
+    copies = max(1, min(16, math.ceil(4 * L2_BYTES / (n * k))))
+    w = [torch.randint(-100, 100, (n, k), device="cuda", dtype=torch.int8).view(torch.float8_e4m3fn) for _ in range(copies)]
+    ws = torch.rand((math.ceil(n / 128), k // 128), device="cuda") * 0.01 + 0.001
+    x = torch.randint(-100, 100, (m, k), device="cuda", dtype=torch.int8).view(torch.float8_e4m3fn)
+    xs = torch.rand(m, device="cuda") * 0.01 + 0.001
+    out = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+    ms = time_ms(lambda i: K.fp8_gemm(x, xs, w[i % copies], ws, out=out, splits=splits, token_tile=tile), reps)
+    byt = n * k + m * k + 2 * m * n
+    return {"kernel": "fp8_gemm", "m": m, "n": n, "k": k, "us": ms * 1e3, "gbs": byt / ms / 1e6,
+            "tflops": 2 * m * n * k / ms / 1e9, "splits": splits if splits else K.pick_splits(m, n, k)}
+
+
+def bench_attn(batch: int, ctx: int, hq: int, hk: int, d: int, splits: int, reps: int) -> dict:
+    pages_per = math.ceil(ctx / 16)
+    layers = max(1, math.ceil(4 * L2_BYTES / (batch * ctx * hk * d * 2)))
+    cache = PagedKVCache(layers=layers, kv_heads=hk, head_dim=d, num_pages=batch * pages_per + 1, max_seqs=batch,
+                         max_pages_per_seq=pages_per, device="cuda")
+    cache.k.view(torch.int8).random_(-100, 100)
+    cache.v.view(torch.int8).random_(-100, 100)
+    cache.k_scale.fill_(0.01)
+    cache.v_scale.fill_(0.01)
+    for b in range(batch):
+        cache.assign(b, b, ctx)
+    q = torch.randn((batch, hq, d), device="cuda").to(torch.bfloat16)
+    sl = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    kvs = [cache.layer(i) for i in range(layers)]
+    ms = time_ms(lambda i: K.paged_attn_decode(q, kvs[i % layers], cache.block_table, sl, sm_scale=0.088, splits=splits, out=out), reps)
+    byt = batch * ctx * hk * (2 * d + 8)
+    return {"kernel": "paged_attn_decode", "batch": batch, "ctx": ctx, "splits": splits, "us": ms * 1e3, "gbs": byt / ms / 1e6}
+
+
+def bench_small(m: int, h: int, i: int, reps: int) -> list[dict]:
+    x = torch.randn((m, h), device="cuda").to(torch.bfloat16)
+    w = torch.ones(h, device="cuda", dtype=torch.bfloat16)
+    gu = torch.randn((m, 2 * i), device="cuda").to(torch.bfloat16)
+    out = []
+    ms = time_ms(lambda _: K.rmsnorm_quant(x, w, 1e-5), reps)
+    out.append({"kernel": "rmsnorm_quant", "m": m, "h": h, "us": ms * 1e3, "gbs": m * h * 3 / ms / 1e6})
+    ms = time_ms(lambda _: K.quant_rows(x), reps)
+    out.append({"kernel": "quant_rows", "m": m, "h": h, "us": ms * 1e3, "gbs": m * h * 3 / ms / 1e6})
+    ms = time_ms(lambda _: K.silu_mul_quant(gu), reps)
+    out.append({"kernel": "silu_mul_quant", "m": m, "i": i, "us": ms * 1e3, "gbs": m * i * 5 / ms / 1e6})
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--json", default="")
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args()
+    pk = peaks()
+    rows = []
+    shapes = [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336), ("lm_head", 128256, 4096)]
+    for m in ((1, 64) if args.quick else (1, 16, 64, 512, 4096)):
+        for name, n, k in shapes:
+            if name == "lm_head" and m > 64:
+                continue
+            r = bench_gemm(m, n, k, args.reps)
+            r["name"] = name
+            rows.append(r)
+    for batch, ctx in ((1, 4096), (64, 4096)):
+        for splits in (1, 4, 16):
+            rows.append(bench_attn(batch, ctx, 32, 8, 128, splits, args.reps))
+    for m in (1, 64, 4096):
+        rows += bench_small(m, 4096, 14336, args.reps)
+    for r in rows:
+        if "gbs" in r:
+            r["hbm_frac"] = r["gbs"] / pk["hbm_gbs"]
+        if "tflops" in r:
+            r["tensor_frac_of_bf16"] = r["tflops"] / pk["tflops"]
+        print(json.dumps({k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()}))
+    if args.json:
+        json.dump({"peaks": pk, "rows": rows}, open(args.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

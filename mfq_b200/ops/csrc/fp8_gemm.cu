@@ -1,0 +1,275 @@
+// Block-scaled FP8 GEMM on tcgen05 tensor cores:  out[M, N] = X[M, K] * W[N, K]^T
+//
+//   W : E4M3, one fp32 multiplier per 128x128 block   (w_scale[ceil(N/128), K/128])
+//   X : E4M3, one fp32 multiplier per token            (x_scale[M])
+//   out : bf16 (optionally + bf16 residual)
+//
+// The weight tile is the UMMA "A" operand (M = 128 output features) and the token tile the "B"
+// operand (N = BT tokens), so the same kernel streams weights at decode batch sizes (BT = 16..64)
+// and runs square tiles at prefill (BT = 128).  Because the weight multiplier changes every 128 inputs,
+// each 128-wide K block is multiplied into a fresh TMEM accumulator (NACC of them rotate) and
+// the epilogue warps fold it, scaled, into fp32 registers while the tensor core already works on
+// the next block.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue
+// (TMEM lane quarter = warp % 4).  Split-K (gridDim.z > 1) writes fp32 partials to a scratch
+// buffer; the last CTA to arrive at a tile's counter reduces them in split order (deterministic)
+// and resets the counter for the next launch.
+//
+// The reference multiplies block-FP8 weights by decoding them to fp16 for wmma or cuBLAS
+// (mfq/kernels/cuda/fp8_sq.cu:42-56,564-592); there the FP8 tensor-core path does not exist.
+#include "common.cuh"
+
+namespace mfq {
+
+constexpr int kTileN = 128;     // weight rows (output features) per CTA
+constexpr int kBlockK = 128;    // fp8 elements per K block = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;
+
+template <int BT>
+struct GemmCfg {
+  static constexpr int kStages = BT >= 128 ? 6 : 8;
+  static constexpr int kAcc = 4;
+  static constexpr int kTmemCols = (kAcc * BT) < 32 ? 32 : kAcc * BT;
+  static constexpr int kStageBytes = kTileN * kBlockK + BT * kBlockK;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+struct GemmParams {
+  const float* w_scale;
+  const float* x_scale;
+  __nv_bfloat16* out;
+  const __nv_bfloat16* residual;
+  float* ws;        // split-K partials: [splits][t_tiles][n_tiles][BT][128]
+  int* counters;    // [t_tiles * n_tiles], zero on entry, zero on exit
+  int* status;
+  int M, N, K;
+  int kb_per_split;
+};
+
+template <int BT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                const GemmParams p) {
+  using Cfg = GemmCfg<BT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::kStages;
+  uint64_t* acc_full = bars + 2 * Cfg::kStages;
+  uint64_t* acc_empty = acc_full + Cfg::kAcc;
+  uint64_t* epi_bar = acc_empty + Cfg::kAcc;  // two one-shot barriers among the epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x, t_tile = blockIdx.y, split = blockIdx.z;
+  const int n0 = n_tile * kTileN, t0 = t_tile * BT;
+  const int kb_total = p.K / kBlockK;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(kb_total, kb0 + p.kb_per_split);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < Cfg::kAcc; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    mbar_init(&epi_bar[0], 4);
+    mbar_init(&epi_bar[1], 4);
+    *abort_flag = 0;
+    *last_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_w);
+      tma_prefetch_desc(&tmap_x);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % Cfg::kStages;
+        if (!mbar_wait(&empty[s], ((i / Cfg::kStages) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutProducer)) break;
+        uint8_t* a = tiles + s * Cfg::kStageBytes;
+        uint8_t* b = a + kTileN * kBlockK;
+        mbar_expect_tx(&full[s], Cfg::kStageBytes);
+        tma_load_2d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0);
+        tma_load_2d(b, &tmap_x, &full[s], (kb0 + i) * kBlockK, t0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(kTileN, BT, 0, 0);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % Cfg::kStages;
+        const int buf = i % Cfg::kAcc;
+        if (!mbar_wait(&acc_empty[buf], ((i / Cfg::kAcc) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutMma)) break;
+        if (!mbar_wait(&full[s], (i / Cfg::kStages) & 1, abort_flag, p.status, kStatusTimeoutMma)) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles + s * Cfg::kStageBytes);
+        const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+        const uint64_t b_desc = umma_desc_k_sw128(a_addr + kTileN * kBlockK);
+        const uint32_t d = tmem_base + buf * BT;
+#pragma unroll
+        for (int k = 0; k < kBlockK / 32; ++k) {
+          // advancing 32 bytes along K inside the swizzle row = +2 in the 16-byte address field
+          umma_f8f6f4(d, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2), idesc, k > 0 ? 1u : 0u);
+        }
+        tc_commit(&empty[s]);      // smem stage reusable once these MMAs have read it
+        tc_commit(&acc_full[buf]); // accumulator block complete
+      }
+    }
+  } else {
+    // ----- epilogue warps: thread owns output feature n0 + q*32 + lane, all BT tokens -----
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int n = n0 + row;
+    float acc[BT];
+#pragma unroll
+    for (int t = 0; t < BT; ++t) acc[t] = 0.f;
+    const float* wsc = p.w_scale + size_t(n_tile) * kb_total;
+    bool ok = true;
+    for (int i = 0; i < nkb; ++i) {
+      const int buf = i % Cfg::kAcc;
+      ok = mbar_wait(&acc_full[buf], (i / Cfg::kAcc) & 1, abort_flag, p.status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const float s = __ldg(wsc + kb0 + i);
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BT;
+      if constexpr (BT >= 32) {
+#pragma unroll
+        for (int c = 0; c < BT; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(__uint_as_float(r[j]), s, acc[c + j]);
+        }
+      } else {
+        uint32_t r[16];
+        tmem_ld_32x16(taddr, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = fmaf(__uint_as_float(r[j]), s, acc[j]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+    if (ok) {
+      const int tl = min(BT, p.M - t0);
+      if (gridDim.z == 1) {
+        if (n < p.N) {
+#pragma unroll
+          for (int t = 0; t < BT; ++t) {
+            if (t < tl) {
+              float v = acc[t] * __ldg(p.x_scale + t0 + t);
+              const size_t o = size_t(t0 + t) * p.N + n;
+              if (p.residual) v += __bfloat162float(p.residual[o]);
+              p.out[o] = __float2bfloat16(v);
+            }
+          }
+        }
+      } else {
+        const int tiles_nt = gridDim.x * gridDim.y;
+        const int tile_id = t_tile * gridDim.x + n_tile;
+        float* mine = p.ws + (size_t(split) * tiles_nt + tile_id) * (BT * kTileN);
+#pragma unroll
+        for (int t = 0; t < BT; ++t) mine[t * kTileN + row] = acc[t];
+        __threadfence();
+        // bounded rendezvous of the four epilogue warps (a plain bar.sync could not time out)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&epi_bar[0]);
+        bool met = mbar_wait(&epi_bar[0], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
+        if (met && threadIdx.x == 64) {
+          const int prev = atomicAdd(p.counters + tile_id, 1);
+          *last_flag = (prev == int(gridDim.z) - 1);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&epi_bar[1]);
+        met = met && mbar_wait(&epi_bar[1], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
+        if (met && *last_flag) {
+          __threadfence();
+          if (n < p.N) {
+#pragma unroll 4
+            for (int t = 0; t < BT; ++t) {
+              if (t < tl) {
+                float v = 0.f;
+                for (int z = 0; z < int(gridDim.z); ++z)
+                  v += __ldcg(p.ws + (size_t(z) * tiles_nt + tile_id) * (BT * kTileN) + t * kTileN + row);
+                v *= __ldg(p.x_scale + t0 + t);
+                const size_t o = size_t(t0 + t) * p.N + n;
+                if (p.residual) v += __bfloat162float(p.residual[o]);
+                p.out[o] = __float2bfloat16(v);
+              }
+            }
+          }
+          if (threadIdx.x == 64) p.counters[tile_id] = 0;
+        }
+      }
+    }
+  }
+
+  // ----- teardown: every thread arrives here, also after an aborted wait -----
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int BT>
+static int launch_gemm(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
+                       const void* residual, float* ws, size_t ws_bytes, int* counters, int counters_len, int* status,
+                       int M, int N, int K, int splits, cudaStream_t stream) {
+  using Cfg = GemmCfg<BT>;
+  CUtensorMap tw, tx;
+  if (make_tmap_2d(&tw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kTileN, kBlockK)) return -2;
+  if (make_tmap_2d(&tx, x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BT, kBlockK)) return -3;
+  const int n_tiles = (N + kTileN - 1) / kTileN, t_tiles = (M + BT - 1) / BT;
+  const int kb_total = K / kBlockK;
+  if (splits < 1) splits = 1;
+  if (splits > kb_total) splits = kb_total;
+  int kb_per = (kb_total + splits - 1) / splits;
+  splits = (kb_total + kb_per - 1) / kb_per;
+  if (splits > 1) {
+    if (size_t(splits) * n_tiles * t_tiles * BT * kTileN * sizeof(float) > ws_bytes) return -4;
+    if (n_tiles * t_tiles > counters_len) return -5;
+  }
+  GemmParams p{w_scale, x_scale, static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(residual),
+               ws, counters, status, M, N, K, kb_per};
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(fp8_gemm_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
+        cudaSuccess)
+      return -6;
+    attr_set = true;
+  }
+  fp8_gemm_kernel<BT><<<dim3(n_tiles, t_tiles, splits), kGemmThreads, Cfg::kSmemBytes, stream>>>(tw, tx, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+}  // namespace mfq
+
+// C ABI.  x: [M, K] E4M3 row-major, w: [N, K] E4M3 row-major, K % 128 == 0, 16-byte aligned bases.
+// token_tile in {16, 32, 64, 128}.  Returns 0 on success (launch queued), negative on a host-side error.
+extern "C" int mfq_fp8_gemm(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
+                            const void* residual, float* ws, size_t ws_bytes, int* counters, int counters_len,
+                            int* status, int M, int N, int K, int token_tile, int splits, cudaStream_t stream) {
+  if (K % 128 != 0 || M <= 0 || N <= 0) return -1;
+  switch (token_tile) {
+    case 16: return mfq::launch_gemm<16>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream);
+    case 32: return mfq::launch_gemm<32>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream);
+    case 64: return mfq::launch_gemm<64>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream);
+    case 128: return mfq::launch_gemm<128>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream);
+    default: return -1;
+  }
+}

@@ -1,0 +1,584 @@
+// Memory-bound building blocks of the decode/prefill step: fused (residual +) RMSNorm + FP8 row
+// quantization, SwiGLU + FP8 quantization, RoPE + paged FP8 KV write, paged GQA decode attention with
+// split-KV, greedy arg-max, embedding gather and the graph-resident step bookkeeping.
+//
+// Reference counterparts (all scalar fp16/fp32 kernels without an FP8 path): norm.cu / acc.cu
+// (acc_rms_norm_*), activation.cu, qk_rope_kv.cu, paged_kv.cu (paged_attention_decode_*_kernel, split +
+// reduce), sampling.cu (greedy arg-max), embedding.cu, acc.cu:465 (decode_graph_commit_kernel).
+#include "common.cuh"
+
+#include <cfloat>
+
+namespace mfq {
+
+constexpr float kE4M3Max = 448.f;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide reductions over <= 1024 threads; `red` is 33 floats of shared memory.
+template <bool kMax>
+__device__ __forceinline__ float block_reduce(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = kMax ? warp_max(v) : warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float x = lane < nw ? red[lane] : (kMax ? -FLT_MAX : 0.f);
+    x = kMax ? warp_max(x) : warp_sum(x);
+    if (lane == 0) red[32] = x;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ float from_e4m3(uint8_t c) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(c, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// ---------------------------------------------------------------------------------------------
+// (x [+ residual]) -> RMSNorm * w -> per-row FP8.  One CTA per row.  Values stay in registers
+// (up to 8 x 8 elements per thread => H <= 8 * 8 * blockDim), so the row is read once.
+// ---------------------------------------------------------------------------------------------
+constexpr int kNormVecs = 8;
+
+__global__ void rmsnorm_quant_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                                     __nv_bfloat16* __restrict__ residual_out, const __nv_bfloat16* __restrict__ w,
+                                     uint8_t* __restrict__ q_out, float* __restrict__ scale_out,
+                                     __nv_bfloat16* __restrict__ y_out, int H, float eps) {
+  __shared__ float red[33];
+  const size_t row = blockIdx.x;
+  const int nvec = H / 8;
+  float v[kNormVecs][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormVecs; ++i) {
+    const int vi = threadIdx.x + i * blockDim.x;
+    if (vi < nvec) {
+      uint4 a = *reinterpret_cast<const uint4*>(x + row * H + vi * 8);
+      const __nv_bfloat16* ab = reinterpret_cast<const __nv_bfloat16*>(&a);
+      if (residual) {
+        uint4 r = *reinterpret_cast<const uint4*>(residual + row * H + vi * 8);
+        const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&r);
+        uint4 o;
+        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ob[j] = __float2bfloat16(__bfloat162float(ab[j]) + __bfloat162float(rb[j]));
+          v[i][j] = __bfloat162float(ob[j]);
+        }
+        *reinterpret_cast<uint4*>(residual_out + row * H + vi * 8) = o;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(ab[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  const float rstd = rsqrtf(block_reduce<false>(ss, red) / float(H) + eps);
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormVecs; ++i) {
+    const int vi = threadIdx.x + i * blockDim.x;
+    if (vi < nvec) {
+      uint4 ww = *reinterpret_cast<const uint4*>(w + vi * 8);
+      const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(&ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // round through bf16 like an unfused norm would, so fused and unfused paths agree bit for bit
+        v[i][j] = __bfloat162float(__float2bfloat16(v[i][j] * rstd * __bfloat162float(wb[j])));
+        amax = fmaxf(amax, fabsf(v[i][j]));
+      }
+    }
+  }
+  amax = block_reduce<true>(amax, red);
+  const float scale = fmaxf(amax, 1e-12f) / kE4M3Max;
+  const float inv = 1.f / scale;
+  if (threadIdx.x == 0 && scale_out) scale_out[row] = scale;
+#pragma unroll
+  for (int i = 0; i < kNormVecs; ++i) {
+    const int vi = threadIdx.x + i * blockDim.x;
+    if (vi < nvec) {
+      if (q_out) {
+        uint2 o;
+        uint8_t* ob = reinterpret_cast<uint8_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ob[j] = to_e4m3(v[i][j] * inv);
+        *reinterpret_cast<uint2*>(q_out + row * H + vi * 8) = o;
+      }
+      if (y_out) {
+        uint4 o;
+        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ob[j] = __float2bfloat16(v[i][j]);
+        *reinterpret_cast<uint4*>(y_out + row * H + vi * 8) = o;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Row quantization.  mode 0: y = x[row, :K]; mode 1 (SwiGLU): y = silu(x[row, :K]) * x[row, K:2K].
+// Two passes over the (cache-resident) row: amax, then encode.
+// ---------------------------------------------------------------------------------------------
+template <int kMode>
+__global__ void quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q_out,
+                                  float* __restrict__ scale_out, int K, int in_stride) {
+  __shared__ float red[33];
+  const size_t row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * in_stride;
+  const int nvec = K / 8;
+  auto value = [&](int vi, float (&y)[8]) {
+    uint4 a = *reinterpret_cast<const uint4*>(xr + vi * 8);
+    const __nv_bfloat16* ab = reinterpret_cast<const __nv_bfloat16*>(&a);
+    if (kMode == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = __bfloat162float(ab[j]);
+    } else {
+      uint4 b = *reinterpret_cast<const uint4*>(xr + K + vi * 8);
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float g = __bfloat162float(ab[j]);
+        const float h = g / (1.f + __expf(-g)) * __bfloat162float(bb[j]);
+        y[j] = __bfloat162float(__float2bfloat16(h));
+      }
+    }
+  };
+  float amax = 0.f;
+  for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+    float y[8];
+    value(vi, y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
+  }
+  amax = block_reduce<true>(amax, red);
+  const float scale = fmaxf(amax, 1e-12f) / kE4M3Max;
+  const float inv = 1.f / scale;
+  if (threadIdx.x == 0) scale_out[row] = scale;
+  for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+    float y[8];
+    value(vi, y);
+    uint2 o;
+    uint8_t* ob = reinterpret_cast<uint8_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ob[j] = to_e4m3(y[j] * inv);
+    *reinterpret_cast<uint2*>(q_out + row * K + vi * 8) = o;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RoPE (rotate-half pairing i <-> i + rot/2 over the first `rot` dims) on Q and K, then K/V -> FP8 pages.
+// qkv: [T, (Hq + 2 Hk) * D] bf16.  One warp per (token, head).  Cache page layout [page][Hk][page_size][D]
+// with one fp32 multiplier per (page, head, slot).  slots[t] = physical page * page_size + offset (< 0: skip).
+// ---------------------------------------------------------------------------------------------
+template <int D>
+__global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
+                                     uint8_t* __restrict__ k_cache, uint8_t* __restrict__ v_cache,
+                                     float* __restrict__ k_scale, float* __restrict__ v_scale, int T, int Hq, int Hk,
+                                     int page_size, int rot, float log2_theta) {
+  constexpr int EPL = D / 32;  // elements per lane
+  const int warps_per_block = blockDim.x >> 5;
+  const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = Hq + 2 * Hk;
+  if (gw >= T * heads) return;
+  const int t = gw / heads, h = gw % heads;
+  const __nv_bfloat16* src = qkv + size_t(t) * heads * D + size_t(h) * D;
+  // lane owns EPL/2 rotation pairs: indices j and j + rot/2 for j = lane*EPL/2 .. (only when below rot/2),
+  // plus pass-through of non-rotated dims; simplest uniform scheme: lane handles dims
+  // [lane*EPL/2, lane*EPL/2 + EPL/2) of each half of the head vector.
+  constexpr int HP = EPL / 2;
+  float lo[HP], hi[HP];
+#pragma unroll
+  for (int j = 0; j < HP; ++j) {
+    lo[j] = __bfloat162float(src[lane * HP + j]);
+    hi[j] = __bfloat162float(src[D / 2 + lane * HP + j]);
+  }
+  const bool is_v = h >= Hq + Hk;
+  if (!is_v) {
+    const float pos = float(positions[t]);
+    const int half_rot = rot / 2;
+    if (rot == D) {
+#pragma unroll
+      for (int j = 0; j < HP; ++j) {
+        const int idx = lane * HP + j;
+        const float inv_freq = exp2f(-log2_theta * (2.f * idx) / float(rot));
+        float s, c;
+        sincosf(pos * inv_freq, &s, &c);
+        const float a = lo[j], b = hi[j];
+        lo[j] = a * c - b * s;
+        hi[j] = b * c + a * s;
+      }
+    } else {
+      // partial rotary: pairs (i, i + rot/2) live inside the first `rot` dims.  Handle through shared
+      // exchange-free recomputation: each lane re-reads its partner element.
+#pragma unroll
+      for (int j = 0; j < HP; ++j) {
+        for (int part = 0; part < 2; ++part) {
+          const int idx = (part ? D / 2 : 0) + lane * HP + j;
+          if (idx < rot) {
+            const int fi = idx % half_rot;
+            const float inv_freq = exp2f(-log2_theta * (2.f * fi) / float(rot));
+            float s, c;
+            sincosf(pos * inv_freq, &s, &c);
+            const float self = part ? hi[j] : lo[j];
+            const float other = __bfloat162float(src[idx < half_rot ? idx + half_rot : idx - half_rot]);
+            const float r = idx < half_rot ? self * c - other * s : self * c + other * s;
+            if (part) hi[j] = r; else lo[j] = r;
+          }
+        }
+      }
+    }
+  }
+  if (h < Hq) {
+    __nv_bfloat16* dst = q_out + size_t(t) * Hq * D + size_t(h) * D;
+#pragma unroll
+    for (int j = 0; j < HP; ++j) {
+      dst[lane * HP + j] = __float2bfloat16(lo[j]);
+      dst[D / 2 + lane * HP + j] = __float2bfloat16(hi[j]);
+    }
+    return;
+  }
+  const int slot = slots[t];
+  if (slot < 0) return;
+  const int kvh = is_v ? h - Hq - Hk : h - Hq;
+  const int page = slot / page_size, off = slot % page_size;
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < HP; ++j) {
+    lo[j] = __bfloat162float(__float2bfloat16(lo[j]));
+    hi[j] = __bfloat162float(__float2bfloat16(hi[j]));
+    amax = fmaxf(amax, fmaxf(fabsf(lo[j]), fabsf(hi[j])));
+  }
+  amax = warp_max(amax);
+  const float scale = fmaxf(amax, 1e-12f) / kE4M3Max;
+  const float inv = 1.f / scale;
+  const size_t base = ((size_t(page) * Hk + kvh) * page_size + off);
+  uint8_t* dst = (is_v ? v_cache : k_cache) + base * D;
+#pragma unroll
+  for (int j = 0; j < HP; ++j) {
+    dst[lane * HP + j] = to_e4m3(lo[j] * inv);
+    dst[D / 2 + lane * HP + j] = to_e4m3(hi[j] * inv);
+  }
+  if (lane == 0) (is_v ? v_scale : k_scale)[base] = scale;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Paged GQA decode attention over FP8 pages with split-KV.
+// grid (B, Hk, splits), 128 threads.  A warp streams 4 tokens per step: lane = (token slot s = lane / 8,
+// 16-dim segment g = lane % 8) for D = 128 (two passes of 8 segments for D = 256).  Each lane keeps an
+// online-softmax state per query head of the group for its token slot; slots, then warps, then splits are
+// merged with the usual (max, sum, acc) rescaling.
+// ---------------------------------------------------------------------------------------------
+template <int D, int G>
+__global__ void __launch_bounds__(128)
+paged_attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t* __restrict__ k_cache,
+                         const uint8_t* __restrict__ v_cache, const float* __restrict__ k_scale,
+                         const float* __restrict__ v_scale, const int* __restrict__ block_table,
+                         const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out,
+                         float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hk, int page_size,
+                         int max_pages, float sm_scale, int q_len) {
+  constexpr int SEG = D / 16;        // 16-element segments per head vector
+  constexpr int TOK = 32 / SEG;      // tokens per warp step
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = lane / SEG, seg = lane % SEG;
+  // q_len > 1: the last q_len positions of the sequence are queries (speculative verify); query r sees
+  // seq_len - q_len + r + 1 tokens.  blockIdx.x enumerates (sequence, query row).
+  const int seq = b / q_len, qr = b % q_len;
+  const int len = seq_lens[seq] - (q_len - 1 - qr);
+  const int per = ((len + nsplit - 1) / nsplit + TOK * 4 - 1) / (TOK * 4) * (TOK * 4);
+  const int begin = split * per, end = min(len, begin + per);
+
+  float qf[G][16];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const __nv_bfloat16* qp = q + (size_t(b) * Hq + kvh * G + g) * D + seg * 16;
+    uint4 a0 = *reinterpret_cast<const uint4*>(qp), a1 = *reinterpret_cast<const uint4*>(qp + 8);
+    const __nv_bfloat16* p0 = reinterpret_cast<const __nv_bfloat16*>(&a0);
+    const __nv_bfloat16* p1 = reinterpret_cast<const __nv_bfloat16*>(&a1);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { qf[g][j] = __bfloat162float(p0[j]) * sm_scale; qf[g][8 + j] = __bfloat162float(p1[j]) * sm_scale; }
+  }
+  float m[G], l[G], acc[G][16];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -FLT_MAX; l[g] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[g][j] = 0.f;
+  }
+  const int* bt = block_table + size_t(seq) * max_pages;
+  for (int t0 = begin + warp * TOK; t0 < end; t0 += 4 * TOK) {
+    const int t = t0 + slot;
+    const bool valid = t < end;
+    float kf[16], vf[16], ks = 0.f, vs = 0.f;
+    if (valid) {
+      const int page = bt[t / page_size], off = t % page_size;
+      const size_t base = (size_t(page) * Hk + kvh) * page_size + off;
+      uint4 kr = *reinterpret_cast<const uint4*>(k_cache + base * D + seg * 16);
+      uint4 vr = *reinterpret_cast<const uint4*>(v_cache + base * D + seg * 16);
+      ks = k_scale[base]; vs = v_scale[base];
+      const uint8_t* kb = reinterpret_cast<const uint8_t*>(&kr);
+      const uint8_t* vb = reinterpret_cast<const uint8_t*>(&vr);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { kf[j] = from_e4m3(kb[j]); vf[j] = from_e4m3(vb[j]); }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { kf[j] = 0.f; vf[j] = 0.f; }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) s = fmaf(qf[g][j], kf[j], s);
+#pragma unroll
+      for (int o = SEG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      s = valid ? s * ks : -FLT_MAX;
+      const float mn = fmaxf(m[g], s);
+      const float corr = __expf(m[g] - mn);
+      const float pexp = valid ? __expf(s - mn) : 0.f;
+      l[g] = l[g] * corr + pexp;
+      const float pv = pexp * vs;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[g][j] = fmaf(acc[g][j], corr, pv * vf[j]);
+      m[g] = mn;
+    }
+  }
+  // merge the TOK token slots of the warp (lanes with equal seg)
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int o = SEG; o < 32; o <<= 1) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
+      const float lo_ = __shfl_xor_sync(0xffffffffu, l[g], o);
+      const float mn = fmaxf(m[g], mo);
+      const float c0 = __expf(m[g] - mn), c1 = __expf(mo - mn);
+      l[g] = l[g] * c0 + lo_ * c1;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], o);
+        acc[g][j] = acc[g][j] * c0 + ao * c1;
+      }
+      m[g] = mn;
+    }
+  }
+  // merge the 4 warps through shared memory
+  __shared__ float s_acc[4][G][D];
+  __shared__ float s_m[4][G], s_l[4][G];
+  if (slot == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) s_acc[warp][g][seg * 16 + j] = acc[g][j];
+      if (seg == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    float mm = fmaxf(fmaxf(s_m[0][g], s_m[1][g]), fmaxf(s_m[2][g], s_m[3][g]));
+    float ll = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float c = __expf(s_m[w][g] - mm);
+      ll += s_l[w][g] * c;
+      a += s_acc[w][g][d] * c;
+    }
+    const size_t hq = size_t(b) * Hq + kvh * G + g;
+    if (nsplit == 1) {
+      out[hq * D + d] = __float2bfloat16(ll > 0.f ? a / ll : 0.f);
+    } else {
+      part_acc[(hq * nsplit + split) * D + d] = a;
+      if (d == 0) { part_ml[(hq * nsplit + split) * 2] = mm; part_ml[(hq * nsplit + split) * 2 + 1] = ll; }
+    }
+  }
+}
+
+template <int D>
+__global__ void attn_reduce_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                   __nv_bfloat16* __restrict__ out, int nsplit) {
+  const size_t hq = blockIdx.x;
+  const int d = threadIdx.x;
+  float mm = -FLT_MAX;
+  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(hq * nsplit + s) * 2]);
+  float ll = 0.f, a = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float c = __expf(part_ml[(hq * nsplit + s) * 2] - mm);
+    ll += part_ml[(hq * nsplit + s) * 2 + 1] * c;
+    a += part_acc[(hq * nsplit + s) * D + d] * c;
+  }
+  out[hq * D + d] = __float2bfloat16(ll > 0.f ? a / ll : 0.f);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Greedy sampling: arg-max over the vocabulary, one CTA per row (lowest index wins ties).
+// ---------------------------------------------------------------------------------------------
+__global__ void argmax_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, int V, int stride) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const __nv_bfloat16* row = logits + size_t(blockIdx.x) * stride;
+  float best = -FLT_MAX;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = __bfloat162float(row[i]);
+    if (v > best) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -FLT_MAX;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) out[blockIdx.x] = bi;
+  }
+}
+
+__global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                             __nv_bfloat16* __restrict__ out, int H) {
+  const size_t row = blockIdx.x;
+  const size_t src = size_t(ids[row]);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(out + row * H)[i] = reinterpret_cast<const uint4*>(table + src * H)[i];
+}
+
+// Per-step bookkeeping that lives inside the captured decode graph: the sampled token becomes the next
+// input, the position advances, the KV slot of the new token is looked up in the page table.
+__global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __restrict__ input_ids,
+                                      int* __restrict__ positions, int* __restrict__ seq_lens,
+                                      int* __restrict__ slots, const int* __restrict__ block_table, int B,
+                                      int max_pages, int page_size, const int* __restrict__ active) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  if (active && !active[b]) { slots[b] = -1; return; }
+  if (sampled) input_ids[b] = sampled[b];
+  const int pos = seq_lens[b];  // position of the token about to be written
+  positions[b] = pos;
+  const int page = block_table[size_t(b) * max_pages + pos / page_size];
+  slots[b] = page * page_size + pos % page_size;
+  seq_lens[b] = pos + 1;
+}
+
+}  // namespace mfq
+
+using namespace mfq;
+
+extern "C" int mfq_rmsnorm_quant(const void* x, const void* residual, void* residual_out, const void* w, void* q_out,
+                                 float* scale_out, void* y_out, int M, int H, float eps, cudaStream_t stream) {
+  if (H % 8 || M <= 0) return -1;
+  int threads = ((H / 8 + kNormVecs - 1) / kNormVecs + 31) / 32 * 32;
+  if (threads < 32) threads = 32;
+  if (threads > 1024) return -1;
+  rmsnorm_quant_kernel<<<M, threads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<__nv_bfloat16*>(residual_out), static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q_out),
+      scale_out, static_cast<__nv_bfloat16*>(y_out), H, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_quant_rows(const void* x, void* q_out, float* scale_out, int M, int K, int in_stride, int swiglu,
+                              cudaStream_t stream) {
+  if (K % 8 || in_stride % 8 || M <= 0) return -1;
+  const int threads = K >= 4096 ? 512 : 256;
+  if (swiglu)
+    quant_rows_kernel<1><<<M, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out), scale_out, K, in_stride);
+  else
+    quant_rows_kernel<0><<<M, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out), scale_out, K, in_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const int* slots, void* q_out, void* k_cache,
+                                 void* v_cache, float* k_scale, float* v_scale, int T, int Hq, int Hk, int D,
+                                 int page_size, int rot, float theta, cudaStream_t stream) {
+  if (T <= 0) return -1;
+  const int warps = T * (Hq + 2 * Hk);
+  const int blocks = (warps + 7) / 8;
+  const float l2t = log2f(theta);
+#define MFQ_ROPE(DD)                                                                                             \
+  rope_kv_write_kernel<DD><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, slots, \
+      static_cast<__nv_bfloat16*>(q_out), static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache),      \
+      k_scale, v_scale, T, Hq, Hk, page_size, rot, l2t)
+  if (D == 128) MFQ_ROPE(128);
+  else if (D == 64) MFQ_ROPE(64);
+  else if (D == 256) MFQ_ROPE(256);
+  else return -1;
+#undef MFQ_ROPE
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                                     const float* v_scale, const int* block_table, const int* seq_lens, void* out,
+                                     float* part_acc, float* part_ml, int B, int Hq, int Hk, int D, int page_size,
+                                     int max_pages, float sm_scale, int splits, int q_len, cudaStream_t stream) {
+  if (B <= 0 || Hq % Hk) return -1;
+  const int G = Hq / Hk;
+  if (splits < 1) splits = 1;
+  dim3 grid(B, Hk, splits);
+#define MFQ_ATTN(DD, GG)                                                                                          \
+  paged_attn_decode_kernel<DD, GG><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(q),                \
+      static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache), k_scale, v_scale, block_table, \
+      seq_lens, static_cast<__nv_bfloat16*>(out), part_acc, part_ml, Hq, Hk, page_size, max_pages, sm_scale, q_len)
+  if (D == 128 && G == 4) MFQ_ATTN(128, 4);
+  else if (D == 128 && G == 1) MFQ_ATTN(128, 1);
+  else if (D == 128 && G == 2) MFQ_ATTN(128, 2);
+  else if (D == 128 && G == 8) MFQ_ATTN(128, 8);
+  else if (D == 64 && G == 2) MFQ_ATTN(64, 2);
+  else if (D == 64 && G == 1) MFQ_ATTN(64, 1);
+  else if (D == 256 && G == 8) MFQ_ATTN(256, 8);
+  else if (D == 256 && G == 1) MFQ_ATTN(256, 1);
+  else return -1;
+#undef MFQ_ATTN
+  if (cudaGetLastError() != cudaSuccess) return -7;
+  if (splits > 1) {
+    if (D == 128) attn_reduce_kernel<128><<<B * Hq, 128, 0, stream>>>(part_acc, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+    else if (D == 64) attn_reduce_kernel<64><<<B * Hq, 64, 0, stream>>>(part_acc, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+    else attn_reduce_kernel<256><<<B * Hq, 256, 0, stream>>>(part_acc, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_argmax(const void* logits, int* out, int B, int V, int stride, cudaStream_t stream) {
+  argmax_kernel<<<B, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), out, V, stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_embed(const int* ids, const void* table, void* out, int T, int H, cudaStream_t stream) {
+  if (H % 8) return -1;
+  embed_kernel<<<T, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_decode_advance(const int* sampled, int* input_ids, int* positions, int* seq_lens, int* slots,
+                                  const int* block_table, int B, int max_pages, int page_size, const int* active,
+                                  cudaStream_t stream) {
+  decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(sampled, input_ids, positions, seq_lens, slots,
+                                                             block_table, B, max_pages, page_size, active);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}

@@ -1,0 +1,139 @@
+"""Python entry points of the CUDA kernels.  All tensors must live on the current CUDA device and be
+contiguous; outputs may be preallocated (needed under CUDA-graph capture) or are allocated here."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .lib import Workspace, check, lib, ptr, stream_ptr
+
+FP8 = torch.float8_e4m3fn
+
+
+def _token_tile(m: int) -> int:
+    return 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
+
+
+def pick_splits(m: int, n: int, k: int, sms: int = 148) -> int:
+    """Split-K factor that fills the SMs when the (n, token) tile grid alone cannot."""
+    tiles = math.ceil(n / 128) * math.ceil(m / _token_tile(m))
+    kb = k // 128
+    if tiles >= sms or kb <= 1:
+        return 1
+    return max(1, min(kb, 16, sms // tiles))
+
+
+def fp8_gemm(x_q: torch.Tensor, x_scale: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor, *,
+             out: torch.Tensor | None = None, residual: torch.Tensor | None = None, splits: int | None = None,
+             token_tile: int | None = None) -> torch.Tensor:
+    """``out[M, N] = (x_q * x_scale[:, None]) @ (w_q * blockscale(w_scale)).T`` in bf16 (+ residual)."""
+    m, k = x_q.shape
+    n = w_q.shape[0]
+    assert w_q.shape[1] == k and k % 128 == 0 and x_q.dtype == FP8 and w_q.dtype == FP8
+    assert x_scale.dtype == torch.float32 and w_scale.dtype == torch.float32 and x_scale.numel() == m
+    assert w_scale.shape == (math.ceil(n / 128), k // 128) and w_scale.is_contiguous()
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x_q.device)
+    ws = Workspace.get(x_q.device)
+    bt = token_tile or _token_tile(m)
+    sp = pick_splits(m, n, k) if splits is None else splits
+    rc = lib().mfq_fp8_gemm(ptr(w_q), ptr(w_scale), ptr(x_q), ptr(x_scale), ptr(out), ptr(residual), ptr(ws.splitk),
+                            ws.splitk.numel(), ptr(ws.counters), ws.counters.numel(), ptr(ws.status), m, n, k, bt, sp,
+                            stream_ptr())
+    check(rc, "fp8_gemm")
+    return out
+
+
+def rmsnorm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, *, residual: torch.Tensor | None = None,
+                  want_q: bool = True, want_y: bool = False, q_out=None, scale_out=None, y_out=None,
+                  residual_out=None):
+    """(x [+ residual]) -> RMSNorm -> fp8 rows.  Returns ``(q, scale, y, new_residual)`` (unused ones None)."""
+    m, h = x.shape
+    dev = x.device
+    if want_q:
+        q_out = torch.empty((m, h), dtype=FP8, device=dev) if q_out is None else q_out
+        scale_out = torch.empty(m, dtype=torch.float32, device=dev) if scale_out is None else scale_out
+    if want_y and y_out is None:
+        y_out = torch.empty_like(x)
+    if residual is not None and residual_out is None:
+        residual_out = torch.empty_like(x)
+    rc = lib().mfq_rmsnorm_quant(ptr(x), ptr(residual), ptr(residual_out), ptr(weight), ptr(q_out), ptr(scale_out),
+                                 ptr(y_out), m, h, float(eps), stream_ptr())
+    check(rc, "rmsnorm_quant")
+    return q_out, scale_out, y_out, residual_out
+
+
+def quant_rows(x: torch.Tensor, *, q_out=None, scale_out=None):
+    m, k = x.shape
+    q_out = torch.empty((m, k), dtype=FP8, device=x.device) if q_out is None else q_out
+    scale_out = torch.empty(m, dtype=torch.float32, device=x.device) if scale_out is None else scale_out
+    check(lib().mfq_quant_rows(ptr(x), ptr(q_out), ptr(scale_out), m, k, x.stride(0), 0, stream_ptr()), "quant_rows")
+    return q_out, scale_out
+
+
+def silu_mul_quant(gate_up: torch.Tensor, *, q_out=None, scale_out=None):
+    """``[M, 2I]`` (gate | up) -> fp8 ``silu(gate) * up`` rows ``[M, I]`` + per-row multiplier."""
+    m, two_i = gate_up.shape
+    i = two_i // 2
+    q_out = torch.empty((m, i), dtype=FP8, device=gate_up.device) if q_out is None else q_out
+    scale_out = torch.empty(m, dtype=torch.float32, device=gate_up.device) if scale_out is None else scale_out
+    check(lib().mfq_quant_rows(ptr(gate_up), ptr(q_out), ptr(scale_out), m, i, gate_up.stride(0), 1, stream_ptr()),
+          "silu_mul_quant")
+    return q_out, scale_out
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, kv, *, n_q: int, n_kv: int,
+                  head_dim: int, theta: float, rot: int | None = None, q_out=None) -> torch.Tensor:
+    """Rotate Q/K, write K/V of each token into the fp8 page pool ``kv`` (a :class:`PagedKV` layer view)."""
+    t = qkv.shape[0]
+    q_out = torch.empty((t, n_q, head_dim), dtype=torch.bfloat16, device=qkv.device) if q_out is None else q_out
+    rc = lib().mfq_rope_kv_write(ptr(qkv), ptr(positions), ptr(slots), ptr(q_out), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale),
+                                 ptr(kv.v_scale), t, n_q, n_kv, head_dim, kv.page_size, rot or head_dim, float(theta),
+                                 stream_ptr())
+    check(rc, "rope_kv_write")
+    return q_out
+
+
+def paged_attn_decode(q: torch.Tensor, kv, block_table: torch.Tensor, seq_lens: torch.Tensor, *, sm_scale: float,
+                      splits: int = 1, q_len: int = 1, out=None) -> torch.Tensor:
+    """``q [B*q_len, Hq, D]`` against the paged fp8 cache; ``seq_lens`` count the query tokens too."""
+    b, hq, d = q.shape
+    hk = kv.k.shape[1]
+    out = torch.empty_like(q) if out is None else out
+    ws = Workspace.get(q.device)
+    if splits > 1:
+        assert b * hq * splits * d <= ws.attn_acc.numel()
+    rc = lib().mfq_paged_attn_decode(ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale), ptr(block_table),
+                                     ptr(seq_lens), ptr(out), ptr(ws.attn_acc), ptr(ws.attn_ml), b, hq, hk, d,
+                                     kv.page_size, block_table.shape[1], float(sm_scale), splits, q_len, stream_ptr())
+    check(rc, "paged_attn_decode", 2 if splits > 1 else 1)
+    return out
+
+
+def argmax(logits: torch.Tensor, *, out=None) -> torch.Tensor:
+    b, v = logits.shape
+    out = torch.empty(b, dtype=torch.int32, device=logits.device) if out is None else out
+    check(lib().mfq_argmax(ptr(logits), ptr(out), b, v, logits.stride(0), stream_ptr()), "argmax")
+    return out
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, *, out=None) -> torch.Tensor:
+    t, h = ids.numel(), table.shape[1]
+    out = torch.empty((t, h), dtype=torch.bfloat16, device=table.device) if out is None else out
+    check(lib().mfq_embed(ptr(ids), ptr(table), ptr(out), t, h, stream_ptr()), "embed")
+    return out
+
+
+def decode_advance(sampled, input_ids, positions, seq_lens, slots, block_table, page_size: int, active=None) -> None:
+    b = input_ids.numel()
+    check(lib().mfq_decode_advance(ptr(sampled), ptr(input_ids), ptr(positions), ptr(seq_lens), ptr(slots),
+                                   ptr(block_table), b, block_table.shape[1], page_size, ptr(active), stream_ptr()),
+          "decode_advance")
+
+
+def attn_prefill(q: torch.Tensor, kv, step, *, n_kv: int, sm_scale: float) -> torch.Tensor:
+    """Causal self-attention over a packed prefill chunk; K/V are read back from the FP8 pages just written."""
+    from . import prefill_attention
+    return prefill_attention.run(q, kv, step, n_kv=n_kv, sm_scale=sm_scale)

@@ -1,0 +1,29 @@
+"""CPU path of the FP8 Llama: decode must agree with re-running the grown prompt through prefill."""
+
+import torch
+
+from mfq_b200.engine.llm_engine import LLMEngine
+from mfq_b200.models.llama import LlamaConfig, LlamaModel, LlamaWeights
+
+
+def test_decode_consistent_with_prefill():
+    cfg = LlamaConfig.tiny()
+    w = LlamaWeights.random_init(cfg, "cpu", seed=5, std=0.05)
+    prompt = torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(0))
+    eng = LLMEngine(LlamaModel(cfg, w), max_batch=1, max_seq_len=64, device="cpu")
+    gen = eng.generate([prompt], 6).tokens[0]
+    for t in range(1, 6):
+        eng2 = LLMEngine(LlamaModel(cfg, w), max_batch=1, max_seq_len=64, device="cpu")
+        grown = torch.cat([prompt, gen[:t].long()])
+        assert int(eng2.prefill(0, grown)) == int(gen[t]), f"token {t} differs between decode and prefill"
+
+
+def test_kv_pages_are_released():
+    cfg = LlamaConfig.tiny()
+    w = LlamaWeights.random_init(cfg, "cpu", seed=5)
+    eng = LLMEngine(LlamaModel(cfg, w), max_batch=1, max_seq_len=64, device="cpu")
+    free0 = eng.cache.allocator.free_pages
+    eng.prefill(0, torch.arange(20))
+    assert eng.cache.allocator.free_pages < free0
+    eng.prefill(0, torch.arange(5))
+    assert eng.cache.allocator.free_pages == free0 - 1
