@@ -106,7 +106,6 @@ def run_ours(args) -> dict:
     batch, ctx, new = args.batch, args.context, args.steps + args.warmup + 8
     weights = LlamaWeights.random_init(cfg, dev, seed=0, tp_rank=rank, tp_size=world)
     model = LlamaModel(cfg, weights, collective=collective)
-    model.attn_splits = args.attn_splits
     engine = LLMEngine(model, max_batch=batch, max_seq_len=ctx + 2 * new + 16)
     ops.count_launches(True)
 
@@ -213,7 +212,6 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--attn-splits", type=int, default=4)
     ap.add_argument("--tiny", action="store_true", help="tiny model, for checking the harness itself")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -1,7 +1,14 @@
 """Paged KV cache with FP8 pages.
 
-Pool layout per layer (what the CUDA kernels index): ``k, v : [pages, kv_heads, page_size, head_dim]``
-E4M3 and ``k_scale, v_scale : [pages, kv_heads, page_size]`` fp32 (one multiplier per token and head).
+Pool layout per layer (what the CUDA kernels index), chosen so that the decode-attention kernel can fetch a
+page with one bulk copy and read tensor-core fragments with single shared-memory loads:
+
+* ``k : [pages, kv_heads, head_dim/64, page_size, 64]`` E4M3 (64-dim chunks, token-major inside a chunk);
+* ``v : [pages, kv_heads, head_dim, page_size]`` E4M3, transposed, the 16 token slots of a page stored in the
+  order ``0,1,8,9, 2,3,10,11, 4,5,12,13, 6,7,14,15`` (:data:`V_TOKEN_ORDER`);
+* ``k_scale, v_scale : [pages, kv_heads, page_size]`` fp32 (one multiplier per token and head).
+
+:func:`k_logical` / :func:`v_logical` give the plain ``[pages, kv_heads, page_size, head_dim]`` views.
 Pages are 16 tokens, like the reference's paged cache (``cpp_runtime/backends/cuda/models/qwen35/paged_kv.h:25-26``),
 whose pages hold fp16/bf16 or TurboQuant codes; FP8 pages halve the decode-attention traffic.  The host
 side keeps a free list and per-sequence page lists; a sequence's block-table row is written to a device
@@ -15,6 +22,19 @@ from dataclasses import dataclass
 import torch
 
 PAGE_SIZE = 16
+V_TOKEN_ORDER = (0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15)  # slot p holds token V_TOKEN_ORDER[p]
+V_SLOT_OF_TOKEN = tuple(V_TOKEN_ORDER.index(t) for t in range(16))
+
+
+def k_logical(k: torch.Tensor) -> torch.Tensor:
+    """``[..., D/64, page, 64]`` physical -> ``[..., page, D]`` logical (a copy)."""
+    return k.transpose(-3, -2).reshape(*k.shape[:-3], k.shape[-2], k.shape[-3] * k.shape[-1])
+
+
+def v_logical(v: torch.Tensor) -> torch.Tensor:
+    """``[..., D, page(slot order)]`` physical -> ``[..., page, D]`` logical (a copy)."""
+    slots = torch.tensor(V_SLOT_OF_TOKEN, device=v.device)
+    return v.index_select(-1, slots).transpose(-1, -2)
 
 
 @dataclass
@@ -63,11 +83,13 @@ class PagedKVCache:
         self.num_pages = num_pages
         self.max_pages_per_seq = max_pages_per_seq
         dev = torch.device(device)
-        shape = (layers, num_pages, kv_heads, page_size, head_dim)
-        self.k = torch.zeros(shape, dtype=torch.float8_e4m3fn, device=dev)
-        self.v = torch.zeros(shape, dtype=torch.float8_e4m3fn, device=dev)
-        self.k_scale = torch.zeros(shape[:-1], dtype=torch.float32, device=dev)
-        self.v_scale = torch.zeros(shape[:-1], dtype=torch.float32, device=dev)
+        if page_size != 16 or head_dim % 64:
+            raise ValueError("the FP8 page layout needs 16-token pages and a head dim that is a multiple of 64")
+        self.head_dim, self.kv_heads, self.layers = head_dim, kv_heads, layers
+        self.k = torch.zeros((layers, num_pages, kv_heads, head_dim // 64, page_size, 64), dtype=torch.float8_e4m3fn, device=dev)
+        self.v = torch.zeros((layers, num_pages, kv_heads, head_dim, page_size), dtype=torch.float8_e4m3fn, device=dev)
+        self.k_scale = torch.zeros((layers, num_pages, kv_heads, page_size), dtype=torch.float32, device=dev)
+        self.v_scale = torch.zeros((layers, num_pages, kv_heads, page_size), dtype=torch.float32, device=dev)
         self.block_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, device=dev)
         self.allocator = PageAllocator(num_pages)
 
@@ -75,8 +97,7 @@ class PagedKVCache:
         return LayerKV(self.k[i], self.v[i], self.k_scale[i], self.v_scale[i], self.page_size)
 
     def bytes_per_token(self) -> int:
-        layers, _, heads, _, dim = self.k.shape
-        return layers * heads * (2 * dim + 8)
+        return self.layers * self.kv_heads * (2 * self.head_dim + 8)
 
     def assign(self, row: int, seq_id: int, tokens: int) -> None:
         """Make block-table ``row`` cover ``tokens`` tokens of ``seq_id`` (allocating pages as needed)."""

@@ -107,6 +107,9 @@ class LLMEngine:
             self.seq_lens[:b] = pos + 1
         step = StepBuffers(input_ids=self.input_ids[:b], positions=self.positions[:b], slots=self.slots[:b],
                            block_table=self.cache.block_table[:b], seq_lens=self.seq_lens[:b])
+        if dev.type == "cuda":
+            from ..ops.kernels import attn_splits_for
+            self.model.attn_splits = attn_splits_for(b, self.model.hk, self.max_seq_len)
         logits = self.model.forward(step, self.cache, prefill=False)
         if dev.type == "cuda":
             ops.argmax(logits, out=self.sampled[:b])

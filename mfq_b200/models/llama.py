@@ -221,10 +221,7 @@ class LlamaModel:
         outs = []
         for i in range(len(step.cu_seqlens) - 1):
             a, b = step.cu_seqlens[i], step.cu_seqlens[i + 1]
-            sl = step.slots[a:b].long()
-            pages, off = sl // kv.page_size, sl % kv.page_size
-            kk = kv.k[pages, :, off].float() * kv.k_scale[pages, :, off][..., None]
-            vv = kv.v[pages, :, off].float() * kv.v_scale[pages, :, off][..., None]
+            kk, vv = ref.gather_slots(kv, step.slots[a:b])
             outs.append(ref.attention(q[a:b], kk, vv, self.sm_scale, causal_offset=0))
         return torch.cat(outs, 0).reshape(t, self.hq * d)
 

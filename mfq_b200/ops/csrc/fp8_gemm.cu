@@ -199,14 +199,20 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         met = met && mbar_wait(&epi_bar[1], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
         if (met && *last_flag) {
           __threadfence();
+          // Sum the partials in split order (own one included, re-read from scratch) so the result does not
+          // depend on which CTA happened to arrive last.  All BT loads of a split are independent.
+#pragma unroll
+          for (int t = 0; t < BT; ++t) acc[t] = 0.f;
+          for (int z = 0; z < int(gridDim.z); ++z) {
+            const float* part = p.ws + (size_t(z) * tiles_nt + tile_id) * (BT * kTileN) + row;
+#pragma unroll
+            for (int t = 0; t < BT; ++t) acc[t] += __ldcg(part + t * kTileN);
+          }
           if (n < p.N) {
-#pragma unroll 4
+#pragma unroll
             for (int t = 0; t < BT; ++t) {
               if (t < tl) {
-                float v = 0.f;
-                for (int z = 0; z < int(gridDim.z); ++z)
-                  v += __ldcg(p.ws + (size_t(z) * tiles_nt + tile_id) * (BT * kTileN) + t * kTileN + row);
-                v *= __ldg(p.x_scale + t0 + t);
+                float v = acc[t] * __ldg(p.x_scale + t0 + t);
                 const size_t o = size_t(t0 + t) * p.N + n;
                 if (p.residual) v += __bfloat162float(p.residual[o]);
                 p.out[o] = __float2bfloat16(v);

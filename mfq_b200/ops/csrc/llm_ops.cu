@@ -269,160 +269,27 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
   const float scale = fmaxf(amax, 1e-12f) / kE4M3Max;
   const float inv = 1.f / scale;
   const size_t base = ((size_t(page) * Hk + kvh) * page_size + off);
-  uint8_t* dst = (is_v ? v_cache : k_cache) + base * D;
+  const size_t ph = size_t(page) * Hk + kvh;
+  if (!is_v) {
+    // K page: [D/64 chunks][page_size tokens][64 dims]
+    uint8_t* dst = k_cache + ph * (size_t(page_size) * D);
 #pragma unroll
-  for (int j = 0; j < HP; ++j) {
-    dst[lane * HP + j] = to_e4m3(lo[j] * inv);
-    dst[D / 2 + lane * HP + j] = to_e4m3(hi[j] * inv);
+    for (int j = 0; j < HP; ++j) {
+      const int d0 = lane * HP + j, d1 = D / 2 + lane * HP + j;
+      dst[(d0 >> 6) * (page_size * 64) + off * 64 + (d0 & 63)] = to_e4m3(lo[j] * inv);
+      dst[(d1 >> 6) * (page_size * 64) + off * 64 + (d1 & 63)] = to_e4m3(hi[j] * inv);
+    }
+  } else {
+    // V page: [D dims][page_size tokens in the order 0,1,8,9,2,3,10,11,4,5,12,13,6,7,14,15]
+    uint8_t* dst = v_cache + ph * (size_t(page_size) * D);
+    const int pos = 4 * ((off & 7) >> 1) + 2 * (off >> 3) + (off & 1);
+#pragma unroll
+    for (int j = 0; j < HP; ++j) {
+      dst[(lane * HP + j) * page_size + pos] = to_e4m3(lo[j] * inv);
+      dst[(D / 2 + lane * HP + j) * page_size + pos] = to_e4m3(hi[j] * inv);
+    }
   }
   if (lane == 0) (is_v ? v_scale : k_scale)[base] = scale;
-}
-
-// ---------------------------------------------------------------------------------------------
-// Paged GQA decode attention over FP8 pages with split-KV.
-// grid (B, Hk, splits), 128 threads.  A warp streams 4 tokens per step: lane = (token slot s = lane / 8,
-// 16-dim segment g = lane % 8) for D = 128 (two passes of 8 segments for D = 256).  Each lane keeps an
-// online-softmax state per query head of the group for its token slot; slots, then warps, then splits are
-// merged with the usual (max, sum, acc) rescaling.
-// ---------------------------------------------------------------------------------------------
-template <int D, int G>
-__global__ void __launch_bounds__(128)
-paged_attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t* __restrict__ k_cache,
-                         const uint8_t* __restrict__ v_cache, const float* __restrict__ k_scale,
-                         const float* __restrict__ v_scale, const int* __restrict__ block_table,
-                         const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out,
-                         float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hk, int page_size,
-                         int max_pages, float sm_scale, int q_len) {
-  constexpr int SEG = D / 16;        // 16-element segments per head vector
-  constexpr int TOK = 32 / SEG;      // tokens per warp step
-  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int slot = lane / SEG, seg = lane % SEG;
-  // q_len > 1: the last q_len positions of the sequence are queries (speculative verify); query r sees
-  // seq_len - q_len + r + 1 tokens.  blockIdx.x enumerates (sequence, query row).
-  const int seq = b / q_len, qr = b % q_len;
-  const int len = seq_lens[seq] - (q_len - 1 - qr);
-  const int per = ((len + nsplit - 1) / nsplit + TOK * 4 - 1) / (TOK * 4) * (TOK * 4);
-  const int begin = split * per, end = min(len, begin + per);
-
-  float qf[G][16];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = q + (size_t(b) * Hq + kvh * G + g) * D + seg * 16;
-    uint4 a0 = *reinterpret_cast<const uint4*>(qp), a1 = *reinterpret_cast<const uint4*>(qp + 8);
-    const __nv_bfloat16* p0 = reinterpret_cast<const __nv_bfloat16*>(&a0);
-    const __nv_bfloat16* p1 = reinterpret_cast<const __nv_bfloat16*>(&a1);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { qf[g][j] = __bfloat162float(p0[j]) * sm_scale; qf[g][8 + j] = __bfloat162float(p1[j]) * sm_scale; }
-  }
-  float m[G], l[G], acc[G][16];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -FLT_MAX; l[g] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) acc[g][j] = 0.f;
-  }
-  const int* bt = block_table + size_t(seq) * max_pages;
-  for (int t0 = begin + warp * TOK; t0 < end; t0 += 4 * TOK) {
-    const int t = t0 + slot;
-    const bool valid = t < end;
-    float kf[16], vf[16], ks = 0.f, vs = 0.f;
-    if (valid) {
-      const int page = bt[t / page_size], off = t % page_size;
-      const size_t base = (size_t(page) * Hk + kvh) * page_size + off;
-      uint4 kr = *reinterpret_cast<const uint4*>(k_cache + base * D + seg * 16);
-      uint4 vr = *reinterpret_cast<const uint4*>(v_cache + base * D + seg * 16);
-      ks = k_scale[base]; vs = v_scale[base];
-      const uint8_t* kb = reinterpret_cast<const uint8_t*>(&kr);
-      const uint8_t* vb = reinterpret_cast<const uint8_t*>(&vr);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) { kf[j] = from_e4m3(kb[j]); vf[j] = from_e4m3(vb[j]); }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) { kf[j] = 0.f; vf[j] = 0.f; }
-    }
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = 0.f;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) s = fmaf(qf[g][j], kf[j], s);
-#pragma unroll
-      for (int o = SEG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      s = valid ? s * ks : -FLT_MAX;
-      const float mn = fmaxf(m[g], s);
-      const float corr = __expf(m[g] - mn);
-      const float pexp = valid ? __expf(s - mn) : 0.f;
-      l[g] = l[g] * corr + pexp;
-      const float pv = pexp * vs;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) acc[g][j] = fmaf(acc[g][j], corr, pv * vf[j]);
-      m[g] = mn;
-    }
-  }
-  // merge the TOK token slots of the warp (lanes with equal seg)
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-#pragma unroll
-    for (int o = SEG; o < 32; o <<= 1) {
-      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
-      const float lo_ = __shfl_xor_sync(0xffffffffu, l[g], o);
-      const float mn = fmaxf(m[g], mo);
-      const float c0 = __expf(m[g] - mn), c1 = __expf(mo - mn);
-      l[g] = l[g] * c0 + lo_ * c1;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], o);
-        acc[g][j] = acc[g][j] * c0 + ao * c1;
-      }
-      m[g] = mn;
-    }
-  }
-  // merge the 4 warps through shared memory
-  __shared__ float s_acc[4][G][D];
-  __shared__ float s_m[4][G], s_l[4][G];
-  if (slot == 0) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) s_acc[warp][g][seg * 16 + j] = acc[g][j];
-      if (seg == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
-    }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx % D;
-    float mm = fmaxf(fmaxf(s_m[0][g], s_m[1][g]), fmaxf(s_m[2][g], s_m[3][g]));
-    float ll = 0.f, a = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float c = __expf(s_m[w][g] - mm);
-      ll += s_l[w][g] * c;
-      a += s_acc[w][g][d] * c;
-    }
-    const size_t hq = size_t(b) * Hq + kvh * G + g;
-    if (nsplit == 1) {
-      out[hq * D + d] = __float2bfloat16(ll > 0.f ? a / ll : 0.f);
-    } else {
-      part_acc[(hq * nsplit + split) * D + d] = a;
-      if (d == 0) { part_ml[(hq * nsplit + split) * 2] = mm; part_ml[(hq * nsplit + split) * 2 + 1] = ll; }
-    }
-  }
-}
-
-template <int D>
-__global__ void attn_reduce_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                   __nv_bfloat16* __restrict__ out, int nsplit) {
-  const size_t hq = blockIdx.x;
-  const int d = threadIdx.x;
-  float mm = -FLT_MAX;
-  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(hq * nsplit + s) * 2]);
-  float ll = 0.f, a = 0.f;
-  for (int s = 0; s < nsplit; ++s) {
-    const float c = __expf(part_ml[(hq * nsplit + s) * 2] - mm);
-    ll += part_ml[(hq * nsplit + s) * 2 + 1] * c;
-    a += part_acc[(hq * nsplit + s) * D + d] * c;
-  }
-  out[hq * D + d] = __float2bfloat16(ll > 0.f ? a / ll : 0.f);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -530,37 +397,6 @@ extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const in
   else if (D == 256) MFQ_ROPE(256);
   else return -1;
 #undef MFQ_ROPE
-  return cudaGetLastError() == cudaSuccess ? 0 : -7;
-}
-
-extern "C" int mfq_paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
-                                     const float* v_scale, const int* block_table, const int* seq_lens, void* out,
-                                     float* part_acc, float* part_ml, int B, int Hq, int Hk, int D, int page_size,
-                                     int max_pages, float sm_scale, int splits, int q_len, cudaStream_t stream) {
-  if (B <= 0 || Hq % Hk) return -1;
-  const int G = Hq / Hk;
-  if (splits < 1) splits = 1;
-  dim3 grid(B, Hk, splits);
-#define MFQ_ATTN(DD, GG)                                                                                          \
-  paged_attn_decode_kernel<DD, GG><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(q),                \
-      static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache), k_scale, v_scale, block_table, \
-      seq_lens, static_cast<__nv_bfloat16*>(out), part_acc, part_ml, Hq, Hk, page_size, max_pages, sm_scale, q_len)
-  if (D == 128 && G == 4) MFQ_ATTN(128, 4);
-  else if (D == 128 && G == 1) MFQ_ATTN(128, 1);
-  else if (D == 128 && G == 2) MFQ_ATTN(128, 2);
-  else if (D == 128 && G == 8) MFQ_ATTN(128, 8);
-  else if (D == 64 && G == 2) MFQ_ATTN(64, 2);
-  else if (D == 64 && G == 1) MFQ_ATTN(64, 1);
-  else if (D == 256 && G == 8) MFQ_ATTN(256, 8);
-  else if (D == 256 && G == 1) MFQ_ATTN(256, 1);
-  else return -1;
-#undef MFQ_ATTN
-  if (cudaGetLastError() != cudaSuccess) return -7;
-  if (splits > 1) {
-    if (D == 128) attn_reduce_kernel<128><<<B * Hq, 128, 0, stream>>>(part_acc, part_ml, static_cast<__nv_bfloat16*>(out), splits);
-    else if (D == 64) attn_reduce_kernel<64><<<B * Hq, 64, 0, stream>>>(part_acc, part_ml, static_cast<__nv_bfloat16*>(out), splits);
-    else attn_reduce_kernel<256><<<B * Hq, 256, 0, stream>>>(part_acc, part_ml, static_cast<__nv_bfloat16*>(out), splits);
-  }
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 

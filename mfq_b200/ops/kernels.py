@@ -17,12 +17,25 @@ def _token_tile(m: int) -> int:
 
 
 def pick_splits(m: int, n: int, k: int, sms: int = 148) -> int:
-    """Split-K factor that fills the SMs when the (n, token) tile grid alone cannot."""
+    """Split-K factor minimizing a wave model of the weight-streaming GEMM.
+
+    cost(s) = waves(s) * (K blocks per CTA + fixed ramp of ~4 blocks) + a small charge for the reduction;
+    it fills the SMs when the (n, token) tile grid alone cannot and avoids a nearly empty last wave.
+    """
     tiles = math.ceil(n / 128) * math.ceil(m / _token_tile(m))
     kb = k // 128
-    if tiles >= sms or kb <= 1:
+    if tiles >= 4 * sms or kb <= 1:
         return 1
-    return max(1, min(kb, 16, sms // tiles))
+    best, best_cost = 1, None
+    for s in range(1, min(kb, 16) + 1):
+        per = math.ceil(kb / s)
+        if s > 1 and per < 2:
+            break
+        ctas = tiles * math.ceil(kb / per)
+        cost = math.ceil(ctas / sms) * (per + 4) + (1.5 if s > 1 else 0.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def fp8_gemm(x_q: torch.Tensor, x_scale: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor, *,
@@ -96,18 +109,27 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tenso
     return q_out
 
 
+def attn_splits_for(batch: int, kv_heads: int, max_len: int, sms: int = 148) -> int:
+    """KV splits that give every SM a few CTAs without cutting a split below four pages."""
+    pages = max(1, (max_len + 15) // 16)
+    want = max(1, (3 * sms) // max(1, batch * kv_heads))
+    return max(1, min(want, (pages + 3) // 4, 64))
+
+
 def paged_attn_decode(q: torch.Tensor, kv, block_table: torch.Tensor, seq_lens: torch.Tensor, *, sm_scale: float,
                       splits: int = 1, q_len: int = 1, out=None) -> torch.Tensor:
     """``q [B*q_len, Hq, D]`` against the paged fp8 cache; ``seq_lens`` count the query tokens too."""
-    b, hq, d = q.shape
+    rows, hq, d = q.shape
+    b = rows // q_len
     hk = kv.k.shape[1]
     out = torch.empty_like(q) if out is None else out
     ws = Workspace.get(q.device)
     if splits > 1:
-        assert b * hq * splits * d <= ws.attn_acc.numel()
-    rc = lib().mfq_paged_attn_decode(ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale), ptr(block_table),
-                                     ptr(seq_lens), ptr(out), ptr(ws.attn_acc), ptr(ws.attn_ml), b, hq, hk, d,
-                                     kv.page_size, block_table.shape[1], float(sm_scale), splits, q_len, stream_ptr())
+        assert rows * hq * splits * d <= ws.attn_acc.numel() and rows * hq * splits * 2 <= ws.attn_ml.numel()
+    rc = lib().mfq_paged_attn_decode_mma(ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
+                                         ptr(block_table), ptr(seq_lens), ptr(out), ptr(ws.attn_acc), ptr(ws.attn_ml), b,
+                                         hq, hk, d, block_table.shape[1], float(sm_scale), splits, q_len,
+                                         ptr(ws.status), stream_ptr())
     check(rc, "paged_attn_decode", 2 if splits > 1 else 1)
     return out
 

@@ -22,7 +22,8 @@ _SIGNATURES = {
     "mfq_rmsnorm_quant": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "mfq_quant_rows": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "mfq_rope_kv_write": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
-    "mfq_paged_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+    
+    "mfq_paged_attn_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp],
     "mfq_argmax": [_vp, _vp, _i, _i, _i, _vp],
     "mfq_embed": [_vp, _vp, _vp, _i, _i, _vp],
     "mfq_decode_advance": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],

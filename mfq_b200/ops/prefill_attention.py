@@ -13,11 +13,9 @@ from .lib import lib
 
 
 def _gather(kv, slots: torch.Tensor):
-    pages = (slots // kv.page_size).long()
-    off = (slots % kv.page_size).long()
-    k = (kv.k[pages, :, off].float() * kv.k_scale[pages, :, off][..., None]).to(torch.bfloat16)
-    v = (kv.v[pages, :, off].float() * kv.v_scale[pages, :, off][..., None]).to(torch.bfloat16)
-    return k, v  # [T, Hk, D]
+    from .reference import gather_slots
+    k, v = gather_slots(kv, slots)
+    return k.to(torch.bfloat16), v.to(torch.bfloat16)  # [T, Hk, D]
 
 
 def run(q: torch.Tensor, kv, step, *, n_kv: int, sm_scale: float) -> torch.Tensor:

@@ -92,13 +92,20 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sm_scale: float
 
 
 def gather_paged(kv, block_table_row: torch.Tensor, length: int):
-    """Dequantized ``k, v [length, Hk, D]`` of one sequence from a :class:`LayerKV`."""
-    ps = kv.page_size
+    """Dequantized ``k, v [length, Hk, D]`` of one sequence from a :class:`LayerKV` (physical page layout)."""
     pos = torch.arange(length, device=kv.k.device)
-    pages = block_table_row.long()[pos // ps]
-    off = pos % ps
-    k = kv.k[pages, :, off].float() * kv.k_scale[pages, :, off][..., None]
-    v = kv.v[pages, :, off].float() * kv.v_scale[pages, :, off][..., None]
+    return gather_slots(kv, block_table_row.long()[pos // kv.page_size] * kv.page_size + pos % kv.page_size)
+
+
+def gather_slots(kv, slots: torch.Tensor):
+    """Dequantized ``k, v [T, Hk, D]`` rows at physical slots (page * page_size + offset)."""
+    from ..engine.kv_cache import V_SLOT_OF_TOKEN
+    ps = kv.page_size
+    pages, off = (slots // ps).long(), (slots % ps).long()
+    k = kv.k[pages, :, :, off]  # [T, Hk, D/64, 64]
+    k = k.reshape(k.shape[0], k.shape[1], -1).float() * kv.k_scale[pages, :, off][..., None]
+    vslot = torch.tensor(V_SLOT_OF_TOKEN, device=slots.device)[off]
+    v = kv.v[pages, :, :, vslot].float() * kv.v_scale[pages, :, off][..., None]
     return k, v
 
 
@@ -113,11 +120,15 @@ def paged_attn_decode(q, kv, block_table, seq_lens, sm_scale, q_len: int = 1):
 
 
 def write_kv(kv, k: torch.Tensor, v: torch.Tensor, slots: torch.Tensor) -> None:
+    from ..engine.kv_cache import V_SLOT_OF_TOKEN
     kq, ks = quant_kv(k)
     vq, vs = quant_kv(v)
     ok = slots >= 0
     pages, off = (slots[ok] // kv.page_size).long(), (slots[ok] % kv.page_size).long()
-    kv.k[pages, :, off] = kq[ok]
-    kv.v[pages, :, off] = vq[ok]
-    kv.k_scale[pages, :, off] = ks[ok]
-    kv.v_scale[pages, :, off] = vs[ok]
+    kq, vq, ks, vs = kq[ok], vq[ok], ks[ok], vs[ok]
+    t, hk, d = kq.shape
+    kv.k[pages, :, :, off] = kq.reshape(t, hk, d // 64, 64)
+    vslot = torch.tensor(V_SLOT_OF_TOKEN, device=slots.device)[off]
+    kv.v[pages, :, :, vslot] = vq
+    kv.k_scale[pages, :, off] = ks
+    kv.v_scale[pages, :, off] = vs

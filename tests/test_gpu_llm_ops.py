@@ -77,14 +77,16 @@ def test_rope_kv_write_and_decode_attention(hq, hk, d):
         ref.write_kv(rkv, k_ref, q3[:, hq + hk :], ref_cache.slots(i, 0, n).cuda())
         assert_close(q, q_ref, rel=1e-2, what="rope q")
     assert torch.equal(cache.block_table, ref_cache.block_table)
-    k_mine = kv.k.float() * kv.k_scale[..., None]
-    k_theirs = rkv.k.float() * rkv.k_scale[..., None]
+    from mfq_b200.engine.kv_cache import k_logical, v_logical
+    k_mine = k_logical(kv.k).float() * kv.k_scale[..., None]
+    k_theirs = k_logical(rkv.k).float() * rkv.k_scale[..., None]
     assert_close(k_mine, k_theirs, rel=0.07, what="k pages")
-    assert_close(kv.v.float() * kv.v_scale[..., None], rkv.v.float() * rkv.v_scale[..., None], rel=0.07, what="v pages")
+    assert_close(v_logical(kv.v).float() * kv.v_scale[..., None], v_logical(rkv.v).float() * rkv.v_scale[..., None],
+                 rel=0.07, what="v pages")
     q = torch.randn((b, hq, d), device="cuda").to(torch.bfloat16)
     seq_lens = torch.tensor(lens, dtype=torch.int32, device="cuda")
     want = ref.paged_attn_decode(q, kv, cache.block_table, seq_lens, 1 / math.sqrt(d))
-    for splits in (1, 3, 8):
+    for splits in (1, 3, 8, 40):
         got = ops.paged_attn_decode(q, kv, cache.block_table, seq_lens, sm_scale=1 / math.sqrt(d), splits=splits)
         assert_close(got, want, rel=2e-2, what=f"decode attention splits={splits}")
 
