@@ -279,3 +279,60 @@ extern "C" int mfq_fp8_gemm(const void* w, const float* w_scale, const void* x, 
     default: return -1;
   }
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in mfq_noalloc.h): the split-K scratch is a file-scope
+// device array instead of caller memory.  Layout: [partials | counters | status word].
+// ---------------------------------------------------------------------------------------------------------
+#include "mfq_noalloc.h"
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[MFQ_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of g_noalloc_scratch per device ordinal.  In host code the array's name is only a handle for
+// cudaGetSymbolAddress; the address a kernel can use has to be asked for, per device.
+unsigned char* g_noalloc_ptr[kMaxDevices] = {};
+
+int noalloc_fail(int code, const char* why) {
+  fprintf(stderr, "mfq_fp8_gemm_noalloc: %s\n", why);
+  return code;
+}
+}  // namespace
+
+extern "C" int mfq_fp8_gemm_noalloc(const void* w, const float* w_scale, const void* x, const float* x_scale,
+                                    void* out, const void* residual, int M, int N, int K, int token_tile, int splits,
+                                    cudaStream_t stream) {
+  if (!w || !w_scale || !x || !x_scale || !out || M <= 0 || N <= 0 || K <= 0 || K % 128 != 0)
+    return noalloc_fail(MFQ_NOALLOC_BAD_ARGUMENT, "null pointer, non-positive size or K not a multiple of 128");
+  if (token_tile != 16 && token_tile != 32 && token_tile != 64 && token_tile != 128)
+    return noalloc_fail(MFQ_NOALLOC_BAD_ARGUMENT, "token_tile must be 16, 32, 64 or 128");
+  const int kb_total = K / 128;
+  if (splits < 1) splits = 1;
+  if (splits > kb_total) splits = kb_total;
+  const long long tiles = (long long)((N + 127) / 128) * ((M + token_tile - 1) / token_tile);
+  const long long partial_bytes = splits > 1 ? (long long)splits * tiles * token_tile * 128 * 4 : 0;
+  if (tiles > MFQ_NOALLOC_MAX_TILES || partial_bytes > (long long)MFQ_NOALLOC_PARTIAL_BYTES)
+    return noalloc_fail(MFQ_NOALLOC_TOO_LARGE,
+                        "problem exceeds the built-in scratch (8 MiB of split-K partials, 4096 output tiles)");
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return noalloc_fail(MFQ_NOALLOC_SETUP_FAILED, "no current CUDA device");
+  if (!g_noalloc_ptr[dev]) {  // set-up, once per device, with that device current
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) return noalloc_fail(MFQ_NOALLOC_SETUP_FAILED, cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  unsigned char* base = g_noalloc_ptr[dev];
+  float* partials = reinterpret_cast<float*>(base);
+  int* counters = reinterpret_cast<int*>(base + MFQ_NOALLOC_PARTIAL_BYTES);
+  int* status = counters + MFQ_NOALLOC_MAX_TILES;
+  // counters and status must start at zero; an earlier call that was interrupted could have left them dirty
+  if (cudaMemsetAsync(counters, 0, size_t(MFQ_NOALLOC_MAX_TILES) * 4 + 256, stream) != cudaSuccess)
+    return noalloc_fail(MFQ_NOALLOC_SETUP_FAILED, "could not clear the scratch counters");
+  const int rc = mfq_fp8_gemm(w, w_scale, x, x_scale, out, residual, partials, MFQ_NOALLOC_PARTIAL_BYTES, counters,
+                              MFQ_NOALLOC_MAX_TILES, status, M, N, K, token_tile, splits, stream);
+  if (rc != 0) return noalloc_fail(rc, "launch failed");
+  return MFQ_NOALLOC_OK;
+}
