@@ -77,17 +77,12 @@ class LLMEngine:
                 input_ids=ids[start:end], positions=torch.arange(start, end, dtype=torch.int32, device=dev),
                 slots=self.cache.slots(seq_id, start, end - start).to(dev), cu_seqlens=[0, end - start])
             rows = torch.tensor([end - start - 1], dtype=torch.int32, device=dev)
-            logits = self.model.forward(step, self.cache, prefill=True, logits_rows=rows)
+            logits = self.model.forward(step, self.cache, prefill=True, logits_rows=rows, gather_logits=False)
             last = logits
-        tok = self._sample(last)
+        tok = self.model.sample_greedy(last)
         self.sampled[row : row + 1] = tok
         self.seq_lens[row] = n
         return tok
-
-    def _sample(self, logits: torch.Tensor) -> torch.Tensor:
-        if logits.is_cuda:
-            return ops.argmax(logits)
-        return logits.float().argmax(-1).to(torch.int32)
 
     def grow(self, row: int, tokens: int) -> None:
         self.cache.assign(row, self.row_seq[row], min(self.max_seq_len, tokens))
@@ -110,11 +105,8 @@ class LLMEngine:
         if dev.type == "cuda":
             from ..ops.kernels import attn_splits_for
             self.model.attn_splits = attn_splits_for(b, self.model.hk, self.max_seq_len)
-        logits = self.model.forward(step, self.cache, prefill=False)
-        if dev.type == "cuda":
-            ops.argmax(logits, out=self.sampled[:b])
-        else:
-            self.sampled[:b] = logits.float().argmax(-1).to(torch.int32)
+        logits = self.model.forward(step, self.cache, prefill=False, gather_logits=False)
+        self.model.sample_greedy(logits, out=self.sampled[:b])
 
     def decode_step(self, b: int) -> None:
         """Advance rows ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device)."""

@@ -226,8 +226,10 @@ class LlamaModel:
         return torch.cat(outs, 0).reshape(t, self.hq * d)
 
     # -- forward ------------------------------------------------------------------------------------------------
-    def forward(self, step: StepBuffers, cache, *, prefill: bool, logits_rows: torch.Tensor | None = None):
-        """Returns bf16 logits ``[rows, vocab]`` (all tokens, or ``logits_rows`` of them)."""
+    def forward(self, step: StepBuffers, cache, *, prefill: bool, logits_rows: torch.Tensor | None = None,
+                gather_logits: bool = True):
+        """Returns bf16 logits ``[rows, vocab]`` (all tokens, or ``logits_rows`` of them).  With tensor parallelism
+        and ``gather_logits=False`` the result is this rank's vocabulary shard, for :meth:`sample_greedy`."""
         w = self.w
         ids = step.input_ids
         h = ops.embed(ids, w.embed) if w.embed.is_cuda else w.embed[ids.long()].clone()
@@ -246,6 +248,18 @@ class LlamaModel:
             h = h[logits_rows.long()] if not h.is_cuda else h.index_select(0, logits_rows.long())
         xq, xs = self._norm_quant(h, w.final_norm)
         logits = w.lm_head(xq, xs)
-        if self.tp > 1:
+        if self.tp > 1 and gather_logits:
             logits = self.collective.gather_columns(logits)
         return logits
+
+    def sample_greedy(self, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Arg-max token per row.  Under TP ``logits`` is this rank's vocabulary shard (``gather_logits=False``)."""
+        if self.tp > 1:
+            return self.collective.argmax(logits, out)
+        if logits.is_cuda:
+            return ops.argmax(logits, out=out)
+        res = logits.float().argmax(-1).to(torch.int32)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res

@@ -35,6 +35,15 @@ struct GemmCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
+// Cross-rank all-reduce context of the fused epilogue (world == 1: disabled).
+struct ArParams {
+  int world = 1, rank = 0;
+  float* bufs[8] = {};        // every rank's partial buffer (own + peer-mapped): 2 halves of half_elems floats
+  uint32_t* flags[8] = {};    // every rank's per-tile arrival counters (own + peer-mapped)
+  uint32_t* expected = nullptr;  // local: value of our flag after the previous launch, per tile
+  size_t half_elems = 0;
+};
+
 struct GemmParams {
   const float* w_scale;
   const float* x_scale;
@@ -45,6 +54,7 @@ struct GemmParams {
   int* status;
   int M, N, K;
   int kb_per_split;
+  ArParams ar;
 };
 
 template <int BT>
@@ -59,8 +69,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   uint64_t* empty = bars + Cfg::kStages;
   uint64_t* acc_full = bars + 2 * Cfg::kStages;
   uint64_t* acc_empty = acc_full + Cfg::kAcc;
-  uint64_t* epi_bar = acc_empty + Cfg::kAcc;  // two one-shot barriers among the epilogue warps
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 2);
+  uint64_t* epi_bar = acc_empty + Cfg::kAcc;  // four one-shot barriers among the epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -76,8 +86,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   if (threadIdx.x == 0) {
     for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
     for (int i = 0; i < Cfg::kAcc; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
-    mbar_init(&epi_bar[0], 4);
-    mbar_init(&epi_bar[1], 4);
+    for (int i = 0; i < 4; ++i) mbar_init(&epi_bar[i], 4);
     *abort_flag = 0;
     *last_flag = 0;
     mbar_fence_init();
@@ -167,21 +176,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
     if (ok) {
       const int tl = min(BT, p.M - t0);
-      if (gridDim.z == 1) {
-        if (n < p.N) {
-#pragma unroll
-          for (int t = 0; t < BT; ++t) {
-            if (t < tl) {
-              float v = acc[t] * __ldg(p.x_scale + t0 + t);
-              const size_t o = size_t(t0 + t) * p.N + n;
-              if (p.residual) v += __bfloat162float(p.residual[o]);
-              p.out[o] = __float2bfloat16(v);
-            }
-          }
-        }
-      } else {
-        const int tiles_nt = gridDim.x * gridDim.y;
-        const int tile_id = t_tile * gridDim.x + n_tile;
+      const int tiles_nt = gridDim.x * gridDim.y;
+      const int tile_id = t_tile * gridDim.x + n_tile;
+      bool owner = true;  // this CTA holds the tile's complete local sum in `acc`
+      if (gridDim.z > 1) {
+        owner = false;
         float* mine = p.ws + (size_t(split) * tiles_nt + tile_id) * (BT * kTileN);
 #pragma unroll
         for (int t = 0; t < BT; ++t) mine[t * kTileN + row] = acc[t];
@@ -208,18 +207,77 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
             for (int t = 0; t < BT; ++t) acc[t] += __ldcg(part + t * kTileN);
           }
-          if (n < p.N) {
+          if (threadIdx.x == 64) p.counters[tile_id] = 0;
+          owner = true;
+        }
+      }
+      if (owner) {
 #pragma unroll
-            for (int t = 0; t < BT; ++t) {
-              if (t < tl) {
-                float v = acc[t] * __ldg(p.x_scale + t0 + t);
-                const size_t o = size_t(t0 + t) * p.N + n;
-                if (p.residual) v += __bfloat162float(p.residual[o]);
-                p.out[o] = __float2bfloat16(v);
+        for (int t = 0; t < BT; ++t) acc[t] *= (t < tl) ? __ldg(p.x_scale + t0 + t) : 0.f;
+        if (p.ar.world > 1) {
+          // ----- one-shot all-reduce over NVLink peer memory, fused into the epilogue -----
+          // Every rank publishes its partial tile in its own (peer-mapped) buffer, bumps the tile's flag on every
+          // peer, waits until all peers bumped ours, then sums the W partials in rank order, so all ranks compute
+          // bit-identical results.  Flags only ever count up (W-1 per launch), which makes the protocol safe under
+          // CUDA-graph replay; the tile's launch count also selects one of two buffers, so a fast rank cannot
+          // overwrite a partial that a slow rank is still reading.
+          const ArParams& ar = p.ar;
+          const uint32_t before = ar.expected[tile_id];
+          const uint32_t target = before + uint32_t(ar.world - 1);
+          const size_t off = size_t((before / uint32_t(ar.world - 1)) & 1u) * ar.half_elems + size_t(tile_id) * (BT * kTileN);
+          float* mine = ar.bufs[ar.rank] + off;
+#pragma unroll
+          for (int t = 0; t < BT; ++t) mine[t * kTileN + row] = acc[t];
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&epi_bar[2]);
+          bool met = mbar_wait(&epi_bar[2], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
+          if (met && threadIdx.x == 64) {
+            for (int r = 0; r < ar.world; ++r)
+              if (r != ar.rank)
+                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[r] + tile_id) : "memory");
+            const uint32_t* my_flag = ar.flags[ar.rank] + tile_id;
+            const unsigned long long t_start = globaltimer_ns();
+            uint32_t seen, spins = 0;
+            while (true) {
+              asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
+              if (int32_t(seen - target) >= 0) break;
+              if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t_start > kWaitBudgetNs)) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, kStatusTimeoutPeer);
+                break;
+              }
+            }
+            ar.expected[tile_id] = target;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&epi_bar[3]);
+          met = met && mbar_wait(&epi_bar[3], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
+          owner = met && !*abort_flag;
+          if (owner) {
+#pragma unroll
+            for (int t = 0; t < BT; ++t) acc[t] = 0.f;
+            for (int r = 0; r < ar.world; ++r) {
+              const float* part = ar.bufs[r] + off + row;
+#pragma unroll
+              for (int t = 0; t < BT; ++t) {
+                float v;
+                asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(part + t * kTileN) : "memory");
+                acc[t] += v;
               }
             }
           }
-          if (threadIdx.x == 64) p.counters[tile_id] = 0;
+        }
+        if (owner && n < p.N) {
+#pragma unroll
+          for (int t = 0; t < BT; ++t) {
+            if (t < tl) {
+              float v = acc[t];
+              const size_t o = size_t(t0 + t) * p.N + n;
+              if (p.residual) v += __bfloat162float(p.residual[o]);
+              p.out[o] = __float2bfloat16(v);
+            }
+          }
         }
       }
     }
@@ -235,7 +293,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 template <int BT>
 static int launch_gemm(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
                        const void* residual, float* ws, size_t ws_bytes, int* counters, int counters_len, int* status,
-                       int M, int N, int K, int splits, cudaStream_t stream) {
+                       int M, int N, int K, int splits, cudaStream_t stream, const ArParams* ar = nullptr) {
   using Cfg = GemmCfg<BT>;
   CUtensorMap tw, tx;
   if (make_tmap_2d(&tw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kTileN, kBlockK)) return -2;
@@ -251,7 +309,11 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
     if (n_tiles * t_tiles > counters_len) return -5;
   }
   GemmParams p{w_scale, x_scale, static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(residual),
-               ws, counters, status, M, N, K, kb_per};
+               ws, counters, status, M, N, K, kb_per, ArParams{}};
+  if (ar) {
+    if (size_t(n_tiles) * t_tiles * BT * kTileN > ar->half_elems) return -8;
+    p.ar = *ar;
+  }
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(fp8_gemm_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
@@ -276,6 +338,34 @@ extern "C" int mfq_fp8_gemm(const void* w, const float* w_scale, const void* x, 
     case 32: return mfq::launch_gemm<32>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream);
     case 64: return mfq::launch_gemm<64>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream);
     case 128: return mfq::launch_gemm<128>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream);
+    default: return -1;
+  }
+}
+
+// Tensor-parallel row-parallel linear: the same GEMM with the cross-rank sum fused into its epilogue.  `bufs` /
+// `flags` hold `world` device pointers each (own buffer at index `rank`, the others peer-mapped); every buffer has
+// 2 * half_elems floats, every flag array at least ceil(N/128) * ceil(M/token_tile) counters, zero before first use.
+// All ranks must issue the same sequence of calls on a context.  `residual` is added after the sum on every rank.
+extern "C" int mfq_fp8_gemm_allreduce(const void* w, const float* w_scale, const void* x, const float* x_scale,
+                                      void* out, const void* residual, float* ws, size_t ws_bytes, int* counters,
+                                      int counters_len, int* status, int M, int N, int K, int token_tile, int splits,
+                                      int world, int rank, void* const* bufs, void* const* flags, void* expected,
+                                      size_t half_elems, cudaStream_t stream) {
+  if (K % 128 != 0 || M <= 0 || N <= 0 || world < 2 || world > 8 || rank < 0 || rank >= world) return -1;
+  mfq::ArParams ar;
+  ar.world = world;
+  ar.rank = rank;
+  for (int r = 0; r < world; ++r) {
+    ar.bufs[r] = static_cast<float*>(bufs[r]);
+    ar.flags[r] = static_cast<uint32_t*>(flags[r]);
+  }
+  ar.expected = static_cast<uint32_t*>(expected);
+  ar.half_elems = half_elems;
+  switch (token_tile) {
+    case 16: return mfq::launch_gemm<16>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
+    case 32: return mfq::launch_gemm<32>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
+    case 64: return mfq::launch_gemm<64>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
+    case 128: return mfq::launch_gemm<128>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
     default: return -1;
   }
 }

@@ -1,0 +1,112 @@
+// Small tensor-parallel collectives fused into their producing kernels, over peer-mapped memory.
+//
+// argmax_allgather: vocabulary-sharded greedy sampling.  Each rank reduces its logits shard to one (value, index)
+// candidate per row, pushes it into every peer's slot table, and picks the global winner once all W candidates of
+// the row have arrived -- 8 bytes per rank and row cross NVLink instead of the full logits (the reference gathers
+// column-parallel outputs to a primary GPU with ncclSend/ncclRecv and samples there,
+// cpp_runtime/backends/cuda/ops/quant_linear.cpp:532-611).
+// Flags only count up (W-1 per launch and row) so the kernel is CUDA-graph replay safe; the launch count of a row
+// selects one of two slot tables so a fast rank cannot overwrite candidates a slow rank still reads.
+#include "common.cuh"
+
+#include <cfloat>
+
+namespace mfq {
+
+struct Candidate { float value; int index; };
+
+struct ArgmaxParams {
+  int world, rank;
+  Candidate* slots[8];   // per rank: [2][world][rows_cap]
+  uint32_t* flags[8];    // per rank: [rows_cap]
+  uint32_t* expected;    // local [rows_cap]
+  int rows_cap;
+};
+
+__global__ void __launch_bounds__(1024)
+argmax_allgather_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, int V, int stride,
+                        int index_offset, ArgmaxParams ap, int* status) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + size_t(row) * stride;
+  float best = -FLT_MAX;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = __bfloat162float(lr[i]);
+    if (v > best) { best = v; bi = i; }
+  }
+  auto merge = [](float& b, int& i, float ov, int oi) {
+    if (ov > b || (ov == b && oi < i)) { b = ov; i = oi; }
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+  __syncthreads();
+  if (warp != 0) return;
+  const int nw = blockDim.x >> 5;
+  best = lane < nw ? sv[lane] : -FLT_MAX;
+  bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if (lane != 0) return;
+  bi += index_offset;
+  if (ap.world == 1) { out[row] = bi; return; }
+  const uint32_t before = ap.expected[row];
+  const uint32_t target = before + uint32_t(ap.world - 1);
+  const size_t table = size_t((before / uint32_t(ap.world - 1)) & 1u) * ap.world * ap.rows_cap;
+  const unsigned long long packed = (unsigned long long)(__float_as_uint(best)) | ((unsigned long long)(uint32_t)bi << 32);
+  for (int r = 0; r < ap.world; ++r) {
+    Candidate* dst = ap.slots[r] + table + size_t(ap.rank) * ap.rows_cap + row;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(packed) : "memory");
+  }
+  __threadfence_system();
+  for (int r = 0; r < ap.world; ++r)
+    if (r != ap.rank) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ap.flags[r] + row) : "memory");
+  const uint32_t* my_flag = ap.flags[ap.rank] + row;
+  const unsigned long long t_start = globaltimer_ns();
+  uint32_t seen, spins = 0;
+  bool ok = true;
+  while (true) {
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
+    if (int32_t(seen - target) >= 0) break;
+    if ((++spins & 0x3F) == 0 && globaltimer_ns() - t_start > kWaitBudgetNs) {
+      atomicCAS(status, 0, kStatusTimeoutPeer);
+      ok = false;
+      break;
+    }
+  }
+  ap.expected[row] = target;
+  if (!ok) return;
+  float gb = -FLT_MAX;
+  int gi = 0x7fffffff;
+  for (int r = 0; r < ap.world; ++r) {
+    unsigned long long pk;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(pk) : "l"(ap.slots[ap.rank] + table + size_t(r) * ap.rows_cap + row) : "memory");
+    merge(gb, gi, __uint_as_float(uint32_t(pk)), int(uint32_t(pk >> 32)));
+  }
+  out[row] = gi;
+}
+
+}  // namespace mfq
+
+// logits: this rank's shard [B, V] (row stride `stride`), index_offset = first vocabulary id of the shard.
+// slots[r]: rank r's table of 2 * world * rows_cap candidates (8 bytes each); flags[r]: rows_cap counters.
+extern "C" int mfq_argmax_allgather(const void* logits, int* out, int B, int V, int stride, int index_offset, int world,
+                                    int rank, void* const* slots, void* const* flags, void* expected, int rows_cap,
+                                    int* status, cudaStream_t stream) {
+  if (B <= 0 || B > rows_cap || world < 1 || world > 8) return -1;
+  mfq::ArgmaxParams ap{};
+  ap.world = world;
+  ap.rank = rank;
+  for (int r = 0; r < world && world > 1; ++r) {
+    ap.slots[r] = static_cast<mfq::Candidate*>(slots[r]);
+    ap.flags[r] = static_cast<uint32_t*>(flags[r]);
+  }
+  ap.expected = static_cast<uint32_t*>(expected);
+  ap.rows_cap = rows_cap;
+  mfq::argmax_allgather_kernel<<<B, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), out, V, stride,
+                                                        index_offset, ap, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}

@@ -1,0 +1,96 @@
+"""Tensor parallelism over the GPUs of one node: symmetric ranks, collectives fused into the kernels.
+
+Every rank owns 1/W of the attention heads and of the MLP intermediate; the residual stream is replicated.
+Row-parallel projections (``o_proj``, ``down``) run :func:`mfq_fp8_gemm_allreduce`, whose epilogue exchanges the
+partial tiles through peer-mapped memory and sums them in rank order (bit-identical on all ranks); the sampled
+token comes from a vocabulary-sharded arg-max that exchanges 8 bytes per rank and row.  The reference instead
+broadcasts activations from, and reduces partial outputs to, one primary GPU through NCCL
+(``cpp_runtime/backends/cuda/ops/quant_linear.cpp:622-761``).  :class:`NcclTensorParallel` is that style of
+baseline (library collectives after an unfused GEMM), kept for A/B measurements.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..ops import kernels as K
+from ..ops.lib import Workspace, check, lib, ptr, stream_ptr
+from .peer_memory import PeerBuffer
+
+
+class _ReduceContext:
+    """Peer buffers of one (token tile, N, token-tile count) geometry."""
+
+    def __init__(self, tp: "TensorParallel", bt: int, n: int, t_tiles: int) -> None:
+        self.tiles = math.ceil(n / 128) * t_tiles
+        self.half_elems = self.tiles * bt * 128
+        self.partials = PeerBuffer(tp.group, 2 * self.half_elems * 4, tp.device)
+        self.flags = PeerBuffer(tp.group, max(256, self.tiles * 4), tp.device)
+        self.expected = torch.zeros(self.tiles, dtype=torch.int32, device=tp.device)
+        self.buf_table = self.partials.table()
+        self.flag_table = self.flags.table()
+
+
+class TensorParallel:
+    def __init__(self, group, device: torch.device, max_rows: int = 8192) -> None:
+        self.group, self.device = group, device
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self._ctx: dict[tuple[int, int, int], _ReduceContext] = {}
+        self.rows_cap = max_rows
+        self._slots = PeerBuffer(group, 2 * self.world * max_rows * 8, device)
+        self._slot_flags = PeerBuffer(group, max_rows * 4, device)
+        self._slot_expected = torch.zeros(max_rows, dtype=torch.int32, device=device)
+
+    def row_parallel_linear(self, lin, x_q: torch.Tensor, x_scale: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        """``h += all_reduce(x_q @ lin^T)`` in place; ``x_q`` holds this rank's input shard."""
+        m, k = x_q.shape
+        n = lin.q.shape[0]
+        bt = K._token_tile(m)
+        key = (bt, n, math.ceil(m / bt))
+        ctx = self._ctx.get(key)
+        if ctx is None:
+            ctx = self._ctx[key] = _ReduceContext(self, *key)
+        ws = Workspace.get(self.device)
+        rc = lib().mfq_fp8_gemm_allreduce(
+            ptr(lin.q), ptr(lin.scale), ptr(x_q), ptr(x_scale), ptr(h), ptr(h), ptr(ws.splitk), ws.splitk.numel(),
+            ptr(ws.counters), ws.counters.numel(), ptr(ws.status), m, n, k, bt, K.pick_splits(m, n, k), self.world,
+            self.rank, ctx.buf_table, ctx.flag_table, ptr(ctx.expected), ctx.half_elems, stream_ptr())
+        check(rc, "fp8_gemm_allreduce")
+        return h
+
+    def argmax(self, logits_shard: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        b, v = logits_shard.shape
+        out = torch.empty(b, dtype=torch.int32, device=self.device) if out is None else out
+        ws = Workspace.get(self.device)
+        rc = lib().mfq_argmax_allgather(ptr(logits_shard), ptr(out), b, v, logits_shard.stride(0), self.rank * v,
+                                        self.world, self.rank, self._slots.table(), self._slot_flags.table(),
+                                        ptr(self._slot_expected), self.rows_cap, ptr(ws.status), stream_ptr())
+        check(rc, "argmax_allgather")
+        return out
+
+    def gather_columns(self, shard: torch.Tensor) -> torch.Tensor:
+        """Full ``[rows, W * cols]`` matrix from column shards (library all-gather; used off the hot path)."""
+        parts = [torch.empty_like(shard) for _ in range(self.world)]
+        dist.all_gather(parts, shard.contiguous(), group=self.group)
+        return torch.cat(parts, dim=1)
+
+
+class NcclTensorParallel(TensorParallel):
+    """Baseline: unfused GEMM followed by NCCL all-reduce / all-gather (what a library-only port would do)."""
+
+    def row_parallel_linear(self, lin, x_q, x_scale, h):
+        partial = K.fp8_gemm(x_q, x_scale, lin.q, lin.scale).float()
+        dist.all_reduce(partial, group=self.group)
+        h.copy_((partial + h.float()).to(torch.bfloat16))
+        return h
+
+    def argmax(self, logits_shard, out=None):
+        full = self.gather_columns(logits_shard)
+        res = K.argmax(full)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res

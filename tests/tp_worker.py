@@ -1,0 +1,74 @@
+"""Child process of the tensor-parallel GPU test: launched by torch.distributed.run, one rank per GPU."""
+
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+from mfq_b200.engine.llm_engine import LLMEngine  # noqa: E402
+from mfq_b200.models.llama import LlamaConfig, LlamaModel, LlamaWeights, StepBuffers  # noqa: E402
+from mfq_b200.ops import Workspace  # noqa: E402
+from mfq_b200.parallel.tensor_parallel import NcclTensorParallel, TensorParallel  # noqa: E402
+
+
+def prefill_logits(model, engine, prompt, dev):
+    n = prompt.numel()
+    engine.cache.assign(0, 10_000, n)
+    step = StepBuffers(input_ids=prompt.to(dev, torch.int32), positions=torch.arange(n, dtype=torch.int32, device=dev),
+                       slots=engine.cache.slots(10_000, 0, n).to(dev), cu_seqlens=[0, n])
+    out = model.forward(step, engine.cache, prefill=True).float()
+    engine.cache.release(10_000)
+    return out
+
+
+def main() -> None:
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    cfg = LlamaConfig.tiny()
+    result = {"world": world}
+    prompt = torch.randint(0, cfg.vocab_size, (48,), generator=torch.Generator().manual_seed(7))
+
+    tp = TensorParallel(dist.group.WORLD, dev)
+    w = LlamaWeights.random_init(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_size=world)
+    model = LlamaModel(cfg, w, collective=tp)
+    engine = LLMEngine(model, max_batch=4, max_seq_len=128)
+    fused = prefill_logits(model, engine, prompt, dev)
+
+    base_model = LlamaModel(cfg, w, collective=NcclTensorParallel(dist.group.WORLD, dev))
+    base_engine = LLMEngine(base_model, max_batch=4, max_seq_len=128, use_graphs=False)
+    nccl = prefill_logits(base_model, base_engine, prompt, dev)
+    result["fused_vs_nccl_max_err"] = float((fused - nccl).abs().max())
+    result["logit_scale"] = float(nccl.abs().max())
+
+    w1 = LlamaWeights.random_init(cfg, dev, seed=3, std=0.05)
+    m1 = LlamaModel(cfg, w1)
+    e1 = LLMEngine(m1, max_batch=4, max_seq_len=128, use_graphs=False)
+    single = prefill_logits(m1, e1, prompt, dev)
+    result["tp_vs_single_max_err"] = float((fused - single).abs().max())
+    result["tp_vs_single_top1"] = float((fused.argmax(-1) == single.argmax(-1)).float().mean())
+
+    # graph decode: every rank must sample the same tokens
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)) for n in (20, 33, 41)]
+    toks = engine.generate(prompts, 10).tokens.to(dev)
+    gathered = [torch.empty_like(toks) for _ in range(world)]
+    dist.all_gather(gathered, toks)
+    result["ranks_agree"] = all(torch.equal(g, gathered[0]) for g in gathered)
+    eager = LLMEngine(LlamaModel(cfg, w, collective=tp), max_batch=4, max_seq_len=128, use_graphs=False)
+    result["graph_equals_eager"] = bool(torch.equal(eager.generate(prompts, 10).tokens.to(dev), toks))
+    torch.cuda.synchronize()
+    Workspace.get(dev).check()
+    dist.barrier()
+    if rank == 0:
+        print("TP_RESULT " + json.dumps(result), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
