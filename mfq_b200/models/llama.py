@@ -199,9 +199,13 @@ class LlamaModel:
         cfg = self.cfg
         d = cfg.head_dim
         t = qkv.shape[0]
+        kd = vd = None
         if qkv.is_cuda:
+            if prefill:
+                kd = torch.empty((t, self.hk, d), dtype=torch.bfloat16, device=qkv.device)
+                vd = torch.empty_like(kd)
             q = ops.rope_kv_write(qkv, step.positions, step.slots, kv, n_q=self.hq, n_kv=self.hk, head_dim=d,
-                                  theta=cfg.rope_theta)
+                                  theta=cfg.rope_theta, kd_out=kd, vd_out=vd)
         else:
             q3 = qkv.view(t, self.hq + 2 * self.hk, d)
             q = ref.rope(q3[:, : self.hq], step.positions, cfg.rope_theta)
@@ -217,7 +221,7 @@ class LlamaModel:
         # prefill over a packed chunk: each sequence attends causally to itself, through the same FP8 rounding
         # of K/V that later decode steps will read back from the pages
         if qkv.is_cuda:
-            return ops.attn_prefill(q, kv, step, n_kv=self.hk, sm_scale=self.sm_scale).reshape(t, self.hq * d)
+            return ops.attn_prefill(q, kd, vd, step.cu_seqlens, self.sm_scale).reshape(t, self.hq * d)
         outs = []
         for i in range(len(step.cu_seqlens) - 1):
             a, b = step.cu_seqlens[i], step.cu_seqlens[i + 1]

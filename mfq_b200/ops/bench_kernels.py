@@ -89,6 +89,28 @@ def bench_attn(batch: int, ctx: int, hq: int, hk: int, d: int, splits: int, reps
     return {"kernel": "paged_attn_decode", "batch": batch, "ctx": ctx, "splits": splits, "us": ms * 1e3, "gbs": byt / ms / 1e6}
 
 
+def bench_prefill(t: int, hq: int, hk: int, reps: int) -> list[dict]:
+    d = 128
+    q = torch.randn((t, hq, d), device="cuda").to(torch.bfloat16)
+    k = torch.randn((t, hk, d), device="cuda").to(torch.bfloat16)
+    v = torch.randn((t, hk, d), device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    ms = time_ms(lambda _: K.attn_prefill_bf16(q, k, v, 0.088, out=out), reps)
+    rows = [{"kernel": "attn_prefill_bf16", "t": t, "hq": hq, "hk": hk, "us": ms * 1e3,
+             "tflops": 4 * t * t * hq * d / 2 / ms / 1e9}]
+    pages = math.ceil(t / 16)
+    cache = PagedKVCache(layers=1, kv_heads=hk, head_dim=d, num_pages=pages + 1, max_seqs=1, max_pages_per_seq=pages, device="cuda")
+    cache.assign(0, 0, t)
+    qkv = torch.randn((t, (hq + 2 * hk) * d), device="cuda").to(torch.bfloat16)
+    pos = torch.arange(t, dtype=torch.int32, device="cuda")
+    slots = cache.slots(0, 0, t).cuda()
+    kd, vd = torch.empty_like(k), torch.empty_like(v)
+    ms = time_ms(lambda _: K.rope_kv_write(qkv, pos, slots, cache.layer(0), n_q=hq, n_kv=hk, head_dim=d, theta=5e5, q_out=out,
+                                           kd_out=kd, vd_out=vd), reps)
+    rows.append({"kernel": "rope_kv_write", "t": t, "us": ms * 1e3, "gbs": t * (hq + 2 * hk) * d * 5 / ms / 1e6})
+    return rows
+
+
 def bench_small(m: int, h: int, i: int, reps: int) -> list[dict]:
     x = torch.randn((m, h), device="cuda").to(torch.bfloat16)
     w = torch.ones(h, device="cuda", dtype=torch.bfloat16)
@@ -108,6 +130,7 @@ def main() -> None:
     ap.add_argument("--json", default="")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--only", default="", help="comma separated kernel families: gemm,attn,small,prefill")
     args = ap.parse_args()
     pk = peaks()
     rows = []
@@ -124,6 +147,8 @@ def main() -> None:
             rows.append(bench_attn(batch, ctx, 32, 8, 128, splits, args.reps))
     for m in (1, 64, 4096):
         rows += bench_small(m, 4096, 14336, args.reps)
+    for t in (1024, 4096):
+        rows += bench_prefill(t, 32, 8, args.reps)
     for r in rows:
         if "gbs" in r:
             r["hbm_frac"] = r["gbs"] / pk["hbm_gbs"]

@@ -11,8 +11,8 @@
 // the epilogue warps fold it, scaled, into fp32 registers while the tensor core already works on
 // the next block.
 //
-// Roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue
-// (TMEM lane quarter = warp % 4).  Split-K (gridDim.z > 1) writes fp32 partials to a scratch
+// Roles: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2.. = epilogue (TMEM lane quarter =
+// warp % 4; token tiles of 64 and 128 use two warps per quarter, each folding half of the token columns).  Split-K (gridDim.z > 1) writes fp32 partials to a scratch
 // buffer; the last CTA to arrive at a tile's counter reduces them in split order (deterministic)
 // and resets the counter for the next launch.
 //
@@ -24,7 +24,6 @@ namespace mfq {
 
 constexpr int kTileN = 128;     // weight rows (output features) per CTA
 constexpr int kBlockK = 128;    // fp8 elements per K block = one 128-byte swizzle row
-constexpr int kGemmThreads = 192;
 
 template <int BT>
 struct GemmCfg {
@@ -32,6 +31,11 @@ struct GemmCfg {
   static constexpr int kAcc = 4;
   static constexpr int kTmemCols = (kAcc * BT) < 32 ? 32 : kAcc * BT;
   static constexpr int kStageBytes = kTileN * kBlockK + BT * kBlockK;
+  // Epilogue warps: one per TMEM lane quarter, doubled for wide token tiles (the two warps of a quarter split the
+  // token columns), so that two warps per scheduler hide each other's TMEM-load and FMA latencies.
+  static constexpr int kEpiWarps = BT >= 64 ? 8 : 4;
+  static constexpr int kCols = BT / (kEpiWarps / 4);   // token columns per epilogue thread
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
@@ -58,7 +62,7 @@ struct GemmParams {
 };
 
 template <int BT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(GemmCfg<BT>::kThreads, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                 const GemmParams p) {
   using Cfg = GemmCfg<BT>;
@@ -85,8 +89,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < Cfg::kAcc; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
-    for (int i = 0; i < 4; ++i) mbar_init(&epi_bar[i], 4);
+    for (int i = 0; i < Cfg::kAcc; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], Cfg::kEpiWarps); }
+    for (int i = 0; i < 4; ++i) mbar_init(&epi_bar[i], Cfg::kEpiWarps);
     *abort_flag = 0;
     *last_flag = 0;
     mbar_fence_init();
@@ -137,13 +141,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       }
     }
   } else {
-    // ----- epilogue warps: thread owns output feature n0 + q*32 + lane, all BT tokens -----
+    // ----- epilogue warps: thread owns output feature n0 + q*32 + lane and CW token columns from col0 -----
+    constexpr int CW = Cfg::kCols;
     const int q = warp & 3;
+    const int col0 = ((warp - 2) >> 2) * CW;
     const int row = q * 32 + lane;
     const int n = n0 + row;
-    float acc[BT];
+    float acc[CW];
 #pragma unroll
-    for (int t = 0; t < BT; ++t) acc[t] = 0.f;
+    for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
     const float* wsc = p.w_scale + size_t(n_tile) * kb_total;
     bool ok = true;
     for (int i = 0; i < nkb; ++i) {
@@ -153,16 +159,22 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       if (!ok) break;
       tc_fence_after();
       const float s = __ldg(wsc + kb0 + i);
-      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BT;
-      if constexpr (BT >= 32) {
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BT + col0;
+      if constexpr (CW == 64) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(taddr, r0);        // both loads in flight before the single wait
+        tmem_ld_32x32(taddr + 32, r1);
+        tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < BT; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c, r);
-          tmem_wait_ld();
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(r0[j]), s, acc[j]);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(__uint_as_float(r[j]), s, acc[c + j]);
-        }
+        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(r1[j]), s, acc[32 + j]);
+      } else if constexpr (CW == 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(r[j]), s, acc[j]);
       } else {
         uint32_t r[16];
         tmem_ld_32x16(taddr, r);
@@ -183,7 +195,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         owner = false;
         float* mine = p.ws + (size_t(split) * tiles_nt + tile_id) * (BT * kTileN);
 #pragma unroll
-        for (int t = 0; t < BT; ++t) mine[t * kTileN + row] = acc[t];
+        for (int tt = 0; tt < CW; ++tt) mine[(col0 + tt) * kTileN + row] = acc[tt];
         __threadfence();
         // bounded rendezvous of the four epilogue warps (a plain bar.sync could not time out)
         __syncwarp();
@@ -201,11 +213,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           // Sum the partials in split order (own one included, re-read from scratch) so the result does not
           // depend on which CTA happened to arrive last.  All BT loads of a split are independent.
 #pragma unroll
-          for (int t = 0; t < BT; ++t) acc[t] = 0.f;
+          for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
           for (int z = 0; z < int(gridDim.z); ++z) {
             const float* part = p.ws + (size_t(z) * tiles_nt + tile_id) * (BT * kTileN) + row;
 #pragma unroll
-            for (int t = 0; t < BT; ++t) acc[t] += __ldcg(part + t * kTileN);
+            for (int tt = 0; tt < CW; ++tt) acc[tt] += __ldcg(part + (col0 + tt) * kTileN);
           }
           if (threadIdx.x == 64) p.counters[tile_id] = 0;
           owner = true;
@@ -213,7 +225,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       }
       if (owner) {
 #pragma unroll
-        for (int t = 0; t < BT; ++t) acc[t] *= (t < tl) ? __ldg(p.x_scale + t0 + t) : 0.f;
+        for (int tt = 0; tt < CW; ++tt) acc[tt] *= (col0 + tt < tl) ? __ldg(p.x_scale + t0 + col0 + tt) : 0.f;
         if (p.ar.world > 1) {
           // ----- one-shot all-reduce over NVLink peer memory, fused into the epilogue -----
           // Every rank publishes its partial tile in its own (peer-mapped) buffer, bumps the tile's flag on every
@@ -227,7 +239,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           const size_t off = size_t((before / uint32_t(ar.world - 1)) & 1u) * ar.half_elems + size_t(tile_id) * (BT * kTileN);
           float* mine = ar.bufs[ar.rank] + off;
 #pragma unroll
-          for (int t = 0; t < BT; ++t) mine[t * kTileN + row] = acc[t];
+          for (int tt = 0; tt < CW; ++tt) mine[(col0 + tt) * kTileN + row] = acc[tt];
           __threadfence_system();
           __syncwarp();
           if (lane == 0) mbar_arrive(&epi_bar[2]);
@@ -256,24 +268,24 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           owner = met && !*abort_flag;
           if (owner) {
 #pragma unroll
-            for (int t = 0; t < BT; ++t) acc[t] = 0.f;
+            for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
             for (int r = 0; r < ar.world; ++r) {
               const float* part = ar.bufs[r] + off + row;
 #pragma unroll
-              for (int t = 0; t < BT; ++t) {
+              for (int tt = 0; tt < CW; ++tt) {
                 float v;
-                asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(part + t * kTileN) : "memory");
-                acc[t] += v;
+                asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(part + (col0 + tt) * kTileN) : "memory");
+                acc[tt] += v;
               }
             }
           }
         }
         if (owner && n < p.N) {
 #pragma unroll
-          for (int t = 0; t < BT; ++t) {
-            if (t < tl) {
-              float v = acc[t];
-              const size_t o = size_t(t0 + t) * p.N + n;
+          for (int tt = 0; tt < CW; ++tt) {
+            if (col0 + tt < tl) {
+              float v = acc[tt];
+              const size_t o = size_t(t0 + col0 + tt) * p.N + n;
               if (p.residual) v += __bfloat162float(p.residual[o]);
               p.out[o] = __float2bfloat16(v);
             }
@@ -321,7 +333,7 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
       return -6;
     attr_set = true;
   }
-  fp8_gemm_kernel<BT><<<dim3(n_tiles, t_tiles, splits), kGemmThreads, Cfg::kSmemBytes, stream>>>(tw, tx, p);
+  fp8_gemm_kernel<BT><<<dim3(n_tiles, t_tiles, splits), Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tw, tx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 

@@ -190,7 +190,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
                                      const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
                                      uint8_t* __restrict__ k_cache, uint8_t* __restrict__ v_cache,
                                      float* __restrict__ k_scale, float* __restrict__ v_scale, int T, int Hq, int Hk,
-                                     int page_size, int rot, float log2_theta) {
+                                     int page_size, int rot, float log2_theta, __nv_bfloat16* __restrict__ kd_out,
+                                     __nv_bfloat16* __restrict__ vd_out) {
   constexpr int EPL = D / 32;  // elements per lane
   const int warps_per_block = blockDim.x >> 5;
   const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -289,6 +290,17 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
       dst[(D / 2 + lane * HP + j) * page_size + pos] = to_e4m3(hi[j] * inv);
     }
   }
+  // Optional contiguous copy of what the pages now hold (code * multiplier), [T, Hk, D] bf16: the prefill attention
+  // of this chunk reads it, so prefill and later decode steps see the same FP8-rounded K/V.
+  __nv_bfloat16* dq = is_v ? vd_out : kd_out;
+  if (dq) {
+    dq += (size_t(t) * Hk + kvh) * D;
+#pragma unroll
+    for (int j = 0; j < HP; ++j) {
+      dq[lane * HP + j] = __float2bfloat16(from_e4m3(to_e4m3(lo[j] * inv)) * scale);
+      dq[D / 2 + lane * HP + j] = __float2bfloat16(from_e4m3(to_e4m3(hi[j] * inv)) * scale);
+    }
+  }
   if (lane == 0) (is_v ? v_scale : k_scale)[base] = scale;
 }
 
@@ -383,7 +395,8 @@ extern "C" int mfq_quant_rows(const void* x, void* q_out, float* scale_out, int 
 
 extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const int* slots, void* q_out, void* k_cache,
                                  void* v_cache, float* k_scale, float* v_scale, int T, int Hq, int Hk, int D,
-                                 int page_size, int rot, float theta, cudaStream_t stream) {
+                                 int page_size, int rot, float theta, void* kd_out, void* vd_out,
+                                 cudaStream_t stream) {
   if (T <= 0) return -1;
   const int warps = T * (Hq + 2 * Hk);
   const int blocks = (warps + 7) / 8;
@@ -391,7 +404,8 @@ extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const in
 #define MFQ_ROPE(DD)                                                                                             \
   rope_kv_write_kernel<DD><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, slots, \
       static_cast<__nv_bfloat16*>(q_out), static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache),      \
-      k_scale, v_scale, T, Hq, Hk, page_size, rot, l2t)
+      k_scale, v_scale, T, Hq, Hk, page_size, rot, l2t, static_cast<__nv_bfloat16*>(kd_out),                   \
+      static_cast<__nv_bfloat16*>(vd_out))
   if (D == 128) MFQ_ROPE(128);
   else if (D == 64) MFQ_ROPE(64);
   else if (D == 256) MFQ_ROPE(256);

@@ -98,13 +98,15 @@ def silu_mul_quant(gate_up: torch.Tensor, *, q_out=None, scale_out=None):
 
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, kv, *, n_q: int, n_kv: int,
-                  head_dim: int, theta: float, rot: int | None = None, q_out=None) -> torch.Tensor:
-    """Rotate Q/K, write K/V of each token into the fp8 page pool ``kv`` (a :class:`PagedKV` layer view)."""
+                  head_dim: int, theta: float, rot: int | None = None, q_out=None, kd_out=None,
+                  vd_out=None) -> torch.Tensor:
+    """Rotate Q/K, write K/V of each token into the fp8 page pool ``kv`` (a :class:`LayerKV`).  ``kd_out`` /
+    ``vd_out`` (``[T, Hk, D]`` bf16) optionally receive the values the pages now hold, for the chunk's attention."""
     t = qkv.shape[0]
     q_out = torch.empty((t, n_q, head_dim), dtype=torch.bfloat16, device=qkv.device) if q_out is None else q_out
     rc = lib().mfq_rope_kv_write(ptr(qkv), ptr(positions), ptr(slots), ptr(q_out), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale),
                                  ptr(kv.v_scale), t, n_q, n_kv, head_dim, kv.page_size, rot or head_dim, float(theta),
-                                 stream_ptr())
+                                 ptr(kd_out), ptr(vd_out), stream_ptr())
     check(rc, "rope_kv_write")
     return q_out
 
@@ -155,7 +157,21 @@ def decode_advance(sampled, input_ids, positions, seq_lens, slots, block_table, 
           "decode_advance")
 
 
-def attn_prefill(q: torch.Tensor, kv, step, *, n_kv: int, sm_scale: float) -> torch.Tensor:
-    """Causal self-attention over a packed prefill chunk; K/V are read back from the FP8 pages just written."""
-    from . import prefill_attention
-    return prefill_attention.run(q, kv, step, n_kv=n_kv, sm_scale=sm_scale)
+def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sm_scale: float, *, out=None) -> torch.Tensor:
+    """Causal attention of one sequence chunk on the tcgen05 kernel: ``q [T, Hq, 128]``, ``k/v [T, Hk, 128]``."""
+    t, hq, d = q.shape
+    out = torch.empty_like(q) if out is None else out
+    ws = Workspace.get(q.device)
+    rc = lib().mfq_attn_prefill_bf16(ptr(q), ptr(k), ptr(v), ptr(out), t, hq, k.shape[1], d, float(sm_scale), ptr(ws.status),
+                                     stream_ptr())
+    check(rc, "attn_prefill_bf16")
+    return out
+
+
+def attn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: list[int], sm_scale: float) -> torch.Tensor:
+    """Causal self-attention over a packed chunk (each sequence attends to itself)."""
+    out = torch.empty_like(q)
+    for i in range(len(cu_seqlens) - 1):
+        a, b = cu_seqlens[i], cu_seqlens[i + 1]
+        attn_prefill_bf16(q[a:b], k[a:b], v[a:b], sm_scale, out=out[a:b])
+    return out
