@@ -59,6 +59,10 @@ struct GemmParams {
   int M, N, K;
   int kb_per_split;
   ArParams ar;
+  // Grouped (mixture-of-experts) mode: blockIdx.y indexes tile_map = (expert, token tile inside the expert), rows of
+  // x / out are the expert-sorted token rows, expert e owning rows [expert_offsets[e], expert_offsets[e+1]).
+  const int2* tile_map = nullptr;
+  const int* expert_offsets = nullptr;
 };
 
 template <int BT>
@@ -81,7 +85,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, t_tile = blockIdx.y, split = blockIdx.z;
-  const int n0 = n_tile * kTileN, t0 = t_tile * BT;
+  const int n0 = n_tile * kTileN;
+  int t0 = t_tile * BT, row_end = p.M, expert = 0;
+  if (p.tile_map) {
+    const int2 tm = p.tile_map[t_tile];
+    if (tm.x < 0) return;  // padding entry of the tile map: uniform for the whole CTA, nothing allocated yet
+    expert = tm.x;
+    t0 = p.expert_offsets[expert] + tm.y * BT;
+    row_end = p.expert_offsets[expert + 1];
+  }
   const int kb_total = p.K / kBlockK;
   const int kb0 = split * p.kb_per_split;
   const int kb1 = min(kb_total, kb0 + p.kb_per_split);
@@ -114,7 +126,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         uint8_t* a = tiles + s * Cfg::kStageBytes;
         uint8_t* b = a + kTileN * kBlockK;
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
-        tma_load_2d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0);
+        if (p.tile_map) tma_load_3d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0, expert);
+        else tma_load_2d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0);
         tma_load_2d(b, &tmap_x, &full[s], (kb0 + i) * kBlockK, t0);
       }
     }
@@ -150,7 +163,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     float acc[CW];
 #pragma unroll
     for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
-    const float* wsc = p.w_scale + size_t(n_tile) * kb_total;
+    const float* wsc = p.w_scale + (size_t(expert) * gridDim.x + n_tile) * kb_total;
     bool ok = true;
     for (int i = 0; i < nkb; ++i) {
       const int buf = i % Cfg::kAcc;
@@ -187,7 +200,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
     if (ok) {
-      const int tl = min(BT, p.M - t0);
+      const int tl = min(BT, row_end - t0);
       const int tiles_nt = gridDim.x * gridDim.y;
       const int tile_id = t_tile * gridDim.x + n_tile;
       bool owner = true;  // this CTA holds the tile's complete local sum in `acc`
@@ -305,12 +318,19 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 template <int BT>
 static int launch_gemm(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
                        const void* residual, float* ws, size_t ws_bytes, int* counters, int counters_len, int* status,
-                       int M, int N, int K, int splits, cudaStream_t stream, const ArParams* ar = nullptr) {
+                       int M, int N, int K, int splits, cudaStream_t stream, const ArParams* ar = nullptr,
+                       int experts = 0, const int2* tile_map = nullptr, const int* expert_offsets = nullptr,
+                       int map_len = 0) {
   using Cfg = GemmCfg<BT>;
   CUtensorMap tw, tx;
-  if (make_tmap_2d(&tw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kTileN, kBlockK)) return -2;
+  if (experts > 0) {
+    if (make_tmap_3d(&tw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, N, experts, uint64_t(K), uint64_t(K) * N, kBlockK, kTileN, 1))
+      return -2;
+  } else if (make_tmap_2d(&tw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kTileN, kBlockK)) {
+    return -2;
+  }
   if (make_tmap_2d(&tx, x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BT, kBlockK)) return -3;
-  const int n_tiles = (N + kTileN - 1) / kTileN, t_tiles = (M + BT - 1) / BT;
+  const int n_tiles = (N + kTileN - 1) / kTileN, t_tiles = experts > 0 ? map_len : (M + BT - 1) / BT;
   const int kb_total = K / kBlockK;
   if (splits < 1) splits = 1;
   if (splits > kb_total) splits = kb_total;
@@ -321,7 +341,7 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
     if (n_tiles * t_tiles > counters_len) return -5;
   }
   GemmParams p{w_scale, x_scale, static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(residual),
-               ws, counters, status, M, N, K, kb_per, ArParams{}};
+               ws, counters, status, M, N, K, kb_per, ArParams{}, tile_map, expert_offsets};
   if (ar) {
     if (size_t(n_tiles) * t_tiles * BT * kTileN > ar->half_elems) return -8;
     p.ar = *ar;
@@ -378,6 +398,23 @@ extern "C" int mfq_fp8_gemm_allreduce(const void* w, const float* w_scale, const
     case 32: return mfq::launch_gemm<32>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
     case 64: return mfq::launch_gemm<64>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
     case 128: return mfq::launch_gemm<128>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
+    default: return -1;
+  }
+}
+
+// Grouped GEMM over expert-sorted token rows (mixture of experts): w [E, N, K] E4M3 with w_scale [E, N/128, K/128];
+// x / out rows are sorted by expert, expert e owning rows [expert_offsets[e], expert_offsets[e+1]); tile_map holds
+// map_len (expert, token-tile) pairs, entries with expert < 0 are padding.  No split-K, no residual.
+extern "C" int mfq_fp8_gemm_grouped(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
+                                    int* status, int rows, int N, int K, int experts, const void* tile_map,
+                                    const int* expert_offsets, int map_len, int token_tile, cudaStream_t stream) {
+  if (K % 128 != 0 || rows <= 0 || N <= 0 || experts <= 0 || map_len <= 0 || N % 128 != 0) return -1;
+  const int2* tm = static_cast<const int2*>(tile_map);
+  switch (token_tile) {
+    case 16: return mfq::launch_gemm<16>(w, w_scale, x, x_scale, out, nullptr, nullptr, 0, nullptr, 0, status, rows, N, K, 1, stream, nullptr, experts, tm, expert_offsets, map_len);
+    case 32: return mfq::launch_gemm<32>(w, w_scale, x, x_scale, out, nullptr, nullptr, 0, nullptr, 0, status, rows, N, K, 1, stream, nullptr, experts, tm, expert_offsets, map_len);
+    case 64: return mfq::launch_gemm<64>(w, w_scale, x, x_scale, out, nullptr, nullptr, 0, nullptr, 0, status, rows, N, K, 1, stream, nullptr, experts, tm, expert_offsets, map_len);
+    case 128: return mfq::launch_gemm<128>(w, w_scale, x, x_scale, out, nullptr, nullptr, 0, nullptr, 0, status, rows, N, K, 1, stream, nullptr, experts, tm, expert_offsets, map_len);
     default: return -1;
   }
 }

@@ -1,0 +1,293 @@
+// Mixture-of-experts routing kernels: fused router (projection + scoring + top-k), route planning (per-expert row
+// ranges + tile map for the grouped GEMM), expert-sorted gather of FP8 activation rows, and the weighted un-permute
+// that adds the expert outputs back into the residual stream.
+//
+// Reference counterparts: moe.cu (moe_topk_kernel and its specialisations, count_experts / scan_expert_counts /
+// fill_tile_experts / scatter_routes, moe_weighted_reduce*_kernel) and float_projection.cu for the router GEMV.
+#include "common.cuh"
+
+#include <cfloat>
+
+namespace mfq {
+
+constexpr int kMaxExperts = 512;
+constexpr int kMaxTopK = 16;
+
+struct RouterParams {
+  const __nv_bfloat16* x;      // [T, H]
+  const __nv_bfloat16* w;      // [E, H]
+  const float* bias;           // [E] selection bias (may be null)
+  int* topk_ids;               // [T, K]
+  float* topk_w;               // [T, K]
+  float* scores_out;           // [T, E] optional (null to skip)
+  int T, H, E, K;
+  int sigmoid;                 // 0: softmax over experts, 1: sigmoid
+  int norm_topk;               // normalise the K selected weights to sum 1
+  float scale;                 // multiplier on the final weights (routed scaling factor)
+  int n_group, topk_group;     // group-limited routing (n_group <= 1: off)
+};
+
+// One CTA per token: router logits by warp-striped dot products, scoring, optional group limiting, K rounds of block
+// arg-max (lowest index wins ties).
+__global__ void __launch_bounds__(256) moe_router_topk_kernel(const RouterParams p) {
+  extern __shared__ float sm[];
+  float* xs = sm;                 // [H]
+  float* sc = sm + p.H;           // [E] scores used for the weights
+  float* sel = sc + p.E;          // [E] scores used for selection (with bias / group mask)
+  __shared__ float red_v[8];
+  __shared__ int red_i[8];
+  __shared__ float grp[64];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < p.H; i += 256) xs[i] = __bfloat162float(p.x[size_t(t) * p.H + i]);
+  __syncthreads();
+  for (int e = warp; e < p.E; e += 8) {
+    const __nv_bfloat16* wr = p.w + size_t(e) * p.H;
+    float acc = 0.f;
+    for (int i = lane * 2; i < p.H; i += 64) {
+      const __nv_bfloat162 w2 = *reinterpret_cast<const __nv_bfloat162*>(wr + i);
+      acc = fmaf(xs[i], __bfloat162float(w2.x), acc);
+      acc = fmaf(xs[i + 1], __bfloat162float(w2.y), acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) sc[e] = acc;
+  }
+  __syncthreads();
+  if (p.sigmoid) {
+    for (int e = tid; e < p.E; e += 256) sc[e] = 1.f / (1.f + __expf(-sc[e]));
+  } else {
+    float mx = -FLT_MAX;
+    for (int e = tid; e < p.E; e += 256) mx = fmaxf(mx, sc[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red_v[warp] = mx;
+    __syncthreads();
+    mx = red_v[0];
+    for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red_v[i]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int e = tid; e < p.E; e += 256) { const float v = __expf(sc[e] - mx); sc[e] = v; sum += v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red_v[warp] = sum;
+    __syncthreads();
+    sum = 0.f;
+    for (int i = 0; i < 8; ++i) sum += red_v[i];
+    const float inv = 1.f / sum;
+    __syncthreads();
+    for (int e = tid; e < p.E; e += 256) sc[e] *= inv;
+  }
+  __syncthreads();
+  for (int e = tid; e < p.E; e += 256) {
+    sel[e] = sc[e] + (p.bias ? p.bias[e] : 0.f);
+    if (p.scores_out) p.scores_out[size_t(t) * p.E + e] = sc[e];
+  }
+  __syncthreads();
+  if (p.n_group > 1) {
+    // group score = sum of the two best selection scores of the group; keep the topk_group best groups
+    const int per = p.E / p.n_group;
+    if (tid < p.n_group) {
+      float a = -FLT_MAX, b = -FLT_MAX;
+      for (int i = 0; i < per; ++i) {
+        const float v = sel[tid * per + i];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      grp[tid] = a + b;
+    }
+    __syncthreads();
+    if (tid < p.n_group) {
+      int better = 0;
+      for (int g = 0; g < p.n_group; ++g) better += (grp[g] > grp[tid]) || (grp[g] == grp[tid] && g < tid);
+      if (better >= p.topk_group) grp[tid] = -FLT_MAX;  // dropped group
+    }
+    __syncthreads();
+    for (int e = tid; e < p.E; e += 256)
+      if (grp[e / per] == -FLT_MAX) sel[e] = -FLT_MAX;
+    __syncthreads();
+  }
+  float wsum = 0.f;
+  for (int k = 0; k < p.K; ++k) {
+    float best = -FLT_MAX;
+    int bi = 0x7fffffff;
+    for (int e = tid; e < p.E; e += 256) {
+      const float v = sel[e];
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { red_v[warp] = best; red_i[warp] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+      for (int i = 1; i < 8; ++i)
+        if (red_v[i] > best || (red_v[i] == best && red_i[i] < bi)) { best = red_v[i]; bi = red_i[i]; }
+      p.topk_ids[size_t(t) * p.K + k] = bi;
+      const float wv = sc[bi];
+      p.topk_w[size_t(t) * p.K + k] = wv;
+      wsum += wv;
+      sel[bi] = -FLT_MAX;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    const float mul = (p.norm_topk ? 1.f / fmaxf(wsum, 1e-20f) : 1.f) * p.scale;
+    for (int k = 0; k < p.K; ++k) p.topk_w[size_t(t) * p.K + k] *= mul;
+  }
+}
+
+// Route plan for the experts [e_lo, e_hi) owned by this rank (one CTA).  Row order inside an expert depends on atomic
+// arrival order; results do not, because each row is computed independently and the un-permute sums a token's K
+// contributions in slot order.
+//   offsets[e - e_lo]   first sorted row of local expert e (offsets[n_local] = total rows)
+//   dest[t*K + k]       sorted row of that (token, slot) pair, -1 if its expert lives on another rank
+//   src_token[row]      token of the sorted row
+//   tile_map[i]         (local expert, token tile inside it) for the grouped GEMM; padded with (-1, -1)
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ topk_ids, int entries, int K, int e_lo,
+                                                        int e_hi, int token_tile, int* __restrict__ offsets,
+                                                        int* __restrict__ dest, int* __restrict__ src_token,
+                                                        int2* __restrict__ tile_map, int map_cap,
+                                                        int* __restrict__ totals) {
+  __shared__ int cnt[kMaxExperts + 1];
+  __shared__ int fill[kMaxExperts];
+  __shared__ int tbase[kMaxExperts + 1];
+  const int n_local = e_hi - e_lo;
+  for (int e = threadIdx.x; e <= n_local; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = topk_ids[i] - e_lo;
+    if (e >= 0 && e < n_local) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0, tiles = 0;
+    for (int e = 0; e < n_local; ++e) {
+      const int c = cnt[e];
+      offsets[e] = run;
+      fill[e] = run;
+      tbase[e] = tiles;
+      run += c;
+      tiles += (c + token_tile - 1) / token_tile;
+    }
+    offsets[n_local] = run;
+    tbase[n_local] = tiles;
+    totals[0] = run;
+    totals[1] = tiles;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = topk_ids[i] - e_lo;
+    int row = -1;
+    if (e >= 0 && e < n_local) {
+      row = atomicAdd(&fill[e], 1);
+      src_token[row] = i / K;
+    }
+    dest[i] = row;
+  }
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) {
+    const int n = tbase[e + 1] - tbase[e];
+    for (int j = 0; j < n; ++j)
+      if (tbase[e] + j < map_cap) tile_map[tbase[e] + j] = make_int2(e, j);
+  }
+  __syncthreads();
+  for (int i = tbase[n_local] + threadIdx.x; i < map_cap; i += blockDim.x) tile_map[i] = make_int2(-1, -1);
+}
+
+// Expert-sorted copy of already quantized activation rows: xq_sorted[row] = xq[src_token[row]] (+ its multiplier).
+__global__ void moe_gather_rows_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs,
+                                       const int* __restrict__ src_token, const int* __restrict__ totals,
+                                       uint8_t* __restrict__ out_q, float* __restrict__ out_s, int H) {
+  const int row = blockIdx.x;
+  if (row >= totals[0]) return;
+  const int t = src_token[row];
+  const uint4* src = reinterpret_cast<const uint4*>(xq + size_t(t) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out_q + size_t(row) * H);
+  for (int i = threadIdx.x; i < H / 16; i += blockDim.x) dst[i] = src[i];
+  if (threadIdx.x == 0) out_s[row] = xs[t];
+}
+
+// out[t] = base[t] (+ extra[t]) + sum_k w[t,k] * y[dest[t,k]]   (rows with dest < 0 are skipped)
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ dest,
+                                   const float* __restrict__ topk_w, const __nv_bfloat16* __restrict__ base,
+                                   const __nv_bfloat16* __restrict__ extra, __nv_bfloat16* __restrict__ out, int H,
+                                   int K) {
+  const int t = blockIdx.x;
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (base) {
+      const uint4 b = *reinterpret_cast<const uint4*>(base + size_t(t) * H + v * 8);
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = __bfloat162float(bb[j]);
+    }
+    if (extra) {
+      const uint4 b = *reinterpret_cast<const uint4*>(extra + size_t(t) * H + v * 8);
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(bb[j]);
+    }
+    for (int k = 0; k < K; ++k) {
+      const int row = dest[size_t(t) * K + k];
+      if (row < 0) continue;
+      const float w = topk_w[size_t(t) * K + k];
+      const uint4 b = *reinterpret_cast<const uint4*>(y + size_t(row) * H + v * 8);
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(w, __bfloat162float(bb[j]), acc[j]);
+    }
+    uint4 o;
+    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ob[j] = __float2bfloat16(acc[j]);
+    *reinterpret_cast<uint4*>(out + size_t(t) * H + v * 8) = o;
+  }
+}
+
+}  // namespace mfq
+
+using namespace mfq;
+
+extern "C" int mfq_moe_router_topk(const void* x, const void* w, const float* bias, int* topk_ids, float* topk_w,
+                                   float* scores_out, int T, int H, int E, int K, int sigmoid, int norm_topk, float scale,
+                                   int n_group, int topk_group, cudaStream_t stream) {
+  if (T <= 0 || E > kMaxExperts || K > kMaxTopK || K > E || H % 2 || n_group > 64 || (n_group > 1 && E % n_group)) return -1;
+  RouterParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), bias, topk_ids, topk_w,
+                 scores_out, T, H, E, K, sigmoid, norm_topk, scale, n_group, topk_group};
+  const size_t smem = size_t(H + 2 * E) * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    if (cudaFuncSetAttribute(moe_router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -6;
+    configured = smem;
+  }
+  moe_router_topk_kernel<<<T, 256, smem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_moe_plan(const int* topk_ids, int T, int K, int e_lo, int e_hi, int token_tile, int* offsets, int* dest,
+                            int* src_token, void* tile_map, int map_cap, int* totals, cudaStream_t stream) {
+  if (e_hi - e_lo > kMaxExperts || e_hi <= e_lo || T <= 0) return -1;
+  moe_plan_kernel<<<1, 1024, 0, stream>>>(topk_ids, T * K, K, e_lo, e_hi, token_tile, offsets, dest, src_token,
+                                          static_cast<int2*>(tile_map), map_cap, totals);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_moe_gather_rows(const void* xq, const float* xs, const int* src_token, const int* totals, void* out_q,
+                                   float* out_s, int max_rows, int H, cudaStream_t stream) {
+  if (H % 16 || max_rows <= 0) return -1;
+  moe_gather_rows_kernel<<<max_rows, 128, 0, stream>>>(static_cast<const uint8_t*>(xq), xs, src_token, totals,
+                                                       static_cast<uint8_t*>(out_q), out_s, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_moe_combine(const void* y, const int* dest, const float* topk_w, const void* base, const void* extra,
+                               void* out, int T, int H, int K, cudaStream_t stream) {
+  if (H % 8 || T <= 0) return -1;
+  moe_combine_kernel<<<T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), dest, topk_w,
+                                            static_cast<const __nv_bfloat16*>(base),
+                                            static_cast<const __nv_bfloat16*>(extra), static_cast<__nv_bfloat16*>(out), H, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}

@@ -1,0 +1,68 @@
+"""MoE kernels (router top-k, route plan, grouped FP8 GEMM, combine) against PyTorch references."""
+
+import pytest
+import torch
+
+from mfq_b200.ops import moe
+from mfq_b200.ops import reference as ref
+from mfq_b200.quantize.fp8_block import quantize_fp8_block_torch
+from gpu_common import assert_close, check_status, require_gpu_lib
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("t,h,e,k,sig,ng,tg", [(5, 256, 8, 2, False, 1, 1), (33, 2048, 512, 10, False, 1, 1),
+                                               (17, 1024, 256, 8, True, 8, 4), (1, 512, 64, 6, True, 1, 1)])
+def test_router_topk(t, h, e, k, sig, ng, tg):
+    require_gpu_lib()
+    g = torch.Generator(device="cuda").manual_seed(e)
+    x = torch.randn((t, h), generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn((e, h), generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    bias = torch.randn(e, generator=g, device="cuda") * 0.1 if sig else None
+    ids, wt, scores = moe.router_topk(x, w, k, bias=bias, sigmoid=sig, n_group=ng, topk_group=tg, scale=2.5 if sig else 1.0,
+                                      want_scores=True)
+    logits = x.float() @ w.float().T
+    s = torch.sigmoid(logits) if sig else torch.softmax(logits, -1)
+    assert_close(scores, s, rel=2e-3, what="scores")
+    sel = scores + (bias if bias is not None else 0)  # selection on the kernel's own scores avoids near-tie flips
+    if ng > 1:
+        per = e // ng
+        gs = sel.view(t, ng, per).topk(2, -1).values.sum(-1)
+        keep = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, gs.topk(tg, -1).indices, True)
+        sel = sel.masked_fill(~keep.repeat_interleave(per, 1), float("-inf"))
+    want_ids = sel.topk(k, -1).indices
+    assert torch.equal(ids.long().sort(-1).values, want_ids.sort(-1).values)
+    want_w = scores.gather(1, ids.long())
+    want_w = want_w / want_w.sum(-1, keepdim=True) * (2.5 if sig else 1.0)
+    assert_close(wt, want_w, rel=1e-4, what="weights")
+
+
+@pytest.mark.parametrize("t,e,k,e_lo,e_hi", [(7, 8, 2, 0, 8), (300, 64, 6, 16, 32), (64, 256, 8, 224, 256)])
+def test_moe_ffn_matches_reference(t, e, k, e_lo, e_hi):
+    require_gpu_lib()
+    h, inter = 512, 256
+    g = torch.Generator(device="cuda").manual_seed(t)
+    x = torch.randn((t, h), generator=g, device="cuda").to(torch.bfloat16)
+    n_local = e_hi - e_lo
+    gu_f = (torch.randn((n_local, 2 * inter, h), generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    dn_f = (torch.randn((n_local, h, inter), generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    gu_q, gu_s = zip(*[quantize_fp8_block_torch(m) for m in gu_f])
+    dn_q, dn_s = zip(*[quantize_fp8_block_torch(m) for m in dn_f])
+    gu_q, gu_s, dn_q, dn_s = torch.stack(gu_q), torch.stack(gu_s), torch.stack(dn_q), torch.stack(dn_s)
+    ids = torch.stack([torch.randperm(e, generator=g, device="cuda")[:k] for _ in range(t)]).to(torch.int32)
+    wt = torch.rand((t, k), generator=g, device="cuda")
+    base = torch.randn((t, h), generator=g, device="cuda").to(torch.bfloat16)
+    xq, xs = ref.quant_rows(x)
+    got = moe.moe_ffn_fp8(xq, xs, ids, wt, gu_q, gu_s, dn_q, dn_s, e_lo=e_lo, base=base)
+    check_status()
+    want = base.float().clone()
+    xd = xq.float() * xs[:, None]
+    for le in range(n_local):
+        tok, slot = (ids == e_lo + le).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        gu = (xd[tok] @ ref.dequant_block(gu_q[le], gu_s[le]).T).to(torch.bfloat16)
+        hq, hs = ref.silu_mul_quant(gu)
+        y = ((hq.float() * hs[:, None]) @ ref.dequant_block(dn_q[le], dn_s[le]).T).to(torch.bfloat16).float()
+        want.index_add_(0, tok, y * wt[tok, slot][:, None])
+    assert_close(got, want, rel=2e-2, what="moe ffn")
