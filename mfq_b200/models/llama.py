@@ -229,6 +229,14 @@ class LlamaModel:
             outs.append(ref.attention(q[a:b], kk, vv, self.sm_scale, causal_offset=0))
         return torch.cat(outs, 0).reshape(t, self.hq * d)
 
+    # -- feed-forward -------------------------------------------------------------------------------------------
+    def _ffn(self, h, layer):
+        """Dense SwiGLU block: ``h + down(silu(gate(x)) * up(x))`` with ``x = rmsnorm(h)``."""
+        xq, xs = self._norm_quant(h, layer.mlp_norm)
+        gu = layer.gate_up(xq, xs)
+        hq_, hs = self._silu_quant(gu)
+        return self._row_parallel(layer.down, hq_, hs, h)
+
     # -- forward ------------------------------------------------------------------------------------------------
     def forward(self, step: StepBuffers, cache, *, prefill: bool, logits_rows: torch.Tensor | None = None,
                 gather_logits: bool = True):
@@ -244,10 +252,7 @@ class LlamaModel:
             attn = self._attention(qkv, kv, step, prefill)
             aq, a_s = self._quant(attn)
             h = self._row_parallel(layer.o_proj, aq, a_s, h)
-            xq, xs = self._norm_quant(h, layer.mlp_norm)
-            gu = layer.gate_up(xq, xs)
-            hq_, hs = self._silu_quant(gu)
-            h = self._row_parallel(layer.down, hq_, hs, h)
+            h = self._ffn(h, layer)
         if logits_rows is not None:
             h = h[logits_rows.long()] if not h.is_cuda else h.index_select(0, logits_rows.long())
         xq, xs = self._norm_quant(h, w.final_norm)

@@ -1,0 +1,195 @@
+"""Mixture-of-experts decoder on the GPU kernels: tensor-parallel attention, expert-parallel routed experts.
+
+Layout under ``W`` ranks (one process per GPU): attention heads, the shared expert and dense FFN layers are
+tensor-parallel exactly like :class:`~mfq_b200.models.llama.LlamaModel`; rank ``r`` additionally owns the routed
+experts ``[r*E/W, (r+1)*E/W)``.  The residual stream is replicated, so every rank routes all tokens itself and
+only gathers rows for its own experts; the weighted expert outputs (+ the shared expert's partial) of all ranks are
+summed by the fused row all-reduce, which also adds the residual.  The reference broadcasts hidden states and
+routes to every GPU and reduces partial outputs to a primary GPU (``cpp_runtime/backends/cuda/core/ffn.cpp:201-300``).
+
+Weights of any checkpoint family (NINT, NVQ, MXFP4, FP8-128SQ, bf16; MFE pools for the experts) are transcoded at
+load time to E4M3 with 128x128 fp32 block multipliers -- the one format the tensor-core GEMMs consume -- which at
+B200 memory sizes (180 GB per GPU) holds even the 671B configuration at EP=8.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from .. import formats as F
+from .. import ops
+from ..ops import moe as moe_ops
+from ..ops import reference as ref
+from ..quantize.fp8_block import quantize_fp8_block_torch
+from .llama import Fp8Linear, LlamaConfig, LlamaLayer, LlamaModel, LlamaWeights
+
+
+@dataclass
+class MoeDecoderConfig(LlamaConfig):
+    num_experts: int = 8
+    top_k: int = 2
+    moe_intermediate: int = 128
+    shared_intermediate: int = 0
+    router: str = "softmax"  # "softmax" | "sigmoid"
+    norm_topk: bool = True
+    routed_scale: float = 1.0
+    n_group: int = 1
+    topk_group: int = 1
+    first_dense_layers: int = 0  # leading layers that use the dense FFN (DeepSeek-style)
+    name: str = "moe-fp8"
+
+    @classmethod
+    def tiny(cls) -> "MoeDecoderConfig":
+        return cls(vocab_size=1024, hidden_size=256, intermediate_size=512, num_layers=2, num_heads=4, num_kv_heads=2,
+                   head_dim=128, rope_theta=1e6, rms_eps=1e-6, num_experts=8, top_k=2, moe_intermediate=128,
+                   shared_intermediate=128, name="tiny-moe-fp8")
+
+
+@dataclass
+class MoeFfn:
+    router: torch.Tensor  # [E, H] bf16
+    router_bias: torch.Tensor | None
+    gate_up: torch.Tensor  # [E_local, 2I, H] fp8
+    gate_up_scale: torch.Tensor
+    down: torch.Tensor  # [E_local, H, I] fp8
+    down_scale: torch.Tensor
+    shared_gate_up: Fp8Linear | None = None
+    shared_down: Fp8Linear | None = None
+    e_lo: int = 0
+    shared_replicated: bool = False  # shared expert too narrow to shard on 128-wide blocks: every rank holds all of it
+
+
+@dataclass
+class MoeLayer(LlamaLayer):
+    moe: MoeFfn | None = None
+
+
+def _stack_fp8(mats: list[torch.Tensor]) -> tuple[torch.Tensor, torch.Tensor]:
+    qs, ss = zip(*[quantize_fp8_block_torch(m) for m in mats])
+    return torch.stack(qs).contiguous(), torch.stack(ss).contiguous()
+
+
+def _to_float(t, device) -> torch.Tensor:
+    """Any checkpoint tensor object -> float32 torch tensor on ``device`` (decode on the host, upload)."""
+    return torch.from_numpy(np.ascontiguousarray(F.dequantize(t))).to(device=device, dtype=torch.float32)
+
+
+class MoeWeights(LlamaWeights):
+    @classmethod
+    def from_tensors(cls, cfg: MoeDecoderConfig, tensors, device, tp_rank: int = 0, tp_size: int = 1) -> "MoeWeights":
+        """Build rank-local FP8 weights from checkpoint tensors under canonical names (a dict or an ``MfqStore``)."""
+        dev = torch.device(device)
+        h, d, w = cfg.hidden_size, cfg.head_dim, tp_size
+        hq, hk = cfg.num_heads, cfg.num_kv_heads
+
+        def get(name):
+            return _to_float(tensors[name], dev)
+
+        def rows(x, parts):
+            return x.reshape(w, parts // w, -1)[tp_rank] if w > 1 else x
+
+        def cols(x, parts):
+            return x.reshape(x.shape[0], w, parts // w)[:, tp_rank].contiguous() if w > 1 else x
+
+        def norm(name):
+            return get(name).to(torch.bfloat16)
+
+        layers = []
+        e_per = cfg.num_experts // w
+        e_lo = tp_rank * e_per
+        for i in range(cfg.num_layers):
+            p = f"model.block.{i}."
+            qkv = torch.cat([rows(get(p + "attention.query.weight"), hq * d), rows(get(p + "attention.key.weight"), hk * d),
+                             rows(get(p + "attention.value.weight"), hk * d)], 0)
+            o = cols(get(p + "attention.output.weight"), hq * d)
+            layer = MoeLayer(attn_norm=norm(p + "attention.norm.weight"), qkv=Fp8Linear.from_float(qkv),
+                             o_proj=Fp8Linear.from_float(o), mlp_norm=norm(p + "mlp.norm.weight"), gate_up=None, down=None)
+            if (p + "mlp.router.weight") in tensors:
+                gate = get(p + "mlp.experts.gate.weight")[e_lo : e_lo + e_per]
+                up = get(p + "mlp.experts.up.weight")[e_lo : e_lo + e_per]
+                down = get(p + "mlp.experts.down.weight")[e_lo : e_lo + e_per]
+                gu_q, gu_s = _stack_fp8([torch.cat([gate[e], up[e]], 0) for e in range(e_per)])
+                dn_q, dn_s = _stack_fp8([down[e] for e in range(e_per)])
+                bias_name = p + "mlp.router.bias"
+                ffn = MoeFfn(router=norm(p + "mlp.router.weight"),
+                             router_bias=get(bias_name) if bias_name in tensors else None,
+                             gate_up=gu_q, gate_up_scale=gu_s, down=dn_q, down_scale=dn_s, e_lo=e_lo)
+                if (p + "mlp.shared_expert.gate.weight") in tensors:
+                    si = cfg.shared_intermediate
+                    sg, su, sd = (get(p + f"mlp.shared_expert.{n}.weight") for n in ("gate", "up", "down"))
+                    if w > 1 and (si // w) % 128 == 0:
+                        sg, su, sd = rows(sg, si), rows(su, si), cols(sd, si)
+                    else:
+                        ffn.shared_replicated = w > 1
+                    ffn.shared_gate_up = Fp8Linear.from_float(torch.cat([sg, su], 0))
+                    ffn.shared_down = Fp8Linear.from_float(sd)
+                layer.moe = ffn
+            else:
+                i_ = cfg.intermediate_size
+                layer.gate_up = Fp8Linear.from_float(torch.cat([rows(get(p + "mlp.gate.weight"), i_), rows(get(p + "mlp.up.weight"), i_)], 0))
+                layer.down = Fp8Linear.from_float(cols(get(p + "mlp.down.weight"), i_))
+            layers.append(layer)
+        head = rows(get("model.output.weight"), cfg.vocab_size)
+        return cls(get("model.token_embedding.weight").to(torch.bfloat16), layers, norm("model.output_norm.weight"),
+                   Fp8Linear.from_float(head), tp_rank, tp_size)
+
+
+class MoeDecoderModel(LlamaModel):
+    """:class:`LlamaModel` whose FFN is a routed mixture of experts wherever the layer carries one."""
+
+    def _ffn(self, h, layer):
+        ffn = getattr(layer, "moe", None)
+        if ffn is None:
+            return super()._ffn(h, layer)
+        cfg = self.cfg
+        if not h.is_cuda:
+            return self._ffn_reference(h, layer, ffn)
+        xq, xs, y, _ = ops.rmsnorm_quant(h, layer.mlp_norm, cfg.rms_eps, want_y=True)
+        ids, wt = moe_ops.router_topk(y, ffn.router, cfg.top_k, bias=ffn.router_bias, sigmoid=cfg.router == "sigmoid",
+                                      norm_topk=cfg.norm_topk, scale=cfg.routed_scale, n_group=cfg.n_group,
+                                      topk_group=cfg.topk_group)
+        shared = None
+        if ffn.shared_gate_up is not None and not (ffn.shared_replicated and self.w.tp_rank != 0):
+            sq, ss = ops.silu_mul_quant(ffn.shared_gate_up(xq, xs))
+            shared = ffn.shared_down(sq, ss)  # this rank's partial of the shared expert (rank 0's whole, if replicated)
+        if self.tp == 1:
+            return moe_ops.moe_ffn_fp8(xq, xs, ids, wt, ffn.gate_up, ffn.gate_up_scale, ffn.down, ffn.down_scale,
+                                       e_lo=ffn.e_lo, base=h, extra=shared, out=h)
+        partial = moe_ops.moe_ffn_fp8(xq, xs, ids, wt, ffn.gate_up, ffn.gate_up_scale, ffn.down, ffn.down_scale,
+                                      e_lo=ffn.e_lo, base=None, extra=shared)
+        return self.collective.allreduce_rows(partial, h)
+
+    def _ffn_reference(self, h, layer, ffn: MoeFfn):
+        """fp32 restatement of the GPU path (same FP8 rounding points), single rank."""
+        cfg = self.cfg
+        xq, xs, y, _ = ref.rmsnorm_quant(h, layer.mlp_norm, cfg.rms_eps)
+        logits = y.float() @ ffn.router.float().T
+        scores = torch.sigmoid(logits) if cfg.router == "sigmoid" else torch.softmax(logits, -1)
+        sel = scores + (ffn.router_bias if ffn.router_bias is not None else 0)
+        if cfg.n_group > 1:
+            per = cfg.num_experts // cfg.n_group
+            gs = sel.view(-1, cfg.n_group, per).topk(2, -1).values.sum(-1)
+            keep = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, gs.topk(cfg.topk_group, -1).indices, True)
+            sel = sel.masked_fill(~keep.repeat_interleave(per, 1), float("-inf"))
+        ids = sel.topk(cfg.top_k, -1).indices
+        wt = scores.gather(1, ids)
+        if cfg.norm_topk:
+            wt = wt / wt.sum(-1, keepdim=True).clamp_min(1e-20)
+        wt = wt * cfg.routed_scale
+        out = h.float().clone()
+        xd = xq.float() * xs[:, None]
+        for le in range(ffn.gate_up.shape[0]):
+            tok, slot = (ids == ffn.e_lo + le).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            gu = (xd[tok] @ ref.dequant_block(ffn.gate_up[le], ffn.gate_up_scale[le]).T).to(torch.bfloat16)
+            hq, hs = ref.silu_mul_quant(gu)
+            ye = ((hq.float() * hs[:, None]) @ ref.dequant_block(ffn.down[le], ffn.down_scale[le]).T).to(torch.bfloat16)
+            out.index_add_(0, tok, ye.float() * wt[tok, slot][:, None])
+        if ffn.shared_gate_up is not None:
+            sq, ss = ref.silu_mul_quant(ffn.shared_gate_up(xq, xs))
+            out += ffn.shared_down(sq, ss).float()
+        return out.to(torch.bfloat16)

@@ -110,3 +110,105 @@ extern "C" int mfq_argmax_allgather(const void* logits, int* out, int B, int V, 
                                                         index_offset, ap, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// allreduce_rows: out[row] = residual[row] + sum over ranks of partial_r[row], one CTA per row, over peer-mapped
+// buffers with the same count-up flag protocol (graph-replay safe, double-buffered).  Used where a layer's partial
+// result is produced by a non-GEMM kernel, e.g. the expert-parallel MoE combine (each rank holds the weighted sum
+// of its own experts).  The reference reduces such partials to its primary GPU with ncclReduce
+// (cpp_runtime/backends/cuda/ops/quant_linear.cpp:629-742).
+// ---------------------------------------------------------------------------------------------------------------
+namespace mfq {
+
+struct RowReduceParams {
+  int world, rank;
+  __nv_bfloat16* bufs[8];   // per rank: [2][rows_cap][H]
+  uint32_t* flags[8];       // per rank: [rows_cap]
+  uint32_t* expected;       // local [rows_cap]
+  int rows_cap;
+};
+
+__global__ void __launch_bounds__(256)
+allreduce_rows_kernel(const __nv_bfloat16* __restrict__ partial, const __nv_bfloat16* __restrict__ residual,
+                      __nv_bfloat16* __restrict__ out, int H, RowReduceParams rp, int* status) {
+  __shared__ int s_ok;
+  const int row = blockIdx.x;
+  const uint32_t before = rp.expected[row];
+  const uint32_t target = before + uint32_t(rp.world - 1);
+  const size_t off = (size_t((before / uint32_t(rp.world - 1)) & 1u) * rp.rows_cap + row) * H;
+  const int nvec = H / 8;
+  uint4* mine = reinterpret_cast<uint4*>(rp.bufs[rp.rank] + off);
+  const uint4* src = reinterpret_cast<const uint4*>(partial + size_t(row) * H);
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) mine[v] = src[v];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < rp.world; ++r)
+      if (r != rp.rank) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(rp.flags[r] + row) : "memory");
+    const uint32_t* my_flag = rp.flags[rp.rank] + row;
+    const unsigned long long t_start = globaltimer_ns();
+    uint32_t seen, spins = 0;
+    int ok = 1;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
+      if (int32_t(seen - target) >= 0) break;
+      if ((++spins & 0x3F) == 0 && globaltimer_ns() - t_start > kWaitBudgetNs) {
+        atomicCAS(status, 0, kStatusTimeoutPeer);
+        ok = 0;
+        break;
+      }
+    }
+    rp.expected[row] = target;
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (residual) {
+      const uint4 b = *reinterpret_cast<const uint4*>(residual + size_t(row) * H + v * 8);
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = __bfloat162float(bb[j]);
+    }
+    for (int r = 0; r < rp.world; ++r) {
+      uint4 b;
+      const uint4* p = reinterpret_cast<const uint4*>(rp.bufs[r] + off) + v;
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p) : "memory");
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(bb[j]);
+    }
+    uint4 o;
+    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ob[j] = __float2bfloat16(acc[j]);
+    *reinterpret_cast<uint4*>(out + size_t(row) * H + v * 8) = o;
+  }
+}
+
+}  // namespace mfq
+
+// partial / residual / out: [rows, H] bf16 (residual may be null; out may alias residual).  bufs[r]: rank r's
+// 2 * rows_cap * H bf16 staging buffer, flags[r]: rows_cap counters (zero before first use).
+extern "C" int mfq_allreduce_rows(const void* partial, const void* residual, void* out, int rows, int H, int world,
+                                  int rank, void* const* bufs, void* const* flags, void* expected, int rows_cap,
+                                  int* status, cudaStream_t stream) {
+  if (rows <= 0 || rows > rows_cap || H % 8 || world < 2 || world > 8) return -1;
+  mfq::RowReduceParams rp{};
+  rp.world = world;
+  rp.rank = rank;
+  for (int r = 0; r < world; ++r) {
+    rp.bufs[r] = static_cast<__nv_bfloat16*>(bufs[r]);
+    rp.flags[r] = static_cast<uint32_t*>(flags[r]);
+  }
+  rp.expected = static_cast<uint32_t*>(expected);
+  rp.rows_cap = rows_cap;
+  mfq::allreduce_rows_kernel<<<rows, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(partial),
+                                                       static_cast<const __nv_bfloat16*>(residual),
+                                                       static_cast<__nv_bfloat16*>(out), H, rp, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}

@@ -11,6 +11,7 @@ baseline (library collectives after an unfused GEMM), kept for A/B measurements.
 
 from __future__ import annotations
 
+import ctypes as C
 import math
 
 import torch
@@ -71,6 +72,30 @@ class TensorParallel:
         check(rc, "argmax_allgather")
         return out
 
+    def allreduce_rows(self, partial: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        """``h += sum over ranks of partial`` in place (one fused kernel over peer memory)."""
+        rows, width = partial.shape
+        key = ("rows", width)
+        ctx = self._ctx.get(key)
+        if ctx is None:
+            cap = self.rows_cap
+
+            class _RowCtx:
+                pass
+            ctx = _RowCtx()
+            ctx.bufs = PeerBuffer(self.group, 2 * cap * width * 2, self.device)
+            ctx.flags = PeerBuffer(self.group, cap * 4, self.device)
+            ctx.expected = torch.zeros(cap, dtype=torch.int32, device=self.device)
+            ctx.buf_table, ctx.flag_table = ctx.bufs.table(), ctx.flags.table()
+            self._ctx[key] = ctx
+        ws = Workspace.get(self.device)
+        fn = lib().mfq_allreduce_rows
+        fn.argtypes = [C.c_void_p] * 3 + [C.c_int] * 4 + [C.c_void_p] * 3 + [C.c_int, C.c_void_p, C.c_void_p]
+        rc = fn(ptr(partial), ptr(h), ptr(h), rows, width, self.world, self.rank, ctx.buf_table, ctx.flag_table,
+                ptr(ctx.expected), self.rows_cap, ptr(ws.status), stream_ptr())
+        check(rc, "allreduce_rows")
+        return h
+
     def gather_columns(self, shard: torch.Tensor) -> torch.Tensor:
         """Full ``[rows, W * cols]`` matrix from column shards (library all-gather; used off the hot path)."""
         parts = [torch.empty_like(shard) for _ in range(self.world)]
@@ -80,6 +105,12 @@ class TensorParallel:
 
 class NcclTensorParallel(TensorParallel):
     """Baseline: unfused GEMM followed by NCCL all-reduce / all-gather (what a library-only port would do)."""
+
+    def allreduce_rows(self, partial, h):
+        total = partial.float()
+        dist.all_reduce(total, group=self.group)
+        h.copy_((total + h.float()).to(torch.bfloat16))
+        return h
 
     def row_parallel_linear(self, lin, x_q, x_scale, h):
         partial = K.fp8_gemm(x_q, x_scale, lin.q, lin.scale).float()

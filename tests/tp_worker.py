@@ -62,6 +62,23 @@ def main() -> None:
     result["ranks_agree"] = all(torch.equal(g, gathered[0]) for g in gathered)
     eager = LLMEngine(LlamaModel(cfg, w, collective=tp), max_batch=4, max_seq_len=128, use_graphs=False)
     result["graph_equals_eager"] = bool(torch.equal(eager.generate(prompts, 10).tokens.to(dev), toks))
+    # expert parallelism: routed experts split over the ranks, shared expert and attention tensor-parallel
+    from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from mfq_b200.models.moe_lm import MoeConfig, init_weights, quantize_moe_checkpoint
+    mcfg = MoeDecoderConfig.tiny()
+    ck = quantize_moe_checkpoint(init_weights(MoeConfig(head_dim=128, hidden_size=256, moe_intermediate=128,
+                                                        shared_intermediate=128), seed=4, std=0.05), "NINT4,NVQ3,MXFP4")
+    ep_model = MoeDecoderModel(mcfg, MoeWeights.from_tensors(mcfg, ck, dev, rank, world), collective=tp)
+    ep_engine = LLMEngine(ep_model, max_batch=4, max_seq_len=128)
+    ep_logits = prefill_logits(ep_model, ep_engine, prompt, dev)
+    one_model = MoeDecoderModel(mcfg, MoeWeights.from_tensors(mcfg, ck, dev))
+    one_logits = prefill_logits(one_model, LLMEngine(one_model, max_batch=4, max_seq_len=128, use_graphs=False), prompt, dev)
+    result["ep_vs_single_max_err"] = float((ep_logits - one_logits).abs().max())
+    result["ep_logit_scale"] = float(one_logits.abs().max())
+    ep_toks = ep_engine.generate(prompts, 6).tokens.to(dev)
+    gathered = [torch.empty_like(ep_toks) for _ in range(world)]
+    dist.all_gather(gathered, ep_toks)
+    result["ep_ranks_agree"] = all(torch.equal(g, gathered[0]) for g in gathered)
     torch.cuda.synchronize()
     Workspace.get(dev).check()
     dist.barrier()
