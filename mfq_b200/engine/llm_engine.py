@@ -1,14 +1,19 @@
-"""In-process generation engine: chunked prefill, CUDA-graph decode, greedy sampling.
+"""In-process generation engine: prefill, CUDA-graph decode, greedy and stochastic sampling, row management.
 
 The decode step is captured once per batch bucket.  Everything a step needs lives on the device: the sampled
 token feeds the next step, positions / sequence lengths / KV slots are advanced by a kernel inside the graph,
-so replaying the graph needs no host work and the host reads tokens back only when it wants them.  (The
-reference replays its decode graph and then synchronizes on ``static_next.item()`` once per token,
-``cpp_runtime/backends/cuda/engine/generation.cpp:304-339``.)
+rows that are not generating are masked by a device-side ``active`` vector, so replaying the graph needs no host
+work and the host reads tokens back only when it wants them.  (The reference replays its decode graph and then
+synchronizes on ``static_next.item()`` once per token, ``cpp_runtime/backends/cuda/engine/generation.cpp:304-339``;
+its batch graphs are cached per row bucket {1,2,4,8,16,32}, ``runtime/batch_decode_graph.h:14-24``.)
+
+The class also implements the backend protocol of :class:`~mfq_b200.engine.scheduler.ContinuousBatchScheduler`
+(``prefill`` / ``decode`` / ``can_grow`` / ``release`` / capacity queries).
 """
 
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 
 import torch
@@ -17,7 +22,14 @@ from .. import ops
 from ..models.llama import LlamaModel, StepBuffers
 from .kv_cache import PAGE_SIZE, PagedKVCache
 
-BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128)
+BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+def bucket_for(n: int) -> int:
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    return n
 
 
 @dataclass
@@ -31,13 +43,12 @@ class GenerationResult:
 
 class LLMEngine:
     def __init__(self, model: LlamaModel, *, max_batch: int = 64, max_seq_len: int = 8192, num_pages: int | None = None,
-                 device=None, use_graphs: bool = True, prefill_chunk: int = 8192) -> None:
+                 device=None, use_graphs: bool = True) -> None:
         self.model = model
         cfg = model.cfg
         self.device = torch.device(device) if device is not None else model.w.embed.device
         self.max_batch = max_batch
         self.max_seq_len = max_seq_len
-        self.prefill_chunk = prefill_chunk
         pages_per_seq = (max_seq_len + PAGE_SIZE - 1) // PAGE_SIZE
         if num_pages is None:
             num_pages = max_batch * pages_per_seq + 1
@@ -49,71 +60,174 @@ class LLMEngine:
         self.seq_lens = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.slots = torch.full((max_batch,), -1, dtype=torch.int32, device=dev)
         self.sampled = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self.active = torch.ones(max_batch, dtype=torch.int32, device=dev)
+        # per-row sampling record, 32 bytes: temperature f32, top_k i32, top_p f32, presence f32, frequency f32,
+        # repetition f32, seed u64 (the layout the sampling kernel reads)
+        self.sample_rows = torch.zeros((max_batch, 8), dtype=torch.int32, device=dev)
+        self.sample_work: torch.Tensor | None = None
         self.use_graphs = use_graphs and dev.type == "cuda"
-        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
-        self._next_seq_id = 0
+        self.graphs: dict[tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self.launches_per_step: dict[int, int] = {}
+        self.row_seq: dict[int, int] = {}
+        self.row_len: dict[int, int] = {}  # host mirror of seq_lens for page management
+        self.row_stochastic: dict[int, bool] = {}
+        self._next_seq_id = 0
+
+    # -- capacity (scheduler backend protocol) ------------------------------------------------------------------
+    def free_tokens(self) -> int:
+        return self.cache.allocator.free_pages * self.cache.page_size
+
+    def tokens_needed(self, tokens: int) -> int:
+        ps = self.cache.page_size
+        return (tokens + ps - 1) // ps * ps
+
+    def can_grow(self, row: int) -> bool:
+        """Make sure the row has a page for its next token; False when the pool is exhausted."""
+        need = self.row_len[row] + 1
+        if need > self.max_seq_len:
+            return False
+        try:
+            self.cache.assign(row, self.row_seq[row], need)
+            return True
+        except MemoryError:
+            return False
+
+    def release(self, row: int) -> None:
+        seq = self.row_seq.pop(row, None)
+        if seq is not None:
+            self.cache.release(seq)
+        self.row_len.pop(row, None)
+        self.row_stochastic.pop(row, None)
+
+    # -- sampling ---------------------------------------------------------------------------------------------------
+    def set_sampling(self, row: int, params) -> None:
+        """Install the row's sampling record (``params``: a :class:`SamplingParams`-like object or None = greedy)."""
+        rec = torch.zeros(8, dtype=torch.int32)
+        stochastic = bool(params is not None and getattr(params, "temperature", 0.0) > 0.0)
+        if params is not None:
+            f = torch.tensor([params.temperature, 0.0, params.top_p, params.presence_penalty, params.frequency_penalty,
+                              params.repetition_penalty], dtype=torch.float32).view(torch.int32)
+            rec[:6] = f
+            rec[1] = int(params.top_k)
+            rec[6:8] = torch.tensor([int(params.seed) & (2 ** 63 - 1)], dtype=torch.int64).view(torch.int32)
+        else:
+            rec[5] = torch.tensor([1.0]).view(torch.int32)[0]
+        self.sample_rows[row] = rec.to(self.device)
+        self.row_stochastic[row] = stochastic
+
+    def _sample(self, logits: torch.Tensor, b: int, stochastic: bool) -> None:
+        if not stochastic:
+            self.model.sample_greedy(logits, out=self.sampled[:b])
+            return
+        if self.model.tp > 1:
+            logits = self.model.collective.gather_columns(logits)
+        if not logits.is_cuda:
+            self._sample_reference(logits, b)
+            return
+        v = logits.shape[1]
+        if self.sample_work is None or self.sample_work.shape[1] != v:
+            self.sample_work = torch.empty((self.max_batch, v), dtype=torch.float32, device=self.device)
+        fn = ops.lib.lib().mfq_sample
+        fn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 6
+        fn.restype = C.c_int
+        rc = fn(logits.data_ptr(), b, v, logits.stride(0), None, self.sample_rows.data_ptr(), self.seq_lens.data_ptr(),
+                self.sample_work.data_ptr(), self.sampled.data_ptr(), ops.lib.stream_ptr())
+        ops.lib.check(rc, "sample")
+
+    def _sample_reference(self, logits: torch.Tensor, b: int) -> None:
+        for r in range(b):
+            rec = self.sample_rows[r].cpu()
+            temp, top_p = rec[:1].view(torch.float32).item(), rec[2:3].view(torch.float32).item()
+            top_k = int(rec[1])
+            l = logits[r].float()
+            if temp <= 0:
+                self.sampled[r] = int(l.argmax())
+                continue
+            l = l / temp
+            if 0 < top_k < l.numel():
+                l = l.masked_fill(l < l.topk(top_k).values[-1], float("-inf"))
+            p = torch.softmax(l, -1)
+            if top_p < 1:
+                sp, si = p.sort(descending=True)
+                keep = (sp.cumsum(0) - sp) < top_p
+                mask = torch.zeros_like(p, dtype=torch.bool).scatter_(0, si[keep], True)
+                p = torch.where(mask, p, torch.zeros_like(p))
+            g = torch.Generator().manual_seed(int(rec[6:8].view(torch.int64)) + int(self.seq_lens[r]))
+            self.sampled[r] = int(torch.multinomial(p / p.sum(), 1, generator=g))
 
     # -- prefill -------------------------------------------------------------------------------------------------
-    def prefill(self, row: int, token_ids: torch.Tensor) -> int:
+    def prefill(self, row: int, token_ids, params=None) -> int:
         """Run the prompt of batch row ``row`` through the model; returns the first generated token id and leaves
         the row ready for decode (``seq_lens[row]`` = prompt length, ``sampled[row]`` = first token)."""
         dev = self.device
-        n = int(token_ids.numel())
+        ids = torch.as_tensor(token_ids, dtype=torch.int32)
+        n = int(ids.numel())
+        if n + 1 > self.max_seq_len:
+            raise ValueError(f"prompt of {n} tokens exceeds the engine's context of {self.max_seq_len}")
+        if row in self.row_seq:
+            self.release(row)
         seq_id = self._next_seq_id
         self._next_seq_id += 1
-        self.row_seq = getattr(self, "row_seq", {})
-        if row in self.row_seq:
-            self.cache.release(self.row_seq[row])
         self.row_seq[row] = seq_id
-        self.cache.assign(row, seq_id, min(self.max_seq_len, n + 1))
-        ids = token_ids.to(dev, dtype=torch.int32, non_blocking=True)
-        last = None
-        for start in range(0, n, self.prefill_chunk):
-            end = min(n, start + self.prefill_chunk)
-            if start > 0:
-                raise NotImplementedError("multi-chunk prefill needs attention over earlier pages")
-            step = StepBuffers(
-                input_ids=ids[start:end], positions=torch.arange(start, end, dtype=torch.int32, device=dev),
-                slots=self.cache.slots(seq_id, start, end - start).to(dev), cu_seqlens=[0, end - start])
-            rows = torch.tensor([end - start - 1], dtype=torch.int32, device=dev)
-            logits = self.model.forward(step, self.cache, prefill=True, logits_rows=rows, gather_logits=False)
-            last = logits
-        tok = self.model.sample_greedy(last)
-        self.sampled[row : row + 1] = tok
+        try:
+            self.cache.assign(row, seq_id, n + 1)
+        except MemoryError:
+            self.release(row)
+            raise
+        self.set_sampling(row, params)
+        ids = ids.to(dev, non_blocking=True)
+        step = StepBuffers(input_ids=ids, positions=torch.arange(n, dtype=torch.int32, device=dev),
+                           slots=self.cache.slots(seq_id, 0, n).to(dev), cu_seqlens=[0, n])
+        last = torch.tensor([n - 1], dtype=torch.int32, device=dev)
+        logits = self.model.forward(step, self.cache, prefill=True, logits_rows=last, gather_logits=False)
         self.seq_lens[row] = n
-        return tok
+        self.row_len[row] = n
+        if self.row_stochastic[row]:
+            # sample row 0 of the one-row logits with this row's record
+            saved_rows, saved_len = self.sample_rows[0].clone(), self.seq_lens[0].clone()
+            saved_tok = self.sampled[0].clone()
+            self.sample_rows[0], self.seq_lens[0] = self.sample_rows[row], n
+            self._sample(logits, 1, True)
+            tok = self.sampled[0].clone()
+            self.sample_rows[0], self.seq_lens[0], self.sampled[0] = saved_rows, saved_len, saved_tok
+            self.seq_lens[row] = n
+        else:
+            tok = self.model.sample_greedy(logits)[0]
+        self.sampled[row] = tok
+        return int(tok)
 
     def grow(self, row: int, tokens: int) -> None:
         self.cache.assign(row, self.row_seq[row], min(self.max_seq_len, tokens))
 
     # -- decode --------------------------------------------------------------------------------------------------
-    def _decode_body(self, b: int) -> None:
+    def _decode_body(self, b: int, stochastic: bool = False) -> None:
         dev = self.device
         if dev.type == "cuda":
             ops.decode_advance(self.sampled[:b], self.input_ids[:b], self.positions[:b], self.seq_lens[:b], self.slots[:b],
-                               self.cache.block_table[:b], self.cache.page_size)
+                               self.cache.block_table[:b], self.cache.page_size, active=self.active[:b])
         else:
-            self.input_ids[:b] = self.sampled[:b]
+            act = self.active[:b].bool()
+            self.input_ids[:b] = torch.where(act, self.sampled[:b], self.input_ids[:b])
             pos = self.seq_lens[:b].clone()
-            self.positions[:b] = pos
+            self.positions[:b] = torch.where(act, pos, self.positions[:b])
             pages = self.cache.block_table[:b].gather(1, (pos // self.cache.page_size).long()[:, None])[:, 0]
-            self.slots[:b] = pages * self.cache.page_size + pos % self.cache.page_size
-            self.seq_lens[:b] = pos + 1
+            self.slots[:b] = torch.where(act, pages * self.cache.page_size + pos % self.cache.page_size,
+                                         torch.full_like(pos, -1))
+            self.seq_lens[:b] = torch.where(act, pos + 1, pos)
         step = StepBuffers(input_ids=self.input_ids[:b], positions=self.positions[:b], slots=self.slots[:b],
                            block_table=self.cache.block_table[:b], seq_lens=self.seq_lens[:b])
         if dev.type == "cuda":
             from ..ops.kernels import attn_splits_for
             self.model.attn_splits = attn_splits_for(b, self.model.hk, self.max_seq_len)
         logits = self.model.forward(step, self.cache, prefill=False, gather_logits=False)
-        self.model.sample_greedy(logits, out=self.sampled[:b])
+        self._sample(logits, b, stochastic)
 
-    def decode_step(self, b: int) -> None:
-        """Advance rows ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device)."""
+    def decode_step(self, b: int, stochastic: bool = False) -> None:
+        """Advance the active rows among ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device)."""
         if not self.use_graphs:
-            self._decode_body(b)
+            self._decode_body(b, stochastic)
             return
-        g = self.graphs.get(b)
+        g = self.graphs.get((b, stochastic))
         if g is None:
             ops.Workspace.get(self.device)
             side = torch.cuda.Stream(device=self.device)
@@ -121,18 +235,31 @@ class LLMEngine:
             saved = (self.seq_lens.clone(), self.sampled.clone())
             with torch.cuda.stream(side):
                 for _ in range(2):
-                    self._decode_body(b)
+                    self._decode_body(b, stochastic)
             torch.cuda.current_stream().wait_stream(side)
             g = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             with torch.cuda.graph(g):
-                self._decode_body(b)
+                self._decode_body(b, stochastic)
             self.launches_per_step[b] = ops.launch_count() - before
             # warm-up and capture ran real steps: roll the sequence state back (the KV rows they wrote get rewritten)
             self.seq_lens.copy_(saved[0])
             self.sampled.copy_(saved[1])
-            self.graphs[b] = g
+            self.graphs[(b, stochastic)] = g
         g.replay()
+
+    def decode(self, rows: list[int]) -> dict[int, int]:
+        """Scheduler entry: one token for each of ``rows`` (other rows are masked off).  Returns ``{row: token}``."""
+        b = bucket_for(max(rows) + 1)
+        b = min(b, self.max_batch)
+        mask = torch.zeros(self.max_batch, dtype=torch.int32)
+        mask[rows] = 1
+        self.active.copy_(mask.to(self.device), non_blocking=True)
+        self.decode_step(b, any(self.row_stochastic.get(r, False) for r in rows))
+        toks = self.sampled[:b].cpu()
+        for r in rows:
+            self.row_len[r] += 1
+        return {r: int(toks[r]) for r in rows}
 
     def step_host(self, host_in: torch.Tensor, host_out: torch.Tensor) -> None:
         """One decode step driven from the host: ``host_in`` (pinned int32 ``[b]``, the tokens to feed) is copied
@@ -156,6 +283,7 @@ class LLMEngine:
         for row, p in enumerate(prompts):
             self.prefill(row, p)
             self.grow(row, int(p.numel()) + max_new_tokens + 1)
+        self.active.fill_(1)
         if cuda:
             ev[1].record()
         out = torch.empty((b, max_new_tokens), dtype=torch.int32, device=self.device)
