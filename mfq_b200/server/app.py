@@ -1,0 +1,285 @@
+"""HTTP surface: OpenAI- and Anthropic-compatible inference, control API, Prometheus metrics.
+
+Route and payload parity with the reference server (``mfq/server/api/routes/openai.py:28-157``,
+``anthropic.py:20-55``, ``runtime.py``, ``docs/api/http.md``):
+
+* ``GET /health``, ``GET /v1``, ``GET /v1/models``, ``GET /v1/models/{id}``
+* ``POST /v1/chat/completions`` -- JSON or SSE ``chat.completion.chunk`` stream; accepts ``max_tokens``,
+  ``temperature``, ``top_p``, ``top_k``, ``presence_penalty``, ``frequency_penalty``, ``repetition_penalty``,
+  ``seed``, ``stop``, ``stream``, ``priority``, ``timeout_seconds``, ``enable_mtp``, ``mtp_max_draft_tokens``
+* ``POST /v1/messages`` (Anthropic; stream or not), ``POST /v1/messages/count_tokens`` -> 501
+* ``GET /metrics`` (text 0.0.4), ``/api/v1/runtime/{status,instances,concurrency}``,
+  ``POST /api/v1/models/{load,unload}``
+* bearer / ``x-api-key`` auth when a key is configured (``/health`` stays open)
+* error envelope ``{"error": {"code", "message", "retryable", "details"}}`` with 429 ``runtime_queue_full``,
+  503 ``runtime_queue_timeout``, 504 ``runtime_deadline_exceeded``.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import json
+import queue
+import time
+import uuid
+
+from fastapi import FastAPI, Request as HttpRequest
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from ..engine.scheduler import BackendFailure, QueueFull, SamplingParams
+from .service import ModelService
+from .tokenizer import _content_text
+
+
+def error_response(status: int, code: str, message: str, retryable: bool = False, details=None) -> JSONResponse:
+    return JSONResponse({"error": {"code": code, "message": message, "retryable": retryable, "details": details or {}}},
+                        status_code=status)
+
+
+_ERROR_STATUS = {"runtime_queue_full": (429, True), "runtime_queue_timeout": (503, True),
+                 "runtime_deadline_exceeded": (504, False), "backend_failure": (500, True), "error": (400, False)}
+
+
+def _params_from(body: dict, stop_ids: tuple[int, ...]) -> SamplingParams:
+    return SamplingParams(
+        max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 256),
+        temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
+        top_p=float(body.get("top_p", 1.0) or 1.0), presence_penalty=float(body.get("presence_penalty", 0.0) or 0.0),
+        frequency_penalty=float(body.get("frequency_penalty", 0.0) or 0.0),
+        repetition_penalty=float(body.get("repetition_penalty", 1.0) or 1.0), seed=int(body.get("seed", 0) or 0),
+        stop_token_ids=stop_ids, enable_mtp=bool(body.get("enable_mtp", False)),
+        mtp_max_draft_tokens=int(body.get("mtp_max_draft_tokens", 3) or 3))
+
+
+class _Stream:
+    """Turns scheduler events of one request into decoded text pieces, honouring stop strings."""
+
+    def __init__(self, service: ModelService, model, req, events, stop: list[str]) -> None:
+        self.service, self.model, self.req, self.events, self.stop = service, model, req, events, stop
+        self.ids: list[int] = []
+        self.text = ""
+        self.finish: str | None = None
+        self.error_code: str | None = None
+
+    async def pieces(self):
+        loop = asyncio.get_running_loop()
+        while True:
+            try:
+                ev = await loop.run_in_executor(None, self.events.get, True, 0.25)
+            except queue.Empty:
+                continue
+            if ev.kind == "token":
+                if ev.token in self.req.params.stop_token_ids:
+                    continue
+                self.ids.append(ev.token)
+                full = self.model.tokenizer.decode(self.ids)
+                piece, self.text = full[len(self.text):], full
+                cut = min((self.text.find(s) for s in self.stop if s and s in self.text), default=-1)
+                if cut >= 0:
+                    keep = cut - (len(self.text) - len(piece))
+                    if keep > 0:
+                        yield piece[:keep]
+                    self.text = self.text[:cut]
+                    self.finish = "stop"
+                    self.service.cancel(self.model, self.req.id)
+                    self.service.record_completion(self.model, self.req, "ok")
+                    return
+                if piece:
+                    yield piece
+            elif ev.kind == "completed":
+                self.finish = self.finish or ("stop" if ev.finish_reason in ("stop", "cancelled") else "length")
+                self.service.record_completion(self.model, self.req, "cancelled" if ev.finish_reason == "cancelled" else "ok")
+                return
+            elif ev.kind == "failed":
+                self.error_code = ev.error_code or "error"
+                result = "timeout" if "deadline" in self.error_code or "timeout" in self.error_code else "error"
+                self.service.record_completion(self.model, self.req, result)
+                return
+
+
+def create_app(service: ModelService, api_key: str | None = None) -> FastAPI:
+    app = FastAPI(title="mfq-b200", version="0.1.0")
+    app.state.service = service
+
+    @app.middleware("http")
+    async def auth(request: HttpRequest, call_next):
+        if api_key and request.url.path not in ("/health",):
+            supplied = request.headers.get("x-api-key")
+            header = request.headers.get("authorization", "")
+            if header.lower().startswith("bearer "):
+                supplied = header[7:].strip()
+            if supplied != api_key:
+                return error_response(401, "unauthorized", "missing or invalid API key")
+        response = await call_next(request)
+        response.headers["x-content-type-options"] = "nosniff"
+        return response
+
+    @app.get("/health")
+    async def health():
+        names = list(service.models)
+        ok = all(lm.scheduler.healthy for lm in service.models.values())
+        return {"status": "ok" if ok else "degraded", "model": names[-1] if names else None, "models": names}
+
+    @app.get("/v1")
+    async def v1_root():
+        return {"object": "api", "endpoints": ["/v1/models", "/v1/chat/completions", "/v1/messages"]}
+
+    def _model_card(lm):
+        return {"id": lm.name, "object": "model", "created": int(lm.loaded_at), "owned_by": "mfq"}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [_model_card(lm) for lm in service.models.values()]}
+
+    @app.get("/v1/models/{model_id}")
+    async def model(model_id: str):
+        if model_id not in service.models:
+            return error_response(404, "model_not_found", f"model {model_id!r} is not loaded")
+        return _model_card(service.models[model_id])
+
+    async def _start(body: dict, messages: list[dict], stop: list[str]):
+        try:
+            lm = service.resolve(body.get("model"))
+        except KeyError as exc:
+            return None, error_response(404, "model_not_found", f"model {exc.args[0]!r} is not loaded")
+        prompt = lm.tokenizer.apply_chat_template(messages, add_generation_prompt=True)
+        ids = lm.tokenizer.encode(prompt)
+        if not ids:
+            return None, error_response(400, "invalid_request", "empty prompt")
+        params = _params_from(body, tuple(lm.tokenizer.stop_ids))
+        try:
+            req, events = await asyncio.get_running_loop().run_in_executor(
+                None, lambda: service.submit(lm, ids, params, priority=int(body.get("priority", 0) or 0),
+                                             timeout_seconds=body.get("timeout_seconds")))
+        except QueueFull as exc:
+            return None, error_response(429, "runtime_queue_full", str(exc), retryable=True)
+        except BackendFailure as exc:
+            return None, error_response(500, "backend_failure", str(exc), retryable=True)
+        return (_Stream(service, lm, req, events, stop), lm, ids), None
+
+    def _failure(stream: _Stream):
+        status, retry = _ERROR_STATUS.get(stream.error_code, (500, False))
+        return error_response(status, stream.error_code, "generation failed", retryable=retry)
+
+    @app.post("/v1/chat/completions")
+    async def chat(request: HttpRequest):
+        body = await request.json()
+        messages = body.get("messages") or []
+        if not messages:
+            return error_response(400, "invalid_request", "messages must not be empty")
+        stop = body.get("stop") or []
+        stop = [stop] if isinstance(stop, str) else list(stop)
+        started, err = await _start(body, messages, stop)
+        if err is not None:
+            return err
+        stream, lm, ids = started
+        cid, created = f"chatcmpl-{uuid.uuid4().hex[:24]}", int(time.time())
+
+        def usage():
+            return {"prompt_tokens": len(ids), "completion_tokens": len(stream.ids), "total_tokens": len(ids) + len(stream.ids)}
+
+        if body.get("stream"):
+            async def sse():
+                def chunk(delta, finish=None, extra=None):
+                    d = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": lm.name,
+                         "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+                    if extra:
+                        d.update(extra)
+                    return f"data: {json.dumps(d)}\n\n"
+                yield chunk({"role": "assistant", "content": ""})
+                async for piece in stream.pieces():
+                    yield chunk({"content": piece})
+                if stream.error_code:
+                    yield f"data: {json.dumps({'error': {'code': stream.error_code, 'message': 'generation failed'}})}\n\n"
+                else:
+                    extra = {"usage": usage()} if (body.get("stream_options") or {}).get("include_usage") else None
+                    yield chunk({}, stream.finish or "stop", extra)
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(sse(), media_type="text/event-stream")
+        async for _ in stream.pieces():
+            pass
+        if stream.error_code:
+            return _failure(stream)
+        return {"id": cid, "object": "chat.completion", "created": created, "model": lm.name,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": stream.text},
+                             "finish_reason": stream.finish or "stop"}], "usage": usage()}
+
+    @app.post("/v1/messages")
+    async def anthropic_messages(request: HttpRequest):
+        body = await request.json()
+        messages = list(body.get("messages") or [])
+        if not messages:
+            return error_response(400, "invalid_request", "messages must not be empty")
+        if body.get("system"):
+            messages = [{"role": "system", "content": _content_text(body["system"])}] + messages
+        started, err = await _start(body, messages, list(body.get("stop_sequences") or []))
+        if err is not None:
+            return err
+        stream, lm, ids = started
+        mid = f"msg_{uuid.uuid4().hex[:24]}"
+
+        def stop_reason():
+            return "end_turn" if stream.finish == "stop" else "max_tokens"
+
+        if body.get("stream"):
+            async def sse():
+                def ev(name, data):
+                    return f"event: {name}\ndata: {json.dumps(data)}\n\n"
+                yield ev("message_start", {"type": "message_start", "message": {
+                    "id": mid, "type": "message", "role": "assistant", "model": lm.name, "content": [],
+                    "stop_reason": None, "usage": {"input_tokens": len(ids), "output_tokens": 0}}})
+                yield ev("content_block_start", {"type": "content_block_start", "index": 0, "content_block": {"type": "text", "text": ""}})
+                async for piece in stream.pieces():
+                    yield ev("content_block_delta", {"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": piece}})
+                yield ev("content_block_stop", {"type": "content_block_stop", "index": 0})
+                if stream.error_code:
+                    yield ev("error", {"type": "error", "error": {"type": stream.error_code, "message": "generation failed"}})
+                else:
+                    yield ev("message_delta", {"type": "message_delta", "delta": {"stop_reason": stop_reason(), "stop_sequence": None},
+                                               "usage": {"output_tokens": len(stream.ids)}})
+                yield ev("message_stop", {"type": "message_stop"})
+            return StreamingResponse(sse(), media_type="text/event-stream")
+        async for _ in stream.pieces():
+            pass
+        if stream.error_code:
+            return _failure(stream)
+        return {"id": mid, "type": "message", "role": "assistant", "model": lm.name,
+                "content": [{"type": "text", "text": stream.text}], "stop_reason": stop_reason(), "stop_sequence": None,
+                "usage": {"input_tokens": len(ids), "output_tokens": len(stream.ids)}}
+
+    @app.post("/v1/messages/count_tokens")
+    async def count_tokens():
+        return error_response(501, "not_implemented", "count_tokens is not provided")
+
+    @app.get("/metrics")
+    async def metrics():
+        return PlainTextResponse(service.metrics.render(service), media_type="text/plain; version=0.0.4")
+
+    @app.get("/api/v1/runtime/status")
+    async def runtime_status():
+        return service.status()
+
+    @app.get("/api/v1/runtime/instances")
+    async def runtime_instances():
+        return service.status()["instances"]
+
+    @app.get("/api/v1/runtime/concurrency")
+    async def concurrency():
+        return [{"model": lm.name, "batch_capacity": lm.request_capacity, "max_queue": lm.scheduler.max_queue,
+                 "queue_timeout": lm.scheduler.queue_timeout} for lm in service.models.values()]
+
+    @app.post("/api/v1/models/load")
+    async def load_model(request: HttpRequest):
+        body = await request.json()
+        try:
+            lm = await asyncio.get_running_loop().run_in_executor(None, service.load, body.get("model", ""))
+        except KeyError:
+            return error_response(404, "model_not_found", "unknown model and no loader configured")
+        return {"model": lm.name, "instance": lm.instance}
+
+    @app.post("/api/v1/models/unload")
+    async def unload_model(request: HttpRequest):
+        body = await request.json()
+        return {"unloaded": service.unload(body.get("model", ""))}
+
+    return app
