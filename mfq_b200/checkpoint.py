@@ -1,0 +1,112 @@
+"""Checkpoint assembly and loading: Hugging Face directory / synthetic model -> ``.mfq`` -> engine.
+
+``model_config.json`` travels as the runtime asset ``__mfq_asset__/model_config.json`` (the reference embeds its
+runtime assets the same way, ``mfq/formats/assets.py:22-37``), tokenizer files under ``__mfq_asset__/hf/...``.
+"""
+
+from __future__ import annotations
+
+import json
+import struct
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from . import formats as F
+from .architectures import config_from_hf, to_canonical
+from .formats.container import ASSET_PREFIX
+
+_ST_DTYPES = {"F32": np.float32, "F16": np.float16, "BF16": np.uint16, "I64": np.int64, "I32": np.int32, "U8": np.uint8,
+              "F8_E4M3": np.uint8}
+
+
+def read_safetensors(path) -> dict[str, np.ndarray]:
+    """Minimal safetensors reader (8-byte header length, JSON header, raw little-endian data); float32 output."""
+    out = {}
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        base = 8 + n
+        for name, meta in header.items():
+            if name == "__metadata__":
+                continue
+            a, b = meta["data_offsets"]
+            f.seek(base + a)
+            raw = np.frombuffer(f.read(b - a), dtype=_ST_DTYPES[meta["dtype"]]).reshape(meta["shape"])
+            if meta["dtype"] == "BF16":
+                raw = F.from_bf16(raw)
+            elif meta["dtype"] == "F8_E4M3":
+                from .formats.mx import e4m3_to_float
+                raw = e4m3_to_float(raw)
+            out[name] = np.asarray(raw, dtype=np.float32) if raw.dtype.kind == "f" else raw
+    return out
+
+
+def read_hf_directory(path) -> tuple[dict, dict[str, np.ndarray], dict[str, bytes]]:
+    """(model config kwargs, canonical float32 tensors, tokenizer assets) of a Hugging Face checkpoint directory."""
+    p = Path(path)
+    hf_cfg = json.loads((p / "config.json").read_text())
+    tensors: dict[str, np.ndarray] = {}
+    for shard in sorted(p.glob("*.safetensors")):
+        tensors.update(read_safetensors(shard))
+    assets = {}
+    for fname in ("tokenizer.json", "tokenizer_config.json", "generation_config.json", "chat_template.jinja"):
+        if (p / fname).exists():
+            assets[f"hf/{fname}"] = (p / fname).read_bytes()
+    return config_from_hf(hf_cfg), to_canonical(tensors), assets
+
+
+def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", expert_mix: str = "", seed: int = 20260908,
+                     device: str = "cpu", progress=None) -> dict[str, object]:
+    """Apply the quantization plan: routed experts by the seeded mix (or the dense rule), 2-D weights by ``dense``
+    (nint2..8 / nvq3 / mxfp4 / fp8 / bf16), norms / router / embeddings-as-requested stay bf16."""
+    from .quantize import balanced_expert_mix, parse_profiles, quantize_expertwise, quantize_matrix
+    profiles = parse_profiles(expert_mix) if expert_mix else ()
+    dense_profile = None if dense == "bf16" else parse_profiles({"fp8": "FP8", "mxfp4": "MXFP4", "nvq3": "NVQ3"}.get(dense, dense.upper()))[0]
+    out: dict[str, object] = {}
+    for name, t in tensors.items():
+        if progress:
+            progress(name)
+        a = np.asarray(t, dtype=np.float32)
+        keep = a.ndim < 2 or "norm" in name or "router" in name or name.endswith(".bias")
+        if ".mlp.experts." in name and a.ndim == 3:
+            use = profiles or ((dense_profile,) if dense_profile else ())
+            if not use:
+                out[name] = F.to_bf16(a)
+                continue
+            assign = balanced_expert_mix(name, a.shape[0], len(use), seed)
+            out[name] = quantize_expertwise(a, assign, tuple(use), device=device)
+        elif keep or dense_profile is None or (dense_profile.family in ("FP8", "MXFP4") and a.shape[-1] % 128):
+            out[name] = F.to_bf16(a)
+        else:
+            out[name] = quantize_matrix(a, dense_profile, device=device)
+    return out
+
+
+def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict[str, bytes] | None = None,
+                    arch: str = "mfq_b200_decoder", extra: dict | None = None) -> None:
+    records = dict(tensors)
+    all_assets = {"model_config.json": json.dumps(config).encode()}
+    all_assets.update(assets or {})
+    for k, v in all_assets.items():
+        records[ASSET_PREFIX + k] = v
+    header = F.FileHeader(model_arch=arch, extra={"runtime_assets": sorted(all_assets), **(extra or {})})
+    F.save(path, header, records)
+
+
+def load_engine(path, device="cuda", *, max_batch: int = 64, max_seq_len: int = 8192, tp_rank: int = 0, tp_size: int = 1,
+                collective=None, use_graphs: bool = True):
+    """``.mfq`` -> (engine, tokenizer, config)."""
+    from .engine.llm_engine import LLMEngine
+    from .models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from .server.tokenizer import tokenizer_from_assets
+    with F.open_mfq(path) as store:
+        assets = store.assets()
+        raw = json.loads(assets["model_config.json"])
+        fields = {f for f in MoeDecoderConfig.__dataclass_fields__}
+        cfg = MoeDecoderConfig(**{k: v for k, v in raw.items() if k in fields})
+        weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size)
+    model = MoeDecoderModel(cfg, weights, collective=collective)
+    engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, use_graphs=use_graphs)
+    return engine, tokenizer_from_assets(assets, cfg.vocab_size), cfg

@@ -1,0 +1,225 @@
+"""``mfq`` command line: build | quantize | inspect | eval | serve | bench.
+
+The sub-commands and their main flags follow the reference CLI (``mfq/cli.py:660-741``, ``docs/cli/*.md``):
+``mfq quantize <in> <out.mfq>`` with ``--bits/--groupsize/--sub-bits``, ``--preset``, ``--random-expert-mix`` +
+``--random-expert-mix-seed``, ``--full-precision``, ``--split-max-size``, ``--device``, ``--dry-run``, ``--overwrite``;
+``mfq serve --model ...`` with ``--host/--port/--api-key-env/--continuous-batching/--ctx-size/--tensor-parallel``;
+``mfq eval kl`` for KLD / top-1 agreement; ``mfq build`` compiles the CUDA library.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+
+def _cmd_build(args) -> int:
+    from .ops.build import build
+    path = build(force=args.force, verbose=args.verbose)
+    manifest = {"backend": "cuda", "arch": "sm_100a", "library": str(path)}
+    Path(args.manifest).parent.mkdir(parents=True, exist_ok=True)
+    Path(args.manifest).write_text(json.dumps(manifest, indent=1))
+    print(json.dumps(manifest))
+    return 0
+
+
+_SYNTHETIC = {
+    "tiny-moe": dict(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                     rope_theta=1e6, rms_eps=1e-6, num_experts=8, top_k=2, moe_intermediate=128),
+    "tiny-moe-128": dict(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128,
+                         rope_theta=1e6, rms_eps=1e-6, num_experts=8, top_k=2, moe_intermediate=128, shared_intermediate=128),
+}
+
+
+def _load_source(args):
+    """-> (config dict, canonical float tensors, assets)."""
+    import numpy as np
+    src = args.input
+    if src.startswith("synthetic:"):
+        from .models.moe_lm import MoeConfig, init_weights
+        kw = _SYNTHETIC[src.split(":", 1)[1]]
+        w = init_weights(MoeConfig(**kw), seed=args.seed)
+        return dict(kw, name=src), {k: v.numpy().astype(np.float32) for k, v in w.items()}, {}
+    p = Path(src)
+    if p.is_dir():
+        from .checkpoint import read_hf_directory
+        return read_hf_directory(p)
+    if p.suffix == ".mfq":
+        from . import formats as F
+        with F.open_mfq(p) as store:
+            assets = store.assets()
+            cfg = json.loads(assets.pop("model_config.json"))
+            tensors = {n: np.asarray(F.dequantize(store[n]), dtype=np.float32) for n in store if not n.startswith("__mfq_asset__/")}
+        return cfg, tensors, assets
+    raise SystemExit(f"cannot detect the source type of {src!r} (expected a Hugging Face directory, an .mfq file or synthetic:<name>)")
+
+
+def _cmd_quantize(args) -> int:
+    from . import formats as F
+    from .checkpoint import quantize_tensors, save_checkpoint
+    out = Path(args.output)
+    if out.exists() and not args.overwrite and not args.dry_run:
+        raise SystemExit(f"{out} exists (use --overwrite)")
+    cfg, tensors, assets = _load_source(args)
+    dense = "bf16" if args.full_precision else (args.format or f"nint{args.bits}")
+    if args.preset:
+        dense = {"S2": "nint2", "S3": "nint3", "S4": "nint4", "S5": "nint5", "S6": "nint6", "S8": "nint8"}[args.preset.split("-")[0].upper()]
+    plan = {n: (list(t.shape), "MFE" if (".mlp.experts." in n and t.ndim == 3 and (args.random_expert_mix or dense != "bf16")) else dense)
+            for n, t in tensors.items()}
+    if args.dry_run:
+        print(json.dumps({"tensors": len(plan), "dense": dense, "expert_mix": args.random_expert_mix, "plan": plan}, indent=1))
+        return 0
+    if dense.startswith("nint") and (args.groupsize or args.sub_bits):
+        from .quantize import expertwise
+        bits = int(dense[4:])
+        gs, k = expertwise._NINT_PRESETS[bits]
+        expertwise._NINT_PRESETS[bits] = (args.groupsize or gs, args.sub_bits or k)
+    q = quantize_tensors(tensors, dense=dense, expert_mix=args.random_expert_mix, seed=args.random_expert_mix_seed,
+                         device=args.device, progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
+    extra = {"quantization": {"dense": dense, "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
+                              "random_expert_mix_seed": args.random_expert_mix_seed if args.random_expert_mix else None}}
+    save_checkpoint(out, cfg, q, assets, extra=extra)
+    size = out.stat().st_size
+    weights = sum(int(t.size) for t in tensors.values())
+    print(json.dumps({"output": str(out), "bytes": size, "weights": weights, "bits_per_weight": round(8 * size / weights, 3)}))
+    return 0
+
+
+def _cmd_inspect(args) -> int:
+    from . import formats as F
+    with F.open_mfq(args.model) as store:
+        rows = [{"name": n, "dtype": store.dtype(n), "bytes": r.nbytes} for n, r in store.records.items()]
+        info = {"arch": store.header.model_arch, "version": store.header.version, "extra": store.header.extra,
+                "tensors": len(rows), "bytes": sum(r["bytes"] for r in rows)}
+    by = {}
+    for r in rows:
+        by[r["dtype"]] = by.get(r["dtype"], 0) + r["bytes"]
+    info["bytes_by_dtype"] = by
+    if args.tensors:
+        info["records"] = rows
+    print(json.dumps(info, indent=1))
+    return 0
+
+
+def _cmd_eval(args) -> int:
+    """KLD / top-1 of a quantized checkpoint against a baseline checkpoint on random or given token windows."""
+    import torch
+    from . import formats as F
+    from .evaluation.kld import compare_logits
+    from .models.moe_lm import MoeConfig, MoeLM, dequantize_checkpoint
+
+    def load(path):
+        with F.open_mfq(path) as store:
+            cfg = json.loads(store.assets()["model_config.json"])
+            tensors = {n: store[n] for n in store if not n.startswith("__mfq_asset__/")}
+        fields = MoeConfig.__dataclass_fields__
+        return MoeConfig(**{k: v for k, v in cfg.items() if k in fields}), dequantize_checkpoint(tensors)
+
+    cfg, base = load(args.base)
+    _, test = load(args.model)
+    g = torch.Generator().manual_seed(args.seed)
+    reports = []
+    for _ in range(args.chunks):
+        ids = torch.randint(0, cfg.vocab_size, (args.ctx,), generator=g)
+        lb, lt = MoeLM(cfg, base).forward(ids), MoeLM(cfg, test).forward(ids)
+        half = args.ctx // 2  # score the second half of each window, like the reference protocol
+        reports.append(compare_logits(lb[half:], lt[half:]))
+    n = len(reports)
+    print(f"kld={sum(r.kld for r in reports) / n:.6g} mean_kld_q_ref={sum(r.reverse_kld for r in reports) / n:.6g} "
+          f"same_top={100 * sum(r.top1_agreement for r in reports) / n:.2f}% chunks={n}")
+    return 0
+
+
+def _cmd_serve(args) -> int:
+    import torch
+    import uvicorn
+    from .checkpoint import load_engine
+    from .server import ModelService, create_app
+    device = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    service = ModelService(max_instances=args.max_runtime_instances, max_queue=args.max_queue, queue_timeout=args.queue_timeout)
+
+    def loader(name_or_path):
+        path = name_or_path if Path(name_or_path).exists() else args.model
+        engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size)
+        return engine, tok
+
+    service.loader = loader
+    engine, tok = loader(args.model)
+    service.add_model(args.model_name or Path(args.model).stem, engine, tok)
+    key = os.environ.get(args.api_key_env) if args.api_key_env else None
+    uvicorn.run(create_app(service, api_key=key), host=args.host, port=args.port, access_log=args.access_log)
+    return 0
+
+
+def _cmd_bench(args) -> int:
+    os.execv(sys.executable, [sys.executable, str(Path(__file__).resolve().parents[1] / "bench.py"), *args.rest])
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="mfq", description="Mixed-format quantization and serving on Blackwell GPUs")
+    sub = ap.add_subparsers(dest="command", required=True)
+    b = sub.add_parser("build", help="compile the sm_100a CUDA library")
+    b.add_argument("--force", action="store_true")
+    b.add_argument("--verbose", action="store_true")
+    b.add_argument("--manifest", default="build/mfq-runtime.json")
+    b.set_defaults(fn=_cmd_build)
+    q = sub.add_parser("quantize", help="convert a Hugging Face directory / .mfq / synthetic model to a packed .mfq")
+    q.add_argument("input")
+    q.add_argument("output")
+    q.add_argument("--bits", type=int, default=4)
+    q.add_argument("--groupsize", type=int, default=0)
+    q.add_argument("--sub-bits", type=int, default=0)
+    q.add_argument("--format", choices=["nint2", "nint3", "nint4", "nint5", "nint6", "nint8", "nvq3", "mxfp4", "fp8", "bf16"])
+    q.add_argument("--preset", help="S2..S8 role presets (uniform NINT width)")
+    q.add_argument("--random-expert-mix", default="", help="comma separated families per routed expert projection")
+    q.add_argument("--random-expert-mix-seed", type=int, default=20260908)
+    q.add_argument("--full-precision", action="store_true")
+    q.add_argument("--device", default="cpu")
+    q.add_argument("--seed", type=int, default=0)
+    q.add_argument("--dry-run", action="store_true")
+    q.add_argument("--overwrite", action="store_true")
+    q.add_argument("--verbose", action="store_true")
+    q.set_defaults(fn=_cmd_quantize)
+    i = sub.add_parser("inspect", help="summarise an .mfq container")
+    i.add_argument("model")
+    i.add_argument("--tensors", action="store_true")
+    i.set_defaults(fn=_cmd_inspect)
+    e = sub.add_parser("eval", help="quality evaluation")
+    es = e.add_subparsers(dest="what", required=True)
+    kl = es.add_parser("kl", help="KLD / top-1 agreement against a baseline checkpoint")
+    kl.add_argument("--model", required=True)
+    kl.add_argument("--base", "--kl-base", dest="base", required=True)
+    kl.add_argument("--chunks", "--kl-chunks", dest="chunks", type=int, default=4)
+    kl.add_argument("--ctx", type=int, default=128)
+    kl.add_argument("--seed", type=int, default=0)
+    kl.set_defaults(fn=_cmd_eval)
+    s = sub.add_parser("serve", help="OpenAI/Anthropic-compatible server")
+    s.add_argument("--model", required=True)
+    s.add_argument("--model-name")
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--port", type=int, default=8090)
+    s.add_argument("--api-key-env")
+    s.add_argument("--continuous-batching", type=int, default=32)
+    s.add_argument("--ctx-size", type=int, default=8192)
+    s.add_argument("--max-runtime-instances", type=int, default=1)
+    s.add_argument("--max-queue", type=int, default=256)
+    s.add_argument("--queue-timeout", type=float, default=30.0)
+    s.add_argument("--device")
+    s.add_argument("--access-log", action="store_true")
+    s.set_defaults(fn=_cmd_serve)
+    be = sub.add_parser("bench", help="run the flagship benchmark (arguments are passed through to bench.py)")
+    be.add_argument("rest", nargs=argparse.REMAINDER)
+    be.set_defaults(fn=_cmd_bench)
+    return ap
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    return int(args.fn(args) or 0)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,31 @@
+"""`mfq` command line on a synthetic tiny MoE: quantize (mixed experts), inspect, eval kl, and loading into the engine."""
+
+import json
+
+import torch
+
+from mfq_b200.cli import main
+
+
+def test_quantize_inspect_eval_and_load(tmp_path, capsys):
+    base, mixed = tmp_path / "base.mfq", tmp_path / "mixed.mfq"
+    assert main(["quantize", "synthetic:tiny-moe-128", str(base), "--full-precision"]) == 0
+    assert main(["quantize", "synthetic:tiny-moe-128", str(mixed), "--format", "nint4", "--random-expert-mix", "NINT4,NVQ3,MXFP4"]) == 0
+    capsys.readouterr()
+    assert main(["inspect", str(mixed)]) == 0
+    info = json.loads(capsys.readouterr().out)
+    assert info["arch"] == "mfq_b200_decoder" and "MFE" in info["bytes_by_dtype"] and "NINT" in info["bytes_by_dtype"]
+    assert info["extra"]["quantization"]["random_expert_mix"] == ["NINT4", "NVQ3", "MXFP4"]
+    assert mixed.stat().st_size < 0.5 * base.stat().st_size
+    assert main(["eval", "kl", "--model", str(mixed), "--base", str(base), "--chunks", "2", "--ctx", "64"]) == 0
+    line = capsys.readouterr().out.strip()
+    assert line.startswith("kld=") and "same_top=" in line
+    assert float(line.split()[0].split("=")[1]) < 0.01
+    assert main(["quantize", "synthetic:tiny-moe-128", str(mixed), "--dry-run"]) == 0
+    # re-quantizing an .mfq source and loading the result into the serving engine (CPU path)
+    again = tmp_path / "again.mfq"
+    assert main(["quantize", str(base), str(again), "--format", "nint8"]) == 0
+    from mfq_b200.checkpoint import load_engine
+    engine, tok, cfg = load_engine(again, "cpu", max_batch=2, max_seq_len=64)
+    out = engine.generate([torch.tensor(tok.encode("hello"))], 4)
+    assert out.tokens.shape == (1, 4) and cfg.num_experts == 8
