@@ -46,6 +46,26 @@ struct ArParams {
   uint32_t* flags[8] = {};    // every rank's per-tile arrival counters (own + peer-mapped)
   uint32_t* expected = nullptr;  // local: value of our flag after the previous launch, per tile
   size_t half_elems = 0;
+  // 0: all-reduce (every rank ends with the full [M, N] sum).  1: reduce-scatter over token rows: rank r owns the
+  // token tiles [r * T/W, (r+1) * T/W); the other ranks push their partial tile into the owner's buffer (one slot
+  // per source rank) and only the owner sums; `out` / `residual` are then the owner's [M/W, N] shard.
+  int mode = 0;
+};
+
+// All-gather -> GEMM context (world == 1: disabled).  The activation is sharded over token rows; the first
+// `push_ctas` blocks of the grid copy this rank's FP8 shard (+ row multipliers) into every rank's gathered buffer
+// over NVLink and bump per-source flags, the GEMM blocks' TMA producers wait for the flag of the rank that owns
+// their token tile and then read the tile from *local* memory, so every byte crosses NVLink once and tiles of
+// early ranks are multiplied while later shards are still in flight.
+struct AgParams {
+  int world = 1, rank = 0, push_ctas = 0, shard_rows = 0;
+  uint8_t* x_full[8] = {};        // every rank's gathered activations: 2 halves of M * K bytes
+  float* xs_full[8] = {};         // every rank's gathered row multipliers: 2 halves of M floats
+  uint32_t* flags[8] = {};        // every rank's arrival counters, one per source rank
+  const uint8_t* x_shard = nullptr;
+  const float* xs_shard = nullptr;
+  const uint32_t* epoch = nullptr;   // completed launches on this context (bumped by a 1-thread kernel afterwards)
+  uint32_t* push_done = nullptr;     // local counter of finished push blocks (returns to zero)
 };
 
 struct GemmParams {
@@ -63,12 +83,13 @@ struct GemmParams {
   // x / out are the expert-sorted token rows, expert e owning rows [expert_offsets[e], expert_offsets[e+1]).
   const int2* tile_map = nullptr;
   const int* expert_offsets = nullptr;
+  AgParams ag;
 };
 
 template <int BT>
 __global__ void __launch_bounds__(GemmCfg<BT>::kThreads, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmap_x_alt, const GemmParams p) {
   using Cfg = GemmCfg<BT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -84,7 +105,37 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x, t_tile = blockIdx.y, split = blockIdx.z;
+  const bool gather = p.ag.world > 1;
+  const uint32_t ag_epoch = gather ? *p.ag.epoch : 0u;
+  if (gather && int(blockIdx.x) < p.ag.push_ctas) {
+    // ----- push block: copy my shard into every rank's gathered buffer, then announce it -----
+    if (blockIdx.y != 0 || blockIdx.z != 0) return;
+    const AgParams& ag = p.ag;
+    const size_t shard_bytes = size_t(ag.shard_rows) * p.K;
+    const size_t half = size_t(ag_epoch & 1u) * size_t(p.M) * p.K;
+    const uint4* src = reinterpret_cast<const uint4*>(ag.x_shard);
+    const size_t nvec = shard_bytes / 16;
+    for (int r = 0; r < ag.world; ++r) {
+      uint4* dst = reinterpret_cast<uint4*>(ag.x_full[r] + half + size_t(ag.rank) * shard_bytes);
+      for (size_t v = size_t(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += size_t(ag.push_ctas) * blockDim.x) dst[v] = src[v];
+      float* sdst = ag.xs_full[r] + size_t(ag_epoch & 1u) * p.M + size_t(ag.rank) * ag.shard_rows;
+      for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < ag.shard_rows; v += ag.push_ctas * blockDim.x) sdst[v] = ag.xs_shard[v];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t prev = atomicAdd(ag.push_done, 1u);
+      if (prev == uint32_t(ag.push_ctas) - 1u) {  // last push block: all of my shard is on its way and fenced
+        *ag.push_done = 0;
+        __threadfence_system();
+        for (int r = 0; r < ag.world; ++r)
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ag.flags[r] + ag.rank) : "memory");
+      }
+    }
+    return;
+  }
+  const int n_tile = int(blockIdx.x) - (gather ? p.ag.push_ctas : 0), t_tile = blockIdx.y, split = blockIdx.z;
+  const int n_tiles_x = int(gridDim.x) - (gather ? p.ag.push_ctas : 0);
   const int n0 = n_tile * kTileN;
   int t0 = t_tile * BT, row_end = p.M, expert = 0;
   if (p.tile_map) {
@@ -120,7 +171,30 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     if (lane == 0) {
       tma_prefetch_desc(&tmap_w);
       tma_prefetch_desc(&tmap_x);
-      for (int i = 0; i < nkb; ++i) {
+      const CUtensorMap* xmap = (gather && (ag_epoch & 1u)) ? &tmap_x_alt : &tmap_x;
+      bool shard_ready = true;
+      if (gather) {
+        // both shards that a token tile may straddle are awaited (tiles are aligned to shards in practice)
+        const int first = t0 / p.ag.shard_rows, last = min(p.ag.world - 1, (t0 + BT - 1) / p.ag.shard_rows);
+        const unsigned long long t_start = globaltimer_ns();
+        for (int src = first; src <= last && shard_ready; ++src) {
+          const uint32_t* f = p.ag.flags[p.ag.rank] + src;
+          uint32_t seen, spins = 0;
+          while (true) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+            if (int32_t(seen - (ag_epoch + 1u)) >= 0) break;
+            if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t_start > kWaitBudgetNs)) {
+              *abort_flag = 1;
+              atomicCAS(p.status, 0, kStatusTimeoutPeer);
+              shard_ready = false;
+              break;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        asm volatile("fence.proxy.async.global;" ::: "memory");  // peers' generic-proxy stores -> my TMA reads
+      }
+      for (int i = 0; shard_ready && i < nkb; ++i) {
         const int s = i % Cfg::kStages;
         if (!mbar_wait(&empty[s], ((i / Cfg::kStages) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutProducer)) break;
         uint8_t* a = tiles + s * Cfg::kStageBytes;
@@ -128,7 +202,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
         if (p.tile_map) tma_load_3d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0, expert);
         else tma_load_2d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0);
-        tma_load_2d(b, &tmap_x, &full[s], (kb0 + i) * kBlockK, t0);
+        tma_load_2d(b, xmap, &full[s], (kb0 + i) * kBlockK, t0);
       }
     }
   } else if (warp == 1) {
@@ -163,7 +237,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     float acc[CW];
 #pragma unroll
     for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
-    const float* wsc = p.w_scale + (size_t(expert) * gridDim.x + n_tile) * kb_total;
+    const float* wsc = p.w_scale + (size_t(expert) * n_tiles_x + n_tile) * kb_total;
     bool ok = true;
     for (int i = 0; i < nkb; ++i) {
       const int buf = i % Cfg::kAcc;
@@ -201,8 +275,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
     if (ok) {
       const int tl = min(BT, row_end - t0);
-      const int tiles_nt = gridDim.x * gridDim.y;
-      const int tile_id = t_tile * gridDim.x + n_tile;
+      const int tiles_nt = n_tiles_x * gridDim.y;
+      const int tile_id = t_tile * n_tiles_x + n_tile;
       bool owner = true;  // this CTA holds the tile's complete local sum in `acc`
       if (gridDim.z > 1) {
         owner = false;
@@ -237,8 +311,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         }
       }
       if (owner) {
+        const float* xsc = gather ? p.ag.xs_full[p.ag.rank] + size_t(ag_epoch & 1u) * p.M : p.x_scale;
 #pragma unroll
-        for (int tt = 0; tt < CW; ++tt) acc[tt] *= (col0 + tt < tl) ? __ldg(p.x_scale + t0 + col0 + tt) : 0.f;
+        for (int tt = 0; tt < CW; ++tt) acc[tt] *= (col0 + tt < tl) ? __ldcg(xsc + t0 + col0 + tt) : 0.f;
         if (p.ar.world > 1) {
           // ----- one-shot all-reduce over NVLink peer memory, fused into the epilogue -----
           // Every rank publishes its partial tile in its own (peer-mapped) buffer, bumps the tile's flag on every
@@ -249,28 +324,43 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           const ArParams& ar = p.ar;
           const uint32_t before = ar.expected[tile_id];
           const uint32_t target = before + uint32_t(ar.world - 1);
-          const size_t off = size_t((before / uint32_t(ar.world - 1)) & 1u) * ar.half_elems + size_t(tile_id) * (BT * kTileN);
-          float* mine = ar.bufs[ar.rank] + off;
+          const size_t half_off = size_t((before / uint32_t(ar.world - 1)) & 1u) * ar.half_elems;
+          const bool rs = ar.mode == 1;
+          const int t_per_rank = int(gridDim.y) / ar.world;            // token tiles owned by each rank (RS)
+          const int tile_owner = rs ? t_tile / t_per_rank : ar.rank;   // AR: everyone "owns" (and sums) every tile
+          const int tiles_owned = t_per_rank * n_tiles_x;
+          const int tile_local = (t_tile % max(t_per_rank, 1)) * n_tiles_x + n_tile;
+          // AR: my partial goes to my own buffer at the tile's slot; RS: into the owner's buffer, slot [me][tile]
+          const size_t off = rs ? half_off + (size_t(ar.rank) * tiles_owned + tile_local) * (BT * kTileN)
+                                : half_off + size_t(tile_id) * (BT * kTileN);
+          float* mine = ar.bufs[tile_owner] + off;
 #pragma unroll
           for (int tt = 0; tt < CW; ++tt) mine[(col0 + tt) * kTileN + row] = acc[tt];
           __threadfence_system();
           __syncwarp();
           if (lane == 0) mbar_arrive(&epi_bar[2]);
           bool met = mbar_wait(&epi_bar[2], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
+          const bool i_sum = !rs || tile_owner == ar.rank;
           if (met && threadIdx.x == 64) {
-            for (int r = 0; r < ar.world; ++r)
-              if (r != ar.rank)
-                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[r] + tile_id) : "memory");
-            const uint32_t* my_flag = ar.flags[ar.rank] + tile_id;
-            const unsigned long long t_start = globaltimer_ns();
-            uint32_t seen, spins = 0;
-            while (true) {
-              asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
-              if (int32_t(seen - target) >= 0) break;
-              if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t_start > kWaitBudgetNs)) {
-                *abort_flag = 1;
-                atomicCAS(p.status, 0, kStatusTimeoutPeer);
-                break;
+            if (!rs) {
+              for (int r = 0; r < ar.world; ++r)
+                if (r != ar.rank)
+                  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[r] + tile_id) : "memory");
+            } else if (tile_owner != ar.rank) {
+              asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[tile_owner] + tile_id) : "memory");
+            }
+            if (i_sum) {
+              const uint32_t* my_flag = ar.flags[ar.rank] + tile_id;
+              const unsigned long long t_start = globaltimer_ns();
+              uint32_t seen, spins = 0;
+              while (true) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
+                if (int32_t(seen - target) >= 0) break;
+                if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t_start > kWaitBudgetNs)) {
+                  *abort_flag = 1;
+                  atomicCAS(p.status, 0, kStatusTimeoutPeer);
+                  break;
+                }
               }
             }
             ar.expected[tile_id] = target;
@@ -278,12 +368,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           __syncwarp();
           if (lane == 0) mbar_arrive(&epi_bar[3]);
           met = met && mbar_wait(&epi_bar[3], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
-          owner = met && !*abort_flag;
+          owner = met && !*abort_flag && i_sum;
           if (owner) {
 #pragma unroll
             for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
             for (int r = 0; r < ar.world; ++r) {
-              const float* part = ar.bufs[r] + off + row;
+              // AR: rank r's buffer, same slot (peer loads).  RS: my buffer, slot of source rank r (local loads).
+              const float* part = rs ? ar.bufs[ar.rank] + half_off + (size_t(r) * tiles_owned + tile_local) * (BT * kTileN) + row
+                                     : ar.bufs[r] + off + row;
 #pragma unroll
               for (int tt = 0; tt < CW; ++tt) {
                 float v;
@@ -291,6 +383,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 acc[tt] += v;
               }
             }
+            if (rs) t0 -= ar.rank * t_per_rank * BT;  // rows of the local output shard
           }
         }
         if (owner && n < p.N) {
@@ -320,7 +413,7 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
                        const void* residual, float* ws, size_t ws_bytes, int* counters, int counters_len, int* status,
                        int M, int N, int K, int splits, cudaStream_t stream, const ArParams* ar = nullptr,
                        int experts = 0, const int2* tile_map = nullptr, const int* expert_offsets = nullptr,
-                       int map_len = 0) {
+                       int map_len = 0, const AgParams* ag = nullptr) {
   using Cfg = GemmCfg<BT>;
   CUtensorMap tw, tx;
   if (experts > 0) {
@@ -329,7 +422,14 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
   } else if (make_tmap_2d(&tw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kTileN, kBlockK)) {
     return -2;
   }
-  if (make_tmap_2d(&tx, x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BT, kBlockK)) return -3;
+  CUtensorMap tx_alt;
+  if (ag) {  // x = this rank's gathered buffer: one map per half
+    if (make_tmap_2d(&tx, ag->x_full[ag->rank], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BT, kBlockK)) return -3;
+    if (make_tmap_2d(&tx_alt, ag->x_full[ag->rank] + size_t(M) * K, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BT, kBlockK)) return -3;
+  } else {
+    if (make_tmap_2d(&tx, x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BT, kBlockK)) return -3;
+    tx_alt = tx;
+  }
   const int n_tiles = (N + kTileN - 1) / kTileN, t_tiles = experts > 0 ? map_len : (M + BT - 1) / BT;
   const int kb_total = K / kBlockK;
   if (splits < 1) splits = 1;
@@ -353,7 +453,9 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
       return -6;
     attr_set = true;
   }
-  fp8_gemm_kernel<BT><<<dim3(n_tiles, t_tiles, splits), Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tw, tx, p);
+  if (ag) p.ag = *ag;
+  const int extra_x = ag ? ag->push_ctas : 0;
+  fp8_gemm_kernel<BT><<<dim3(n_tiles + extra_x, t_tiles, splits), Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tw, tx, tx_alt, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
@@ -378,13 +480,19 @@ extern "C" int mfq_fp8_gemm(const void* w, const float* w_scale, const void* x, 
 // `flags` hold `world` device pointers each (own buffer at index `rank`, the others peer-mapped); every buffer has
 // 2 * half_elems floats, every flag array at least ceil(N/128) * ceil(M/token_tile) counters, zero before first use.
 // All ranks must issue the same sequence of calls on a context.  `residual` is added after the sum on every rank.
+// reduce_scatter != 0: GEMM -> reduce-scatter over token rows (M must be a multiple of world * token_tile): `out` and
+// `residual` are this rank's [M / world, N] shard; non-owners push their partial tiles and do not wait.  Two
+// reduce-scatter launches on one context must be separated by something that depends on every owner's result (in the
+// model: the all-gather that follows), otherwise a fast rank could overwrite partials an owner has not summed yet.
 extern "C" int mfq_fp8_gemm_allreduce(const void* w, const float* w_scale, const void* x, const float* x_scale,
                                       void* out, const void* residual, float* ws, size_t ws_bytes, int* counters,
                                       int counters_len, int* status, int M, int N, int K, int token_tile, int splits,
                                       int world, int rank, void* const* bufs, void* const* flags, void* expected,
-                                      size_t half_elems, cudaStream_t stream) {
+                                      size_t half_elems, int reduce_scatter, cudaStream_t stream) {
   if (K % 128 != 0 || M <= 0 || N <= 0 || world < 2 || world > 8 || rank < 0 || rank >= world) return -1;
+  if (reduce_scatter && (((M + token_tile - 1) / token_tile) % world != 0 || M % token_tile != 0)) return -9;
   mfq::ArParams ar;
+  ar.mode = reduce_scatter ? 1 : 0;
   ar.world = world;
   ar.rank = rank;
   for (int r = 0; r < world; ++r) {
@@ -400,6 +508,45 @@ extern "C" int mfq_fp8_gemm_allreduce(const void* w, const float* w_scale, const
     case 128: return mfq::launch_gemm<128>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
     default: return -1;
   }
+}
+
+__global__ void bump_epoch_kernel(uint32_t* epoch) { *epoch += 1; }
+
+// All-gather -> GEMM: x_shard [M / world, K] E4M3 (+ xs_shard multipliers) is this rank's slice of the token rows; the
+// kernel gathers all slices through peer memory while it multiplies (see AgParams) and writes out [M, N] bf16.
+// x_full[r] / xs_full[r] / flags[r]: rank r's gathered buffers (2 * M * K bytes, 2 * M floats, `world` counters);
+// epoch, push_done: local words, zero before first use.  M must be a multiple of world.
+extern "C" int mfq_fp8_gemm_allgather(const void* w, const float* w_scale, const void* x_shard, const float* xs_shard,
+                                      void* out, int* status, int M, int N, int K, int token_tile, int world, int rank,
+                                      void* const* x_full, void* const* xs_full, void* const* flags, void* epoch,
+                                      void* push_done, int push_ctas, cudaStream_t stream) {
+  if (K % 128 != 0 || M <= 0 || N <= 0 || world < 2 || world > 8 || M % world != 0 || push_ctas < 1) return -1;
+  if ((size_t(M / world) * K) % 16 != 0) return -1;
+  mfq::AgParams ag;
+  ag.world = world;
+  ag.rank = rank;
+  ag.push_ctas = push_ctas;
+  ag.shard_rows = M / world;
+  for (int r = 0; r < world; ++r) {
+    ag.x_full[r] = static_cast<uint8_t*>(x_full[r]);
+    ag.xs_full[r] = static_cast<float*>(xs_full[r]);
+    ag.flags[r] = static_cast<uint32_t*>(flags[r]);
+  }
+  ag.x_shard = static_cast<const uint8_t*>(x_shard);
+  ag.xs_shard = xs_shard;
+  ag.epoch = static_cast<const uint32_t*>(epoch);
+  ag.push_done = static_cast<uint32_t*>(push_done);
+  int rc;
+  switch (token_tile) {
+    case 16: rc = mfq::launch_gemm<16>(w, w_scale, nullptr, nullptr, out, nullptr, nullptr, 0, nullptr, 0, status, M, N, K, 1, stream, nullptr, 0, nullptr, nullptr, 0, &ag); break;
+    case 32: rc = mfq::launch_gemm<32>(w, w_scale, nullptr, nullptr, out, nullptr, nullptr, 0, nullptr, 0, status, M, N, K, 1, stream, nullptr, 0, nullptr, nullptr, 0, &ag); break;
+    case 64: rc = mfq::launch_gemm<64>(w, w_scale, nullptr, nullptr, out, nullptr, nullptr, 0, nullptr, 0, status, M, N, K, 1, stream, nullptr, 0, nullptr, nullptr, 0, &ag); break;
+    case 128: rc = mfq::launch_gemm<128>(w, w_scale, nullptr, nullptr, out, nullptr, nullptr, 0, nullptr, 0, status, M, N, K, 1, stream, nullptr, 0, nullptr, nullptr, 0, &ag); break;
+    default: return -1;
+  }
+  if (rc != 0) return rc;
+  bump_epoch_kernel<<<1, 1, 0, stream>>>(static_cast<uint32_t*>(epoch));
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
 // Grouped GEMM over expert-sorted token rows (mixture of experts): w [E, N, K] E4M3 with w_scale [E, N/128, K/128];

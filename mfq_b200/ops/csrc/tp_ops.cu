@@ -212,3 +212,38 @@ extern "C" int mfq_allreduce_rows(const void* partial, const void* residual, voi
                                                        static_cast<__nv_bfloat16*>(out), H, rp, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// peer_barrier: every rank bumps a counter on every peer and waits until all peers bumped its own (bounded wait).
+// Stream-ordered on each rank, so it separates "everything before" on all ranks from "everything after".
+// ---------------------------------------------------------------------------------------------------------------
+namespace mfq {
+__global__ void peer_barrier_kernel(int world, int rank, uint32_t* f0, uint32_t* f1, uint32_t* f2, uint32_t* f3, uint32_t* f4,
+                                    uint32_t* f5, uint32_t* f6, uint32_t* f7, uint32_t* expected, int* status) {
+  uint32_t* flags[8] = {f0, f1, f2, f3, f4, f5, f6, f7};
+  const uint32_t target = *expected + uint32_t(world - 1);
+  __threadfence_system();
+  for (int r = 0; r < world; ++r)
+    if (r != rank) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flags[r]) : "memory");
+  const unsigned long long t_start = globaltimer_ns();
+  uint32_t seen, spins = 0;
+  while (true) {
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags[rank]) : "memory");
+    if (int32_t(seen - target) >= 0) break;
+    if ((++spins & 0x3F) == 0 && globaltimer_ns() - t_start > kWaitBudgetNs) {
+      atomicCAS(status, 0, kStatusTimeoutPeer);
+      break;
+    }
+  }
+  *expected = target;
+}
+}  // namespace mfq
+
+extern "C" int mfq_peer_barrier(int world, int rank, void* const* flags, void* expected, int* status, cudaStream_t stream) {
+  if (world < 2 || world > 8) return -1;
+  uint32_t* f[8] = {};
+  for (int r = 0; r < world; ++r) f[r] = static_cast<uint32_t*>(flags[r]);
+  mfq::peer_barrier_kernel<<<1, 1, 0, stream>>>(world, rank, f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7],
+                                                static_cast<uint32_t*>(expected), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}

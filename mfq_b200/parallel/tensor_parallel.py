@@ -58,9 +58,63 @@ class TensorParallel:
         rc = lib().mfq_fp8_gemm_allreduce(
             ptr(lin.q), ptr(lin.scale), ptr(x_q), ptr(x_scale), ptr(h), ptr(h), ptr(ws.splitk), ws.splitk.numel(),
             ptr(ws.counters), ws.counters.numel(), ptr(ws.status), m, n, k, bt, K.pick_splits(m, n, k), self.world,
-            self.rank, ctx.buf_table, ctx.flag_table, ptr(ctx.expected), ctx.half_elems, stream_ptr())
+            self.rank, ctx.buf_table, ctx.flag_table, ptr(ctx.expected), ctx.half_elems, 0, stream_ptr())
         check(rc, "fp8_gemm_allreduce")
         return h
+
+    def gemm_reduce_scatter(self, lin, x_q: torch.Tensor, x_scale: torch.Tensor, residual_shard: torch.Tensor | None = None,
+                            token_tile: int = 128) -> torch.Tensor:
+        """Row-parallel GEMM whose epilogue reduce-scatters over token rows: returns this rank's ``[M/W, N]`` shard of
+        ``sum_r x_r @ lin_r^T (+ residual_shard)``.  ``M`` must be a multiple of ``W * token_tile``."""
+        m, k = x_q.shape
+        n = lin.q.shape[0]
+        key = ("rs", token_tile, n, math.ceil(m / token_tile))
+        ctx = self._ctx.get(key)
+        if ctx is None:
+            ctx = self._ctx[key] = _ReduceContext(self, token_tile, n, math.ceil(m / token_tile))
+        out = torch.empty((m // self.world, n), dtype=torch.bfloat16, device=self.device)
+        ws = Workspace.get(self.device)
+        rc = lib().mfq_fp8_gemm_allreduce(
+            ptr(lin.q), ptr(lin.scale), ptr(x_q), ptr(x_scale), ptr(out), ptr(residual_shard), ptr(ws.splitk),
+            ws.splitk.numel(), ptr(ws.counters), ws.counters.numel(), ptr(ws.status), m, n, k, token_tile, 1, self.world,
+            self.rank, ctx.buf_table, ctx.flag_table, ptr(ctx.expected), ctx.half_elems, 1, stream_ptr())
+        check(rc, "fp8_gemm_reduce_scatter")
+        return out
+
+    def allgather_gemm(self, lin, xq_shard: torch.Tensor, xs_shard: torch.Tensor, token_tile: int = 128,
+                       push_ctas: int = 16) -> torch.Tensor:
+        """Column-parallel GEMM over token-sharded input: gathers the shards through peer memory inside the kernel
+        and returns ``[M, N_local]``."""
+        ms, k = xq_shard.shape
+        m = ms * self.world
+        n = lin.q.shape[0]
+        key = ("ag", m, k)
+        ctx = self._ctx.get(key)
+        if ctx is None:
+            class _AgCtx:
+                pass
+            ctx = _AgCtx()
+            ctx.x = PeerBuffer(self.group, 2 * m * k, self.device)
+            ctx.xs = PeerBuffer(self.group, 2 * m * 4, self.device)
+            ctx.flags = PeerBuffer(self.group, 256, self.device)
+            ctx.words = torch.zeros(2, dtype=torch.int32, device=self.device)  # epoch, push_done
+            ctx.tables = (ctx.x.table(), ctx.xs.table(), ctx.flags.table())
+            self._ctx[key] = ctx
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
+        ws = Workspace.get(self.device)
+        rc = lib().mfq_fp8_gemm_allgather(ptr(lin.q), ptr(lin.scale), ptr(xq_shard), ptr(xs_shard), ptr(out), ptr(ws.status),
+                                          m, n, k, token_tile, self.world, self.rank, *ctx.tables, ctx.words.data_ptr(),
+                                          ctx.words.data_ptr() + 4, push_ctas, stream_ptr())
+        check(rc, "fp8_gemm_allgather", 2)
+        return out
+
+    def barrier(self) -> None:
+        """Device-side barrier of all ranks on the current stream (bounded wait, no host synchronisation)."""
+        if not hasattr(self, "_bar"):
+            self._bar = (PeerBuffer(self.group, 256, self.device), torch.zeros(1, dtype=torch.int32, device=self.device))
+        flags, expected = self._bar
+        ws = Workspace.get(self.device)
+        check(lib().mfq_peer_barrier(self.world, self.rank, flags.table(), ptr(expected), ptr(ws.status), stream_ptr()), "peer_barrier")
 
     def argmax(self, logits_shard: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         b, v = logits_shard.shape

@@ -62,6 +62,35 @@ def main() -> None:
     result["ranks_agree"] = all(torch.equal(g, gathered[0]) for g in gathered)
     eager = LLMEngine(LlamaModel(cfg, w, collective=tp), max_batch=4, max_seq_len=128, use_graphs=False)
     result["graph_equals_eager"] = bool(torch.equal(eager.generate(prompts, 10).tokens.to(dev), toks))
+    # fused GEMM -> reduce-scatter and all-gather -> GEMM against unfused references
+    from mfq_b200.models.llama import Fp8Linear
+    from mfq_b200.ops import reference as ref
+    g = torch.Generator(device=dev).manual_seed(11)  # same values on every rank
+    m_tok, n_out, k_full = 256 * world, 384, 512 * world
+    x_full = torch.randn((m_tok, k_full), generator=g, device=dev).to(torch.bfloat16)
+    w_full = (torch.randn((n_out, k_full), generator=g, device=dev) * 0.05).to(torch.bfloat16)
+    ks = k_full // world
+    xq, xs = ref.quant_rows(x_full[:, rank * ks:(rank + 1) * ks])
+    lin = Fp8Linear.from_float(w_full[:, rank * ks:(rank + 1) * ks].contiguous())
+    partial = ref.fp8_gemm(xq, xs, lin.q, lin.scale).float()
+    dist.all_reduce(partial)
+    res = torch.randn((m_tok, n_out), generator=g, device=dev).to(torch.bfloat16)
+    rows = slice(rank * m_tok // world, (rank + 1) * m_tok // world)
+    for it in range(3):
+        got = tp.gemm_reduce_scatter(lin, xq, xs, res[rows].contiguous(), token_tile=128)
+        tp.barrier()
+    want = (partial[rows] + res[rows].float())
+    result["rs_max_err"] = float((got.float() - want).abs().max() / want.abs().max())
+    w_col = Fp8Linear.from_float((torch.randn((256, 512), generator=g, device=dev) * 0.05).to(torch.bfloat16))
+    xa = torch.randn((m_tok, 512), generator=g, device=dev).to(torch.bfloat16)
+    xaq, xas = ref.quant_rows(xa)
+    for it in range(3):
+        got_ag = tp.allgather_gemm(w_col, xaq[rows].contiguous(), xas[rows].contiguous(), token_tile=128, push_ctas=4)
+    want_ag = ref.fp8_gemm(xaq, xas, w_col.q, w_col.scale).float()
+    result["ag_max_err"] = float((got_ag.float() - want_ag).abs().max() / want_ag.abs().max())
+    torch.cuda.synchronize()
+    Workspace.get(dev).check()
+
     # expert parallelism: routed experts split over the ranks, shared expert and attention tensor-parallel
     from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
     from mfq_b200.models.moe_lm import MoeConfig, init_weights, quantize_moe_checkpoint
@@ -75,6 +104,7 @@ def main() -> None:
     one_logits = prefill_logits(one_model, LLMEngine(one_model, max_batch=4, max_seq_len=128, use_graphs=False), prompt, dev)
     result["ep_vs_single_max_err"] = float((ep_logits - one_logits).abs().max())
     result["ep_logit_scale"] = float(one_logits.abs().max())
+    result["ep_vs_single_mean_err"] = float((ep_logits - one_logits).abs().mean())
     ep_toks = ep_engine.generate(prompts, 6).tokens.to(dev)
     gathered = [torch.empty_like(ep_toks) for _ in range(world)]
     dist.all_gather(gathered, ep_toks)
