@@ -14,12 +14,28 @@ import torch.distributed as dist
 from ..ops.lib import lib
 
 
+class _RawCudaMemory:
+    """Exposes a raw device range through ``__cuda_array_interface__`` so torch can alias it without copying."""
+
+    def __init__(self, address: int, nbytes: int, owner) -> None:
+        self.owner = owner  # keeps the allocation alive as long as the tensor
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 3,
+                                         "strides": None}
+
+
+def alias_device_memory(address: int, nbytes: int, device: torch.device, owner=None) -> torch.Tensor:
+    """uint8 tensor over ``[address, address + nbytes)`` of ``device`` (zero-copy)."""
+    with torch.cuda.device(device):
+        return torch.as_tensor(_RawCudaMemory(address, nbytes, owner), device=device)
+
+
 class PeerBuffer:
     def __init__(self, group, nbytes: int, device: torch.device) -> None:
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.nbytes = nbytes
+        self.device = device
         L = lib()
         L.mfq_ipc_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]
         L.mfq_ipc_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
@@ -46,6 +62,10 @@ class PeerBuffer:
                 self._opened.append(p.value)
         self._own = own.value
         dist.barrier(group=group)
+
+    def local_tensor(self) -> torch.Tensor:
+        """This rank's own allocation as a uint8 tensor (zero-copy alias; peers write into it)."""
+        return alias_device_memory(self._own, self.nbytes, self.device, owner=self)
 
     def table(self):
         """ctypes array of ``world`` device pointers (index = rank)."""

@@ -109,6 +109,45 @@ def main() -> None:
     gathered = [torch.empty_like(ep_toks) for _ in range(world)]
     dist.all_gather(gathered, ep_toks)
     result["ep_ranks_agree"] = all(torch.equal(g, gathered[0]) for g in gathered)
+    # token-sharded dispatch -> local experts -> combine through peer memory, against all experts on one GPU
+    from mfq_b200.ops import moe as moe_ops
+    from mfq_b200.ops import reference as ref
+    from mfq_b200.parallel.expert_parallel import ExpertParallel, NcclExpertParallel
+    from mfq_b200.quantize.fp8_block import quantize_fp8_block_torch
+    g = torch.Generator(device=dev).manual_seed(11)  # same stream on every rank: identical global problem
+    t_all, hh, inter, ne, kk = 96 * world, 512, 256, 8 * world, 4
+    xa = torch.randn((t_all, hh), generator=g, device=dev).to(torch.bfloat16)
+    gu_f = (torch.randn((ne, 2 * inter, hh), generator=g, device=dev) * 0.05).to(torch.bfloat16)
+    dn_f = (torch.randn((ne, hh, inter), generator=g, device=dev) * 0.05).to(torch.bfloat16)
+    gq, gs = (torch.stack(z) for z in zip(*[quantize_fp8_block_torch(m) for m in gu_f]))
+    dq, ds = (torch.stack(z) for z in zip(*[quantize_fp8_block_torch(m) for m in dn_f]))
+    ids_all = torch.stack([torch.randperm(ne, generator=g, device=dev)[:kk] for _ in range(t_all)]).to(torch.int32)
+    wt_all = torch.rand((t_all, kk), generator=g, device=dev)
+    base_all = torch.randn((t_all, hh), generator=g, device=dev).to(torch.bfloat16)
+    xq_all, xs_all = ref.quant_rows(xa)
+    want_all = moe_ops.moe_ffn_fp8(xq_all, xs_all, ids_all, wt_all, gq, gs, dq, ds, base=base_all).float()
+    # uneven shards: rank r owns a different number of tokens
+    cuts = [0] + [int(t_all * (r + 1) / world) - (7 if r + 1 < world else 0) for r in range(world)]
+    lo, hi = cuts[rank], cuts[rank + 1]
+    e_per = ne // world
+    mine = slice(rank * e_per, (rank + 1) * e_per)
+    ep = ExpertParallel(dist.group.WORLD, dev, num_experts=ne, top_k=kk, hidden=hh, max_tokens=128 * world)
+    a2a_err = 0.0
+    for _ in range(3):
+        got = ep.moe_ffn(xq_all[lo:hi].contiguous(), xs_all[lo:hi].contiguous(), ids_all[lo:hi].contiguous(),
+                         wt_all[lo:hi].contiguous(), gq[mine].contiguous(), gs[mine].contiguous(), dq[mine].contiguous(),
+                         ds[mine].contiguous(), base=base_all[lo:hi].contiguous(), cap=max(b - a for a, b in zip(cuts, cuts[1:])))
+        a2a_err = max(a2a_err, float((got.float() - want_all[lo:hi]).abs().max() / want_all.abs().max()))
+    # library baseline moves the same rows
+    nep = NcclExpertParallel(dist.group.WORLD, dev, num_experts=ne, top_k=kk, hidden=hh, max_tokens=0)
+    rx, rs_, rids, rw, ctx = nep.dispatch(xq_all[lo:hi].contiguous(), xs_all[lo:hi].contiguous(), ids_all[lo:hi].contiguous(),
+                                          wt_all[lo:hi].contiguous())
+    y_tok = moe_ops.moe_ffn_fp8(rx, rs_, rids, rw, gq[mine].contiguous(), gs[mine].contiguous(), dq[mine].contiguous(),
+                                ds[mine].contiguous(), e_lo=rank * e_per, base=None)
+    got_n = nep.combine(y_tok, ctx, base=base_all[lo:hi])
+    errs = torch.tensor([a2a_err, float((got_n.float() - want_all[lo:hi]).abs().max() / want_all.abs().max())], device=dev)
+    dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+    result["a2a_max_err"], result["a2a_nccl_max_err"] = float(errs[0]), float(errs[1])
     torch.cuda.synchronize()
     Workspace.get(dev).check()
     dist.barrier()
