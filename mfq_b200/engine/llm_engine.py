@@ -43,16 +43,20 @@ class GenerationResult:
 
 class LLMEngine:
     def __init__(self, model: LlamaModel, *, max_batch: int = 64, max_seq_len: int = 8192, num_pages: int | None = None,
-                 device=None, use_graphs: bool = True) -> None:
+                 device=None, use_graphs: bool = True, mtp_draft_tokens: int = 0) -> None:
+        """``mtp_draft_tokens`` (K, 0 = off): with a model that carries an MTP head, greedy rows decode by
+        draft/verify cycles that confirm between 1 and K+1 tokens each (:meth:`mtp_step`)."""
         self.model = model
         cfg = model.cfg
+        has_head = getattr(model.w, "mtp", None) is not None
+        self.mtp_k = mtp_draft_tokens if has_head else 0
         self.device = torch.device(device) if device is not None else model.w.embed.device
         self.max_batch = max_batch
         self.max_seq_len = max_seq_len
         pages_per_seq = (max_seq_len + PAGE_SIZE - 1) // PAGE_SIZE
         if num_pages is None:
             num_pages = max_batch * pages_per_seq + 1
-        self.cache = PagedKVCache(layers=cfg.num_layers, kv_heads=model.hk, head_dim=cfg.head_dim, num_pages=num_pages,
+        self.cache = PagedKVCache(layers=cfg.num_layers + (1 if has_head else 0), kv_heads=model.hk, head_dim=cfg.head_dim, num_pages=num_pages,
                                   max_seqs=max_batch, max_pages_per_seq=pages_per_seq, device=self.device)
         dev = self.device
         self.input_ids = torch.zeros(max_batch, dtype=torch.int32, device=dev)
@@ -72,6 +76,23 @@ class LLMEngine:
         self.row_len: dict[int, int] = {}  # host mirror of seq_lens for page management
         self.row_stochastic: dict[int, bool] = {}
         self._next_seq_id = 0
+        if self.mtp_k:
+            k, w = self.mtp_k, self.mtp_k + 1
+            if w * (cfg.num_heads // max(1, cfg.num_kv_heads)) > 16:
+                raise ValueError("the verify window (K+1 tokens x query heads per KV head) exceeds 16 attention rows")
+
+            def i32(*shape, fill=0):
+                return torch.full(shape, fill, dtype=torch.int32, device=dev)
+            self.draft = i32(max_batch, k)
+            self.v_ids, self.v_pos, self.v_slots = i32(max_batch * w), i32(max_batch * w), i32(max_batch * w, fill=-1)
+            self.v_lens = i32(max_batch)
+            self.targets, self.head_next = i32(max_batch * w), i32(max_batch * w)
+            self.out_tokens, self.n_out, self.accept_row = i32(max_batch, w, fill=-1), i32(max_batch), i32(max_batch)
+            self.c_tok, self.c_ids, self.c_pos, self.c_lens = i32(max_batch), i32(max_batch), i32(max_batch), i32(max_batch)
+            self.c_slots = i32(max_batch, fill=-1)
+            self.mtp_counters = torch.zeros(2, dtype=torch.int64, device=dev)  # drafted, accepted
+            self.mtp_graphs: dict[int, torch.cuda.CUDAGraph] = {}
+            self.mtp_cycles = 0
 
     # -- capacity (scheduler backend protocol) ------------------------------------------------------------------
     def free_tokens(self) -> int:
@@ -83,7 +104,7 @@ class LLMEngine:
 
     def can_grow(self, row: int) -> bool:
         """Make sure the row has a page for its next token; False when the pool is exhausted."""
-        need = self.row_len[row] + 1
+        need = self.row_len[row] + 1 + self.mtp_k  # a verify window writes K rows past the next token
         if need > self.max_seq_len:
             return False
         try:
@@ -179,7 +200,10 @@ class LLMEngine:
         step = StepBuffers(input_ids=ids, positions=torch.arange(n, dtype=torch.int32, device=dev),
                            slots=self.cache.slots(seq_id, 0, n).to(dev), cu_seqlens=[0, n])
         last = torch.tensor([n - 1], dtype=torch.int32, device=dev)
-        logits = self.model.forward(step, self.cache, prefill=True, logits_rows=last, gather_logits=False)
+        logits = self.model.forward(step, self.cache, prefill=True, logits_rows=last, gather_logits=False,
+                                    return_hidden=bool(self.mtp_k))
+        if self.mtp_k:
+            logits, hidden = logits
         self.seq_lens[row] = n
         self.row_len[row] = n
         if self.row_stochastic[row]:
@@ -194,26 +218,36 @@ class LLMEngine:
         else:
             tok = self.model.sample_greedy(logits)[0]
         self.sampled[row] = tok
+        if self.mtp_k:
+            # teacher-forced priming of the head over the prompt: position i pairs hidden[i] with token i+1
+            nxt = torch.cat([ids[1:], tok.reshape(1).to(torch.int32)])
+            mstep = StepBuffers(input_ids=nxt, positions=step.positions, slots=step.slots, cu_seqlens=[0, n])
+            mlogits, mhid = self.model.mtp_forward(mstep, self.cache, hidden, prefill=True, logits_rows=last)
+            self.draft[row, 0] = self.model.sample_greedy(mlogits)[0]
+            self._mtp_chain(row, row + 1, mhid[n - 1 : n].contiguous(), masked=False)
         return int(tok)
 
     def grow(self, row: int, tokens: int) -> None:
         self.cache.assign(row, self.row_seq[row], min(self.max_seq_len, tokens))
 
     # -- decode --------------------------------------------------------------------------------------------------
+    def _advance(self, sampled, input_ids, positions, seq_lens, slots, table, active) -> None:
+        """Feed ``sampled`` as the next input: its position, KV slot, and ``seq_lens += 1`` (active rows only)."""
+        if self.device.type == "cuda":
+            ops.decode_advance(sampled, input_ids, positions, seq_lens, slots, table, self.cache.page_size, active=active)
+            return
+        act = active.bool() if active is not None else torch.ones_like(sampled, dtype=torch.bool)
+        input_ids.copy_(torch.where(act, sampled, input_ids))
+        pos = seq_lens.clone()
+        positions.copy_(torch.where(act, pos, positions))
+        pages = table.gather(1, (pos // self.cache.page_size).long()[:, None])[:, 0]
+        slots.copy_(torch.where(act, pages * self.cache.page_size + pos % self.cache.page_size, torch.full_like(pos, -1)))
+        seq_lens.copy_(torch.where(act, pos + 1, pos))
+
     def _decode_body(self, b: int, stochastic: bool = False) -> None:
         dev = self.device
-        if dev.type == "cuda":
-            ops.decode_advance(self.sampled[:b], self.input_ids[:b], self.positions[:b], self.seq_lens[:b], self.slots[:b],
-                               self.cache.block_table[:b], self.cache.page_size, active=self.active[:b])
-        else:
-            act = self.active[:b].bool()
-            self.input_ids[:b] = torch.where(act, self.sampled[:b], self.input_ids[:b])
-            pos = self.seq_lens[:b].clone()
-            self.positions[:b] = torch.where(act, pos, self.positions[:b])
-            pages = self.cache.block_table[:b].gather(1, (pos // self.cache.page_size).long()[:, None])[:, 0]
-            self.slots[:b] = torch.where(act, pages * self.cache.page_size + pos % self.cache.page_size,
-                                         torch.full_like(pos, -1))
-            self.seq_lens[:b] = torch.where(act, pos + 1, pos)
+        self._advance(self.sampled[:b], self.input_ids[:b], self.positions[:b], self.seq_lens[:b], self.slots[:b],
+                      self.cache.block_table[:b], self.active[:b])
         step = StepBuffers(input_ids=self.input_ids[:b], positions=self.positions[:b], slots=self.slots[:b],
                            block_table=self.cache.block_table[:b], seq_lens=self.seq_lens[:b])
         if dev.type == "cuda":
@@ -248,13 +282,97 @@ class LLMEngine:
             self.graphs[(b, stochastic)] = g
         g.replay()
 
-    def decode(self, rows: list[int]) -> dict[int, int]:
-        """Scheduler entry: one token for each of ``rows`` (other rows are masked off).  Returns ``{row: token}``."""
+    # -- MTP draft / verify ---------------------------------------------------------------------------------------
+    def _mtp_chain(self, r0: int, r1: int, hid: torch.Tensor, masked: bool = True) -> None:
+        """Drafts 2..K of rows ``[r0, r1)``: the head runs on its own previous output and draft, one position at a
+        time past the confirmed sequence (those KV rows are provisional and get rewritten by the next cycle)."""
+        if self.mtp_k < 2:
+            return
+        table = self.cache.block_table[r0:r1]
+        tok, ids, pos, lens, slots = (t[r0:r1] for t in (self.c_tok, self.c_ids, self.c_pos, self.c_lens, self.c_slots))
+        lens.copy_(self.seq_lens[r0:r1])
+        for j in range(2, self.mtp_k + 1):
+            tok.copy_(self.draft[r0:r1, j - 2])
+            self._advance(tok, ids, pos, lens, slots, table, self.active[r0:r1] if masked else None)
+            step = StepBuffers(input_ids=ids, positions=pos, slots=slots, block_table=table, seq_lens=lens)
+            logits, hid = self.model.mtp_forward(step, self.cache, hid, prefill=False)
+            self.model.sample_greedy(logits, out=tok)
+            self.draft[r0:r1, j - 1].copy_(tok)
+
+    def _mtp_body(self, b: int) -> None:
+        from ..ops import mtp as mtp_ops
+        k, w = self.mtp_k, self.mtp_k + 1
+        table = self.cache.block_table[:b]
+        ids, pos, slots, lens = self.v_ids[: b * w], self.v_pos[: b * w], self.v_slots[: b * w], self.v_lens[:b]
+        mtp_ops.prepare(self.sampled[:b], self.draft[:b], self.seq_lens[:b], table, self.active[:b], ids, pos, slots, lens,
+                        self.cache.page_size)
+        if self.device.type == "cuda":
+            from ..ops.kernels import attn_splits_for
+            self.model.attn_splits = attn_splits_for(b, self.model.hk, self.max_seq_len)
+        step = StepBuffers(input_ids=ids, positions=pos, slots=slots, block_table=table, seq_lens=lens, q_len=w)
+        logits, hidden = self.model.forward(step, self.cache, prefill=False, gather_logits=False, return_hidden=True)
+        targets = self.model.sample_greedy(logits, out=self.targets[: b * w])
+        # the head sees the TRUE successor of every window position, so whatever prefix is accepted its KV rows and
+        # its prediction at the last confirmed position are exact
+        mstep = StepBuffers(input_ids=targets, positions=pos, slots=slots, block_table=table, seq_lens=lens, q_len=w)
+        mlogits, mhid = self.model.mtp_forward(mstep, self.cache, hidden, prefill=False)
+        head_next = self.model.sample_greedy(mlogits, out=self.head_next[: b * w])
+        mtp_ops.accept(targets, head_next, self.active[:b], self.draft[:b], self.sampled[:b], self.seq_lens[:b],
+                       self.out_tokens[:b], self.n_out[:b], self.accept_row[:b], self.mtp_counters)
+        if k > 1:
+            self._mtp_chain(0, b, mtp_ops.select_rows(mhid, self.accept_row[:b], w))
+
+    def mtp_step(self, b: int) -> None:
+        """One draft/verify cycle for the active rows among ``[0, b)``: confirms ``n_out[r]`` in 1..K+1 tokens per
+        row (``out_tokens[r, :n_out[r]]``), all state stays on the device (one CUDA graph per batch bucket)."""
+        self.mtp_cycles += 1
+        if not self.use_graphs:
+            self._mtp_body(b)
+            return
+        g = self.mtp_graphs.get(b)
+        if g is None:
+            ops.Workspace.get(self.device)
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            saved = [t.clone() for t in (self.seq_lens, self.sampled, self.draft, self.mtp_counters)]
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._mtp_body(b)
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(g):
+                self._mtp_body(b)
+            self.launches_per_step[("mtp", b)] = ops.launch_count() - before
+            for dst, src in zip((self.seq_lens, self.sampled, self.draft, self.mtp_counters), saved):
+                dst.copy_(src)
+            self.mtp_graphs[b] = g
+        g.replay()
+
+    def mtp_stats(self) -> dict:
+        """Draft acceptance so far (the reference reports the same through its ``mtp_stats`` frame)."""
+        drafted, accepted = (int(v) for v in self.mtp_counters.cpu()) if self.mtp_k else (0, 0)
+        return {"draft_tokens": self.mtp_k, "drafted": drafted, "accepted": accepted,
+                "acceptance_rate": accepted / drafted if drafted else 0.0,
+                "tokens_per_cycle": 1.0 + (accepted / drafted * self.mtp_k if drafted else 0.0), "cycles": getattr(self, "mtp_cycles", 0)}
+
+    def decode(self, rows: list[int]) -> dict:
+        """Scheduler entry: advance each of ``rows`` (other rows are masked off).  Returns ``{row: token}``, or
+        ``{row: [tokens]}`` when the rows decode through MTP cycles."""
         b = bucket_for(max(rows) + 1)
         b = min(b, self.max_batch)
         mask = torch.zeros(self.max_batch, dtype=torch.int32)
         mask[rows] = 1
         self.active.copy_(mask.to(self.device), non_blocking=True)
+        if self.mtp_k and not any(self.row_stochastic.get(r, False) for r in rows):
+            self.mtp_step(b)
+            toks, counts = self.out_tokens[:b].cpu(), self.n_out[:b].cpu()
+            out = {}
+            for r in rows:
+                n = int(counts[r])
+                self.row_len[r] += n
+                out[r] = [int(t) for t in toks[r, :n]]
+            return out
         self.decode_step(b, any(self.row_stochastic.get(r, False) for r in rows))
         toks = self.sampled[:b].cpu()
         for r in rows:
@@ -272,8 +390,9 @@ class LLMEngine:
             torch.cuda.current_stream().synchronize()
 
     # -- convenience ---------------------------------------------------------------------------------------------
-    def generate(self, prompts: list[torch.Tensor], max_new_tokens: int) -> GenerationResult:
-        """Static-batch greedy generation (all prompts prefilled, then decoded together)."""
+    def generate(self, prompts: list[torch.Tensor], max_new_tokens: int, use_mtp: bool = False) -> GenerationResult:
+        """Static-batch greedy generation (all prompts prefilled, then decoded together).  ``use_mtp`` decodes by
+        draft/verify cycles (the host reads the per-row confirmed counts once per cycle)."""
         b = len(prompts)
         assert b <= self.max_batch
         cuda = self.device.type == "cuda"
@@ -282,15 +401,30 @@ class LLMEngine:
             ev[0].record()
         for row, p in enumerate(prompts):
             self.prefill(row, p)
-            self.grow(row, int(p.numel()) + max_new_tokens + 1)
+            self.grow(row, int(p.numel()) + max_new_tokens + 1 + 2 * self.mtp_k)
         self.active.fill_(1)
         if cuda:
             ev[1].record()
         out = torch.empty((b, max_new_tokens), dtype=torch.int32, device=self.device)
         out[:, 0] = self.sampled[:b]
-        for t in range(1, max_new_tokens):
-            self.decode_step(b)
-            out[:, t] = self.sampled[:b]
+        if use_mtp and self.mtp_k:
+            got = [1] * b
+            host = out.cpu()
+            while min(got) < max_new_tokens:
+                self.mtp_step(b)
+                toks, counts = self.out_tokens[:b].cpu(), self.n_out[:b].cpu()
+                for r in range(b):
+                    n = min(int(counts[r]), max_new_tokens - got[r])
+                    host[r, got[r] : got[r] + n] = toks[r, :n]
+                    got[r] += n
+                # rows that are done stop drafting; their state no longer matters
+                self.active[:b] = torch.tensor([int(g < max_new_tokens) for g in got], dtype=torch.int32).to(self.device)
+            out.copy_(host)
+            self.active.fill_(1)
+        else:
+            for t in range(1, max_new_tokens):
+                self.decode_step(b)
+                out[:, t] = self.sampled[:b]
         if cuda:
             ev[2].record()
             torch.cuda.synchronize()

@@ -104,7 +104,7 @@ class Backend(Protocol):
     def free_tokens(self) -> int: ...
     def tokens_needed(self, tokens: int) -> int: ...
     def prefill(self, row: int, tokens: list[int], params: SamplingParams) -> int: ...
-    def decode(self, rows: list[int]) -> dict[int, int]: ...
+    def decode(self, rows: list[int]) -> dict[int, int | list[int]]: ...  # a list: tokens confirmed by one MTP cycle
     def can_grow(self, row: int) -> bool: ...
     def release(self, row: int) -> None: ...
 
@@ -316,10 +316,13 @@ class ContinuousBatchScheduler:
             req = self.running.get(row)
             if req is None:
                 continue
-            self.stats.decode_tokens += 1
-            if self._accept_token(req, out[row]):
-                self._release(row)
-                self._finish(req, req.finish_reason)
+            produced = out[row] if isinstance(out[row], (list, tuple)) else [out[row]]
+            for tok in produced:  # an MTP cycle confirms several tokens; a stop token or the length cap ends early
+                self.stats.decode_tokens += 1
+                if self._accept_token(req, tok):
+                    self._release(row)
+                    self._finish(req, req.finish_reason)
+                    break
 
     def step(self) -> bool:
         """One scheduling step (a prefill or a batched decode).  Returns False when there was nothing to do."""

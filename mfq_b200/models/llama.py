@@ -88,6 +88,19 @@ class LlamaLayer:
 
 
 @dataclass
+class MtpHead:
+    """Multi-token-prediction module: ``z = eh_proj([rmsnorm(embed(next token)); rmsnorm(hidden)])`` followed by one
+    decoder block with its own KV layer; the output norm and the LM head are the main model's unless it has its own
+    norm (DeepSeek-V3 / Qwen3-Next style; reference: ``cpp_runtime/backends/cuda/engine/mtp.cpp``)."""
+
+    enorm: torch.Tensor
+    hnorm: torch.Tensor
+    eh_proj: Fp8Linear  # [H, 2H], replicated under tensor parallelism
+    layer: LlamaLayer
+    final_norm: torch.Tensor | None = None
+
+
+@dataclass
 class LlamaWeights:
     embed: torch.Tensor  # [V, H] bf16
     layers: list[LlamaLayer]
@@ -95,10 +108,11 @@ class LlamaWeights:
     lm_head: Fp8Linear
     tp_rank: int = 0
     tp_size: int = 1
+    mtp: MtpHead | None = None
 
     @classmethod
     def random_init(cls, cfg: LlamaConfig, device, seed: int = 0, std: float = 0.02, tp_rank: int = 0,
-                    tp_size: int = 1) -> "LlamaWeights":
+                    tp_size: int = 1, mtp: bool = False) -> "LlamaWeights":
         """N(0, std) weights, quantized layer by layer on ``device``.  Every rank draws the full matrix from the
         same seed and keeps its shard, so TP=n and TP=1 hold the same model."""
         dev = torch.device(device)
@@ -114,7 +128,7 @@ class LlamaWeights:
             return w.reshape(tp_size, parts // tp_size, -1)[tp_rank] if tp_size > 1 else w
 
         layers = []
-        for _ in range(cfg.num_layers):
+        for _ in range(cfg.num_layers + (1 if mtp else 0)):  # the last one becomes the MTP block
             wq, wk, wv = rnd(hq * d, h), rnd(hk * d, h), rnd(hk * d, h)
             wo = rnd(h, hq * d)
             wg, wu, wd = rnd(i, h), rnd(i, h), rnd(h, i)
@@ -136,8 +150,12 @@ class LlamaWeights:
         head = rnd(cfg.vocab_size, h)
         if tp_size > 1:
             head = rows_shard(head, cfg.vocab_size)
+        head_module = None
+        if mtp:
+            ones = torch.ones(h, dtype=torch.bfloat16, device=dev)
+            head_module = MtpHead(ones.clone(), ones.clone(), Fp8Linear.from_float(rnd(h, 2 * h)), layers.pop())
         return cls(embed, layers, torch.ones(h, dtype=torch.bfloat16, device=dev), Fp8Linear.from_float(head),
-                   tp_rank, tp_size)
+                   tp_rank, tp_size, head_module)
 
     def nbytes(self) -> int:
         total = self.embed.numel() * 2 + self.lm_head.q.numel()
@@ -238,28 +256,61 @@ class LlamaModel:
         return self._row_parallel(layer.down, hq_, hs, h)
 
     # -- forward ------------------------------------------------------------------------------------------------
-    def forward(self, step: StepBuffers, cache, *, prefill: bool, logits_rows: torch.Tensor | None = None,
-                gather_logits: bool = True):
-        """Returns bf16 logits ``[rows, vocab]`` (all tokens, or ``logits_rows`` of them).  With tensor parallelism
-        and ``gather_logits=False`` the result is this rank's vocabulary shard, for :meth:`sample_greedy`."""
-        w = self.w
-        ids = step.input_ids
-        h = ops.embed(ids, w.embed) if w.embed.is_cuda else w.embed[ids.long()].clone()
-        for li, layer in enumerate(w.layers):
-            kv = cache.layer(li)
-            xq, xs = self._norm_quant(h, layer.attn_norm)
-            qkv = layer.qkv(xq, xs)
-            attn = self._attention(qkv, kv, step, prefill)
-            aq, a_s = self._quant(attn)
-            h = self._row_parallel(layer.o_proj, aq, a_s, h)
-            h = self._ffn(h, layer)
-        if logits_rows is not None:
-            h = h[logits_rows.long()] if not h.is_cuda else h.index_select(0, logits_rows.long())
-        xq, xs = self._norm_quant(h, w.final_norm)
-        logits = w.lm_head(xq, xs)
+    def _embed(self, ids):
+        return ops.embed(ids, self.w.embed) if self.w.embed.is_cuda else self.w.embed[ids.long()].clone()
+
+    def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
+        xq, xs = self._norm_quant(h, layer.attn_norm)
+        qkv = layer.qkv(xq, xs)
+        attn = self._attention(qkv, kv, step, prefill)
+        aq, a_s = self._quant(attn)
+        h = self._row_parallel(layer.o_proj, aq, a_s, h)
+        return self._ffn(h, layer)
+
+    def _head(self, h, norm, gather_logits: bool):
+        xq, xs = self._norm_quant(h, norm)
+        logits = self.w.lm_head(xq, xs)
         if self.tp > 1 and gather_logits:
             logits = self.collective.gather_columns(logits)
         return logits
+
+    def forward(self, step: StepBuffers, cache, *, prefill: bool, logits_rows: torch.Tensor | None = None,
+                gather_logits: bool = True, return_hidden: bool = False):
+        """Returns bf16 logits ``[rows, vocab]`` (all tokens, or ``logits_rows`` of them).  With tensor parallelism
+        and ``gather_logits=False`` the result is this rank's vocabulary shard, for :meth:`sample_greedy`.
+        ``return_hidden`` adds the residual stream of every token before the output norm (the MTP head's input)."""
+        w = self.w
+        h = self._embed(step.input_ids)
+        for li, layer in enumerate(w.layers):
+            h = self._block(h, layer, cache.layer(li), step, prefill)
+        hidden = h
+        if logits_rows is not None:
+            h = h[logits_rows.long()] if not h.is_cuda else h.index_select(0, logits_rows.long())
+        logits = self._head(h, w.final_norm, gather_logits)
+        return (logits, hidden) if return_hidden else logits
+
+    def mtp_forward(self, step: StepBuffers, cache, hidden: torch.Tensor, *, prefill: bool,
+                    logits_rows: torch.Tensor | None = None):
+        """MTP head over the tokens of ``step``: row ``i`` pairs ``hidden[i]`` (the main model's, or the head's own
+        previous output when drafts are chained) with the embedding of ``step.input_ids[i]`` -- the token that
+        FOLLOWS that position -- and predicts the token after it.  The head's KV rows go to cache layer
+        ``num_layers`` at ``step.slots``.  Returns (vocabulary-shard logits, the head's output hidden states)."""
+        m = self.w.mtp
+        eps = self.cfg.rms_eps
+        e = self._embed(step.input_ids)
+        if e.is_cuda:
+            _, _, ye, _ = ops.rmsnorm_quant(e, m.enorm, eps, want_q=False, want_y=True)
+            _, _, yh, _ = ops.rmsnorm_quant(hidden, m.hnorm, eps, want_q=False, want_y=True)
+        else:
+            _, _, ye, _ = ref.rmsnorm_quant(e, m.enorm, eps)
+            _, _, yh, _ = ref.rmsnorm_quant(hidden, m.hnorm, eps)
+        zq, zs = self._quant(torch.cat([ye, yh], dim=1))
+        h = m.eh_proj(zq, zs)
+        h = self._block(h, m.layer, cache.layer(self.cfg.num_layers), step, prefill)
+        out_hidden = h
+        if logits_rows is not None:
+            h = h[logits_rows.long()] if not h.is_cuda else h.index_select(0, logits_rows.long())
+        return self._head(h, m.final_norm if m.final_norm is not None else self.w.final_norm, False), out_hidden
 
     def sample_greedy(self, logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """Arg-max token per row.  Under TP ``logits`` is this rank's vocabulary shard (``gather_logits=False``)."""

@@ -19,8 +19,6 @@ def test_tp_matches_single_gpu_and_nccl_baseline(world):
     require_gpu_lib()
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    if world > 2:
-        pytest.skip("the tiny test model has 2 KV heads")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29617", str(Path(__file__).with_name("tp_worker.py"))]

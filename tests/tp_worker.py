@@ -1,5 +1,6 @@
 """Child process of the tensor-parallel GPU test: launched by torch.distributed.run, one rank per GPU."""
 
+import dataclasses
 import json
 import os
 import sys
@@ -32,6 +33,8 @@ def main() -> None:
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     cfg = LlamaConfig.tiny()
+    if world > 2:  # enough heads / width for every rank to own whole 128-wide blocks
+        cfg = dataclasses.replace(cfg, num_heads=8, num_kv_heads=8, intermediate_size=128 * world)
     result = {"world": world}
     prompt = torch.randint(0, cfg.vocab_size, (48,), generator=torch.Generator().manual_seed(7))
 
@@ -95,8 +98,10 @@ def main() -> None:
     from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
     from mfq_b200.models.moe_lm import MoeConfig, init_weights, quantize_moe_checkpoint
     mcfg = MoeDecoderConfig.tiny()
+    heads = dict(num_heads=8, num_kv_heads=8) if world > 2 else {}
+    mcfg = dataclasses.replace(mcfg, **heads)
     ck = quantize_moe_checkpoint(init_weights(MoeConfig(head_dim=128, hidden_size=256, moe_intermediate=128,
-                                                        shared_intermediate=128), seed=4, std=0.05), "NINT4,NVQ3,MXFP4")
+                                                        shared_intermediate=128, **heads), seed=4, std=0.05), "NINT4,NVQ3,MXFP4")
     ep_model = MoeDecoderModel(mcfg, MoeWeights.from_tensors(mcfg, ck, dev, rank, world), collective=tp)
     ep_engine = LLMEngine(ep_model, max_batch=4, max_seq_len=128)
     ep_logits = prefill_logits(ep_model, ep_engine, prompt, dev)
