@@ -334,8 +334,28 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           const size_t off = rs ? half_off + (size_t(ar.rank) * tiles_owned + tile_local) * (BT * kTileN)
                                 : half_off + size_t(tile_id) * (BT * kTileN);
           float* mine = ar.bufs[tile_owner] + off;
+          const int ew = warp - 2;  // epilogue warp index: owns the contiguous chunk [ew][CW][32] of an RS slot
+          if (rs) {
+            // Reduce-scatter: the partial leaves through shared memory as ONE bulk copy per warp (8 KB for a 128-token
+            // tile) instead of 4-byte stores, which is what NVLink needs to run near its rate.  The pipeline stages
+            // are free by now: the last MMA of this tile has completed, so every TMA load was consumed.
+            float* stage = reinterpret_cast<float*>(tiles) + ew * (CW * 32);
 #pragma unroll
-          for (int tt = 0; tt < CW; ++tt) mine[(col0 + tt) * kTileN + row] = acc[tt];
+            for (int tt = 0; tt < CW; ++tt) stage[tt * 32 + lane] = acc[tt];
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(mine + ew * (CW * 32)),
+                           "r"(smem_u32(stage)), "r"(uint32_t(CW * 32 * sizeof(float)))
+                           : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+              asm volatile("fence.proxy.async;" ::: "memory");
+            }
+          } else {
+#pragma unroll
+            for (int tt = 0; tt < CW; ++tt) mine[(col0 + tt) * kTileN + row] = acc[tt];
+          }
           __threadfence_system();
           __syncwarp();
           if (lane == 0) mbar_arrive(&epi_bar[2]);
@@ -374,12 +394,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
             for (int r = 0; r < ar.world; ++r) {
               // AR: rank r's buffer, same slot (peer loads).  RS: my buffer, slot of source rank r (local loads).
-              const float* part = rs ? ar.bufs[ar.rank] + half_off + (size_t(r) * tiles_owned + tile_local) * (BT * kTileN) + row
-                                     : ar.bufs[r] + off + row;
+              const float* part = rs ? ar.bufs[ar.rank] + half_off + (size_t(r) * tiles_owned + tile_local) * (BT * kTileN) +
+                                           ew * (CW * 32) + lane
+                                     : ar.bufs[r] + off + row + col0 * kTileN;
+              const int stride = rs ? 32 : kTileN;
 #pragma unroll
               for (int tt = 0; tt < CW; ++tt) {
                 float v;
-                asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(part + (col0 + tt) * kTileN) : "memory");
+                asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(part + tt * stride) : "memory");
                 acc[tt] += v;
               }
             }

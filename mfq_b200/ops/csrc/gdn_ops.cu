@@ -1,0 +1,210 @@
+// Gated DeltaNet (linear attention with the gated delta rule) for decode, verify windows and prefill.
+//
+// Per value head h (key head h / (Hv/Hk)), with a [dk, dv] fp32 state S carried across tokens:
+//   q, k   <- l2norm(silu(conv1d(q, k)))   (q also scaled by dk^-1/2);  v <- silu(conv1d(v))
+//   decay  =  exp(-exp(A_log[h]) * softplus(a_t[h] + dt_bias[h]));      beta = sigmoid(b_t[h])
+//   S      <- decay * S;   delta = (v - S^T k) * beta;   S <- S + k delta^T;   o = S^T q
+//   y      =  rmsnorm(o) * w * silu(z)                                  (per head, over dv)
+// Kernels:
+//   gdn_conv        causal depthwise conv (4 taps) + SiLU over the packed q|k|v channels; a FIR, so every (token,
+//                   channel) is independent; the 3-token history of each sequence lives in a conv state.
+//   gdn_recurrent   one CTA per (sequence, value head), one thread per state column: the column S[:, j] stays in 128
+//                   registers for the whole token run, so a token costs 3*dk FMAs per thread and no cross-thread
+//                   reduction; k/q are normalised once per token in shared memory; the gated RMSNorm is fused.
+//                   State is read once and written once per launch (decode: 2 x 64 KB per head -- the HBM floor);
+//                   with `ckpt` the state after EVERY token of a short window is written instead, so that an MTP
+//                   verify pass can keep the state of the last accepted token (gdn_select).
+// Sequences are a regular [B, L] grid (decode: L = 1; verify: L = K+1; prefill: B = 1); slot[b] < 0 skips a row.
+// Reference counterparts: cpp_runtime/backends/cuda/kernels gdn_decode_core_kernel, ssm_conv_*_decode,
+// gdn_rms_norm_gate_kernel, gdn_prefill_chunk.cu (chunked mma.sync prefill), gdn_decode_window.cu (verify window).
+#include "common.cuh"
+
+namespace mfq {
+
+// x [B*L, C] bf16 (pre-conv), conv_state [slots, 3, C] fp32 (oldest first), w [C, 4] fp32, out [B*L, C] fp32.
+// conv_ckpt (optional) [B, L, 3, C]: history after each token, for verify windows (then conv_state is left alone).
+__global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ conv_state,
+                                const float* __restrict__ w, const int* __restrict__ slot, float* __restrict__ out,
+                                float* __restrict__ conv_ckpt, int L, int C) {
+  const int b = blockIdx.y;
+  const int s = slot[b];
+  if (s < 0) return;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float w0 = w[c * 4], w1 = w[c * 4 + 1], w2 = w[c * 4 + 2], w3 = w[c * 4 + 3];
+  float* st = conv_state + size_t(s) * 3 * C;
+  const float h0 = st[c], h1 = st[C + c], h2 = st[2 * C + c];
+  auto in = [&](int t) -> float {  // input of token t of this row; negative t reads the carried history
+    if (t >= 0) return __bfloat162float(x[(size_t(b) * L + t) * C + c]);
+    return t == -1 ? h2 : t == -2 ? h1 : h0;
+  };
+  for (int t = blockIdx.z; t < L; t += gridDim.z) {
+    const float y = w0 * in(t - 3) + w1 * in(t - 2) + w2 * in(t - 1) + w3 * in(t);
+    out[(size_t(b) * L + t) * C + c] = y / (1.f + __expf(-y));
+    if (conv_ckpt) {
+      float* ck = conv_ckpt + (size_t(b) * L + t) * 3 * C;
+      ck[c] = in(t - 2); ck[C + c] = in(t - 1); ck[2 * C + c] = in(t);
+    }
+  }
+}
+
+// History update, as a launch of its own AFTER the convolution: blocks of the convolution that handle the first
+// tokens still read the old history, so it cannot be overwritten by a sibling block of the same grid.
+__global__ void gdn_conv_state_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ conv_state,
+                                      const int* __restrict__ slot, int L, int C) {
+  const int b = blockIdx.y;
+  const int s = slot[b];
+  if (s < 0) return;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float* st = conv_state + size_t(s) * 3 * C;
+  const float h0 = st[c], h1 = st[C + c], h2 = st[2 * C + c];
+  auto in = [&](int t) -> float {
+    if (t >= 0) return __bfloat162float(x[(size_t(b) * L + t) * C + c]);
+    return t == -1 ? h2 : t == -2 ? h1 : h0;
+  };
+  const float n0 = in(L - 3), n1 = in(L - 2), n2 = in(L - 1);
+  st[c] = n0; st[C + c] = n1; st[2 * C + c] = n2;
+}
+
+struct GdnParams {
+  const float* qkv;         // [B*L, 2*Hk*dk + Hv*dv] fp32 after conv+SiLU (q | k | v)
+  const __nv_bfloat16* z;   // [B*L, Hv*dv] output gate (pre-SiLU)
+  const __nv_bfloat16* a;   // [B*L, Hv]
+  const __nv_bfloat16* bb;  // [B*L, Hv]
+  const float* A_log;       // [Hv]
+  const float* dt_bias;     // [Hv]
+  const float* norm_w;      // [dv]
+  float* state;             // [slots, Hv, dk, dv]
+  float* ckpt;              // optional [B, L, Hv, dk, dv]
+  const int* slot;          // [B]
+  __nv_bfloat16* y;         // [B*L, Hv*dv]
+  int L, Hk, Hv;
+  float eps;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(DV) gdn_recurrent_kernel(const GdnParams p) {
+  static_assert(DK == 128 && DV == 128, "one thread per state column, four k/q values per lane");
+  __shared__ float k_s[DK], q_s[DK];
+  __shared__ float red[DV / 32];
+  __shared__ float gate_s[2];
+  const int b = blockIdx.x / p.Hv, h = blockIdx.x % p.Hv;
+  const int slot = p.slot[b];
+  if (slot < 0) return;
+  const int col = threadIdx.x, lane = col & 31, warp = col >> 5;
+  const int hk = h / (p.Hv / p.Hk);
+  const int C = 2 * p.Hk * DK + p.Hv * DV;
+  float s[DK];
+  float* st = p.state + (size_t(slot) * p.Hv + h) * DK * DV;
+#pragma unroll
+  for (int i = 0; i < DK; ++i) s[i] = st[i * DV + col];
+  const float scale = rsqrtf(float(DK));
+  const float neg_a = -__expf(p.A_log[h]), dtb = p.dt_bias[h], nw = p.norm_w[col];
+  for (int t = 0; t < p.L; ++t) {
+    const size_t tok = size_t(b) * p.L + t;
+    const float* row = p.qkv + tok * C;
+    // warp 0 normalises q, warp 1 normalises k, warp 2 computes the gates
+    if (warp < 2) {
+      const float* src = row + (warp == 0 ? 0 : p.Hk * DK) + hk * DK;
+      const float4 v4 = *reinterpret_cast<const float4*>(src + lane * 4);
+      float ss = v4.x * v4.x + v4.y * v4.y + v4.z * v4.z + v4.w * v4.w;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float inv = rsqrtf(ss + 1e-6f) * (warp == 0 ? scale : 1.f);
+      float* dst = warp == 0 ? q_s : k_s;
+      dst[lane * 4] = v4.x * inv; dst[lane * 4 + 1] = v4.y * inv; dst[lane * 4 + 2] = v4.z * inv; dst[lane * 4 + 3] = v4.w * inv;
+    } else if (warp == 2 && lane == 0) {
+      const float av = __bfloat162float(p.a[tok * p.Hv + h]) + dtb;
+      const float sp = av > 20.f ? av : log1pf(__expf(av));
+      gate_s[0] = __expf(neg_a * sp);
+      gate_s[1] = 1.f / (1.f + __expf(-__bfloat162float(p.bb[tok * p.Hv + h])));
+    }
+    __syncthreads();
+    const float decay = gate_s[0], beta = gate_s[1];
+    float kv = 0.f;
+#pragma unroll
+    for (int i = 0; i < DK; ++i) kv = fmaf(s[i], k_s[i], kv);
+    const float v = row[2 * p.Hk * DK + h * DV + col];
+    const float delta = (v - decay * kv) * beta;
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < DK; ++i) {
+      s[i] = fmaf(s[i], decay, k_s[i] * delta);
+      o = fmaf(s[i], q_s[i], o);
+    }
+    // gated RMSNorm over the head's dv outputs
+    float ss = o * o;
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sft);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < DV / 32; ++i) tot += red[i];
+    const float zg = __bfloat162float(p.z[tok * p.Hv * DV + h * DV + col]);
+    const float yv = o * rsqrtf(tot / float(DV) + p.eps) * nw * (zg / (1.f + __expf(-zg)));
+    p.y[tok * p.Hv * DV + h * DV + col] = __float2bfloat16(yv);
+    if (p.ckpt) {
+      float* ck = p.ckpt + ((size_t(b) * p.L + t) * p.Hv + h) * DK * DV;
+#pragma unroll
+      for (int i = 0; i < DK; ++i) ck[i * DV + col] = s[i];
+    }
+    __syncthreads();  // k_s / q_s / red are rewritten by the next token
+  }
+  if (!p.ckpt) {
+#pragma unroll
+    for (int i = 0; i < DK; ++i) st[i * DV + col] = s[i];
+  }
+}
+
+// After a verify window: state[slot[b]] <- ckpt[b, keep[b]], conv_state likewise (keep = index of the last accepted
+// window position).  One CTA per (row, head); rows with slot < 0 are skipped.
+__global__ void gdn_select_kernel(const float* __restrict__ ckpt, const float* __restrict__ conv_ckpt,
+                                  float* __restrict__ state, float* __restrict__ conv_state, const int* __restrict__ slot,
+                                  const int* __restrict__ keep, int L, int Hv, int head_elems, int C) {
+  const int b = blockIdx.x / Hv, h = blockIdx.x % Hv;
+  const int s = slot[b];
+  if (s < 0) return;
+  const int t = min(max(keep[b], 0), L - 1);
+  const float4* src = reinterpret_cast<const float4*>(ckpt + ((size_t(b) * L + t) * Hv + h) * head_elems);
+  float4* dst = reinterpret_cast<float4*>(state + (size_t(s) * Hv + h) * head_elems);
+  for (int i = threadIdx.x; i < head_elems / 4; i += blockDim.x) dst[i] = src[i];
+  if (h == 0) {
+    const float* cs = conv_ckpt + (size_t(b) * L + t) * 3 * C;
+    float* cd = conv_state + size_t(s) * 3 * C;
+    for (int i = threadIdx.x; i < 3 * C; i += blockDim.x) cd[i] = cs[i];
+  }
+}
+
+}  // namespace mfq
+
+using namespace mfq;
+
+extern "C" int mfq_gdn_conv(const void* x, float* conv_state, const float* w, const int* slot, float* out, float* conv_ckpt,
+                            int B, int L, int C, cudaStream_t stream) {
+  if (B <= 0 || L <= 0 || C <= 0) return -1;
+  dim3 grid((C + 255) / 256, B, min(L, 64));
+  gdn_conv_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), conv_state, w, slot, out, conv_ckpt, L, C);
+  if (!conv_ckpt)
+    gdn_conv_state_kernel<<<dim3((C + 255) / 256, B), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), conv_state, slot, L, C);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_gdn_recurrent(const float* qkv, const void* z, const void* a, const void* b, const float* A_log,
+                                 const float* dt_bias, const float* norm_w, float* state, float* ckpt, const int* slot,
+                                 void* y, int B, int L, int Hk, int Hv, int dk, int dv, float eps, cudaStream_t stream) {
+  if (B <= 0 || L <= 0 || dk != 128 || dv != 128 || Hk <= 0 || Hv % Hk) return -1;
+  GdnParams p{qkv, static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(a),
+              static_cast<const __nv_bfloat16*>(b), A_log, dt_bias, norm_w, state, ckpt, slot,
+              static_cast<__nv_bfloat16*>(y), L, Hk, Hv, eps};
+  gdn_recurrent_kernel<128, 128><<<B * Hv, 128, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_gdn_select(const float* ckpt, const float* conv_ckpt, float* state, float* conv_state, const int* slot,
+                              const int* keep, int B, int L, int Hv, int dk, int dv, int C, cudaStream_t stream) {
+  if (B <= 0 || L <= 0 || (dk * dv) % 4) return -1;
+  gdn_select_kernel<<<B * Hv, 256, 0, stream>>>(ckpt, conv_ckpt, state, conv_state, slot, keep, L, Hv, dk * dv, C);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}

@@ -4,8 +4,9 @@ Run one process per GPU::
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 -m mfq_b200.parallel.bench_collectives
 
-Per case it prints one JSON line: fused and baseline time (CUDA events, max over ranks of the per-rank median, L2
-flushed and ranks aligned by a device-side barrier before every timed launch), the roofline time -- the slower of
+Per case it prints one JSON line: fused and baseline time (CUDA events around one CUDA-graph replay of the op, max
+over ranks of the per-rank median, L2 flushed and ranks aligned by a device-side barrier before every timed replay;
+the library all-to-all baseline synchronises with the host for its split sizes and runs eagerly), the roofline time -- the slower of
 FLOPs / GEMM peak and NVLink bytes / link bandwidth -- and the achieved fraction of it.
 
 Cases: row-parallel GEMM + all-reduce (small M) / reduce-scatter (M a multiple of W*128), all-gather + column-parallel
@@ -33,7 +34,24 @@ LINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU
 FP8_PEAK_TFLOPS = 2 * 1590.0  # twice the measured cuBLAS bf16 burst figure
 
 
-def _time(fn, tp: TensorParallel, flush: torch.Tensor, iters: int, warmup: int = 3) -> float:
+def _graphed(fn):
+    """``fn`` as a CUDA-graph replay (host launch cost out of the measurement); eager if it cannot be captured."""
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.graph(g):
+            fn()
+    except Exception:  # e.g. a library op that synchronises with the host
+        torch.cuda.synchronize()
+        return fn
+    return g.replay
+
+
+def _time(fn, tp: TensorParallel, flush: torch.Tensor, iters: int, warmup: int = 3, graph: bool = True) -> float:
+    if graph:
+        fn = _graphed(fn)
     pairs = []
     for i in range(warmup + iters):  # no host synchronisation inside: the host runs ahead while the flush executes
         flush.zero_()
@@ -138,15 +156,26 @@ def a2a_cases(tp: TensorParallel, dev, flush, args, emit) -> None:
             def fused_combine():
                 ep.combine(state["y"], state["plan"], state["recv"])
             evs = []
-            y_rows = torch.zeros((w * t * topk, hidden), dtype=torch.bfloat16, device=dev)
+            state["y"] = torch.zeros((w * t * topk, hidden), dtype=torch.bfloat16, device=dev)
+
+            def dispatch_and_plan():
+                fused_dispatch()
+                state["plan"] = moe_ops.plan_routes(state["recv"].ids, e_lo, e_lo + ep.e_per)
+            # dispatch and combine must alternate strictly, also while warming up and capturing
+            for _ in range(2):
+                dispatch_and_plan(); fused_combine()
+            torch.cuda.synchronize()
+            g_d, g_c = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_d):
+                dispatch_and_plan()
+            with torch.cuda.graph(g_c):
+                fused_combine()
             for i in range(3 + args.iters):
                 flush.zero_(); tp.barrier()
                 a, b, c, d = (torch.cuda.Event(enable_timing=True) for _ in range(4))
-                a.record(); fused_dispatch(); b.record()
-                state["plan"] = moe_ops.plan_routes(state["recv"].ids, e_lo, e_lo + ep.e_per)
-                state["y"] = y_rows
+                a.record(); g_d.replay(); b.record()
                 flush.zero_(); tp.barrier()
-                c.record(); fused_combine(); d.record()
+                c.record(); g_c.replay(); d.record()
                 evs.append((a, b, c, d))
             torch.cuda.synchronize()
             d_times = [a.elapsed_time(b) * 1e3 for a, b, _, _ in evs[3:]]
