@@ -197,8 +197,19 @@ class LLMEngine:
             raise
         self.set_sampling(row, params)
         ids = ids.to(dev, non_blocking=True)
-        step = StepBuffers(input_ids=ids, positions=torch.arange(n, dtype=torch.int32, device=dev),
-                           slots=self.cache.slots(seq_id, 0, n).to(dev), cu_seqlens=[0, n])
+        positions = torch.arange(n, dtype=torch.int32, device=dev)
+        slots = self.cache.slots(seq_id, 0, n).to(dev)
+        cu = [0, n]
+        tp = self.model.tp
+        if tp > 1 and n >= tp * 128 and n % (tp * 128):
+            # pad to a whole number of token tiles per rank so the row-parallel GEMMs take the reduce-scatter path;
+            # the pad rows form a sequence of their own and write no KV
+            pad = tp * 128 - n % (tp * 128)
+            ids = torch.cat([ids, torch.zeros(pad, dtype=torch.int32, device=dev)])
+            positions = torch.cat([positions, torch.arange(pad, dtype=torch.int32, device=dev)])
+            slots = torch.cat([slots, torch.full((pad,), -1, dtype=torch.int32, device=dev)])
+            cu = [0, n, n + pad]
+        step = StepBuffers(input_ids=ids, positions=positions, slots=slots, cu_seqlens=cu)
         last = torch.tensor([n - 1], dtype=torch.int32, device=dev)
         logits = self.model.forward(step, self.cache, prefill=True, logits_rows=last, gather_logits=False,
                                     return_hidden=bool(self.mtp_k))
@@ -220,8 +231,8 @@ class LLMEngine:
         self.sampled[row] = tok
         if self.mtp_k:
             # teacher-forced priming of the head over the prompt: position i pairs hidden[i] with token i+1
-            nxt = torch.cat([ids[1:], tok.reshape(1).to(torch.int32)])
-            mstep = StepBuffers(input_ids=nxt, positions=step.positions, slots=step.slots, cu_seqlens=[0, n])
+            nxt = torch.cat([ids[1:n], tok.reshape(1).to(torch.int32), ids[n:]])
+            mstep = StepBuffers(input_ids=nxt, positions=step.positions, slots=step.slots, cu_seqlens=cu)
             mlogits, mhid = self.model.mtp_forward(mstep, self.cache, hidden, prefill=True, logits_rows=last)
             self.draft[row, 0] = self.model.sample_greedy(mlogits)[0]
             self._mtp_chain(row, row + 1, mhid[n - 1 : n].contiguous(), masked=False)

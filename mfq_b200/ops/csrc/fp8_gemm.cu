@@ -322,23 +322,28 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           // CUDA-graph replay; the tile's launch count also selects one of two buffers, so a fast rank cannot
           // overwrite a partial that a slow rank is still reading.
           const ArParams& ar = p.ar;
-          const uint32_t before = ar.expected[tile_id];
-          const uint32_t target = before + uint32_t(ar.world - 1);
-          const size_t half_off = size_t((before / uint32_t(ar.world - 1)) & 1u) * ar.half_elems;
           const bool rs = ar.mode == 1;
+          const uint32_t before = ar.expected[tile_id];
+          // AR: flags advance by W-1 per launch; RS: `expected` simply counts the launches of this tile
+          const uint32_t target = before + uint32_t(ar.world - 1);
+          const size_t half_off = size_t((rs ? before : before / uint32_t(ar.world - 1)) & 1u) * ar.half_elems;
           const int t_per_rank = int(gridDim.y) / ar.world;            // token tiles owned by each rank (RS)
           const int tile_owner = rs ? t_tile / t_per_rank : ar.rank;   // AR: everyone "owns" (and sums) every tile
           const int tiles_owned = t_per_rank * n_tiles_x;
           const int tile_local = (t_tile % max(t_per_rank, 1)) * n_tiles_x + n_tile;
-          // AR: my partial goes to my own buffer at the tile's slot; RS: into the owner's buffer, slot [me][tile]
+          // AR: my partial goes to my own buffer at the slot of the tile; RS: into the owner buffer, slot [me][tile]
           const size_t off = rs ? half_off + (size_t(ar.rank) * tiles_owned + tile_local) * (BT * kTileN)
                                 : half_off + size_t(tile_id) * (BT * kTileN);
           float* mine = ar.bufs[tile_owner] + off;
-          const int ew = warp - 2;  // epilogue warp index: owns the contiguous chunk [ew][CW][32] of an RS slot
           if (rs) {
-            // Reduce-scatter: the partial leaves through shared memory as ONE bulk copy per warp (8 KB for a 128-token
-            // tile) instead of 4-byte stores, which is what NVLink needs to run near its rate.  The pipeline stages
-            // are free by now: the last MMA of this tile has completed, so every TMA load was consumed.
+            // Reduce-scatter: every rank (the owner too) sends its partial tile to the slot table of the owner while
+            // the other CTAs keep computing -- the transfer overlaps the math tile by tile -- and nobody waits here:
+            // the owner sums the W slots of its tiles in a short trailing kernel (rs_reduce_kernel), in rank order.
+            // The partial leaves through shared memory as ONE bulk copy per warp (8 KB for a 128-token tile) instead
+            // of 4-byte stores, which is what NVLink needs to run near its rate.  The pipeline stages are free by
+            // now: the last MMA of this tile has completed, so every TMA load was consumed.  Slot layout:
+            // [epilogue warp][token column inside the chunk of that warp][32 rows].
+            const int ew = warp - 2;
             float* stage = reinterpret_cast<float*>(tiles) + ew * (CW * 32);
 #pragma unroll
             for (int tt = 0; tt < CW; ++tt) stage[tt * 32 + lane] = acc[tt];
@@ -352,35 +357,36 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
               asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
               asm volatile("fence.proxy.async;" ::: "memory");
             }
+            __threadfence_system();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&epi_bar[2]);
+            const bool met = mbar_wait(&epi_bar[2], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
+            if (met && threadIdx.x == 64) {
+              asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[tile_owner] + tile_id) : "memory");
+              ar.expected[tile_id] = before + 1u;
+            }
+            owner = false;
           } else {
 #pragma unroll
-            for (int tt = 0; tt < CW; ++tt) mine[(col0 + tt) * kTileN + row] = acc[tt];
-          }
+          for (int tt = 0; tt < CW; ++tt) mine[(col0 + tt) * kTileN + row] = acc[tt];
           __threadfence_system();
           __syncwarp();
           if (lane == 0) mbar_arrive(&epi_bar[2]);
           bool met = mbar_wait(&epi_bar[2], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
-          const bool i_sum = !rs || tile_owner == ar.rank;
           if (met && threadIdx.x == 64) {
-            if (!rs) {
-              for (int r = 0; r < ar.world; ++r)
-                if (r != ar.rank)
-                  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[r] + tile_id) : "memory");
-            } else if (tile_owner != ar.rank) {
-              asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[tile_owner] + tile_id) : "memory");
-            }
-            if (i_sum) {
-              const uint32_t* my_flag = ar.flags[ar.rank] + tile_id;
-              const unsigned long long t_start = globaltimer_ns();
-              uint32_t seen, spins = 0;
-              while (true) {
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
-                if (int32_t(seen - target) >= 0) break;
-                if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t_start > kWaitBudgetNs)) {
-                  *abort_flag = 1;
-                  atomicCAS(p.status, 0, kStatusTimeoutPeer);
-                  break;
-                }
+            for (int r = 0; r < ar.world; ++r)
+              if (r != ar.rank)
+                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[r] + tile_id) : "memory");
+            const uint32_t* my_flag = ar.flags[ar.rank] + tile_id;
+            const unsigned long long t_start = globaltimer_ns();
+            uint32_t seen, spins = 0;
+            while (true) {
+              asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
+              if (int32_t(seen - target) >= 0) break;
+              if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t_start > kWaitBudgetNs)) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, kStatusTimeoutPeer);
+                break;
               }
             }
             ar.expected[tile_id] = target;
@@ -388,25 +394,21 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           __syncwarp();
           if (lane == 0) mbar_arrive(&epi_bar[3]);
           met = met && mbar_wait(&epi_bar[3], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
-          owner = met && !*abort_flag && i_sum;
+          owner = met && !*abort_flag;
           if (owner) {
 #pragma unroll
             for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
             for (int r = 0; r < ar.world; ++r) {
-              // AR: rank r's buffer, same slot (peer loads).  RS: my buffer, slot of source rank r (local loads).
-              const float* part = rs ? ar.bufs[ar.rank] + half_off + (size_t(r) * tiles_owned + tile_local) * (BT * kTileN) +
-                                           ew * (CW * 32) + lane
-                                     : ar.bufs[r] + off + row + col0 * kTileN;
-              const int stride = rs ? 32 : kTileN;
+              const float* part = ar.bufs[r] + off + row + col0 * kTileN;  // buffer of rank r, same slot (peer loads)
+              float v[CW];
 #pragma unroll
-              for (int tt = 0; tt < CW; ++tt) {
-                float v;
-                asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(part + tt * stride) : "memory");
-                acc[tt] += v;
-              }
+              for (int tt = 0; tt < CW; ++tt)
+                asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v[tt]) : "l"(part + tt * kTileN) : "memory");
+#pragma unroll
+              for (int tt = 0; tt < CW; ++tt) acc[tt] += v[tt];
             }
-            if (rs) t0 -= ar.rank * t_per_rank * BT;  // rows of the local output shard
           }
+          }  // all-reduce
         }
         if (owner && n < p.N) {
 #pragma unroll
@@ -498,6 +500,77 @@ extern "C" int mfq_fp8_gemm(const void* w, const float* w_scale, const void* x, 
   }
 }
 
+namespace mfq {
+// Trailing kernel of the GEMM -> reduce-scatter: one CTA per owned tile waits (bounded) until all W ranks delivered
+// their partial of the tile, sums the W slots in rank order (bit-identical run to run), adds the residual and writes
+// the bf16 rows of the output shard of this rank.
+__global__ void __launch_bounds__(128)
+rs_reduce_kernel(ArParams ar, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual, int N, int BT,
+                 int CW, int n_tiles, int t_per_rank, int* status) {
+  __shared__ int s_ok;
+  const int tile_local = blockIdx.x, t_local = tile_local / n_tiles, n_tile = tile_local % n_tiles;
+  const int tile_id = (ar.rank * t_per_rank + t_local) * n_tiles + n_tile;
+  const uint32_t launches = ar.expected[tile_id];  // the GEMM kernel of this launch already counted itself
+  if (threadIdx.x == 0) {
+    const uint32_t target = launches * uint32_t(ar.world);
+    const uint32_t* f = ar.flags[ar.rank] + tile_id;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t seen, spins = 0;
+    int ok = 1;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+      if (int32_t(seen - target) >= 0) break;
+      if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
+        atomicCAS(status, 0, kStatusTimeoutPeer);
+        ok = 0;
+        break;
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const size_t half_off = size_t((launches - 1u) & 1u) * ar.half_elems;
+  const int tiles_owned = t_per_rank * n_tiles;
+  const int row = threadIdx.x, n = n_tile * kTileN + row;
+  const int q = row >> 5, lane = row & 31;
+  const float* base = ar.bufs[ar.rank] + half_off + size_t(tile_local) * (BT * kTileN);
+  // the epilogue warp that produced (row quarter q, column half) is warp (q + 2) & 3 among the four warps of that half
+  const size_t src_stride = size_t(tiles_owned) * (BT * kTileN);
+  constexpr int kBatch = 4;  // columns in flight per thread: kBatch * 4 independent loads before the first add
+  for (int c0 = 0; c0 < BT; c0 += kBatch) {
+    float v[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) v[j] = 0.f;
+#pragma unroll 1
+    for (int r0 = 0; r0 < ar.world; r0 += 4) {
+      float part[kBatch][4];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int c = c0 + j;
+        const int ew = 4 * (c / CW) + ((q + 2) & 3);
+        const float* src = base + size_t(ew) * (CW * 32) + size_t(c % CW) * 32 + lane;
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) part[j][rr] = (r0 + rr < ar.world) ? __ldcg(src + size_t(r0 + rr) * src_stride) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j)
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) v[j] += part[j][rr];  // rank order
+    }
+    if (n < N) {
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const size_t o = size_t(t_local * BT + c0 + j) * N + n;
+        float val = v[j];
+        if (residual) val += __bfloat162float(residual[o]);
+        out[o] = __float2bfloat16(val);
+      }
+    }
+  }
+}
+}  // namespace mfq
+
 // Tensor-parallel row-parallel linear: the same GEMM with the cross-rank sum fused into its epilogue.  `bufs` /
 // `flags` hold `world` device pointers each (own buffer at index `rank`, the others peer-mapped); every buffer has
 // 2 * half_elems floats, every flag array at least ceil(N/128) * ceil(M/token_tile) counters, zero before first use.
@@ -523,13 +596,21 @@ extern "C" int mfq_fp8_gemm_allreduce(const void* w, const float* w_scale, const
   }
   ar.expected = static_cast<uint32_t*>(expected);
   ar.half_elems = half_elems;
+  int rc;
   switch (token_tile) {
-    case 16: return mfq::launch_gemm<16>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
-    case 32: return mfq::launch_gemm<32>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
-    case 64: return mfq::launch_gemm<64>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
-    case 128: return mfq::launch_gemm<128>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar);
+    case 16: rc = mfq::launch_gemm<16>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar); break;
+    case 32: rc = mfq::launch_gemm<32>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar); break;
+    case 64: rc = mfq::launch_gemm<64>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar); break;
+    case 128: rc = mfq::launch_gemm<128>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar); break;
     default: return -1;
   }
+  if (rc != 0 || !reduce_scatter) return rc;
+  const int n_tiles = (N + mfq::kTileN - 1) / mfq::kTileN, t_per_rank = (M / token_tile) / world;
+  const int cw = token_tile / (token_tile >= 64 ? 2 : 1);  // token columns per epilogue warp (GemmCfg::kCols)
+  mfq::rs_reduce_kernel<<<n_tiles * t_per_rank, 128, 0, stream>>>(ar, static_cast<__nv_bfloat16*>(out),
+                                                                 static_cast<const __nv_bfloat16*>(residual), N, token_tile,
+                                                                 cw, n_tiles, t_per_rank, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
 __global__ void bump_epoch_kernel(uint32_t* epoch) { *epoch += 1; }

@@ -247,3 +247,99 @@ extern "C" int mfq_peer_barrier(int world, int rank, void* const* flags, void* e
                                                 static_cast<uint32_t*>(expected), status);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// allgather_rows: every rank holds `rows` rows of `row_bytes` bytes; afterwards every rank holds all W * rows rows
+// in rank order.  The push kernel stores the local shard into every rank's staging buffer (16-byte coalesced
+// stores; half `epoch & 1`), the last CTA bumps one flag per destination; the collect kernel waits for the W flags
+// (bounded) and copies the staging half into `out`.  Together with the GEMM -> reduce-scatter epilogue this is the
+// two-shot all-reduce used for wide token batches, where a one-shot exchange would move W times the bytes.
+// ---------------------------------------------------------------------------------------------------------------
+namespace mfq {
+
+struct GatherParams {
+  int world, rank;
+  uint8_t* bufs[8];      // per rank: [2][world * shard_cap_bytes]
+  uint32_t* flags[8];    // per rank: [world]
+  uint32_t* words;       // local: [0] completed gathers, [1] CTA arrival counter
+  size_t half_bytes;     // bytes of one staging half
+};
+
+__global__ void __launch_bounds__(256)
+allgather_push_kernel(const uint8_t* __restrict__ shard, size_t shard_bytes, GatherParams gp) {
+  __shared__ int is_last;
+  const uint32_t epoch = gp.words[0];
+  const size_t base = size_t(epoch & 1u) * gp.half_bytes + size_t(gp.rank) * shard_bytes;
+  const size_t nvec = shard_bytes / 16;
+  const uint4* src = reinterpret_cast<const uint4*>(shard);
+  for (size_t v = size_t(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += size_t(gridDim.x) * blockDim.x) {
+    const uint4 val = src[v];
+    for (int r = 0; r < gp.world; ++r) reinterpret_cast<uint4*>(gp.bufs[r] + base)[v] = val;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    is_last = atomicAdd(&gp.words[1], 1u) == gridDim.x - 1;
+    __threadfence();
+  }
+  __syncthreads();
+  if (!is_last) return;
+  if (int(threadIdx.x) < gp.world)
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(gp.flags[threadIdx.x] + gp.rank) : "memory");
+  if (threadIdx.x == 0) { gp.words[1] = 0; gp.words[0] = epoch + 1; }
+}
+
+__global__ void __launch_bounds__(256)
+allgather_collect_kernel(uint8_t* __restrict__ out, size_t total_bytes, GatherParams gp, int* status) {
+  __shared__ int s_ok;
+  const uint32_t target = gp.words[0];  // already counts the push of this gather
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (int(threadIdx.x) < gp.world) {
+    const uint32_t* f = gp.flags[gp.rank] + threadIdx.x;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t seen, spins = 0;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+      if (int32_t(seen - target) >= 0) break;
+      if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
+        atomicCAS(status, 0, kStatusTimeoutPeer);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const uint4* src = reinterpret_cast<const uint4*>(gp.bufs[gp.rank] + size_t((target - 1u) & 1u) * gp.half_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(out);
+  for (size_t v = size_t(blockIdx.x) * blockDim.x + threadIdx.x; v < total_bytes / 16; v += size_t(gridDim.x) * blockDim.x) {
+    uint4 val;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "l"(src + v) : "memory");
+    dst[v] = val;
+  }
+}
+
+}  // namespace mfq
+
+// shard: this rank's [rows, row_bytes] block; out: [world * rows, row_bytes].  bufs[r]: rank r's staging buffer of
+// 2 * half_bytes bytes (half_bytes >= world * rows * row_bytes); flags[r]: world counters; words: 2 local counters.
+extern "C" int mfq_allgather_rows(const void* shard, void* out, long long shard_bytes, int world, int rank,
+                                  void* const* bufs, void* const* flags, void* words, long long half_bytes, int* status,
+                                  cudaStream_t stream) {
+  if (shard_bytes <= 0 || shard_bytes % 16 || world < 2 || world > 8 || shard_bytes * world > half_bytes) return -1;
+  mfq::GatherParams gp{};
+  gp.world = world;
+  gp.rank = rank;
+  for (int r = 0; r < world; ++r) {
+    gp.bufs[r] = static_cast<uint8_t*>(bufs[r]);
+    gp.flags[r] = static_cast<uint32_t*>(flags[r]);
+  }
+  gp.words = static_cast<uint32_t*>(words);
+  gp.half_bytes = size_t(half_bytes);
+  const int blocks = int(std::min<long long>(2 * 148, (shard_bytes / 16 + 255) / 256));
+  mfq::allgather_push_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(shard), size_t(shard_bytes), gp);
+  mfq::allgather_collect_kernel<<<2 * 148, 256, 0, stream>>>(static_cast<uint8_t*>(out), size_t(shard_bytes) * world, gp, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}

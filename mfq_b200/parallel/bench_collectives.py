@@ -106,8 +106,9 @@ def gemm_cases(tp: TensorParallel, dev, flush, args, emit) -> None:
             link_bytes = (w - 1) * m * n * 4  # one-shot: every rank reads every peer's partial
             name = "gemm_allreduce"
         baseline = _time(base, tp, flush, args.iters)
+        local = _time(lambda: K.fp8_gemm(xq, xs, lin.q, lin.scale), tp, flush, args.iters)
         roof = max(flops / (FP8_PEAK_TFLOPS * 1e12), link_bytes / (LINK_GBS * 1e9)) * 1e6
-        emit(dict(case=name, M=m, N=n, K=kfull, fused_us=fused, nccl_us=baseline, roofline_us=roof,
+        emit(dict(case=name, M=m, N=n, K=kfull, fused_us=fused, nccl_us=baseline, local_gemm_us=local, roofline_us=roof,
                   frac_of_roofline=roof / fused, speedup_vs_nccl=baseline / fused))
         # column-parallel over token-sharded input: all-gather -> GEMM
         if m % w == 0 and (m // w) * kfull % 16 == 0:
@@ -220,13 +221,16 @@ def main() -> None:
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     tp = TensorParallel(dist.group.WORLD, dev, max_rows=max(args.m + [8192]))
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = torch.empty(1 << 30, dtype=torch.uint8, device=dev)  # written before every timed replay: L2 flush + host slack
 
     def emit(rec):
         rec["world"] = tp.world
         if rank == 0:
             print("SWEEP " + json.dumps({k: (round(v, 3) if isinstance(v, float) else v) for k, v in rec.items()}), flush=True)
 
+    # what the method itself costs: the same flush / barrier / graph replay around a one-element kernel
+    one = torch.zeros(1, device=dev)
+    emit(dict(case="timing_floor", floor_us=_time(lambda: one.add_(1.0), tp, flush, args.iters)))
     if "gemm" not in args.skip:
         gemm_cases(tp, dev, flush, args, emit)
     if "a2a" not in args.skip:

@@ -49,6 +49,12 @@ class TensorParallel:
         """``h += all_reduce(x_q @ lin^T)`` in place; ``x_q`` holds this rank's input shard."""
         m, k = x_q.shape
         n = lin.q.shape[0]
+        if m % (self.world * 128) == 0:
+            # wide batches: two-shot (reduce-scatter in the GEMM epilogue, then all-gather of the bf16 rows) moves
+            # 2(W-1)/W of the output per rank instead of the (W-1)x of the one-shot exchange
+            rows = m // self.world
+            shard = self.gemm_reduce_scatter(lin, x_q, x_scale, h[self.rank * rows:(self.rank + 1) * rows])
+            return self.allgather_rows(shard, out=h)
         bt = K._token_tile(m)
         key = (bt, n, math.ceil(m / bt))
         ctx = self._ctx.get(key)
@@ -78,7 +84,7 @@ class TensorParallel:
             ptr(lin.q), ptr(lin.scale), ptr(x_q), ptr(x_scale), ptr(out), ptr(residual_shard), ptr(ws.splitk),
             ws.splitk.numel(), ptr(ws.counters), ws.counters.numel(), ptr(ws.status), m, n, k, token_tile, 1, self.world,
             self.rank, ctx.buf_table, ctx.flag_table, ptr(ctx.expected), ctx.half_elems, 1, stream_ptr())
-        check(rc, "fp8_gemm_reduce_scatter")
+        check(rc, "fp8_gemm_reduce_scatter", 2)
         return out
 
     def allgather_gemm(self, lin, xq_shard: torch.Tensor, xs_shard: torch.Tensor, token_tile: int = 128,
@@ -106,6 +112,32 @@ class TensorParallel:
                                           m, n, k, token_tile, self.world, self.rank, *ctx.tables, ctx.words.data_ptr(),
                                           ctx.words.data_ptr() + 4, push_ctas, stream_ptr())
         check(rc, "fp8_gemm_allgather", 2)
+        return out
+
+    def allgather_rows(self, shard: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """``[rows, width]`` per rank -> ``[W * rows, width]`` in rank order on every rank (peer-memory push)."""
+        shard = shard.contiguous()
+        nbytes = shard.numel() * shard.element_size()
+        half = self.world * nbytes
+        key = ("gather", half)
+        ctx = self._ctx.get(key)
+        if ctx is None:
+            class _GatherCtx:
+                pass
+            ctx = _GatherCtx()
+            ctx.bufs = PeerBuffer(self.group, 2 * half, self.device)
+            ctx.flags = PeerBuffer(self.group, 256, self.device)
+            ctx.words = torch.zeros(2, dtype=torch.int32, device=self.device)
+            ctx.tables = (ctx.bufs.table(), ctx.flags.table())
+            self._ctx[key] = ctx
+        if out is None:
+            out = torch.empty((self.world * shard.shape[0],) + tuple(shard.shape[1:]), dtype=shard.dtype, device=self.device)
+        fn = lib().mfq_allgather_rows
+        fn.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                       C.c_longlong, C.c_void_p, C.c_void_p]
+        ws = Workspace.get(self.device)
+        check(fn(ptr(shard), ptr(out), nbytes, self.world, self.rank, *ctx.tables, ptr(ctx.words), half, ptr(ws.status),
+                 stream_ptr()), "allgather_rows", 2)
         return out
 
     def barrier(self) -> None:

@@ -84,6 +84,12 @@ def main() -> None:
         tp.barrier()
     want = (partial[rows] + res[rows].float())
     result["rs_max_err"] = float((got.float() - want).abs().max() / want.abs().max())
+    # wide-batch row-parallel linear = reduce-scatter epilogue + all-gather of rows, repeated without barriers
+    for it in range(3):
+        h_full = res.clone()
+        tp.row_parallel_linear(lin, xq, xs, h_full)
+    want_full = partial + res.float()
+    result["ar2_max_err"] = float((h_full.float() - want_full).abs().max() / want_full.abs().max())
     w_col = Fp8Linear.from_float((torch.randn((256, 512), generator=g, device=dev) * 0.05).to(torch.bfloat16))
     xa = torch.randn((m_tok, 512), generator=g, device=dev).to(torch.bfloat16)
     xaq, xas = ref.quant_rows(xa)
