@@ -76,6 +76,10 @@ class LLMEngine:
         self.row_len: dict[int, int] = {}  # host mirror of seq_lens for page management
         self.row_stochastic: dict[int, bool] = {}
         self._next_seq_id = 0
+        # models with recurrent (linear-attention) state keep it per batch row
+        self.rec_state = model.make_state(max_batch) if hasattr(model, "make_state") else None
+        self.row_ids = torch.arange(max_batch, dtype=torch.int32, device=dev)
+        self.state_slots = torch.full((max_batch,), -1, dtype=torch.int32, device=dev)
         if self.mtp_k:
             k, w = self.mtp_k, self.mtp_k + 1
             if w * (cfg.num_heads // max(1, cfg.num_kv_heads)) > 16:
@@ -201,7 +205,11 @@ class LLMEngine:
         slots = self.cache.slots(seq_id, 0, n).to(dev)
         cu = [0, n]
         tp = self.model.tp
-        if tp > 1 and n >= tp * 128 and n % (tp * 128):
+        state_slots = None
+        if self.rec_state is not None:
+            self.rec_state.reset(row)
+            state_slots = self.row_ids[row : row + 1]
+        if tp > 1 and n >= tp * 128 and n % (tp * 128) and self.rec_state is None:
             # pad to a whole number of token tiles per rank so the row-parallel GEMMs take the reduce-scatter path;
             # the pad rows form a sequence of their own and write no KV
             pad = tp * 128 - n % (tp * 128)
@@ -209,7 +217,7 @@ class LLMEngine:
             positions = torch.cat([positions, torch.arange(pad, dtype=torch.int32, device=dev)])
             slots = torch.cat([slots, torch.full((pad,), -1, dtype=torch.int32, device=dev)])
             cu = [0, n, n + pad]
-        step = StepBuffers(input_ids=ids, positions=positions, slots=slots, cu_seqlens=cu)
+        step = StepBuffers(input_ids=ids, positions=positions, slots=slots, cu_seqlens=cu, state_slots=state_slots)
         last = torch.tensor([n - 1], dtype=torch.int32, device=dev)
         logits = self.model.forward(step, self.cache, prefill=True, logits_rows=last, gather_logits=False,
                                     return_hidden=bool(self.mtp_k))
@@ -259,8 +267,12 @@ class LLMEngine:
         dev = self.device
         self._advance(self.sampled[:b], self.input_ids[:b], self.positions[:b], self.seq_lens[:b], self.slots[:b],
                       self.cache.block_table[:b], self.active[:b])
+        state_slots = None
+        if self.rec_state is not None:
+            state_slots = self.state_slots[:b]
+            torch.where(self.active[:b] > 0, self.row_ids[:b], torch.full_like(self.row_ids[:b], -1), out=state_slots)
         step = StepBuffers(input_ids=self.input_ids[:b], positions=self.positions[:b], slots=self.slots[:b],
-                           block_table=self.cache.block_table[:b], seq_lens=self.seq_lens[:b])
+                           block_table=self.cache.block_table[:b], seq_lens=self.seq_lens[:b], state_slots=state_slots)
         if dev.type == "cuda":
             from ..ops.kernels import attn_splits_for
             self.model.attn_splits = attn_splits_for(b, self.model.hk, self.max_seq_len)
@@ -278,6 +290,7 @@ class LLMEngine:
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream())
             saved = (self.seq_lens.clone(), self.sampled.clone())
+            saved_rec = (self.rec_state.conv.clone(), self.rec_state.state.clone()) if self.rec_state is not None else None
             with torch.cuda.stream(side):
                 for _ in range(2):
                     self._decode_body(b, stochastic)
@@ -290,6 +303,9 @@ class LLMEngine:
             # warm-up and capture ran real steps: roll the sequence state back (the KV rows they wrote get rewritten)
             self.seq_lens.copy_(saved[0])
             self.sampled.copy_(saved[1])
+            if saved_rec is not None:  # the recurrent state cannot be "rewritten later" like KV rows: put it back
+                self.rec_state.conv.copy_(saved_rec[0])
+                self.rec_state.state.copy_(saved_rec[1])
             self.graphs[(b, stochastic)] = g
         g.replay()
 

@@ -1,0 +1,302 @@
+"""Hybrid decoder in the style of Qwen3-Next / Qwen3.5: Gated-DeltaNet layers interleaved with gated full attention,
+mixture-of-experts (or dense) feed-forward blocks.
+
+* linear-attention layers: ``qkv | z | b | a`` come out of ONE FP8 GEMM (the four projections share the input, so
+  their weights are stacked), causal conv + SiLU, the gated delta-rule recurrence with fused gated RMSNorm
+  (:mod:`mfq_b200.ops.gdn`), then the row-parallel output projection.  State per sequence: ``[Hv, dk, dv]`` fp32 and a
+  three-token conv history; it is addressed by the engine's batch row.
+* full-attention layers (every ``full_attention_interval``-th): per-head RMSNorm of q and k, partial rotary embedding,
+  FP8 paged KV, and an output gate ``sigmoid(gate) * attention`` whose projection is stacked behind q|k|v in the same
+  GEMM and applied inside the quantization that feeds ``o_proj``.
+* feed-forward: the routed-experts block of :class:`~mfq_b200.models.moe_decoder.MoeDecoderModel` (shared expert
+  included) or the dense SwiGLU block.
+
+Canonical tensor names follow the reference schema (``mfq/architectures/tensor_schema.py:559-593``):
+``model.block.N.linear_attention.{qkv,gate,alpha,beta,conv,output,norm}.weight``, ``...linear_attention.{a,dt_bias}``,
+``model.block.N.attention.{query_norm,key_norm}.weight``; the reference runs this family through
+``cpp_runtime/backends/cuda/models/qwen35/linear_attention.h``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..ops import gdn
+from ..ops import reference as ref
+from .llama import Fp8Linear, LlamaLayer, StepBuffers
+from .moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeLayer, MoeWeights, _to_float
+
+
+@dataclass
+class HybridConfig(MoeDecoderConfig):
+    full_attention_interval: int = 4  # layers 3, 7, 11 ... are full attention, the rest linear attention
+    linear_k_heads: int = 16
+    linear_v_heads: int = 32
+    linear_head_dim: int = 128
+    partial_rotary: float = 0.25
+    qk_norm: bool = True
+    attn_output_gate: bool = True
+    name: str = "hybrid-gdn-fp8"
+
+    def is_linear(self, layer: int) -> bool:
+        return (layer + 1) % self.full_attention_interval != 0
+
+    @property
+    def conv_dim(self) -> int:
+        return (2 * self.linear_k_heads + self.linear_v_heads) * self.linear_head_dim
+
+    @classmethod
+    def tiny(cls) -> "HybridConfig":
+        return cls(vocab_size=1024, hidden_size=256, intermediate_size=512, num_layers=4, num_heads=4, num_kv_heads=2,
+                   head_dim=128, rope_theta=1e6, rms_eps=1e-6, num_experts=8, top_k=2, moe_intermediate=128,
+                   shared_intermediate=128, full_attention_interval=2, linear_k_heads=2, linear_v_heads=4,
+                   linear_head_dim=128, name="tiny-hybrid-fp8")
+
+
+@dataclass
+class GdnWeights:
+    in_proj: Fp8Linear  # rows: q | k | v | z | b | a
+    conv_w: torch.Tensor  # [C, 4] fp32
+    A_log: torch.Tensor  # [Hv] fp32
+    dt_bias: torch.Tensor  # [Hv] fp32
+    norm_w: torch.Tensor  # [dv] fp32
+    out_proj: Fp8Linear  # [H, Hv*dv]
+    k_heads: int
+    v_heads: int
+
+
+@dataclass
+class HybridLayer(MoeLayer):
+    gdn: GdnWeights | None = None
+    q_norm: torch.Tensor | None = None  # [D] fp32
+    k_norm: torch.Tensor | None = None
+    gated: bool = False  # qkv rows are followed by the output-gate projection
+
+
+class GdnState:
+    """Recurrent state of the linear-attention layers for ``slots`` sequences (slot = engine batch row)."""
+
+    def __init__(self, cfg: HybridConfig, slots: int, device, tp: int = 1) -> None:
+        hv, d = cfg.linear_v_heads // tp, cfg.linear_head_dim
+        c = cfg.conv_dim // tp
+        n = sum(cfg.is_linear(i) for i in range(cfg.num_layers))
+        self.index = {i: j for j, i in enumerate(i for i in range(cfg.num_layers) if cfg.is_linear(i))}
+        self.conv = torch.zeros((n, slots, 3, c), dtype=torch.float32, device=device)
+        self.state = torch.zeros((n, slots, hv, d, d), dtype=torch.float32, device=device)
+
+    def reset(self, slot: int) -> None:
+        self.conv[:, slot].zero_()
+        self.state[:, slot].zero_()
+
+    def layer(self, i: int):
+        j = self.index[i]
+        return self.conv[j], self.state[j]
+
+
+class HybridWeights(MoeWeights):
+    @classmethod
+    def from_tensors(cls, cfg: HybridConfig, tensors, device, tp_rank: int = 0, tp_size: int = 1) -> "HybridWeights":
+        """Rank-local FP8 weights from canonical checkpoint tensors.  Linear-attention heads, like attention heads,
+        are split over the ranks; their stacked input projection keeps the q | k | v | z | b | a row order per rank."""
+        dev = torch.device(device)
+        w = tp_size
+        base = super().from_tensors(cfg, _with_placeholders(cfg, tensors), dev, tp_rank, tp_size)
+        d = cfg.linear_head_dim
+        hk, hv = cfg.linear_k_heads, cfg.linear_v_heads
+
+        def get(name):
+            return _to_float(tensors[name], dev)
+
+        def rows(x, parts):
+            return x.reshape(w, parts // w, *x.shape[1:])[tp_rank] if w > 1 else x
+
+        layers = []
+        for i, layer in enumerate(base.layers):
+            p = f"model.block.{i}."
+            hl = HybridLayer(**{k: getattr(layer, k) for k in layer.__dataclass_fields__})
+            if cfg.is_linear(i):
+                q = p + "linear_attention."
+                qkv = get(q + "qkv.weight")  # [2*hk*d + hv*d, H] in q | k | v order
+                wq, wk, wv = qkv[: hk * d], qkv[hk * d : 2 * hk * d], qkv[2 * hk * d :]
+                stacked = torch.cat([rows(wq, hk * d), rows(wk, hk * d), rows(wv, hv * d), rows(get(q + "gate.weight"), hv * d),
+                                     rows(get(q + "beta.weight"), hv), rows(get(q + "alpha.weight"), hv)], 0)
+                conv = get(q + "conv.weight").reshape(-1, 4)  # [C, 4] (a [C, 1, 4] depthwise kernel flattens to this)
+                conv = torch.cat([rows(conv[: hk * d], hk * d), rows(conv[hk * d : 2 * hk * d], hk * d), rows(conv[2 * hk * d :], hv * d)], 0)
+                out_w = get(q + "output.weight")
+                if w > 1:
+                    out_w = out_w.reshape(out_w.shape[0], w, hv * d // w)[:, tp_rank].contiguous()
+                hl.gdn = GdnWeights(Fp8Linear.from_float(stacked), conv.contiguous(), rows(get(q + "a"), hv).contiguous(),
+                                    rows(get(q + "dt_bias"), hv).contiguous(), get(q + "norm.weight").contiguous(),
+                                    Fp8Linear.from_float(out_w), hk // w, hv // w)
+                hl.qkv = hl.o_proj = None
+            else:
+                a = p + "attention."
+                if cfg.qk_norm:
+                    hl.q_norm, hl.k_norm = get(a + "query_norm.weight").contiguous(), get(a + "key_norm.weight").contiguous()
+                if cfg.attn_output_gate:
+                    gate = rows(get(a + "gate.weight"), cfg.num_heads * cfg.head_dim)
+                    hl.qkv = Fp8Linear.from_float(torch.cat([hl.qkv.dequant().to(dev), gate], 0))
+                    hl.gated = True
+            layers.append(hl)
+        return cls(base.embed, layers, base.final_norm, base.lm_head, tp_rank, tp_size)
+
+
+def _with_placeholders(cfg: HybridConfig, tensors):
+    """The MoE loader reads q/k/v/o of every layer; linear-attention layers have none, so they get zero stand-ins
+    (dropped again right after)."""
+    class _View(dict):
+        def __missing__(self, name):
+            return tensors[name]
+
+        def __contains__(self, name):
+            return dict.__contains__(self, name) or name in tensors
+
+    view = _View()
+    import numpy as np
+    h, d = cfg.hidden_size, cfg.head_dim
+    for i in range(cfg.num_layers):
+        if cfg.is_linear(i):
+            p = f"model.block.{i}.attention."
+            view[p + "query.weight"] = np.zeros((cfg.num_heads * d, h), dtype=np.float32)
+            view[p + "key.weight"] = np.zeros((cfg.num_kv_heads * d, h), dtype=np.float32)
+            view[p + "value.weight"] = np.zeros((cfg.num_kv_heads * d, h), dtype=np.float32)
+            view[p + "output.weight"] = np.zeros((h, cfg.num_heads * d), dtype=np.float32)
+    return view
+
+
+def init_hybrid_weights(cfg: HybridConfig, seed: int = 0, std: float = 0.02) -> dict[str, torch.Tensor]:
+    """Random bf16-representable weights of a hybrid model under canonical names (tests, synthetic benchmarks)."""
+    from .moe_lm import MoeConfig, init_weights
+    w = init_weights(MoeConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, num_layers=cfg.num_layers,
+                               num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
+                               num_experts=cfg.num_experts, top_k=cfg.top_k, moe_intermediate=cfg.moe_intermediate,
+                               shared_intermediate=cfg.shared_intermediate), seed=seed, std=std)
+    g = torch.Generator().manual_seed(seed + 1)
+
+    def rnd(*shape, scale=std):
+        return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).float()
+
+    h, d, hk, hv = cfg.hidden_size, cfg.linear_head_dim, cfg.linear_k_heads, cfg.linear_v_heads
+    for i in range(cfg.num_layers):
+        p = f"model.block.{i}."
+        if cfg.is_linear(i):
+            for name in ("query", "key", "value", "output"):
+                del w[p + f"attention.{name}.weight"]
+            q = p + "linear_attention."
+            w[q + "qkv.weight"] = rnd(cfg.conv_dim, h)
+            w[q + "gate.weight"] = rnd(hv * d, h)
+            w[q + "alpha.weight"] = rnd(hv, h)
+            w[q + "beta.weight"] = rnd(hv, h)
+            w[q + "conv.weight"] = rnd(cfg.conv_dim, 1, 4, scale=0.5)
+            w[q + "a"] = rnd(hv, scale=0.5)
+            w[q + "dt_bias"] = rnd(hv, scale=0.5)
+            w[q + "norm.weight"] = 1 + rnd(d, scale=0.1)
+            w[q + "output.weight"] = rnd(h, hv * d)
+        else:
+            a = p + "attention."
+            if cfg.qk_norm:
+                w[a + "query_norm.weight"] = 1 + rnd(cfg.head_dim, scale=0.1)
+                w[a + "key_norm.weight"] = 1 + rnd(cfg.head_dim, scale=0.1)
+            if cfg.attn_output_gate:
+                w[a + "gate.weight"] = rnd(cfg.num_heads * cfg.head_dim, h)
+    return w
+
+
+class HybridModel(MoeDecoderModel):
+    """:class:`MoeDecoderModel` whose token mixer is, per layer, Gated DeltaNet or gated full attention."""
+
+    def __init__(self, cfg: HybridConfig, weights, collective=None) -> None:
+        super().__init__(cfg, weights, collective)
+        self.state: GdnState | None = None
+        self.rot = max(2, int(cfg.head_dim * cfg.partial_rotary) // 2 * 2)
+
+    def make_state(self, slots: int) -> GdnState:
+        self.state = GdnState(self.cfg, slots, self.w.embed.device, self.tp)
+        return self.state
+
+    # -- linear attention ---------------------------------------------------------------------------------------------
+    def _gdn_mixer(self, h, layer: HybridLayer, li: int, step: StepBuffers):
+        cfg, g = self.cfg, layer.gdn
+        d = cfg.linear_head_dim
+        xq, xs = self._norm_quant(h, layer.attn_norm)
+        proj = g.in_proj(xq, xs)  # [T, C + Hv*d + 2*Hv]
+        c = (2 * g.k_heads + g.v_heads) * d
+        zw = g.v_heads * d
+        mixed, z = proj[:, :c], proj[:, c : c + zw]
+        b, a = proj[:, c + zw : c + zw + g.v_heads], proj[:, c + zw + g.v_heads : c + zw + 2 * g.v_heads]
+        conv_state, state = self.state.layer(li)
+        slots = step.state_slots
+        L = step.q_len if step.block_table is not None else h.shape[0]
+        if not h.is_cuda:
+            mixed, z, a, b = (t.contiguous() for t in (mixed, z, a, b))
+        qkv = gdn.conv(mixed, conv_state, g.conv_w, slots, L)
+        y = gdn.recurrent(qkv, z, a, b, g.A_log, g.dt_bias, g.norm_w, state, slots, L, g.k_heads, g.v_heads, cfg.rms_eps)
+        yq, ys = self._quant(y)
+        return self._row_parallel(g.out_proj, yq, ys, h)
+
+    # -- gated attention ----------------------------------------------------------------------------------------------
+    def _gated_attention(self, h, layer: HybridLayer, kv, step: StepBuffers, prefill: bool):
+        cfg = self.cfg
+        d, t = cfg.head_dim, h.shape[0]
+        xq, xs = self._norm_quant(h, layer.attn_norm)
+        qkv = layer.qkv(xq, xs)  # [T, (Hq + 2Hk) * D (+ Hq * D gate)]
+        width = (self.hq + 2 * self.hk) * d
+        gate = qkv[:, width:] if layer.gated else None
+        if qkv.is_cuda:
+            kd = vd = None
+            if prefill:
+                kd = torch.empty((t, self.hk, d), dtype=torch.bfloat16, device=qkv.device)
+                vd = torch.empty_like(kd)
+            q = ops.rope_kv_write(qkv, step.positions, step.slots, kv, n_q=self.hq, n_kv=self.hk, head_dim=d, theta=cfg.rope_theta,
+                                  rot=self.rot, kd_out=kd, vd_out=vd, q_norm=layer.q_norm, k_norm=layer.k_norm,
+                                  norm_eps=cfg.rms_eps)
+            if prefill:
+                o = ops.attn_prefill(q, kd, vd, step.cu_seqlens, self.sm_scale)
+            else:
+                o = ops.paged_attn_decode(q, kv, step.block_table, step.seq_lens, sm_scale=self.sm_scale,
+                                          splits=self.attn_splits, q_len=step.q_len)
+            o = o.reshape(t, self.hq * d)
+            aq, a_s = ops.kernels.gate_quant_rows(o, gate) if gate is not None else self._quant(o)
+        else:
+            q3 = qkv[:, :width].reshape(t, self.hq + 2 * self.hk, d)
+
+            def headnorm(x, w):
+                if w is None:
+                    return x
+                xf = x.float()
+                return (xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + cfg.rms_eps) * w).to(torch.bfloat16)
+            q = ref.rope(headnorm(q3[:, : self.hq], layer.q_norm), step.positions, cfg.rope_theta, self.rot)
+            k = ref.rope(headnorm(q3[:, self.hq : self.hq + self.hk], layer.k_norm), step.positions, cfg.rope_theta, self.rot)
+            ref.write_kv(kv, k, q3[:, self.hq + self.hk :], step.slots)
+            if prefill:
+                outs = []
+                for i in range(len(step.cu_seqlens) - 1):
+                    lo, hi = step.cu_seqlens[i], step.cu_seqlens[i + 1]
+                    kk, vv = ref.gather_slots(kv, step.slots[lo:hi])
+                    outs.append(ref.attention(q[lo:hi], kk, vv, self.sm_scale, causal_offset=0))
+                o = torch.cat(outs, 0)
+            else:
+                o = ref.paged_attn_decode(q, kv, step.block_table, step.seq_lens, self.sm_scale, step.q_len)
+            o = o.reshape(t, self.hq * d)
+            if gate is not None:
+                o = (o.float() * torch.sigmoid(gate.float())).to(torch.bfloat16)
+            aq, a_s = self._quant(o)
+        return self._row_parallel(layer.o_proj, aq, a_s, h)
+
+    def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
+        li = self._layer_index[id(layer)]
+        if layer.gdn is not None:
+            h = self._gdn_mixer(h, layer, li, step)
+        else:
+            h = self._gated_attention(h, layer, kv, step, prefill)
+        return self._ffn(h, layer)
+
+    def forward(self, step: StepBuffers, cache, **kw):
+        if self.state is None:
+            raise RuntimeError("call make_state(slots) before the first forward")
+        if not hasattr(self, "_layer_index"):
+            self._layer_index = {id(l): i for i, l in enumerate(self.w.layers)}
+        return super().forward(step, cache, **kw)

@@ -178,6 +178,8 @@ class StepBuffers:
     # prefill: cumulative sequence boundaries (host list) of the packed chunk
     cu_seqlens: list[int] = field(default_factory=list)
     q_len: int = 1
+    # models with recurrent state (linear attention): state slot of every row ([B] int32, -1 = leave the row alone)
+    state_slots: torch.Tensor | None = None
 
 
 class LlamaModel:

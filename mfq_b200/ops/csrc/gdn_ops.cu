@@ -25,7 +25,7 @@ namespace mfq {
 // conv_ckpt (optional) [B, L, 3, C]: history after each token, for verify windows (then conv_state is left alone).
 __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ conv_state,
                                 const float* __restrict__ w, const int* __restrict__ slot, float* __restrict__ out,
-                                float* __restrict__ conv_ckpt, int L, int C) {
+                                float* __restrict__ conv_ckpt, int L, int C, int xs) {
   const int b = blockIdx.y;
   const int s = slot[b];
   if (s < 0) return;
@@ -35,7 +35,7 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, float* __re
   float* st = conv_state + size_t(s) * 3 * C;
   const float h0 = st[c], h1 = st[C + c], h2 = st[2 * C + c];
   auto in = [&](int t) -> float {  // input of token t of this row; negative t reads the carried history
-    if (t >= 0) return __bfloat162float(x[(size_t(b) * L + t) * C + c]);
+    if (t >= 0) return __bfloat162float(x[(size_t(b) * L + t) * xs + c]);
     return t == -1 ? h2 : t == -2 ? h1 : h0;
   };
   for (int t = blockIdx.z; t < L; t += gridDim.z) {
@@ -51,7 +51,7 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, float* __re
 // History update, as a launch of its own AFTER the convolution: blocks of the convolution that handle the first
 // tokens still read the old history, so it cannot be overwritten by a sibling block of the same grid.
 __global__ void gdn_conv_state_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ conv_state,
-                                      const int* __restrict__ slot, int L, int C) {
+                                      const int* __restrict__ slot, int L, int C, int xs) {
   const int b = blockIdx.y;
   const int s = slot[b];
   if (s < 0) return;
@@ -60,7 +60,7 @@ __global__ void gdn_conv_state_kernel(const __nv_bfloat16* __restrict__ x, float
   float* st = conv_state + size_t(s) * 3 * C;
   const float h0 = st[c], h1 = st[C + c], h2 = st[2 * C + c];
   auto in = [&](int t) -> float {
-    if (t >= 0) return __bfloat162float(x[(size_t(b) * L + t) * C + c]);
+    if (t >= 0) return __bfloat162float(x[(size_t(b) * L + t) * xs + c]);
     return t == -1 ? h2 : t == -2 ? h1 : h0;
   };
   const float n0 = in(L - 3), n1 = in(L - 2), n2 = in(L - 1);
@@ -81,6 +81,7 @@ struct GdnParams {
   __nv_bfloat16* y;         // [B*L, Hv*dv]
   int L, Hk, Hv;
   float eps;
+  int z_stride, ab_stride;  // elements between token rows of z and of a / b (they may be column slices of one GEMM output)
 };
 
 template <int DK, int DV>
@@ -115,10 +116,10 @@ __global__ void __launch_bounds__(DV) gdn_recurrent_kernel(const GdnParams p) {
       float* dst = warp == 0 ? q_s : k_s;
       dst[lane * 4] = v4.x * inv; dst[lane * 4 + 1] = v4.y * inv; dst[lane * 4 + 2] = v4.z * inv; dst[lane * 4 + 3] = v4.w * inv;
     } else if (warp == 2 && lane == 0) {
-      const float av = __bfloat162float(p.a[tok * p.Hv + h]) + dtb;
+      const float av = __bfloat162float(p.a[tok * p.ab_stride + h]) + dtb;
       const float sp = av > 20.f ? av : log1pf(__expf(av));
       gate_s[0] = __expf(neg_a * sp);
-      gate_s[1] = 1.f / (1.f + __expf(-__bfloat162float(p.bb[tok * p.Hv + h])));
+      gate_s[1] = 1.f / (1.f + __expf(-__bfloat162float(p.bb[tok * p.ab_stride + h])));
     }
     __syncthreads();
     const float decay = gate_s[0], beta = gate_s[1];
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(DV) gdn_recurrent_kernel(const GdnParams p) {
     float tot = 0.f;
 #pragma unroll
     for (int i = 0; i < DV / 32; ++i) tot += red[i];
-    const float zg = __bfloat162float(p.z[tok * p.Hv * DV + h * DV + col]);
+    const float zg = __bfloat162float(p.z[tok * p.z_stride + h * DV + col]);
     const float yv = o * rsqrtf(tot / float(DV) + p.eps) * nw * (zg / (1.f + __expf(-zg)));
     p.y[tok * p.Hv * DV + h * DV + col] = __float2bfloat16(yv);
     if (p.ckpt) {
@@ -182,22 +183,23 @@ __global__ void gdn_select_kernel(const float* __restrict__ ckpt, const float* _
 using namespace mfq;
 
 extern "C" int mfq_gdn_conv(const void* x, float* conv_state, const float* w, const int* slot, float* out, float* conv_ckpt,
-                            int B, int L, int C, cudaStream_t stream) {
-  if (B <= 0 || L <= 0 || C <= 0) return -1;
+                            int B, int L, int C, int x_stride, cudaStream_t stream) {
+  if (B <= 0 || L <= 0 || C <= 0 || x_stride < C) return -1;
   dim3 grid((C + 255) / 256, B, min(L, 64));
-  gdn_conv_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), conv_state, w, slot, out, conv_ckpt, L, C);
+  gdn_conv_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), conv_state, w, slot, out, conv_ckpt, L, C, x_stride);
   if (!conv_ckpt)
-    gdn_conv_state_kernel<<<dim3((C + 255) / 256, B), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), conv_state, slot, L, C);
+    gdn_conv_state_kernel<<<dim3((C + 255) / 256, B), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), conv_state, slot, L, C, x_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
 extern "C" int mfq_gdn_recurrent(const float* qkv, const void* z, const void* a, const void* b, const float* A_log,
                                  const float* dt_bias, const float* norm_w, float* state, float* ckpt, const int* slot,
-                                 void* y, int B, int L, int Hk, int Hv, int dk, int dv, float eps, cudaStream_t stream) {
+                                 void* y, int B, int L, int Hk, int Hv, int dk, int dv, float eps, int z_stride, int ab_stride,
+                                 cudaStream_t stream) {
   if (B <= 0 || L <= 0 || dk != 128 || dv != 128 || Hk <= 0 || Hv % Hk) return -1;
   GdnParams p{qkv, static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(a),
               static_cast<const __nv_bfloat16*>(b), A_log, dt_bias, norm_w, state, ckpt, slot,
-              static_cast<__nv_bfloat16*>(y), L, Hk, Hv, eps};
+              static_cast<__nv_bfloat16*>(y), L, Hk, Hv, eps, z_stride, ab_stride};
   gdn_recurrent_kernel<128, 128><<<B * Hv, 128, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }

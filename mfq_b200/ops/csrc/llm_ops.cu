@@ -131,15 +131,18 @@ __global__ void rmsnorm_quant_kernel(const __nv_bfloat16* __restrict__ x, const 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Row quantization.  mode 0: y = x[row, :K]; mode 1 (SwiGLU): y = silu(x[row, :K]) * x[row, K:2K].
+// Row quantization.  mode 0: y = x[row, :K]; mode 1 (SwiGLU): y = silu(x[row, :K]) * x[row, K:2K];
+// mode 2 (attention output gate): y = x[row, :K] * sigmoid(x2[row, :K]) with x2 a second, separately strided tensor.
 // Two passes over the (cache-resident) row: amax, then encode.
 // ---------------------------------------------------------------------------------------------
 template <int kMode>
 __global__ void quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q_out,
-                                  float* __restrict__ scale_out, int K, int in_stride) {
+                                  float* __restrict__ scale_out, int K, int in_stride,
+                                  const __nv_bfloat16* __restrict__ x2 = nullptr, int x2_stride = 0) {
   __shared__ float red[33];
   const size_t row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * in_stride;
+  const __nv_bfloat16* gr = kMode == 2 ? x2 + row * x2_stride : nullptr;
   const int nvec = K / 8;
   auto value = [&](int vi, float (&y)[8]) {
     uint4 a = *reinterpret_cast<const uint4*>(xr + vi * 8);
@@ -147,6 +150,14 @@ __global__ void quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* 
     if (kMode == 0) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) y[j] = __bfloat162float(ab[j]);
+    } else if (kMode == 2) {
+      uint4 b = *reinterpret_cast<const uint4*>(gr + vi * 8);
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float h = __bfloat162float(ab[j]) / (1.f + __expf(-__bfloat162float(bb[j])));
+        y[j] = __bfloat162float(__float2bfloat16(h));
+      }
     } else {
       uint4 b = *reinterpret_cast<const uint4*>(xr + K + vi * 8);
       const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
@@ -191,7 +202,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
                                      uint8_t* __restrict__ k_cache, uint8_t* __restrict__ v_cache,
                                      float* __restrict__ k_scale, float* __restrict__ v_scale, int T, int Hq, int Hk,
                                      int page_size, int rot, float log2_theta, __nv_bfloat16* __restrict__ kd_out,
-                                     __nv_bfloat16* __restrict__ vd_out) {
+                                     __nv_bfloat16* __restrict__ vd_out, const float* __restrict__ q_norm_w,
+                                     const float* __restrict__ k_norm_w, float norm_eps, int row_stride) {
   constexpr int EPL = D / 32;  // elements per lane
   const int warps_per_block = blockDim.x >> 5;
   const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -199,7 +211,7 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
   const int heads = Hq + 2 * Hk;
   if (gw >= T * heads) return;
   const int t = gw / heads, h = gw % heads;
-  const __nv_bfloat16* src = qkv + size_t(t) * heads * D + size_t(h) * D;
+  const __nv_bfloat16* src = qkv + size_t(t) * row_stride + size_t(h) * D;  // rows may carry extra trailing columns
   // lane owns EPL/2 rotation pairs: indices j and j + rot/2 for j = lane*EPL/2 .. (only when below rot/2),
   // plus pass-through of non-rotated dims; simplest uniform scheme: lane handles dims
   // [lane*EPL/2, lane*EPL/2 + EPL/2) of each half of the head vector.
@@ -211,6 +223,22 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
     hi[j] = __bfloat162float(src[D / 2 + lane * HP + j]);
   }
   const bool is_v = h >= Hq + Hk;
+  // optional per-head RMSNorm of q and k before the rotation (QK-norm); nw_scale folds 1/rms into the partner reads
+  const float* nw = is_v ? nullptr : (h < Hq ? q_norm_w : k_norm_w);
+  float inv_rms = 1.f;
+  if (nw) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < HP; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    inv_rms = rsqrtf(ss / float(D) + norm_eps);
+#pragma unroll
+    for (int j = 0; j < HP; ++j) {
+      lo[j] *= inv_rms * nw[lane * HP + j];
+      hi[j] *= inv_rms * nw[D / 2 + lane * HP + j];
+    }
+  }
   if (!is_v) {
     const float pos = float(positions[t]);
     const int half_rot = rot / 2;
@@ -238,7 +266,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
             float s, c;
             sincosf(pos * inv_freq, &s, &c);
             const float self = part ? hi[j] : lo[j];
-            const float other = __bfloat162float(src[idx < half_rot ? idx + half_rot : idx - half_rot]);
+            const int pidx = idx < half_rot ? idx + half_rot : idx - half_rot;
+            const float other = __bfloat162float(src[pidx]) * (nw ? inv_rms * nw[pidx] : 1.f);
             const float r = idx < half_rot ? self * c - other * s : self * c + other * s;
             if (part) hi[j] = r; else lo[j] = r;
           }
@@ -393,11 +422,24 @@ extern "C" int mfq_quant_rows(const void* x, void* q_out, float* scale_out, int 
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
-extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const int* slots, void* q_out, void* k_cache,
-                                 void* v_cache, float* k_scale, float* v_scale, int T, int Hq, int Hk, int D,
-                                 int page_size, int rot, float theta, void* kd_out, void* vd_out,
-                                 cudaStream_t stream) {
-  if (T <= 0) return -1;
+// fp8 rows of x * sigmoid(gate): the output gate of gated attention, fused with the quantization that feeds o_proj.
+extern "C" int mfq_gate_quant_rows(const void* x, const void* gate, void* q_out, float* scale_out, int M, int K,
+                                   int in_stride, int gate_stride, cudaStream_t stream) {
+  if (K % 8 || in_stride % 8 || gate_stride % 8 || M <= 0) return -1;
+  quant_rows_kernel<2><<<M, K >= 4096 ? 512 : 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out),
+                                                                scale_out, K, in_stride, static_cast<const __nv_bfloat16*>(gate),
+                                                                gate_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+// q_norm_w / k_norm_w ([D] fp32, may be null): per-head RMSNorm of q / k before the rotation; row_stride: elements
+// between token rows of qkv (>= (Hq + 2 Hk) * D; an attention output gate may follow the v heads).
+extern "C" int mfq_rope_kv_write_ex(const void* qkv, const int* positions, const int* slots, void* q_out, void* k_cache,
+                                    void* v_cache, float* k_scale, float* v_scale, int T, int Hq, int Hk, int D,
+                                    int page_size, int rot, float theta, void* kd_out, void* vd_out,
+                                    const float* q_norm_w, const float* k_norm_w, float norm_eps, int row_stride,
+                                    cudaStream_t stream) {
+  if (T <= 0 || row_stride < (Hq + 2 * Hk) * D) return -1;
   const int warps = T * (Hq + 2 * Hk);
   const int blocks = (warps + 7) / 8;
   const float l2t = log2f(theta);
@@ -405,13 +447,21 @@ extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const in
   rope_kv_write_kernel<DD><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, slots, \
       static_cast<__nv_bfloat16*>(q_out), static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache),      \
       k_scale, v_scale, T, Hq, Hk, page_size, rot, l2t, static_cast<__nv_bfloat16*>(kd_out),                   \
-      static_cast<__nv_bfloat16*>(vd_out))
+      static_cast<__nv_bfloat16*>(vd_out), q_norm_w, k_norm_w, norm_eps, row_stride)
   if (D == 128) MFQ_ROPE(128);
   else if (D == 64) MFQ_ROPE(64);
   else if (D == 256) MFQ_ROPE(256);
   else return -1;
 #undef MFQ_ROPE
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const int* slots, void* q_out, void* k_cache,
+                                 void* v_cache, float* k_scale, float* v_scale, int T, int Hq, int Hk, int D,
+                                 int page_size, int rot, float theta, void* kd_out, void* vd_out,
+                                 cudaStream_t stream) {
+  return mfq_rope_kv_write_ex(qkv, positions, slots, q_out, k_cache, v_cache, k_scale, v_scale, T, Hq, Hk, D, page_size, rot,
+                              theta, kd_out, vd_out, nullptr, nullptr, 0.f, (Hq + 2 * Hk) * D, stream);
 }
 
 extern "C" int mfq_argmax(const void* logits, int* out, int B, int V, int stride, cudaStream_t stream) {

@@ -24,8 +24,8 @@ def _lib():
     global _bound
     L = lib()
     if not _bound:
-        L.mfq_gdn_conv.argtypes = [_vp] * 6 + [_i] * 3 + [_vp]
-        L.mfq_gdn_recurrent.argtypes = [_vp] * 11 + [_i] * 6 + [_f, _vp]
+        L.mfq_gdn_conv.argtypes = [_vp] * 6 + [_i] * 4 + [_vp]
+        L.mfq_gdn_recurrent.argtypes = [_vp] * 11 + [_i] * 6 + [_f, _i, _i, _vp]
         L.mfq_gdn_select.argtypes = [_vp] * 6 + [_i] * 6 + [_vp]
         _bound = True
     return L
@@ -39,7 +39,8 @@ def conv(x: torch.Tensor, conv_state: torch.Tensor, w: torch.Tensor, slot: torch
     b = n // L
     out = torch.empty((n, c), dtype=torch.float32, device=x.device)
     if x.is_cuda:
-        check(_lib().mfq_gdn_conv(ptr(x), ptr(conv_state), ptr(w), ptr(slot), ptr(out), ptr(conv_ckpt), b, L, c, stream_ptr()),
+        check(_lib().mfq_gdn_conv(ptr(x), ptr(conv_state), ptr(w), ptr(slot), ptr(out), ptr(conv_ckpt), b, L, c, x.stride(0),
+                                  stream_ptr()),
               "gdn_conv", 1 if conv_ckpt is not None else 2)
         return out
     xs = x.float().view(b, L, c)
@@ -69,7 +70,8 @@ def recurrent(qkv: torch.Tensor, z: torch.Tensor, a: torch.Tensor, b: torch.Tens
     y = torch.empty((n, Hv * dv), dtype=torch.bfloat16, device=qkv.device)
     if qkv.is_cuda:
         check(_lib().mfq_gdn_recurrent(ptr(qkv), ptr(z), ptr(a), ptr(b), ptr(A_log), ptr(dt_bias), ptr(norm_w), ptr(state),
-                                       ptr(ckpt), ptr(slot), ptr(y), rows, L, Hk, Hv, dk, dv, float(eps), stream_ptr()),
+                                       ptr(ckpt), ptr(slot), ptr(y), rows, L, Hk, Hv, dk, dv, float(eps), z.stride(0), a.stride(0),
+                                       stream_ptr()),
               "gdn_recurrent")
         return y
     rep = Hv // Hk
