@@ -58,9 +58,13 @@ def read_hf_directory(path) -> tuple[dict, dict[str, np.ndarray], dict[str, byte
 
 
 def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", expert_mix: str = "", seed: int = 20260908,
-                     device: str = "cpu", progress=None) -> dict[str, object]:
+                     device: str = "cpu", progress=None, widths: dict[str, int | None] | None = None,
+                     imatrix: dict[str, np.ndarray] | None = None, scheme: dict | None = None) -> dict[str, object]:
     """Apply the quantization plan: routed experts by the seeded mix (or the dense rule), 2-D weights by ``dense``
-    (nint2..8 / nvq3 / mxfp4 / fp8 / bf16), norms / router / embeddings-as-requested stay bf16."""
+    (nint2..8 / nvq3 / mxfp4 / fp8 / bf16), norms / router / embeddings-as-requested stay bf16.
+    ``widths`` (a preset plan: tensor -> NINT width, None = keep) overrides ``dense`` per tensor; ``imatrix`` supplies
+    per-input-channel importance to the NINT search; ``scheme`` (``mfq.calibration-scheme.v3``, expert-wise) fixes the
+    family of every routed expert projection."""
     from .quantize import balanced_expert_mix, parse_profiles, quantize_expertwise, quantize_matrix
     profiles = parse_profiles(expert_mix) if expert_mix else ()
     dense_profile = None if dense == "bf16" else parse_profiles({"fp8": "FP8", "mxfp4": "MXFP4", "nvq3": "NVQ3"}.get(dense, dense.upper()))[0]
@@ -70,17 +74,33 @@ def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", ex
             progress(name)
         a = np.asarray(t, dtype=np.float32)
         keep = a.ndim < 2 or "norm" in name or "router" in name or name.endswith(".bias")
+        profile = dense_profile
+        if widths is not None and name in widths:
+            profile = None if widths[name] is None else parse_profiles(f"NINT{widths[name]}")[0]
         if ".mlp.experts." in name and a.ndim == 3:
-            use = profiles or ((dense_profile,) if dense_profile else ())
+            fixed = [x for x in (scheme or {}).get("assignments", []) if x["tensor"] == name]
+            if fixed:
+                families = sorted({x["family"] for x in fixed})
+                use = parse_profiles(",".join(families))
+                assign = np.zeros(a.shape[0], dtype=np.int64)
+                for x in fixed:
+                    assign[int(x["expert_id"])] = families.index(x["family"])
+                out[name] = quantize_expertwise(a, assign, tuple(use), device=device)
+                continue
+            use = profiles or ((profile,) if profile else ())
             if not use:
                 out[name] = F.to_bf16(a)
                 continue
             assign = balanced_expert_mix(name, a.shape[0], len(use), seed)
             out[name] = quantize_expertwise(a, assign, tuple(use), device=device)
-        elif keep or dense_profile is None or (dense_profile.family in ("FP8", "MXFP4") and a.shape[-1] % 128):
+        elif keep or profile is None or (profile.family in ("FP8", "MXFP4") and a.shape[-1] % 128):
             out[name] = F.to_bf16(a)
         else:
-            out[name] = quantize_matrix(a, dense_profile, device=device)
+            imp = None
+            if imatrix is not None and profile.nint is not None:
+                from .calibration.imatrix import input_importance
+                imp = input_importance(imatrix, name)
+            out[name] = quantize_matrix(a, profile, device=device, importance=imp) if imp is not None else quantize_matrix(a, profile, device=device)
     return out
 
 

@@ -11,6 +11,8 @@ from __future__ import annotations
 
 import argparse
 import json
+
+import numpy as np
 import os
 import sys
 from pathlib import Path
@@ -65,10 +67,26 @@ def _cmd_quantize(args) -> int:
         raise SystemExit(f"{out} exists (use --overwrite)")
     cfg, tensors, assets = _load_source(args)
     dense = "bf16" if args.full_precision else (args.format or f"nint{args.bits}")
+    widths = None
     if args.preset:
-        dense = {"S2": "nint2", "S3": "nint3", "S4": "nint4", "S5": "nint5", "S6": "nint6", "S8": "nint8"}[args.preset.split("-")[0].upper()]
-    plan = {n: (list(t.shape), "MFE" if (".mlp.experts." in n and t.ndim == 3 and (args.random_expert_mix or dense != "bf16")) else dense)
-            for n, t in tensors.items()}
+        from .quantize import presets
+        preset = presets.normalize_preset(args.preset)
+        dense = f"nint{presets.PRESETS[preset]}"
+        topo = presets.Topology(int(cfg.get("num_layers", 0)), int(cfg.get("num_heads", 1)), int(cfg.get("num_kv_heads", 1)))
+        widths = presets.plan(preset, {n: tuple(t.shape) for n, t in tensors.items()}, topo)
+    imatrix = scheme = None
+    if args.imatrix:
+        from .calibration.imatrix import load as load_imatrix
+        imatrix = load_imatrix(args.imatrix)
+    if args.ew_scheme:
+        scheme = json.loads(Path(args.ew_scheme).read_text())
+    def _label(n, t):
+        if ".mlp.experts." in n and t.ndim == 3 and (args.random_expert_mix or scheme or dense != "bf16"):
+            return "MFE"
+        if widths is not None and n in widths:
+            return "bf16" if widths[n] is None else f"nint{widths[n]}"
+        return dense
+    plan = {n: (list(t.shape), _label(n, t)) for n, t in tensors.items()}
     if args.dry_run:
         print(json.dumps({"tensors": len(plan), "dense": dense, "expert_mix": args.random_expert_mix, "plan": plan}, indent=1))
         return 0
@@ -78,13 +96,61 @@ def _cmd_quantize(args) -> int:
         gs, k = expertwise._NINT_PRESETS[bits]
         expertwise._NINT_PRESETS[bits] = (args.groupsize or gs, args.sub_bits or k)
     q = quantize_tensors(tensors, dense=dense, expert_mix=args.random_expert_mix, seed=args.random_expert_mix_seed,
-                         device=args.device, progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
-    extra = {"quantization": {"dense": dense, "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
+                         widths=widths, imatrix=imatrix, scheme=scheme, device=args.device, progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
+    extra = {"quantization": {"dense": dense, "preset": args.preset or None, "imatrix": bool(imatrix), "ew_scheme": bool(scheme), "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
                               "random_expert_mix_seed": args.random_expert_mix_seed if args.random_expert_mix else None}}
     save_checkpoint(out, cfg, q, assets, extra=extra)
     size = out.stat().st_size
     weights = sum(int(t.size) for t in tensors.values())
     print(json.dumps({"output": str(out), "bytes": size, "weights": weights, "bits_per_weight": round(8 * size / weights, 3)}))
+    return 0
+
+
+def _cmd_calibrate(args) -> int:
+    cfg, tensors, _assets = _load_source(args)
+    if args.calibrate_cmd == "alphaq":
+        from .calibration import alphaq
+        from .quantize import presets
+        stats, sizes = {}, {}
+        for name, t in tensors.items():
+            if not presets.quantizable(name, t.shape):
+                continue
+            if t.ndim == 3:
+                for e in range(t.shape[0]):
+                    stats[f"{name}#{e}"] = alphaq.weight_statistics(t[e])
+                    sizes[f"{name}#{e}"] = int(t[e].size)
+            else:
+                stats[name] = alphaq.weight_statistics(t)
+                sizes[name] = int(t.size)
+        imp = alphaq.importance(stats)
+        cands = {k: float(v) for k, v in (item.split(":") for item in args.candidates.split(","))}
+        choice = alphaq.allocate(imp, sizes, cands, args.target_bpw * sum(sizes.values()))
+        doc = {"format": "mfq.alphaq-allocation.v1", "target_bpw": args.target_bpw, "candidates": cands,
+               "tensors": {k: {"alpha": stats[k].alpha, "variance": stats[k].variance, "importance": imp[k], "family": choice[k]}
+                           for k in stats}}
+        Path(args.output).write_text(json.dumps(doc, indent=1))
+        used = sum(sizes[k] * cands[c] for k, c in choice.items()) / max(1, sum(sizes.values()))
+        print(json.dumps({"output": args.output, "tensors": len(stats), "bits_per_weight": round(used, 3)}))
+        return 0
+    # imatrix: run the fp32 reference model with recording linears
+    import torch
+    from .calibration.imatrix import ImatrixCollector
+    from .models.moe_lm import MoeConfig, MoeLM
+    fields = MoeConfig.__dataclass_fields__
+    mcfg = MoeConfig(**{k: v for k, v in cfg.items() if k in fields})
+    col = ImatrixCollector()
+    model = MoeLM(mcfg, {k: torch.from_numpy(np.asarray(v, dtype=np.float32)) for k, v in tensors.items()}, observer=col.observe)
+    g = torch.Generator().manual_seed(args.seed)
+    for _ in range(args.chunks):
+        model.forward(torch.randint(0, mcfg.vocab_size, (args.ctx,), generator=g))
+    col.save(args.output)
+    print(json.dumps({"output": args.output, "layers": len(col.sum_in)}))
+    return 0
+
+
+def _cmd_solve_ew(args) -> int:
+    from .calibration.ew_solver import solve_files
+    print(json.dumps(solve_files(args.importance, args.candidates, args.budget, args.output_scheme, args.report)))
     return 0
 
 
@@ -173,7 +239,9 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--groupsize", type=int, default=0)
     q.add_argument("--sub-bits", type=int, default=0)
     q.add_argument("--format", choices=["nint2", "nint3", "nint4", "nint5", "nint6", "nint8", "nvq3", "mxfp4", "fp8", "bf16"])
-    q.add_argument("--preset", help="S2..S8 role presets (uniform NINT width)")
+    q.add_argument("--preset", help="role-based mixed-width NINT preset: S2-S S2-M S3-S S3-M S3-L S4-S S4-M S5-S S5-M S6 S8")
+    q.add_argument("--imatrix", help="importance matrix (.npz from `mfq calibrate imatrix`) for the NINT search")
+    q.add_argument("--ew-scheme", "--scheme", dest="ew_scheme", help="mfq.calibration-scheme.v3 from `mfq solve-ew`")
     q.add_argument("--random-expert-mix", default="", help="comma separated families per routed expert projection")
     q.add_argument("--random-expert-mix-seed", type=int, default=20260908)
     q.add_argument("--full-precision", action="store_true")
@@ -183,6 +251,30 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--overwrite", action="store_true")
     q.add_argument("--verbose", action="store_true")
     q.set_defaults(fn=_cmd_quantize)
+    c = sub.add_parser("calibrate", help="importance statistics for bit allocation")
+    cs = c.add_subparsers(dest="calibrate_cmd", required=True)
+    ca = cs.add_parser("alphaq", help="calibration-free spectral importance of every 2-D / expert weight + allocation")
+    ca.add_argument("input")
+    ca.add_argument("--target-bpw", type=float, default=4.0)
+    ca.add_argument("--candidates", default="NINT2:2.6,NINT3:3.6,NINT4:4.5,NINT5:5.5,NINT6:6.5,NINT8:8.5")
+    ca.add_argument("--output", required=True, help="JSON: per-tensor alpha / variance / importance / chosen family")
+    ca.add_argument("--seed", type=int, default=0)
+    ci = cs.add_parser("imatrix", help="input-channel importance of every linear layer on random or given token windows")
+    ci.add_argument("input")
+    ci.add_argument("--output", required=True)
+    ci.add_argument("--chunks", type=int, default=4)
+    ci.add_argument("--ctx", type=int, default=128)
+    ci.add_argument("--seed", type=int, default=0)
+    se = sub.add_parser("solve-ew", help="expert-wise joint budget solver (MILP) -> calibration scheme")
+    se.add_argument("--importance", required=True)
+    se.add_argument("--candidates", required=True)
+    se.add_argument("--budget", required=True)
+    se.add_argument("--output-scheme", required=True)
+    se.add_argument("--report")
+    se.set_defaults(fn=_cmd_solve_ew)
+    ca.set_defaults(fn=_cmd_calibrate)
+    ci.set_defaults(fn=_cmd_calibrate)
+
     i = sub.add_parser("inspect", help="summarise an .mfq container")
     i.add_argument("model")
     i.add_argument("--tensors", action="store_true")

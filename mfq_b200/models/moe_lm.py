@@ -121,10 +121,19 @@ def route(logits: torch.Tensor, cfg: MoeConfig) -> tuple[torch.Tensor, torch.Ten
 class MoeLM:
     """fp32 forward with a plain KV list (no paging): prefill a prompt, then decode token by token."""
 
-    def __init__(self, cfg: MoeConfig, weights: dict[str, torch.Tensor]) -> None:
+    def __init__(self, cfg: MoeConfig, weights: dict[str, torch.Tensor], observer=None) -> None:
+        """``observer(name, x, y)`` (optional) sees input and output of every named 2-D projection: the hook the
+        importance-matrix collection uses."""
         self.cfg, self.w = cfg, weights
+        self.observer = observer
         self.k_cache: list[torch.Tensor] = []
         self.v_cache: list[torch.Tensor] = []
+
+    def _lin(self, name: str, x: torch.Tensor) -> torch.Tensor:
+        y = x @ self.w[name].T
+        if self.observer is not None:
+            self.observer(name, x, y)
+        return y
 
     def reset(self) -> None:
         self.k_cache, self.v_cache = [], []
@@ -140,8 +149,8 @@ class MoeLM:
             he = torch.nn.functional.silu(xe @ gate[e].T) * (xe @ up[e].T)
             out.index_add_(0, tok, (he @ down[e].T) * wt[tok, slot][:, None])
         if cfg.shared_intermediate:
-            hs = torch.nn.functional.silu(x @ w[p + "mlp.shared_expert.gate.weight"].T) * (x @ w[p + "mlp.shared_expert.up.weight"].T)
-            out = out + hs @ w[p + "mlp.shared_expert.down.weight"].T
+            hs = torch.nn.functional.silu(self._lin(p + "mlp.shared_expert.gate.weight", x)) * self._lin(p + "mlp.shared_expert.up.weight", x)
+            out = out + self._lin(p + "mlp.shared_expert.down.weight", hs)
         return out
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
@@ -155,9 +164,9 @@ class MoeLM:
         for i in range(cfg.num_layers):
             p = f"model.block.{i}."
             h = _rms(x, w[p + "attention.norm.weight"], cfg.rms_eps)
-            q = _rope((h @ w[p + "attention.query.weight"].T).view(t, cfg.num_heads, cfg.head_dim), pos, cfg.rope_theta)
-            k = _rope((h @ w[p + "attention.key.weight"].T).view(t, cfg.num_kv_heads, cfg.head_dim), pos, cfg.rope_theta)
-            v = (h @ w[p + "attention.value.weight"].T).view(t, cfg.num_kv_heads, cfg.head_dim)
+            q = _rope(self._lin(p + "attention.query.weight", h).view(t, cfg.num_heads, cfg.head_dim), pos, cfg.rope_theta)
+            k = _rope(self._lin(p + "attention.key.weight", h).view(t, cfg.num_kv_heads, cfg.head_dim), pos, cfg.rope_theta)
+            v = self._lin(p + "attention.value.weight", h).view(t, cfg.num_kv_heads, cfg.head_dim)
             if len(self.k_cache) <= i:
                 self.k_cache.append(k)
                 self.v_cache.append(v)
@@ -170,7 +179,7 @@ class MoeLM:
             mask = torch.arange(kk.shape[0])[None, :] > pos[:, None]
             s = s.masked_fill(mask[None], float("-inf"))
             a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vv).reshape(t, -1)
-            x = x + a @ w[p + "attention.output.weight"].T
+            x = x + self._lin(p + "attention.output.weight", a)
             x = x + self._moe(_rms(x, w[p + "mlp.norm.weight"], cfg.rms_eps), p)
         x = _rms(x, w["model.output_norm.weight"], cfg.rms_eps)
-        return x @ w["model.output.weight"].T
+        return self._lin("model.output.weight", x)

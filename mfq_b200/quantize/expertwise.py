@@ -75,10 +75,10 @@ def balanced_expert_mix(tensor_name: str, n_experts: int, n_profiles: int, seed:
     return idx
 
 
-def quantize_matrix(w, profile: ExpertProfile, device="cpu"):
-    """One ``[out, in]`` (or stacked) matrix -> family tensor object."""
+def quantize_matrix(w, profile: ExpertProfile, device="cpu", importance=None):
+    """One ``[out, in]`` (or stacked) matrix -> family tensor object (``importance``: per-input weights, NINT only)."""
     if profile.nint is not None:
-        return quantize_nint(w, profile.nint, device=device)
+        return quantize_nint(w, profile.nint, device=device, importance=importance)
     if profile.nvq is not None:
         return quantize_nvq(w, profile.nvq, device=device)
     if profile.family == "MXFP4":

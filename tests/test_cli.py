@@ -29,3 +29,25 @@ def test_quantize_inspect_eval_and_load(tmp_path, capsys):
     engine, tok, cfg = load_engine(again, "cpu", max_batch=2, max_seq_len=64)
     out = engine.generate([torch.tensor(tok.encode("hello"))], 4)
     assert out.tokens.shape == (1, 4) and cfg.num_experts == 8
+
+
+def test_preset_imatrix_alphaq_flow(tmp_path, capsys):
+    """quantize --preset (role-based widths), calibrate imatrix -> quantize --imatrix, calibrate alphaq."""
+    import json
+
+    from mfq_b200 import cli, formats as F
+    out = tmp_path / "p.mfq"
+    assert cli.main(["quantize", "synthetic:tiny-moe", str(out), "--preset", "S3-M"]) == 0
+    with F.open_mfq(out) as st:
+        widths = {n: int(st[n].spec.bits) for n in st if st.dtype(n) == "NINT"}
+        assert st.header.extra["quantization"]["preset"] == "S3-M"
+    assert widths["model.output.weight"] == 6 and widths["model.block.0.attention.value.weight"] == 5
+    assert widths["model.block.0.attention.query.weight"] == 3 and widths["model.block.0.attention.output.weight"] == 4
+    im = tmp_path / "im.npz"
+    assert cli.main(["calibrate", "imatrix", "synthetic:tiny-moe", "--output", str(im), "--chunks", "2", "--ctx", "32"]) == 0
+    assert cli.main(["quantize", "synthetic:tiny-moe", str(tmp_path / "q.mfq"), "--bits", "4", "--imatrix", str(im)]) == 0
+    aq = tmp_path / "aq.json"
+    assert cli.main(["calibrate", "alphaq", "synthetic:tiny-moe", "--output", str(aq), "--target-bpw", "4.0"]) == 0
+    doc = json.loads(aq.read_text())
+    assert doc["format"] == "mfq.alphaq-allocation.v1" and len(doc["tensors"]) > 10
+    capsys.readouterr()
