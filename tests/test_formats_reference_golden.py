@@ -101,3 +101,19 @@ def test_mx_fp8_mfe_and_file_match_reference(reference_pkg, tmp_path):
     path2 = tmp_path / "y.mfq"
     rio.save(path2, RefHeader(version=2, model_arch="arch", extra={"k": {"v": [1, 2]}}), loaded)
     assert path.read_bytes() == path2.read_bytes()
+
+
+def test_nint8_zero_matches_reference(reference_pkg, tmp_path):
+    from mfq.formats import nint8_zero as r80
+    from mfq_b200.formats import nint8zero
+    w = (RNG.standard_normal((24, 96)) * 0.05).astype(np.float32)
+    mine = nint8zero.quantize_nint8_zero(w)
+    theirs = r80.quantize_nint8_zero(w, axis=0)
+    blob = nint8zero.pack_nint8_zero(mine)
+    assert blob == r80.pack_nint8_zero(theirs)  # same rule, same bytes
+    back = r80.unpack_nint8_zero(blob)
+    np.testing.assert_array_equal(np.asarray(back.q), mine.q)
+    np.testing.assert_array_equal(F.dequantize(nint8zero.unpack_nint8_zero(blob)), F.dequantize(mine))
+    container.save(tmp_path / "z.mfq", container.FileHeader(model_arch="t"), {"model.a.weight": mine})
+    with container.open_mfq(tmp_path / "z.mfq") as st:
+        assert st.dtype("model.a.weight") == "NINT8-0" and np.array_equal(st["model.a.weight"].q, mine.q)

@@ -193,3 +193,15 @@ def test_sharded_store(tmp_path):
 def test_legacy_dtype_names():
     assert F.canonical_dtype("NINT4") == "NINT" and F.canonical_dtype("NVQ3J-L") == "NVQ"
     assert F.canonical_dtype("NINTM") == "MFE" and F.canonical_dtype("BF16") == "BF16"
+
+
+def test_nint8_zero_roundtrip():
+    import numpy as np
+    from mfq_b200 import formats as F
+    from mfq_b200.formats import nint8zero
+    w = (np.random.default_rng(0).standard_normal((3, 8, 64)) * 0.1).astype(np.float32)
+    t = nint8zero.quantize_nint8_zero(w, axis=1)
+    back = nint8zero.unpack_nint8_zero(nint8zero.pack_nint8_zero(t))
+    assert back.shape == (3, 8, 64) and back.axis == 1
+    deq = F.dequantize(back)
+    assert deq.shape == w.shape and np.abs(deq - w).max() <= np.abs(w).max() / 127 * 0.51 + 1e-4
