@@ -36,7 +36,8 @@ struct GemmCfg {
   static constexpr int kEpiWarps = BT >= 64 ? 8 : 4;
   static constexpr int kCols = BT / (kEpiWarps / 4);   // token columns per epilogue thread
   static constexpr int kThreads = 64 + 32 * kEpiWarps;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int kXsBytes = kEpiWarps * kCols * 4;  // per-warp copy of the row multipliers of its token columns
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kXsBytes;
 };
 
 // Cross-rank all-reduce context of the fused epilogue (world == 1: disabled).
@@ -102,6 +103,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  float* xs_smem = reinterpret_cast<float*>(tiles + Cfg::kStages * Cfg::kStageBytes + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -238,6 +240,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
     for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
     const float* wsc = p.w_scale + (size_t(expert) * n_tiles_x + n_tile) * kb_total;
+    // The token multipliers are fetched now, under the main loop, into this warp's own smem slice (no cross-warp
+    // sync needed); at the end they cost a broadcast LDS instead of an exposed global load per column.  In gather
+    // mode they only exist once the peers' flags arrived, so that mode reads them at the end.
+    float* xs_w = xs_smem + (warp - 2) * CW;
+    if (!gather) {
+      for (int j = lane; j < CW; j += 32) xs_w[j] = (t0 + col0 + j < row_end) ? __ldg(p.x_scale + t0 + col0 + j) : 0.f;
+    }
     bool ok = true;
     for (int i = 0; i < nkb; ++i) {
       const int buf = i % Cfg::kAcc;
@@ -310,10 +319,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           owner = true;
         }
       }
+      __syncwarp();
       if (owner) {
         const float* xsc = gather ? p.ag.xs_full[p.ag.rank] + size_t(ag_epoch & 1u) * p.M : p.x_scale;
 #pragma unroll
-        for (int tt = 0; tt < CW; ++tt) acc[tt] *= (col0 + tt < tl) ? __ldcg(xsc + t0 + col0 + tt) : 0.f;
+        for (int tt = 0; tt < CW; ++tt) {
+          // gathered multipliers were written by peers during this launch: L2-coherent loads at this point
+          const float xm = gather ? ((col0 + tt < tl) ? __ldcg(xsc + t0 + col0 + tt) : 0.f) : xs_w[tt];
+          acc[tt] *= xm;
+        }
         if (p.ar.world > 1) {
           // ----- one-shot all-reduce over NVLink peer memory, fused into the epilogue -----
           // Every rank publishes its partial tile in its own (peer-mapped) buffer, bumps the tile's flag on every

@@ -217,11 +217,25 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
   // [lane*EPL/2, lane*EPL/2 + EPL/2) of each half of the head vector.
   constexpr int HP = EPL / 2;
   float lo[HP], hi[HP];
+  // explicit vector loads: with a run-time row stride the compiler can no longer prove the alignment itself
+  // (the host entry checks that the stride is a multiple of 8 elements)
+  auto load_half = [&](const __nv_bfloat16* ptr, float (&dst)[HP]) {
+    if constexpr (HP == 2) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(ptr);
+      dst[0] = __bfloat162float(v.x);
+      dst[1] = __bfloat162float(v.y);
+    } else if constexpr (HP == 4) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(ptr);
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
 #pragma unroll
-  for (int j = 0; j < HP; ++j) {
-    lo[j] = __bfloat162float(src[lane * HP + j]);
-    hi[j] = __bfloat162float(src[D / 2 + lane * HP + j]);
-  }
+      for (int j = 0; j < 4; ++j) dst[j] = __bfloat162float(e[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < HP; ++j) dst[j] = __bfloat162float(ptr[j]);
+    }
+  };
+  load_half(src + lane * HP, lo);
+  load_half(src + D / 2 + lane * HP, hi);
   const bool is_v = h >= Hq + Hk;
   // optional per-head RMSNorm of q and k before the rotation (QK-norm); nw_scale folds 1/rms into the partner reads
   const float* nw = is_v ? nullptr : (h < Hq ? q_norm_w : k_norm_w);
@@ -439,7 +453,7 @@ extern "C" int mfq_rope_kv_write_ex(const void* qkv, const int* positions, const
                                     int page_size, int rot, float theta, void* kd_out, void* vd_out,
                                     const float* q_norm_w, const float* k_norm_w, float norm_eps, int row_stride,
                                     cudaStream_t stream) {
-  if (T <= 0 || row_stride < (Hq + 2 * Hk) * D) return -1;
+  if (T <= 0 || row_stride < (Hq + 2 * Hk) * D || row_stride % 8) return -1;
   const int warps = T * (Hq + 2 * Hk);
   const int blocks = (warps + 7) / 8;
   const float l2t = log2f(theta);
