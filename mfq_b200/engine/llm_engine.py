@@ -70,7 +70,7 @@ class LLMEngine:
         self.sample_rows = torch.zeros((max_batch, 8), dtype=torch.int32, device=dev)
         self.sample_work: torch.Tensor | None = None
         self.use_graphs = use_graphs and dev.type == "cuda"
-        self.graphs: dict[tuple[int, bool], torch.cuda.CUDAGraph] = {}
+        self.graphs: dict[tuple[int, bool, int], torch.cuda.CUDAGraph] = {}
         self.launches_per_step: dict[int, int] = {}
         self.row_seq: dict[int, int] = {}
         self.row_len: dict[int, int] = {}  # host mirror of seq_lens for page management
@@ -274,17 +274,23 @@ class LLMEngine:
         step = StepBuffers(input_ids=self.input_ids[:b], positions=self.positions[:b], slots=self.slots[:b],
                            block_table=self.cache.block_table[:b], seq_lens=self.seq_lens[:b], state_slots=state_slots)
         if dev.type == "cuda":
-            from ..ops.kernels import attn_splits_for
-            self.model.attn_splits = attn_splits_for(b, self.model.hk, self.max_seq_len)
+            self.model.attn_splits = self._splits_now(b)
         logits = self.model.forward(step, self.cache, prefill=False, gather_logits=False)
         self._sample(logits, b, stochastic)
+
+    def _splits_now(self, b: int) -> int:
+        """Attention KV splits for the current contexts (host mirror of the row lengths; a graph is kept per value)."""
+        from ..ops.kernels import attn_splits_for
+        longest = max(self.row_len.values(), default=self.max_seq_len)
+        return attn_splits_for(b, self.model.hk, min(self.max_seq_len, longest))
 
     def decode_step(self, b: int, stochastic: bool = False) -> None:
         """Advance the active rows among ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device)."""
         if not self.use_graphs:
             self._decode_body(b, stochastic)
             return
-        g = self.graphs.get((b, stochastic))
+        key = (b, stochastic, self._splits_now(b))
+        g = self.graphs.get(key)
         if g is None:
             ops.Workspace.get(self.device)
             side = torch.cuda.Stream(device=self.device)
@@ -306,7 +312,7 @@ class LLMEngine:
             if saved_rec is not None:  # the recurrent state cannot be "rewritten later" like KV rows: put it back
                 self.rec_state.conv.copy_(saved_rec[0])
                 self.rec_state.state.copy_(saved_rec[1])
-            self.graphs[(b, stochastic)] = g
+            self.graphs[key] = g
         g.replay()
 
     # -- MTP draft / verify ---------------------------------------------------------------------------------------
@@ -334,8 +340,7 @@ class LLMEngine:
         mtp_ops.prepare(self.sampled[:b], self.draft[:b], self.seq_lens[:b], table, self.active[:b], ids, pos, slots, lens,
                         self.cache.page_size)
         if self.device.type == "cuda":
-            from ..ops.kernels import attn_splits_for
-            self.model.attn_splits = attn_splits_for(b, self.model.hk, self.max_seq_len)
+            self.model.attn_splits = self._splits_now(b)
         step = StepBuffers(input_ids=ids, positions=pos, slots=slots, block_table=table, seq_lens=lens, q_len=w)
         logits, hidden = self.model.forward(step, self.cache, prefill=False, gather_logits=False, return_hidden=True)
         targets = self.model.sample_greedy(logits, out=self.targets[: b * w])

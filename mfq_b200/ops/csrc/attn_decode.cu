@@ -64,6 +64,8 @@ paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t*
                              const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out,
                              float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hk, int max_pages,
                              float scale_log2, int q_len, int* status) {
+  pdl_trigger();
+  pdl_wait();
   using L = AttnSmem<D>;
   constexpr int KSTEPS = D / 16, NBD = D / 8;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -265,6 +267,8 @@ paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t*
 template <int D>
 __global__ void attn_reduce_log2_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                         __nv_bfloat16* __restrict__ out, int nsplit) {
+  pdl_trigger();
+  pdl_wait();
   const size_t hq = blockIdx.x;
   const int d = threadIdx.x;
   float mm = kNeg;
@@ -291,13 +295,13 @@ static int launch_attn(const void* q, const void* k_cache, const void* v_cache, 
     attr = true;
   }
   const float scale_log2 = sm_scale * 1.4426950408889634f;
-  paged_attn_decode_mma_kernel<D><<<dim3(B, Hk, splits), 128, L::kTotal, stream>>>(
+  launch_kernel(paged_attn_decode_mma_kernel<D>, dim3(B, Hk, splits), dim3(128), L::kTotal, stream, 
       static_cast<const __nv_bfloat16*>(q), static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache),
       k_scale, v_scale, block_table, seq_lens, static_cast<__nv_bfloat16*>(out), part_acc, part_ml, Hq, Hk, max_pages,
       scale_log2, q_len, status);
   if (cudaGetLastError() != cudaSuccess) return -7;
   if (splits > 1) {
-    attn_reduce_log2_kernel<D><<<B * q_len * Hq, D, 0, stream>>>(part_acc, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+    launch_kernel(attn_reduce_log2_kernel<D>, dim3(B * q_len * Hq), dim3(D), 0, stream, part_acc, part_ml, static_cast<__nv_bfloat16*>(out), splits);
     if (cudaGetLastError() != cudaSuccess) return -7;
   }
   return 0;

@@ -104,6 +104,15 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ----- programmatic dependent launch -----
+// Kernels of the decode path are launched with the programmatic-serialization attribute: a kernel may be scheduled
+// while its predecessor in the stream drains, run its prologue (barrier init, TMEM allocation, index math) and
+// then block in pdl_wait() until the predecessor has completed and flushed its writes.  Every such kernel calls
+// pdl_trigger() first thing, so its own successor may be scheduled as early as possible; correctness only depends on
+// pdl_wait() preceding the first access to memory another kernel produced (and the first global write).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ----- tcgen05 / TMEM -----
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {  // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
@@ -249,5 +258,31 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : int(r);
+}
+}  // namespace mfq
+
+
+// Host side: launch with the programmatic-serialization attribute (MFQ_PDL=0 in the environment turns it off).
+#include <cstdlib>
+#include <utility>
+namespace mfq {
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("MFQ_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 }  // namespace mfq

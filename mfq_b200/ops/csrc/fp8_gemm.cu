@@ -108,6 +108,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const bool gather = p.ag.world > 1;
+  pdl_trigger();
+  // Modes whose prologue already reads memory an earlier kernel wrote (the gathered-activation epoch, the route plan
+  // of the grouped mode) wait for their predecessor right away; the plain GEMM first sets up barriers and TMEM.
+  const bool early_inputs = gather || p.tile_map != nullptr;
+  if (early_inputs) pdl_wait();
   const uint32_t ag_epoch = gather ? *p.ag.epoch : 0u;
   if (gather && int(blockIdx.x) < p.ag.push_ctas) {
     // ----- push block: copy my shard into every rank's gathered buffer, then announce it -----
@@ -168,6 +173,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (!early_inputs) pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -493,7 +499,7 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
   }
   if (ag) p.ag = *ag;
   const int extra_x = ag ? ag->push_ctas : 0;
-  fp8_gemm_kernel<BT><<<dim3(n_tiles + extra_x, t_tiles, splits), Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tw, tx, tx_alt, p);
+  launch_kernel(fp8_gemm_kernel<BT>, dim3(n_tiles + extra_x, t_tiles, splits), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tw, tx, tx_alt, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 

@@ -58,6 +58,8 @@ __global__ void rmsnorm_quant_kernel(const __nv_bfloat16* __restrict__ x, const 
                                      __nv_bfloat16* __restrict__ residual_out, const __nv_bfloat16* __restrict__ w,
                                      uint8_t* __restrict__ q_out, float* __restrict__ scale_out,
                                      __nv_bfloat16* __restrict__ y_out, int H, float eps) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[33];
   const size_t row = blockIdx.x;
   const int nvec = H / 8;
@@ -139,6 +141,8 @@ template <int kMode>
 __global__ void quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q_out,
                                   float* __restrict__ scale_out, int K, int in_stride,
                                   const __nv_bfloat16* __restrict__ x2 = nullptr, int x2_stride = 0) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[33];
   const size_t row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * in_stride;
@@ -204,6 +208,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
                                      int page_size, int rot, float log2_theta, __nv_bfloat16* __restrict__ kd_out,
                                      __nv_bfloat16* __restrict__ vd_out, const float* __restrict__ q_norm_w,
                                      const float* __restrict__ k_norm_w, float norm_eps, int row_stride) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int EPL = D / 32;  // elements per lane
   const int warps_per_block = blockDim.x >> 5;
   const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -351,6 +357,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
 // Greedy sampling: arg-max over the vocabulary, one CTA per row (lowest index wins ties).
 // ---------------------------------------------------------------------------------------------
 __global__ void argmax_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, int V, int stride) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const __nv_bfloat16* row = logits + size_t(blockIdx.x) * stride;
@@ -385,6 +393,8 @@ __global__ void argmax_kernel(const __nv_bfloat16* __restrict__ logits, int* __r
 
 __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                              __nv_bfloat16* __restrict__ out, int H) {
+  pdl_trigger();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const size_t src = size_t(ids[row]);
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x)
@@ -397,6 +407,8 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
                                       int* __restrict__ positions, int* __restrict__ seq_lens,
                                       int* __restrict__ slots, const int* __restrict__ block_table, int B,
                                       int max_pages, int page_size, const int* __restrict__ active) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   if (active && !active[b]) { slots[b] = -1; return; }
@@ -418,7 +430,7 @@ extern "C" int mfq_rmsnorm_quant(const void* x, const void* residual, void* resi
   int threads = ((H / 8 + kNormVecs - 1) / kNormVecs + 31) / 32 * 32;
   if (threads < 32) threads = 32;
   if (threads > 1024) return -1;
-  rmsnorm_quant_kernel<<<M, threads, 0, stream>>>(
+  launch_kernel(rmsnorm_quant_kernel, dim3(M), dim3(threads), 0, stream,
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
       static_cast<__nv_bfloat16*>(residual_out), static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q_out),
       scale_out, static_cast<__nv_bfloat16*>(y_out), H, eps);
@@ -430,9 +442,9 @@ extern "C" int mfq_quant_rows(const void* x, void* q_out, float* scale_out, int 
   if (K % 8 || in_stride % 8 || M <= 0) return -1;
   const int threads = K >= 4096 ? 512 : 256;
   if (swiglu)
-    quant_rows_kernel<1><<<M, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out), scale_out, K, in_stride);
+    launch_kernel(quant_rows_kernel<1>, dim3(M), dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out), scale_out, K, in_stride, static_cast<const __nv_bfloat16*>(nullptr), 0);
   else
-    quant_rows_kernel<0><<<M, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out), scale_out, K, in_stride);
+    launch_kernel(quant_rows_kernel<0>, dim3(M), dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out), scale_out, K, in_stride, static_cast<const __nv_bfloat16*>(nullptr), 0);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
@@ -440,7 +452,7 @@ extern "C" int mfq_quant_rows(const void* x, void* q_out, float* scale_out, int 
 extern "C" int mfq_gate_quant_rows(const void* x, const void* gate, void* q_out, float* scale_out, int M, int K,
                                    int in_stride, int gate_stride, cudaStream_t stream) {
   if (K % 8 || in_stride % 8 || gate_stride % 8 || M <= 0) return -1;
-  quant_rows_kernel<2><<<M, K >= 4096 ? 512 : 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out),
+  launch_kernel(quant_rows_kernel<2>, dim3(M), dim3(K >= 4096 ? 512 : 256), 0, stream, static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out),
                                                                 scale_out, K, in_stride, static_cast<const __nv_bfloat16*>(gate),
                                                                 gate_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
@@ -458,7 +470,7 @@ extern "C" int mfq_rope_kv_write_ex(const void* qkv, const int* positions, const
   const int blocks = (warps + 7) / 8;
   const float l2t = log2f(theta);
 #define MFQ_ROPE(DD)                                                                                             \
-  rope_kv_write_kernel<DD><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, slots, \
+  launch_kernel(rope_kv_write_kernel<DD>, dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(qkv), positions, slots, \
       static_cast<__nv_bfloat16*>(q_out), static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache),      \
       k_scale, v_scale, T, Hq, Hk, page_size, rot, l2t, static_cast<__nv_bfloat16*>(kd_out),                   \
       static_cast<__nv_bfloat16*>(vd_out), q_norm_w, k_norm_w, norm_eps, row_stride)
@@ -479,20 +491,20 @@ extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const in
 }
 
 extern "C" int mfq_argmax(const void* logits, int* out, int B, int V, int stride, cudaStream_t stream) {
-  argmax_kernel<<<B, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), out, V, stride);
+  launch_kernel(argmax_kernel, dim3(B), dim3(1024), 0, stream, static_cast<const __nv_bfloat16*>(logits), out, V, stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
 extern "C" int mfq_embed(const int* ids, const void* table, void* out, int T, int H, cudaStream_t stream) {
   if (H % 8) return -1;
-  embed_kernel<<<T, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), H);
+  launch_kernel(embed_kernel, dim3(T), dim3(128), 0, stream, ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), H);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
 extern "C" int mfq_decode_advance(const int* sampled, int* input_ids, int* positions, int* seq_lens, int* slots,
                                   const int* block_table, int B, int max_pages, int page_size, const int* active,
                                   cudaStream_t stream) {
-  decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(sampled, input_ids, positions, seq_lens, slots,
+  launch_kernel(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, sampled, input_ids, positions, seq_lens, slots,
                                                              block_table, B, max_pages, page_size, active);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }

@@ -125,11 +125,13 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tenso
     return q_out
 
 
-def attn_splits_for(batch: int, kv_heads: int, max_len: int, sms: int = 148) -> int:
-    """KV splits that give every SM a few CTAs without cutting a split below four pages."""
-    pages = max(1, (max_len + 15) // 16)
-    want = max(1, (3 * sms) // max(1, batch * kv_heads))
-    return max(1, min(want, (pages + 3) // 4, 64))
+def attn_splits_for(batch: int, kv_heads: int, ctx_len: int) -> int:
+    """KV splits per (sequence, KV head) for the decode attention, fitted to a sweep on B200 (batch 8..128, contexts
+    1k/4k): enough CTAs to occupy the GPU (~256) when the batch is small, about 1300 tokens per split when the
+    context is long, never below 256 tokens per split."""
+    by_ctas = -(-256 // max(1, batch * kv_heads))
+    by_len = int(ctx_len / 1300 + 0.5)
+    return max(1, min(max(by_ctas, by_len), max(1, ctx_len // 256), 64))
 
 
 def paged_attn_decode(q: torch.Tensor, kv, block_table: torch.Tensor, seq_lens: torch.Tensor, *, sm_scale: float,
