@@ -341,7 +341,12 @@ class LLMEngine:
                         self.cache.page_size)
         if self.device.type == "cuda":
             self.model.attn_splits = self._splits_now(b)
-        step = StepBuffers(input_ids=ids, positions=pos, slots=slots, block_table=table, seq_lens=lens, q_len=w)
+        state_slots = None
+        if self.rec_state is not None:
+            state_slots = self.state_slots[:b]
+            torch.where(self.active[:b] > 0, self.row_ids[:b], torch.full_like(self.row_ids[:b], -1), out=state_slots)
+        step = StepBuffers(input_ids=ids, positions=pos, slots=slots, block_table=table, seq_lens=lens, q_len=w,
+                           state_slots=state_slots, verify=self.rec_state is not None)
         logits, hidden = self.model.forward(step, self.cache, prefill=False, gather_logits=False, return_hidden=True)
         targets = self.model.sample_greedy(logits, out=self.targets[: b * w])
         # the head sees the TRUE successor of every window position, so whatever prefix is accepted its KV rows and
@@ -351,6 +356,8 @@ class LLMEngine:
         head_next = self.model.sample_greedy(mlogits, out=self.head_next[: b * w])
         mtp_ops.accept(targets, head_next, self.active[:b], self.draft[:b], self.sampled[:b], self.seq_lens[:b],
                        self.out_tokens[:b], self.n_out[:b], self.accept_row[:b], self.mtp_counters)
+        if self.rec_state is not None:  # recurrent layers keep the state after the last accepted window position
+            self.model.commit_verify(b, w, state_slots, self.accept_row[:b])
         if k > 1:
             self._mtp_chain(0, b, mtp_ops.select_rows(mhid, self.accept_row[:b], w))
 
@@ -367,6 +374,7 @@ class LLMEngine:
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream())
             saved = [t.clone() for t in (self.seq_lens, self.sampled, self.draft, self.mtp_counters)]
+            saved_rec = (self.rec_state.conv.clone(), self.rec_state.state.clone()) if self.rec_state is not None else None
             with torch.cuda.stream(side):
                 for _ in range(2):
                     self._mtp_body(b)
@@ -378,6 +386,9 @@ class LLMEngine:
             self.launches_per_step[("mtp", b)] = ops.launch_count() - before
             for dst, src in zip((self.seq_lens, self.sampled, self.draft, self.mtp_counters), saved):
                 dst.copy_(src)
+            if saved_rec is not None:
+                self.rec_state.conv.copy_(saved_rec[0])
+                self.rec_state.state.copy_(saved_rec[1])
             self.mtp_graphs[b] = g
         g.replay()
 

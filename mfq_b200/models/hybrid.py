@@ -87,9 +87,27 @@ class GdnState:
         self.conv = torch.zeros((n, slots, 3, c), dtype=torch.float32, device=device)
         self.state = torch.zeros((n, slots, hv, d, d), dtype=torch.float32, device=device)
 
+        self._ckpt: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
+
     def reset(self, slot: int) -> None:
         self.conv[:, slot].zero_()
         self.state[:, slot].zero_()
+
+    def checkpoints(self, rows: int, window: int):
+        """Per-layer verify-window checkpoints ``(conv [n, rows, L, 3, C], state [n, rows, L, Hv, d, d])`` (allocated once
+        per geometry; 2 MB per layer, row and window position at d = 128, Hv = 32)."""
+        key = (rows, window)
+        if key not in self._ckpt:
+            n, _, _, c = self.conv.shape
+            self._ckpt[key] = (torch.zeros((n, rows, window, 3, c), dtype=torch.float32, device=self.conv.device),
+                               torch.zeros((n, rows, window) + tuple(self.state.shape[2:]), dtype=torch.float32, device=self.conv.device))
+        return self._ckpt[key]
+
+    def commit(self, rows: int, window: int, slots: torch.Tensor, keep: torch.Tensor) -> None:
+        """After a verify window: every layer adopts the checkpoint of window position ``keep[b]`` for row ``b``."""
+        conv_ck, state_ck = self.checkpoints(rows, window)
+        for j in range(self.conv.shape[0]):
+            gdn.select(state_ck[j], conv_ck[j], self.state[j], self.conv[j], slots, keep)
 
     def layer(self, i: int):
         j = self.index[i]
@@ -232,8 +250,15 @@ class HybridModel(MoeDecoderModel):
         L = step.q_len if step.block_table is not None else h.shape[0]
         if not h.is_cuda:
             mixed, z, a, b = (t.contiguous() for t in (mixed, z, a, b))
-        qkv = gdn.conv(mixed, conv_state, g.conv_w, slots, L)
-        y = gdn.recurrent(qkv, z, a, b, g.A_log, g.dt_bias, g.norm_w, state, slots, L, g.k_heads, g.v_heads, cfg.rms_eps)
+        conv_ck = state_ck = None
+        if step.verify:
+            rows = h.shape[0] // L
+            conv_all, state_all = self.state.checkpoints(rows, L)
+            j = self.state.index[li]
+            conv_ck, state_ck = conv_all[j], state_all[j]
+        qkv = gdn.conv(mixed, conv_state, g.conv_w, slots, L, conv_ckpt=conv_ck)
+        y = gdn.recurrent(qkv, z, a, b, g.A_log, g.dt_bias, g.norm_w, state, slots, L, g.k_heads, g.v_heads, cfg.rms_eps,
+                          ckpt=state_ck)
         yq, ys = self._quant(y)
         return self._row_parallel(g.out_proj, yq, ys, h)
 
@@ -287,16 +312,24 @@ class HybridModel(MoeDecoderModel):
         return self._row_parallel(layer.o_proj, aq, a_s, h)
 
     def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
-        li = self._layer_index[id(layer)]
-        if layer.gdn is not None:
+        li = self._layer_index.get(id(layer))  # None: a block outside the stack (the MTP head's attention block)
+        if getattr(layer, "gdn", None) is not None:
             h = self._gdn_mixer(h, layer, li, step)
-        else:
+        elif isinstance(layer, HybridLayer):
             h = self._gated_attention(h, layer, kv, step, prefill)
+        else:
+            return super()._block(h, layer, kv, step, prefill)
         return self._ffn(h, layer)
+
+    def commit_verify(self, rows: int, window: int, slots: torch.Tensor, keep: torch.Tensor) -> None:
+        self.state.commit(rows, window, slots, keep)
 
     def forward(self, step: StepBuffers, cache, **kw):
         if self.state is None:
             raise RuntimeError("call make_state(slots) before the first forward")
-        if not hasattr(self, "_layer_index"):
-            self._layer_index = {id(l): i for i, l in enumerate(self.w.layers)}
+        self._layer_index = {id(l): i for i, l in enumerate(self.w.layers)}
         return super().forward(step, cache, **kw)
+
+    def mtp_forward(self, step: StepBuffers, cache, hidden, **kw):
+        self._layer_index = {id(l): i for i, l in enumerate(self.w.layers)}
+        return super().mtp_forward(step, cache, hidden, **kw)

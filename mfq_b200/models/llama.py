@@ -180,6 +180,9 @@ class StepBuffers:
     q_len: int = 1
     # models with recurrent state (linear attention): state slot of every row ([B] int32, -1 = leave the row alone)
     state_slots: torch.Tensor | None = None
+    # MTP verify window: recurrent layers write per-token state checkpoints instead of committing their state;
+    # the engine commits the checkpoint of the last accepted token afterwards
+    verify: bool = False
 
 
 class LlamaModel:

@@ -45,3 +45,39 @@ def test_hybrid_gpu_matches_cpu_reference_and_graph_decode():
         gpu.release(r)
     first = gpu.prefill(0, prompts[1])
     assert first == int(toks[1, 0])
+
+
+def test_hybrid_mtp_cycles_on_gpu():
+    """Graph-captured draft/verify cycles with recurrent-state checkpoints: same tokens as plain greedy decoding."""
+    require_gpu_lib()
+    from mfq_b200.models.llama import LlamaWeights
+    cfg = HybridConfig.tiny()
+    w = HybridWeights.from_tensors(cfg, init_hybrid_weights(cfg, seed=3, std=0.05), "cuda")
+    w.mtp = LlamaWeights.random_init(cfg, "cuda", seed=9, std=0.05, mtp=True).mtp
+    eng = LLMEngine(HybridModel(cfg, w), max_batch=4, max_seq_len=128, mtp_draft_tokens=2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)) for n in (9, 14, 33)]
+    plain = eng.generate(prompts, 12).tokens
+    for r in range(3):
+        eng.release(r)
+    spec = eng.generate(prompts, 12, use_mtp=True).tokens
+    check_status()
+    agree = []
+    for r in range(3):
+        a, b = plain[r].tolist(), spec[r].tolist()
+        n = 0
+        while n < len(a) and a[n] == b[n]:
+            n += 1
+        agree.append(n / len(a))
+    assert min(agree) >= 0.4 and sum(agree) / 3 >= 0.7, agree
+    for r in range(3):
+        eng.release(r)
+    truth = plain[1].tolist()
+    eng.prefill(0, prompts[1])
+    eng.grow(0, 64)
+    eng.draft[0] = torch.tensor(truth[1:3], dtype=torch.int32, device="cuda")
+    eng.active.zero_()
+    eng.active[0] = 1
+    eng.mtp_step(1)
+    n = int(eng.n_out[0])
+    assert n >= 2 and eng.out_tokens[0, :n].tolist() == truth[1 : 1 + n]
+    check_status()

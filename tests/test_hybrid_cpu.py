@@ -47,3 +47,45 @@ def test_rows_do_not_disturb_each_other():
     eng.release(0)
     both = eng.generate([p0, p1], 6).tokens
     assert both[0].tolist() == solo
+
+
+def _with_mtp_head(cfg, w, seed=9):
+    """Attach a random MTP head (dense attention block) to hybrid weights."""
+    from mfq_b200.models.llama import LlamaWeights, MtpHead
+    donor = LlamaWeights.random_init(cfg, "cpu", seed=seed, std=0.05, mtp=True)
+    w.mtp = donor.mtp
+    return w
+
+
+def test_mtp_cycles_on_hybrid_model_are_lossless():
+    """Verify windows checkpoint the recurrent state per token and commit the accepted prefix: the tokens must be
+    the ones plain greedy decoding produces."""
+    cfg = HybridConfig.tiny()
+    w = _with_mtp_head(cfg, HybridWeights.from_tensors(cfg, init_hybrid_weights(cfg, seed=3, std=0.05), "cpu"))
+    eng = LLMEngine(HybridModel(cfg, w), max_batch=2, max_seq_len=96, device="cpu", mtp_draft_tokens=2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)) for n in (9, 14)]
+    plain = eng.generate(prompts, 10).tokens
+    for r in range(2):
+        eng.release(r)
+    spec = eng.generate(prompts, 10, use_mtp=True).tokens
+    for r in range(2):
+        a, b = plain[r].tolist(), spec[r].tolist()
+        n = 0
+        while n < len(a) and a[n] == b[n]:
+            n += 1
+        assert n >= 8, (a, b)  # float summation order may flip a near-tie late in the sequence
+    # oracle drafts: all accepted, state committed at the last window position
+    for r in range(2):
+        eng.release(r)
+    truth = plain[0].tolist()
+    eng.prefill(0, prompts[0])
+    eng.grow(0, 40)
+    eng.draft[0] = torch.tensor(truth[1:3], dtype=torch.int32)
+    eng.active.zero_()
+    eng.active[0] = 1
+    eng.mtp_step(1)
+    n = int(eng.n_out[0])
+    assert n >= 2 and eng.out_tokens[0, :n].tolist() == truth[1 : 1 + n]
+    # and decoding on from the committed state still follows the plain sequence
+    eng.decode_step(1)
+    assert int(eng.sampled[0]) == truth[1 + n]
