@@ -97,9 +97,13 @@ class _Stream:
                 return
 
 
-def create_app(service: ModelService, api_key: str | None = None) -> FastAPI:
+def create_app(service: ModelService, api_key: str | None = None, sessions=None) -> FastAPI:
+    """``sessions``: a :class:`~mfq_b200.server.sessions.SessionStore` (in-memory when omitted)."""
+    from .sessions import SessionStore
     app = FastAPI(title="mfq-b200", version="0.1.0")
     app.state.service = service
+    store = sessions if sessions is not None else SessionStore()
+    app.state.sessions = store
 
     @app.middleware("http")
     async def auth(request: HttpRequest, call_next):
@@ -281,5 +285,50 @@ def create_app(service: ModelService, api_key: str | None = None) -> FastAPI:
     async def unload_model(request: HttpRequest):
         body = await request.json()
         return {"unloaded": service.unload(body.get("model", ""))}
+
+    # ---- sessions (chat history kept by the server for its clients) ----------------------------------------------
+    @app.get("/api/v1/sessions")
+    async def list_sessions():
+        return {"sessions": store.list()}
+
+    @app.post("/api/v1/sessions")
+    async def create_session(request: HttpRequest):
+        body = await request.json() if await request.body() else {}
+        return store.create(body.get("title", ""), body.get("model"), body.get("meta"))
+
+    @app.get("/api/v1/sessions/{sid}")
+    async def get_session(sid: str):
+        s = store.get(sid)
+        return s if s is not None else error_response(404, "session_not_found", f"no session {sid!r}")
+
+    @app.post("/api/v1/sessions/{sid}/messages")
+    async def append_message(sid: str, request: HttpRequest):
+        body = await request.json()
+        try:
+            seq = store.append(sid, body.get("role", "user"), body.get("content", ""), body.get("meta"))
+        except KeyError:
+            return error_response(404, "session_not_found", f"no session {sid!r}")
+        return {"seq": seq}
+
+    @app.patch("/api/v1/sessions/{sid}")
+    async def rename_session(sid: str, request: HttpRequest):
+        body = await request.json()
+        ok = store.rename(sid, body.get("title", ""))
+        return {"renamed": True} if ok else error_response(404, "session_not_found", f"no session {sid!r}")
+
+    @app.delete("/api/v1/sessions/{sid}")
+    async def delete_session(sid: str):
+        return {"deleted": store.delete(sid)}
+
+    @app.get("/api/v1/runtime/sampling-profile")
+    async def sampling_profile(model: str | None = None):
+        """Effective sampling defaults of a loaded model and where they come from."""
+        from ..formats import runtime_profile as rp
+        try:
+            lm = service.resolve(model)
+        except KeyError:
+            return error_response(404, "model_not_found", f"model {model!r} is not loaded")
+        meta = getattr(lm, "meta", None) or {}
+        return rp.resolve(meta.get("header_extra"), meta.get("assets"), meta.get("architecture"))
 
     return app

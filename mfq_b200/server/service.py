@@ -28,6 +28,7 @@ class LoadedModel:
     instance: str = field(default_factory=lambda: str(uuid.uuid4()))
     loaded_at: float = field(default_factory=time.time)
     request_capacity: int = 0
+    meta: dict = field(default_factory=dict)  # header_extra / assets / architecture of the checkpoint, when known
 
 
 class ModelService:

@@ -109,3 +109,20 @@ def test_api_key():
         assert c.get("/v1/models", headers={"authorization": "Bearer s3cret"}).status_code == 200
         assert c.get("/metrics", headers={"x-api-key": "s3cret"}).status_code == 200
     service.shutdown()
+
+
+def test_sessions_and_sampling_profile(client):
+    client, _service = client
+    s = client.post("/api/v1/sessions", json={"title": "t1", "model": "tiny"}).json()
+    sid = s["id"]
+    assert client.post(f"/api/v1/sessions/{sid}/messages", json={"role": "user", "content": "hi"}).json() == {"seq": 0}
+    assert client.post(f"/api/v1/sessions/{sid}/messages", json={"role": "assistant", "content": "yo"}).json() == {"seq": 1}
+    got = client.get(f"/api/v1/sessions/{sid}").json()
+    assert [m["content"] for m in got["messages"]] == ["hi", "yo"] and got["title"] == "t1"
+    assert client.patch(f"/api/v1/sessions/{sid}", json={"title": "t2"}).json() == {"renamed": True}
+    assert client.get("/api/v1/sessions").json()["sessions"][0]["title"] == "t2"
+    assert client.get("/api/v1/sessions/nope").status_code == 404
+    assert client.post("/api/v1/sessions/nope/messages", json={"content": "x"}).status_code == 404
+    assert client.delete(f"/api/v1/sessions/{sid}").json() == {"deleted": True}
+    prof = client.get("/api/v1/runtime/sampling-profile").json()
+    assert prof["source"] == "builtin" and prof["chat"]["top_p"] == 1.0
