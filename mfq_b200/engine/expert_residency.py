@@ -1,0 +1,158 @@
+"""MoE expert residency: an HBM slot arena in front of a pinned-host tier.
+
+Models whose routed experts exceed the GPU keep every expert in pinned host memory and only ``slots`` of them in HBM.
+The grouped expert GEMMs index the ARENA (``[slots, ...]``), so routing ids are translated expert -> slot before the
+route plan and no kernel changes:
+
+    ids_slot = residency.ensure(topk_ids)        # uploads what is missing, returns slot ids (same shape)
+    moe_ffn_fp8(x, xs, ids_slot, w, arena.gate_up, arena.gate_up_scale, arena.down, arena.down_scale, e_lo=0, ...)
+
+* ``ensure`` reads the step's expert histogram on the host (one small D2H), pins the experts the step uses, evicts
+  the least recently used unpinned slots for the missing ones (C++ slot book), and issues the uploads with
+  ``non_blocking`` copies on a side stream; the compute stream waits on an event (stream-ordered, no spinning).
+* ``rebalance`` between steps swaps cold residents for hotter absent experts (C++ ranker, exponential heat).
+* When a step needs more distinct experts than there are slots it is processed in waves of at most ``slots`` experts.
+
+Reference: the residency manager, pinned expert arena and slot book of
+``cpp_runtime/backends/cuda/runtime/moe_residency_manager.*``, ``storage/moe_expert_cache*``,
+``engine/include/moe_cache_policy.h``; there the device polls host-written ready flags, here readiness is an event.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from .. import native
+
+
+@dataclass
+class ExpertArena:
+    gate_up: torch.Tensor  # [slots, 2I, H] fp8
+    gate_up_scale: torch.Tensor
+    down: torch.Tensor  # [slots, H, I] fp8
+    down_scale: torch.Tensor
+
+
+class ExpertResidency:
+    def __init__(self, gate_up: torch.Tensor, gate_up_scale: torch.Tensor, down: torch.Tensor, down_scale: torch.Tensor,
+                 slots: int, device, heat_decay: float = 0.9) -> None:
+        """The four tensors hold ALL experts on the host (``[E, ...]``); they are pinned when the device is a GPU."""
+        self.device = torch.device(device)
+        self.n = gate_up.shape[0]
+        self.slots = min(slots, self.n)
+        cuda = self.device.type == "cuda"
+        self.host = tuple(t.contiguous().pin_memory() if cuda else t.contiguous() for t in (gate_up, gate_up_scale, down, down_scale))
+        self.arena = ExpertArena(*(torch.empty((self.slots,) + tuple(t.shape[1:]), dtype=t.dtype, device=self.device) for t in self.host))
+        self.book = native.SlotBook(self.slots)
+        self.slot_of = np.full(self.n, -1, dtype=np.int32)
+        self.slot_of_dev = torch.full((self.n,), -1, dtype=torch.int32, device=self.device)
+        self.heat = np.zeros(self.n, dtype=np.float64)
+        self.decay = heat_decay
+        self.copy_stream = torch.cuda.Stream(device=self.device) if cuda else None
+        self.stats = {"hits": 0, "uploads": 0, "evictions": 0, "waves": 0, "upload_bytes": 0}
+        self.bytes_per_expert = sum(t[0].numel() * t[0].element_size() for t in self.host)
+
+    # -- uploads ------------------------------------------------------------------------------------------------
+    def _upload(self, expert: int, slot: int) -> None:
+        for dst, src in zip((self.arena.gate_up, self.arena.gate_up_scale, self.arena.down, self.arena.down_scale), self.host):
+            dst[slot].copy_(src[expert], non_blocking=True)
+        self.stats["uploads"] += 1
+        self.stats["upload_bytes"] += self.bytes_per_expert
+
+    def _make_resident(self, experts: list[int]) -> None:
+        """All of ``experts`` (at most ``slots`` many) resident and pinned; uploads ordered before later compute."""
+        missing = [e for e in experts if self.slot_of[e] < 0]
+        for e in experts:
+            if self.slot_of[e] >= 0:
+                self.book.lookup(int(e))
+                self.book.pin(int(e), +1)
+                self.stats["hits"] += 1
+        if missing:
+            ctx = torch.cuda.stream(self.copy_stream) if self.copy_stream is not None else _Null()
+            if self.copy_stream is not None:
+                self.copy_stream.wait_stream(torch.cuda.current_stream(self.device))  # slots may still be read
+            with ctx:
+                for e in missing:
+                    slot, evicted = self.book.acquire(int(e))
+                    if evicted is not None:
+                        self.slot_of[evicted] = -1
+                        self.stats["evictions"] += 1
+                    self.slot_of[e] = slot
+                    self.book.pin(int(e), +1)
+                    self._upload(int(e), slot)
+            if self.copy_stream is not None:
+                torch.cuda.current_stream(self.device).wait_stream(self.copy_stream)
+        self.slot_of_dev.copy_(torch.from_numpy(self.slot_of), non_blocking=True)
+
+    def _unpin(self, experts: list[int]) -> None:
+        for e in experts:
+            self.book.pin(int(e), -1)
+
+    # -- per step -----------------------------------------------------------------------------------------------
+    def waves(self, topk_ids: torch.Tensor) -> list[list[int]]:
+        """Experts the step uses, hottest first, cut into groups of at most ``slots``; also updates the heat."""
+        flat = topk_ids.reshape(-1).cpu().numpy().astype(np.int64)
+        counts = np.bincount(flat[flat >= 0], minlength=self.n)[: self.n]  # negative ids: experts of other ranks
+        self.heat = self.heat * self.decay + counts
+        used = [int(e) for e in np.argsort(-counts, kind="stable") if counts[e] > 0]
+        return [used[i : i + self.slots] for i in range(0, len(used), self.slots)]
+
+    def run(self, topk_ids: torch.Tensor, fn):
+        """Calls ``fn(ids_slot, arena)`` once per wave and sums the results.  ``ids_slot`` has the shape of
+        ``topk_ids`` with arena slots for the wave's experts and -1 elsewhere (the route plan skips -1)."""
+        out = None
+        for wave in self.waves(topk_ids):
+            self.stats["waves"] += 1
+            self._make_resident(wave)
+            in_wave = torch.zeros(self.n, dtype=torch.bool, device=self.device)
+            in_wave[torch.as_tensor(wave, device=self.device, dtype=torch.long)] = True
+            ids = topk_ids.long().clamp(min=0)
+            mine = in_wave[ids] & (topk_ids >= 0)
+            ids_slot = torch.where(mine, self.slot_of_dev[ids], torch.full_like(self.slot_of_dev[ids], -1)).to(torch.int32)
+            part = fn(ids_slot, self.arena)
+            out = part if out is None else out + part
+            self._unpin(wave)
+        return out
+
+    # -- between steps ------------------------------------------------------------------------------------------
+    def rebalance(self, max_swaps: int = 4, hysteresis: float = 0.25) -> list[tuple[int, int]]:
+        """Swap cold residents for hotter absent experts; returns the (evicted, loaded) pairs."""
+        swaps = native.moe_rank_swaps(self.heat, (self.slot_of >= 0).astype(np.uint8), max_swaps, hysteresis)
+        done = []
+        for evict, load in swaps:
+            slot = int(self.slot_of[evict])
+            if slot < 0 or self.book.pin(int(evict), 0) > 0:
+                continue
+            # re-key the slot: acquire for the newcomer evicts the LRU entry, so touch everything else first
+            self.book.lookup(int(evict))
+            for e in np.flatnonzero(self.slot_of >= 0):
+                if e != evict:
+                    self.book.lookup(int(e))
+            got, evicted = self.book.acquire(int(load))
+            if evicted is not None:
+                self.slot_of[evicted] = -1
+            self.slot_of[load] = got
+            self._make_resident_noop_upload(int(load), got)
+            done.append((int(evict), int(load)))
+        self.slot_of_dev.copy_(torch.from_numpy(self.slot_of), non_blocking=True)
+        return done
+
+    def _make_resident_noop_upload(self, expert: int, slot: int) -> None:
+        if self.copy_stream is not None:
+            self.copy_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.copy_stream):
+                self._upload(expert, slot)
+            torch.cuda.current_stream(self.device).wait_stream(self.copy_stream)
+        else:
+            self._upload(expert, slot)
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False

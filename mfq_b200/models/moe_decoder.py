@@ -59,6 +59,7 @@ class MoeFfn:
     shared_gate_up: Fp8Linear | None = None
     shared_down: Fp8Linear | None = None
     e_lo: int = 0
+    residency: object | None = None  # ExpertResidency: experts live on the host, `gate_up`/`down` are its HBM arena
     shared_replicated: bool = False  # shared expert too narrow to shard on 128-wide blocks: every rank holds all of it
 
 
@@ -79,8 +80,11 @@ def _to_float(t, device) -> torch.Tensor:
 
 class MoeWeights(LlamaWeights):
     @classmethod
-    def from_tensors(cls, cfg: MoeDecoderConfig, tensors, device, tp_rank: int = 0, tp_size: int = 1) -> "MoeWeights":
-        """Build rank-local FP8 weights from checkpoint tensors under canonical names (a dict or an ``MfqStore``)."""
+    def from_tensors(cls, cfg: MoeDecoderConfig, tensors, device, tp_rank: int = 0, tp_size: int = 1,
+                     expert_slots: int | None = None) -> "MoeWeights":
+        """Build rank-local FP8 weights from checkpoint tensors under canonical names (a dict or an ``MfqStore``).
+        ``expert_slots`` < experts per rank keeps the routed experts in (pinned) host memory behind an HBM arena of
+        that many slots (:class:`~mfq_b200.engine.expert_residency.ExpertResidency`); such a model decodes eagerly."""
         dev = torch.device(device)
         h, d, w = cfg.hidden_size, cfg.head_dim, tp_size
         hq, hk = cfg.num_heads, cfg.num_kv_heads
@@ -117,6 +121,11 @@ class MoeWeights(LlamaWeights):
                 ffn = MoeFfn(router=norm(p + "mlp.router.weight"),
                              router_bias=get(bias_name) if bias_name in tensors else None,
                              gate_up=gu_q, gate_up_scale=gu_s, down=dn_q, down_scale=dn_s, e_lo=e_lo)
+                if expert_slots is not None and expert_slots < e_per:
+                    from ..engine.expert_residency import ExpertResidency
+                    ffn.residency = ExpertResidency(gu_q.cpu(), gu_s.cpu(), dn_q.cpu(), dn_s.cpu(), expert_slots, dev)
+                    arena = ffn.residency.arena
+                    ffn.gate_up, ffn.gate_up_scale, ffn.down, ffn.down_scale = arena.gate_up, arena.gate_up_scale, arena.down, arena.down_scale
                 if (p + "mlp.shared_expert.gate.weight") in tensors:
                     si = cfg.shared_intermediate
                     sg, su, sd = (get(p + f"mlp.shared_expert.{n}.weight") for n in ("gate", "up", "down"))
@@ -155,6 +164,20 @@ class MoeDecoderModel(LlamaModel):
         if ffn.shared_gate_up is not None and not (ffn.shared_replicated and self.w.tp_rank != 0):
             sq, ss = ops.silu_mul_quant(ffn.shared_gate_up(xq, xs))
             shared = ffn.shared_down(sq, ss)  # this rank's partial of the shared expert (rank 0's whole, if replicated)
+        if ffn.residency is not None:
+            # host-tier experts: translate expert -> arena slot (uploading what is missing), in waves if needed
+            local = ids - ffn.e_lo
+            local = torch.where((local >= 0) & (local < ffn.residency.n), local, torch.full_like(local, -1))
+            part = ffn.residency.run(local, lambda ids_slot, arena: moe_ops.moe_ffn_fp8(
+                xq, xs, ids_slot, wt, arena.gate_up, arena.gate_up_scale, arena.down, arena.down_scale, e_lo=0, base=None).float())
+            if part is None:  # no token of this step uses a local expert
+                part = torch.zeros_like(h, dtype=torch.float32)
+            out = h.float() + part + (shared.float() if shared is not None else 0)
+            partial = out.to(torch.bfloat16)
+            if self.tp == 1:
+                h.copy_(partial)
+                return h
+            return self.collective.allreduce_rows((part + (shared.float() if shared is not None else 0)).to(torch.bfloat16), h)
         if self.tp == 1:
             return moe_ops.moe_ffn_fp8(xq, xs, ids, wt, ffn.gate_up, ffn.gate_up_scale, ffn.down, ffn.down_scale,
                                        e_lo=ffn.e_lo, base=h, extra=shared, out=h)

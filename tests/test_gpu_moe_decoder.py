@@ -39,3 +39,33 @@ def test_moe_decoder_gpu_matches_cpu_and_graphs():
     b = LLMEngine(model, max_batch=2, max_seq_len=96, use_graphs=True).generate(prompts, 8)
     assert torch.equal(a.tokens, b.tokens)
     check_status()
+
+
+def test_host_tier_experts_match_all_resident():
+    """Experts behind a 3-slot HBM arena (uploads on demand, waves when a step needs more) give the same logits."""
+    import torch
+    from gpu_common import check_status, require_gpu_lib
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.llama import StepBuffers
+    from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from mfq_b200.models.moe_lm import MoeConfig, init_weights
+    require_gpu_lib()
+    cfg = MoeDecoderConfig.tiny()
+    tensors = init_weights(MoeConfig(head_dim=128, hidden_size=256, moe_intermediate=128, shared_intermediate=128), seed=4, std=0.05)
+    prompt = torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(3))
+
+    def logits(weights):
+        eng = LLMEngine(MoeDecoderModel(cfg, weights), max_batch=2, max_seq_len=64, use_graphs=False)
+        eng.cache.assign(0, 1, 24)
+        step = StepBuffers(input_ids=prompt.cuda().int(), positions=torch.arange(24, dtype=torch.int32, device="cuda"),
+                           slots=eng.cache.slots(1, 0, 24).cuda(), cu_seqlens=[0, 24])
+        return eng.model.forward(step, eng.cache, prefill=True).float().cpu()
+
+    full = logits(MoeWeights.from_tensors(cfg, tensors, "cuda"))
+    tiered_w = MoeWeights.from_tensors(cfg, tensors, "cuda", expert_slots=3)
+    tiered = logits(tiered_w)
+    check_status()
+    res = tiered_w.layers[0].moe.residency
+    assert res is not None and res.stats["uploads"] >= 3 and res.stats["waves"] >= 2  # 8 experts, 3 slots
+    scale = float(full.abs().max())
+    assert float((full - tiered).abs().max()) <= 0.02 * scale  # same FP8 experts; only the summation order differs
