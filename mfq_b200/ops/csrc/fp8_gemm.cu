@@ -122,7 +122,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const size_t half = size_t(ag_epoch & 1u) * size_t(p.M) * p.K;
     const uint4* src = reinterpret_cast<const uint4*>(ag.x_shard);
     const size_t nvec = shard_bytes / 16;
-    for (int r = 0; r < ag.world; ++r) {
+    for (int rr = 0; rr < ag.world; ++rr) {
+      const int r = (ag.rank + rr) % ag.world;  // own copy first, then a different destination on every rank (no incast)
       uint4* dst = reinterpret_cast<uint4*>(ag.x_full[r] + half + size_t(ag.rank) * shard_bytes);
       for (size_t v = size_t(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += size_t(ag.push_ctas) * blockDim.x) dst[v] = src[v];
       float* sdst = ag.xs_full[r] + size_t(ag_epoch & 1u) * p.M + size_t(ag.rank) * ag.shard_rows;
@@ -141,7 +142,19 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
     return;
   }
-  const int n_tile = int(blockIdx.x) - (gather ? p.ag.push_ctas : 0), t_tile = blockIdx.y, split = blockIdx.z;
+  const int n_tile = int(blockIdx.x) - (gather ? p.ag.push_ctas : 0), split = blockIdx.z;
+  // Reduce-scatter: rank r starts with the token tiles owned by rank r+1 and ends with its own, so that at any moment
+  // the W ranks push their partials to W different owners instead of all into one GPU's NVLink ingress.
+  int t_tile = blockIdx.y;
+  if (p.ar.world > 1 && p.ar.mode == 1) {
+    t_tile = int((blockIdx.y + unsigned(p.ar.rank + 1) * (gridDim.y / unsigned(p.ar.world))) % gridDim.y);
+  } else if (gather && gridDim.y % unsigned(p.ag.world) == 0) {
+    // All-gather: shards reach this rank in the order own, rank-1, rank-2, ... (see the push loop), so the token
+    // tiles are visited in that order and the first tiles never wait for the last shard to arrive.
+    const int per = int(gridDim.y) / p.ag.world;
+    const int shard = (p.ag.rank - int(blockIdx.y) / per + p.ag.world) % p.ag.world;
+    t_tile = shard * per + int(blockIdx.y) % per;
+  }
   const int n_tiles_x = int(gridDim.x) - (gather ? p.ag.push_ctas : 0);
   const int n0 = n_tile * kTileN;
   int t0 = t_tile * BT, row_end = p.M, expert = 0;
@@ -394,9 +407,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           if (lane == 0) mbar_arrive(&epi_bar[2]);
           bool met = mbar_wait(&epi_bar[2], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
           if (met && threadIdx.x == 64) {
-            for (int r = 0; r < ar.world; ++r)
-              if (r != ar.rank)
-                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[r] + tile_id) : "memory");
+            // one system-scope fence orders the whole CTA's partial (observed through the mbarrier) before the W-1
+            // flag updates, which can then be relaxed and leave back to back instead of one release round trip each
+            __threadfence_system();
+            for (int r = 0; r < ar.world; ++r) {
+              const int peer = (ar.rank + 1 + r) % ar.world;
+              if (peer != ar.rank)
+                asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[peer] + tile_id) : "memory");
+            }
             const uint32_t* my_flag = ar.flags[ar.rank] + tile_id;
             const unsigned long long t_start = globaltimer_ns();
             uint32_t seen, spins = 0;
@@ -416,16 +434,28 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           met = met && mbar_wait(&epi_bar[3], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
           owner = met && !*abort_flag;
           if (owner) {
+            // Sum the W partials in rank order.  All ranks' loads of a group of 4 token columns are issued before the
+            // first add, so the (remote) round trips overlap instead of running one rank after the other.
 #pragma unroll
-            for (int tt = 0; tt < CW; ++tt) acc[tt] = 0.f;
-            for (int r = 0; r < ar.world; ++r) {
-              const float* part = ar.bufs[r] + off + row + col0 * kTileN;  // buffer of rank r, same slot (peer loads)
-              float v[CW];
+            for (int c0 = 0; c0 < CW; c0 += 4) {
+              float v[8][4];
 #pragma unroll
-              for (int tt = 0; tt < CW; ++tt)
-                asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v[tt]) : "l"(part + tt * kTileN) : "memory");
+              for (int r = 0; r < 8; ++r) {
+                const float* part = ar.bufs[r < ar.world ? r : ar.rank] + off + row + (col0 + c0) * kTileN;
 #pragma unroll
-              for (int tt = 0; tt < CW; ++tt) acc[tt] += v[tt];
+                for (int j = 0; j < 4; ++j) {
+                  v[r][j] = 0.f;
+                  if (r < ar.world)
+                    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v[r][j]) : "l"(part + j * kTileN) : "memory");
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float sum = 0.f;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) sum += v[r][j];  // zeros beyond the world size
+                acc[c0 + j] = sum;
+              }
             }
           }
           }  // all-reduce

@@ -62,8 +62,8 @@ argmax_allgather_kernel(const __nv_bfloat16* __restrict__ logits, int* __restric
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(packed) : "memory");
   }
   __threadfence_system();
-  for (int r = 0; r < ap.world; ++r)
-    if (r != ap.rank) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ap.flags[r] + row) : "memory");
+  for (int r = 0; r < ap.world; ++r)  // ordered by the fence above: relaxed updates leave back to back
+    if (r != ap.rank) asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(ap.flags[r] + row) : "memory");
   const uint32_t* my_flag = ap.flags[ap.rank] + row;
   const unsigned long long t_start = globaltimer_ns();
   uint32_t seen, spins = 0;
@@ -143,8 +143,9 @@ allreduce_rows_kernel(const __nv_bfloat16* __restrict__ partial, const __nv_bflo
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();  // orders the CTA's row (observed through the barrier above) before the relaxed updates
     for (int r = 0; r < rp.world; ++r)
-      if (r != rp.rank) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(rp.flags[r] + row) : "memory");
+      if (r != rp.rank) asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(rp.flags[r] + row) : "memory");
     const uint32_t* my_flag = rp.flags[rp.rank] + row;
     const unsigned long long t_start = globaltimer_ns();
     uint32_t seen, spins = 0;
@@ -173,12 +174,19 @@ allreduce_rows_kernel(const __nv_bfloat16* __restrict__ partial, const __nv_bflo
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = __bfloat162float(bb[j]);
     }
-    for (int r = 0; r < rp.world; ++r) {
-      uint4 b;
-      const uint4* p = reinterpret_cast<const uint4*>(rp.bufs[r] + off) + v;
-      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                   : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p) : "memory");
-      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+    uint4 parts[8];  // every rank's vector is requested before the first add: the remote round trips overlap
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      parts[r] = make_uint4(0, 0, 0, 0);
+      if (r < rp.world) {
+        const uint4* p = reinterpret_cast<const uint4*>(rp.bufs[r] + off) + v;
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(parts[r].x), "=r"(parts[r].y), "=r"(parts[r].z), "=r"(parts[r].w) : "l"(p) : "memory");
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {  // rank order; bf16 zero bits beyond the world size add nothing
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&parts[r]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(bb[j]);
     }
@@ -274,7 +282,8 @@ allgather_push_kernel(const uint8_t* __restrict__ shard, size_t shard_bytes, Gat
   const uint4* src = reinterpret_cast<const uint4*>(shard);
   for (size_t v = size_t(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += size_t(gridDim.x) * blockDim.x) {
     const uint4 val = src[v];
-    for (int r = 0; r < gp.world; ++r) reinterpret_cast<uint4*>(gp.bufs[r] + base)[v] = val;
+    for (int rr = 0; rr < gp.world; ++rr)  // start with a different destination on every rank (no incast)
+      reinterpret_cast<uint4*>(gp.bufs[(gp.rank + 1 + rr) % gp.world] + base)[v] = val;
   }
   __threadfence_system();
   __syncthreads();
