@@ -107,7 +107,7 @@ def run_ours(args) -> dict:
 
     cfg = LlamaConfig.tiny() if args.tiny else LlamaConfig.llama_8b()
     batch, ctx, new = args.batch, args.context, args.steps + args.warmup + 8
-    weights = LlamaWeights.random_init(cfg, dev, seed=0, tp_rank=rank if tp > 1 else 0, tp_size=tp)
+    weights = LlamaWeights.random_init(cfg, dev, seed=0, tp_rank=rank if tp > 1 else 0, tp_size=tp, weight_format=args.weights)
     model = LlamaModel(cfg, weights, collective=collective)
     engine = LLMEngine(model, max_batch=batch, max_seq_len=ctx + 2 * new + 16)
     ops.count_launches(True)
@@ -188,7 +188,8 @@ def run_ours(args) -> dict:
         "vs_baseline": round(value / PUBLISHED_BATCHED_DECODE_TOK_S, 2), "dtype": "fp8_e4m3 weights/activations/KV, bf16 residual stream, fp32 accumulate",
         "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)", "impl": "ours",
         "config": {"model": cfg.name, "params_b": round(cfg.param_count() / 1e9, 2), "global_batch": batch * replicas, "seq_len": ctx,
-                   "parallelism": f"tp{world}" if tp > 1 else f"dp{world}", "per_gpu_batch": batch if tp == 1 else None, "kv": "fp8 paged, 16-token pages", "weights": "E4M3, 128x128 fp32 block scales",
+                   "parallelism": f"tp{world}" if tp > 1 else f"dp{world}", "per_gpu_batch": batch if tp == 1 else None, "kv": "fp8 paged, 16-token pages", "weights": "E4M3, 128x128 fp32 block scales" if args.weights == "fp8" else
+                   "4-bit codes + bf16 (scale, min) per 32 inputs, decoded inside the GEMM pipeline (LM head: E4M3)",
                    "l2": "inputs larger than L2 (every step streams all weights)"},
         "clocks": clocks,
         "e2e": {"value": round(replicas * batch * args.steps / (e2e_ms / 1e3), 2), "unit": "tok/s",
@@ -220,6 +221,8 @@ def main() -> None:
     ap.add_argument("--parallelism", choices=["dp", "tp"], default="dp",
                     help="N > 1: dp = one replica per GPU, batch per GPU fixed (weak scaling); tp = one model sharded "
                          "over the GPUs with the collectives fused into the kernels (strong scaling)")
+    ap.add_argument("--weights", choices=["fp8", "w4"], default="fp8",
+                    help="block linears in block-scaled FP8 (default) or in the 4-bit NINT-native format (single GPU)")
     ap.add_argument("--tiny", action="store_true", help="tiny model, for checking the harness itself")
     args = ap.parse_args()
     if args.warmup < 3:

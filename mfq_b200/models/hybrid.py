@@ -260,7 +260,7 @@ class HybridModel(MoeDecoderModel):
         y = gdn.recurrent(qkv, z, a, b, g.A_log, g.dt_bias, g.norm_w, state, slots, L, g.k_heads, g.v_heads, cfg.rms_eps,
                           ckpt=state_ck)
         yq, ys = self._quant(y)
-        return self._row_parallel(g.out_proj, yq, ys, h)
+        return self._row_parallel(g.out_proj, yq, ys, h=h)
 
     # -- gated attention ----------------------------------------------------------------------------------------------
     def _gated_attention(self, h, layer: HybridLayer, kv, step: StepBuffers, prefill: bool):
@@ -309,7 +309,7 @@ class HybridModel(MoeDecoderModel):
             if gate is not None:
                 o = (o.float() * torch.sigmoid(gate.float())).to(torch.bfloat16)
             aq, a_s = self._quant(o)
-        return self._row_parallel(layer.o_proj, aq, a_s, h)
+        return self._row_parallel(layer.o_proj, aq, a_s, h=h)
 
     def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
         li = self._layer_index.get(id(layer))  # None: a block outside the stack (the MTP head's attention block)

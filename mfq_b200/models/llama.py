@@ -62,6 +62,7 @@ class Fp8Linear:
 
     q: torch.Tensor
     scale: torch.Tensor
+    input_kind = "fp8"  # consumes per-row quantized E4M3 activations
 
     @classmethod
     def from_float(cls, w: torch.Tensor) -> "Fp8Linear":
@@ -75,6 +76,33 @@ class Fp8Linear:
 
     def dequant(self) -> torch.Tensor:
         return ref.dequant_block(self.q, self.scale)
+
+
+@dataclass
+class W4Linear:
+    """4-bit group-quantized weights decoded inside the GEMM pipeline (``ops/csrc/w4_gemm.cu``): the NINT-native
+    path for code widths up to 4 bits.  Consumes bf16 activations."""
+
+    w: "object"  # ops.w4.W4Weight
+    input_kind = "bf16"
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor, group_size: int = 32) -> "W4Linear":
+        from ..ops import w4
+        return cls(w4.quantize_torch(w, group_size))
+
+    @classmethod
+    def from_nint(cls, t, device) -> "W4Linear":
+        from ..ops import w4
+        return cls(w4.from_nint(t).to(device))
+
+    def __call__(self, x: torch.Tensor, residual: torch.Tensor | None = None, out=None):
+        from ..ops import w4
+        return w4.w4_gemm(x, self.w, residual=residual, out=out)
+
+    def dequant(self) -> torch.Tensor:
+        from ..ops import w4
+        return w4.dequantize(self.w)
 
 
 @dataclass
@@ -112,7 +140,7 @@ class LlamaWeights:
 
     @classmethod
     def random_init(cls, cfg: LlamaConfig, device, seed: int = 0, std: float = 0.02, tp_rank: int = 0,
-                    tp_size: int = 1, mtp: bool = False) -> "LlamaWeights":
+                    tp_size: int = 1, mtp: bool = False, weight_format: str = "fp8") -> "LlamaWeights":
         """N(0, std) weights, quantized layer by layer on ``device``.  Every rank draws the full matrix from the
         same seed and keeps its shard, so TP=n and TP=1 hold the same model."""
         dev = torch.device(device)
@@ -123,6 +151,10 @@ class LlamaWeights:
 
         def rnd(rows, cols):
             return torch.randn((rows, cols), generator=gen, device=dev, dtype=torch.float32).mul_(std).to(torch.bfloat16)
+
+        lin = W4Linear.from_float if weight_format == "w4" else Fp8Linear.from_float  # block linears; the head stays FP8
+        if weight_format == "w4" and tp_size > 1:
+            raise ValueError("the 4-bit path is single-GPU for now")
 
         def rows_shard(w, parts):  # split output rows into tp_size equal shards, keep ours
             return w.reshape(tp_size, parts // tp_size, -1)[tp_rank] if tp_size > 1 else w
@@ -139,11 +171,11 @@ class LlamaWeights:
                 wd = wd.reshape(h, tp_size, i // tp_size)[:, tp_rank].contiguous()
             layers.append(LlamaLayer(
                 attn_norm=torch.ones(h, dtype=torch.bfloat16, device=dev),
-                qkv=Fp8Linear.from_float(torch.cat([wq, wk, wv], 0)),
-                o_proj=Fp8Linear.from_float(wo),
+                qkv=lin(torch.cat([wq, wk, wv], 0)),
+                o_proj=lin(wo),
                 mlp_norm=torch.ones(h, dtype=torch.bfloat16, device=dev),
-                gate_up=Fp8Linear.from_float(torch.cat([wg, wu], 0)),
-                down=Fp8Linear.from_float(wd),
+                gate_up=lin(torch.cat([wg, wu], 0)),
+                down=lin(wd),
             ))
             del wq, wk, wv, wo, wg, wu, wd
         embed = rnd(cfg.vocab_size, h)
@@ -211,11 +243,30 @@ class LlamaModel:
     def _silu_quant(self, gu):
         return ops.silu_mul_quant(gu) if gu.is_cuda else ref.silu_mul_quant(gu)
 
-    def _row_parallel(self, lin: Fp8Linear, xq, xs, h):
+    def _row_parallel(self, lin, *x_in, h):
         """Input-sharded projection + residual.  At TP>1 every rank adds its partial; rank 0 carries the residual."""
         if self.tp == 1:
-            return lin(xq, xs, residual=h, out=h if h.is_cuda else None)
-        return self.collective.row_parallel_linear(lin, xq, xs, h)
+            return lin(*x_in, residual=h, out=h if h.is_cuda else None)
+        return self.collective.row_parallel_linear(lin, *x_in, h)
+
+    # inputs of a linear in the form it consumes: (fp8 rows, multipliers) or (bf16,)
+    def _in_norm(self, h, norm_w, lin):
+        if lin.input_kind == "bf16":
+            if h.is_cuda:
+                return (ops.rmsnorm_quant(h, norm_w, self.cfg.rms_eps, want_q=False, want_y=True)[2],)
+            return (ref.rmsnorm(h, norm_w, self.cfg.rms_eps),)
+        return self._norm_quant(h, norm_w)
+
+    def _in_plain(self, x, lin):
+        return (x,) if lin.input_kind == "bf16" else self._quant(x)
+
+    def _in_silu(self, gu, lin):
+        if lin.input_kind == "bf16":
+            if gu.is_cuda:
+                return (ops.kernels.silu_mul(gu),)
+            i = gu.shape[1] // 2
+            return ((torch.nn.functional.silu(gu[:, :i].float()) * gu[:, i:].float()).to(torch.bfloat16),)
+        return self._silu_quant(gu)
 
     # -- attention ----------------------------------------------------------------------------------------------
     def _attention(self, qkv, kv, step: StepBuffers, prefill: bool):
@@ -255,21 +306,17 @@ class LlamaModel:
     # -- feed-forward -------------------------------------------------------------------------------------------
     def _ffn(self, h, layer):
         """Dense SwiGLU block: ``h + down(silu(gate(x)) * up(x))`` with ``x = rmsnorm(h)``."""
-        xq, xs = self._norm_quant(h, layer.mlp_norm)
-        gu = layer.gate_up(xq, xs)
-        hq_, hs = self._silu_quant(gu)
-        return self._row_parallel(layer.down, hq_, hs, h)
+        gu = layer.gate_up(*self._in_norm(h, layer.mlp_norm, layer.gate_up))
+        return self._row_parallel(layer.down, *self._in_silu(gu, layer.down), h=h)
 
     # -- forward ------------------------------------------------------------------------------------------------
     def _embed(self, ids):
         return ops.embed(ids, self.w.embed) if self.w.embed.is_cuda else self.w.embed[ids.long()].clone()
 
     def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
-        xq, xs = self._norm_quant(h, layer.attn_norm)
-        qkv = layer.qkv(xq, xs)
+        qkv = layer.qkv(*self._in_norm(h, layer.attn_norm, layer.qkv))
         attn = self._attention(qkv, kv, step, prefill)
-        aq, a_s = self._quant(attn)
-        h = self._row_parallel(layer.o_proj, aq, a_s, h)
+        h = self._row_parallel(layer.o_proj, *self._in_plain(attn, layer.o_proj), h=h)
         return self._ffn(h, layer)
 
     def _head(self, h, norm, gather_logits: bool):

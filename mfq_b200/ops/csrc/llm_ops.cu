@@ -508,3 +508,36 @@ extern "C" int mfq_decode_advance(const int* sampled, int* input_ids, int* posit
                                                              block_table, B, max_pages, page_size, active);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU without quantization: out[row, :I] = silu(x[row, :I]) * x[row, I:2I] in bf16 (input of bf16-activation GEMMs).
+// ---------------------------------------------------------------------------------------------
+namespace mfq {
+__global__ void silu_mul_bf16_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int I, int in_stride) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * in_stride;
+  for (int v = threadIdx.x; v < I / 8; v += blockDim.x) {
+    const uint4 a = *reinterpret_cast<const uint4*>(xr + v * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(xr + I + v * 8);
+    const __nv_bfloat16* ab = reinterpret_cast<const __nv_bfloat16*>(&a);
+    const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+    uint4 o;
+    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g = __bfloat162float(ab[j]);
+      ob[j] = __float2bfloat16(g / (1.f + __expf(-g)) * __bfloat162float(bb[j]));
+    }
+    *reinterpret_cast<uint4*>(out + row * I + v * 8) = o;
+  }
+}
+}  // namespace mfq
+
+extern "C" int mfq_silu_mul_bf16(const void* x, void* out, int M, int I, int in_stride, cudaStream_t stream) {
+  if (M <= 0 || I % 8 || in_stride % 8) return -1;
+  mfq::launch_kernel(mfq::silu_mul_bf16_kernel, dim3(M), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x),
+                     static_cast<__nv_bfloat16*>(out), I, in_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}

@@ -97,6 +97,14 @@ def silu_mul_quant(gate_up: torch.Tensor, *, q_out=None, scale_out=None):
     return q_out, scale_out
 
 
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """``[M, 2I]`` (gate | up) -> bf16 ``silu(gate) * up`` ``[M, I]`` (input of the bf16-activation GEMMs)."""
+    m, two_i = gate_up.shape
+    out = torch.empty((m, two_i // 2), dtype=torch.bfloat16, device=gate_up.device)
+    check(lib().mfq_silu_mul_bf16(ptr(gate_up), ptr(out), m, two_i // 2, gate_up.stride(0), stream_ptr()), "silu_mul")
+    return out
+
+
 def gate_quant_rows(x: torch.Tensor, gate: torch.Tensor):
     """fp8 rows of ``x * sigmoid(gate)`` (+ per-row multipliers); ``gate`` may be a strided column slice."""
     m, k = x.shape

@@ -27,3 +27,22 @@ def test_kv_pages_are_released():
     assert eng.cache.allocator.free_pages < free0
     eng.prefill(0, torch.arange(5))
     assert eng.cache.allocator.free_pages == free0 - 1
+
+
+def test_w4_weights_decode_consistent_with_prefill():
+    """The 4-bit weight path (CPU reference of the in-pipeline-decode GEMM): a decode step continues the prefill."""
+    import torch
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.llama import LlamaConfig, LlamaModel, LlamaWeights, W4Linear
+    cfg = LlamaConfig.tiny()
+    w = LlamaWeights.random_init(cfg, "cpu", seed=1, std=0.05, weight_format="w4")
+    assert isinstance(w.layers[0].qkv, W4Linear) and w.layers[0].qkv.w.bits_per_weight <= 5.01
+    eng = LLMEngine(LlamaModel(cfg, w), max_batch=2, max_seq_len=64, device="cpu")
+    prompt = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(0))
+    first = eng.prefill(0, prompt)
+    eng.grow(0, 32)
+    eng.active.zero_()
+    eng.active[0] = 1
+    eng.decode_step(1)
+    second = int(eng.sampled[0])
+    assert eng.prefill(1, torch.cat([prompt, torch.tensor([first])])) == second
