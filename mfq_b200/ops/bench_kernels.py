@@ -69,6 +69,19 @@ def bench_gemm(m: int, n: int, k: int, reps: int, splits=None, tile=None) -> dic
             "tflops": 2 * m * n * k / ms / 1e9, "splits": splits if splits else K.pick_splits(m, n, k)}
 
 
+def bench_w4_gemm(m: int, n: int, k: int, reps: int, splits=None) -> dict:
+    """4-bit in-pipeline-decode GEMM: same shapes as the FP8 GEMM, 5 bits per weight of HBM traffic."""
+    from . import w4
+    copies = max(1, min(16, math.ceil(4 * L2_BYTES / (n * k * 5 // 8))))
+    base = w4.quantize_torch(torch.randn((n, k), device="cuda") * 0.02)
+    ws = [base] + [w4.W4Weight(base.packed.clone(), base.group.clone(), n, k, base.group_size) for _ in range(copies - 1)]
+    x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    out = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+    ms = time_ms(lambda i: w4.w4_gemm(x, ws[i % copies], out=out, splits=splits), reps)
+    byt = n * k * 5 // 8 + 2 * m * k + 2 * m * n
+    return {"kernel": "w4_gemm", "m": m, "n": n, "k": k, "us": ms * 1e3, "gbs": byt / ms / 1e6, "tflops": 2 * m * n * k / ms / 1e9}
+
+
 def bench_attn(batch: int, ctx: int, hq: int, hk: int, d: int, splits: int, reps: int) -> dict:
     pages_per = math.ceil(ctx / 16)
     layers = max(1, math.ceil(4 * L2_BYTES / (batch * ctx * hk * d * 2)))
@@ -140,6 +153,11 @@ def main() -> None:
             if name == "lm_head" and m > 64:
                 continue
             r = bench_gemm(m, n, k, args.reps)
+            r["name"] = name
+            rows.append(r)
+    for m in ((1, 64) if args.quick else (1, 16, 64, 512, 4096)):
+        for name, n, k in shapes[:4]:
+            r = bench_w4_gemm(m, n, k, args.reps)
             r["name"] = name
             rows.append(r)
     for batch, ctx in ((1, 4096), (64, 4096)):

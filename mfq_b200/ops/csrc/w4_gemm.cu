@@ -7,13 +7,13 @@
 //   warp 0      loader: per 64-wide K block one bulk copy of the packed tile (128 rows x 32 B) and one TMA tile of
 //               bf16 activations (BT x 64), into a ring of kStages stages
 //   warp 1      issues tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32 in TMEM), weights = A operand (128 rows)
-//   warps 2..5  decode: thread r owns weight row r of the tile.  A 32-bit word holds 8 codes in the order
+//   warps 2..9  decode, two teams of four warps on alternate K blocks: thread r owns weight row r of the tile.  A 32-bit word holds 8 codes in the order
 //               (c0 c2 c4 c6 | c1 c3 c5 c7) per 16-bit half, so  (w >> 4j) & 0x000F000F | 0x43004300  is the bf16 pair
 //               (128 + c_2j, 128 + c_2j+1); an exact bf16x2 subtraction of 128 and ONE bf16x2 FMA with (s, s), (-b, -b) finish two weights; the
-//               8 weights of a word are one 16-byte store into the 128B-swizzled A tile (ring of kAStages).  Group
-//               parameters come from global memory, transposed so the 128 threads read 512 contiguous bytes, and are
-//               fetched one K block ahead.  After the last block the same warps run the epilogue (they cover the
-//               four TMEM lane quarters).
+//               8 weights of a word are one 16-byte store into the 128B-swizzled A tile (ring of kAStages).  The group
+//               parameters of a K block are 512-byte rows of a [tile][group][row] table and arrive with the stage
+//               (one more bulk copy), so the decode never waits on global memory.  After the last block warps 2..5
+//               run the epilogue (they cover the four TMEM lane quarters).
 //
 // One accumulator lives in TMEM for the whole K range (the affine decode is exact, nothing is folded per block);
 // split-K partials are reduced by the last-arriving CTA in split order (deterministic).  Waits are bounded.
@@ -30,12 +30,14 @@ constexpr int kW4PackedBytes = kW4TileN * kW4BlockK / 2;  // 4096
 template <int BT>
 struct W4Cfg {
   static constexpr int kStages = BT >= 128 ? 4 : 8;
-  static constexpr int kAStages = 3;
+  static constexpr int kAStages = 4;
   static constexpr int kXBytes = BT * kW4BlockK * 2;
-  static constexpr int kStageBytes = kW4PackedBytes + kXBytes;   // packed codes + activations (both 1024-aligned)
+  static constexpr int kGroupBytes = 2048;                        // up to 4 groups x 128 rows x 4 B per K block
+  static constexpr int kXOffset = kW4PackedBytes + kGroupBytes;   // activations start 1024-aligned
+  static constexpr int kStageBytes = kXOffset + kXBytes;          // packed codes + group parameters + activations
   static constexpr int kABytes = kW4TileN * kW4BlockK * 2;      // 16 KB decoded bf16 tile
   static constexpr int kTmemCols = BT < 32 ? 32 : BT;
-  static constexpr int kThreads = 192;
+  static constexpr int kThreads = 320;  // loader, MMA issuer, 8 decode warps
   static constexpr int kSmemBytes = kStages * kStageBytes + kAStages * kABytes + 1024 + 256;
 };
 
@@ -104,13 +106,22 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) {
         const int s = i % Cfg::kStages;
         if (!mbar_wait(&empty[s], ((i / Cfg::kStages) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutProducer)) break;
         uint8_t* st = stages + s * Cfg::kStageBytes;
-        mbar_expect_tx(&full[s], Cfg::kStageBytes);
-        const uint8_t* src = p.packed + (size_t(n_tile) * kb_total + kb0 + i) * kW4PackedBytes;
+        // group parameters of the block: groups g_lo..g_hi are 512-byte rows, contiguous in the [tile][group][row] table
+        const int kb = kb0 + i;
+        const int g_lo = (kb * 8) / p.words_per_group, g_hi = (kb * 8 + 7) / p.words_per_group;
+        const uint32_t gbytes = uint32_t(g_hi - g_lo + 1) * kW4TileN * 4;
+        mbar_expect_tx(&full[s], kW4PackedBytes + gbytes + Cfg::kXBytes);
+        const uint8_t* src = p.packed + (size_t(n_tile) * kb_total + kb) * kW4PackedBytes;
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                      ::"r"(smem_u32(st)), "l"(reinterpret_cast<uint64_t>(src)), "r"(uint32_t(kW4PackedBytes)),
                      "r"(smem_u32(&full[s]))
                      : "memory");
-        tma_load_2d(st + kW4PackedBytes, &tmap_x, &full[s], (kb0 + i) * kW4BlockK, t0);
+        const uint32_t* gsrc = p.group + (size_t(n_tile) * p.groups + g_lo) * kW4TileN;
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(smem_u32(st + kW4PackedBytes)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(gbytes),
+                     "r"(smem_u32(&full[s]))
+                     : "memory");
+        tma_load_2d(st + Cfg::kXOffset, &tmap_x, &full[s], kb * kW4BlockK, t0);
       }
     }
   } else if (warp == 1) {
@@ -122,7 +133,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) {
         if (!mbar_wait(&a_ready[a], (i / Cfg::kAStages) & 1, abort_flag, p.status, kStatusTimeoutMma)) break;
         tc_fence_after();
         const uint32_t a_addr = smem_u32(a_tiles + a * Cfg::kABytes);
-        const uint32_t b_addr = smem_u32(stages + s * Cfg::kStageBytes + kW4PackedBytes);
+        const uint32_t b_addr = smem_u32(stages + s * Cfg::kStageBytes + Cfg::kXOffset);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_f16(tmem_acc, umma_desc_k_sw128(a_addr + ks * 32), umma_desc_k_sw128(b_addr + ks * 32), idesc, (i | ks) != 0);
@@ -132,38 +143,38 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) {
       tc_commit(acc_done);
     }
   } else {
-    // ----- decode warps (thread = weight row), then epilogue -----
-    const int row = (warp - 2) * 32 + lane;
-    const uint32_t* gp = p.group + size_t(n_tile) * p.groups * kW4TileN + row;
-    const int words_per_block = kW4BlockK / 8;  // 8
-    auto group_of = [&](int kb, int w) { return (kb * words_per_block + w) / p.words_per_group; };
-    // group parameters of the first block; every later block is fetched while the previous one is converted
-    uint32_t gcur[words_per_block], gnext[words_per_block];
-    if (nkb > 0) {
-#pragma unroll
-      for (int w = 0; w < words_per_block; ++w) gcur[w] = __ldg(gp + size_t(group_of(kb0, w)) * kW4TileN);
-    }
+    // ----- decode warps, then epilogue -----
+    // Two teams of four warps (thread = weight row) take alternate K blocks, so two blocks are being converted at
+    // any time and the per-block latency chain (barrier wait, shared loads, convert, stores, proxy fence) overlaps.
+    const int team = (warp - 2) >> 2;
+    const int row = ((warp - 2) & 3) * 32 + lane;
+    // group of the block's first word, kept incrementally (no integer division in the loop): word index W lies in
+    // group W / words_per_group, the words of block kb are kb * 8 + {0..7}
+    const int wpg = p.words_per_group;
+    int r_block = ((kb0 + team) * 8) % wpg;  // offset of the block's word 0 inside its group
     bool ok = true;
-    for (int i = 0; i < nkb; ++i) {
+    for (int i = team; i < nkb; i += 2) {
       const int s = i % Cfg::kStages, a = i % Cfg::kAStages;
-      if (i + 1 < nkb) {
-#pragma unroll
-        for (int w = 0; w < words_per_block; ++w) gnext[w] = __ldg(gp + size_t(group_of(kb0 + i + 1, w)) * kW4TileN);
-      }
       ok = mbar_wait(&full[s], (i / Cfg::kStages) & 1, abort_flag, p.status, kStatusTimeoutEpilogue) &&
            mbar_wait(&a_free[a], ((i / Cfg::kAStages) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      const uint4* src = reinterpret_cast<const uint4*>(stages + s * Cfg::kStageBytes + row * 32);
-      const uint4 lo = src[0], hi = src[1];
+      const uint8_t* st = stages + s * Cfg::kStageBytes;
+      const uint4 lo = *reinterpret_cast<const uint4*>(st + row * 32), hi = *reinterpret_cast<const uint4*>(st + row * 32 + 16);
+      const uint32_t* gsm = reinterpret_cast<const uint32_t*>(st + kW4PackedBytes) + row;  // [group - first group][128 rows]
       const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
       uint8_t* dst_row = a_tiles + a * Cfg::kABytes + row * 128;
+      int local = 0, left = wpg - r_block;  // group index among the stage's groups; words left in that group
+      uint32_t s2 = 0, b2 = 0;
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
-        const uint32_t g = gcur[w];
-        uint32_t s2, b2;  // (s, s) and (bias, bias) as bf16x2
-        asm("prmt.b32 %0, %1, %1, 0x1010;" : "=r"(s2) : "r"(g));
-        asm("prmt.b32 %0, %1, %1, 0x3232;" : "=r"(b2) : "r"(g));
+        if (w == 0 || left == 0) {  // a new group starts: fetch (s, s) and (-b, -b) as bf16x2
+          if (w != 0) { ++local; left = wpg; }
+          const uint32_t g = gsm[local * kW4TileN];
+          asm("prmt.b32 %0, %1, %1, 0x1010;" : "=r"(s2) : "r"(g));
+          asm("prmt.b32 %0, %1, %1, 0x3232;" : "=r"(b2) : "r"(g));
+        }
+        --left;
         uint4 o;
         uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
@@ -181,9 +192,9 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) {
         mbar_arrive(&a_ready[a]);
         mbar_arrive(&empty[s]);  // this warp is done with the packed codes of the stage
       }
-#pragma unroll
-      for (int w = 0; w < words_per_block; ++w) gcur[w] = gnext[w];
+      r_block = (r_block + 16) % wpg;  // my next block is two blocks (sixteen words) further
     }
+    if (warp >= 6) ok = false;  // the epilogue is run by warps 2..5 (one per TMEM lane quarter)
     // ----- epilogue: TMEM -> registers -> (split-K reduce) -> bf16 -----
     if (ok) ok = mbar_wait(acc_done, 0, abort_flag, p.status, kStatusTimeoutEpilogue);
     ok = __all_sync(0xffffffffu, ok);
@@ -284,11 +295,11 @@ static int launch_w4(const W4Params& p0, const void* x, int splits, size_t ws_by
 }  // namespace mfq
 
 // x [M, K] bf16 row-major; packed / group in the layouts of W4Params (see w4_repack on the Python side);
-// group_size in {16, 24, 32, 64} (a multiple of 8), K a multiple of 64 and of group_size; out [M, N] bf16.
+// group_size >= 16 and a multiple of 8 (16, 24, 32, 64 ...: at most four groups meet a 64-wide K block), K a multiple of 64 and of group_size; out [M, N] bf16.
 extern "C" int mfq_w4_gemm(const void* packed, const void* group, const void* x, void* out, const void* residual, float* ws,
                            size_t ws_bytes, int* counters, int counters_len, int* status, int M, int N, int K, int group_size,
                            int token_tile, int splits, cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || K % 64 || group_size < 8 || group_size % 8 || K % group_size) return -1;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 64 || group_size < 16 || group_size % 8 || K % group_size) return -1;
   mfq::W4Params p{static_cast<const uint8_t*>(packed), static_cast<const uint32_t*>(group), static_cast<__nv_bfloat16*>(out),
                   static_cast<const __nv_bfloat16*>(residual), ws, counters, status, M, N, K, K / group_size, group_size / 8, 0};
   switch (token_tile) {
