@@ -2,7 +2,9 @@
 
 Each case launches one kernel three times on inputs of a few hundred MB (larger than the 126 MB L2, small enough
 for a multi-pass capture to finish in about a minute) and exits.  Cases: ``gemm_prefill`` (M=4096, N=K=4096),
-``gemm_decode`` (M=64, N=28672, K=4096), ``attn_decode`` (64 sequences x 4096 tokens), ``attn_prefill`` (T=2048).
+``gemm_decode`` (M=64, N=28672, K=4096), ``attn_decode`` (64 sequences x 4096 tokens), ``attn_prefill`` (T=2048),
+``w4_decode`` / ``w4_prefill`` (the 4-bit in-pipeline-decode GEMM at the same shapes), ``gdn_decode`` (Gated DeltaNet step,
+64 sequences), ``moe_dispatch`` (expert-parallel dispatch + combine kernels at world 1, 4096 tokens).
 """
 
 from __future__ import annotations
@@ -55,8 +57,55 @@ def attn_prefill() -> None:
         K.attn_prefill_bf16(q, k, v, 0.088)
 
 
+def w4_gemm(m: int, n: int, k: int) -> None:
+    from . import w4
+    base = w4.quantize_torch(torch.randn((n, k), device="cuda") * 0.02)
+    ws = [base] + [w4.W4Weight(base.packed.clone(), base.group.clone(), n, k, base.group_size) for _ in range(2)]
+    x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    out = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+    for i in range(3):
+        w4.w4_gemm(x, ws[i], out=out)
+
+
+def gdn_decode() -> None:
+    """Gated DeltaNet decode step: 64 sequences x 32 value heads, one token each (state 2 MB per sequence)."""
+    from . import gdn
+    b, hk, hv, d = 64, 16, 32, 128
+    c = (2 * hk + hv) * d
+    x = torch.randn((b, c), device="cuda").to(torch.bfloat16)
+    z = torch.randn((b, hv * d), device="cuda").to(torch.bfloat16)
+    a = torch.randn((b, hv), device="cuda").to(torch.bfloat16)
+    bb = torch.randn((b, hv), device="cuda").to(torch.bfloat16)
+    w = torch.randn((c, 4), device="cuda") * 0.5
+    slot = torch.arange(b, dtype=torch.int32, device="cuda")
+    states = [torch.randn((b, hv, d, d), device="cuda") * 0.1 for _ in range(3)]  # 3 x 134 MB: each launch streams its own
+    conv = torch.zeros((b, 3, c), device="cuda")
+    al, dt, nw = torch.zeros(hv, device="cuda"), torch.zeros(hv, device="cuda"), torch.ones(d, device="cuda")
+    for i in range(3):
+        qkv = gdn.conv(x, conv, w, slot, 1)
+        gdn.recurrent(qkv, z, a, bb, al, dt, nw, states[i], slot, 1, hk, hv)
+
+
+def moe_dispatch() -> None:
+    """Dispatch + combine kernels on one GPU (world 1): 4096 tokens, hidden 7168, 256 experts, top-8."""
+    from . import moe
+    from ..parallel.expert_parallel import ExpertParallel
+    t, h, e, k = 4096, 7168, 256, 8
+    ep = ExpertParallel(None, torch.device("cuda"), num_experts=e, top_k=k, hidden=h, max_tokens=t)
+    xq = _fp8((t, h))
+    xs = torch.rand(t, device="cuda")
+    ids = torch.stack([torch.randperm(e, device="cuda")[:k] for _ in range(t)]).to(torch.int32)
+    wt = torch.rand((t, k), device="cuda")
+    y = torch.zeros((t * k, h), dtype=torch.bfloat16, device="cuda")
+    for _ in range(3):
+        recv = ep.dispatch(xq, xs, ids, wt)
+        plan = moe.plan_routes(recv.ids, 0, e)
+        ep.combine(y, plan, recv)
+
+
 CASES = {"gemm_prefill": lambda: gemm(4096, 4096, 4096), "gemm_decode": lambda: gemm(64, 28672, 4096),
-         "attn_decode": attn_decode, "attn_prefill": attn_prefill}
+         "attn_decode": attn_decode, "attn_prefill": attn_prefill, "w4_decode": lambda: w4_gemm(64, 28672, 4096),
+         "w4_prefill": lambda: w4_gemm(4096, 4096, 4096), "gdn_decode": gdn_decode, "moe_dispatch": moe_dispatch}
 
 if __name__ == "__main__":
     CASES[sys.argv[1]]()
