@@ -1,4 +1,5 @@
-// Group-quantized 4-bit weight GEMM (NINT-native path):  out[t, n] = sum_k x[t, k] * (s[n, g(k)] * q[n, k] - b[n, g(k)])
+// Group-quantized 4-bit weight GEMM (NINT-native and MXFP4 paths):
+//   out[t, n] = sum_k x[t, k] * w[n, k],   w = s[n, g(k)] * q[n, k] - b[n, g(k)]  (NINT)   or   e2m1(q[n, k]) * 2^(e[n, g(k)] - 127)  (MXFP4)
 //
 // The NINT families store b-bit codes with an affine (scale, min) pair per group of `gs` consecutive inputs.  For
 // code widths up to 4 bits the checkpoint is repacked once, at load, into a GPU layout (w4_repack in Python) and this
@@ -52,7 +53,8 @@ struct W4Params {
   int M, N, K, groups, words_per_group, kb_per_split;
 };
 
-template <int BT>
+// KIND 0: affine codes (NINT):  w = s * c - b.   KIND 1: MXFP4:  w = e2m1(c) * 2^(e - 127), one E8M0 exponent per 32.
+template <int BT, int KIND>
 __global__ void __launch_bounds__(W4Cfg<BT>::kThreads, 1)
 w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) {
   using Cfg = W4Cfg<BT>;
@@ -177,12 +179,38 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) {
         --left;
         uint4 o;
         uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+        if constexpr (KIND == 0) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t pair = ((words[w] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // bf16 (128 + c, 128 + c')
-          uint32_t qf;  // (c, c') exactly: integers below 256 are exact in bf16, so is the subtraction
-          asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(qf) : "r"(pair), "r"(0x43004300u));
-          asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(ov[j]) : "r"(qf), "r"(s2), "r"(b2));  // s * c - b, one rounding
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t pair = ((words[w] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // bf16 (128 + c, 128 + c')
+            uint32_t qf;  // (c, c') exactly: integers below 256 are exact in bf16, so is the subtraction
+            asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(qf) : "r"(pair), "r"(0x43004300u));
+            asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(ov[j]) : "r"(qf), "r"(s2), "r"(b2));  // s * c - b, one rounding
+          }
+        } else {
+          // E2M1 magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6} as bf16 = high bytes {00,3F,3F,3F,40,40,40,40}, low bytes
+          // {00,00,80,C0,00,40,80,C0}: byte-permute instructions look four codes up at once (selector = code & 7)
+          const uint32_t idx = words[w] & 0x77777777u;
+          uint32_t hiA, hiB, loA, loB;  // A: nibbles 0..3 (even columns), B: nibbles 4..7 (odd columns)
+          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(hiA) : "r"(0x3F3F3F00u), "r"(0x40404040u), "r"(idx & 0xFFFFu));
+          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(hiB) : "r"(0x3F3F3F00u), "r"(0x40404040u), "r"(idx >> 16));
+          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(loA) : "r"(0xC0800000u), "r"(0xC0804000u), "r"(idx & 0xFFFFu));
+          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(loB) : "r"(0xC0800000u), "r"(0xC0804000u), "r"(idx >> 16));
+          uint32_t a01, a23, b01, b23;  // (bf16 n0, bf16 n1), (n2, n3), (n4, n5), (n6, n7)
+          asm("prmt.b32 %0, %1, %2, 0x5140;" : "=r"(a01) : "r"(loA), "r"(hiA));
+          asm("prmt.b32 %0, %1, %2, 0x7362;" : "=r"(a23) : "r"(loA), "r"(hiA));
+          asm("prmt.b32 %0, %1, %2, 0x5140;" : "=r"(b01) : "r"(loB), "r"(hiB));
+          asm("prmt.b32 %0, %1, %2, 0x7362;" : "=r"(b23) : "r"(loB), "r"(hiB));
+          uint32_t mag[4];  // word j = (column 2j, column 2j+1) = (nibble j, nibble j + 4)
+          asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(mag[0]) : "r"(a01), "r"(b01));
+          asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(mag[1]) : "r"(a01), "r"(b01));
+          asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(mag[2]) : "r"(a23), "r"(b23));
+          asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(mag[3]) : "r"(a23), "r"(b23));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t sign = ((words[w] >> (4 * j)) & 0x00080008u) << 12;  // code bit 3 -> bf16 sign bit
+            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(ov[j]) : "r"(mag[j] | sign), "r"(s2));  // exact: s2 is a power of two
+          }
         }
         *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) = o;  // 128-byte swizzle: chunk ^= row % 8
       }
@@ -267,7 +295,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) {
   if (warp == 1) tmem_dealloc(tmem_acc, Cfg::kTmemCols);
 }
 
-template <int BT>
+template <int BT, int KIND>
 static int launch_w4(const W4Params& p0, const void* x, int splits, size_t ws_bytes, int counters_len, cudaStream_t stream) {
   using Cfg = W4Cfg<BT>;
   W4Params p = p0;
@@ -284,11 +312,11 @@ static int launch_w4(const W4Params& p0, const void* x, int splits, size_t ws_by
   }
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(w4_gemm_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(w4_gemm_kernel<BT, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
       return -6;
     attr_set = true;
   }
-  launch_kernel(w4_gemm_kernel<BT>, dim3(n_tiles, t_tiles, splits), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tx, p);
+  launch_kernel(w4_gemm_kernel<BT, KIND>, dim3(n_tiles, t_tiles, splits), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
@@ -298,15 +326,19 @@ static int launch_w4(const W4Params& p0, const void* x, int splits, size_t ws_by
 // group_size >= 16 and a multiple of 8 (16, 24, 32, 64 ...: at most four groups meet a 64-wide K block), K a multiple of 64 and of group_size; out [M, N] bf16.
 extern "C" int mfq_w4_gemm(const void* packed, const void* group, const void* x, void* out, const void* residual, float* ws,
                            size_t ws_bytes, int* counters, int counters_len, int* status, int M, int N, int K, int group_size,
-                           int token_tile, int splits, cudaStream_t stream) {
+                           int token_tile, int splits, int kind, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || K % 64 || group_size < 16 || group_size % 8 || K % group_size) return -1;
+  if (kind != 0 && (kind != 1 || group_size != 32)) return -1;  // MXFP4 blocks are 32 wide
   mfq::W4Params p{static_cast<const uint8_t*>(packed), static_cast<const uint32_t*>(group), static_cast<__nv_bfloat16*>(out),
                   static_cast<const __nv_bfloat16*>(residual), ws, counters, status, M, N, K, K / group_size, group_size / 8, 0};
+#define MFQ_W4(BT) (kind == 0 ? mfq::launch_w4<BT, 0>(p, x, splits, ws_bytes, counters_len, stream) \
+                              : mfq::launch_w4<BT, 1>(p, x, splits, ws_bytes, counters_len, stream))
   switch (token_tile) {
-    case 16: return mfq::launch_w4<16>(p, x, splits, ws_bytes, counters_len, stream);
-    case 32: return mfq::launch_w4<32>(p, x, splits, ws_bytes, counters_len, stream);
-    case 64: return mfq::launch_w4<64>(p, x, splits, ws_bytes, counters_len, stream);
-    case 128: return mfq::launch_w4<128>(p, x, splits, ws_bytes, counters_len, stream);
+    case 16: return MFQ_W4(16);
+    case 32: return MFQ_W4(32);
+    case 64: return MFQ_W4(64);
+    case 128: return MFQ_W4(128);
     default: return -1;
   }
+#undef MFQ_W4
 }

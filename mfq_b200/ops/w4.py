@@ -30,9 +30,10 @@ class W4Weight:
     n: int
     k: int
     group_size: int
+    kind: int = 0  # 0: affine codes (NINT), 1: MXFP4 (E2M1 codes, one power-of-two multiplier per 32 inputs)
 
     def to(self, device) -> "W4Weight":
-        return W4Weight(self.packed.to(device), self.group.to(device), self.n, self.k, self.group_size)
+        return W4Weight(self.packed.to(device), self.group.to(device), self.n, self.k, self.group_size, self.kind)
 
     @property
     def bits_per_weight(self) -> float:
@@ -102,6 +103,24 @@ def quantize_torch(w: torch.Tensor, group_size: int = 32) -> W4Weight:
     return repack_torch(codes, s, -lo, group_size)
 
 
+_E2M1 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], dtype=np.float32)
+
+
+def from_mxfp4(t) -> W4Weight:
+    """MXFP4 tensor (two E2M1 codes per byte, low nibble first; one E8M0 exponent per 32) -> :class:`W4Weight`."""
+    rows, cols = t.shape
+    if cols % BLOCK_K:
+        raise ValueError("MXFP4 rows must be a multiple of 64 wide for the GEMM layout")
+    raw = np.asarray(t.values, dtype=np.uint8).reshape(rows, cols // 2)
+    codes = np.empty((rows, cols), dtype=np.uint8)
+    codes[:, 0::2], codes[:, 1::2] = raw & 0xF, raw >> 4
+    w = repack(codes, np.zeros((rows, cols // 32), np.float32), np.zeros((rows, cols // 32), np.float32), 32)
+    e = np.zeros((w.packed.shape[0] * TILE_N, cols // 32), dtype=np.uint32)
+    e[:rows] = np.asarray(t.scales, dtype=np.uint8).reshape(rows, cols // 32)
+    g = (e << 7).reshape(-1, TILE_N, cols // 32).transpose(0, 2, 1)  # bf16 bits of 2^(e - 127) in the low half
+    return W4Weight(w.packed, torch.from_numpy(np.ascontiguousarray(g).view(np.int32).copy()), rows, cols, 32, kind=1)
+
+
 def from_nint(t) -> W4Weight:
     """NINT tensor (every row at most 4 code bits, 2-D, group size a multiple of 8) -> :class:`W4Weight`."""
     gs = t.spec.groupsize
@@ -125,6 +144,9 @@ def dequantize(w: W4Weight) -> torch.Tensor:
     cols[..., _NIBBLE_COLUMN] = nib
     q = cols.transpose(0, 2, 1, 3, 4).reshape(w.packed.shape[0] * TILE_N, -1).astype(np.float32)  # [n_pad, K]
     g = w.group.cpu().numpy().view(np.uint32).transpose(0, 2, 1).reshape(-1, w.group.shape[1])
+    if w.kind == 1:
+        s = torch.from_numpy((g & 0xFFFF).astype(np.int16)).view(torch.bfloat16).float().repeat_interleave(32, 1)
+        return (torch.from_numpy(_E2M1[q.astype(np.int64)]) * s)[: w.n]
     s = torch.from_numpy((g & 0xFFFF).astype(np.int16)).view(torch.bfloat16).float()
     bias = torch.from_numpy((g >> 16).astype(np.int16)).view(torch.bfloat16).float()
     s, bias = s.repeat_interleave(w.group_size, 1), bias.repeat_interleave(w.group_size, 1)
@@ -146,8 +168,8 @@ def w4_gemm(x: torch.Tensor, w: W4Weight, *, residual: torch.Tensor | None = Non
     sp = K.pick_splits(m, w.n, k // 2) if splits is None else splits  # K blocks are 64 wide here: same work model
     ws = Workspace.get(x.device)
     fn = lib().mfq_w4_gemm
-    fn.argtypes = [C.c_void_p] * 6 + [C.c_size_t, C.c_void_p, C.c_int, C.c_void_p] + [C.c_int] * 6 + [C.c_void_p]
+    fn.argtypes = [C.c_void_p] * 6 + [C.c_size_t, C.c_void_p, C.c_int, C.c_void_p] + [C.c_int] * 7 + [C.c_void_p]
     rc = fn(ptr(w.packed), ptr(w.group), ptr(x), ptr(out), ptr(residual), ptr(ws.splitk), ws.splitk.numel(), ptr(ws.counters),
-            ws.counters.numel(), ptr(ws.status), m, w.n, k, w.group_size, bt, sp, stream_ptr())
+            ws.counters.numel(), ptr(ws.status), m, w.n, k, w.group_size, bt, sp, w.kind, stream_ptr())
     check(rc, "w4_gemm")
     return out

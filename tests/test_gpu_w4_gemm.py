@@ -49,3 +49,19 @@ def test_w4_from_nint_checkpoint_tensor():
     want = x.float() @ torch.from_numpy(nint.dequantize_nint(t)).cuda().T  # the checkpoint's own reconstruction
     assert_close(got.float(), want, rel=2e-2, what="w4 gemm vs NINT dequantization")
     assert w.bits_per_weight < 5.5
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (48, 300, 2048), (200, 512, 4096)])
+def test_mxfp4_kind_matches_checkpoint_dequantization(m, n, k):
+    """MXFP4 tensors run through the same pipeline with the E2M1 table decode: exact weights, bf16 x bf16 products."""
+    require_gpu_lib()
+    from mfq_b200 import formats as F
+    from mfq_b200.quantize.mxfp4 import quantize_mxfp4
+    rng = np.random.default_rng(m)
+    t = quantize_mxfp4((rng.standard_normal((n, k)) * 0.05).astype(np.float32))
+    w = w4.from_mxfp4(t)
+    x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    got = w4.w4_gemm(x, w.to("cuda"))
+    check_status()
+    want = x.float() @ torch.from_numpy(F.dequantize(t)).cuda().T
+    assert_close(got.float(), want, rel=1e-2, what="mxfp4 gemm")
