@@ -115,7 +115,8 @@ def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict
     F.save(path, header, records)
 
 
-def load_engine(path, device="cuda", *, max_batch: int = 64, max_seq_len: int = 8192, tp_rank: int = 0, tp_size: int = 1,
+def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots: int | None = None, max_batch: int = 64,
+                max_seq_len: int = 8192, tp_rank: int = 0, tp_size: int = 1,
                 collective=None, use_graphs: bool = True):
     """``.mfq`` -> (engine, tokenizer, config)."""
     from .engine.llm_engine import LLMEngine
@@ -126,7 +127,7 @@ def load_engine(path, device="cuda", *, max_batch: int = 64, max_seq_len: int = 
         raw = json.loads(assets["model_config.json"])
         fields = {f for f in MoeDecoderConfig.__dataclass_fields__}
         cfg = MoeDecoderConfig(**{k: v for k, v in raw.items() if k in fields})
-        weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size)
+        weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size, expert_slots=expert_slots, native_4bit=native_4bit)
     model = MoeDecoderModel(cfg, weights, collective=collective)
     engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, use_graphs=use_graphs)
     return engine, tokenizer_from_assets(assets, cfg.vocab_size), cfg

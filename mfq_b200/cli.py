@@ -209,7 +209,8 @@ def _cmd_serve(args) -> int:
 
     def loader(name_or_path):
         path = name_or_path if Path(name_or_path).exists() else args.model
-        engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size)
+        engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size,
+                                        native_4bit=args.native_4bit, expert_slots=args.moe_gpu_cache_slots)
         return engine, tok
 
     service.loader = loader
@@ -301,6 +302,10 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--queue-timeout", type=float, default=30.0)
     s.add_argument("--device")
     s.add_argument("--access-log", action="store_true")
+    s.add_argument("--native-4bit", action="store_true",
+                   help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
+    s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
+                   help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
     s.set_defaults(fn=_cmd_serve)
     be = sub.add_parser("bench", help="run the flagship benchmark (arguments are passed through to bench.py)")
     be.add_argument("rest", nargs=argparse.REMAINDER)

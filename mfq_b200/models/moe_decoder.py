@@ -81,10 +81,12 @@ def _to_float(t, device) -> torch.Tensor:
 class MoeWeights(LlamaWeights):
     @classmethod
     def from_tensors(cls, cfg: MoeDecoderConfig, tensors, device, tp_rank: int = 0, tp_size: int = 1,
-                     expert_slots: int | None = None) -> "MoeWeights":
+                     expert_slots: int | None = None, native_4bit: bool = False) -> "MoeWeights":
         """Build rank-local FP8 weights from checkpoint tensors under canonical names (a dict or an ``MfqStore``).
         ``expert_slots`` < experts per rank keeps the routed experts in (pinned) host memory behind an HBM arena of
-        that many slots (:class:`~mfq_b200.engine.expert_residency.ExpertResidency`); such a model decodes eagerly."""
+        that many slots (:class:`~mfq_b200.engine.expert_residency.ExpertResidency`); such a model decodes eagerly.
+        ``native_4bit`` (single GPU): attention and dense-FFN projections stored as NINT (<= 4 code bits) or MXFP4 keep
+        their 4-bit codes and run through the in-pipeline-decode GEMM instead of being transcoded to FP8."""
         dev = torch.device(device)
         h, d, w = cfg.hidden_size, cfg.head_dim, tp_size
         hq, hk = cfg.num_heads, cfg.num_kv_heads
@@ -101,16 +103,31 @@ class MoeWeights(LlamaWeights):
         def norm(name):
             return get(name).to(torch.bfloat16)
 
+        def linear(names, float_builder):
+            """4-bit native when every named tensor allows it, else FP8 from the float matrix ``float_builder()``."""
+            if native_4bit and w == 1:
+                from ..models.llama import W4Linear
+                from ..ops import w4 as w4ops
+                parts = [w4ops.from_checkpoint_tensor(tensors[n]) for n in names]
+                if all(p is not None for p in parts):
+                    try:
+                        return W4Linear(w4ops.concat_rows(parts).to(dev))
+                    except ValueError:
+                        pass
+            return Fp8Linear.from_float(float_builder())
+
         layers = []
         e_per = cfg.num_experts // w
         e_lo = tp_rank * e_per
         for i in range(cfg.num_layers):
             p = f"model.block.{i}."
-            qkv = torch.cat([rows(get(p + "attention.query.weight"), hq * d), rows(get(p + "attention.key.weight"), hk * d),
-                             rows(get(p + "attention.value.weight"), hk * d)], 0)
-            o = cols(get(p + "attention.output.weight"), hq * d)
-            layer = MoeLayer(attn_norm=norm(p + "attention.norm.weight"), qkv=Fp8Linear.from_float(qkv),
-                             o_proj=Fp8Linear.from_float(o), mlp_norm=norm(p + "mlp.norm.weight"), gate_up=None, down=None)
+            qkv_names = [p + f"attention.{n}.weight" for n in ("query", "key", "value")]
+            layer = MoeLayer(
+                attn_norm=norm(p + "attention.norm.weight"),
+                qkv=linear(qkv_names, lambda: torch.cat([rows(get(qkv_names[0]), hq * d), rows(get(qkv_names[1]), hk * d),
+                                                         rows(get(qkv_names[2]), hk * d)], 0)),
+                o_proj=linear([p + "attention.output.weight"], lambda: cols(get(p + "attention.output.weight"), hq * d)),
+                mlp_norm=norm(p + "mlp.norm.weight"), gate_up=None, down=None)
             if (p + "mlp.router.weight") in tensors:
                 gate = get(p + "mlp.experts.gate.weight")[e_lo : e_lo + e_per]
                 up = get(p + "mlp.experts.up.weight")[e_lo : e_lo + e_per]
@@ -138,8 +155,9 @@ class MoeWeights(LlamaWeights):
                 layer.moe = ffn
             else:
                 i_ = cfg.intermediate_size
-                layer.gate_up = Fp8Linear.from_float(torch.cat([rows(get(p + "mlp.gate.weight"), i_), rows(get(p + "mlp.up.weight"), i_)], 0))
-                layer.down = Fp8Linear.from_float(cols(get(p + "mlp.down.weight"), i_))
+                layer.gate_up = linear([p + "mlp.gate.weight", p + "mlp.up.weight"],
+                                       lambda: torch.cat([rows(get(p + "mlp.gate.weight"), i_), rows(get(p + "mlp.up.weight"), i_)], 0))
+                layer.down = linear([p + "mlp.down.weight"], lambda: cols(get(p + "mlp.down.weight"), i_))
             layers.append(layer)
         head = rows(get("model.output.weight"), cfg.vocab_size)
         return cls(get("model.token_embedding.weight").to(torch.bfloat16), layers, norm("model.output_norm.weight"),

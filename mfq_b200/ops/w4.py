@@ -136,6 +136,30 @@ def from_nint(t) -> W4Weight:
     return repack(codes, scale, shift, gs)
 
 
+def concat_rows(parts: list[W4Weight]) -> W4Weight:
+    """Stack weights along the output dimension (fused q|k|v, gate|up): every part but the last must hold a multiple
+    of 128 rows, all parts the same K, group size and kind."""
+    k, gs, kind = parts[0].k, parts[0].group_size, parts[0].kind
+    if any((p.k, p.group_size, p.kind) != (k, gs, kind) for p in parts) or any(p.n % TILE_N for p in parts[:-1]):
+        raise ValueError("parts do not stack: different geometry or a part that is not a whole number of 128-row tiles")
+    return W4Weight(torch.cat([p.packed for p in parts], 0), torch.cat([p.group for p in parts], 0), sum(p.n for p in parts), k, gs, kind)
+
+
+def from_checkpoint_tensor(t) -> W4Weight | None:
+    """:class:`W4Weight` for a checkpoint tensor the 4-bit GEMM can run natively (2-D NINT with at most 4 code bits
+    and a group size that is a multiple of 8, or MXFP4), else None."""
+    from ..formats.mx import MxTensor
+    from ..formats.nint import NintTensor
+    try:
+        if isinstance(t, NintTensor) and len(t.shape) == 2 and t.axis == 0:
+            return from_nint(t)
+        if isinstance(t, MxTensor) and t.dtype == "MXFP4":
+            return from_mxfp4(t)
+    except ValueError:
+        return None
+    return None
+
+
 def dequantize(w: W4Weight) -> torch.Tensor:
     """fp32 ``[N, K]`` matrix exactly as the kernel's decode warps produce it (bf16-rounded values)."""
     packed = w.packed.cpu().numpy().view("<u4").reshape(w.packed.shape[0], w.packed.shape[1], TILE_N, 8)

@@ -35,3 +35,37 @@ def test_fp8_moe_decoder_tracks_fp32_model():
     # and generation runs end to end through the engine
     out = LLMEngine(model, max_batch=1, max_seq_len=64, device="cpu").generate([prompt], 4)
     assert out.tokens.shape == (1, 4)
+
+
+def test_native_4bit_loading_keeps_nint_codes():
+    """NINT4 attention projections stay 4-bit (in-pipeline-decode GEMM) and predict like the FP8-transcoded model."""
+    import torch
+    import mfq_b200.quantize.expertwise as ew
+    from mfq_b200.checkpoint import quantize_tensors
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.llama import StepBuffers, W4Linear
+    from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from mfq_b200.models.moe_lm import MoeConfig, init_weights
+    cfg = MoeDecoderConfig.tiny()
+    t = init_weights(MoeConfig(head_dim=128, hidden_size=256, moe_intermediate=128, shared_intermediate=128), seed=4, std=0.05)
+    old = ew._NINT_PRESETS[4]
+    ew._NINT_PRESETS[4] = (32, 6)
+    try:
+        q = quantize_tensors({k: v.numpy() for k, v in t.items()}, dense="nint4")
+    finally:
+        ew._NINT_PRESETS[4] = old
+    native = MoeWeights.from_tensors(cfg, q, "cpu", native_4bit=True)
+    fp8 = MoeWeights.from_tensors(cfg, q, "cpu")
+    assert isinstance(native.layers[0].qkv, W4Linear) and native.layers[0].qkv.w.n == (4 + 2 * 2) * 128
+    assert not isinstance(fp8.layers[0].qkv, W4Linear)
+    prompt = torch.randint(0, cfg.vocab_size, (20,), generator=torch.Generator().manual_seed(1))
+
+    def logits(w):
+        eng = LLMEngine(MoeDecoderModel(cfg, w), max_batch=1, max_seq_len=64, device="cpu")
+        eng.cache.assign(0, 1, 20)
+        step = StepBuffers(input_ids=prompt.int(), positions=torch.arange(20, dtype=torch.int32), slots=eng.cache.slots(1, 0, 20),
+                           cu_seqlens=[0, 20])
+        return eng.model.forward(step, eng.cache, prefill=True).float()
+    a, b = logits(native), logits(fp8)
+    scale = float(b.abs().max())
+    assert float((a - b).abs().mean()) <= 0.03 * scale  # same checkpoint; FP8 transcoding vs exact 4-bit reconstruction
