@@ -129,5 +129,7 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
         cfg = MoeDecoderConfig(**{k: v for k, v in raw.items() if k in fields})
         weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size, expert_slots=expert_slots, native_4bit=native_4bit)
     model = MoeDecoderModel(cfg, weights, collective=collective)
-    engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, use_graphs=use_graphs)
+    # host-tier experts read the routing on the host every step, which a captured graph cannot do
+    engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device,
+                       use_graphs=use_graphs and expert_slots is None)
     return engine, tokenizer_from_assets(assets, cfg.vocab_size), cfg

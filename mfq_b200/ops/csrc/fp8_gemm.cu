@@ -387,17 +387,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                            "r"(smem_u32(stage)), "r"(uint32_t(CW * 32 * sizeof(float)))
                            : "memory");
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-              asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-              asm volatile("fence.proxy.async;" ::: "memory");
+              // Only the READ of the staging buffer has to finish before this CTA may exit; the NVLink writes drain
+              // while the next CTA on this SM runs its main loop.  Nobody is told per tile: the kernel's completion
+              // completes its copies, a cross-rank barrier follows on the stream, and only then the owner sums.
+              asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             }
-            __threadfence_system();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&epi_bar[2]);
-            const bool met = mbar_wait(&epi_bar[2], 0, abort_flag, p.status, kStatusTimeoutEpilogue);
-            if (met && threadIdx.x == 64) {
-              asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ar.flags[tile_owner] + tile_id) : "memory");
-              ar.expected[tile_id] = before + 1u;
-            }
+            if (threadIdx.x == 64) ar.expected[tile_id] = before + 1u;  // launch count of the tile: selects the buffer half
             owner = false;
           } else {
 #pragma unroll
@@ -551,35 +547,15 @@ extern "C" int mfq_fp8_gemm(const void* w, const float* w_scale, const void* x, 
 }
 
 namespace mfq {
-// Trailing kernel of the GEMM -> reduce-scatter: one CTA per owned tile waits (bounded) until all W ranks delivered
-// their partial of the tile, sums the W slots in rank order (bit-identical run to run), adds the residual and writes
-// the bf16 rows of the output shard of this rank.
+// Trailing kernel of the GEMM -> reduce-scatter, launched after a cross-rank barrier (every rank's GEMM kernel, and
+// with it every push, has completed): one CTA per owned tile sums the W slots in rank order (bit-identical run to
+// run), adds the residual and writes the bf16 rows of the output shard of this rank.
 __global__ void __launch_bounds__(128)
 rs_reduce_kernel(ArParams ar, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual, int N, int BT,
-                 int CW, int n_tiles, int t_per_rank, int* status) {
-  __shared__ int s_ok;
+                 int CW, int n_tiles, int t_per_rank) {
   const int tile_local = blockIdx.x, t_local = tile_local / n_tiles, n_tile = tile_local % n_tiles;
   const int tile_id = (ar.rank * t_per_rank + t_local) * n_tiles + n_tile;
   const uint32_t launches = ar.expected[tile_id];  // the GEMM kernel of this launch already counted itself
-  if (threadIdx.x == 0) {
-    const uint32_t target = launches * uint32_t(ar.world);
-    const uint32_t* f = ar.flags[ar.rank] + tile_id;
-    const unsigned long long t0 = globaltimer_ns();
-    uint32_t seen, spins = 0;
-    int ok = 1;
-    while (true) {
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
-      if (int32_t(seen - target) >= 0) break;
-      if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
-        atomicCAS(status, 0, kStatusTimeoutPeer);
-        ok = 0;
-        break;
-      }
-    }
-    s_ok = ok;
-  }
-  __syncthreads();
-  if (!s_ok) return;
   const size_t half_off = size_t((launches - 1u) & 1u) * ar.half_elems;
   const int tiles_owned = t_per_rank * n_tiles;
   const int row = threadIdx.x, n = n_tile * kTileN + row;
@@ -654,12 +630,25 @@ extern "C" int mfq_fp8_gemm_allreduce(const void* w, const float* w_scale, const
     case 128: rc = mfq::launch_gemm<128>(w, w_scale, x, x_scale, out, residual, ws, ws_bytes, counters, counters_len, status, M, N, K, splits, stream, &ar); break;
     default: return -1;
   }
-  if (rc != 0 || !reduce_scatter) return rc;
+  return rc;  // reduce-scatter: the caller runs a cross-rank barrier on the stream, then mfq_rs_reduce
+}
+
+// Second half of the GEMM -> reduce-scatter (see rs_reduce_kernel).  Same geometry arguments as the GEMM call.
+extern "C" int mfq_rs_reduce(void* out, const void* residual, int M, int N, int token_tile, int world, int rank,
+                             void* const* bufs, void* expected, size_t half_elems, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || world < 2 || world > 8 || M % (token_tile * world)) return -1;
+  mfq::ArParams ar;
+  ar.mode = 1;
+  ar.world = world;
+  ar.rank = rank;
+  for (int r = 0; r < world; ++r) ar.bufs[r] = static_cast<float*>(bufs[r]);
+  ar.expected = static_cast<uint32_t*>(expected);
+  ar.half_elems = half_elems;
   const int n_tiles = (N + mfq::kTileN - 1) / mfq::kTileN, t_per_rank = (M / token_tile) / world;
   const int cw = token_tile / (token_tile >= 64 ? 2 : 1);  // token columns per epilogue warp (GemmCfg::kCols)
   mfq::rs_reduce_kernel<<<n_tiles * t_per_rank, 128, 0, stream>>>(ar, static_cast<__nv_bfloat16*>(out),
                                                                  static_cast<const __nv_bfloat16*>(residual), N, token_tile,
-                                                                 cw, n_tiles, t_per_rank, status);
+                                                                 cw, n_tiles, t_per_rank);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 

@@ -84,7 +84,14 @@ class TensorParallel:
             ptr(lin.q), ptr(lin.scale), ptr(x_q), ptr(x_scale), ptr(out), ptr(residual_shard), ptr(ws.splitk),
             ws.splitk.numel(), ptr(ws.counters), ws.counters.numel(), ptr(ws.status), m, n, k, token_tile, 1, self.world,
             self.rank, ctx.buf_table, ctx.flag_table, ptr(ctx.expected), ctx.half_elems, 1, stream_ptr())
-        check(rc, "fp8_gemm_reduce_scatter", 2)
+        check(rc, "fp8_gemm_reduce_scatter")
+        # every rank's pushes are complete once its GEMM kernel is: meet on the stream, then sum the owned tiles
+        self.barrier()
+        fn = lib().mfq_rs_reduce
+        fn.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t,
+                       C.c_void_p]
+        check(fn(ptr(out), ptr(residual_shard), m, n, token_tile, self.world, self.rank, ctx.buf_table, ptr(ctx.expected),
+                 ctx.half_elems, stream_ptr()), "rs_reduce")
         return out
 
     def allgather_gemm(self, lin, xq_shard: torch.Tensor, xs_shard: torch.Tensor, token_tile: int = 128,
