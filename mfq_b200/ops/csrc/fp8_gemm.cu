@@ -66,7 +66,7 @@ struct AgParams {
   const uint8_t* x_shard = nullptr;
   const float* xs_shard = nullptr;
   const uint32_t* epoch = nullptr;   // completed launches on this context (bumped by a 1-thread kernel afterwards)
-  uint32_t* push_done = nullptr;     // local counter of finished push blocks (returns to zero)
+  uint32_t* push_done = nullptr;     // local counters of finished push blocks, one per destination step (return to zero)
 };
 
 struct GemmParams {
@@ -125,19 +125,26 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     for (int rr = 0; rr < ag.world; ++rr) {
       const int r = (ag.rank + rr) % ag.world;  // own copy first, then a different destination on every rank (no incast)
       uint4* dst = reinterpret_cast<uint4*>(ag.x_full[r] + half + size_t(ag.rank) * shard_bytes);
-      for (size_t v = size_t(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += size_t(ag.push_ctas) * blockDim.x) dst[v] = src[v];
+      const size_t stride = size_t(ag.push_ctas) * blockDim.x;
+      size_t v = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+      for (; v + 3 * stride < nvec; v += 4 * stride) {  // four independent 16-byte copies in flight per thread
+        const uint4 a0 = src[v], a1 = src[v + stride], a2 = src[v + 2 * stride], a3 = src[v + 3 * stride];
+        dst[v] = a0; dst[v + stride] = a1; dst[v + 2 * stride] = a2; dst[v + 3 * stride] = a3;
+      }
+      for (; v < nvec; v += stride) dst[v] = src[v];
       float* sdst = ag.xs_full[r] + size_t(ag_epoch & 1u) * p.M + size_t(ag.rank) * ag.shard_rows;
-      for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < ag.shard_rows; v += ag.push_ctas * blockDim.x) sdst[v] = ag.xs_shard[v];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const uint32_t prev = atomicAdd(ag.push_done, 1u);
-      if (prev == uint32_t(ag.push_ctas) - 1u) {  // last push block: all of my shard is on its way and fenced
-        *ag.push_done = 0;
-        __threadfence_system();
-        for (int r = 0; r < ag.world; ++r)
+      for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ag.shard_rows; i += ag.push_ctas * blockDim.x) sdst[i] = ag.xs_shard[i];
+      // one completion counter per destination: a rank learns that my shard has arrived as soon as ITS copy is done
+      // (my own tiles after the local copy, rank+1 next, ...), not when the whole fan-out has finished
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const uint32_t prev = atomicAdd(ag.push_done + rr, 1u);
+        if (prev == uint32_t(ag.push_ctas) - 1u) {
+          ag.push_done[rr] = 0;
+          __threadfence_system();
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ag.flags[r] + ag.rank) : "memory");
+        }
       }
     }
     return;
@@ -657,7 +664,7 @@ __global__ void bump_epoch_kernel(uint32_t* epoch) { *epoch += 1; }
 // All-gather -> GEMM: x_shard [M / world, K] E4M3 (+ xs_shard multipliers) is this rank's slice of the token rows; the
 // kernel gathers all slices through peer memory while it multiplies (see AgParams) and writes out [M, N] bf16.
 // x_full[r] / xs_full[r] / flags[r]: rank r's gathered buffers (2 * M * K bytes, 2 * M floats, `world` counters);
-// epoch, push_done: local words, zero before first use.  M must be a multiple of world.
+// epoch (1 word), push_done (`world` words): local, zero before first use.  M must be a multiple of world.
 extern "C" int mfq_fp8_gemm_allgather(const void* w, const float* w_scale, const void* x_shard, const float* xs_shard,
                                       void* out, int* status, int M, int N, int K, int token_tile, int world, int rank,
                                       void* const* x_full, void* const* xs_full, void* const* flags, void* epoch,

@@ -95,10 +95,12 @@ class TensorParallel:
         return out
 
     def allgather_gemm(self, lin, xq_shard: torch.Tensor, xs_shard: torch.Tensor, token_tile: int = 128,
-                       push_ctas: int = 16) -> torch.Tensor:
+                       push_ctas: int | None = None) -> torch.Tensor:
         """Column-parallel GEMM over token-sharded input: gathers the shards through peer memory inside the kernel
         and returns ``[M, N_local]``."""
         ms, k = xq_shard.shape
+        if push_ctas is None:  # one push block per 64 KB of shard, at most 32: tiny shards are latency-, not bandwidth-bound
+            push_ctas = max(1, min(32, (ms * k) // 65536))
         m = ms * self.world
         n = lin.q.shape[0]
         key = ("ag", m, k)
@@ -110,7 +112,7 @@ class TensorParallel:
             ctx.x = PeerBuffer(self.group, 2 * m * k, self.device)
             ctx.xs = PeerBuffer(self.group, 2 * m * 4, self.device)
             ctx.flags = PeerBuffer(self.group, 256, self.device)
-            ctx.words = torch.zeros(2, dtype=torch.int32, device=self.device)  # epoch, push_done
+            ctx.words = torch.zeros(16, dtype=torch.int32, device=self.device)  # epoch, then one push counter per destination
             ctx.tables = (ctx.x.table(), ctx.xs.table(), ctx.flags.table())
             self._ctx[key] = ctx
         out = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
