@@ -43,10 +43,11 @@ class GenerationResult:
 
 class LLMEngine:
     def __init__(self, model: LlamaModel, *, max_batch: int = 64, max_seq_len: int = 8192, num_pages: int | None = None,
-                 device=None, use_graphs: bool = True, mtp_draft_tokens: int = 0) -> None:
+                 device=None, use_graphs: bool = True, mtp_draft_tokens: int = 0, prefill_chunk: int = 8192) -> None:
         """``mtp_draft_tokens`` (K, 0 = off): with a model that carries an MTP head, greedy rows decode by
         draft/verify cycles that confirm between 1 and K+1 tokens each (:meth:`mtp_step`)."""
         self.model = model
+        self.prefill_chunk = prefill_chunk  # prompts longer than this are prefilled in chunks that attend to the cached past
         cfg = model.cfg
         has_head = getattr(model.w, "mtp", None) is not None
         self.mtp_k = mtp_draft_tokens if has_head else 0
@@ -201,28 +202,12 @@ class LLMEngine:
             raise
         self.set_sampling(row, params)
         ids = ids.to(dev, non_blocking=True)
-        positions = torch.arange(n, dtype=torch.int32, device=dev)
-        slots = self.cache.slots(seq_id, 0, n).to(dev)
-        cu = [0, n]
-        tp = self.model.tp
         state_slots = None
         if self.rec_state is not None:
             self.rec_state.reset(row)
             state_slots = self.row_ids[row : row + 1]
-        if tp > 1 and n >= tp * 128 and n % (tp * 128) and self.rec_state is None:
-            # pad to a whole number of token tiles per rank so the row-parallel GEMMs take the reduce-scatter path;
-            # the pad rows form a sequence of their own and write no KV
-            pad = tp * 128 - n % (tp * 128)
-            ids = torch.cat([ids, torch.zeros(pad, dtype=torch.int32, device=dev)])
-            positions = torch.cat([positions, torch.arange(pad, dtype=torch.int32, device=dev)])
-            slots = torch.cat([slots, torch.full((pad,), -1, dtype=torch.int32, device=dev)])
-            cu = [0, n, n + pad]
-        step = StepBuffers(input_ids=ids, positions=positions, slots=slots, cu_seqlens=cu, state_slots=state_slots)
         last = torch.tensor([n - 1], dtype=torch.int32, device=dev)
-        logits = self.model.forward(step, self.cache, prefill=True, logits_rows=last, gather_logits=False,
-                                    return_hidden=bool(self.mtp_k))
-        if self.mtp_k:
-            logits, hidden = logits
+        logits, hidden = self._prefill_span(row, seq_id, ids, 0, n, state_slots)
         self.seq_lens[row] = n
         self.row_len[row] = n
         if self.row_stochastic[row]:
@@ -239,12 +224,51 @@ class LLMEngine:
         self.sampled[row] = tok
         if self.mtp_k:
             # teacher-forced priming of the head over the prompt: position i pairs hidden[i] with token i+1
-            nxt = torch.cat([ids[1:n], tok.reshape(1).to(torch.int32), ids[n:]])
-            mstep = StepBuffers(input_ids=nxt, positions=step.positions, slots=step.slots, cu_seqlens=cu)
+            nxt = torch.cat([ids[1:n], tok.reshape(1).to(torch.int32)])
+            mstep = StepBuffers(input_ids=nxt, positions=torch.arange(n, dtype=torch.int32, device=dev),
+                                slots=self.cache.slots(seq_id, 0, n).to(dev), cu_seqlens=[0, n])
             mlogits, mhid = self.model.mtp_forward(mstep, self.cache, hidden, prefill=True, logits_rows=last)
             self.draft[row, 0] = self.model.sample_greedy(mlogits)[0]
             self._mtp_chain(row, row + 1, mhid[n - 1 : n].contiguous(), masked=False)
         return int(tok)
+
+    def _prefill_span(self, row: int, seq_id: int, ids: torch.Tensor, start: int, end: int, state_slots):
+        """Run tokens ``[start, end)`` of the row's sequence (``ids`` holds the whole prompt, on the device) through
+        the model in chunks of at most ``prefill_chunk``; tokens before ``start`` must already be in the KV pages.
+        Returns (logits of the last token, hidden states of the span if an MTP head needs them)."""
+        dev = self.device
+        tp = self.model.tp
+        want_hidden = bool(self.mtp_k)
+        hidden_parts, logits = [], None
+        c0 = start
+        while c0 < end:
+            c1 = min(end, c0 + self.prefill_chunk)
+            m = c1 - c0
+            chunk_ids = ids[c0:c1]
+            positions = torch.arange(c0, c1, dtype=torch.int32, device=dev)
+            slots = self.cache.slots(seq_id, c0, m).to(dev)
+            cu = [0, m]
+            single = c0 == 0 and c1 == end
+            if single and tp > 1 and m >= tp * 128 and m % (tp * 128) and self.rec_state is None:
+                # pad to a whole number of token tiles per rank so the row-parallel GEMMs take the reduce-scatter path;
+                # the pad rows form a sequence of their own and write no KV
+                pad = tp * 128 - m % (tp * 128)
+                chunk_ids = torch.cat([chunk_ids, torch.zeros(pad, dtype=torch.int32, device=dev)])
+                positions = torch.cat([positions, torch.arange(pad, dtype=torch.int32, device=dev)])
+                slots = torch.cat([slots, torch.full((pad,), -1, dtype=torch.int32, device=dev)])
+                cu = [0, m, m + pad]
+            step = StepBuffers(input_ids=chunk_ids, positions=positions, slots=slots, cu_seqlens=cu, state_slots=state_slots,
+                               past_len=c0, block_table=self.cache.block_table[row : row + 1] if c0 else None)
+            is_last = c1 == end
+            rows = torch.tensor([m - 1], dtype=torch.int32, device=dev) if is_last else torch.zeros(1, dtype=torch.int32, device=dev)
+            out = self.model.forward(step, self.cache, prefill=True, logits_rows=rows, gather_logits=False, return_hidden=want_hidden)
+            if want_hidden:
+                out, hid = out
+                hidden_parts.append(hid[:m])
+            if is_last:
+                logits = out
+            c0 = c1
+        return logits, (torch.cat(hidden_parts, 0) if want_hidden else None)
 
     def grow(self, row: int, tokens: int) -> None:
         self.cache.assign(row, self.row_seq[row], min(self.max_seq_len, tokens))

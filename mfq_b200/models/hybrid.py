@@ -247,7 +247,7 @@ class HybridModel(MoeDecoderModel):
         b, a = proj[:, c + zw : c + zw + g.v_heads], proj[:, c + zw + g.v_heads : c + zw + 2 * g.v_heads]
         conv_state, state = self.state.layer(li)
         slots = step.state_slots
-        L = step.q_len if step.block_table is not None else h.shape[0]
+        L = h.shape[0] if step.cu_seqlens else step.q_len  # prefill: one sequence, the whole chunk; else the decode window
         if not h.is_cuda:
             mixed, z, a, b = (t.contiguous() for t in (mixed, z, a, b))
         conv_ck = state_ck = None
@@ -279,7 +279,7 @@ class HybridModel(MoeDecoderModel):
                                   rot=self.rot, kd_out=kd, vd_out=vd, q_norm=layer.q_norm, k_norm=layer.k_norm,
                                   norm_eps=cfg.rms_eps)
             if prefill:
-                o = ops.attn_prefill(q, kd, vd, step.cu_seqlens, self.sm_scale)
+                o = self._prefill_attention(q, kd, vd, kv, step)
             else:
                 o = ops.paged_attn_decode(q, kv, step.block_table, step.seq_lens, sm_scale=self.sm_scale,
                                           splits=self.attn_splits, q_len=step.q_len)
@@ -297,12 +297,7 @@ class HybridModel(MoeDecoderModel):
             k = ref.rope(headnorm(q3[:, self.hq : self.hq + self.hk], layer.k_norm), step.positions, cfg.rope_theta, self.rot)
             ref.write_kv(kv, k, q3[:, self.hq + self.hk :], step.slots)
             if prefill:
-                outs = []
-                for i in range(len(step.cu_seqlens) - 1):
-                    lo, hi = step.cu_seqlens[i], step.cu_seqlens[i + 1]
-                    kk, vv = ref.gather_slots(kv, step.slots[lo:hi])
-                    outs.append(ref.attention(q[lo:hi], kk, vv, self.sm_scale, causal_offset=0))
-                o = torch.cat(outs, 0)
+                o = self._prefill_attention(q, None, None, kv, step)
             else:
                 o = ref.paged_attn_decode(q, kv, step.block_table, step.seq_lens, self.sm_scale, step.q_len)
             o = o.reshape(t, self.hq * d)

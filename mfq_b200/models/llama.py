@@ -215,6 +215,9 @@ class StepBuffers:
     # MTP verify window: recurrent layers write per-token state checkpoints instead of committing their state;
     # the engine commits the checkpoint of the last accepted token afterwards
     verify: bool = False
+    # chunked prefill / restored prefix: tokens of the sequence that are already in the KV pages (the chunk attends to
+    # them too); the chunk must then be a single sequence and `block_table` its page-id row ([1, max_pages])
+    past_len: int = 0
 
 
 class LlamaModel:
@@ -292,16 +295,30 @@ class LlamaModel:
             else:
                 o = ref.paged_attn_decode(q, kv, step.block_table, step.seq_lens, self.sm_scale, step.q_len)
             return o.reshape(t, self.hq * d)
-        # prefill over a packed chunk: each sequence attends causally to itself, through the same FP8 rounding
-        # of K/V that later decode steps will read back from the pages
-        if qkv.is_cuda:
-            return ops.attn_prefill(q, kd, vd, step.cu_seqlens, self.sm_scale).reshape(t, self.hq * d)
+        return self._prefill_attention(q, kd, vd, kv, step).reshape(t, self.hq * d)
+
+    def _prefill_attention(self, q, kd, vd, kv, step: StepBuffers):
+        """Causal attention of a prefill chunk, ``[T, Hq, D]``.  Each sequence of a packed chunk attends to itself,
+        through the same FP8 rounding of K/V that later decode steps read back from the pages (``kd`` / ``vd`` on the
+        GPU); a chunk with ``past_len`` > 0 also attends to the sequence's cached past."""
+        if step.past_len > 0:
+            row = step.block_table[0]
+            if q.is_cuda:
+                kp, vp = ops.kernels.kv_gather_dequant(kv, row, step.past_len)
+                return ops.attn_prefill_bf16(q, torch.cat([kp, kd], 0), torch.cat([vp, vd], 0), self.sm_scale)
+            ps = kv.page_size
+            past = torch.arange(step.past_len)
+            kp, vp = ref.gather_slots(kv, row[(past // ps).long()] * ps + past % ps)
+            kc, vc = ref.gather_slots(kv, step.slots)
+            return ref.attention(q, torch.cat([kp, kc], 0), torch.cat([vp, vc], 0), self.sm_scale, causal_offset=step.past_len)
+        if q.is_cuda:
+            return ops.attn_prefill(q, kd, vd, step.cu_seqlens, self.sm_scale)
         outs = []
         for i in range(len(step.cu_seqlens) - 1):
             a, b = step.cu_seqlens[i], step.cu_seqlens[i + 1]
             kk, vv = ref.gather_slots(kv, step.slots[a:b])
             outs.append(ref.attention(q[a:b], kk, vv, self.sm_scale, causal_offset=0))
-        return torch.cat(outs, 0).reshape(t, self.hq * d)
+        return torch.cat(outs, 0)
 
     # -- feed-forward -------------------------------------------------------------------------------------------
     def _ffn(self, h, layer):

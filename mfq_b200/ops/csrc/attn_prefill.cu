@@ -32,7 +32,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 struct PrefillParams {
   __nv_bfloat16* out;  // [T, Hq, 128]
-  int T, Hq, Hk;
+  int T, Hq, Hk;       // T: query rows
+  int Tk, offset;      // keys available; query row i sees keys 0 .. i + offset (offset = Tk - T: tokens before the chunk)
   float scale_log2;
   int* status;
 };
@@ -65,7 +66,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int qb = num_qb - 1 - blockIdx.x;  // heavy blocks first
   const int hq = blockIdx.y;
   const int kvh = hq / (p.Hq / p.Hk);
-  const int nblk = qb + 1;                 // causal: key blocks 0..qb
+  // causal with a past: the last query of the block sees keys up to (qb + 1) * kQB - 1 + offset
+  const int nblk = min((p.Tk + kKB - 1) / kKB, ((qb + 1) * kQB + p.offset + kKB - 1) / kKB);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -165,7 +167,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       if (!ok) break;
       tc_fence_after();
       const int key0 = j * kKB + half * 64;
-      const bool diag = (j == qb) || ((j + 1) * kKB > p.T);
+      // masking is needed where the block reaches past the FIRST query's horizon or past the last key
+      const bool diag = ((j + 1) * kKB - 1 > qb * kQB + p.offset) || ((j + 1) * kKB > p.Tk);
       // pass 1: maximum over this thread's 64 columns, then exchange with the partner thread of the row
       float mx = -FLT_MAX;
       {
@@ -180,8 +183,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int ka = key0 + i, kb = key0 + 32 + i;
-            mx = fmaxf(mx, (ka <= q_idx && ka < p.T) ? __uint_as_float(r0[i]) : -FLT_MAX);
-            mx = fmaxf(mx, (kb <= q_idx && kb < p.T) ? __uint_as_float(r1[i]) : -FLT_MAX);
+            mx = fmaxf(mx, (ka <= q_idx + p.offset && ka < p.Tk) ? __uint_as_float(r0[i]) : -FLT_MAX);
+            mx = fmaxf(mx, (kb <= q_idx + p.offset && kb < p.Tk) ? __uint_as_float(r1[i]) : -FLT_MAX);
           }
         }
       }
@@ -229,8 +232,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -mb));
           if (diag) {
             const int key = key0 + c + i;
-            if (!(key <= q_idx && key < p.T)) p0 = 0.f;
-            if (!(key + 1 <= q_idx && key + 1 < p.T)) p1 = 0.f;
+            if (!(key <= q_idx + p.offset && key < p.Tk)) p0 = 0.f;
+            if (!(key + 1 <= q_idx + p.offset && key + 1 < p.Tk)) p1 = 0.f;
           }
           psum += p0 + p1;
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
@@ -294,21 +297,28 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
 }  // namespace mfq
 
-// q: [T, Hq, 128] bf16, k/v: [T, Hk, 128] bf16 (contiguous), out: [T, Hq, 128] bf16.  Causal within the chunk.
-extern "C" int mfq_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, int T, int Hq, int Hk,
+// q: [T, Hq, 128] bf16, k/v: [Tk, Hk, 128] bf16 (contiguous), out: [T, Hq, 128] bf16.  Tk >= T: the first Tk - T keys
+// are the sequence's past (earlier chunks / a restored prefix); query i attends to keys 0 .. i + (Tk - T).
+extern "C" int mfq_attn_prefill_past(const void* q, const void* k, const void* v, void* out, int T, int Tk, int Hq, int Hk,
                                      int D, float sm_scale, int* status, cudaStream_t stream) {
   using namespace mfq;
-  if (D != 128 || T <= 0 || Hq % Hk) return -1;
+  if (D != 128 || T <= 0 || Tk < T || Hq % Hk) return -1;
   CUtensorMap tq, tk, tv;
   if (make_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, uint64_t(Hq) * D, uint64_t(Hq) * D * 2, kQB, 64)) return -2;
-  if (make_tmap_2d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, uint64_t(Hk) * D, uint64_t(Hk) * D * 2, kKB, 64)) return -3;
-  if (make_tmap_2d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, uint64_t(Hk) * D, uint64_t(Hk) * D * 2, kKB, 64)) return -4;
+  if (make_tmap_2d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tk, uint64_t(Hk) * D, uint64_t(Hk) * D * 2, kKB, 64)) return -3;
+  if (make_tmap_2d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tk, uint64_t(Hk) * D, uint64_t(Hk) * D * 2, kKB, 64)) return -4;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return -6;
     attr = true;
   }
-  PrefillParams p{static_cast<__nv_bfloat16*>(out), T, Hq, Hk, sm_scale * 1.4426950408889634f, status};
+  PrefillParams p{static_cast<__nv_bfloat16*>(out), T, Hq, Hk, Tk, Tk - T, sm_scale * 1.4426950408889634f, status};
   attn_prefill_kernel<<<dim3((T + kQB - 1) / kQB, Hq), kPrefillThreads, kPrefillSmem, stream>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+// Self-contained chunk (no past): Tk = T.
+extern "C" int mfq_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, int T, int Hq, int Hk,
+                                     int D, float sm_scale, int* status, cudaStream_t stream) {
+  return mfq_attn_prefill_past(q, k, v, out, T, T, Hq, Hk, D, sm_scale, status, stream);
 }

@@ -541,3 +541,51 @@ extern "C" int mfq_silu_mul_bf16(const void* x, void* out, int M, int I, int in_
                      static_cast<__nv_bfloat16*>(out), I, in_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Past K/V of one sequence out of the FP8 pages into contiguous bf16 [T, Hk, D] (code * multiplier): the keys /
+// values a later prefill chunk attends to (chunked prefill, restored prefix).  One warp per (token, KV head).
+// ---------------------------------------------------------------------------------------------
+namespace mfq {
+template <int D>
+__global__ void kv_gather_dequant_kernel(const uint8_t* __restrict__ k_cache, const uint8_t* __restrict__ v_cache,
+                                         const float* __restrict__ k_scale, const float* __restrict__ v_scale,
+                                         const int* __restrict__ block_row, __nv_bfloat16* __restrict__ kd,
+                                         __nv_bfloat16* __restrict__ vd, int T, int Hk, int page_size) {
+  pdl_trigger();
+  pdl_wait();
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (gw >= T * Hk) return;
+  const int t = gw / Hk, h = gw % Hk;
+  const int page = block_row[t / page_size], off = t % page_size;
+  const size_t ph = size_t(page) * Hk + h;
+  const float ks = k_scale[ph * page_size + off], vs = v_scale[ph * page_size + off];
+  const uint8_t* kp = k_cache + ph * (size_t(page_size) * D);
+  const uint8_t* vp = v_cache + ph * (size_t(page_size) * D);
+  const int pos = 4 * ((off & 7) >> 1) + 2 * (off >> 3) + (off & 1);  // slot of the token inside a V page
+  __nv_bfloat16* ko = kd + (size_t(t) * Hk + h) * D;
+  __nv_bfloat16* vo = vd + (size_t(t) * Hk + h) * D;
+  for (int d = lane; d < D; d += 32) {
+    ko[d] = __float2bfloat16(from_e4m3(kp[(d >> 6) * (page_size * 64) + off * 64 + (d & 63)]) * ks);
+    vo[d] = __float2bfloat16(from_e4m3(vp[d * page_size + pos]) * vs);
+  }
+}
+}  // namespace mfq
+
+// block_row: the sequence's page ids ([ceil(T / page_size)] int32, device); kd / vd: [T, Hk, D] bf16.
+extern "C" int mfq_kv_gather_dequant(const void* k_cache, const void* v_cache, const float* k_scale, const float* v_scale,
+                                     const int* block_row, void* kd, void* vd, int T, int Hk, int D, int page_size,
+                                     cudaStream_t stream) {
+  if (T <= 0 || Hk <= 0 || page_size != 16) return -1;
+  const int blocks = (T * Hk + 7) / 8;
+#define MFQ_GATHER(DD)                                                                                              \
+  mfq::launch_kernel(mfq::kv_gather_dequant_kernel<DD>, dim3(blocks), dim3(256), 0, stream,                        \
+                     static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache), k_scale, v_scale,  \
+                     block_row, static_cast<__nv_bfloat16*>(kd), static_cast<__nv_bfloat16*>(vd), T, Hk, page_size)
+  if (D == 128) MFQ_GATHER(128);
+  else if (D == 64) MFQ_GATHER(64);
+  else if (D == 256) MFQ_GATHER(256);
+  else return -1;
+#undef MFQ_GATHER
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}

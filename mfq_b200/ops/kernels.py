@@ -182,14 +182,25 @@ def decode_advance(sampled, input_ids, positions, seq_lens, slots, block_table, 
 
 
 def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sm_scale: float, *, out=None) -> torch.Tensor:
-    """Causal attention of one sequence chunk on the tcgen05 kernel: ``q [T, Hq, 128]``, ``k/v [T, Hk, 128]``."""
+    """Causal attention of one sequence chunk on the tcgen05 kernel: ``q [T, Hq, 128]``, ``k/v [Tk, Hk, 128]`` with
+    ``Tk >= T``: the first ``Tk - T`` keys are the sequence's past, query ``i`` sees keys ``0 .. i + (Tk - T)``."""
     t, hq, d = q.shape
     out = torch.empty_like(q) if out is None else out
     ws = Workspace.get(q.device)
-    rc = lib().mfq_attn_prefill_bf16(ptr(q), ptr(k), ptr(v), ptr(out), t, hq, k.shape[1], d, float(sm_scale), ptr(ws.status),
-                                     stream_ptr())
+    rc = lib().mfq_attn_prefill_past(ptr(q), ptr(k), ptr(v), ptr(out), t, k.shape[0], hq, k.shape[1], d, float(sm_scale),
+                                     ptr(ws.status), stream_ptr())
     check(rc, "attn_prefill_bf16")
     return out
+
+
+def kv_gather_dequant(kv, block_row: torch.Tensor, tokens: int):
+    """The first ``tokens`` cached K/V rows of one sequence (its page ids in ``block_row``) as bf16 ``[tokens, Hk, D]``."""
+    hk, d = kv.k.shape[1], kv.k.shape[2] * kv.k.shape[4]
+    kd = torch.empty((tokens, hk, d), dtype=torch.bfloat16, device=block_row.device)
+    vd = torch.empty_like(kd)
+    check(lib().mfq_kv_gather_dequant(ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale), ptr(block_row), ptr(kd), ptr(vd),
+                                      tokens, hk, d, kv.page_size, stream_ptr()), "kv_gather_dequant")
+    return kd, vd
 
 
 def attn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: list[int], sm_scale: float) -> torch.Tensor:

@@ -26,6 +26,8 @@ _SIGNATURES = {
     "mfq_argmax_allgather": [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp],
     "mfq_rmsnorm_quant": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "mfq_quant_rows": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "mfq_kv_gather_dequant": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "mfq_attn_prefill_past": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp],
     "mfq_silu_mul_bf16": [_vp, _vp, _i, _i, _i, _vp],
     "mfq_gate_quant_rows": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "mfq_rope_kv_write_ex": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _f, _i, _vp],

@@ -89,3 +89,12 @@ def test_mtp_cycles_on_hybrid_model_are_lossless():
     # and decoding on from the committed state still follows the plain sequence
     eng.decode_step(1)
     assert int(eng.sampled[0]) == truth[1 + n]
+
+
+def test_hybrid_chunked_prefill_carries_recurrent_state():
+    cfg = HybridConfig.tiny()
+    w = HybridWeights.from_tensors(cfg, init_hybrid_weights(cfg, seed=3, std=0.05), "cpu")
+    prompt = torch.randint(0, cfg.vocab_size, (37,), generator=torch.Generator().manual_seed(5))
+    whole = LLMEngine(HybridModel(cfg, w), max_batch=1, max_seq_len=96, device="cpu")
+    parts = LLMEngine(HybridModel(cfg, w), max_batch=1, max_seq_len=96, device="cpu", prefill_chunk=16)
+    assert whole.generate([prompt], 5).tokens[0].tolist() == parts.generate([prompt], 5).tokens[0].tolist()

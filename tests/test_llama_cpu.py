@@ -46,3 +46,19 @@ def test_w4_weights_decode_consistent_with_prefill():
     eng.decode_step(1)
     second = int(eng.sampled[0])
     assert eng.prefill(1, torch.cat([prompt, torch.tensor([first])])) == second
+
+
+def test_chunked_prefill_equals_one_shot_prefill():
+    """A prompt prefilled in chunks (each chunk attends to the cached past) predicts what the one-shot prefill predicts,
+    and decoding continues identically."""
+    import torch
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.llama import LlamaConfig, LlamaModel, LlamaWeights
+    cfg = LlamaConfig.tiny()
+    w = LlamaWeights.random_init(cfg, "cpu", seed=2, std=0.05)
+    prompt = torch.randint(0, cfg.vocab_size, (45,), generator=torch.Generator().manual_seed(3))
+    whole = LLMEngine(LlamaModel(cfg, w), max_batch=1, max_seq_len=96, device="cpu")
+    parts = LLMEngine(LlamaModel(cfg, w), max_batch=1, max_seq_len=96, device="cpu", prefill_chunk=16)
+    a = whole.generate([prompt], 6).tokens[0].tolist()
+    b = parts.generate([prompt], 6).tokens[0].tolist()
+    assert a == b
