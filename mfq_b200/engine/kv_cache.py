@@ -96,6 +96,37 @@ class PagedKVCache:
     def layer(self, i: int) -> LayerKV:
         return LayerKV(self.k[i], self.v[i], self.k_scale[i], self.v_scale[i], self.page_size)
 
+    # -- page export / import (prefix cache, session snapshots) ------------------------------------------------------
+    def export_pages(self, page_ids: list[int]):
+        """All layers' K, V and multipliers of the given pages as one contiguous uint8 numpy array (host)."""
+        import numpy as np
+        idx = torch.tensor(page_ids, dtype=torch.long, device=self.k.device)
+        parts = [(t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t).index_select(1, idx).contiguous().view(torch.uint8).reshape(-1)
+                 for t in (self.k, self.v, self.k_scale, self.v_scale)]
+        return np.ascontiguousarray(torch.cat(parts).cpu().numpy())
+
+    def page_blob_bytes(self, pages: int) -> int:
+        per = self.kv_heads * self.page_size * (2 * self.head_dim + 8)
+        return self.layers * pages * per
+
+    def import_pages(self, page_ids: list[int], blob) -> None:
+        """Inverse of :meth:`export_pages` into (possibly different) physical pages."""
+        idx = torch.tensor(page_ids, dtype=torch.long, device=self.k.device)
+        raw = torch.from_numpy(blob).to(self.k.device)
+        off = 0
+        for t in (self.k, self.v, self.k_scale, self.v_scale):
+            shape = (t.shape[0], len(page_ids)) + tuple(t.shape[2:])
+            n = 1
+            for d in shape:
+                n *= d
+            nbytes = n * t.element_size()
+            src = raw[off : off + nbytes]
+            if t.dtype == torch.float8_e4m3fn:  # index ops go through the byte view (no fp8 index kernels on every device)
+                t.view(torch.uint8).index_copy_(1, idx, src.view(shape))
+            else:
+                t.index_copy_(1, idx, src.view(t.dtype).view(shape))
+            off += nbytes
+
     def bytes_per_token(self) -> int:
         return self.layers * self.kv_heads * (2 * self.head_dim + 8)
 

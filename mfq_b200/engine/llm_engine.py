@@ -43,11 +43,16 @@ class GenerationResult:
 
 class LLMEngine:
     def __init__(self, model: LlamaModel, *, max_batch: int = 64, max_seq_len: int = 8192, num_pages: int | None = None,
-                 device=None, use_graphs: bool = True, mtp_draft_tokens: int = 0, prefill_chunk: int = 8192) -> None:
+                 device=None, use_graphs: bool = True, mtp_draft_tokens: int = 0, prefill_chunk: int = 8192,
+                 prefix_cache=None, prefix_salt: str = "") -> None:
         """``mtp_draft_tokens`` (K, 0 = off): with a model that carries an MTP head, greedy rows decode by
         draft/verify cycles that confirm between 1 and K+1 tokens each (:meth:`mtp_step`)."""
         self.model = model
         self.prefill_chunk = prefill_chunk  # prompts longer than this are prefilled in chunks that attend to the cached past
+        # content-addressed KV blocks (mfq_b200.native.PrefixCache): a prompt whose leading 256-token blocks are cached
+        # gets their pages restored instead of recomputed.  `prefix_salt` must name the model (weights + KV format).
+        self.prefix_cache, self.prefix_salt = prefix_cache, prefix_salt
+        self.prefix_stats = {"lookups": 0, "blocks_hit": 0, "blocks_stored": 0, "tokens_skipped": 0}
         cfg = model.cfg
         has_head = getattr(model.w, "mtp", None) is not None
         self.mtp_k = mtp_draft_tokens if has_head else 0
@@ -207,7 +212,9 @@ class LLMEngine:
             self.rec_state.reset(row)
             state_slots = self.row_ids[row : row + 1]
         last = torch.tensor([n - 1], dtype=torch.int32, device=dev)
-        logits, hidden = self._prefill_span(row, seq_id, ids, 0, n, state_slots)
+        start, keys = self._restore_prefix(seq_id, token_ids, n)
+        logits, hidden = self._prefill_span(row, seq_id, ids, start, n, state_slots)
+        self._store_prefix(seq_id, keys, start)
         self.seq_lens[row] = n
         self.row_len[row] = n
         if self.row_stochastic[row]:
@@ -231,6 +238,46 @@ class LLMEngine:
             self.draft[row, 0] = self.model.sample_greedy(mlogits)[0]
             self._mtp_chain(row, row + 1, mhid[n - 1 : n].contiguous(), masked=False)
         return int(tok)
+
+    def _prefix_usable(self) -> bool:
+        # recurrent state and the MTP head's priming need every prompt position: those models always prefill in full
+        return self.prefix_cache is not None and self.rec_state is None and not self.mtp_k
+
+    def _restore_prefix(self, seq_id: int, token_ids, n: int):
+        """Restore the longest cached run of leading blocks into the sequence's pages.  Returns (tokens restored, keys
+        of all full blocks that may be cached: at least one token is always left to compute, for the logits)."""
+        if not self._prefix_usable():
+            return 0, None
+        pc = self.prefix_cache
+        bt = pc.block_tokens
+        usable = (n - 1) // bt * bt
+        if usable == 0:
+            return 0, None
+        keys = pc.keys(torch.as_tensor(token_ids, dtype=torch.int32)[:usable].numpy(), salt=self.prefix_salt)
+        self.prefix_stats["lookups"] += 1
+        pages = self.cache.allocator.owned[seq_id]
+        per_block = bt // self.cache.page_size
+        nbytes = self.cache.page_blob_bytes(per_block)
+        hit = 0
+        for i in range(pc.match(keys)):
+            blob = pc.get(keys[i], nbytes)
+            if blob is None or blob.nbytes != nbytes:
+                break
+            self.cache.import_pages(pages[i * per_block : (i + 1) * per_block], blob)
+            hit += 1
+        self.prefix_stats["blocks_hit"] += hit
+        self.prefix_stats["tokens_skipped"] += hit * bt
+        return hit * bt, keys
+
+    def _store_prefix(self, seq_id: int, keys, start: int) -> None:
+        if keys is None:
+            return
+        pc = self.prefix_cache
+        per_block = pc.block_tokens // self.cache.page_size
+        pages = self.cache.allocator.owned[seq_id]
+        for i in range(start // pc.block_tokens, len(keys)):
+            pc.put(keys[i], self.cache.export_pages(pages[i * per_block : (i + 1) * per_block]))
+            self.prefix_stats["blocks_stored"] += 1
 
     def _prefill_span(self, row: int, seq_id: int, ids: torch.Tensor, start: int, end: int, state_slots):
         """Run tokens ``[start, end)`` of the row's sequence (``ids`` holds the whole prompt, on the device) through

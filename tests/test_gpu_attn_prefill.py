@@ -84,3 +84,30 @@ def test_kv_gather_dequant_and_chunked_engine_prefill():
     kr, vr = ref.gather_slots(kv, row[(t // 16).long()] * 16 + t % 16)
     assert_close(kd.float(), kr.float(), rel=1e-2, what="gathered K")
     assert_close(vd.float(), vr.float(), rel=1e-2, what="gathered V")
+
+
+def test_prefix_cache_restores_pages_on_gpu(tmp_path):
+    import torch
+    from mfq_b200 import native
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.llama import LlamaConfig, LlamaModel, LlamaWeights
+    from gpu_common import check_status, require_gpu_lib
+    require_gpu_lib()
+    cfg = LlamaConfig.tiny()
+    w = LlamaWeights.random_init(cfg, "cuda", seed=2, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    shared = torch.randint(0, cfg.vocab_size, (300,), generator=g)
+    p1 = torch.cat([shared, torch.randint(0, cfg.vocab_size, (20,), generator=g)])
+    pc = native.PrefixCache(tmp_path / "kv", ram_budget=256 << 20, disk_budget=0, block_tokens=256)
+    eng = LLMEngine(LlamaModel(cfg, w), max_batch=2, max_seq_len=512, prefix_cache=pc, prefix_salt="tiny")
+    first = eng.generate([p1], 6).tokens[0].tolist()
+    assert eng.prefix_stats["blocks_stored"] == 1
+    eng.release(0)
+    again = eng.generate([p1], 6).tokens[0].tolist()  # 256 tokens restored, 64 recomputed against them
+    check_status()
+    assert eng.prefix_stats["blocks_hit"] == 1
+    n = 0
+    while n < 6 and first[n] == again[n]:
+        n += 1
+    assert n >= 5, (first, again)
+    pc.close()
