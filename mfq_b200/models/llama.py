@@ -305,7 +305,7 @@ class LlamaModel:
             row = step.block_table[0]
             if q.is_cuda:
                 kp, vp = ops.kernels.kv_gather_dequant(kv, row, step.past_len)
-                return ops.attn_prefill_bf16(q, torch.cat([kp, kd], 0), torch.cat([vp, vd], 0), self.sm_scale)
+                return ops.kernels.attn_prefill_bf16(q, torch.cat([kp, kd], 0), torch.cat([vp, vd], 0), self.sm_scale)
             ps = kv.page_size
             past = torch.arange(step.past_len)
             kp, vp = ref.gather_slots(kv, row[(past // ps).long()] * ps + past % ps)
