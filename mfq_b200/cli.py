@@ -211,6 +211,14 @@ def _cmd_serve(args) -> int:
         path = name_or_path if Path(name_or_path).exists() else args.model
         engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size,
                                         native_4bit=args.native_4bit, expert_slots=args.moe_gpu_cache_slots)
+        if args.session_cache_gb > 0:
+            from .engine.session_cache import SessionSnapshotCache
+            engine.session_cache = SessionSnapshotCache(int(args.session_cache_gb * (1 << 30)))
+        if args.prefix_cache_dir:
+            from . import native
+            engine.prefix_cache = native.PrefixCache(args.prefix_cache_dir, ram_budget=int(args.prefix_cache_ram_gb * (1 << 30)),
+                                                     disk_budget=int(args.prefix_cache_disk_gb * (1 << 30)))
+            engine.prefix_salt = f"{Path(path).name}:{Path(path).stat().st_size}"
         return engine, tok
 
     service.loader = loader
@@ -306,6 +314,11 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--session-cache-gb", type=float, default=8.0,
+                   help="host memory for per-conversation KV (+ recurrent state) snapshots, keyed by the request's session_id (0: off)")
+    s.add_argument("--prefix-cache-dir", default=None, help="directory of the content-addressed KV prefix cache (256-token blocks)")
+    s.add_argument("--prefix-cache-ram-gb", type=float, default=4.0)
+    s.add_argument("--prefix-cache-disk-gb", type=float, default=64.0)
     s.set_defaults(fn=_cmd_serve)
     be = sub.add_parser("bench", help="run the flagship benchmark (arguments are passed through to bench.py)")
     be.add_argument("rest", nargs=argparse.REMAINDER)

@@ -53,6 +53,7 @@ class LLMEngine:
         # gets their pages restored instead of recomputed.  `prefix_salt` must name the model (weights + KV format).
         self.prefix_cache, self.prefix_salt = prefix_cache, prefix_salt
         self.prefix_stats = {"lookups": 0, "blocks_hit": 0, "blocks_stored": 0, "tokens_skipped": 0}
+        self.session_cache = None  # a SessionSnapshotCache: per-conversation KV (+ recurrent state) snapshots
         cfg = model.cfg
         has_head = getattr(model.w, "mtp", None) is not None
         self.mtp_k = mtp_draft_tokens if has_head else 0
@@ -187,9 +188,11 @@ class LLMEngine:
             self.sampled[r] = int(torch.multinomial(p / p.sum(), 1, generator=g))
 
     # -- prefill -------------------------------------------------------------------------------------------------
-    def prefill(self, row: int, token_ids, params=None) -> int:
+    def prefill(self, row: int, token_ids, params=None, session: str | None = None) -> int:
         """Run the prompt of batch row ``row`` through the model; returns the first generated token id and leaves
-        the row ready for decode (``seq_lens[row]`` = prompt length, ``sampled[row]`` = first token)."""
+        the row ready for decode (``seq_lens[row]`` = prompt length, ``sampled[row]`` = first token).  With ``session``
+        and a :attr:`session_cache`, the history of that conversation is restored from its snapshot when the prompt
+        extends it."""
         dev = self.device
         ids = torch.as_tensor(token_ids, dtype=torch.int32)
         n = int(ids.numel())
@@ -212,7 +215,11 @@ class LLMEngine:
             self.rec_state.reset(row)
             state_slots = self.row_ids[row : row + 1]
         last = torch.tensor([n - 1], dtype=torch.int32, device=dev)
-        start, keys = self._restore_prefix(seq_id, token_ids, n)
+        start, keys = 0, None
+        if session is not None and self.session_cache is not None and not self.mtp_k:
+            start = self.session_cache.restore(self, row, session, [int(t) for t in ids.tolist()])
+        if start == 0:
+            start, keys = self._restore_prefix(seq_id, token_ids, n)
         logits, hidden = self._prefill_span(row, seq_id, ids, start, n, state_slots)
         self._store_prefix(seq_id, keys, start)
         self.seq_lens[row] = n
@@ -238,6 +245,14 @@ class LLMEngine:
             self.draft[row, 0] = self.model.sample_greedy(mlogits)[0]
             self._mtp_chain(row, row + 1, mhid[n - 1 : n].contiguous(), masked=False)
         return int(tok)
+
+    def save_session(self, row: int, session: str, tokens) -> None:
+        """Keep row ``row``'s KV pages (and recurrent state) as the snapshot of conversation ``session``.  ``tokens``
+        is the conversation so far; only the part whose KV is in the cache (``seq_lens[row]`` tokens) is covered."""
+        if self.session_cache is None or self.mtp_k:
+            return
+        n = int(self.seq_lens[row])
+        self.session_cache.save(self, row, session, [int(t) for t in tokens[:n]])
 
     def _prefix_usable(self) -> bool:
         # recurrent state and the MTP head's priming need every prompt position: those models always prefill in full

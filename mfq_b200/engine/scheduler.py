@@ -69,6 +69,7 @@ class Request:
     priority: int = 0
     timeout_seconds: float | None = None
     on_event: Callable[["Event"], None] | None = None
+    session: str | None = None  # conversation id: the backend may keep / restore a snapshot of its KV state
     id: int = -1
     # runtime state
     arrival: float = 0.0
@@ -187,6 +188,14 @@ class ContinuousBatchScheduler:
         self.stats.failed += 1
         self._emit(req, Event("failed", req.id, error_code=req.finish_reason, metrics=self._metrics(req)))
 
+    def _snapshot(self, req: Request) -> None:
+        """A finished turn of a conversation leaves its KV state with the backend for the next turn."""
+        if req.session is not None and hasattr(self.backend, "save_session"):
+            try:
+                self.backend.save_session(req.row, req.session, req.context)
+            except Exception:  # a snapshot is an optimisation: never fail the request over it
+                pass
+
     def _release(self, row: int) -> None:
         self.running.pop(row, None)
         self.backend.release(row)
@@ -268,7 +277,10 @@ class ContinuousBatchScheduler:
             self.running[row] = req
             self.stats.admitted += 1
             try:
-                tok = self.backend.prefill(row, req.context, req.params)
+                if req.session is not None and hasattr(self.backend, "save_session"):
+                    tok = self.backend.prefill(row, req.context, req.params, session=req.session)
+                else:
+                    tok = self.backend.prefill(row, req.context, req.params)
             except MemoryError:
                 self.running.pop(row, None)
                 self.backend.release(row)
@@ -282,6 +294,7 @@ class ContinuousBatchScheduler:
                 return True
             self.stats.prefill_tokens += len(req.context)
             if self._accept_token(req, tok):
+                self._snapshot(req)
                 self._release(row)
                 self._finish(req, req.finish_reason)
             return True
@@ -320,6 +333,7 @@ class ContinuousBatchScheduler:
             for tok in produced:  # an MTP cycle confirms several tokens; a stop token or the length cap ends early
                 self.stats.decode_tokens += 1
                 if self._accept_token(req, tok):
+                    self._snapshot(req)
                     self._release(row)
                     self._finish(req, req.finish_reason)
                     break

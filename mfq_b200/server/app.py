@@ -6,7 +6,7 @@ Route and payload parity with the reference server (``mfq/server/api/routes/open
 * ``GET /health``, ``GET /v1``, ``GET /v1/models``, ``GET /v1/models/{id}``
 * ``POST /v1/chat/completions`` -- JSON or SSE ``chat.completion.chunk`` stream; accepts ``max_tokens``,
   ``temperature``, ``top_p``, ``top_k``, ``presence_penalty``, ``frequency_penalty``, ``repetition_penalty``,
-  ``seed``, ``stop``, ``stream``, ``priority``, ``timeout_seconds``, ``enable_mtp``, ``mtp_max_draft_tokens``
+  ``seed``, ``stop``, ``stream``, ``priority``, ``timeout_seconds``, ``session_id`` (KV snapshot reuse across turns), ``enable_mtp``, ``mtp_max_draft_tokens``
 * ``POST /v1/messages`` (Anthropic; stream or not), ``POST /v1/messages/count_tokens`` -> 501
 * ``GET /metrics`` (text 0.0.4), ``/api/v1/runtime/{status,instances,concurrency}``,
   ``POST /api/v1/models/{load,unload}``
@@ -154,7 +154,8 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None)
         try:
             req, events = await asyncio.get_running_loop().run_in_executor(
                 None, lambda: service.submit(lm, ids, params, priority=int(body.get("priority", 0) or 0),
-                                             timeout_seconds=body.get("timeout_seconds")))
+                                             timeout_seconds=body.get("timeout_seconds"),
+                                             session=body.get("session_id")))
         except QueueFull as exc:
             return None, error_response(429, "runtime_queue_full", str(exc), retryable=True)
         except BackendFailure as exc:

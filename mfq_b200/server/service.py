@@ -83,9 +83,10 @@ class ModelService:
 
     # ---- requests ------------------------------------------------------------------------------------------------
     def submit(self, model: LoadedModel, prompt_ids: list[int], params: SamplingParams, *, priority: int = 0,
-               timeout_seconds: float | None = None) -> tuple[Request, "queue.Queue[Event]"]:
+               timeout_seconds: float | None = None, session: str | None = None) -> tuple[Request, "queue.Queue[Event]"]:
         events: "queue.Queue[Event]" = queue.Queue()
-        req = Request(prompt_ids, params, priority=priority, timeout_seconds=timeout_seconds, on_event=events.put)
+        req = Request(prompt_ids, params, priority=priority, timeout_seconds=timeout_seconds, on_event=events.put,
+                      session=str(session) if session else None)
         done = threading.Event()
         box: dict = {}
         self._inbox.put(("submit", model, req, box, done))
