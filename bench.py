@@ -205,6 +205,93 @@ def run_ours(args) -> dict:
     return result if rank == 0 else {}
 
 
+def run_hybrid(args) -> dict:
+    """Second model family (one GPU): the Qwen3-Next-style 80B-total / 3B-active hybrid -- 36 Gated-DeltaNet layers,
+    12 gated-attention layers with 256-wide heads, 512 routed experts (top 10) + a shared expert per layer, an MTP
+    draft head -- all weights in block FP8 (about 80 GB).  Reports prefill of one prompt, single-stream decode without
+    and with draft/verify cycles, and batched decode."""
+    import torch
+
+    from mfq_b200 import ops
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.hybrid import HybridConfig, HybridModel, random_hybrid_weights
+
+    if args.gpus != 1:
+        raise SystemExit("--model hybrid80b runs on one GPU")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = HybridConfig.tiny() if args.tiny else HybridConfig.next_80b()
+    batch, ctx, new = args.batch, args.context, args.steps + args.warmup + 8
+    t0 = time.time()
+    weights = random_hybrid_weights(cfg, dev, seed=0, mtp=True)
+    torch.cuda.synchronize()
+    build_s = time.time() - t0
+    engine = LLMEngine(HybridModel(cfg, weights), max_batch=batch, max_seq_len=ctx + 4 * new + 16, mtp_draft_tokens=1)
+    gen = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab_size, (ctx,), generator=gen) for _ in range(batch)]
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(0) as clocks:
+            a.record()
+            for _ in range(steps):
+                fn()
+            z.record()
+            torch.cuda.synchronize()
+        return a.elapsed_time(z), clocks.summary()
+
+    engine.prefill(0, prompts[0])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    engine.prefill(0, prompts[0])
+    e1.record()
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1)
+    for row in range(batch):
+        if row:
+            engine.prefill(row, prompts[row])
+        engine.grow(row, ctx + 4 * new + 8)
+    engine.active.fill_(1)
+    torch.cuda.synchronize()
+    ops.Workspace.get(dev).check()
+    ms64, clocks = timed(lambda: engine.decode_step(batch), args.steps, args.warmup)
+    ms1, _ = timed(lambda: engine.decode_step(1), args.steps, args.warmup)
+    cycles0 = dict(engine.mtp_stats())
+    ms1_mtp, _ = timed(lambda: engine.mtp_step(1), args.steps, args.warmup)
+    stats = engine.mtp_stats()
+    ms64_mtp, _ = timed(lambda: engine.mtp_step(batch), args.steps, args.warmup)
+    torch.cuda.synchronize()
+    ops.Workspace.get(dev).check()
+    value = batch * args.steps / (ms64 / 1e3)
+    return {
+        "metric": "decode_tok_s_bs64", "value": round(value, 2), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms64 / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / PUBLISHED_BATCHED_DECODE_TOK_S, 2),
+        "dtype": "fp8_e4m3 weights/activations/KV, bf16 residual stream, fp32 accumulate and recurrent state",
+        "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)", "impl": "ours",
+        "config": {"model": cfg.name, "global_batch": batch, "seq_len": ctx, "parallelism": "dp1",
+                   "weights_gb": round(weights.nbytes() / 1e9, 1) if hasattr(weights, "nbytes") else None,
+                   "l2": "inputs larger than L2 (the routed experts of a step alone exceed it)"},
+        "clocks": clocks,
+        "extra": {"decode_tok_s_bs1": round(args.steps / (ms1 / 1e3), 2), "ms_per_step_bs1": round(ms1 / args.steps, 4),
+                  "mtp_cycle_ms_bs1": round(ms1_mtp / args.steps, 4), "mtp_cycle_ms_bs64": round(ms64_mtp / args.steps, 4),
+                  "mtp_acceptance_random_head": stats.get("acceptance_rate"),
+                  "mtp_note": "one draft token per cycle; a random-init draft head is never accepted, so a cycle yields one "
+                              "token here -- at the reference's published 88% acceptance a cycle yields 1.88",
+                  "decode_tok_s_bs1_mtp_at_88pct": round(1.88 * args.steps / (ms1_mtp / 1e3), 2),
+                  "prefill_tok_s": round(ctx / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 2),
+                  "weight_build_s": round(build_s, 1),
+                  "vs_baseline_bs1": round(args.steps / (ms1 / 1e3) / 62.9, 2),
+                  "vs_baseline_prefill": round(ctx / (prefill_ms / 1e3) / 1779.7, 2),
+                  "baseline_note": "reference: same model family (V1-S tier) on one RTX 3090 Ti + 32 GiB host RAM: prefill 1,779.7, "
+                                   "decode 62.9, MTP decode 87.0 tok/s; continuous batching 156.56 tok/s"},
+    }
+
+
 def run_reference(args) -> dict:
     from baseline import reference_arm
     return reference_arm.run(args)
@@ -224,10 +311,15 @@ def main() -> None:
     ap.add_argument("--weights", choices=["fp8", "w4"], default="fp8",
                     help="block linears in block-scaled FP8 (default) or in the 4-bit NINT-native format (single GPU)")
     ap.add_argument("--tiny", action="store_true", help="tiny model, for checking the harness itself")
+    ap.add_argument("--model", choices=["llama8b", "hybrid80b"], default="llama8b",
+                    help="llama8b: the flagship; hybrid80b: the Gated-DeltaNet + MoE hybrid with an MTP head (one GPU)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        out = run_reference(args)
+    else:
+        out = run_hybrid(args) if args.model == "hybrid80b" else run_ours(args)
     if out:
         print(json.dumps(out), flush=True)
 

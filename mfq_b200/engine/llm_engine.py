@@ -194,6 +194,7 @@ class LLMEngine:
         and a :attr:`session_cache`, the history of that conversation is restored from its snapshot when the prompt
         extends it."""
         dev = self.device
+        self._bind_state()
         ids = torch.as_tensor(token_ids, dtype=torch.int32)
         n = int(ids.numel())
         if n + 1 > self.max_seq_len:
@@ -253,6 +254,11 @@ class LLMEngine:
             return
         n = int(self.seq_lens[row])
         self.session_cache.save(self, row, session, [int(t) for t in tokens[:n]])
+
+    def _bind_state(self) -> None:
+        """Engines that share one model object each own a recurrent state: point the model at this engine's."""
+        if self.rec_state is not None:
+            self.model.state = self.rec_state
 
     def _prefix_usable(self) -> bool:
         # recurrent state and the MTP head's priming need every prompt position: those models always prefill in full
@@ -372,6 +378,7 @@ class LLMEngine:
 
     def decode_step(self, b: int, stochastic: bool = False) -> None:
         """Advance the active rows among ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device)."""
+        self._bind_state()
         if not self.use_graphs:
             self._decode_body(b, stochastic)
             return
@@ -451,6 +458,7 @@ class LLMEngine:
         """One draft/verify cycle for the active rows among ``[0, b)``: confirms ``n_out[r]`` in 1..K+1 tokens per
         row (``out_tokens[r, :n_out[r]]``), all state stays on the device (one CUDA graph per batch bucket)."""
         self.mtp_cycles += 1
+        self._bind_state()
         if not self.use_graphs:
             self._mtp_body(b)
             return

@@ -27,7 +27,7 @@ from .. import ops
 from ..ops import gdn
 from ..ops import reference as ref
 from .llama import Fp8Linear, LlamaLayer, StepBuffers
-from .moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeLayer, MoeWeights, _to_float
+from .moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeFfn, MoeLayer, MoeWeights, _to_float
 
 
 @dataclass
@@ -47,6 +47,15 @@ class HybridConfig(MoeDecoderConfig):
     @property
     def conv_dim(self) -> int:
         return (2 * self.linear_k_heads + self.linear_v_heads) * self.linear_head_dim
+
+    @classmethod
+    def next_80b(cls) -> "HybridConfig":
+        """Qwen3-Next-style 80B-total / 3B-active hybrid: 48 layers in a 3 linear : 1 full attention pattern, 512 routed
+        experts (top 10) plus one shared expert per layer, 256-wide attention heads."""
+        return cls(vocab_size=151936, hidden_size=2048, intermediate_size=5120, num_layers=48, num_heads=16, num_kv_heads=2,
+                   head_dim=256, rope_theta=1e7, rms_eps=1e-6, num_experts=512, top_k=10, moe_intermediate=512,
+                   shared_intermediate=512, full_attention_interval=4, linear_k_heads=16, linear_v_heads=32,
+                   linear_head_dim=128, name="hybrid-next-80b-fp8")
 
     @classmethod
     def tiny(cls) -> "HybridConfig":
@@ -114,7 +123,27 @@ class GdnState:
         return self.conv[j], self.state[j]
 
 
+def _tensor_bytes(obj, seen=None) -> int:
+    """Bytes of every tensor reachable through dataclass fields, lists and tuples of ``obj``."""
+    seen = set() if seen is None else seen
+    if isinstance(obj, torch.Tensor):
+        if obj.data_ptr() in seen:
+            return 0
+        seen.add(obj.data_ptr())
+        return obj.numel() * obj.element_size()
+    if isinstance(obj, (list, tuple)):
+        return sum(_tensor_bytes(o, seen) for o in obj)
+    if hasattr(obj, "__dataclass_fields__"):
+        return sum(_tensor_bytes(getattr(obj, f), seen) for f in obj.__dataclass_fields__)
+    if hasattr(obj, "__dict__") and not isinstance(obj, type):
+        return sum(_tensor_bytes(v, seen) for v in vars(obj).values() if isinstance(v, (torch.Tensor, list, tuple)) or hasattr(v, "__dataclass_fields__"))
+    return 0
+
+
 class HybridWeights(MoeWeights):
+    def nbytes(self) -> int:
+        return _tensor_bytes(self)
+
     @classmethod
     def from_tensors(cls, cfg: HybridConfig, tensors, device, tp_rank: int = 0, tp_size: int = 1) -> "HybridWeights":
         """Rank-local FP8 weights from canonical checkpoint tensors.  Linear-attention heads, like attention heads,
@@ -160,6 +189,76 @@ class HybridWeights(MoeWeights):
                     hl.gated = True
             layers.append(hl)
         return cls(base.embed, layers, base.final_norm, base.lm_head, tp_rank, tp_size)
+
+
+def _quant_stack(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``[E, N, K]`` float -> (E4M3 ``[E, N, K]``, fp32 scales ``[E, N/128, K/128]``), N and K multiples of 128."""
+    e, n, k = w.shape
+    tiles = w.float().reshape(e, n // 128, 128, k // 128, 128)
+    scale = (tiles.abs().amax(dim=(2, 4)) / 448.0).clamp_min(1e-12)
+    q = (tiles / scale[:, :, None, :, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return q.reshape(e, n, k).contiguous(), scale.contiguous()
+
+
+def random_hybrid_weights(cfg: HybridConfig, device, seed: int = 0, std: float = 0.02, mtp: bool = False,
+                          expert_chunk: int = 64) -> HybridWeights:
+    """N(0, std) weights drawn and quantized to block FP8 on ``device``, layer by layer (single GPU).  Only one chunk of
+    ``expert_chunk`` experts exists in float at a time, so the 80B configuration builds inside its FP8 footprint."""
+    from .llama import MtpHead
+    dev = torch.device(device)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    h, d, hq, hkv = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+    ld, lk, lv = cfg.linear_head_dim, cfg.linear_k_heads, cfg.linear_v_heads
+    e, mi, si = cfg.num_experts, cfg.moe_intermediate, cfg.shared_intermediate
+
+    def rnd(*shape, scale=std):
+        return torch.randn(shape, generator=gen, device=dev, dtype=torch.float32).mul_(scale).to(torch.bfloat16)
+
+    def ones(n):
+        return torch.ones(n, dtype=torch.bfloat16, device=dev)
+
+    def experts(n, k):
+        qs, ss = [], []
+        for lo in range(0, e, expert_chunk):
+            q, s_ = _quant_stack(rnd(min(expert_chunk, e - lo), n, k))
+            qs.append(q)
+            ss.append(s_)
+        return torch.cat(qs), torch.cat(ss)
+
+    def moe():
+        gu_q, gu_s = experts(2 * mi, h)
+        dn_q, dn_s = experts(h, mi)
+        ffn = MoeFfn(router=rnd(e, h), router_bias=None, gate_up=gu_q, gate_up_scale=gu_s, down=dn_q, down_scale=dn_s)
+        if si:
+            ffn.shared_gate_up = Fp8Linear.from_float(rnd(2 * si, h))
+            ffn.shared_down = Fp8Linear.from_float(rnd(h, si))
+        return ffn
+
+    layers = []
+    for i in range(cfg.num_layers):
+        layer = HybridLayer(attn_norm=ones(h), qkv=None, o_proj=None, mlp_norm=ones(h), gate_up=None, down=None, moe=moe())
+        if cfg.is_linear(i):
+            rows = 2 * lk * ld + 2 * lv * ld + 2 * lv  # q | k | v | z | b | a
+            layer.gdn = GdnWeights(Fp8Linear.from_float(rnd(rows, h)), rnd(cfg.conv_dim, 4, scale=0.3).float().contiguous(),
+                                   torch.zeros(lv, dtype=torch.float32, device=dev).uniform_(-2.0, 0.5, generator=gen),
+                                   rnd(lv, scale=0.5).float().contiguous(), (1 + rnd(ld, scale=0.1).float()).contiguous(),
+                                   Fp8Linear.from_float(rnd(h, lv * ld)), lk, lv)
+        else:
+            gate_rows = hq * d if cfg.attn_output_gate else 0
+            layer.qkv = Fp8Linear.from_float(rnd((hq + 2 * hkv) * d + gate_rows, h))
+            layer.o_proj = Fp8Linear.from_float(rnd(h, hq * d))
+            layer.gated = bool(gate_rows)
+            if cfg.qk_norm:
+                layer.q_norm, layer.k_norm = (1 + rnd(d, scale=0.1).float()).contiguous(), (1 + rnd(d, scale=0.1).float()).contiguous()
+        layers.append(layer)
+    head = None
+    if mtp:
+        # the draft head: one dense-attention block with a routed FFN of its own, fed by eh_proj([embed; hidden])
+        blk = HybridLayer(attn_norm=ones(h), qkv=Fp8Linear.from_float(rnd((hq + 2 * hkv) * d, h)),
+                          o_proj=Fp8Linear.from_float(rnd(h, hq * d)), mlp_norm=ones(h), gate_up=None, down=None, moe=moe())
+        head = MtpHead(ones(h), ones(h), Fp8Linear.from_float(rnd(h, 2 * h)), blk)
+    return HybridWeights(rnd(cfg.vocab_size, h), layers, ones(h), Fp8Linear.from_float(rnd(cfg.vocab_size, h)), 0, 1, head)
 
 
 def _with_placeholders(cfg: HybridConfig, tensors):

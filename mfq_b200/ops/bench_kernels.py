@@ -99,17 +99,16 @@ def bench_attn(batch: int, ctx: int, hq: int, hk: int, d: int, splits: int, reps
     kvs = [cache.layer(i) for i in range(layers)]
     ms = time_ms(lambda i: K.paged_attn_decode(q, kvs[i % layers], cache.block_table, sl, sm_scale=0.088, splits=splits, out=out), reps)
     byt = batch * ctx * hk * (2 * d + 8)
-    return {"kernel": "paged_attn_decode", "batch": batch, "ctx": ctx, "splits": splits, "us": ms * 1e3, "gbs": byt / ms / 1e6}
+    return {"kernel": "paged_attn_decode", "batch": batch, "ctx": ctx, "hq": hq, "hk": hk, "d": d, "splits": splits, "us": ms * 1e3, "gbs": byt / ms / 1e6}
 
 
-def bench_prefill(t: int, hq: int, hk: int, reps: int) -> list[dict]:
-    d = 128
+def bench_prefill(t: int, hq: int, hk: int, reps: int, d: int = 128) -> list[dict]:
     q = torch.randn((t, hq, d), device="cuda").to(torch.bfloat16)
     k = torch.randn((t, hk, d), device="cuda").to(torch.bfloat16)
     v = torch.randn((t, hk, d), device="cuda").to(torch.bfloat16)
     out = torch.empty_like(q)
     ms = time_ms(lambda _: K.attn_prefill_bf16(q, k, v, 0.088, out=out), reps)
-    rows = [{"kernel": "attn_prefill_bf16", "t": t, "hq": hq, "hk": hk, "us": ms * 1e3,
+    rows = [{"kernel": "attn_prefill_bf16", "t": t, "hq": hq, "hk": hk, "d": d, "us": ms * 1e3,
              "tflops": 4 * t * t * hq * d / 2 / ms / 1e9}]
     pages = math.ceil(t / 16)
     cache = PagedKVCache(layers=1, kv_heads=hk, head_dim=d, num_pages=pages + 1, max_seqs=1, max_pages_per_seq=pages, device="cuda")
@@ -143,30 +142,35 @@ def main() -> None:
     ap.add_argument("--json", default="")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--only", default="", help="comma separated kernel families: gemm,attn,small,prefill")
+    ap.add_argument("--only", default="", help="comma separated kernel families: gemm,w4,attn,small,prefill")
     args = ap.parse_args()
     pk = peaks()
     rows = []
+    only = set(filter(None, args.only.split(",")))
+    want = lambda family: not only or family in only
     shapes = [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336), ("lm_head", 128256, 4096)]
-    for m in ((1, 64) if args.quick else (1, 16, 64, 512, 4096)):
+    for m in ((1, 64) if args.quick else (1, 16, 64, 512, 4096)) if want("gemm") else ():
         for name, n, k in shapes:
             if name == "lm_head" and m > 64:
                 continue
             r = bench_gemm(m, n, k, args.reps)
             r["name"] = name
             rows.append(r)
-    for m in ((1, 64) if args.quick else (1, 16, 64, 512, 4096)):
+    for m in ((1, 64) if args.quick else (1, 16, 64, 512, 4096)) if want("w4") else ():
         for name, n, k in shapes[:4]:
             r = bench_w4_gemm(m, n, k, args.reps)
             r["name"] = name
             rows.append(r)
-    for batch, ctx in ((1, 4096), (64, 4096)):
+    for batch, ctx in ((1, 4096), (64, 4096)) if want("attn") else ():
         for splits in (1, 4, K.attn_splits_for(batch, 8, ctx)):
             rows.append(bench_attn(batch, ctx, 32, 8, 128, splits, args.reps))
-    for m in (1, 64, 4096):
+        # 256-wide heads of the hybrid model: 16 query heads on 2 KV heads
+        rows.append(bench_attn(batch, ctx, 16, 2, 256, K.attn_splits_for(batch, 2, ctx), args.reps))
+    for m in (1, 64, 4096) if want("small") else ():
         rows += bench_small(m, 4096, 14336, args.reps)
-    for t in (1024, 4096):
+    for t in (1024, 4096) if want("prefill") else ():
         rows += bench_prefill(t, 32, 8, args.reps)
+        rows += bench_prefill(t, 16, 2, args.reps, d=256)[:1]
     for r in rows:
         if "gbs" in r:
             r["hbm_frac"] = r["gbs"] / pk["hbm_gbs"]

@@ -319,6 +319,9 @@ extern "C" int mfq_paged_attn_decode_mma(const void* q, const void* k_cache, con
   if (D == 128)
     return mfq::launch_attn<128>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_acc, part_ml,
                                  B, Hq, Hk, max_pages, sm_scale, splits, q_len, status, stream);
+  if (D == 256)
+    return mfq::launch_attn<256>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_acc, part_ml,
+                                 B, Hq, Hk, max_pages, sm_scale, splits, q_len, status, stream);
   if (D == 64)
     return mfq::launch_attn<64>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_acc, part_ml, B,
                                 Hq, Hk, max_pages, sm_scale, splits, q_len, status, stream);

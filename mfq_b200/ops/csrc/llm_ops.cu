@@ -391,6 +391,51 @@ __global__ void argmax_kernel(const __nv_bfloat16* __restrict__ logits, int* __r
   }
 }
 
+// Wide vocabularies, few rows: the row is split over several CTAs.  Each folds its best (value, index) into a 64-bit
+// key -- order-preserving value bits above the inverted index, so the larger value and then the lower index win an
+// atomicMax -- and the last CTA of the row to arrive writes the result and clears the row's scratch for the next
+// launch.  The scratch is static device memory: nothing to allocate, safe under graph capture; launches that share
+// it must be ordered on one stream.
+constexpr int kArgmaxRows = 8192;
+__device__ unsigned long long g_argmax_key[kArgmaxRows];
+__device__ unsigned int g_argmax_count[kArgmaxRows];
+
+__global__ void argmax_split_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, int V, int stride) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ unsigned long long sk[8];
+  const int b = blockIdx.x, seg = blockIdx.y, nseg = gridDim.y;
+  const int per = (V + nseg - 1) / nseg;
+  const int lo = seg * per, hi = min(V, lo + per);
+  const __nv_bfloat16* row = logits + size_t(b) * stride;
+  unsigned long long key = 0ull;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const uint32_t u = __float_as_uint(__bfloat162float(row[i]));
+    const uint32_t ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    const unsigned long long k = (static_cast<unsigned long long>(ord) << 32) | (0xffffffffu - uint32_t(i));
+    key = k > key ? k : key;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+    key = other > key ? other : key;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sk[warp] = key;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x >> 5); ++w) key = sk[w] > key ? sk[w] : key;
+    atomicMax(&g_argmax_key[b], key);
+    __threadfence();
+    if (atomicAdd(&g_argmax_count[b], 1u) == uint32_t(nseg - 1)) {
+      __threadfence();
+      const unsigned long long best = atomicExch(&g_argmax_key[b], 0ull);
+      out[b] = int(0xffffffffu - uint32_t(best & 0xffffffffull));
+      g_argmax_count[b] = 0u;
+    }
+  }
+}
+
 __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                              __nv_bfloat16* __restrict__ out, int H) {
   pdl_trigger();
@@ -430,6 +475,8 @@ extern "C" int mfq_rmsnorm_quant(const void* x, const void* residual, void* resi
   int threads = ((H / 8 + kNormVecs - 1) / kNormVecs + 31) / 32 * 32;
   if (threads < 32) threads = 32;
   if (threads > 1024) return -1;
+  // few rows (decode): the kernel is pure latency, so spread a row over as many threads as it has 16-byte vectors
+  if (M <= 1024) threads = min(1024, max(threads, (H / 8 + 31) / 32 * 32));
   launch_kernel(rmsnorm_quant_kernel, dim3(M), dim3(threads), 0, stream,
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
       static_cast<__nv_bfloat16*>(residual_out), static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q_out),
@@ -491,7 +538,11 @@ extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const in
 }
 
 extern "C" int mfq_argmax(const void* logits, int* out, int B, int V, int stride, cudaStream_t stream) {
-  launch_kernel(argmax_kernel, dim3(B), dim3(1024), 0, stream, static_cast<const __nv_bfloat16*>(logits), out, V, stride);
+  const int segs = V / 4096 > 32 ? 32 : V / 4096;
+  if (segs >= 2 && B <= kArgmaxRows && B * segs <= 4096)
+    launch_kernel(argmax_split_kernel, dim3(B, segs), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(logits), out, V, stride);
+  else
+    launch_kernel(argmax_kernel, dim3(B), dim3(1024), 0, stream, static_cast<const __nv_bfloat16*>(logits), out, V, stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 

@@ -25,7 +25,102 @@ struct RouterParams {
   int norm_topk;               // normalise the K selected weights to sum 1
   float scale;                 // multiplier on the final weights (routed scaling factor)
   int n_group, topk_group;     // group-limited routing (n_group <= 1: off)
+  const float* logits;         // [T, E] precomputed router logits (null: this kernel computes the dot products)
 };
+
+// ---------------------------------------------------------------------------------------------
+// Router logits on tensor cores: logits[t, e] = x[t, :] . w[e, :]  (bf16 in, fp32 accumulate, mma.sync m16n8k16).
+// A dot product does not care about the order of its terms, so a thread loads 8 contiguous elements of a row (16 bytes)
+// and feeds them to two MMAs as its k-slots; the x and w fragments use the same assignment, which keeps the result exact.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 ld_row16(const __nv_bfloat16* base, int row, int rows, int H, int k) {
+  return row < rows ? __ldg(reinterpret_cast<const uint4*>(base + size_t(row) * H + k)) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// Few tokens (T <= 16 * MB <= 64): one CTA per 8 experts, its 4 warps split the hidden dimension and every warp
+// covers all tokens, so E / 8 CTAs stream the router matrix once.
+template <int MB>
+__global__ void __launch_bounds__(128) router_logits_small_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                  const __nv_bfloat16* __restrict__ w,
+                                                                  float* __restrict__ logits, int T, int H, int E) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float part[4][MB * 16][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, c = lane & 3;
+  const int e0 = blockIdx.x * 8;
+  const int chunks = H / 32, per = (chunks + 3) / 4;
+  const int c_lo = warp * per, c_hi = min(chunks, c_lo + per);
+  float acc[MB][4];
+#pragma unroll
+  for (int m = 0; m < MB; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+#pragma unroll 4
+  for (int ch = c_lo; ch < c_hi; ++ch) {
+    const int k = ch * 32 + 8 * c;
+    const uint4 b = ld_row16(w, e0 + g8, E, H, k);
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      const uint4 lo = ld_row16(x, m * 16 + g8, T, H, k);
+      const uint4 hi = ld_row16(x, m * 16 + g8 + 8, T, H, k);
+      mma_bf16(acc[m], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
+      mma_bf16(acc[m], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MB; ++m) {
+    part[warp][m * 16 + g8][2 * c] = acc[m][0];
+    part[warp][m * 16 + g8][2 * c + 1] = acc[m][1];
+    part[warp][m * 16 + g8 + 8][2 * c] = acc[m][2];
+    part[warp][m * 16 + g8 + 8][2 * c + 1] = acc[m][3];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < MB * 16 * 8; i += 128) {
+    const int t = i >> 3, col = i & 7;
+    if (t < T && e0 + col < E) logits[size_t(t) * E + e0 + col] = part[0][t][col] + part[1][t][col] + part[2][t][col] + part[3][t][col];
+  }
+}
+
+// Many tokens: a CTA computes 64 tokens x 64 experts, one warp per 16 tokens.
+__global__ void __launch_bounds__(128) router_logits_tile_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                 const __nv_bfloat16* __restrict__ w,
+                                                                 float* __restrict__ logits, int T, int H, int E) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, c = lane & 3;
+  const int t0 = blockIdx.x * 64 + warp * 16, e0 = blockIdx.y * 64;
+  float acc[8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll 2
+  for (int k0 = 0; k0 < H; k0 += 32) {
+    const int k = k0 + 8 * c;
+    const uint4 lo = ld_row16(x, t0 + g8, T, H, k);
+    const uint4 hi = ld_row16(x, t0 + g8 + 8, T, H, k);
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const uint4 b = ld_row16(w, e0 + n * 8 + g8, E, H, k);
+      mma_bf16(acc[n], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
+      mma_bf16(acc[n], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < 8; ++n) {
+    const int e = e0 + n * 8 + 2 * c;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int t = t0 + g8 + 8 * half;
+      if (t < T) {
+        if (e < E) logits[size_t(t) * E + e] = acc[n][2 * half];
+        if (e + 1 < E) logits[size_t(t) * E + e + 1] = acc[n][2 * half + 1];
+      }
+    }
+  }
+}
 
 // One CTA per token: router logits by warp-striped dot products, scoring, optional group limiting, K rounds of block
 // arg-max (lowest index wins ties).
@@ -38,9 +133,13 @@ __global__ void __launch_bounds__(256) moe_router_topk_kernel(const RouterParams
   __shared__ int red_i[8];
   __shared__ float grp[64];
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < p.H; i += 256) xs[i] = __bfloat162float(p.x[size_t(t) * p.H + i]);
+  if (p.logits) {
+    for (int e = tid; e < p.E; e += 256) sc[e] = p.logits[size_t(t) * p.E + e];
+  } else {
+    for (int i = tid; i < p.H; i += 256) xs[i] = __bfloat162float(p.x[size_t(t) * p.H + i]);
+  }
   __syncthreads();
-  for (int e = warp; e < p.E; e += 8) {
+  for (int e = warp; e < (p.logits ? 0 : p.E); e += 8) {
     const __nv_bfloat16* wr = p.w + size_t(e) * p.H;
     float acc = 0.f;
     for (int i = lane * 2; i < p.H; i += 64) {
@@ -161,20 +260,44 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
     if (e >= 0 && e < n_local) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0, tiles = 0;
-    for (int e = 0; e < n_local; ++e) {
-      const int c = cnt[e];
-      offsets[e] = run;
-      fill[e] = run;
-      tbase[e] = tiles;
-      run += c;
-      tiles += (c + token_tile - 1) / token_tile;
+  {
+    // exclusive prefix sums of the per-expert row and tile counts: one expert per thread, warp scans, then a scan of
+    // the 32 warp totals (the block has 1024 threads and at most 512 experts)
+    __shared__ int wrow[32], wtile[32];
+    const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+    const int c = e < n_local ? cnt[e] : 0;
+    const int tl = (c + token_tile - 1) / token_tile;
+    int ir = c, it = tl;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int ur = __shfl_up_sync(0xffffffffu, ir, o), ut = __shfl_up_sync(0xffffffffu, it, o);
+      if (lane >= o) { ir += ur; it += ut; }
     }
-    offsets[n_local] = run;
-    tbase[n_local] = tiles;
-    totals[0] = run;
-    totals[1] = tiles;
+    if (lane == 31) { wrow[warp] = ir; wtile[warp] = it; }
+    __syncthreads();
+    if (warp == 0) {
+      int vr = wrow[lane], vt = wtile[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int ur = __shfl_up_sync(0xffffffffu, vr, o), ut = __shfl_up_sync(0xffffffffu, vt, o);
+        if (lane >= o) { vr += ur; vt += ut; }
+      }
+      wrow[lane] = vr;
+      wtile[lane] = vt;
+    }
+    __syncthreads();
+    const int base_r = warp ? wrow[warp - 1] : 0, base_t = warp ? wtile[warp - 1] : 0;
+    if (e < n_local) {
+      offsets[e] = base_r + ir - c;
+      fill[e] = base_r + ir - c;
+      tbase[e] = base_t + it - tl;
+    }
+    if (e == n_local) {  // totals: everything before this (empty) slot
+      offsets[n_local] = base_r + ir;
+      tbase[n_local] = base_t + it;
+      totals[0] = base_r + ir;
+      totals[1] = base_t + it;
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < entries; i += blockDim.x) {
@@ -251,12 +374,25 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const in
 
 using namespace mfq;
 
+// ``logits``: optional [T, E] fp32 scratch.  With it (and H a multiple of 32) the dot products run on tensor cores
+// spread over the whole GPU and the per-token CTAs only score and select; without it one CTA per token does everything.
 extern "C" int mfq_moe_router_topk(const void* x, const void* w, const float* bias, int* topk_ids, float* topk_w,
-                                   float* scores_out, int T, int H, int E, int K, int sigmoid, int norm_topk, float scale,
-                                   int n_group, int topk_group, cudaStream_t stream) {
+                                   float* scores_out, float* logits, int T, int H, int E, int K, int sigmoid, int norm_topk,
+                                   float scale, int n_group, int topk_group, cudaStream_t stream) {
   if (T <= 0 || E > kMaxExperts || K > kMaxTopK || K > E || H % 2 || n_group > 64 || (n_group > 1 && E % n_group)) return -1;
-  RouterParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), bias, topk_ids, topk_w,
-                 scores_out, T, H, E, K, sigmoid, norm_topk, scale, n_group, topk_group};
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wb = static_cast<const __nv_bfloat16*>(w);
+  if (logits && H % 32 == 0) {
+    const int eb = (E + 7) / 8;
+    if (T <= 16) launch_kernel(router_logits_small_kernel<1>, dim3(eb), dim3(128), 0, stream, xb, wb, logits, T, H, E);
+    else if (T <= 32) launch_kernel(router_logits_small_kernel<2>, dim3(eb), dim3(128), 0, stream, xb, wb, logits, T, H, E);
+    else if (T <= 64) launch_kernel(router_logits_small_kernel<4>, dim3(eb), dim3(128), 0, stream, xb, wb, logits, T, H, E);
+    else router_logits_tile_kernel<<<dim3((T + 63) / 64, (E + 63) / 64), 128, 0, stream>>>(xb, wb, logits, T, H, E);
+    if (cudaGetLastError() != cudaSuccess) return -7;
+  } else {
+    logits = nullptr;
+  }
+  RouterParams p{xb, wb, bias, topk_ids, topk_w, scores_out, T, H, E, K, sigmoid, norm_topk, scale, n_group, topk_group, logits};
   const size_t smem = size_t(H + 2 * E) * sizeof(float);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {

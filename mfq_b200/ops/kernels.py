@@ -182,11 +182,16 @@ def decode_advance(sampled, input_ids, positions, seq_lens, slots, block_table, 
 
 
 def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sm_scale: float, *, out=None) -> torch.Tensor:
-    """Causal attention of one sequence chunk on the tcgen05 kernel: ``q [T, Hq, 128]``, ``k/v [Tk, Hk, 128]`` with
-    ``Tk >= T``: the first ``Tk - T`` keys are the sequence's past, query ``i`` sees keys ``0 .. i + (Tk - T)``."""
+    """Causal attention of one sequence chunk on the tcgen05 kernels: ``q [T, Hq, D]``, ``k/v [Tk, Hk, D]`` (D 128 or
+    256) with ``Tk >= T``: the first ``Tk - T`` keys are the sequence's past, query ``i`` sees keys ``0 .. i + (Tk - T)``."""
     t, hq, d = q.shape
     out = torch.empty_like(q) if out is None else out
     ws = Workspace.get(q.device)
+    if d == 256:
+        rc = lib().mfq_attn_prefill_d256(ptr(q), ptr(k), ptr(v), ptr(out), t, k.shape[0], hq, k.shape[1], float(sm_scale),
+                                         ptr(ws.status), stream_ptr())
+        check(rc, "attn_prefill_d256")
+        return out
     rc = lib().mfq_attn_prefill_past(ptr(q), ptr(k), ptr(v), ptr(out), t, k.shape[0], hq, k.shape[1], d, float(sm_scale),
                                      ptr(ws.status), stream_ptr())
     check(rc, "attn_prefill_bf16")

@@ -19,7 +19,7 @@ from .lib import Workspace, check, lib, ptr, stream_ptr
 
 _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
 _SIGS = {
-    "mfq_moe_router_topk": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "mfq_moe_router_topk": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
     "mfq_moe_plan": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp],
     "mfq_moe_gather_rows": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "mfq_moe_combine": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
@@ -59,7 +59,8 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, k: int, *, bias: torch.Tensor 
     ids = torch.empty((t, k), dtype=torch.int32, device=x.device)
     wt = torch.empty((t, k), dtype=torch.float32, device=x.device)
     scores = torch.empty((t, e), dtype=torch.float32, device=x.device) if want_scores else None
-    rc = _lib().mfq_moe_router_topk(ptr(x), ptr(w), ptr(bias), ptr(ids), ptr(wt), ptr(scores), t, h, e, k, int(sigmoid),
+    logits = torch.empty((t, e), dtype=torch.float32, device=x.device) if h % 32 == 0 else None
+    rc = _lib().mfq_moe_router_topk(ptr(x), ptr(w), ptr(bias), ptr(ids), ptr(wt), ptr(scores), ptr(logits), t, h, e, k, int(sigmoid),
                                     int(norm_topk), float(scale), n_group, topk_group, stream_ptr())
     check(rc, "moe_router_topk")
     return (ids, wt, scores) if want_scores else (ids, wt)
@@ -70,7 +71,8 @@ def plan_routes(topk_ids: torch.Tensor, e_lo: int, e_hi: int, token_tile: int | 
     dev = topk_ids.device
     n_local = e_hi - e_lo
     bt = token_tile or K._token_tile(max(1, (t * k) // max(1, n_local)))
-    map_cap = math.ceil(t * k / bt) + n_local
+    # tiles = sum over non-empty experts of ceil(rows / tile): at most one per route, and at most one partial tile per expert
+    map_cap = min(t * k, math.ceil(t * k / bt) + min(n_local, t * k))
     plan = RoutePlan(torch.empty(n_local + 1, dtype=torch.int32, device=dev),
                      torch.empty((t, k), dtype=torch.int32, device=dev), torch.empty(t * k, dtype=torch.int32, device=dev),
                      torch.empty((map_cap, 2), dtype=torch.int32, device=dev), torch.empty(2, dtype=torch.int32, device=dev),

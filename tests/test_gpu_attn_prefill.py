@@ -26,6 +26,24 @@ def test_prefill_attention_matches_reference(t, hq, hk):
     assert_close(got, want, rel=2e-2, what=f"prefill attention T={t}")
 
 
+@pytest.mark.parametrize("t,past,hq,hk", [(128, 0, 4, 2), (300, 0, 8, 1), (1024, 0, 2, 2), (1, 0, 4, 1), (200, 77, 8, 2),
+                                           (64, 1000, 4, 1), (2048, 0, 2, 1)])
+def test_prefill_attention_head_dim_256(t, past, hq, hk):
+    """The 256-wide kernel keeps O in TMEM and rescales it lazily; large-magnitude late keys force rescales."""
+    require_gpu_lib()
+    g = torch.Generator(device="cuda").manual_seed(7 * t + past)
+    q = torch.randn((t, hq, 256), generator=g, device="cuda").to(torch.bfloat16)
+    k = torch.randn((past + t, hk, 256), generator=g, device="cuda")
+    # growing key magnitude: the running maximum keeps rising, so the rescale path runs many times
+    k = (k * torch.linspace(0.5, 3.0, past + t, device="cuda")[:, None, None]).to(torch.bfloat16)
+    v = torch.randn((past + t, hk, 256), generator=g, device="cuda").to(torch.bfloat16)
+    scale = 1 / math.sqrt(256)
+    got = ops.kernels.attn_prefill_bf16(q, k, v, scale)
+    check_status()
+    want = ref.attention(q, k, v, scale, causal_offset=past)
+    assert_close(got, want, rel=2e-2, what=f"prefill attention D=256 T={t} past={past}")
+
+
 def test_packed_sequences_do_not_mix():
     require_gpu_lib()
     q = torch.randn((200, 4, 128), device="cuda").to(torch.bfloat16)

@@ -22,9 +22,11 @@ def _prefill_logits(eng, prompt, dev):
     return out
 
 
-def test_hybrid_gpu_matches_cpu_reference_and_graph_decode():
+@pytest.mark.parametrize("head_dim", [128, 256])
+def test_hybrid_gpu_matches_cpu_reference_and_graph_decode(head_dim):
+    import dataclasses
     require_gpu_lib()
-    cfg = HybridConfig.tiny()
+    cfg = dataclasses.replace(HybridConfig.tiny(), head_dim=head_dim)
     tensors = init_hybrid_weights(cfg, seed=3, std=0.05)
     prompt = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(2))
     gpu = LLMEngine(HybridModel(cfg, HybridWeights.from_tensors(cfg, tensors, "cuda")), max_batch=4, max_seq_len=128)

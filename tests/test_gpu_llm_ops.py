@@ -54,7 +54,7 @@ def make_cache(hk, d, batch, max_len):
                         max_pages_per_seq=math.ceil(max_len / 16), device="cuda")
 
 
-@pytest.mark.parametrize("hq,hk,d", [(8, 2, 128), (4, 4, 128), (4, 2, 64)])
+@pytest.mark.parametrize("hq,hk,d", [(8, 2, 128), (4, 4, 128), (4, 2, 64), (16, 2, 256), (4, 1, 256)])
 def test_rope_kv_write_and_decode_attention(hq, hk, d):
     require_gpu_lib()
     lens = [1, 17, 200, 513]
