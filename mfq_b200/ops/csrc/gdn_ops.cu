@@ -159,6 +159,165 @@ __global__ void __launch_bounds__(DV) gdn_recurrent_kernel(const GdnParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Long rows (prefill).  The recurrence is sequential in the token, so the time per token is what counts:
+//   1. a parallel pre-pass normalises q and k in place and turns (a, b) into (decay, beta) per token and head;
+//   2. the recurrence runs with FOUR threads per state column (32 state rows each, partial dot products joined by two
+//      shuffles), inputs staged eight tokens at a time through shared memory with cp.async, and no block-wide
+//      synchronisation inside a token;
+//   3. a parallel post-pass applies the gated RMSNorm to the raw outputs.
+// The reference covers long rows with a chunked WY kernel on mma.sync (gdn_prefill_chunk.cu).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gdn_prep_kernel(float* __restrict__ qkv, const __nv_bfloat16* __restrict__ a,
+                                                       const __nv_bfloat16* __restrict__ bb, const float* __restrict__ A_log,
+                                                       const float* __restrict__ dt_bias, float* __restrict__ gates, int Hk,
+                                                       int Hv, int ab_stride) {
+  const size_t tok = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int C = 2 * Hk * 128 + Hv * 128;
+  float* row = qkv + tok * C;
+  for (int vec = warp; vec < 2 * Hk; vec += 8) {  // q heads, then k heads
+    float4* p4 = reinterpret_cast<float4*>(row + vec * 128) + lane;
+    float4 v = *p4;
+    float ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = rsqrtf(ss + 1e-6f) * (vec < Hk ? rsqrtf(128.f) : 1.f);
+    v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
+    *p4 = v;
+  }
+  for (int h = threadIdx.x; h < Hv; h += 256) {
+    const float av = __bfloat162float(a[tok * ab_stride + h]) + dt_bias[h];
+    const float sp = av > 20.f ? av : log1pf(__expf(av));
+    gates[(tok * Hv + h) * 2] = __expf(-__expf(A_log[h]) * sp);
+    gates[(tok * Hv + h) * 2 + 1] = 1.f / (1.f + __expf(-__bfloat162float(bb[tok * ab_stride + h])));
+  }
+}
+
+constexpr int kGdnTC = 8;        // tokens per shared-memory stage
+constexpr int kGdnQK = 4 * 36;   // a 128-vector stored as four 32-float groups, 36 floats apart (no bank conflicts)
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+
+// qkv holds normalised q and k (gdn_prep_kernel); o_raw [B*L, Hv*128] fp32 receives q . S after each token.
+__global__ void __launch_bounds__(512) gdn_prefill_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
+                                                          float* __restrict__ state, const int* __restrict__ slot_of,
+                                                          float* __restrict__ o_raw, int L, int Hk, int Hv) {
+  __shared__ __align__(16) float q_s[2][kGdnTC][kGdnQK];
+  __shared__ __align__(16) float k_s[2][kGdnTC][kGdnQK];
+  __shared__ __align__(16) float v_s[2][kGdnTC][128];
+  __shared__ __align__(8) float g_s[2][kGdnTC][2];
+  const int b = blockIdx.x / Hv, h = blockIdx.x % Hv;
+  const int slot = slot_of[b];
+  if (slot < 0) return;
+  const int col = threadIdx.x >> 2, rg = threadIdx.x & 3;
+  const int hk = h / (Hv / Hk);
+  const int C = 2 * Hk * 128 + Hv * 128;
+  float* st = state + (size_t(slot) * Hv + h) * 128 * 128;
+  float s[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) s[i] = st[(rg * 32 + i) * 128 + col];
+
+  auto load_stage = [&](int chunk, int stage) {
+    const int t0 = chunk * kGdnTC;
+    for (int idx = threadIdx.x; idx < kGdnTC * 96; idx += 512) {
+      const int tt = idx / 96, r = idx % 96, which = r >> 5, e4 = r & 31;
+      if (t0 + tt >= L) continue;
+      const float* row = qkv + (size_t(b) * L + t0 + tt) * C;
+      if (which == 2) {
+        cp_async16(&v_s[stage][tt][e4 * 4], row + 2 * Hk * 128 + h * 128 + e4 * 4);
+      } else {
+        float* dst = (which == 0 ? q_s[stage][tt] : k_s[stage][tt]) + (e4 >> 3) * 36 + (e4 & 7) * 4;
+        cp_async16(dst, row + (which == 0 ? 0 : Hk * 128) + hk * 128 + e4 * 4);
+      }
+    }
+    if (threadIdx.x < kGdnTC && t0 + int(threadIdx.x) < L)
+      cp_async8(&g_s[stage][threadIdx.x][0], gates + ((size_t(b) * L + t0 + threadIdx.x) * Hv + h) * 2);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const int chunks = (L + kGdnTC - 1) / kGdnTC;
+  load_stage(0, 0);
+  for (int c = 0; c < chunks; ++c) {
+    const int stage = c & 1;
+    if (c + 1 < chunks) {
+      load_stage(c + 1, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const int n = min(kGdnTC, L - c * kGdnTC);
+    for (int tt = 0; tt < n; ++tt) {
+      const float* kp = k_s[stage][tt] + rg * 36;
+      const float* qp = q_s[stage][tt] + rg * 36;
+      float kk[32];
+      float kv0 = 0.f, kv1 = 0.f, kv2 = 0.f, kv3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
+        kk[i] = k4.x; kk[i + 1] = k4.y; kk[i + 2] = k4.z; kk[i + 3] = k4.w;
+        kv0 = fmaf(s[i], k4.x, kv0); kv1 = fmaf(s[i + 1], k4.y, kv1);
+        kv2 = fmaf(s[i + 2], k4.z, kv2); kv3 = fmaf(s[i + 3], k4.w, kv3);
+      }
+      float kv = (kv0 + kv1) + (kv2 + kv3);
+      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      const float decay = g_s[stage][tt][0], beta = g_s[stage][tt][1];
+      const float delta = (v_s[stage][tt][col] - decay * kv) * beta;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(qp + i);
+        s[i] = fmaf(s[i], decay, kk[i] * delta);             o0 = fmaf(s[i], q4.x, o0);
+        s[i + 1] = fmaf(s[i + 1], decay, kk[i + 1] * delta); o1 = fmaf(s[i + 1], q4.y, o1);
+        s[i + 2] = fmaf(s[i + 2], decay, kk[i + 2] * delta); o2 = fmaf(s[i + 2], q4.z, o2);
+        s[i + 3] = fmaf(s[i + 3], decay, kk[i + 3] * delta); o3 = fmaf(s[i + 3], q4.w, o3);
+      }
+      float o = (o0 + o1) + (o2 + o3);
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (rg == 0) o_raw[((size_t(b) * L + c * kGdnTC + tt) * Hv + h) * 128 + col] = o;
+    }
+    __syncthreads();  // the stage is refilled two chunks from now
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) st[(rg * 32 + i) * 128 + col] = s[i];
+}
+
+// y = o * rsqrt(mean(o^2) + eps) * norm_w * silu(z): one warp per (token, head).
+__global__ void __launch_bounds__(256) gdn_gated_norm_kernel(const float* __restrict__ o_raw, const __nv_bfloat16* __restrict__ z,
+                                                             const float* __restrict__ norm_w, __nv_bfloat16* __restrict__ y,
+                                                             size_t pairs, int Hv, float eps, int z_stride) {
+  const size_t pair = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const int lane = threadIdx.x & 31;
+  const size_t tok = pair / Hv;
+  const int h = int(pair % Hv);
+  const float4 o = *reinterpret_cast<const float4*>(o_raw + pair * 128 + lane * 4);
+  float ss = o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
+#pragma unroll
+  for (int sft = 16; sft > 0; sft >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sft);
+  const float r = rsqrtf(ss / 128.f + eps);
+  const float4 nw = *reinterpret_cast<const float4*>(norm_w + lane * 4);
+  const uint2 zr = *reinterpret_cast<const uint2*>(z + tok * z_stride + h * 128 + lane * 4);
+  const __nv_bfloat16* zb = reinterpret_cast<const __nv_bfloat16*>(&zr);
+  const float ov[4] = {o.x, o.y, o.z, o.w}, wv[4] = {nw.x, nw.y, nw.z, nw.w};
+  uint2 out;
+  __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&out);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float zg = __bfloat162float(zb[j]);
+    ob[j] = __float2bfloat16(ov[j] * r * wv[j] * (zg / (1.f + __expf(-zg))));
+  }
+  *reinterpret_cast<uint2*>(y + pair * 128 + lane * 4) = out;
+}
+
 // After a verify window: state[slot[b]] <- ckpt[b, keep[b]], conv_state likewise (keep = index of the last accepted
 // window position).  One CTA per (row, head); rows with slot < 0 are skipped.
 __global__ void gdn_select_kernel(const float* __restrict__ ckpt, const float* __restrict__ conv_ckpt,
@@ -201,6 +360,23 @@ extern "C" int mfq_gdn_recurrent(const float* qkv, const void* z, const void* a,
               static_cast<const __nv_bfloat16*>(b), A_log, dt_bias, norm_w, state, ckpt, slot,
               static_cast<__nv_bfloat16*>(y), L, Hk, Hv, eps, z_stride, ab_stride};
   gdn_recurrent_kernel<128, 128><<<B * Hv, 128, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+// Long rows without checkpoints.  qkv is normalised IN PLACE; o_raw [B*L, Hv*128] and gates [B*L, Hv, 2] are fp32 scratch.
+extern "C" int mfq_gdn_prefill(float* qkv, const void* z, const void* a, const void* b, const float* A_log, const float* dt_bias,
+                               const float* norm_w, float* state, const int* slot, void* y, float* o_raw, float* gates, int B,
+                               int L, int Hk, int Hv, int dk, int dv, float eps, int z_stride, int ab_stride,
+                               cudaStream_t stream) {
+  if (B <= 0 || L <= 0 || dk != 128 || dv != 128 || Hk <= 0 || Hv % Hk || z_stride % 4) return -1;
+  const size_t tokens = size_t(B) * L;
+  gdn_prep_kernel<<<unsigned(tokens), 256, 0, stream>>>(qkv, static_cast<const __nv_bfloat16*>(a),
+                                                         static_cast<const __nv_bfloat16*>(b), A_log, dt_bias, gates, Hk, Hv,
+                                                         ab_stride);
+  gdn_prefill_kernel<<<B * Hv, 512, 0, stream>>>(qkv, gates, state, slot, o_raw, L, Hk, Hv);
+  const size_t pairs = tokens * Hv;
+  gdn_gated_norm_kernel<<<unsigned((pairs + 7) / 8), 256, 0, stream>>>(o_raw, static_cast<const __nv_bfloat16*>(z), norm_w,
+                                                                       static_cast<__nv_bfloat16*>(y), pairs, Hv, eps, z_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 

@@ -18,6 +18,7 @@ from .lib import check, lib, ptr, stream_ptr
 
 _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
 _bound = False
+PREFILL_MIN_TOKENS = 8  # rows longer than this take the prefill kernels
 
 
 def _lib():
@@ -27,6 +28,7 @@ def _lib():
         L.mfq_gdn_conv.argtypes = [_vp] * 6 + [_i] * 4 + [_vp]
         L.mfq_gdn_recurrent.argtypes = [_vp] * 11 + [_i] * 6 + [_f, _i, _i, _vp]
         L.mfq_gdn_select.argtypes = [_vp] * 6 + [_i] * 6 + [_vp]
+        L.mfq_gdn_prefill.argtypes = [_vp] * 12 + [_i] * 6 + [_f, _i, _i, _vp]
         _bound = True
     return L
 
@@ -68,6 +70,14 @@ def recurrent(qkv: torch.Tensor, z: torch.Tensor, a: torch.Tensor, b: torch.Tens
     rows = n // L
     dk, dv = state.shape[2], state.shape[3]
     y = torch.empty((n, Hv * dv), dtype=torch.bfloat16, device=qkv.device)
+    if qkv.is_cuda and ckpt is None and L > PREFILL_MIN_TOKENS:
+        # long rows: pre-pass / 4-threads-per-column recurrence / post-pass (normalises q and k inside ``qkv`` in place)
+        o_raw = torch.empty((n, Hv * dv), dtype=torch.float32, device=qkv.device)
+        gates = torch.empty((n, Hv, 2), dtype=torch.float32, device=qkv.device)
+        check(_lib().mfq_gdn_prefill(ptr(qkv), ptr(z), ptr(a), ptr(b), ptr(A_log), ptr(dt_bias), ptr(norm_w), ptr(state), ptr(slot),
+                                     ptr(y), ptr(o_raw), ptr(gates), rows, L, Hk, Hv, dk, dv, float(eps), z.stride(0), a.stride(0),
+                                     stream_ptr()), "gdn_prefill")
+        return y
     if qkv.is_cuda:
         check(_lib().mfq_gdn_recurrent(ptr(qkv), ptr(z), ptr(a), ptr(b), ptr(A_log), ptr(dt_bias), ptr(norm_w), ptr(state),
                                        ptr(ckpt), ptr(slot), ptr(y), rows, L, Hk, Hv, dk, dv, float(eps), z.stride(0), a.stride(0),

@@ -36,12 +36,13 @@ def _run(t, dev, L, hk, hv, ckpt=False):
     cck = torch.zeros((b, L, 3, d["x"].shape[1]), device=dev) if ckpt else None
     sck = torch.zeros((b, L, hv, 128, 128), device=dev) if ckpt else None
     qkv = gdn.conv(d["x"], d["conv_state"], d["w"], d["slot"], L, conv_ckpt=cck)
+    conv_out = qkv.clone()  # long rows normalise q and k inside qkv
     y = gdn.recurrent(qkv, d["z"], d["a"], d["b"], d["A_log"], d["dt_bias"], d["norm_w"], d["state"], d["slot"], L, hk, hv,
                       ckpt=sck)
-    return qkv, y, d, cck, sck
+    return conv_out, y, d, cck, sck
 
 
-@pytest.mark.parametrize("b,L,hk,hv", [(5, 1, 2, 4), (1, 67, 2, 2), (3, 4, 1, 2)])
+@pytest.mark.parametrize("b,L,hk,hv", [(5, 1, 2, 4), (1, 67, 2, 2), (3, 4, 1, 2), (1, 9, 1, 2), (3, 300, 2, 4), (1, 1024, 1, 1)])
 def test_gdn_matches_reference(b, L, hk, hv):
     require_gpu_lib()
     t, _ = _problem(b, L, hk, hv, slots=b + 2, seed=b * 10 + L)
