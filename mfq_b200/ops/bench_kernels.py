@@ -65,7 +65,8 @@ def bench_gemm(m: int, n: int, k: int, reps: int, splits=None, tile=None) -> dic
     out = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
     ms = time_ms(lambda i: K.fp8_gemm(x, xs, w[i % copies], ws, out=out, splits=splits, token_tile=tile), reps)
     byt = n * k + m * k + 2 * m * n
-    return {"kernel": "fp8_gemm", "m": m, "n": n, "k": k, "us": ms * 1e3, "gbs": byt / ms / 1e6,
+    gemv = m <= K.GEMV_MAX_ROWS and n % 16 == 0 and splits is None and tile is None and K.gemv_enabled()
+    return {"kernel": "fp8_gemv" if gemv else "fp8_gemm", "m": m, "n": n, "k": k, "us": ms * 1e3, "gbs": byt / ms / 1e6,
             "tflops": 2 * m * n * k / ms / 1e9, "splits": splits if splits else K.pick_splits(m, n, k)}
 
 
@@ -156,6 +157,10 @@ def main() -> None:
             r = bench_gemm(m, n, k, args.reps)
             r["name"] = name
             rows.append(r)
+            if r["kernel"] == "fp8_gemv":  # the tcgen05 GEMM on the same shape, for comparison
+                r = bench_gemm(m, n, k, args.reps, splits=K.pick_splits(m, n, k), tile=16)
+                r["name"] = name
+                rows.append(r)
     for m in ((1, 64) if args.quick else (1, 16, 64, 512, 4096)) if want("w4") else ():
         for name, n, k in shapes[:4]:
             r = bench_w4_gemm(m, n, k, args.reps)

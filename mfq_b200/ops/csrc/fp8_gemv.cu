@@ -1,0 +1,185 @@
+// Weight-streaming block-scaled FP8 GEMV / skinny GEMM for 1..16 token rows (single-stream decode, speculative
+// verify windows, and the per-expert tiles of a decode-sized MoE step).
+//
+// With this few rows the product is pure weight streaming and what counts is latency: no tensor maps, no TMEM, no
+// pipeline to fill.  A CTA owns 16 output rows; its eight warps split the K range by 128-wide blocks.  A thread reads
+// 16 contiguous bytes of a weight row straight from global memory and feeds them to two
+// `mma.sync.m16n8k32.e4m3` as its k-slots; the activation fragment uses the same slot assignment, so every
+// 64-byte chunk contributes its exact dot product (fp32 accumulate).  Each 128-wide block is accumulated on its own
+// and folded with that block's fp32 weight multiplier; the row multiplier of the activations is applied at the end,
+// the warps' partial sums meet in shared memory, the residual is added and bf16 rows are written.
+// The weight slice of a warp is prefetched into L2 before the grid dependency wait, so under programmatic dependent
+// launch it streams in while the previous kernel drains.
+//
+// The reference's counterparts are its scalar small-M kernels (mfq/kernels/cuda: mxfp8_small_m_kernel,
+// nint_matmul_kernel and the sq_mmq family).
+#include "common.cuh"
+
+namespace mfq {
+
+__device__ __forceinline__ void mma_e4m3(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct GemvParams {
+  const uint8_t* w;        // [experts][N][K] E4M3
+  const float* w_scale;    // [experts][ceil(N/128)][K/128]
+  const uint8_t* x;        // [rows][K] E4M3
+  const float* x_scale;    // [rows]
+  __nv_bfloat16* out;      // [rows][N]
+  const __nv_bfloat16* residual;  // [rows][N] or null
+  int M, N, K;
+  const int2* tile_map;    // grouped: (expert, 16-row tile inside the expert) per blockIdx.y; (-1, -1) pads
+  const int* offsets;      // grouped: first sorted row of every expert (+ total)
+};
+
+constexpr int kWarps = 8;  // K-split inside a CTA
+
+// NB: 8-token column blocks per CTA, 1 (<= 8 rows) or 2 (<= 16 rows).  RG: 16-row groups of the weight matrix per CTA;
+// the kWarps / RG warps of a group split K.  Expert tiles use RG = 2: a CTA's life is a chain of dependent loads
+// (tile map, offsets, weights), so it has to carry enough bytes to be worth that latency.
+template <int NB, int RG>
+__global__ void __launch_bounds__(kWarps * 32, 2) fp8_gemv_kernel(const GemvParams p) {
+  pdl_trigger();
+  constexpr int kSplit = kWarps / RG;
+  __shared__ float part[kWarps][16][NB * 8];
+  const int lane = threadIdx.x & 31, g8 = lane >> 2, c = lane & 3;
+  const int rg = (threadIdx.x >> 5) / kSplit, warp = (threadIdx.x >> 5) % kSplit;  // warp: index inside the K split
+  const int n0 = (blockIdx.x * RG + rg) * 16;
+  const int kblocks = p.K >> 7;
+  const uint8_t* w = p.w;
+  const float* wsc = p.w_scale;
+  int row0 = 0, rows = p.M;
+  const int nblocks128 = (p.N + 127) >> 7;
+
+  // this warp's weight slice -> L2, before the dependency wait (weights never depend on the previous kernel)
+  if (!p.tile_map) {
+    const uint8_t* base = w + size_t(n0) * p.K;
+    for (int kb = warp; kb < kblocks; kb += kSplit)
+      if (lane < 16) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + size_t(lane) * p.K + kb * 128));
+  }
+  pdl_wait();
+  if (p.tile_map) {
+    const int2 tm = p.tile_map[blockIdx.y];
+    if (tm.x < 0) return;
+    const int lo = p.offsets[tm.x] + tm.y * (NB * 8);
+    row0 = lo;
+    rows = min(NB * 8, p.offsets[tm.x + 1] - lo);
+    w += size_t(tm.x) * p.N * p.K;
+    wsc += size_t(tm.x) * nblocks128 * kblocks;
+  }
+  const uint8_t* w_lo = w + size_t(n0 + g8) * p.K + 16 * c;
+  const uint8_t* w_hi = w_lo + size_t(8) * p.K;
+  const float* ws_row = wsc + size_t(n0 >> 7) * kblocks;
+  const uint8_t* xr[NB];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) xr[nb] = p.x + size_t(row0 + nb * 8 + g8) * p.K + 16 * c;
+  bool live[NB];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) live[nb] = nb * 8 + g8 < rows;
+
+  float acc[NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f;
+  // Batches of kBatch k-blocks: every weight load of a batch is issued before the first MMA consumes one, so a warp
+  // keeps kBatch * 2 KB in flight (a warp issues in order; interleaving loads and MMAs would expose the DRAM latency
+  // once per k-block).
+  constexpr int kBatch = 4;
+  for (int kb0 = warp; kb0 < kblocks; kb0 += kSplit * kBatch) {
+    uint4 a_lo0[kBatch], a_hi0[kBatch], a_lo1[kBatch], a_hi1[kBatch];
+    float wscale[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int kb = kb0 + u * kSplit;
+      if (kb < kblocks) {
+        const int k = kb * 128;
+        a_lo0[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
+        a_hi0[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
+        a_lo1[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k + 64));
+        a_hi1[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k + 64));
+        wscale[u] = __ldg(ws_row + kb);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int kb = kb0 + u * kSplit;
+      if (kb < kblocks) {
+        const int k = kb * 128;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          uint4 b0 = make_uint4(0u, 0u, 0u, 0u), b1 = b0;
+          if (live[nb]) {
+            b0 = *reinterpret_cast<const uint4*>(xr[nb] + k);
+            b1 = *reinterpret_cast<const uint4*>(xr[nb] + k + 64);
+          }
+          float blk[4] = {0.f, 0.f, 0.f, 0.f};
+          mma_e4m3(blk, a_lo0[u].x, a_hi0[u].x, a_lo0[u].y, a_hi0[u].y, b0.x, b0.y);
+          mma_e4m3(blk, a_lo0[u].z, a_hi0[u].z, a_lo0[u].w, a_hi0[u].w, b0.z, b0.w);
+          mma_e4m3(blk, a_lo1[u].x, a_hi1[u].x, a_lo1[u].y, a_hi1[u].y, b1.x, b1.y);
+          mma_e4m3(blk, a_lo1[u].z, a_hi1[u].z, a_lo1[u].w, a_hi1[u].w, b1.z, b1.w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[nb][e] = fmaf(blk[e], wscale[u], acc[nb][e]);
+        }
+      }
+    }
+  }
+  float (*mine)[NB * 8] = part[rg * kSplit + warp];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    mine[g8][nb * 8 + 2 * c] = acc[nb][0];
+    mine[g8][nb * 8 + 2 * c + 1] = acc[nb][1];
+    mine[g8 + 8][nb * 8 + 2 * c] = acc[nb][2];
+    mine[g8 + 8][nb * 8 + 2 * c + 1] = acc[nb][3];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < RG * 16 * NB * 8; i += kWarps * 32) {
+    const int grp = i / (16 * NB * 8), j = i % (16 * NB * 8);
+    const int tok = j >> 4, r = j & 15;  // consecutive threads -> consecutive output columns of one token
+    if (tok >= rows) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int wp = 0; wp < kSplit; ++wp) v += part[grp * kSplit + wp][r][tok];
+    v *= p.x_scale[row0 + tok];
+    const size_t o = size_t(row0 + tok) * p.N + (blockIdx.x * RG + grp) * 16 + r;
+    if (p.residual) v += __bfloat162float(p.residual[o]);
+    p.out[o] = __float2bfloat16(v);
+  }
+}
+
+static int launch_gemv(const GemvParams& p, int tiles, int nb, cudaStream_t stream) {
+  if (p.tile_map && p.N % 32 == 0) {
+    launch_kernel(fp8_gemv_kernel<2, 2>, dim3(p.N / 32, tiles), dim3(kWarps * 32), 0, stream, p);
+  } else {
+    const dim3 grid(p.N / 16, tiles);
+    if (nb == 1) launch_kernel(fp8_gemv_kernel<1, 1>, grid, dim3(kWarps * 32), 0, stream, p);
+    else launch_kernel(fp8_gemv_kernel<2, 1>, grid, dim3(kWarps * 32), 0, stream, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+}  // namespace mfq
+
+// out[M, N] = x_scale[m] * sum over 128-blocks of w_scale * (x_q . w_q) (+ residual), M <= 16, N % 16 == 0, K % 128 == 0.
+extern "C" int mfq_fp8_gemv(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
+                            const void* residual, int M, int N, int K, cudaStream_t stream) {
+  if (M <= 0 || M > 16 || N % 16 || K % 128 || N <= 0) return -1;
+  mfq::GemvParams p{static_cast<const uint8_t*>(w), w_scale, static_cast<const uint8_t*>(x), x_scale,
+                    static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(residual), M, N, K, nullptr, nullptr};
+  return mfq::launch_gemv(p, 1, M <= 8 ? 1 : 2, stream);
+}
+
+// Grouped form for expert-sorted rows: tile_map entries are (expert, 16-row tile) as the route plan writes them with a
+// token tile of 16; expert e owns rows [offsets[e], offsets[e + 1]).
+extern "C" int mfq_fp8_gemv_grouped(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
+                                    int N, int K, const void* tile_map, int map_cap, const int* offsets,
+                                    cudaStream_t stream) {
+  if (N % 16 || K % 128 || N <= 0 || map_cap <= 0) return -1;
+  mfq::GemvParams p{static_cast<const uint8_t*>(w), w_scale, static_cast<const uint8_t*>(x), x_scale,
+                    static_cast<__nv_bfloat16*>(out), nullptr, 0, N, K, static_cast<const int2*>(tile_map), offsets};
+  return mfq::launch_gemv(p, map_cap, 2, stream);
+}

@@ -26,6 +26,8 @@ namespace mfq {
 __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ conv_state,
                                 const float* __restrict__ w, const int* __restrict__ slot, float* __restrict__ out,
                                 float* __restrict__ conv_ckpt, int L, int C, int xs) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.y;
   const int s = slot[b];
   if (s < 0) return;
@@ -52,6 +54,8 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, float* __re
 // tokens still read the old history, so it cannot be overwritten by a sibling block of the same grid.
 __global__ void gdn_conv_state_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ conv_state,
                                       const int* __restrict__ slot, int L, int C, int xs) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.y;
   const int s = slot[b];
   if (s < 0) return;
@@ -86,6 +90,8 @@ struct GdnParams {
 
 template <int DK, int DV>
 __global__ void __launch_bounds__(DV) gdn_recurrent_kernel(const GdnParams p) {
+  pdl_trigger();
+  pdl_wait();
   static_assert(DK == 128 && DV == 128, "one thread per state column, four k/q values per lane");
   __shared__ float k_s[DK], q_s[DK];
   __shared__ float red[DV / 32];
@@ -323,6 +329,8 @@ __global__ void __launch_bounds__(256) gdn_gated_norm_kernel(const float* __rest
 __global__ void gdn_select_kernel(const float* __restrict__ ckpt, const float* __restrict__ conv_ckpt,
                                   float* __restrict__ state, float* __restrict__ conv_state, const int* __restrict__ slot,
                                   const int* __restrict__ keep, int L, int Hv, int head_elems, int C) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x / Hv, h = blockIdx.x % Hv;
   const int s = slot[b];
   if (s < 0) return;
@@ -345,9 +353,9 @@ extern "C" int mfq_gdn_conv(const void* x, float* conv_state, const float* w, co
                             int B, int L, int C, int x_stride, cudaStream_t stream) {
   if (B <= 0 || L <= 0 || C <= 0 || x_stride < C) return -1;
   dim3 grid((C + 255) / 256, B, min(L, 64));
-  gdn_conv_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), conv_state, w, slot, out, conv_ckpt, L, C, x_stride);
+  launch_kernel(gdn_conv_kernel, grid, dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), conv_state, w, slot, out, conv_ckpt, L, C, x_stride);
   if (!conv_ckpt)
-    gdn_conv_state_kernel<<<dim3((C + 255) / 256, B), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), conv_state, slot, L, C, x_stride);
+    launch_kernel(gdn_conv_state_kernel, dim3((C + 255) / 256, B), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), conv_state, slot, L, C, x_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
@@ -359,7 +367,7 @@ extern "C" int mfq_gdn_recurrent(const float* qkv, const void* z, const void* a,
   GdnParams p{qkv, static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(a),
               static_cast<const __nv_bfloat16*>(b), A_log, dt_bias, norm_w, state, ckpt, slot,
               static_cast<__nv_bfloat16*>(y), L, Hk, Hv, eps, z_stride, ab_stride};
-  gdn_recurrent_kernel<128, 128><<<B * Hv, 128, 0, stream>>>(p);
+  launch_kernel(gdn_recurrent_kernel<128, 128>, dim3(B * Hv), dim3(128), 0, stream, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
@@ -383,6 +391,6 @@ extern "C" int mfq_gdn_prefill(float* qkv, const void* z, const void* a, const v
 extern "C" int mfq_gdn_select(const float* ckpt, const float* conv_ckpt, float* state, float* conv_state, const int* slot,
                               const int* keep, int B, int L, int Hv, int dk, int dv, int C, cudaStream_t stream) {
   if (B <= 0 || L <= 0 || (dk * dv) % 4) return -1;
-  gdn_select_kernel<<<B * Hv, 256, 0, stream>>>(ckpt, conv_ckpt, state, conv_state, slot, keep, L, Hv, dk * dv, C);
+  launch_kernel(gdn_select_kernel, dim3(B * Hv), dim3(256), 0, stream, ckpt, conv_ckpt, state, conv_state, slot, keep, L, Hv, dk * dv, C);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }

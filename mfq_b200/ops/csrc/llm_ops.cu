@@ -476,7 +476,7 @@ extern "C" int mfq_rmsnorm_quant(const void* x, const void* residual, void* resi
   if (threads < 32) threads = 32;
   if (threads > 1024) return -1;
   // few rows (decode): the kernel is pure latency, so spread a row over as many threads as it has 16-byte vectors
-  if (M <= 1024) threads = min(1024, max(threads, (H / 8 + 31) / 32 * 32));
+  if (M <= 1024) threads = max(threads, min(512, (H / 8 + 31) / 32 * 32));  // 512: the register file allows no more
   launch_kernel(rmsnorm_quant_kernel, dim3(M), dim3(threads), 0, stream,
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
       static_cast<__nv_bfloat16*>(residual_out), static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q_out),

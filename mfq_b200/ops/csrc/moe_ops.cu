@@ -91,6 +91,8 @@ __global__ void __launch_bounds__(128) router_logits_small_kernel(const __nv_bfl
 __global__ void __launch_bounds__(128) router_logits_tile_kernel(const __nv_bfloat16* __restrict__ x,
                                                                  const __nv_bfloat16* __restrict__ w,
                                                                  float* __restrict__ logits, int T, int H, int E) {
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, c = lane & 3;
   const int t0 = blockIdx.x * 64 + warp * 16, e0 = blockIdx.y * 64;
   float acc[8][4];
@@ -125,6 +127,8 @@ __global__ void __launch_bounds__(128) router_logits_tile_kernel(const __nv_bflo
 // One CTA per token: router logits by warp-striped dot products, scoring, optional group limiting, K rounds of block
 // arg-max (lowest index wins ties).
 __global__ void __launch_bounds__(256) moe_router_topk_kernel(const RouterParams p) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float sm[];
   float* xs = sm;                 // [H]
   float* sc = sm + p.H;           // [E] scores used for the weights
@@ -249,6 +253,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
                                                         int* __restrict__ dest, int* __restrict__ src_token,
                                                         int2* __restrict__ tile_map, int map_cap,
                                                         int* __restrict__ totals) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ int cnt[kMaxExperts + 1];
   __shared__ int fill[kMaxExperts];
   __shared__ int tbase[kMaxExperts + 1];
@@ -322,6 +328,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
 __global__ void moe_gather_rows_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs,
                                        const int* __restrict__ src_token, const int* __restrict__ totals,
                                        uint8_t* __restrict__ out_q, float* __restrict__ out_s, int H) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   if (row >= totals[0]) return;
   const int t = src_token[row];
@@ -336,6 +344,8 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const in
                                    const float* __restrict__ topk_w, const __nv_bfloat16* __restrict__ base,
                                    const __nv_bfloat16* __restrict__ extra, __nv_bfloat16* __restrict__ out, int H,
                                    int K) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
     float acc[8];
@@ -387,7 +397,7 @@ extern "C" int mfq_moe_router_topk(const void* x, const void* w, const float* bi
     if (T <= 16) launch_kernel(router_logits_small_kernel<1>, dim3(eb), dim3(128), 0, stream, xb, wb, logits, T, H, E);
     else if (T <= 32) launch_kernel(router_logits_small_kernel<2>, dim3(eb), dim3(128), 0, stream, xb, wb, logits, T, H, E);
     else if (T <= 64) launch_kernel(router_logits_small_kernel<4>, dim3(eb), dim3(128), 0, stream, xb, wb, logits, T, H, E);
-    else router_logits_tile_kernel<<<dim3((T + 63) / 64, (E + 63) / 64), 128, 0, stream>>>(xb, wb, logits, T, H, E);
+    else launch_kernel(router_logits_tile_kernel, dim3((T + 63) / 64, (E + 63) / 64), dim3(128), 0, stream, xb, wb, logits, T, H, E);
     if (cudaGetLastError() != cudaSuccess) return -7;
   } else {
     logits = nullptr;
@@ -399,14 +409,14 @@ extern "C" int mfq_moe_router_topk(const void* x, const void* w, const float* bi
     if (cudaFuncSetAttribute(moe_router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -6;
     configured = smem;
   }
-  moe_router_topk_kernel<<<T, 256, smem, stream>>>(p);
+  launch_kernel(moe_router_topk_kernel, dim3(T), dim3(256), smem, stream, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
 extern "C" int mfq_moe_plan(const int* topk_ids, int T, int K, int e_lo, int e_hi, int token_tile, int* offsets, int* dest,
                             int* src_token, void* tile_map, int map_cap, int* totals, cudaStream_t stream) {
   if (e_hi - e_lo > kMaxExperts || e_hi <= e_lo || T <= 0) return -1;
-  moe_plan_kernel<<<1, 1024, 0, stream>>>(topk_ids, T * K, K, e_lo, e_hi, token_tile, offsets, dest, src_token,
+  launch_kernel(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, topk_ids, T * K, K, e_lo, e_hi, token_tile, offsets, dest, src_token,
                                           static_cast<int2*>(tile_map), map_cap, totals);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
@@ -414,7 +424,7 @@ extern "C" int mfq_moe_plan(const int* topk_ids, int T, int K, int e_lo, int e_h
 extern "C" int mfq_moe_gather_rows(const void* xq, const float* xs, const int* src_token, const int* totals, void* out_q,
                                    float* out_s, int max_rows, int H, cudaStream_t stream) {
   if (H % 16 || max_rows <= 0) return -1;
-  moe_gather_rows_kernel<<<max_rows, 128, 0, stream>>>(static_cast<const uint8_t*>(xq), xs, src_token, totals,
+  launch_kernel(moe_gather_rows_kernel, dim3(max_rows), dim3(128), 0, stream, static_cast<const uint8_t*>(xq), xs, src_token, totals,
                                                        static_cast<uint8_t*>(out_q), out_s, H);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
@@ -422,7 +432,7 @@ extern "C" int mfq_moe_gather_rows(const void* xq, const float* xs, const int* s
 extern "C" int mfq_moe_combine(const void* y, const int* dest, const float* topk_w, const void* base, const void* extra,
                                void* out, int T, int H, int K, cudaStream_t stream) {
   if (H % 8 || T <= 0) return -1;
-  moe_combine_kernel<<<T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), dest, topk_w,
+  launch_kernel(moe_combine_kernel, dim3(T), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(y), dest, topk_w,
                                             static_cast<const __nv_bfloat16*>(base),
                                             static_cast<const __nv_bfloat16*>(extra), static_cast<__nv_bfloat16*>(out), H, K);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;

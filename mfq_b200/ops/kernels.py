@@ -12,6 +12,15 @@ from .lib import Workspace, check, lib, ptr, stream_ptr
 FP8 = torch.float8_e4m3fn
 
 
+GEMV_MAX_ROWS = 16  # up to this many rows the weight-streaming kernel (fp8_gemv.cu) replaces the tcgen05 GEMM
+
+
+def gemv_enabled() -> bool:
+    """``MFQ_GEMV=0`` in the environment sends every shape through the tcgen05 GEMM (A/B measurements)."""
+    import os
+    return os.environ.get("MFQ_GEMV", "1") != "0"
+
+
 def _token_tile(m: int) -> int:
     return 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
 
@@ -49,6 +58,10 @@ def fp8_gemm(x_q: torch.Tensor, x_scale: torch.Tensor, w_q: torch.Tensor, w_scal
     assert w_scale.shape == (math.ceil(n / 128), k // 128) and w_scale.is_contiguous()
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=x_q.device)
+    if m <= GEMV_MAX_ROWS and n % 16 == 0 and splits is None and token_tile is None and gemv_enabled():
+        rc = lib().mfq_fp8_gemv(ptr(w_q), ptr(w_scale), ptr(x_q), ptr(x_scale), ptr(out), ptr(residual), m, n, k, stream_ptr())
+        check(rc, "fp8_gemv")
+        return out
     ws = Workspace.get(x_q.device)
     bt = token_tile or _token_tile(m)
     sp = pick_splits(m, n, k) if splits is None else splits

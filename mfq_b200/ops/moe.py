@@ -97,6 +97,12 @@ def fp8_gemm_grouped(x_q: torch.Tensor, x_s: torch.Tensor, w: torch.Tensor, w_sc
     rows, k = x_q.shape
     e, n, _ = w.shape
     out = torch.empty((rows, n), dtype=torch.bfloat16, device=x_q.device)
+    if plan.token_tile == 16 and n % 16 == 0 and K.gemv_enabled():
+        # decode-sized steps: a handful of rows per expert -> the weight-streaming kernel (no TMA / TMEM set-up)
+        rc = lib().mfq_fp8_gemv_grouped(ptr(w), ptr(w_scale), ptr(x_q), ptr(x_s), ptr(out), n, k, ptr(plan.tile_map),
+                                        plan.tile_map.shape[0], ptr(plan.offsets), stream_ptr())
+        check(rc, "fp8_gemv_grouped")
+        return out
     ws = Workspace.get(x_q.device)
     rc = _lib().mfq_fp8_gemm_grouped(ptr(w), ptr(w_scale), ptr(x_q), ptr(x_s), ptr(out), ptr(ws.status), rows, n, k, e,
                                      ptr(plan.tile_map), ptr(plan.offsets), plan.tile_map.shape[0], plan.token_tile,

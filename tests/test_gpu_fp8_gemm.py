@@ -59,3 +59,21 @@ def test_fp8_gemm_all_token_tiles():
     for tile in (16, 32, 64, 128):
         assert_close(ops.fp8_gemm(xq, xs, wq, ws, token_tile=tile, splits=1), want, what=f"tile {tile}")
     check_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 128), (1, 4096, 4096), (4, 6144, 2048), (8, 2048, 14336), (9, 272, 1024),
+                                   (16, 1040, 512), (2, 151936, 256)])
+def test_weight_streaming_gemv_matches_reference(m, n, k):
+    """Rows <= 16 without explicit tiling take the mma.sync weight-streaming kernel (residual add in place included)."""
+    require_gpu_lib()
+    xq, xs, wq, ws = make(m, n, k, seed=3 * m + n)
+    res = torch.randn((m, n), device="cuda").to(torch.bfloat16)
+    want = ref.fp8_gemm(xq, xs, wq, ws, residual=res)
+    got = ops.fp8_gemm(xq, xs, wq, ws, residual=res)
+    check_status()
+    assert_close(got, want, what=f"gemv {m}x{n}x{k}")
+    # the tcgen05 GEMM agrees on the same problem
+    assert_close(ops.fp8_gemm(xq, xs, wq, ws, residual=res, splits=1), want, what="gemm on the gemv shape")
+    h = res.clone()
+    ops.fp8_gemm(xq, xs, wq, ws, residual=h, out=h)
+    assert_close(h, want, what="gemv residual in place")
