@@ -36,6 +36,7 @@ struct GemvParams {
   int M, N, K;
   const int2* tile_map;    // grouped: (expert, 16-row tile inside the expert) per blockIdx.y; (-1, -1) pads
   const int* offsets;      // grouped: first sorted row of every expert (+ total)
+  const int* src_token;    // grouped, optional: sorted row -> row of x / x_scale (the gather is folded into the loads)
 };
 
 constexpr int kWarps = 8;  // K-split inside a CTA
@@ -77,11 +78,14 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fp8_gemv_kernel(const GemvPara
   const uint8_t* w_hi = w_lo + size_t(8) * p.K;
   const float* ws_row = wsc + size_t(n0 >> 7) * kblocks;
   const uint8_t* xr[NB];
-#pragma unroll
-  for (int nb = 0; nb < NB; ++nb) xr[nb] = p.x + size_t(row0 + nb * 8 + g8) * p.K + 16 * c;
   bool live[NB];
 #pragma unroll
-  for (int nb = 0; nb < NB; ++nb) live[nb] = nb * 8 + g8 < rows;
+  for (int nb = 0; nb < NB; ++nb) {
+    live[nb] = nb * 8 + g8 < rows;
+    int xrow = row0 + nb * 8 + g8;
+    if (p.src_token && live[nb]) xrow = p.src_token[xrow];
+    xr[nb] = p.x + size_t(xrow) * p.K + 16 * c;
+  }
 
   float acc[NB][4];
 #pragma unroll
@@ -144,7 +148,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fp8_gemv_kernel(const GemvPara
     float v = 0.f;
 #pragma unroll
     for (int wp = 0; wp < kSplit; ++wp) v += part[grp * kSplit + wp][r][tok];
-    v *= p.x_scale[row0 + tok];
+    v *= p.x_scale[p.src_token ? p.src_token[row0 + tok] : row0 + tok];
     const size_t o = size_t(row0 + tok) * p.N + (blockIdx.x * RG + grp) * 16 + r;
     if (p.residual) v += __bfloat162float(p.residual[o]);
     p.out[o] = __float2bfloat16(v);
@@ -169,17 +173,18 @@ extern "C" int mfq_fp8_gemv(const void* w, const float* w_scale, const void* x, 
                             const void* residual, int M, int N, int K, cudaStream_t stream) {
   if (M <= 0 || M > 16 || N % 16 || K % 128 || N <= 0) return -1;
   mfq::GemvParams p{static_cast<const uint8_t*>(w), w_scale, static_cast<const uint8_t*>(x), x_scale,
-                    static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(residual), M, N, K, nullptr, nullptr};
+                    static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(residual), M, N, K, nullptr, nullptr, nullptr};
   return mfq::launch_gemv(p, 1, M <= 8 ? 1 : 2, stream);
 }
 
 // Grouped form for expert-sorted rows: tile_map entries are (expert, 16-row tile) as the route plan writes them with a
 // token tile of 16; expert e owns rows [offsets[e], offsets[e + 1]).
+// src_token (optional): x / x_scale are the UNSORTED token rows and sorted row r reads row src_token[r].
 extern "C" int mfq_fp8_gemv_grouped(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
                                     int N, int K, const void* tile_map, int map_cap, const int* offsets,
-                                    cudaStream_t stream) {
+                                    const int* src_token, cudaStream_t stream) {
   if (N % 16 || K % 128 || N <= 0 || map_cap <= 0) return -1;
   mfq::GemvParams p{static_cast<const uint8_t*>(w), w_scale, static_cast<const uint8_t*>(x), x_scale,
-                    static_cast<__nv_bfloat16*>(out), nullptr, 0, N, K, static_cast<const int2*>(tile_map), offsets};
+                    static_cast<__nv_bfloat16*>(out), nullptr, 0, N, K, static_cast<const int2*>(tile_map), offsets, src_token};
   return mfq::launch_gemv(p, map_cap, 2, stream);
 }

@@ -25,7 +25,7 @@ namespace mfq {
 // conv_ckpt (optional) [B, L, 3, C]: history after each token, for verify windows (then conv_state is left alone).
 __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ conv_state,
                                 const float* __restrict__ w, const int* __restrict__ slot, float* __restrict__ out,
-                                float* __restrict__ conv_ckpt, int L, int C, int xs) {
+                                float* __restrict__ conv_ckpt, int L, int C, int xs, int update_state) {
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.y;
@@ -47,6 +47,11 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, float* __re
       float* ck = conv_ckpt + (size_t(b) * L + t) * 3 * C;
       ck[c] = in(t - 2); ck[C + c] = in(t - 1); ck[2 * C + c] = in(t);
     }
+  }
+  // a grid with one z slice has read the whole history of this channel by now: it may shift it in place
+  if (update_state) {
+    const float n0 = in(L - 3), n1 = in(L - 2), n2 = in(L - 1);
+    st[c] = n0; st[C + c] = n1; st[2 * C + c] = n2;
   }
 }
 
@@ -168,8 +173,8 @@ __global__ void __launch_bounds__(DV) gdn_recurrent_kernel(const GdnParams p) {
 // ---------------------------------------------------------------------------------------------
 // Long rows (prefill).  The recurrence is sequential in the token, so the time per token is what counts:
 //   1. a parallel pre-pass normalises q and k in place and turns (a, b) into (decay, beta) per token and head;
-//   2. the recurrence runs with FOUR threads per state column (32 state rows each, partial dot products joined by two
-//      shuffles), inputs staged eight tokens at a time through shared memory with cp.async, and no block-wide
+//   2. the recurrence runs with four threads per pair of state columns (32 state rows each, partial dot products joined
+//      by two shuffles), inputs staged eight tokens at a time through shared memory with cp.async, and no block-wide
 //      synchronisation inside a token;
 //   3. a parallel post-pass applies the gated RMSNorm to the raw outputs.
 // The reference covers long rows with a chunked WY kernel on mma.sync (gdn_prefill_chunk.cu).
@@ -211,33 +216,43 @@ __device__ __forceinline__ void cp_async8(void* smem_dst, const void* gsrc) {
 }
 
 // qkv holds normalised q and k (gdn_prep_kernel); o_raw [B*L, Hv*128] fp32 receives q . S after each token.
-__global__ void __launch_bounds__(512) gdn_prefill_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
+// One CTA = (row, head, half of the 128 state columns): 128 threads = 32 column pairs x 4 row groups.  A thread keeps
+// 2 x 32 state values; the k and q values it reads from shared memory serve both of its columns, which halves the
+// shared-memory traffic per FMA (the limiter of this kernel), and the two halves of a head run on different SMs.
+__global__ void __launch_bounds__(128) gdn_prefill_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
                                                           float* __restrict__ state, const int* __restrict__ slot_of,
                                                           float* __restrict__ o_raw, int L, int Hk, int Hv) {
   __shared__ __align__(16) float q_s[2][kGdnTC][kGdnQK];
   __shared__ __align__(16) float k_s[2][kGdnTC][kGdnQK];
-  __shared__ __align__(16) float v_s[2][kGdnTC][128];
+  __shared__ __align__(16) float v_s[2][kGdnTC][64];
   __shared__ __align__(8) float g_s[2][kGdnTC][2];
-  const int b = blockIdx.x / Hv, h = blockIdx.x % Hv;
+  const int half = blockIdx.x & 1, bh = blockIdx.x >> 1;
+  const int b = bh / Hv, h = bh % Hv;
   const int slot = slot_of[b];
   if (slot < 0) return;
-  const int col = threadIdx.x >> 2, rg = threadIdx.x & 3;
+  const int pair = threadIdx.x >> 2, rg = threadIdx.x & 3;
+  const int col = half * 64 + 2 * pair;  // this thread's columns: col, col + 1
   const int hk = h / (Hv / Hk);
   const int C = 2 * Hk * 128 + Hv * 128;
   float* st = state + (size_t(slot) * Hv + h) * 128 * 128;
-  float s[32];
+  float s0[32], s1[32];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) s[i] = st[(rg * 32 + i) * 128 + col];
+  for (int i = 0; i < 32; ++i) {
+    const float2 v = *reinterpret_cast<const float2*>(st + (rg * 32 + i) * 128 + col);
+    s0[i] = v.x; s1[i] = v.y;
+  }
 
   auto load_stage = [&](int chunk, int stage) {
     const int t0 = chunk * kGdnTC;
-    for (int idx = threadIdx.x; idx < kGdnTC * 96; idx += 512) {
-      const int tt = idx / 96, r = idx % 96, which = r >> 5, e4 = r & 31;
+    for (int idx = threadIdx.x; idx < kGdnTC * 80; idx += 128) {
+      const int tt = idx / 80, r = idx % 80;
       if (t0 + tt >= L) continue;
       const float* row = qkv + (size_t(b) * L + t0 + tt) * C;
-      if (which == 2) {
-        cp_async16(&v_s[stage][tt][e4 * 4], row + 2 * Hk * 128 + h * 128 + e4 * 4);
+      if (r >= 64) {
+        const int e4 = r - 64;  // 16 float4 = this half's 64 v values
+        cp_async16(&v_s[stage][tt][e4 * 4], row + 2 * Hk * 128 + h * 128 + half * 64 + e4 * 4);
       } else {
+        const int which = r >> 5, e4 = r & 31;
         float* dst = (which == 0 ? q_s[stage][tt] : k_s[stage][tt]) + (e4 >> 3) * 36 + (e4 & 7) * 4;
         cp_async16(dst, row + (which == 0 ? 0 : Hk * 128) + hk * 128 + e4 * 4);
       }
@@ -263,37 +278,47 @@ __global__ void __launch_bounds__(512) gdn_prefill_kernel(const float* __restric
       const float* kp = k_s[stage][tt] + rg * 36;
       const float* qp = q_s[stage][tt] + rg * 36;
       float kk[32];
-      float kv0 = 0.f, kv1 = 0.f, kv2 = 0.f, kv3 = 0.f;
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;  // kv partial sums: a* column 0, b* column 1
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
         kk[i] = k4.x; kk[i + 1] = k4.y; kk[i + 2] = k4.z; kk[i + 3] = k4.w;
-        kv0 = fmaf(s[i], k4.x, kv0); kv1 = fmaf(s[i + 1], k4.y, kv1);
-        kv2 = fmaf(s[i + 2], k4.z, kv2); kv3 = fmaf(s[i + 3], k4.w, kv3);
+        a0 = fmaf(s0[i], k4.x, a0); a1 = fmaf(s0[i + 1], k4.y, a1);
+        a0 = fmaf(s0[i + 2], k4.z, a0); a1 = fmaf(s0[i + 3], k4.w, a1);
+        b0 = fmaf(s1[i], k4.x, b0); b1 = fmaf(s1[i + 1], k4.y, b1);
+        b0 = fmaf(s1[i + 2], k4.z, b0); b1 = fmaf(s1[i + 3], k4.w, b1);
       }
-      float kv = (kv0 + kv1) + (kv2 + kv3);
-      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
-      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      float kv0 = a0 + a1, kv1 = b0 + b1;
+      kv0 += __shfl_xor_sync(0xffffffffu, kv0, 1); kv1 += __shfl_xor_sync(0xffffffffu, kv1, 1);
+      kv0 += __shfl_xor_sync(0xffffffffu, kv0, 2); kv1 += __shfl_xor_sync(0xffffffffu, kv1, 2);
       const float decay = g_s[stage][tt][0], beta = g_s[stage][tt][1];
-      const float delta = (v_s[stage][tt][col] - decay * kv) * beta;
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      const float2 vv = *reinterpret_cast<const float2*>(&v_s[stage][tt][2 * pair]);
+      const float d0 = (vv.x - decay * kv0) * beta, d1 = (vv.y - decay * kv1) * beta;
+      a0 = a1 = b0 = b1 = 0.f;  // now the q . S partial sums
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         const float4 q4 = *reinterpret_cast<const float4*>(qp + i);
-        s[i] = fmaf(s[i], decay, kk[i] * delta);             o0 = fmaf(s[i], q4.x, o0);
-        s[i + 1] = fmaf(s[i + 1], decay, kk[i + 1] * delta); o1 = fmaf(s[i + 1], q4.y, o1);
-        s[i + 2] = fmaf(s[i + 2], decay, kk[i + 2] * delta); o2 = fmaf(s[i + 2], q4.z, o2);
-        s[i + 3] = fmaf(s[i + 3], decay, kk[i + 3] * delta); o3 = fmaf(s[i + 3], q4.w, o3);
+        const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s0[i + e] = fmaf(s0[i + e], decay, kk[i + e] * d0);
+          s1[i + e] = fmaf(s1[i + e], decay, kk[i + e] * d1);
+        }
+        a0 = fmaf(s0[i], qv[0], a0); a1 = fmaf(s0[i + 1], qv[1], a1);
+        a0 = fmaf(s0[i + 2], qv[2], a0); a1 = fmaf(s0[i + 3], qv[3], a1);
+        b0 = fmaf(s1[i], qv[0], b0); b1 = fmaf(s1[i + 1], qv[1], b1);
+        b0 = fmaf(s1[i + 2], qv[2], b0); b1 = fmaf(s1[i + 3], qv[3], b1);
       }
-      float o = (o0 + o1) + (o2 + o3);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      if (rg == 0) o_raw[((size_t(b) * L + c * kGdnTC + tt) * Hv + h) * 128 + col] = o;
+      float o0 = a0 + a1, o1 = b0 + b1;
+      o0 += __shfl_xor_sync(0xffffffffu, o0, 1); o1 += __shfl_xor_sync(0xffffffffu, o1, 1);
+      o0 += __shfl_xor_sync(0xffffffffu, o0, 2); o1 += __shfl_xor_sync(0xffffffffu, o1, 2);
+      if (rg == 0)
+        *reinterpret_cast<float2*>(o_raw + ((size_t(b) * L + c * kGdnTC + tt) * Hv + h) * 128 + col) = make_float2(o0, o1);
     }
     __syncthreads();  // the stage is refilled two chunks from now
   }
 #pragma unroll
-  for (int i = 0; i < 32; ++i) st[(rg * 32 + i) * 128 + col] = s[i];
+  for (int i = 0; i < 32; ++i) *reinterpret_cast<float2*>(st + (rg * 32 + i) * 128 + col) = make_float2(s0[i], s1[i]);
 }
 
 // y = o * rsqrt(mean(o^2) + eps) * norm_w * silu(z): one warp per (token, head).
@@ -353,8 +378,9 @@ extern "C" int mfq_gdn_conv(const void* x, float* conv_state, const float* w, co
                             int B, int L, int C, int x_stride, cudaStream_t stream) {
   if (B <= 0 || L <= 0 || C <= 0 || x_stride < C) return -1;
   dim3 grid((C + 255) / 256, B, min(L, 64));
-  launch_kernel(gdn_conv_kernel, grid, dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), conv_state, w, slot, out, conv_ckpt, L, C, x_stride);
-  if (!conv_ckpt)
+  const int fused_state = (!conv_ckpt && grid.z == 1) ? 1 : 0;  // decode: no second launch
+  launch_kernel(gdn_conv_kernel, grid, dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), conv_state, w, slot, out, conv_ckpt, L, C, x_stride, fused_state);
+  if (!conv_ckpt && !fused_state)
     launch_kernel(gdn_conv_state_kernel, dim3((C + 255) / 256, B), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), conv_state, slot, L, C, x_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
@@ -381,7 +407,7 @@ extern "C" int mfq_gdn_prefill(float* qkv, const void* z, const void* a, const v
   gdn_prep_kernel<<<unsigned(tokens), 256, 0, stream>>>(qkv, static_cast<const __nv_bfloat16*>(a),
                                                          static_cast<const __nv_bfloat16*>(b), A_log, dt_bias, gates, Hk, Hv,
                                                          ab_stride);
-  gdn_prefill_kernel<<<B * Hv, 512, 0, stream>>>(qkv, gates, state, slot, o_raw, L, Hk, Hv);
+  gdn_prefill_kernel<<<B * Hv * 2, 128, 0, stream>>>(qkv, gates, state, slot, o_raw, L, Hk, Hv);
   const size_t pairs = tokens * Hv;
   gdn_gated_norm_kernel<<<unsigned((pairs + 7) / 8), 256, 0, stream>>>(o_raw, static_cast<const __nv_bfloat16*>(z), norm_w,
                                                                        static_cast<__nv_bfloat16*>(y), pairs, Hv, eps, z_stride);

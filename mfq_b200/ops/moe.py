@@ -92,17 +92,31 @@ def gather_rows(x_q: torch.Tensor, x_s: torch.Tensor, plan: RoutePlan):
     return out_q, out_s
 
 
-def fp8_gemm_grouped(x_q: torch.Tensor, x_s: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, plan: RoutePlan):
-    """``w [E_local, N, K]`` E4M3, ``w_scale [E_local, N/128, K/128]``; rows of ``x_q`` are expert-sorted."""
-    rows, k = x_q.shape
+# Above this many routes per step the expert tiles stop being latency-bound and the tcgen05 grouped GEMM streams the
+# weights faster (measured on the 512-expert hybrid: 640 routes -> 27 ms / step with the GEMM, 31 ms with the GEMV).
+GEMV_MAX_ROUTES = 256
+
+
+def grouped_gemv_ok(plan: RoutePlan, n: int) -> bool:
+    """Decode-sized steps (a handful of rows per expert) take the weight-streaming kernel (no TMA / TMEM set-up)."""
+    return plan.token_tile == 16 and n % 16 == 0 and plan.max_rows <= GEMV_MAX_ROUTES and K.gemv_enabled()
+
+
+def fp8_gemm_grouped(x_q: torch.Tensor, x_s: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, plan: RoutePlan,
+                     gather: bool = False):
+    """``w [E_local, N, K]`` E4M3, ``w_scale [E_local, N/128, K/128]``; rows of ``x_q`` are expert-sorted -- or, with
+    ``gather`` (weight-streaming kernel only), the unsorted token rows, read through the plan's row -> token map."""
+    k = x_q.shape[1]
+    rows = plan.max_rows if gather else x_q.shape[0]
     e, n, _ = w.shape
     out = torch.empty((rows, n), dtype=torch.bfloat16, device=x_q.device)
-    if plan.token_tile == 16 and n % 16 == 0 and K.gemv_enabled():
-        # decode-sized steps: a handful of rows per expert -> the weight-streaming kernel (no TMA / TMEM set-up)
+    if grouped_gemv_ok(plan, n):
         rc = lib().mfq_fp8_gemv_grouped(ptr(w), ptr(w_scale), ptr(x_q), ptr(x_s), ptr(out), n, k, ptr(plan.tile_map),
-                                        plan.tile_map.shape[0], ptr(plan.offsets), stream_ptr())
+                                        plan.tile_map.shape[0], ptr(plan.offsets), ptr(plan.src_token) if gather else None,
+                                        stream_ptr())
         check(rc, "fp8_gemv_grouped")
         return out
+    assert not gather
     ws = Workspace.get(x_q.device)
     rc = _lib().mfq_fp8_gemm_grouped(ptr(w), ptr(w_scale), ptr(x_q), ptr(x_s), ptr(out), ptr(ws.status), rows, n, k, e,
                                      ptr(plan.tile_map), ptr(plan.offsets), plan.tile_map.shape[0], plan.token_tile,
@@ -126,8 +140,11 @@ def moe_ffn_fp8(x_q, x_s, topk_ids, topk_w, gate_up, gate_up_scale, down, down_s
     """Routed experts of one layer for this rank's experts ``[e_lo, e_lo + E_local)``; returns
     ``base + extra + sum_k w * expert_k(x)`` (only local experts contribute)."""
     plan = plan_routes(topk_ids, e_lo, e_lo + gate_up.shape[0])
-    xq_s, xs_s = gather_rows(x_q, x_s, plan)
-    gu = fp8_gemm_grouped(xq_s, xs_s, gate_up, gate_up_scale, plan)
+    if grouped_gemv_ok(plan, gate_up.shape[1]):
+        gu = fp8_gemm_grouped(x_q, x_s, gate_up, gate_up_scale, plan, gather=True)  # the gather is folded into the loads
+    else:
+        xq_s, xs_s = gather_rows(x_q, x_s, plan)
+        gu = fp8_gemm_grouped(xq_s, xs_s, gate_up, gate_up_scale, plan)
     hq, hs = K.silu_mul_quant(gu)
     y = fp8_gemm_grouped(hq, hs, down, down_scale, plan)
     return combine(y, plan, topk_w, base, extra, out)

@@ -4,7 +4,9 @@ Each case launches one kernel three times on inputs of a few hundred MB (larger 
 for a multi-pass capture to finish in about a minute) and exits.  Cases: ``gemm_prefill`` (M=4096, N=K=4096),
 ``gemm_decode`` (M=64, N=28672, K=4096), ``attn_decode`` (64 sequences x 4096 tokens), ``attn_prefill`` (T=2048),
 ``w4_decode`` / ``w4_prefill`` (the 4-bit in-pipeline-decode GEMM at the same shapes), ``gdn_decode`` (Gated DeltaNet step,
-64 sequences), ``moe_dispatch`` (expert-parallel dispatch + combine kernels at world 1, 4096 tokens).
+64 sequences), ``moe_dispatch`` (expert-parallel dispatch + combine kernels at world 1, 4096 tokens), ``gemv_decode``
+(the weight-streaming FP8 kernel, M=1, N=28672, K=4096), ``attn_prefill_d256`` (T=2048, 16 query / 2 KV heads of 256),
+``gdn_prefill`` (the long-row Gated DeltaNet path, 2048 tokens, 32 heads).
 """
 
 from __future__ import annotations
@@ -57,6 +59,33 @@ def attn_prefill() -> None:
         K.attn_prefill_bf16(q, k, v, 0.088)
 
 
+def attn_prefill_d256() -> None:
+    t, hq, hk, d = 2048, 16, 2, 256
+    q = torch.randn((t, hq, d), device="cuda").to(torch.bfloat16)
+    k = torch.randn((t, hk, d), device="cuda").to(torch.bfloat16)
+    v = torch.randn((t, hk, d), device="cuda").to(torch.bfloat16)
+    for _ in range(3):
+        K.attn_prefill_bf16(q, k, v, 1 / 16)
+
+
+def gdn_prefill() -> None:
+    from . import gdn
+    L, hk, hv, d = 2048, 16, 32, 128
+    c = 2 * hk * d + hv * d
+    x = (torch.randn((L, c), device="cuda") * 0.8).to(torch.bfloat16)
+    z = torch.randn((L, hv * d), device="cuda").to(torch.bfloat16)
+    a = torch.randn((L, hv), device="cuda").to(torch.bfloat16)
+    b = torch.randn((L, hv), device="cuda").to(torch.bfloat16)
+    w = torch.randn((c, 4), device="cuda") * 0.5
+    A_log, dt_bias, norm_w = torch.randn(hv, device="cuda") * 0.5, torch.randn(hv, device="cuda") * 0.5, torch.ones(d, device="cuda")
+    conv_state = torch.zeros((1, 3, c), device="cuda")
+    state = torch.zeros((1, hv, d, d), device="cuda")
+    slot = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        qkv = gdn.conv(x, conv_state, w, slot, L)
+        gdn.recurrent(qkv, z, a, b, A_log, dt_bias, norm_w, state, slot, L, hk, hv)
+
+
 def w4_gemm(m: int, n: int, k: int) -> None:
     from . import w4
     base = w4.quantize_torch(torch.randn((n, k), device="cuda") * 0.02)
@@ -105,7 +134,8 @@ def moe_dispatch() -> None:
 
 CASES = {"gemm_prefill": lambda: gemm(4096, 4096, 4096), "gemm_decode": lambda: gemm(64, 28672, 4096),
          "attn_decode": attn_decode, "attn_prefill": attn_prefill, "w4_decode": lambda: w4_gemm(64, 28672, 4096),
-         "w4_prefill": lambda: w4_gemm(4096, 4096, 4096), "gdn_decode": gdn_decode, "moe_dispatch": moe_dispatch}
+         "w4_prefill": lambda: w4_gemm(4096, 4096, 4096), "gdn_decode": gdn_decode, "moe_dispatch": moe_dispatch,
+         "gemv_decode": lambda: gemm(1, 28672, 4096), "attn_prefill_d256": attn_prefill_d256, "gdn_prefill": gdn_prefill}
 
 if __name__ == "__main__":
     CASES[sys.argv[1]]()
