@@ -49,6 +49,9 @@ def _load_source(args):
     if p.is_dir():
         from .checkpoint import read_hf_directory
         return read_hf_directory(p)
+    if p.suffix == ".gguf":
+        from .formats.gguf import read_gguf
+        return read_gguf(p)
     if p.suffix == ".mfq":
         from . import formats as F
         with F.open_mfq(p) as store:
@@ -56,7 +59,7 @@ def _load_source(args):
             cfg = json.loads(assets.pop("model_config.json"))
             tensors = {n: np.asarray(F.dequantize(store[n]), dtype=np.float32) for n in store if not n.startswith("__mfq_asset__/")}
         return cfg, tensors, assets
-    raise SystemExit(f"cannot detect the source type of {src!r} (expected a Hugging Face directory, an .mfq file or synthetic:<name>)")
+    raise SystemExit(f"cannot detect the source type of {src!r} (expected a Hugging Face directory, a .gguf file, an .mfq file or synthetic:<name>)")
 
 
 def _cmd_quantize(args) -> int:
