@@ -228,7 +228,11 @@ def _cmd_serve(args) -> int:
     engine, tok = loader(args.model)
     service.add_model(args.model_name or Path(args.model).stem, engine, tok)
     key = os.environ.get(args.api_key_env) if args.api_key_env else None
-    uvicorn.run(create_app(service, api_key=key), host=args.host, port=args.port, access_log=args.access_log)
+    cluster = None
+    if args.cluster_peer:
+        from .server.cluster import ClusterBackend
+        cluster = ClusterBackend(args.cluster_peer)
+    uvicorn.run(create_app(service, api_key=key, cluster=cluster), host=args.host, port=args.port, access_log=args.access_log)
     return 0
 
 
@@ -317,6 +321,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--cluster-peer", action="append", default=[],
+                   help="base URL of another server of this kind; models it serves are routed there (repeatable)")
     s.add_argument("--session-cache-gb", type=float, default=8.0,
                    help="host memory for per-conversation KV (+ recurrent state) snapshots, keyed by the request's session_id (0: off)")
     s.add_argument("--prefix-cache-dir", default=None, help="directory of the content-addressed KV prefix cache (256-token blocks)")

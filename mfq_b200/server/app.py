@@ -97,11 +97,16 @@ class _Stream:
                 return
 
 
-def create_app(service: ModelService, api_key: str | None = None, sessions=None) -> FastAPI:
-    """``sessions``: a :class:`~mfq_b200.server.sessions.SessionStore` (in-memory when omitted)."""
+def create_app(service: ModelService, api_key: str | None = None, sessions=None, cluster=None, hardware=None) -> FastAPI:
+    """``sessions``: a :class:`~mfq_b200.server.sessions.SessionStore` (in-memory when omitted); ``cluster``: a
+    :class:`~mfq_b200.server.cluster.ClusterBackend` whose peers serve models that are not loaded here; ``hardware``:
+    a :class:`~mfq_b200.server.hardware.HardwareMonitor`."""
+    from .hardware import HardwareMonitor
     from .sessions import SessionStore
     app = FastAPI(title="mfq-b200", version="0.1.0")
     app.state.service = service
+    app.state.cluster = cluster
+    monitor = hardware if hardware is not None else HardwareMonitor()
     store = sessions if sessions is not None else SessionStore()
     app.state.sessions = store
 
@@ -133,7 +138,11 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None)
 
     @app.get("/v1/models")
     async def models():
-        return {"object": "list", "data": [_model_card(lm) for lm in service.models.values()]}
+        cards = [_model_card(lm) for lm in service.models.values()]
+        if cluster is not None:
+            local = {c["id"] for c in cards}
+            cards += [{"id": m, "object": "model", "created": 0, "owned_by": "mfq-cluster"} for m in cluster.models() if m not in local]
+        return {"object": "list", "data": cards}
 
     @app.get("/v1/models/{model_id}")
     async def model(model_id: str):
@@ -166,9 +175,30 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None)
         status, retry = _ERROR_STATUS.get(stream.error_code, (500, False))
         return error_response(status, stream.error_code, "generation failed", retryable=retry)
 
+    async def _remote(path: str, body: dict):
+        """Models that only a cluster peer serves: forward the request as it is (streaming bodies line by line)."""
+        from .cluster import NoPeer
+        loop = asyncio.get_running_loop()
+        try:
+            status, out, _peer = await loop.run_in_executor(None, lambda: cluster.forward(path, body, bool(body.get("stream"))))
+        except NoPeer:
+            return error_response(503, "no_healthy_peer", f"no healthy cluster peer serves {body.get('model')!r}", retryable=True)
+        if body.get("stream") and status < 400:
+            return StreamingResponse(iter(out), media_type="text/event-stream")
+        if body.get("stream"):
+            out = json.loads(b"".join(out) or b"{}")
+        return JSONResponse(out, status_code=status)
+
+    def _is_remote(body: dict) -> bool:
+        name = body.get("model")
+        return bool(cluster is not None and name and name not in service.models and service.loader is None
+                    and name in cluster.models())
+
     @app.post("/v1/chat/completions")
     async def chat(request: HttpRequest):
         body = await request.json()
+        if _is_remote(body):
+            return await _remote("/v1/chat/completions", body)
         messages = body.get("messages") or []
         if not messages:
             return error_response(400, "invalid_request", "messages must not be empty")
@@ -267,6 +297,39 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None)
     @app.get("/api/v1/runtime/instances")
     async def runtime_instances():
         return service.status()["instances"]
+
+    @app.get("/api/v1/hardware")
+    async def hardware_snapshot():
+        return monitor.snapshot()
+
+    @app.get("/api/v1/cluster")
+    async def cluster_status():
+        return {"peers": cluster.status() if cluster is not None else []}
+
+    @app.get("/api/v1/runtime/cache")
+    async def cache_entries():
+        out = []
+        for lm in service.models.values():
+            eng = getattr(lm, "engine", None)
+            sc, pc = getattr(eng, "session_cache", None), getattr(eng, "prefix_cache", None)
+            out.append({"model": lm.name,
+                        "sessions": {"entries": len(sc.entries), "bytes": sc.bytes, **sc.stats} if sc is not None else None,
+                        "prefix": dict(getattr(eng, "prefix_stats", {})) if pc is not None else None})
+        return {"caches": out}
+
+    @app.post("/api/v1/runtime/cache/purge")
+    async def cache_purge(request: HttpRequest):
+        body = await request.json()
+        dropped = 0
+        for lm in service.models.values():
+            sc = getattr(getattr(lm, "engine", None), "session_cache", None)
+            if sc is None or body.get("model") not in (None, lm.name):
+                continue
+            for sid in [body["session"]] if body.get("session") else list(sc.entries):
+                if sid in sc.entries:
+                    sc.drop(sid)
+                    dropped += 1
+        return {"dropped": dropped}
 
     @app.get("/api/v1/runtime/concurrency")
     async def concurrency():
