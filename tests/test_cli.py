@@ -51,3 +51,12 @@ def test_preset_imatrix_alphaq_flow(tmp_path, capsys):
     doc = json.loads(aq.read_text())
     assert doc["format"] == "mfq.alphaq-allocation.v1" and len(doc["tensors"]) > 10
     capsys.readouterr()
+
+
+def test_diagnose_runs_the_format_checks_on_cpu(capsys):
+    import json
+    from mfq_b200.cli import main
+    assert main(["diagnose", "--check", "nint", "--check", "container", "--check", "fp8-block"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    assert report["ok"] and set(report["checks"]) == {"nint", "container", "fp8-block"}
+    assert report["checks"]["nint"]["snr_db"] > 18

@@ -125,3 +125,11 @@ def test_argmax_embed_advance():
     ops.decode_advance(sampled, ids, pos, sl, slots, bt, 16)
     assert ids.tolist() == [11, 12] and pos.tolist() == [15, 16] and sl.tolist() == [16, 17]
     assert slots.tolist() == [1 * 16 + 15, 22 * 16 + 0]
+
+
+def test_diagnose_kernel_checks_pass():
+    require_gpu_lib()
+    from mfq_b200 import diagnostics
+    report = diagnostics.run()
+    assert report["ok"], report
+    assert {"fp8-gemm", "attention", "engine"} <= set(report["checks"])
