@@ -173,8 +173,8 @@ __global__ void __launch_bounds__(DV) gdn_recurrent_kernel(const GdnParams p) {
 // ---------------------------------------------------------------------------------------------
 // Long rows (prefill).  The recurrence is sequential in the token, so the time per token is what counts:
 //   1. a parallel pre-pass normalises q and k in place and turns (a, b) into (decay, beta) per token and head;
-//   2. the recurrence runs with four threads per pair of state columns (32 state rows each, partial dot products joined
-//      by two shuffles), inputs staged eight tokens at a time through shared memory with cp.async, and no block-wide
+//   2. the recurrence runs with eight threads per pair of state columns (16 state rows each, partial dot products
+//      joined by three shuffles), inputs staged eight tokens at a time through shared memory with cp.async, and no block-wide
 //      synchronisation inside a token;
 //   3. a parallel post-pass applies the gated RMSNorm to the raw outputs.
 // The reference covers long rows with a chunked WY kernel on mma.sync (gdn_prefill_chunk.cu).
@@ -206,7 +206,10 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(float* __restrict__ qkv, 
 }
 
 constexpr int kGdnTC = 8;        // tokens per shared-memory stage
-constexpr int kGdnQK = 4 * 36;   // a 128-vector stored as four 32-float groups, 36 floats apart (no bank conflicts)
+constexpr int kGdnRG = 8;        // threads per pair of state columns (row groups)
+constexpr int kGdnRows = 128 / kGdnRG;  // state rows per thread
+constexpr int kGdnGS = kGdnRows + 4;    // a 128-vector is stored as row groups kGdnGS floats apart (no bank conflicts)
+constexpr int kGdnQK = kGdnRG * kGdnGS;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
@@ -216,10 +219,10 @@ __device__ __forceinline__ void cp_async8(void* smem_dst, const void* gsrc) {
 }
 
 // qkv holds normalised q and k (gdn_prep_kernel); o_raw [B*L, Hv*128] fp32 receives q . S after each token.
-// One CTA = (row, head, half of the 128 state columns): 128 threads = 32 column pairs x 4 row groups.  A thread keeps
-// 2 x 32 state values; the k and q values it reads from shared memory serve both of its columns, which halves the
+// One CTA = (row, head, half of the 128 state columns): 256 threads = 32 column pairs x 8 row groups.  A thread keeps
+// 2 x 16 state values; the k and q values it reads from shared memory serve both of its columns, which halves the
 // shared-memory traffic per FMA (the limiter of this kernel), and the two halves of a head run on different SMs.
-__global__ void __launch_bounds__(128) gdn_prefill_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
+__global__ void __launch_bounds__(32 * kGdnRG) gdn_prefill_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
                                                           float* __restrict__ state, const int* __restrict__ slot_of,
                                                           float* __restrict__ o_raw, int L, int Hk, int Hv) {
   __shared__ __align__(16) float q_s[2][kGdnTC][kGdnQK];
@@ -230,21 +233,21 @@ __global__ void __launch_bounds__(128) gdn_prefill_kernel(const float* __restric
   const int b = bh / Hv, h = bh % Hv;
   const int slot = slot_of[b];
   if (slot < 0) return;
-  const int pair = threadIdx.x >> 2, rg = threadIdx.x & 3;
+  const int pair = threadIdx.x / kGdnRG, rg = threadIdx.x % kGdnRG;
   const int col = half * 64 + 2 * pair;  // this thread's columns: col, col + 1
   const int hk = h / (Hv / Hk);
   const int C = 2 * Hk * 128 + Hv * 128;
   float* st = state + (size_t(slot) * Hv + h) * 128 * 128;
-  float s0[32], s1[32];
+  float s0[kGdnRows], s1[kGdnRows];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const float2 v = *reinterpret_cast<const float2*>(st + (rg * 32 + i) * 128 + col);
+  for (int i = 0; i < kGdnRows; ++i) {
+    const float2 v = *reinterpret_cast<const float2*>(st + (rg * kGdnRows + i) * 128 + col);
     s0[i] = v.x; s1[i] = v.y;
   }
 
   auto load_stage = [&](int chunk, int stage) {
     const int t0 = chunk * kGdnTC;
-    for (int idx = threadIdx.x; idx < kGdnTC * 80; idx += 128) {
+    for (int idx = threadIdx.x; idx < kGdnTC * 80; idx += 32 * kGdnRG) {
       const int tt = idx / 80, r = idx % 80;
       if (t0 + tt >= L) continue;
       const float* row = qkv + (size_t(b) * L + t0 + tt) * C;
@@ -253,7 +256,7 @@ __global__ void __launch_bounds__(128) gdn_prefill_kernel(const float* __restric
         cp_async16(&v_s[stage][tt][e4 * 4], row + 2 * Hk * 128 + h * 128 + half * 64 + e4 * 4);
       } else {
         const int which = r >> 5, e4 = r & 31;
-        float* dst = (which == 0 ? q_s[stage][tt] : k_s[stage][tt]) + (e4 >> 3) * 36 + (e4 & 7) * 4;
+        float* dst = (which == 0 ? q_s[stage][tt] : k_s[stage][tt]) + (e4 * 4 / kGdnRows) * kGdnGS + (e4 * 4 % kGdnRows);
         cp_async16(dst, row + (which == 0 ? 0 : Hk * 128) + hk * 128 + e4 * 4);
       }
     }
@@ -275,12 +278,12 @@ __global__ void __launch_bounds__(128) gdn_prefill_kernel(const float* __restric
     __syncthreads();
     const int n = min(kGdnTC, L - c * kGdnTC);
     for (int tt = 0; tt < n; ++tt) {
-      const float* kp = k_s[stage][tt] + rg * 36;
-      const float* qp = q_s[stage][tt] + rg * 36;
-      float kk[32];
+      const float* kp = k_s[stage][tt] + rg * kGdnGS;
+      const float* qp = q_s[stage][tt] + rg * kGdnGS;
+      float kk[kGdnRows];
       float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;  // kv partial sums: a* column 0, b* column 1
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
+      for (int i = 0; i < kGdnRows; i += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
         kk[i] = k4.x; kk[i + 1] = k4.y; kk[i + 2] = k4.z; kk[i + 3] = k4.w;
         a0 = fmaf(s0[i], k4.x, a0); a1 = fmaf(s0[i + 1], k4.y, a1);
@@ -289,14 +292,17 @@ __global__ void __launch_bounds__(128) gdn_prefill_kernel(const float* __restric
         b0 = fmaf(s1[i + 2], k4.z, b0); b1 = fmaf(s1[i + 3], k4.w, b1);
       }
       float kv0 = a0 + a1, kv1 = b0 + b1;
-      kv0 += __shfl_xor_sync(0xffffffffu, kv0, 1); kv1 += __shfl_xor_sync(0xffffffffu, kv1, 1);
-      kv0 += __shfl_xor_sync(0xffffffffu, kv0, 2); kv1 += __shfl_xor_sync(0xffffffffu, kv1, 2);
+#pragma unroll
+      for (int o = 1; o < kGdnRG; o <<= 1) {
+        kv0 += __shfl_xor_sync(0xffffffffu, kv0, o);
+        kv1 += __shfl_xor_sync(0xffffffffu, kv1, o);
+      }
       const float decay = g_s[stage][tt][0], beta = g_s[stage][tt][1];
       const float2 vv = *reinterpret_cast<const float2*>(&v_s[stage][tt][2 * pair]);
       const float d0 = (vv.x - decay * kv0) * beta, d1 = (vv.y - decay * kv1) * beta;
       a0 = a1 = b0 = b1 = 0.f;  // now the q . S partial sums
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
+      for (int i = 0; i < kGdnRows; i += 4) {
         const float4 q4 = *reinterpret_cast<const float4*>(qp + i);
         const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
@@ -310,15 +316,18 @@ __global__ void __launch_bounds__(128) gdn_prefill_kernel(const float* __restric
         b0 = fmaf(s1[i + 2], qv[2], b0); b1 = fmaf(s1[i + 3], qv[3], b1);
       }
       float o0 = a0 + a1, o1 = b0 + b1;
-      o0 += __shfl_xor_sync(0xffffffffu, o0, 1); o1 += __shfl_xor_sync(0xffffffffu, o1, 1);
-      o0 += __shfl_xor_sync(0xffffffffu, o0, 2); o1 += __shfl_xor_sync(0xffffffffu, o1, 2);
+#pragma unroll
+      for (int o = 1; o < kGdnRG; o <<= 1) {
+        o0 += __shfl_xor_sync(0xffffffffu, o0, o);
+        o1 += __shfl_xor_sync(0xffffffffu, o1, o);
+      }
       if (rg == 0)
         *reinterpret_cast<float2*>(o_raw + ((size_t(b) * L + c * kGdnTC + tt) * Hv + h) * 128 + col) = make_float2(o0, o1);
     }
     __syncthreads();  // the stage is refilled two chunks from now
   }
 #pragma unroll
-  for (int i = 0; i < 32; ++i) *reinterpret_cast<float2*>(st + (rg * 32 + i) * 128 + col) = make_float2(s0[i], s1[i]);
+  for (int i = 0; i < kGdnRows; ++i) *reinterpret_cast<float2*>(st + (rg * kGdnRows + i) * 128 + col) = make_float2(s0[i], s1[i]);
 }
 
 // y = o * rsqrt(mean(o^2) + eps) * norm_w * silu(z): one warp per (token, head).
@@ -407,7 +416,7 @@ extern "C" int mfq_gdn_prefill(float* qkv, const void* z, const void* a, const v
   gdn_prep_kernel<<<unsigned(tokens), 256, 0, stream>>>(qkv, static_cast<const __nv_bfloat16*>(a),
                                                          static_cast<const __nv_bfloat16*>(b), A_log, dt_bias, gates, Hk, Hv,
                                                          ab_stride);
-  gdn_prefill_kernel<<<B * Hv * 2, 128, 0, stream>>>(qkv, gates, state, slot, o_raw, L, Hk, Hv);
+  gdn_prefill_kernel<<<B * Hv * 2, 32 * kGdnRG, 0, stream>>>(qkv, gates, state, slot, o_raw, L, Hk, Hv);
   const size_t pairs = tokens * Hv;
   gdn_gated_norm_kernel<<<unsigned((pairs + 7) / 8), 256, 0, stream>>>(o_raw, static_cast<const __nv_bfloat16*>(z), norm_w,
                                                                        static_cast<__nv_bfloat16*>(y), pairs, Hv, eps, z_stride);
