@@ -122,6 +122,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const size_t half = size_t(ag_epoch & 1u) * size_t(p.M) * p.K;
     const uint4* src = reinterpret_cast<const uint4*>(ag.x_shard);
     const size_t nvec = shard_bytes / 16;
+    const bool small_shard = shard_bytes <= (256u << 10);
     for (int rr = 0; rr < ag.world; ++rr) {
       const int r = (ag.rank + rr) % ag.world;  // own copy first, then a different destination on every rank (no incast)
       uint4* dst = reinterpret_cast<uint4*>(ag.x_full[r] + half + size_t(ag.rank) * shard_bytes);
@@ -134,6 +135,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       for (; v < nvec; v += stride) dst[v] = src[v];
       float* sdst = ag.xs_full[r] + size_t(ag_epoch & 1u) * p.M + size_t(ag.rank) * ag.shard_rows;
       for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ag.shard_rows; i += ag.push_ctas * blockDim.x) sdst[i] = ag.xs_shard[i];
+      if (small_shard) continue;  // announced below, after ONE fence for the whole fan-out
       // one completion counter per destination: a rank learns that my shard has arrived as soon as ITS copy is done
       // (my own tiles after the local copy, rank+1 next, ...), not when the whole fan-out has finished
       __threadfence_system();
@@ -144,6 +146,23 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           ag.push_done[rr] = 0;
           __threadfence_system();
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ag.flags[r] + ag.rank) : "memory");
+        }
+      }
+    }
+    if (small_shard) {
+      // a system-scope fence costs a round trip to the farthest destination; with a few KB per destination the copies
+      // are cheaper than the fences, so fence once and raise every flag together
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const uint32_t prev = atomicAdd(ag.push_done, 1u);
+        if (prev == uint32_t(ag.push_ctas) - 1u) {
+          ag.push_done[0] = 0;
+          __threadfence_system();
+          for (int rr = 0; rr < ag.world; ++rr) {
+            const int r = (ag.rank + rr) % ag.world;
+            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ag.flags[r] + ag.rank) : "memory");
+          }
         }
       }
     }

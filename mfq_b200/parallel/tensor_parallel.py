@@ -100,7 +100,7 @@ class TensorParallel:
         and returns ``[M, N_local]``."""
         ms, k = xq_shard.shape
         if push_ctas is None:  # one push block per 64 KB of shard, at most 32: tiny shards are latency-, not bandwidth-bound
-            push_ctas = max(1, min(32, (ms * k) // 65536))
+            push_ctas = max(4, min(32, (ms * k) // 65536))
         m = ms * self.world
         n = lin.q.shape[0]
         key = ("ag", m, k)
