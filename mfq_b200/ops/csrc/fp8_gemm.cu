@@ -85,6 +85,7 @@ struct GemmParams {
   const int2* tile_map = nullptr;
   const int* expert_offsets = nullptr;
   AgParams ag;
+  int stages = 0;  // depth of the shared-memory ring actually used (<= GemmCfg::kStages); fewer stages = more CTAs per SM
 };
 
 template <int BT>
@@ -94,16 +95,17 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   using Cfg = GemmCfg<BT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + Cfg::kStages * Cfg::kStageBytes);
+  const int stages = p.stages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + stages * Cfg::kStageBytes);
   uint64_t* full = bars;
-  uint64_t* empty = bars + Cfg::kStages;
-  uint64_t* acc_full = bars + 2 * Cfg::kStages;
+  uint64_t* empty = bars + stages;
+  uint64_t* acc_full = bars + 2 * stages;
   uint64_t* acc_empty = acc_full + Cfg::kAcc;
   uint64_t* epi_bar = acc_empty + Cfg::kAcc;  // four one-shot barriers among the epilogue warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
-  float* xs_smem = reinterpret_cast<float*>(tiles + Cfg::kStages * Cfg::kStageBytes + 256);
+  float* xs_smem = reinterpret_cast<float*>(tiles + stages * Cfg::kStageBytes + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -197,7 +199,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int nkb = kb1 - kb0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
     for (int i = 0; i < Cfg::kAcc; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], Cfg::kEpiWarps); }
     for (int i = 0; i < 4; ++i) mbar_init(&epi_bar[i], Cfg::kEpiWarps);
     *abort_flag = 0;
@@ -241,9 +243,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         fence_proxy_async_smem();
         asm volatile("fence.proxy.async.global;" ::: "memory");  // peers' generic-proxy stores -> my TMA reads
       }
-      for (int i = 0; shard_ready && i < nkb; ++i) {
-        const int s = i % Cfg::kStages;
-        if (!mbar_wait(&empty[s], ((i / Cfg::kStages) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutProducer)) break;
+      int s = 0;
+      uint32_t ring_phase = 0;  // ring position and wrap parity, kept incrementally: the depth is a run-time value
+      for (int i = 0; shard_ready && i < nkb; ++i, s = (s + 1 == stages ? 0 : s + 1), ring_phase ^= (s == 0 ? 1u : 0u)) {
+        if (!mbar_wait(&empty[s], ring_phase ^ 1u, abort_flag, p.status, kStatusTimeoutProducer)) break;
         uint8_t* a = tiles + s * Cfg::kStageBytes;
         uint8_t* b = a + kTileN * kBlockK;
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
@@ -255,11 +258,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(kTileN, BT, 0, 0);
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % Cfg::kStages;
+      int s = 0;
+      uint32_t ring_phase = 0;
+      for (int i = 0; i < nkb; ++i, s = (s + 1 == stages ? 0 : s + 1), ring_phase ^= (s == 0 ? 1u : 0u)) {
         const int buf = i % Cfg::kAcc;
         if (!mbar_wait(&acc_empty[buf], ((i / Cfg::kAcc) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutMma)) break;
-        if (!mbar_wait(&full[s], (i / Cfg::kStages) & 1, abort_flag, p.status, kStatusTimeoutMma)) break;
+        if (!mbar_wait(&full[s], ring_phase, abort_flag, p.status, kStatusTimeoutMma)) break;
         tc_fence_after();
         const uint32_t a_addr = smem_u32(tiles + s * Cfg::kStageBytes);
         const uint64_t a_desc = umma_desc_k_sw128(a_addr);
@@ -551,7 +555,18 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
   }
   if (ag) p.ag = *ag;
   const int extra_x = ag ? ag->push_ctas : 0;
-  launch_kernel(fp8_gemm_kernel<BT>, dim3(n_tiles + extra_x, t_tiles, splits), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tw, tx, tx_alt, p);
+  // Ring depth.  The fused-collective modes stage their output in the ring and keep all of it.  A plain or grouped
+  // launch whose grid is larger than one wave of SMs takes a shallower ring instead, so that two or three CTAs share an
+  // SM and one CTA's ramp-up and epilogue hide under another's main loop.
+  p.stages = Cfg::kStages;
+  if (!ar && !ag) {
+    static const int forced = [] { const char* e = getenv("MFQ_GEMM_STAGES"); return e ? atoi(e) : 0; }();
+    const long ctas = long(n_tiles) * t_tiles * splits;
+    if (forced > 0) p.stages = forced < Cfg::kStages ? (forced < 2 ? 2 : forced) : Cfg::kStages;
+    else if (ctas > 148 && BT <= 64) p.stages = kb_per < 4 ? (kb_per < 2 ? 2 : kb_per) : 4;
+  }
+  const int smem_bytes = p.stages * Cfg::kStageBytes + 1024 + 256 + Cfg::kXsBytes;
+  launch_kernel(fp8_gemm_kernel<BT>, dim3(n_tiles + extra_x, t_tiles, splits), dim3(Cfg::kThreads), smem_bytes, stream, tw, tx, tx_alt, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
