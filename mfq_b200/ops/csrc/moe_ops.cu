@@ -61,16 +61,28 @@ __global__ void __launch_bounds__(128) router_logits_small_kernel(const __nv_bfl
   float acc[MB][4];
 #pragma unroll
   for (int m = 0; m < MB; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
-#pragma unroll 4
-  for (int ch = c_lo; ch < c_hi; ++ch) {
-    const int k = ch * 32 + 8 * c;
-    const uint4 b = ld_row16(w, e0 + g8, E, H, k);
+  // batches of kB chunks: all loads of a batch are issued before the first MMA needs one (a warp issues in order)
+  constexpr int kB = MB == 1 ? 8 : MB == 2 ? 4 : 2;
+  for (int ch0 = c_lo; ch0 < c_hi; ch0 += kB) {
+    uint4 b[kB], lo[kB][MB], hi[kB][MB];
 #pragma unroll
-    for (int m = 0; m < MB; ++m) {
-      const uint4 lo = ld_row16(x, m * 16 + g8, T, H, k);
-      const uint4 hi = ld_row16(x, m * 16 + g8 + 8, T, H, k);
-      mma_bf16(acc[m], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
-      mma_bf16(acc[m], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+    for (int u = 0; u < kB; ++u) {
+      const int k = (ch0 + u) * 32 + 8 * c;
+      const bool in = ch0 + u < c_hi;
+      b[u] = in ? ld_row16(w, e0 + g8, E, H, k) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int m = 0; m < MB; ++m) {
+        lo[u][m] = in ? ld_row16(x, m * 16 + g8, T, H, k) : make_uint4(0u, 0u, 0u, 0u);
+        hi[u][m] = in ? ld_row16(x, m * 16 + g8 + 8, T, H, k) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kB; ++u) {
+#pragma unroll
+      for (int m = 0; m < MB; ++m) {
+        mma_bf16(acc[m], lo[u][m].x, hi[u][m].x, lo[u][m].y, hi[u][m].y, b[u].x, b[u].y);
+        mma_bf16(acc[m], lo[u][m].z, hi[u][m].z, lo[u][m].w, hi[u][m].w, b[u].z, b[u].w);
+      }
     }
   }
 #pragma unroll
@@ -241,6 +253,80 @@ __global__ void __launch_bounds__(256) moe_router_topk_kernel(const RouterParams
   }
 }
 
+// Scoring and top-k with one WARP per token (logits precomputed, E <= 1024, no group limiting): a lane keeps E / 32
+// scores in registers, every selection round is a register scan plus five shuffles, and nothing synchronises a block.
+__global__ void __launch_bounds__(128) moe_router_topk_warp_kernel(const RouterParams p) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= p.T) return;
+  constexpr int kMaxPer = 32;
+  const int per = (p.E + 31) >> 5;
+  float sc[kMaxPer], sel[kMaxPer];
+  float mx = -FLT_MAX;
+#pragma unroll
+  for (int i = 0; i < kMaxPer; ++i) {
+    const int e = i * 32 + lane;
+    sc[i] = (i < per && e < p.E) ? p.logits[size_t(t) * p.E + e] : -FLT_MAX;
+    mx = fmaxf(mx, sc[i]);
+  }
+  if (p.sigmoid) {
+#pragma unroll
+    for (int i = 0; i < kMaxPer; ++i)
+      if (i < per) sc[i] = sc[i] == -FLT_MAX ? -FLT_MAX : 1.f / (1.f + __expf(-sc[i]));
+  } else {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxPer; ++i)
+      if (i < per) {
+        const float v = sc[i] == -FLT_MAX ? 0.f : __expf(sc[i] - mx);
+        sc[i] = v;
+        sum += v;
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int i = 0; i < kMaxPer; ++i)
+      if (i < per) sc[i] = (i * 32 + lane < p.E) ? sc[i] * inv : -FLT_MAX;
+  }
+#pragma unroll
+  for (int i = 0; i < kMaxPer; ++i) {
+    const int e = i * 32 + lane;
+    const bool live = i < per && e < p.E;
+    sel[i] = live ? sc[i] + (p.bias ? p.bias[e] : 0.f) : -FLT_MAX;
+    if (live && p.scores_out) p.scores_out[size_t(t) * p.E + e] = sc[i];
+  }
+  float wsum = 0.f, my_w = 0.f;
+  int my_id = 0;
+  for (int k = 0; k < p.K; ++k) {
+    float best = -FLT_MAX, best_w = 0.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxPer; ++i)
+      if (i < per && sel[i] > best) { best = sel[i]; bi = i * 32 + lane; best_w = sc[i]; }  // ascending i: lowest index wins ties
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o), ow = __shfl_xor_sync(0xffffffffu, best_w, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; best_w = ow; }
+    }
+    if (lane == k) { my_id = bi; my_w = best_w; }
+    wsum += best_w;
+#pragma unroll
+    for (int i = 0; i < kMaxPer; ++i)
+      if (i == (bi >> 5) && lane == (bi & 31)) sel[i] = -FLT_MAX;
+  }
+  if (lane < p.K) {
+    const float mul = (p.norm_topk ? 1.f / fmaxf(wsum, 1e-20f) : 1.f) * p.scale;
+    p.topk_ids[size_t(t) * p.K + lane] = my_id;
+    p.topk_w[size_t(t) * p.K + lane] = my_w * mul;
+  }
+}
+
 // Route plan for the experts [e_lo, e_hi) owned by this rank (one CTA).  Row order inside an expert depends on atomic
 // arrival order; results do not, because each row is computed independently and the un-permute sums a token's K
 // contributions in slot order.
@@ -403,6 +489,10 @@ extern "C" int mfq_moe_router_topk(const void* x, const void* w, const float* bi
     logits = nullptr;
   }
   RouterParams p{xb, wb, bias, topk_ids, topk_w, scores_out, T, H, E, K, sigmoid, norm_topk, scale, n_group, topk_group, logits};
+  if (logits && n_group <= 1 && E <= 1024 && K <= 32) {
+    launch_kernel(moe_router_topk_warp_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -7;
+  }
   const size_t smem = size_t(H + 2 * E) * sizeof(float);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
