@@ -155,7 +155,9 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None,
             lm = service.resolve(body.get("model"))
         except KeyError as exc:
             return None, error_response(404, "model_not_found", f"model {exc.args[0]!r} is not loaded")
-        prompt = lm.tokenizer.apply_chat_template(messages, add_generation_prompt=True)
+        from . import tools as tool_ops
+        prompt = lm.tokenizer.apply_chat_template(tool_ops.with_tools(messages, tool_ops.normalise(body.get("tools"))),
+                                                  add_generation_prompt=True)
         ids = lm.tokenizer.encode(prompt)
         if not ids:
             return None, error_response(400, "invalid_request", "empty prompt")
@@ -235,9 +237,15 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None,
             pass
         if stream.error_code:
             return _failure(stream)
+        message, finish = {"role": "assistant", "content": stream.text}, stream.finish or "stop"
+        if body.get("tools"):
+            from . import tools as tool_ops
+            text, calls = tool_ops.extract(stream.text)
+            if calls:
+                message = {"role": "assistant", "content": text or None, "tool_calls": tool_ops.openai_calls(calls)}
+                finish = "tool_calls"
         return {"id": cid, "object": "chat.completion", "created": created, "model": lm.name,
-                "choices": [{"index": 0, "message": {"role": "assistant", "content": stream.text},
-                             "finish_reason": stream.finish or "stop"}], "usage": usage()}
+                "choices": [{"index": 0, "message": message, "finish_reason": finish}], "usage": usage()}
 
     @app.post("/v1/messages")
     async def anthropic_messages(request: HttpRequest):
@@ -278,8 +286,14 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None,
             pass
         if stream.error_code:
             return _failure(stream)
+        content, reason = [{"type": "text", "text": stream.text}], stop_reason()
+        if body.get("tools"):
+            from . import tools as tool_ops
+            text, calls = tool_ops.extract(stream.text)
+            if calls:
+                content, reason = tool_ops.anthropic_blocks(text, calls), "tool_use"
         return {"id": mid, "type": "message", "role": "assistant", "model": lm.name,
-                "content": [{"type": "text", "text": stream.text}], "stop_reason": stop_reason(), "stop_sequence": None,
+                "content": content, "stop_reason": reason, "stop_sequence": None,
                 "usage": {"input_tokens": len(ids), "output_tokens": len(stream.ids)}}
 
     @app.post("/v1/messages/count_tokens")
