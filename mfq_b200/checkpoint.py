@@ -117,8 +117,9 @@ def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict
 
 def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots: int | None = None, max_batch: int = 64,
                 max_seq_len: int = 8192, tp_rank: int = 0, tp_size: int = 1,
-                collective=None, use_graphs: bool = True):
-    """``.mfq`` -> (engine, tokenizer, config)."""
+                collective=None, use_graphs: bool = True, kv_budget_bytes: int | None = None):
+    """``.mfq`` -> (engine, tokenizer, config).  ``kv_budget_bytes`` caps the paged KV pool (see ``engine/kv_budget.py``);
+    on a GPU it defaults to 90 % of the memory that is free once the weights are resident."""
     from .engine.llm_engine import LLMEngine
     from .models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
     from .server.tokenizer import tokenizer_from_assets
@@ -130,6 +131,14 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
         weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size, expert_slots=expert_slots, native_4bit=native_4bit)
     model = MoeDecoderModel(cfg, weights, collective=collective)
     # host-tier experts read the routing on the host every step, which a captured graph cannot do
-    engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device,
+    num_pages = None
+    if kv_budget_bytes is None and str(device).startswith("cuda"):
+        from .engine.kv_budget import device_budget
+        kv_budget_bytes = device_budget(device)
+    if kv_budget_bytes is not None:
+        from .engine.kv_budget import plan
+        num_pages = plan(budget_bytes=kv_budget_bytes, layers=cfg.num_layers, kv_heads=model.hk, head_dim=cfg.head_dim,
+                         max_batch=max_batch, max_seq_len=max_seq_len).num_pages
+    engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, num_pages=num_pages,
                        use_graphs=use_graphs and expert_slots is None)
     return engine, tokenizer_from_assets(assets, cfg.vocab_size), cfg

@@ -213,7 +213,8 @@ def _cmd_serve(args) -> int:
     def loader(name_or_path):
         path = name_or_path if Path(name_or_path).exists() else args.model
         engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size,
-                                        native_4bit=args.native_4bit, expert_slots=args.moe_gpu_cache_slots)
+                                        native_4bit=args.native_4bit, expert_slots=args.moe_gpu_cache_slots,
+                                        kv_budget_bytes=int(args.kv_budget_gb * (1 << 30)) if args.kv_budget_gb else None)
         if args.session_cache_gb > 0:
             from .engine.session_cache import SessionSnapshotCache
             engine.session_cache = SessionSnapshotCache(int(args.session_cache_gb * (1 << 30)))
@@ -325,6 +326,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--kv-budget-gb", type=float, default=0.0,
+                   help="cap of the paged KV pool (default on a GPU: 90%% of the memory free after loading the weights)")
     s.add_argument("--cluster-peer", action="append", default=[],
                    help="base URL of another server of this kind; models it serves are routed there (repeatable)")
     s.add_argument("--session-cache-gb", type=float, default=8.0,
