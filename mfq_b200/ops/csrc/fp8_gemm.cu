@@ -89,7 +89,7 @@ struct GemmParams {
 };
 
 template <int BT>
-__global__ void __launch_bounds__(GemmCfg<BT>::kThreads, 1)
+__global__ void __launch_bounds__(GemmCfg<BT>::kThreads, (BT <= 64 ? 2 : 1))
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                 const __grid_constant__ CUtensorMap tmap_x_alt, const GemmParams p) {
   using Cfg = GemmCfg<BT>;
