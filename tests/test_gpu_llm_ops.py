@@ -131,5 +131,6 @@ def test_diagnose_kernel_checks_pass():
     require_gpu_lib()
     from mfq_b200 import diagnostics
     report = diagnostics.run()
-    assert report["ok"], report
+    failed = {k: v for k, v in report["checks"].items() if not v["ok"]}
+    assert report["ok"], (failed, report.get("device_status"))
     assert {"fp8-gemm", "attention", "engine"} <= set(report["checks"])
