@@ -103,8 +103,18 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None,
     a :class:`~mfq_b200.server.hardware.HardwareMonitor`."""
     from .hardware import HardwareMonitor
     from .sessions import SessionStore
-    app = FastAPI(title="mfq-b200", version="0.1.0")
+    from contextlib import asynccontextmanager
+    from .jobs import JobManager
+    jobs = JobManager()
+
+    @asynccontextmanager
+    async def lifespan(_app):
+        yield
+        jobs.shutdown()  # child processes started through the jobs API end with the server
+
+    app = FastAPI(title="mfq-b200", version="0.1.0", lifespan=lifespan)
     app.state.service = service
+    app.state.jobs = jobs
     app.state.cluster = cluster
     monitor = hardware if hardware is not None else HardwareMonitor()
     store = sessions if sessions is not None else SessionStore()
@@ -311,6 +321,35 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None,
     @app.get("/api/v1/runtime/instances")
     async def runtime_instances():
         return service.status()["instances"]
+
+    # ---- jobs (quantize / eval / inspect ... as child processes) -----------------------------------------------------
+    @app.get("/api/v1/jobs")
+    async def list_jobs():
+        return {"jobs": [j.describe(0) for j in jobs.jobs.values()]}
+
+    @app.post("/api/v1/jobs")
+    async def start_job(request: HttpRequest):
+        body = await request.json()
+        try:
+            job = jobs.submit(str(body.get("kind", "")), list(body.get("args") or []))
+        except ValueError as exc:
+            return error_response(400, "invalid_request", str(exc))
+        except RuntimeError as exc:
+            return error_response(429, "too_many_jobs", str(exc), retryable=True)
+        return JSONResponse(job.describe(), status_code=202)
+
+    @app.get("/api/v1/jobs/{jid}")
+    async def get_job(jid: str):
+        job = jobs.jobs.get(jid)
+        return job.describe() if job is not None else error_response(404, "job_not_found", f"no job {jid!r}")
+
+    @app.post("/api/v1/jobs/{jid}/cancel")
+    async def cancel_job(jid: str):
+        return {"cancelled": jobs.cancel(jid)}
+
+    @app.delete("/api/v1/jobs/{jid}")
+    async def delete_job(jid: str):
+        return {"deleted": jobs.delete(jid)}
 
     @app.get("/api/v1/hardware")
     async def hardware_snapshot():
