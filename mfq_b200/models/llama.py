@@ -128,6 +128,23 @@ class MtpHead:
     final_norm: torch.Tensor | None = None
 
 
+def kv_head_rows(w: torch.Tensor, kv_heads: int, head_dim: int, rank: int, world: int) -> torch.Tensor:
+    """Rows of a K or V projection that rank ``rank`` of ``world`` keeps: ``kv_heads / world`` heads each while there are
+    enough of them, else the single head that the rank's query heads share (that head is then replicated over
+    ``world / kv_heads`` ranks, each of which caches it)."""
+    if world == 1:
+        return w
+    if kv_heads >= world:
+        if kv_heads % world:
+            raise ValueError(f"{kv_heads} KV heads do not split over {world} ranks")
+        per = kv_heads // world * head_dim
+        return w[rank * per : (rank + 1) * per]
+    if world % kv_heads:
+        raise ValueError(f"{world} ranks do not split over {kv_heads} KV heads")
+    head = rank // (world // kv_heads)
+    return w[head * head_dim : (head + 1) * head_dim]
+
+
 @dataclass
 class LlamaWeights:
     embed: torch.Tensor  # [V, H] bf16
@@ -165,7 +182,8 @@ class LlamaWeights:
             wo = rnd(h, hq * d)
             wg, wu, wd = rnd(i, h), rnd(i, h), rnd(h, i)
             if tp_size > 1:
-                wq, wk, wv = rows_shard(wq, hq * d), rows_shard(wk, hk * d), rows_shard(wv, hk * d)
+                wq = rows_shard(wq, hq * d)
+                wk, wv = kv_head_rows(wk, hk, d, tp_rank, tp_size), kv_head_rows(wv, hk, d, tp_rank, tp_size)
                 wg, wu = rows_shard(wg, i), rows_shard(wu, i)
                 wo = wo.reshape(h, tp_size, hq * d // tp_size)[:, tp_rank].contiguous()
                 wd = wd.reshape(h, tp_size, i // tp_size)[:, tp_rank].contiguous()

@@ -24,7 +24,7 @@ from .. import ops
 from ..ops import moe as moe_ops
 from ..ops import reference as ref
 from ..quantize.fp8_block import quantize_fp8_block_torch
-from .llama import Fp8Linear, LlamaConfig, LlamaLayer, LlamaModel, LlamaWeights
+from .llama import kv_head_rows, Fp8Linear, LlamaConfig, LlamaLayer, LlamaModel, LlamaWeights
 
 
 @dataclass
@@ -124,8 +124,8 @@ class MoeWeights(LlamaWeights):
             qkv_names = [p + f"attention.{n}.weight" for n in ("query", "key", "value")]
             layer = MoeLayer(
                 attn_norm=norm(p + "attention.norm.weight"),
-                qkv=linear(qkv_names, lambda: torch.cat([rows(get(qkv_names[0]), hq * d), rows(get(qkv_names[1]), hk * d),
-                                                         rows(get(qkv_names[2]), hk * d)], 0)),
+                qkv=linear(qkv_names, lambda: torch.cat([rows(get(qkv_names[0]), hq * d), kv_head_rows(get(qkv_names[1]), hk, d, tp_rank, w),
+                                                         kv_head_rows(get(qkv_names[2]), hk, d, tp_rank, w)], 0)),
                 o_proj=linear([p + "attention.output.weight"], lambda: cols(get(p + "attention.output.weight"), hq * d)),
                 mlp_norm=norm(p + "mlp.norm.weight"), gate_up=None, down=None)
             if (p + "mlp.router.weight") in tensors:
@@ -204,7 +204,7 @@ class MoeDecoderModel(LlamaModel):
         return self.collective.allreduce_rows(partial, h)
 
     def _ffn_reference(self, h, layer, ffn: MoeFfn):
-        """fp32 restatement of the GPU path (same FP8 rounding points), single rank."""
+        """fp32 restatement of the GPU path (same FP8 rounding points); under TP/EP every rank adds its experts' partial."""
         cfg = self.cfg
         xq, xs, y, _ = ref.rmsnorm_quant(h, layer.mlp_norm, cfg.rms_eps)
         logits = y.float() @ ffn.router.float().T
@@ -220,7 +220,7 @@ class MoeDecoderModel(LlamaModel):
         if cfg.norm_topk:
             wt = wt / wt.sum(-1, keepdim=True).clamp_min(1e-20)
         wt = wt * cfg.routed_scale
-        out = h.float().clone()
+        out = torch.zeros_like(h, dtype=torch.float32)  # this rank's experts (+ its share of the shared expert)
         xd = xq.float() * xs[:, None]
         for le in range(ffn.gate_up.shape[0]):
             tok, slot = (ids == ffn.e_lo + le).nonzero(as_tuple=True)
@@ -230,7 +230,9 @@ class MoeDecoderModel(LlamaModel):
             hq, hs = ref.silu_mul_quant(gu)
             ye = ((hq.float() * hs[:, None]) @ ref.dequant_block(ffn.down[le], ffn.down_scale[le]).T).to(torch.bfloat16)
             out.index_add_(0, tok, ye.float() * wt[tok, slot][:, None])
-        if ffn.shared_gate_up is not None:
+        if ffn.shared_gate_up is not None and not (ffn.shared_replicated and self.w.tp_rank != 0):
             sq, ss = ref.silu_mul_quant(ffn.shared_gate_up(xq, xs))
             out += ffn.shared_down(sq, ss).float()
-        return out.to(torch.bfloat16)
+        if self.tp > 1:
+            return self.collective.allreduce_rows(out.to(torch.bfloat16), h)
+        return (h.float() + out).to(torch.bfloat16)
