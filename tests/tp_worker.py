@@ -120,6 +120,30 @@ def main() -> None:
     gathered = [torch.empty_like(ep_toks) for _ in range(world)]
     dist.all_gather(gathered, ep_toks)
     result["ep_ranks_agree"] = all(torch.equal(g, gathered[0]) for g in gathered)
+    if world == 2:
+        # hybrid model (Gated DeltaNet + gated attention + experts) with every head kind split over the two ranks
+        from mfq_b200.models.hybrid import HybridConfig, HybridModel, HybridWeights, init_hybrid_weights
+        hcfg = HybridConfig.tiny()
+        ht = init_hybrid_weights(hcfg, seed=3, std=0.05)
+
+        def hybrid_logits(model, graphs):
+            eng = LLMEngine(model, max_batch=4, max_seq_len=128, use_graphs=graphs)
+            n = prompt.numel()
+            eng.cache.assign(0, 20_000, n)
+            eng.rec_state.reset(0)
+            step = StepBuffers(input_ids=prompt.to(dev, torch.int32), positions=torch.arange(n, dtype=torch.int32, device=dev),
+                               slots=eng.cache.slots(20_000, 0, n).to(dev), cu_seqlens=[0, n], state_slots=eng.row_ids[:1])
+            out = model.forward(step, eng.cache, prefill=True).float()
+            eng.cache.release(20_000)
+            return out, eng
+        h_tp, h_eng = hybrid_logits(HybridModel(hcfg, HybridWeights.from_tensors(hcfg, ht, dev, rank, world), collective=tp), True)
+        h_one, _ = hybrid_logits(HybridModel(hcfg, HybridWeights.from_tensors(hcfg, ht, dev)), False)
+        result["hybrid_tp_cos"] = float(torch.nn.functional.cosine_similarity(h_tp.flatten(), h_one.flatten(), dim=0))
+        result["hybrid_tp_row_cos"] = float(torch.nn.functional.cosine_similarity(h_tp, h_one, dim=1).median())
+        h_toks = h_eng.generate(prompts, 6).tokens.to(dev)
+        got = [torch.empty_like(h_toks) for _ in range(world)]
+        dist.all_gather(got, h_toks)
+        result["hybrid_ranks_agree"] = all(torch.equal(g, got[0]) for g in got)
     # token-sharded dispatch -> local experts -> combine through peer memory, against all experts on one GPU
     from mfq_b200.ops import moe as moe_ops
     from mfq_b200.ops import reference as ref
