@@ -216,41 +216,64 @@ def run_hybrid(args) -> dict:
     from mfq_b200.engine.llm_engine import LLMEngine
     from mfq_b200.models.hybrid import HybridConfig, HybridModel, random_hybrid_weights
 
-    if args.gpus != 1:
-        raise SystemExit("--model hybrid80b runs on one GPU")
-    dev = torch.device("cuda", 0)
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+    dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    collective = None
+    if world > 1:  # one model over the GPUs: heads tensor-parallel, experts split over the ranks
+        from mfq_b200.parallel.tensor_parallel import TensorParallel
+        dist.init_process_group("nccl", device_id=dev)
+        collective = TensorParallel(dist.group.WORLD, dev)
     cfg = HybridConfig.tiny() if args.tiny else HybridConfig.next_80b()
     batch, ctx, new = args.batch, args.context, args.steps + args.warmup + 8
+    use_mtp = world == 1  # draft/verify cycles are measured on one GPU only
     t0 = time.time()
-    weights = random_hybrid_weights(cfg, dev, seed=0, mtp=True)
+    weights = random_hybrid_weights(cfg, dev, seed=0, mtp=use_mtp, tp_rank=rank, tp_size=world)
     torch.cuda.synchronize()
     build_s = time.time() - t0
-    engine = LLMEngine(HybridModel(cfg, weights), max_batch=batch, max_seq_len=ctx + 4 * new + 16, mtp_draft_tokens=1)
+    engine = LLMEngine(HybridModel(cfg, weights, collective=collective), max_batch=batch, max_seq_len=ctx + 4 * new + 16,
+                       mtp_draft_tokens=1 if use_mtp else 0)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
     gen = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, cfg.vocab_size, (ctx,), generator=gen) for _ in range(batch)]
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):
             fn()
-        torch.cuda.synchronize()
+        sync()
         a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(0) as clocks:
+        with ClockSampler(local) as clocks:
             a.record()
             for _ in range(steps):
                 fn()
             z.record()
-            torch.cuda.synchronize()
-        return a.elapsed_time(z), clocks.summary()
+            sync()
+        return max_over_ranks(a.elapsed_time(z)), clocks.summary()
 
     engine.prefill(0, prompts[0])
-    torch.cuda.synchronize()
+    sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     engine.prefill(0, prompts[0])
     e1.record()
-    torch.cuda.synchronize()
-    prefill_ms = e0.elapsed_time(e1)
+    sync()
+    prefill_ms = max_over_ranks(e0.elapsed_time(e1))
     for row in range(batch):
         if row:
             engine.prefill(row, prompts[row])
@@ -260,29 +283,33 @@ def run_hybrid(args) -> dict:
     ops.Workspace.get(dev).check()
     ms64, clocks = timed(lambda: engine.decode_step(batch), args.steps, args.warmup)
     ms1, _ = timed(lambda: engine.decode_step(1), args.steps, args.warmup)
-    cycles0 = dict(engine.mtp_stats())
-    ms1_mtp, _ = timed(lambda: engine.mtp_step(1), args.steps, args.warmup)
-    stats = engine.mtp_stats()
-    ms64_mtp, _ = timed(lambda: engine.mtp_step(batch), args.steps, args.warmup)
-    torch.cuda.synchronize()
+    ms1_mtp = ms64_mtp = float("nan")
+    stats = {}
+    if use_mtp:
+        ms1_mtp, _ = timed(lambda: engine.mtp_step(1), args.steps, args.warmup)
+        stats = engine.mtp_stats()
+        ms64_mtp, _ = timed(lambda: engine.mtp_step(batch), args.steps, args.warmup)
+    sync()
     ops.Workspace.get(dev).check()
     value = batch * args.steps / (ms64 / 1e3)
-    return {
-        "metric": "decode_tok_s_bs64", "value": round(value, 2), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms64 / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+    num = lambda v, nd=4: None if v != v else round(v, nd)  # NaN (not measured at this N) -> null
+    result = {
+        "metric": "decode_tok_s_bs64", "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms64 / args.steps, 4), "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": round(value / PUBLISHED_BATCHED_DECODE_TOK_S, 2),
         "dtype": "fp8_e4m3 weights/activations/KV, bf16 residual stream, fp32 accumulate and recurrent state",
         "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)", "impl": "ours",
-        "config": {"model": cfg.name, "global_batch": batch, "seq_len": ctx, "parallelism": "dp1",
+        "config": {"model": cfg.name, "global_batch": batch, "seq_len": ctx, "parallelism": f"tp{world}+ep{world}" if world > 1 else "dp1",
                    "weights_gb": round(weights.nbytes() / 1e9, 1) if hasattr(weights, "nbytes") else None,
                    "l2": "inputs larger than L2 (the routed experts of a step alone exceed it)"},
         "clocks": clocks,
         "extra": {"decode_tok_s_bs1": round(args.steps / (ms1 / 1e3), 2), "ms_per_step_bs1": round(ms1 / args.steps, 4),
-                  "mtp_cycle_ms_bs1": round(ms1_mtp / args.steps, 4), "mtp_cycle_ms_bs64": round(ms64_mtp / args.steps, 4),
+                  "mtp_cycle_ms_bs1": num(ms1_mtp / args.steps), "mtp_cycle_ms_bs64": num(ms64_mtp / args.steps),
                   "mtp_acceptance_random_head": stats.get("acceptance_rate"),
                   "mtp_note": "one draft token per cycle; a random-init draft head is never accepted, so a cycle yields one "
                               "token here -- at the reference's published 88% acceptance a cycle yields 1.88",
-                  "decode_tok_s_bs1_mtp_at_88pct": round(1.88 * args.steps / (ms1_mtp / 1e3), 2),
+                  "decode_tok_s_bs1_mtp_at_88pct": num(1.88 * args.steps / (ms1_mtp / 1e3), 2),
                   "prefill_tok_s": round(ctx / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 2),
                   "weight_build_s": round(build_s, 1),
                   "vs_baseline_bs1": round(args.steps / (ms1 / 1e3) / 62.9, 2),
@@ -290,6 +317,9 @@ def run_hybrid(args) -> dict:
                   "baseline_note": "reference: same model family (V1-S tier) on one RTX 3090 Ti + 32 GiB host RAM: prefill 1,779.7, "
                                    "decode 62.9, MTP decode 87.0 tok/s; continuous batching 156.56 tok/s"},
     }
+    if world > 1:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
 
 
 def run_reference(args) -> dict:

@@ -201,16 +201,28 @@ def _quant_stack(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
 
 
 def random_hybrid_weights(cfg: HybridConfig, device, seed: int = 0, std: float = 0.02, mtp: bool = False,
-                          expert_chunk: int = 64) -> HybridWeights:
-    """N(0, std) weights drawn and quantized to block FP8 on ``device``, layer by layer (single GPU).  Only one chunk of
-    ``expert_chunk`` experts exists in float at a time, so the 80B configuration builds inside its FP8 footprint."""
-    from .llama import MtpHead
+                          expert_chunk: int = 64, tp_rank: int = 0, tp_size: int = 1) -> HybridWeights:
+    """N(0, std) weights drawn and quantized to block FP8 on ``device``, layer by layer.  Only one chunk of
+    ``expert_chunk`` experts exists in float at a time, so the 80B configuration builds inside its FP8 footprint.
+    Under tensor / expert parallelism every rank draws the (small) dense matrices in full from the common stream and keeps
+    its slice, and draws only its own experts, each chunk from a generator seeded by the chunk's global position: all
+    ranks hold shards of one and the same model, whatever ``tp_size`` is."""
+    from .llama import MtpHead, kv_head_rows
     dev = torch.device(device)
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)
+    egen = torch.Generator(device=dev)
+    w, r = tp_size, tp_rank
     h, d, hq, hkv = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
     ld, lk, lv = cfg.linear_head_dim, cfg.linear_k_heads, cfg.linear_v_heads
     e, mi, si = cfg.num_experts, cfg.moe_intermediate, cfg.shared_intermediate
+    if e % w or hq % w or lk % w or lv % w or cfg.vocab_size % w:
+        raise ValueError(f"heads / experts / vocabulary of {cfg.name} do not split over {w} ranks")
+    e_per = e // w
+    chunk = min(expert_chunk, e_per)
+    while e_per % chunk:
+        chunk -= 1
+    counter = [0]  # global position of the next expert chunk: the same sequence on every rank
 
     def rnd(*shape, scale=std):
         return torch.randn(shape, generator=gen, device=dev, dtype=torch.float32).mul_(scale).to(torch.bfloat16)
@@ -218,47 +230,74 @@ def random_hybrid_weights(cfg: HybridConfig, device, seed: int = 0, std: float =
     def ones(n):
         return torch.ones(n, dtype=torch.bfloat16, device=dev)
 
+    def rows(x, parts):  # this rank's share of `parts` leading rows
+        return x.reshape(w, parts // w, *x.shape[1:])[r] if w > 1 else x
+
+    def cols(x, parts):
+        return x.reshape(x.shape[0], w, parts // w)[:, r].contiguous() if w > 1 else x
+
     def experts(n, k):
         qs, ss = [], []
-        for lo in range(0, e, expert_chunk):
-            q, s_ = _quant_stack(rnd(min(expert_chunk, e - lo), n, k))
-            qs.append(q)
-            ss.append(s_)
+        for lo in range(0, e, chunk):
+            mine = r * e_per <= lo < (r + 1) * e_per
+            if mine:
+                egen.manual_seed(seed * 1_000_003 + 7919 * counter[0] + 1)
+                x = torch.randn((chunk, n, k), generator=egen, device=dev, dtype=torch.float32).mul_(std).to(torch.bfloat16)
+                q, s_ = _quant_stack(x)
+                qs.append(q)
+                ss.append(s_)
+            counter[0] += 1
         return torch.cat(qs), torch.cat(ss)
 
     def moe():
         gu_q, gu_s = experts(2 * mi, h)
         dn_q, dn_s = experts(h, mi)
-        ffn = MoeFfn(router=rnd(e, h), router_bias=None, gate_up=gu_q, gate_up_scale=gu_s, down=dn_q, down_scale=dn_s)
+        ffn = MoeFfn(router=rnd(e, h), router_bias=None, gate_up=gu_q, gate_up_scale=gu_s, down=dn_q, down_scale=dn_s,
+                     e_lo=r * e_per)
         if si:
-            ffn.shared_gate_up = Fp8Linear.from_float(rnd(2 * si, h))
-            ffn.shared_down = Fp8Linear.from_float(rnd(h, si))
+            sg, su, sd = rnd(si, h), rnd(si, h), rnd(h, si)
+            if w > 1 and (si // w) % 128 == 0:
+                sg, su, sd = rows(sg, si), rows(su, si), cols(sd, si)
+            else:
+                ffn.shared_replicated = w > 1
+            ffn.shared_gate_up = Fp8Linear.from_float(torch.cat([sg, su], 0))
+            ffn.shared_down = Fp8Linear.from_float(sd)
         return ffn
+
+    def attention(gated: bool):
+        wq, wk, wv = rnd(hq * d, h), rnd(hkv * d, h), rnd(hkv * d, h)
+        parts = [rows(wq, hq * d), kv_head_rows(wk, hkv, d, r, w), kv_head_rows(wv, hkv, d, r, w)]
+        if gated:
+            parts.append(rows(rnd(hq * d, h), hq * d))
+        return Fp8Linear.from_float(torch.cat(parts, 0)), Fp8Linear.from_float(cols(rnd(h, hq * d), hq * d))
 
     layers = []
     for i in range(cfg.num_layers):
         layer = HybridLayer(attn_norm=ones(h), qkv=None, o_proj=None, mlp_norm=ones(h), gate_up=None, down=None, moe=moe())
         if cfg.is_linear(i):
-            rows = 2 * lk * ld + 2 * lv * ld + 2 * lv  # q | k | v | z | b | a
-            layer.gdn = GdnWeights(Fp8Linear.from_float(rnd(rows, h)), rnd(cfg.conv_dim, 4, scale=0.3).float().contiguous(),
-                                   torch.zeros(lv, dtype=torch.float32, device=dev).uniform_(-2.0, 0.5, generator=gen),
-                                   rnd(lv, scale=0.5).float().contiguous(), (1 + rnd(ld, scale=0.1).float()).contiguous(),
-                                   Fp8Linear.from_float(rnd(h, lv * ld)), lk, lv)
+            stacked = torch.cat([rows(rnd(lk * ld, h), lk * ld), rows(rnd(lk * ld, h), lk * ld), rows(rnd(lv * ld, h), lv * ld),
+                                 rows(rnd(lv * ld, h), lv * ld), rows(rnd(lv, h), lv), rows(rnd(lv, h), lv)], 0)  # q | k | v | z | b | a
+            conv = rnd(cfg.conv_dim, 4, scale=0.3).float()
+            conv = torch.cat([rows(conv[: lk * ld], lk * ld), rows(conv[lk * ld : 2 * lk * ld], lk * ld), rows(conv[2 * lk * ld :], lv * ld)], 0)
+            a_log = torch.zeros(lv, dtype=torch.float32, device=dev).uniform_(-2.0, 0.5, generator=gen)
+            layer.gdn = GdnWeights(Fp8Linear.from_float(stacked), conv.contiguous(), rows(a_log, lv).contiguous(),
+                                   rows(rnd(lv, scale=0.5).float(), lv).contiguous(), (1 + rnd(ld, scale=0.1).float()).contiguous(),
+                                   Fp8Linear.from_float(cols(rnd(h, lv * ld), lv * ld)), lk // w, lv // w)
         else:
-            gate_rows = hq * d if cfg.attn_output_gate else 0
-            layer.qkv = Fp8Linear.from_float(rnd((hq + 2 * hkv) * d + gate_rows, h))
-            layer.o_proj = Fp8Linear.from_float(rnd(h, hq * d))
-            layer.gated = bool(gate_rows)
+            layer.qkv, layer.o_proj = attention(cfg.attn_output_gate)
+            layer.gated = bool(cfg.attn_output_gate)
             if cfg.qk_norm:
                 layer.q_norm, layer.k_norm = (1 + rnd(d, scale=0.1).float()).contiguous(), (1 + rnd(d, scale=0.1).float()).contiguous()
         layers.append(layer)
     head = None
     if mtp:
         # the draft head: one dense-attention block with a routed FFN of its own, fed by eh_proj([embed; hidden])
-        blk = HybridLayer(attn_norm=ones(h), qkv=Fp8Linear.from_float(rnd((hq + 2 * hkv) * d, h)),
-                          o_proj=Fp8Linear.from_float(rnd(h, hq * d)), mlp_norm=ones(h), gate_up=None, down=None, moe=moe())
+        qkv, o_proj = attention(False)
+        blk = HybridLayer(attn_norm=ones(h), qkv=qkv, o_proj=o_proj, mlp_norm=ones(h), gate_up=None, down=None, moe=moe())
         head = MtpHead(ones(h), ones(h), Fp8Linear.from_float(rnd(h, 2 * h)), blk)
-    return HybridWeights(rnd(cfg.vocab_size, h), layers, ones(h), Fp8Linear.from_float(rnd(cfg.vocab_size, h)), 0, 1, head)
+    embed = rnd(cfg.vocab_size, h)
+    lm_head = Fp8Linear.from_float(rows(rnd(cfg.vocab_size, h), cfg.vocab_size))
+    return HybridWeights(embed, layers, ones(h), lm_head, r, w, head)
 
 
 def _with_placeholders(cfg: HybridConfig, tensors):

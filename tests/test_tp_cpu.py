@@ -107,3 +107,19 @@ def test_hybrid_tensor_parallel_matches_single_rank():
     # four MoE layers and the recurrent state amplify the rounding noise (and flip a few expert choices); a wrong head
     # or shard mapping lands near 0.3
     _check_parallel(cfg, build, 2, prompt, tol=0.05, min_cos=0.95, min_row_cos=0.97)
+
+
+def test_random_hybrid_weights_are_shards_of_one_model():
+    """The random-init builder used by the benchmark: every rank draws only its experts, yet TP = 2 is the same model
+    as TP = 1 (also with the MTP head's block)."""
+    from mfq_b200.models.hybrid import HybridConfig, HybridModel, random_hybrid_weights
+    cfg = HybridConfig.tiny()
+    one = random_hybrid_weights(cfg, "cpu", seed=2, std=0.05, mtp=True, expert_chunk=3)
+    two = [random_hybrid_weights(cfg, "cpu", seed=2, std=0.05, mtp=True, expert_chunk=3, tp_rank=r, tp_size=2) for r in range(2)]
+    full = one.layers[0].moe.gate_up
+    assert torch.equal(torch.cat([t.layers[0].moe.gate_up for t in two]).view(torch.uint8), full.view(torch.uint8))
+    assert two[1].layers[0].moe.e_lo == cfg.num_experts // 2 and torch.equal(two[0].embed, one.embed)
+    assert torch.equal(torch.cat([t.mtp.layer.moe.down for t in two]).view(torch.uint8), one.mtp.layer.moe.down.view(torch.uint8))
+    prompt = torch.randint(0, cfg.vocab_size, (21,), generator=torch.Generator().manual_seed(8))
+    build = lambda rank, w, coll: HybridModel(cfg, one if w == 1 else two[rank], collective=coll)
+    _check_parallel(cfg, build, 2, prompt, tol=0.05, min_cos=0.95, min_row_cos=0.97)
