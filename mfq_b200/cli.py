@@ -187,6 +187,14 @@ def _cmd_eval(args) -> int:
         fields = MoeConfig.__dataclass_fields__
         return MoeConfig(**{k: v for k, v in cfg.items() if k in fields}), dequantize_checkpoint(tensors)
 
+    if str(args.base).endswith("_logit3_") or Path(args.base).suffix in (".logit3", ".ref"):
+        # the baseline is a reference-logits file (written by `mfq wt2-reference` or by the reference's own tool)
+        from .evaluation.reference_logits import score_against_reference
+        cfg, test = load(args.model)
+        lm = MoeLM(cfg, test)
+        rep = score_against_reference(args.base, lambda ids: lm.forward(torch.as_tensor(ids.astype("int64"))).float().numpy())
+        print(" ".join(f"{k}={v:.6g}" if isinstance(v, float) else f"{k}={v}" for k, v in rep.items()))
+        return 0
     cfg, base = load(args.base)
     _, test = load(args.model)
     g = torch.Generator().manual_seed(args.seed)
@@ -199,6 +207,36 @@ def _cmd_eval(args) -> int:
     n = len(reports)
     print(f"kld={sum(r.kld for r in reports) / n:.6g} mean_kld_q_ref={sum(r.reverse_kld for r in reports) / n:.6g} "
           f"same_top={100 * sum(r.top1_agreement for r in reports) / n:.2f}% chunks={n}")
+    return 0
+
+
+def _cmd_wt2_reference(args) -> int:
+    """Write the baseline's reference-logits file (``_logit3_`` format: per scored position the full distribution as
+    uint16 log-probability codes) over token windows from a file of token ids or, without one, seeded random windows."""
+    import numpy as np
+    import torch
+    from . import formats as F
+    from .evaluation.reference_logits import write_reference
+    from .models.moe_lm import MoeConfig, MoeLM, dequantize_checkpoint
+    with F.open_mfq(args.model) as store:
+        cfg_d = json.loads(store.assets()["model_config.json"])
+        tensors = {n: store[n] for n in store if not n.startswith("__mfq_asset__/")}
+    cfg = MoeConfig(**{k: v for k, v in cfg_d.items() if k in MoeConfig.__dataclass_fields__})
+    lm = MoeLM(cfg, dequantize_checkpoint(tensors))
+    if args.tokens:
+        ids = np.fromfile(args.tokens, dtype="<i4")
+        chunks = min(args.chunks, len(ids) // args.ctx)
+        if chunks < 1:
+            raise SystemExit(f"{args.tokens} holds fewer than {args.ctx} token ids")
+        windows = ids[: chunks * args.ctx].reshape(chunks, args.ctx)
+    else:
+        g = torch.Generator().manual_seed(args.seed)
+        windows = torch.randint(0, cfg.vocab_size, (args.chunks, args.ctx), generator=g).numpy().astype("<i4")
+    nll = write_reference(args.output, windows, lambda w: lm.forward(torch.as_tensor(w.astype("int64"))).float().numpy())
+    from .evaluation.reference_logits import scored_span
+    scored = windows.shape[0] * scored_span(args.ctx)[1]
+    print(json.dumps({"output": args.output, "chunks": int(windows.shape[0]), "ctx": args.ctx, "baseline_nll": nll,
+                      "baseline_ppl": float(np.exp(nll / max(1, scored)))}))
     return 0
 
 
@@ -309,6 +347,14 @@ def build_parser() -> argparse.ArgumentParser:
     kl.add_argument("--ctx", type=int, default=128)
     kl.add_argument("--seed", type=int, default=0)
     kl.set_defaults(fn=_cmd_eval)
+    wr = sub.add_parser("wt2-reference", help="write a baseline's reference-logits file (_logit3_) for `eval kl --base`")
+    wr.add_argument("--model", required=True, help="baseline .mfq (usually the full-precision checkpoint)")
+    wr.add_argument("--output", required=True)
+    wr.add_argument("--tokens", help="little-endian int32 token ids (e.g. a tokenized WikiText-2 test split); default: random windows")
+    wr.add_argument("--chunks", type=int, default=4)
+    wr.add_argument("--ctx", type=int, default=128)
+    wr.add_argument("--seed", type=int, default=0)
+    wr.set_defaults(fn=_cmd_wt2_reference)
     s = sub.add_parser("serve", help="OpenAI/Anthropic-compatible server")
     s.add_argument("--model", required=True)
     s.add_argument("--model-name")

@@ -60,3 +60,23 @@ def test_diagnose_runs_the_format_checks_on_cpu(capsys):
     report = json.loads(capsys.readouterr().out)
     assert report["ok"] and set(report["checks"]) == {"nint", "container", "fp8-block"}
     assert report["checks"]["nint"]["snr_db"] > 18
+
+
+def test_wt2_reference_and_eval_against_it(tmp_path, capsys):
+    """Baseline checkpoint -> reference-logits file -> `eval kl --base <file>`: the baseline scores ~0 KLD against its own
+    file, a 3-bit quantization scores worse."""
+    import json
+    from mfq_b200.cli import main
+    base, q3, ref = tmp_path / "base.mfq", tmp_path / "q3.mfq", tmp_path / "base._logit3_"
+    assert main(["quantize", "synthetic:tiny-moe", str(base), "--full-precision"]) == 0
+    assert main(["quantize", "synthetic:tiny-moe", str(q3), "--bits", "3"]) == 0
+    capsys.readouterr()
+    assert main(["wt2-reference", "--model", str(base), "--output", str(ref), "--chunks", "2", "--ctx", "32"]) == 0
+    info = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert info["chunks"] == 2 and ref.exists() and info["baseline_ppl"] > 1
+    assert main(["eval", "kl", "--model", str(base), "--base", str(ref)]) == 0
+    own = dict(kv.split("=") for kv in capsys.readouterr().out.split())
+    assert main(["eval", "kl", "--model", str(q3), "--base", str(ref)]) == 0
+    quant = dict(kv.split("=") for kv in capsys.readouterr().out.split())
+    assert float(own["kld"]) < 1e-3 and float(own["same_top"]) > 0.97
+    assert float(quant["kld"]) > float(own["kld"])
