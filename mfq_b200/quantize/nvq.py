@@ -48,6 +48,26 @@ def _assign(cross: torch.Tensor, quad: torch.Tensor, scale: torch.Tensor) -> tor
     return (s * s * quad - 2.0 * s * cross).argmin(-1)
 
 
+def fused_assign_available(x: torch.Tensor, vec: int) -> bool:
+    """The fused CUDA assignment (``ops/csrc/quant_ops.cu``) serves CUDA tensors with 4- or 8-wide vectors."""
+    if not x.is_cuda or vec not in (4, 8):
+        return False
+    from ..ops import lib as _lib
+    return _lib.available()
+
+
+def assign_fused(xv: torch.Tensor, wv: torch.Tensor, table: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """Nearest codeword of every vector under the weighted error, without the ``[V, C]`` cost matrices:
+    ``xv, wv [V, vec]``, ``table [C, vec]``, ``scale [V]`` -> indices ``[V]`` (int64)."""
+    from ..ops.lib import check, lib, ptr, stream_ptr
+    v, vec = xv.shape
+    idx = torch.empty(v, dtype=torch.int32, device=xv.device)
+    rc = lib().mfq_nvq_assign(ptr(xv.contiguous()), ptr(wv.contiguous()), ptr(scale.contiguous().float()),
+                              ptr(table.contiguous().float()), ptr(idx), v, table.shape[0], vec, stream_ptr())
+    check(rc, "nvq_assign")
+    return idx.to(torch.int64)
+
+
 def _refit(xg, wg, idx, table, vpg):
     code = table[idx].reshape(xg.shape)
     num = (wg * xg * code).sum(-1)
@@ -60,8 +80,14 @@ def _search(xg: torch.Tensor, wg: torch.Tensor, table: torch.Tensor, vec: int, s
     vpg = gs // vec
     xv = xg.reshape(g * vpg, vec)
     wv = wg.reshape(g * vpg, vec)
-    cross = (wv * xv) @ table.T
-    quad = wv @ (table * table).T
+    fused = fused_assign_available(xg, vec)
+    if fused:
+        cross = quad = None  # never materialised on the GPU path
+        assign = lambda sc: assign_fused(xv, wv, table, sc)
+    else:
+        cross = (wv * xv) @ table.T
+        quad = wv @ (table * table).T
+        assign = lambda sc: _assign(cross, quad, sc)
     qmax = float(table.max())
     amax = xg.abs().amax(-1)
     best_err = torch.full((g,), float("inf"), device=xg.device)
@@ -69,9 +95,9 @@ def _search(xg: torch.Tensor, wg: torch.Tensor, table: torch.Tensor, vec: int, s
     best_idx = torch.zeros((g, vpg), dtype=torch.long, device=xg.device)
     for off in torch.linspace(-0.12 * qmax, 0.12 * qmax, steps).tolist():
         s0 = torch.where(amax > 0, amax / (qmax + off), torch.zeros_like(amax))
-        idx = _assign(cross, quad, s0.repeat_interleave(vpg)).reshape(g, vpg)
+        idx = assign(s0.repeat_interleave(vpg)).reshape(g, vpg)
         s1, _ = _refit(xg, wg, idx, table, vpg)
-        idx = _assign(cross, quad, s1.repeat_interleave(vpg)).reshape(g, vpg)
+        idx = assign(s1.repeat_interleave(vpg)).reshape(g, vpg)
         s2, code = _refit(xg, wg, idx, table, vpg)
         diff = s2[:, None] * code - xg
         err = (wg * diff * diff).sum(-1)
@@ -79,7 +105,7 @@ def _search(xg: torch.Tensor, wg: torch.Tensor, table: torch.Tensor, vec: int, s
         best_err = torch.where(take, err, best_err)
         best_scale = torch.where(take, s2, best_scale)
         best_idx[take] = idx[take]
-    return best_scale, best_idx, cross, quad
+    return best_scale, best_idx, assign
 
 
 def quantize_nvq(weight, spec: NvqSpec, *, axis: int = 0, importance=None, search_steps: int = 19,
@@ -111,7 +137,7 @@ def quantize_nvq(weight, spec: NvqSpec, *, axis: int = 0, importance=None, searc
         target, masks = encode_even_parity(rows, torch.where(wobj > 0, wobj, torch.full_like(wobj, 1e-12)))
         xg = target.reshape(o * ng, gs)
         wg = wobj.reshape(o * ng, gs)
-        raw, idx, cross, quad = _search(xg, wg, table, vec, search_steps)
+        raw, idx, assign = _search(xg, wg, table, vec, search_steps)
         raw2 = raw.reshape(o, ng)
         top = raw2.amax(-1)
         d = torch.where(top > 0, (top / levels).to(torch.float16).to(torch.float32), torch.zeros_like(top))
@@ -120,7 +146,7 @@ def quantize_nvq(weight, spec: NvqSpec, *, axis: int = 0, importance=None, searc
 
         def reassign(anchor):
             eff = (anchor[:, None] * sub).reshape(-1)
-            return _assign(cross, quad, eff.repeat_interleave(vpg)).reshape(o * ng, vpg)
+            return assign(eff.repeat_interleave(vpg)).reshape(o * ng, vpg)
 
         def refit(index):
             code = table[index].reshape(o, ng, gs) * sub[:, :, None]
