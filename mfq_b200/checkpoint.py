@@ -107,7 +107,9 @@ def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", ex
 def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict[str, bytes] | None = None,
                     arch: str = "mfq_b200_decoder", extra: dict | None = None) -> None:
     records = dict(tensors)
-    all_assets = {"model_config.json": json.dumps(config).encode()}
+    from .formats import model_graph
+    all_assets = {"model_config.json": json.dumps(config).encode(),
+                  model_graph.ASSET_NAME: model_graph.to_bytes(model_graph.build_graph(config, tensors.keys(), arch))}
     all_assets.update(assets or {})
     for k, v in all_assets.items():
         records[ASSET_PREFIX + k] = v

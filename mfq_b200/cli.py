@@ -163,6 +163,12 @@ def _cmd_inspect(args) -> int:
         rows = [{"name": n, "dtype": store.dtype(n), "bytes": r.nbytes} for n, r in store.records.items()]
         info = {"arch": store.header.model_arch, "version": store.header.version, "extra": store.header.extra,
                 "tensors": len(rows), "bytes": sum(r["bytes"] for r in rows)}
+        graph = store.assets().get("model_graph.json")
+        if graph:
+            from .formats.model_graph import parse_graph
+            g = parse_graph(graph)
+            info["graph"] = {"backbone": g.backbone, "text_layers": g.text_layers, "predictor_layers": g.predictor_layers,
+                             "capabilities": list(g.capabilities)}
     by = {}
     for r in rows:
         by[r["dtype"]] = by.get(r["dtype"], 0) + r["bytes"]
