@@ -273,6 +273,12 @@ def _cmd_serve(args) -> int:
     engine, tok = loader(args.model)
     service.add_model(args.model_name or Path(args.model).stem, engine, tok)
     key = os.environ.get(args.api_key_env) if args.api_key_env else None
+    if args.api_keys_file:
+        from .server.auth import KeyStore
+        store = KeyStore(args.api_keys_file)
+        if key:
+            store.add(key, ("admin",), name="startup key")
+        key = store
     cluster = None
     if args.cluster_peer:
         from .server.cluster import ClusterBackend
@@ -378,6 +384,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--api-keys-file", default=None,
+                   help="JSON store of API keys with scopes (inference / read / admin); keys are kept as SHA-256 digests")
     s.add_argument("--kv-budget-gb", type=float, default=0.0,
                    help="cap of the paged KV pool (default on a GPU: 90%% of the memory free after loading the weights)")
     s.add_argument("--cluster-peer", action="append", default=[],

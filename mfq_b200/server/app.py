@@ -97,8 +97,8 @@ class _Stream:
                 return
 
 
-def create_app(service: ModelService, api_key: str | None = None, sessions=None, cluster=None, hardware=None) -> FastAPI:
-    """``sessions``: a :class:`~mfq_b200.server.sessions.SessionStore` (in-memory when omitted); ``cluster``: a
+def create_app(service: ModelService, api_key=None, sessions=None, cluster=None, hardware=None) -> FastAPI:
+    """``api_key``: one key with every scope, or a :class:`~mfq_b200.server.auth.KeyStore`; ``sessions``: a :class:`~mfq_b200.server.sessions.SessionStore` (in-memory when omitted); ``cluster``: a
     :class:`~mfq_b200.server.cluster.ClusterBackend` whose peers serve models that are not loaded here; ``hardware``:
     a :class:`~mfq_b200.server.hardware.HardwareMonitor`."""
     from .hardware import HardwareMonitor
@@ -120,15 +120,24 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None,
     store = sessions if sessions is not None else SessionStore()
     app.state.sessions = store
 
+    from .auth import KeyStore, required_scope
+    keys = api_key if isinstance(api_key, KeyStore) else KeyStore()
+    if isinstance(api_key, str) and api_key:
+        keys.add(api_key, ("admin",), name="startup key")
+    app.state.keys = keys
+
     @app.middleware("http")
     async def auth(request: HttpRequest, call_next):
-        if api_key and request.url.path not in ("/health",):
+        scope = required_scope(request.method, request.url.path)
+        if scope is not None and keys.keys:
             supplied = request.headers.get("x-api-key")
             header = request.headers.get("authorization", "")
             if header.lower().startswith("bearer "):
                 supplied = header[7:].strip()
-            if supplied != api_key:
+            if keys.scopes_of(supplied) is None:
                 return error_response(401, "unauthorized", "missing or invalid API key")
+            if not keys.allows(supplied, scope):
+                return error_response(403, "forbidden", f"this key lacks the {scope!r} scope")
         response = await call_next(request)
         response.headers["x-content-type-options"] = "nosniff"
         return response
@@ -350,6 +359,23 @@ def create_app(service: ModelService, api_key: str | None = None, sessions=None,
     @app.delete("/api/v1/jobs/{jid}")
     async def delete_job(jid: str):
         return {"deleted": jobs.delete(jid)}
+
+    @app.get("/api/v1/auth/keys")
+    async def list_keys():
+        return {"keys": keys.listing()}
+
+    @app.post("/api/v1/auth/keys")
+    async def create_key(request: HttpRequest):
+        body = await request.json()
+        try:
+            key, rec = keys.create(tuple(body.get("scopes") or ("inference",)), str(body.get("name", "")))
+        except ValueError as exc:
+            return error_response(400, "invalid_request", str(exc))
+        return {"key": key, **rec}  # the only time the key itself is shown
+
+    @app.delete("/api/v1/auth/keys/{key_id}")
+    async def revoke_key(key_id: str):
+        return {"revoked": keys.revoke(key_id)}
 
     @app.get("/api/v1/hardware")
     async def hardware_snapshot():
