@@ -216,6 +216,40 @@ def _cmd_eval(args) -> int:
     return 0
 
 
+def _cmd_optimize_layout(args) -> int:
+    """Rewrite a checkpoint into the layout the runtime executes: projections and routed experts as E4M3 with 128x128
+    fp32 multipliers (what the loader would otherwise produce from NINT / NVQ at every start), 4-bit tensors kept as
+    they are with ``--keep-4bit`` (for ``serve --native-4bit``).  Norms, routers and embeddings stay bf16."""
+    import numpy as np
+    from . import formats as F
+    from .checkpoint import quantize_tensors, save_checkpoint
+    from .ops import w4 as w4ops
+    out = Path(args.output)
+    if out.exists() and not args.overwrite:
+        raise SystemExit(f"{out} exists (use --overwrite)")
+    kept, floats = {}, {}
+    with F.open_mfq(args.input) as store:
+        assets = store.assets()
+        cfg = json.loads(assets.pop("model_config.json"))
+        assets.pop("model_graph.json", None)  # rebuilt on save
+        arch, extra = store.header.model_arch, dict(store.header.extra or {})
+        for n in store:
+            if n.startswith("__mfq_asset__/"):
+                continue
+            t = store[n]
+            if args.keep_4bit and ".mlp.experts." not in n and w4ops.from_checkpoint_tensor(t) is not None:
+                kept[n] = t
+            else:
+                floats[n] = np.asarray(F.dequantize(t), dtype=np.float32)
+    q = quantize_tensors(floats, dense="fp8", expert_mix="FP8", device=args.device)
+    q.update(kept)
+    extra.pop("runtime_assets", None)
+    extra["layout"] = {"kind": "native", "dense": "FP8-128SQ", "kept_4bit": sorted(kept)}
+    save_checkpoint(out, cfg, q, assets, arch=arch, extra=extra)
+    print(json.dumps({"output": str(out), "bytes": out.stat().st_size, "transcoded": len(floats), "kept_4bit": len(kept)}))
+    return 0
+
+
 def _cmd_wt2_reference(args) -> int:
     """Write the baseline's reference-logits file (``_logit3_`` format: per scored position the full distribution as
     uint16 log-probability codes) over token windows from a file of token ids or, without one, seeded random windows."""
@@ -359,6 +393,13 @@ def build_parser() -> argparse.ArgumentParser:
     kl.add_argument("--ctx", type=int, default=128)
     kl.add_argument("--seed", type=int, default=0)
     kl.set_defaults(fn=_cmd_eval)
+    ol = sub.add_parser("optimize-layout", help="rewrite a checkpoint into the runtime's native execution layout")
+    ol.add_argument("--input", required=True)
+    ol.add_argument("--output", required=True)
+    ol.add_argument("--overwrite", action="store_true")
+    ol.add_argument("--keep-4bit", action="store_true", help="leave NINT (<= 4 bits) / MXFP4 projections as they are")
+    ol.add_argument("--device", default="cpu")
+    ol.set_defaults(fn=_cmd_optimize_layout)
     wr = sub.add_parser("wt2-reference", help="write a baseline's reference-logits file (_logit3_) for `eval kl --base`")
     wr.add_argument("--model", required=True, help="baseline .mfq (usually the full-precision checkpoint)")
     wr.add_argument("--output", required=True)

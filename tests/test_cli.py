@@ -80,3 +80,30 @@ def test_wt2_reference_and_eval_against_it(tmp_path, capsys):
     quant = dict(kv.split("=") for kv in capsys.readouterr().out.split())
     assert float(own["kld"]) < 1e-3 and float(own["same_top"]) > 0.97
     assert float(quant["kld"]) > float(own["kld"])
+
+
+def test_optimize_layout_transcodes_to_the_runtime_format(tmp_path, capsys):
+    import json
+    from mfq_b200 import formats as F
+    from mfq_b200.cli import main
+    src, dst = tmp_path / "q4.mfq", tmp_path / "native.mfq"
+    # groups of 32 divide the 256-wide rows, which is what the 4-bit GEMM needs to take a tensor as it is
+    assert main(["quantize", "synthetic:tiny-moe-128", str(src), "--bits", "4", "--groupsize", "32",
+                 "--random-expert-mix", "NINT4,NVQ3,MXFP4"]) == 0
+    capsys.readouterr()
+    assert main(["optimize-layout", "--input", str(src), "--output", str(dst), "--keep-4bit"]) == 0
+    info = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert info["transcoded"] > 0 and info["kept_4bit"] > 0
+    with F.open_mfq(dst) as store:
+        assert store.header.extra["layout"]["dense"] == "FP8-128SQ"
+        dtypes = {n: store.dtype(n) for n in store if not n.startswith("__mfq_asset__/")}
+        assert "model_graph.json" in store.assets()
+    assert dtypes["model.block.0.attention.query.weight"].startswith("NINT")       # kept as 4-bit
+    assert dtypes["model.block.0.mlp.experts.gate.weight"] == "MFE"                 # experts re-pooled as FP8
+    # the optimized file serves the same model (KLD against the 4-bit source is tiny: FP8 on top of the 4-bit values)
+    assert main(["eval", "kl", "--model", str(dst), "--base", str(src), "--chunks", "1", "--ctx", "32"]) == 0
+    kld = float(capsys.readouterr().out.split("kld=")[1].split()[0])
+    assert kld < 0.02
+    import pytest
+    with pytest.raises(SystemExit):  # an existing output needs --overwrite
+        main(["optimize-layout", "--input", str(src), "--output", str(dst)])
