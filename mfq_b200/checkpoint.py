@@ -105,16 +105,21 @@ def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", ex
 
 
 def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict[str, bytes] | None = None,
-                    arch: str = "mfq_b200_decoder", extra: dict | None = None) -> None:
-    records = dict(tensors)
+                    arch: str = "mfq_b200_decoder", extra: dict | None = None, shard_bytes: int | None = None):
+    """Write the checkpoint; with ``shard_bytes`` as ``stem-0000i-of-0000N.mfq`` files (returns their paths)."""
+    records = {}
     from .formats import model_graph
     all_assets = {"model_config.json": json.dumps(config).encode(),
                   model_graph.ASSET_NAME: model_graph.to_bytes(model_graph.build_graph(config, tensors.keys(), arch))}
     all_assets.update(assets or {})
-    for k, v in all_assets.items():
+    for k, v in all_assets.items():  # assets first: they land in the first shard
         records[ASSET_PREFIX + k] = v
+    records.update(tensors)
     header = F.FileHeader(model_arch=arch, extra={"runtime_assets": sorted(all_assets), **(extra or {})})
+    if shard_bytes:
+        return F.save_sharded(path, header, records, shard_bytes)
     F.save(path, header, records)
+    return [path]
 
 
 def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots: int | None = None, max_batch: int = 64,

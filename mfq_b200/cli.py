@@ -102,10 +102,12 @@ def _cmd_quantize(args) -> int:
                          widths=widths, imatrix=imatrix, scheme=scheme, device=args.device, progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
     extra = {"quantization": {"dense": dense, "preset": args.preset or None, "imatrix": bool(imatrix), "ew_scheme": bool(scheme), "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
                               "random_expert_mix_seed": args.random_expert_mix_seed if args.random_expert_mix else None}}
-    save_checkpoint(out, cfg, q, assets, extra=extra)
-    size = out.stat().st_size
+    paths = save_checkpoint(out, cfg, q, assets, extra=extra,
+                            shard_bytes=int(args.shard_size_gb * (1 << 30)) if args.shard_size_gb else None)
+    size = sum(Path(p).stat().st_size for p in paths)
     weights = sum(int(t.size) for t in tensors.values())
-    print(json.dumps({"output": str(out), "bytes": size, "weights": weights, "bits_per_weight": round(8 * size / weights, 3)}))
+    print(json.dumps({"output": str(paths[0]), "shards": len(paths), "bytes": size, "weights": weights,
+                      "bits_per_weight": round(8 * size / weights, 3)}))
     return 0
 
 
@@ -351,6 +353,7 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--dry-run", action="store_true")
     q.add_argument("--overwrite", action="store_true")
     q.add_argument("--verbose", action="store_true")
+    q.add_argument("--shard-size-gb", type=float, default=0.0, help="write name-0000i-of-0000N.mfq shards of at most this size")
     q.set_defaults(fn=_cmd_quantize)
     c = sub.add_parser("calibrate", help="importance statistics for bit allocation")
     cs = c.add_subparsers(dest="calibrate_cmd", required=True)

@@ -1,7 +1,7 @@
 """Byte-level codecs of the ``.mfq`` checkpoint container and its tensor families."""
 
 from .container import (ASSET_DTYPE, ASSET_PREFIX, MFQ_MAGIC, FileHeader, MfqStore, TensorRecord, canonical_dtype,
-                        load, open_mfq, pack_tensor, save, shard_paths, unpack_tensor, write_streaming)
+                        load, open_mfq, pack_tensor, save, save_sharded, shard_paths, unpack_tensor, write_streaming)
 from .dense import Bf16Array, Fp8E4M3Array, from_bf16, to_bf16
 from .fp8sq import FP8_128SQ_DTYPE, MXFP8_SQ_DTYPE, Fp8SqTensor, block_fp8_tensor, dequantize_fp8sq
 from .mfe import MfePool, MfeTensor

@@ -41,7 +41,7 @@ _SHARD_RE = re.compile(r"^(?P<stem>.+)-(?P<index>\d{5})-of-(?P<count>\d{5})\.mfq
 
 __all__ = [
     "MFQ_MAGIC", "ASSET_DTYPE", "ASSET_PREFIX", "FileHeader", "TensorRecord", "MfqStore", "save", "load",
-    "open_mfq", "pack_tensor", "unpack_tensor", "canonical_dtype", "write_streaming", "shard_paths",
+    "open_mfq", "pack_tensor", "unpack_tensor", "canonical_dtype", "write_streaming", "save_sharded", "shard_paths",
 ]
 
 
@@ -150,6 +150,33 @@ def save(path, header: FileHeader, tensors: Mapping[str, Any]) -> None:
         for _dt, blob in packed.values():
             f.write(blob)
     os.replace(tmp, path)
+
+
+def save_sharded(path, header: FileHeader, tensors: Mapping[str, Any], max_bytes: int) -> list[Path]:
+    """Write ``tensors`` as ``stem-00001-of-0000N.mfq`` files of at most ``max_bytes`` of blobs each (a tensor is never
+    split; one larger than the limit gets a shard of its own).  Every shard carries the header; the asset records go to
+    the first.  Returns the shard paths; ``open_mfq`` on any of them opens the whole checkpoint."""
+    p = Path(path)
+    stem = p.name[: -len(".mfq")] if p.name.endswith(".mfq") else p.name
+    packed = {name: pack_tensor(t) for name, t in tensors.items()}
+    groups: list[list[str]] = [[]]
+    size = 0
+    for name, (_dt, blob) in packed.items():
+        if groups[-1] and size + len(blob) > max_bytes:
+            groups.append([])
+            size = 0
+        groups[-1].append(name)
+        size += len(blob)
+    paths = [p.with_name(f"{stem}-{i:05d}-of-{len(groups):05d}.mfq") for i in range(1, len(groups) + 1)]
+    for shard, names in zip(paths, groups):
+        records = [(n, packed[n][0], len(packed[n][1])) for n in names]
+        tmp = f"{shard}.tmp-{os.getpid()}"
+        with open(tmp, "wb") as f:
+            f.write(_header_bytes(header, records))
+            for n in names:
+                f.write(packed[n][1])
+        os.replace(tmp, shard)
+    return paths
 
 
 def write_streaming(path, header: FileHeader, items: list[tuple[str, str, int]], blob_iter) -> None:

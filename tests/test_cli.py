@@ -107,3 +107,21 @@ def test_optimize_layout_transcodes_to_the_runtime_format(tmp_path, capsys):
     import pytest
     with pytest.raises(SystemExit):  # an existing output needs --overwrite
         main(["optimize-layout", "--input", str(src), "--output", str(dst)])
+
+
+def test_sharded_output_opens_as_one_checkpoint(tmp_path, capsys):
+    import json
+    from mfq_b200 import formats as F
+    from mfq_b200.cli import main
+    whole, stem = tmp_path / "whole.mfq", tmp_path / "parts.mfq"
+    assert main(["quantize", "synthetic:tiny-moe", str(whole), "--bits", "4"]) == 0
+    capsys.readouterr()
+    assert main(["quantize", "synthetic:tiny-moe", str(stem), "--bits", "4", "--shard-size-gb", "0.0003"]) == 0
+    info = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert info["shards"] >= 3 and info["output"].endswith("-00001-of-%05d.mfq" % info["shards"])
+    with F.open_mfq(whole) as a, F.open_mfq(info["output"]) as b:
+        assert sorted(a) == sorted(b) and a.assets()["model_config.json"] == b.assets()["model_config.json"]
+        n = "model.block.1.attention.output.weight"
+        assert (F.dequantize(a[n]) == F.dequantize(b[n])).all()
+    # a sharded checkpoint is a valid input of the other commands
+    assert main(["inspect", info["output"]]) == 0
