@@ -256,12 +256,15 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
             pass
         if stream.error_code:
             return _failure(stream)
-        message, finish = {"role": "assistant", "content": stream.text}, stream.finish or "stop"
+        from . import tools as tool_ops
+        reasoning, answer = tool_ops.split_reasoning(stream.text)
+        message, finish = {"role": "assistant", "content": answer}, stream.finish or "stop"
+        if reasoning is not None:
+            message["reasoning_content"] = reasoning
         if body.get("tools"):
-            from . import tools as tool_ops
-            text, calls = tool_ops.extract(stream.text)
+            text, calls = tool_ops.extract(answer)
             if calls:
-                message = {"role": "assistant", "content": text or None, "tool_calls": tool_ops.openai_calls(calls)}
+                message.update(content=text or None, tool_calls=tool_ops.openai_calls(calls))
                 finish = "tool_calls"
         return {"id": cid, "object": "chat.completion", "created": created, "model": lm.name,
                 "choices": [{"index": 0, "message": message, "finish_reason": finish}], "usage": usage()}

@@ -86,3 +86,18 @@ def openai_calls(calls: list[dict]) -> list[dict]:
 def anthropic_blocks(text: str, calls: list[dict]) -> list[dict]:
     blocks = [{"type": "text", "text": text}] if text or not calls else []
     return blocks + [{"type": "tool_use", "id": c["id"].replace("call_", "toolu_"), "name": c["name"], "input": c["arguments"]} for c in calls]
+
+
+_THINK = re.compile(r"^\s*<think>(.*?)</think>\s*", re.S)
+
+
+def split_reasoning(text: str) -> tuple[str | None, str]:
+    """A leading ``<think>...</think>`` block (reasoning models) -> (reasoning, remaining answer); an unterminated block
+    (generation stopped while thinking) is all reasoning."""
+    m = _THINK.match(text)
+    if m:
+        return m.group(1).strip(), text[m.end():]
+    stripped = text.lstrip()
+    if stripped.startswith("<think>"):
+        return stripped[len("<think>"):].strip(), ""
+    return None, text

@@ -66,3 +66,13 @@ def test_openai_and_anthropic_tool_calls(client):
     body = r.json()
     assert body["stop_reason"] == "tool_use" and body["content"][0] == {"type": "text", "text": "Let me check."}
     assert body["content"][1]["type"] == "tool_use" and body["content"][1]["input"] == {"city": "Oslo"}
+
+
+def test_reasoning_block_is_split_from_the_answer(client):
+    c, backend = client
+    assert tools.split_reasoning("<think>a\nb</think>\n\nfinal") == ("a\nb", "final")
+    assert tools.split_reasoning("plain") == (None, "plain") and tools.split_reasoning("<think>cut off") == ("cut off", "")
+    backend.text = "<think>the user greets me</think>Hello!"
+    r = c.post("/v1/chat/completions", json={"model": "m", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 200})
+    msg = r.json()["choices"][0]["message"]
+    assert msg["content"] == "Hello!" and msg["reasoning_content"] == "the user greets me"
