@@ -103,8 +103,29 @@ class MoeWeights(LlamaWeights):
         def norm(name):
             return get(name).to(torch.bfloat16)
 
+        def fp8_direct(names):
+            """Checkpoint tensors that already are E4M3 + 128x128 fp32 multipliers (a checkpoint in the native layout)
+            are adopted as they are -- stacked along the rows when every part holds whole 128-row blocks -- instead
+            of being decoded to float and quantized again.  Single rank only (shards cut through the blocks)."""
+            if w != 1:
+                return None
+            from ..formats.fp8sq import Fp8SqTensor
+            parts = [tensors[n] for n in names]
+            if not all(isinstance(p, Fp8SqTensor) and p.dtype == "FP8-128SQ" and p.scale_dtype == "F32" and p.row_q_bits is None
+                       and tuple(p.block_shape) == (128, 128) and p.shape[1] % 128 == 0 for p in parts):
+                return None
+            if len(parts) > 1 and any(p.shape[0] % 128 for p in parts[:-1]):
+                return None
+            q = torch.from_numpy(np.concatenate([np.asarray(p.codes, dtype=np.uint8) for p in parts], 0)).to(dev).view(torch.float8_e4m3fn)
+            sc = torch.from_numpy(np.concatenate([np.asarray(p.scales, dtype=np.float32) for p in parts], 0)).to(dev)
+            return Fp8Linear(q.contiguous(), sc.contiguous())
+
         def linear(names, float_builder):
-            """4-bit native when every named tensor allows it, else FP8 from the float matrix ``float_builder()``."""
+            """4-bit native when every named tensor allows it, FP8 blocks adopted directly when the checkpoint stores
+            them, else FP8 from the float matrix ``float_builder()``."""
+            direct = fp8_direct(names)
+            if direct is not None:
+                return direct
             if native_4bit and w == 1:
                 from ..models.llama import W4Linear
                 from ..ops import w4 as w4ops

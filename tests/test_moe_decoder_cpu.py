@@ -69,3 +69,29 @@ def test_native_4bit_loading_keeps_nint_codes():
     a, b = logits(native), logits(fp8)
     scale = float(b.abs().max())
     assert float((a - b).abs().mean()) <= 0.03 * scale  # same checkpoint; FP8 transcoding vs exact 4-bit reconstruction
+
+
+def test_native_layout_checkpoint_loads_without_requantizing(tmp_path):
+    """A checkpoint written by ``optimize-layout`` holds E4M3 blocks: the loader adopts them bit for bit, and the model
+    is the one the 4-bit source loads to (whose float values get the same FP8 blocks)."""
+    import numpy as np
+    import torch
+    from mfq_b200 import formats as F
+    from mfq_b200.cli import main
+    from mfq_b200.formats.fp8sq import Fp8SqTensor
+    from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeWeights
+    src, dst = tmp_path / "q4.mfq", tmp_path / "native.mfq"
+    assert main(["quantize", "synthetic:tiny-moe-128", str(src), "--bits", "4"]) == 0
+    assert main(["optimize-layout", "--input", str(src), "--output", str(dst)]) == 0
+    import json
+    with F.open_mfq(dst) as store:
+        cfg_d = json.loads(store.assets()["model_config.json"])
+        cfg = MoeDecoderConfig(**{k: v for k, v in cfg_d.items() if k in MoeDecoderConfig.__dataclass_fields__})
+        t = store["model.block.0.attention.query.weight"]
+        assert isinstance(t, Fp8SqTensor)
+        native = MoeWeights.from_tensors(cfg, store, "cpu")
+        assert np.array_equal(native.layers[0].qkv.q.view(torch.uint8)[: t.shape[0]].numpy(), t.codes)
+    with F.open_mfq(src) as store:
+        source = MoeWeights.from_tensors(cfg, store, "cpu")
+    assert torch.equal(native.layers[0].qkv.q.view(torch.uint8), source.layers[0].qkv.q.view(torch.uint8))
+    assert torch.allclose(native.layers[1].o_proj.scale, source.layers[1].o_proj.scale, rtol=1e-6)
