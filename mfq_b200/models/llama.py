@@ -249,6 +249,7 @@ class LlamaModel:
         self.hk = max(1, cfg.num_kv_heads // self.tp)
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.attn_splits = 1
+        self.attn_rot = None  # leading dims of a head that are rotated (None: all of them)
 
     # -- primitive dispatch -------------------------------------------------------------------------------------
     def _norm_quant(self, x, w):
@@ -300,11 +301,11 @@ class LlamaModel:
                 kd = torch.empty((t, self.hk, d), dtype=torch.bfloat16, device=qkv.device)
                 vd = torch.empty_like(kd)
             q = ops.rope_kv_write(qkv, step.positions, step.slots, kv, n_q=self.hq, n_kv=self.hk, head_dim=d,
-                                  theta=cfg.rope_theta, kd_out=kd, vd_out=vd)
+                                  theta=cfg.rope_theta, rot=self.attn_rot, kd_out=kd, vd_out=vd)
         else:
             q3 = qkv.view(t, self.hq + 2 * self.hk, d)
-            q = ref.rope(q3[:, : self.hq], step.positions, cfg.rope_theta)
-            k = ref.rope(q3[:, self.hq : self.hq + self.hk], step.positions, cfg.rope_theta)
+            q = ref.rope(q3[:, : self.hq], step.positions, cfg.rope_theta, self.attn_rot)
+            k = ref.rope(q3[:, self.hq : self.hq + self.hk], step.positions, cfg.rope_theta, self.attn_rot)
             ref.write_kv(kv, k, q3[:, self.hq + self.hk :], step.slots)
         if not prefill:
             if qkv.is_cuda:

@@ -1,0 +1,166 @@
+"""Multi-head latent attention (DeepSeek-V3 style) on top of the MoE decoder.
+
+Projections: ``q = q_b(rmsnorm(q_a(x)))`` (or one ``q_b`` when the query is not compressed), ``kv_a(x)`` gives the shared
+latent ``c`` (``kv_lora_rank``) and one rotary key part for all heads, ``kv_b(rmsnorm(c))`` expands the latent into a
+non-rotary key part and a value per head.  A head's score is ``q_nope . k_nope + q_rope . k_rope`` scaled by
+``1 / sqrt(nope + rope)``.
+
+Execution here is the direct (non-absorbed) form on the existing 256-wide attention kernels: every head's query and key
+are laid out as ``[rope | nope | 0]`` (64 + 128 + 64 zeros = 256; the rotary part first, because the rope / page-write
+kernel rotates the leading dims) and its value as ``[v | 0]``; a consistent permutation plus zero padding leaves every dot
+product unchanged, and the first ``v_head_dim`` columns of the attention output are the result.  The paged cache therefore
+holds expanded per-head keys and values (FP8), not the latent: this runs the model family correctly on the GPU kernels
+that exist, at a cache cost of ``2 * 256`` bytes per head and token instead of ``kv_lora_rank + rope``.  The
+latent cache with weight-absorbed decode is the form to build next.  Reference: ``cpp_runtime/models/deepseek_v4`` /
+``glm_dsa`` graphs and ``mfq/kernels/cuda/deepseek_v4_attention.cu``.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import reference as ref
+from .llama import Fp8Linear, StepBuffers
+from .moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeFfn, MoeLayer, MoeWeights
+
+PADDED_HEAD = 256
+
+
+@dataclass
+class MlaConfig(MoeDecoderConfig):
+    q_lora_rank: int = 1536  # 0: queries are projected directly
+    kv_lora_rank: int = 512
+    qk_nope_head_dim: int = 128
+    qk_rope_head_dim: int = 64
+    v_head_dim: int = 128
+    name: str = "mla-moe-fp8"
+
+    def __post_init__(self):
+        if self.qk_nope_head_dim + self.qk_rope_head_dim > PADDED_HEAD or self.v_head_dim > PADDED_HEAD:
+            raise ValueError("head parts do not fit the 256-wide attention kernels")
+        # the cache and the attention kernels see plain multi-head attention with padded 256-wide heads
+        self.head_dim = PADDED_HEAD
+        self.num_kv_heads = self.num_heads
+
+    @classmethod
+    def tiny(cls) -> "MlaConfig":
+        return cls(vocab_size=1024, hidden_size=256, intermediate_size=512, num_layers=3, num_heads=2, num_kv_heads=2,
+                   head_dim=PADDED_HEAD, rope_theta=1e4, rms_eps=1e-6, num_experts=8, top_k=2, moe_intermediate=128,
+                   shared_intermediate=128, router="sigmoid", n_group=2, topk_group=1, routed_scale=2.5, first_dense_layers=1,
+                   q_lora_rank=128, kv_lora_rank=128, name="tiny-mla-moe-fp8")
+
+    @classmethod
+    def v3_style(cls, num_layers: int = 61) -> "MlaConfig":
+        """The DeepSeek-V3 geometry (671B with 61 layers); fewer layers give a model of the same widths that fits."""
+        return cls(vocab_size=129280, hidden_size=7168, intermediate_size=18432, num_layers=num_layers, num_heads=128,
+                   num_kv_heads=128, head_dim=PADDED_HEAD, rope_theta=1e4, rms_eps=1e-6, num_experts=256, top_k=8,
+                   moe_intermediate=2048, shared_intermediate=2048, router="sigmoid", n_group=8, topk_group=4,
+                   routed_scale=2.5, first_dense_layers=min(3, num_layers), name=f"v3-style-mla-moe-{num_layers}l")
+
+
+@dataclass
+class MlaWeights:
+    q_a: Fp8Linear | None  # [q_lora, H]
+    q_a_norm: torch.Tensor | None
+    q_b: Fp8Linear  # [Hq * (nope + rope), q_lora or H]
+    kv_a: Fp8Linear  # [kv_lora + rope, H]
+    kv_a_norm: torch.Tensor
+    kv_b: Fp8Linear  # [Hq * (nope + v), kv_lora]
+
+
+@dataclass
+class MlaLayer(MoeLayer):
+    mla: MlaWeights | None = None
+
+
+class MlaModel(MoeDecoderModel):
+    """:class:`MoeDecoderModel` whose attention blocks are latent attention wherever the layer carries ``mla`` weights."""
+
+    def __init__(self, cfg: MlaConfig, weights, collective=None) -> None:
+        super().__init__(cfg, weights, collective=collective)
+        if self.tp != 1:
+            raise NotImplementedError("latent attention is single-rank for now")
+        self.sm_scale = 1.0 / math.sqrt(cfg.qk_nope_head_dim + cfg.qk_rope_head_dim)
+        self.attn_rot = cfg.qk_rope_head_dim
+
+    def _mla_heads(self, h, layer):
+        """Per-head (query, key, value) in the padded 256-wide layout: ``[T, 3 * Hq, 256]`` bf16, rows q | k | v."""
+        cfg, m = self.cfg, layer.mla
+        nope, rope, vd, hq = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, self.hq
+        t = h.shape[0]
+        xq, xs = self._norm_quant(h, layer.attn_norm)
+        if m.q_a is not None:
+            q = m.q_b(*self._norm_quant(m.q_a(xq, xs), m.q_a_norm))
+        else:
+            q = m.q_b(xq, xs)
+        ckv = m.kv_a(xq, xs)  # [T, kv_lora + rope]
+        latent = ckv[:, : cfg.kv_lora_rank].contiguous()
+        kvb = m.kv_b(*self._norm_quant(latent, m.kv_a_norm)).view(t, hq, nope + vd)
+        q = q.view(t, hq, nope + rope)
+        out = torch.zeros((t, 3 * hq, PADDED_HEAD), dtype=torch.bfloat16, device=h.device)
+        out[:, :hq, :rope] = q[:, :, nope:]
+        out[:, :hq, rope : rope + nope] = q[:, :, :nope]
+        out[:, hq : 2 * hq, :rope] = ckv[:, None, cfg.kv_lora_rank :]  # one rotary key part shared by all heads
+        out[:, hq : 2 * hq, rope : rope + nope] = kvb[:, :, :nope]
+        out[:, 2 * hq :, :vd] = kvb[:, :, nope:]
+        return out
+
+    def _mla_attention(self, h, layer, kv, step: StepBuffers, prefill: bool):
+        """Attention output in the shape ``o_proj`` consumes: ``[T, Hq * v_head_dim]``."""
+        t = h.shape[0]
+        qkv = self._mla_heads(h, layer).view(t, 3 * self.hq * PADDED_HEAD)
+        o = self._attention(qkv, kv, step, prefill).view(t, self.hq, PADDED_HEAD)
+        return o[:, :, : self.cfg.v_head_dim].reshape(t, self.hq * self.cfg.v_head_dim)
+
+    def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
+        if getattr(layer, "mla", None) is None:
+            return super()._block(h, layer, kv, step, prefill)
+        attn = self._mla_attention(h, layer, kv, step, prefill)
+        h = self._row_parallel(layer.o_proj, *self._in_plain(attn, layer.o_proj), h=h)
+        return self._ffn(h, layer)
+
+
+def random_mla_weights(cfg: MlaConfig, device, seed: int = 0, std: float = 0.02, expert_chunk: int = 32) -> MoeWeights:
+    """N(0, std) weights in block FP8, drawn layer by layer on ``device`` (routed experts one chunk at a time)."""
+    from .hybrid import _quant_stack
+    dev = torch.device(device)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    h, hq = cfg.hidden_size, cfg.num_heads
+    nope, rope, vd = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+    e, mi, si = cfg.num_experts, cfg.moe_intermediate, cfg.shared_intermediate
+
+    def rnd(*shape, scale=std):
+        return torch.randn(shape, generator=gen, device=dev, dtype=torch.float32).mul_(scale).to(torch.bfloat16)
+
+    def ones(n):
+        return torch.ones(n, dtype=torch.bfloat16, device=dev)
+
+    def lin(n, k):
+        return Fp8Linear.from_float(rnd(n, k))
+
+    def experts(n, k):
+        qs, ss = zip(*[_quant_stack(rnd(min(expert_chunk, e - lo), n, k)) for lo in range(0, e, expert_chunk)])
+        return torch.cat(qs), torch.cat(ss)
+
+    layers = []
+    for i in range(cfg.num_layers):
+        q_in = cfg.q_lora_rank or h
+        mla = MlaWeights(lin(cfg.q_lora_rank, h) if cfg.q_lora_rank else None, ones(cfg.q_lora_rank) if cfg.q_lora_rank else None,
+                         lin(hq * (nope + rope), q_in), lin(cfg.kv_lora_rank + rope, h), ones(cfg.kv_lora_rank),
+                         lin(hq * (nope + vd), cfg.kv_lora_rank))
+        layer = MlaLayer(attn_norm=ones(h), qkv=None, o_proj=lin(h, hq * vd), mlp_norm=ones(h), gate_up=None, down=None, mla=mla)
+        if i < cfg.first_dense_layers:
+            layer.gate_up, layer.down = lin(2 * cfg.intermediate_size, h), lin(h, cfg.intermediate_size)
+        else:
+            gu_q, gu_s = experts(2 * mi, h)
+            dn_q, dn_s = experts(h, mi)
+            bias = torch.randn(e, generator=gen, device=dev, dtype=torch.float32) * 0.01 if cfg.router == "sigmoid" else None
+            layer.moe = MoeFfn(router=rnd(e, h), router_bias=bias, gate_up=gu_q, gate_up_scale=gu_s, down=dn_q, down_scale=dn_s)
+            if si:
+                layer.moe.shared_gate_up, layer.moe.shared_down = lin(2 * si, h), lin(h, si)
+        layers.append(layer)
+    return MoeWeights(rnd(cfg.vocab_size, h), layers, ones(h), lin(cfg.vocab_size, h), 0, 1)

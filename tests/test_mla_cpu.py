@@ -1,0 +1,72 @@
+"""Latent attention (DeepSeek-V3 style) on the CPU reference path: the padded-head execution equals the textbook
+formula, prefill and decode agree, chunked prefill agrees with a whole prefill."""
+
+import math
+
+import torch
+
+from mfq_b200.engine.llm_engine import LLMEngine
+from mfq_b200.models.llama import StepBuffers
+from mfq_b200.models.mla import MlaConfig, MlaModel, random_mla_weights
+from mfq_b200.ops import reference as ref
+
+
+def _model(seed=1):
+    cfg = MlaConfig.tiny()
+    return cfg, MlaModel(cfg, random_mla_weights(cfg, "cpu", seed=seed, std=0.05, expert_chunk=3))
+
+
+def test_config_presents_padded_multi_head_attention_to_the_cache():
+    cfg = MlaConfig.tiny()
+    assert cfg.head_dim == 256 and cfg.num_kv_heads == cfg.num_heads
+    big = MlaConfig.v3_style()
+    assert (big.q_lora_rank, big.kv_lora_rank, big.qk_nope_head_dim, big.qk_rope_head_dim, big.v_head_dim) == (1536, 512, 128, 64, 128)
+    assert big.num_experts == 256 and big.top_k == 8 and big.first_dense_layers == 3 and big.n_group == 8
+
+
+def test_padded_execution_equals_the_textbook_formula():
+    cfg, model = _model()
+    layer = model.w.layers[0]
+    m = layer.mla
+    t, hq = 11, cfg.num_heads
+    nope, rope, vd = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+    h = (torch.randn((t, cfg.hidden_size), generator=torch.Generator().manual_seed(0)) * 0.5).to(torch.bfloat16)
+    eng = LLMEngine(model, max_batch=1, max_seq_len=64, device="cpu")
+    eng.cache.assign(0, 5, t)
+    pos = torch.arange(t, dtype=torch.int32)
+    step = StepBuffers(input_ids=torch.zeros(t, dtype=torch.int32), positions=pos, slots=eng.cache.slots(5, 0, t), cu_seqlens=[0, t])
+    got = model._mla_attention(h, layer, eng.cache.layer(0), step, prefill=True).float()
+
+    # the same projections (same FP8 rounding points), then attention written out head by head
+    xq, xs = ref.rmsnorm_quant(h, layer.attn_norm, cfg.rms_eps)[:2]
+    cq = m.q_a(xq, xs)
+    q = m.q_b(*ref.rmsnorm_quant(cq, m.q_a_norm, cfg.rms_eps)[:2]).view(t, hq, nope + rope)
+    ckv = m.kv_a(xq, xs)
+    kvb = m.kv_b(*ref.rmsnorm_quant(ckv[:, : cfg.kv_lora_rank].contiguous(), m.kv_a_norm, cfg.rms_eps)[:2]).view(t, hq, nope + vd)
+    q_rope = ref.rope(q[:, :, nope:], pos, cfg.rope_theta).float()
+    k_rope = ref.rope(ckv[:, None, cfg.kv_lora_rank :], pos, cfg.rope_theta).float()  # [t, 1, rope]
+    # keys and values pass through the FP8 cache: quantize per (token, head) over the full padded vector, like the pages
+    k_full = torch.cat([k_rope.expand(t, hq, rope), kvb[:, :, :nope].float()], -1)
+    kq, ks = ref.quant_kv(torch.nn.functional.pad(k_full, (0, 256 - nope - rope)).to(torch.bfloat16))
+    vq, vs = ref.quant_kv(torch.nn.functional.pad(kvb[:, :, nope:].float(), (0, 256 - vd)).to(torch.bfloat16))
+    k_deq = (kq.float() * ks[..., None])[..., : nope + rope]
+    v_deq = (vq.float() * vs[..., None])[..., :vd]
+    q_full = torch.cat([q_rope, q[:, :, :nope].float()], -1)
+    scores = torch.einsum("thd,shd->hts", q_full, k_deq) / math.sqrt(nope + rope)
+    scores = scores.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1), float("-inf"))
+    want = torch.einsum("hts,shd->thd", torch.softmax(scores, -1), v_deq).reshape(t, hq * vd)
+    err = (got - want).abs().max() / want.abs().max()
+    assert float(err) < 2e-2, float(err)
+
+
+def test_prefill_decode_and_chunked_prefill_agree():
+    cfg, model = _model(seed=2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)) for n in (17, 29)]
+    whole = LLMEngine(model, max_batch=2, max_seq_len=96, device="cpu")
+    toks = whole.generate(prompts, 6).tokens
+    parts = LLMEngine(model, max_batch=2, max_seq_len=96, device="cpu", prefill_chunk=8)
+    assert torch.equal(parts.generate(prompts, 6).tokens, toks)
+    # a decode step continues the sequence like a longer prefill would: prefill(prompt + first tokens) picks the next one
+    longer = torch.cat([prompts[1], toks[1, :3].to(prompts[1].dtype)])
+    again = LLMEngine(model, max_batch=1, max_seq_len=96, device="cpu")
+    assert again.prefill(0, longer) == int(toks[1, 3])
