@@ -24,6 +24,12 @@ LAYER_SUFFIX = {
     "self_attn.k_proj.weight": "attention.key.weight",
     "self_attn.v_proj.weight": "attention.value.weight",
     "self_attn.o_proj.weight": "attention.output.weight",
+    "self_attn.q_a_proj.weight": "attention.query_a.weight",
+    "self_attn.q_a_layernorm.weight": "attention.query_a_norm.weight",
+    "self_attn.q_b_proj.weight": "attention.query_b.weight",
+    "self_attn.kv_a_proj_with_mqa.weight": "attention.key_value_a.weight",
+    "self_attn.kv_a_layernorm.weight": "attention.key_value_a_norm.weight",
+    "self_attn.kv_b_proj.weight": "attention.key_value_b.source.weight",
     "self_attn.q_norm.weight": "attention.query_norm.weight",
     "self_attn.k_norm.weight": "attention.key_norm.weight",
     "mlp.gate_proj.weight": "mlp.gate.weight",
@@ -99,6 +105,10 @@ def config_from_hf(hf: dict) -> dict:
         "rope_theta": float(hf.get("rope_theta", 1e4)), "rms_eps": float(hf.get("rms_norm_eps", 1e-5)),
         "name": hf.get("_name_or_path") or hf.get("model_type", "model"),
     }
+    if hf.get("kv_lora_rank"):  # latent attention (DeepSeek-V2/V3 style)
+        cfg.update(q_lora_rank=int(hf.get("q_lora_rank") or 0), kv_lora_rank=int(hf["kv_lora_rank"]),
+                   qk_nope_head_dim=int(hf.get("qk_nope_head_dim", 128)), qk_rope_head_dim=int(hf.get("qk_rope_head_dim", 64)),
+                   v_head_dim=int(hf.get("v_head_dim", 128)))
     experts = hf.get("num_experts") or hf.get("num_local_experts") or hf.get("n_routed_experts") or 0
     if experts:
         cfg.update(num_experts=experts, top_k=hf.get("num_experts_per_tok", 2),

@@ -133,10 +133,18 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
     with F.open_mfq(path) as store:
         assets = store.assets()
         raw = json.loads(assets["model_config.json"])
-        fields = {f for f in MoeDecoderConfig.__dataclass_fields__}
-        cfg = MoeDecoderConfig(**{k: v for k, v in raw.items() if k in fields})
-        weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size, expert_slots=expert_slots, native_4bit=native_4bit)
-    model = MoeDecoderModel(cfg, weights, collective=collective)
+        if raw.get("kv_lora_rank"):  # latent attention family
+            from .models.mla import MlaConfig, MlaModel, mla_weights_from_tensors
+            if tp_size != 1:
+                raise NotImplementedError("latent-attention checkpoints load on a single rank")
+            cfg = MlaConfig(**{k: v for k, v in raw.items() if k in MlaConfig.__dataclass_fields__})
+            weights = mla_weights_from_tensors(cfg, store, device)
+            model = MlaModel(cfg, weights)
+        else:
+            fields = {f for f in MoeDecoderConfig.__dataclass_fields__}
+            cfg = MoeDecoderConfig(**{k: v for k, v in raw.items() if k in fields})
+            weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size, expert_slots=expert_slots, native_4bit=native_4bit)
+            model = MoeDecoderModel(cfg, weights, collective=collective)
     # host-tier experts read the routing on the host every step, which a captured graph cannot do
     num_pages = None
     if kv_budget_bytes is None and str(device).startswith("cuda"):

@@ -33,6 +33,8 @@ def backbone_of(config: dict) -> str:
     """Backbone family of a config: hybrid (linear + full attention), mixture of experts, or dense decoder."""
     if config.get("full_attention_interval") or config.get("linear_v_heads"):
         return "hybrid_gdn_moe"
+    if config.get("kv_lora_rank"):
+        return "mla_moe"
     if config.get("num_experts"):
         return "moe_decoder"
     return "dense_decoder"

@@ -164,3 +164,83 @@ def random_mla_weights(cfg: MlaConfig, device, seed: int = 0, std: float = 0.02,
                 layer.moe.shared_gate_up, layer.moe.shared_down = lin(2 * si, h), lin(h, si)
         layers.append(layer)
     return MoeWeights(rnd(cfg.vocab_size, h), layers, ones(h), lin(cfg.vocab_size, h), 0, 1)
+
+
+def mla_weights_from_tensors(cfg: MlaConfig, tensors, device) -> MoeWeights:
+    """Weights from checkpoint tensors under canonical names: the generic loader builds embeddings, norms, feed-forward
+    blocks and ``o_proj`` (query / key / value of the plain attention do not exist in such a checkpoint and get zero
+    stand-ins that are dropped again); the latent-attention projections are read here.  HF's rotary layout of the
+    rope parts (interleaved pairs) is converted to the rotate-half layout this runtime uses."""
+    import numpy as np
+    from .moe_decoder import _to_float
+    dev = torch.device(device)
+    nope, rope, vd, hq = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.num_heads
+
+    class _View(dict):
+        def __missing__(self, name):
+            return tensors[name]
+
+        def __contains__(self, name):
+            return dict.__contains__(self, name) or name in tensors
+
+    view = _View()
+    for i in range(cfg.num_layers):
+        p = f"model.block.{i}.attention."
+        for n, rows in (("query", hq), ("key", hq), ("value", hq)):
+            view[p + n + ".weight"] = np.zeros((rows * 128, cfg.hidden_size), dtype=np.float32)
+    plain_cfg = MoeDecoderConfig(**{k: getattr(cfg, k) for k in MoeDecoderConfig.__dataclass_fields__})
+    plain_cfg.head_dim = 128  # only sizes the stand-ins; o_proj takes its true width (Hq * v) from the tensor itself
+    base = MoeWeights.from_tensors(plain_cfg, view, dev)
+
+    def get(name):
+        return _to_float(tensors[name], dev)
+
+    def deinterleave(w, heads, lead):
+        """Rows of every head: ``lead`` untouched rows, then ``rope`` rows stored as pairs (0,1),(2,3).. -> halves."""
+        w = w.reshape(heads, lead + rope, -1)
+        r = w[:, lead:]
+        r = torch.cat([r[:, 0::2], r[:, 1::2]], 1)
+        return torch.cat([w[:, :lead], r], 1).reshape(heads * (lead + rope), -1)
+
+    layers = []
+    for i, layer in enumerate(base.layers):
+        p = f"model.block.{i}.attention."
+        q_a = q_a_norm = None
+        if cfg.q_lora_rank:
+            q_a = Fp8Linear.from_float(get(p + "query_a.weight"))
+            q_a_norm = get(p + "query_a_norm.weight").to(torch.bfloat16)
+        kv_a = get(p + "key_value_a.weight")
+        kv_a = torch.cat([kv_a[: cfg.kv_lora_rank], deinterleave(kv_a[cfg.kv_lora_rank :], 1, 0)], 0)
+        mla = MlaWeights(q_a, q_a_norm, Fp8Linear.from_float(deinterleave(get(p + "query_b.weight"), hq, nope)),
+                         Fp8Linear.from_float(kv_a), get(p + "key_value_a_norm.weight").to(torch.bfloat16),
+                         Fp8Linear.from_float(get(p + "key_value_b.source.weight")))
+        ml = MlaLayer(**{k: getattr(layer, k) for k in layer.__dataclass_fields__}, mla=mla)
+        ml.qkv = None
+        layers.append(ml)
+    return MoeWeights(base.embed, layers, base.final_norm, base.lm_head, 0, 1)
+
+
+def init_mla_tensors(cfg: MlaConfig, seed: int = 0, std: float = 0.02) -> dict[str, torch.Tensor]:
+    """Random weights of an MLA model under canonical names (tests, synthetic checkpoints), in HF's rotary layout."""
+    from .moe_lm import MoeConfig, init_weights
+    w = init_weights(MoeConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, num_layers=cfg.num_layers,
+                               num_heads=cfg.num_heads, num_kv_heads=cfg.num_heads, head_dim=cfg.v_head_dim,
+                               num_experts=cfg.num_experts, top_k=cfg.top_k, moe_intermediate=cfg.moe_intermediate,
+                               shared_intermediate=cfg.shared_intermediate), seed=seed, std=std)
+    g = torch.Generator().manual_seed(seed + 17)
+    rnd = lambda *shape: (torch.randn(shape, generator=g) * std).to(torch.bfloat16).float()
+    h, hq = cfg.hidden_size, cfg.num_heads
+    nope, rope, vd = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+    for i in range(cfg.num_layers):
+        p = f"model.block.{i}.attention."
+        for n in ("query", "key", "value"):
+            w.pop(p + n + ".weight", None)
+        if cfg.q_lora_rank:
+            w[p + "query_a.weight"] = rnd(cfg.q_lora_rank, h)
+            w[p + "query_a_norm.weight"] = 1 + rnd(cfg.q_lora_rank)
+        w[p + "query_b.weight"] = rnd(hq * (nope + rope), cfg.q_lora_rank or h)
+        w[p + "key_value_a.weight"] = rnd(cfg.kv_lora_rank + rope, h)
+        w[p + "key_value_a_norm.weight"] = 1 + rnd(cfg.kv_lora_rank)
+        w[p + "key_value_b.source.weight"] = rnd(hq * (nope + vd), cfg.kv_lora_rank)
+        w[p + "output.weight"] = rnd(h, hq * vd)
+    return w

@@ -70,3 +70,45 @@ def test_prefill_decode_and_chunked_prefill_agree():
     longer = torch.cat([prompts[1], toks[1, :3].to(prompts[1].dtype)])
     again = LLMEngine(model, max_batch=1, max_seq_len=96, device="cpu")
     assert again.prefill(0, longer) == int(toks[1, 3])
+
+
+def test_rope_rows_are_deinterleaved_like_the_hf_layout():
+    """HF stores the rotary rows as interleaved pairs and rotates (x0, x1), (x2, x3), ...; this runtime rotates halves.
+    Re-ordering the rows (even ones first) makes both give the same attention scores."""
+    g = torch.Generator().manual_seed(0)
+    rope, t = 8, 5
+    wq, wk = torch.randn((rope, 16), generator=g), torch.randn((rope, 16), generator=g)
+    x = torch.randn((t, 16), generator=g)
+    pos = torch.arange(t, dtype=torch.int32)
+    inv = 10000.0 ** (-torch.arange(0, rope, 2).float() / rope)
+    ang = pos.float()[:, None] * inv[None]
+
+    def hf(v):  # rotate interleaved pairs
+        a, b = v[:, 0::2], v[:, 1::2]
+        return torch.stack([a * ang.cos() - b * ang.sin(), b * ang.cos() + a * ang.sin()], -1).reshape(t, rope)
+    want = hf(x @ wq.T) @ hf(x @ wk.T).T
+    de = lambda w: torch.cat([w[0::2], w[1::2]], 0)
+    ours = lambda w: ref.rope((x @ de(w).T)[:, None, :].to(torch.float32), pos, 10000.0).float()[:, 0]
+    got = ours(wq) @ ours(wk).T
+    assert float((got - want).abs().max()) <= 0.01 * float(want.abs().max())  # ref.rope rounds its output to bf16
+
+
+def test_checkpoint_round_trip_serves_the_same_model(tmp_path):
+    import dataclasses
+    import numpy as np
+    from mfq_b200 import formats as F
+    from mfq_b200.checkpoint import load_engine, quantize_tensors, save_checkpoint
+    from mfq_b200.models.mla import init_mla_tensors, mla_weights_from_tensors
+    cfg = dataclasses.replace(MlaConfig.tiny(), first_dense_layers=0, n_group=1, topk_group=1, router="softmax", routed_scale=1.0)
+    tensors = {k: v.numpy().astype(np.float32) for k, v in init_mla_tensors(cfg, seed=3, std=0.05).items()}
+    path = tmp_path / "mla.mfq"
+    save_checkpoint(path, dataclasses.asdict(cfg), quantize_tensors(tensors, dense="bf16"))
+    with F.open_mfq(path) as store:
+        assert "model.block.0.attention.key_value_b.source.weight" in list(store)
+        from mfq_b200.formats.model_graph import parse_graph
+        assert parse_graph(store.assets()["model_graph.json"]).backbone == "mla_moe"
+    eng, _tok, loaded_cfg = load_engine(path, "cpu", max_batch=1, max_seq_len=64)
+    assert type(eng.model).__name__ == "MlaModel" and loaded_cfg.kv_lora_rank == cfg.kv_lora_rank
+    direct = LLMEngine(MlaModel(cfg, mla_weights_from_tensors(cfg, tensors, "cpu")), max_batch=1, max_seq_len=64, device="cpu")
+    prompt = torch.randint(0, cfg.vocab_size, (15,), generator=torch.Generator().manual_seed(1))
+    assert torch.equal(eng.generate([prompt], 4).tokens, direct.generate([prompt], 4).tokens)
