@@ -36,11 +36,19 @@ class MlaConfig(MoeDecoderConfig):
     qk_nope_head_dim: int = 128
     qk_rope_head_dim: int = 64
     v_head_dim: int = 128
+    absorbed: bool = False  # latent cache + weight-absorbed attention (reference path on CPU tensors only)
     name: str = "mla-moe-fp8"
 
     def __post_init__(self):
         if self.qk_nope_head_dim + self.qk_rope_head_dim > PADDED_HEAD or self.v_head_dim > PADDED_HEAD:
             raise ValueError("head parts do not fit the 256-wide attention kernels")
+        if self.absorbed:
+            # the cache holds one shared row per token: [rotary key part | normalised latent]
+            if (self.kv_lora_rank + self.qk_rope_head_dim) % 64:
+                raise ValueError("latent + rotary width must be a multiple of 64 (cache chunking)")
+            self.head_dim = self.kv_lora_rank + self.qk_rope_head_dim
+            self.num_kv_heads = 1
+            return
         # the cache and the attention kernels see plain multi-head attention with padded 256-wide heads
         self.head_dim = PADDED_HEAD
         self.num_kv_heads = self.num_heads
@@ -85,6 +93,44 @@ class MlaModel(MoeDecoderModel):
             raise NotImplementedError("latent attention is single-rank for now")
         self.sm_scale = 1.0 / math.sqrt(cfg.qk_nope_head_dim + cfg.qk_rope_head_dim)
         self.attn_rot = cfg.qk_rope_head_dim
+        if cfg.absorbed:
+            self.hk = 1  # all query heads attend to the one latent row per token
+            self._absorb: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+    def _absorbed_weights(self, layer):
+        """kv_b split per head into the key part ``[Hq, nope, latent]`` and the value part ``[Hq, v, latent]``."""
+        key = id(layer)
+        if key not in self._absorb:
+            cfg = self.cfg
+            wkv = layer.mla.kv_b.dequant().float().view(self.hq, cfg.qk_nope_head_dim + cfg.v_head_dim, cfg.kv_lora_rank)
+            self._absorb[key] = (wkv[:, : cfg.qk_nope_head_dim].contiguous(), wkv[:, cfg.qk_nope_head_dim :].contiguous())
+        return self._absorb[key]
+
+    def _mla_absorbed(self, h, layer, kv, step: StepBuffers, prefill: bool):
+        """Weight-absorbed form: ``q_nope . (W_k c) = (W_k^T q_nope) . c`` and ``sum_s p_s W_v c_s = W_v sum_s p_s c_s``,
+        so keys and values never exist per head: the cache keeps ``[k_rope | c]`` once per token (``kv_lora + rope``
+        values instead of ``2 * Hq * 256``), queries are mapped into the latent space, attention runs as Hq query heads
+        over one shared key/value row, and the latent output is expanded by ``W_v`` afterwards."""
+        if h.is_cuda:
+            raise NotImplementedError("the latent-cache path has no GPU kernel yet (576-wide shared-row attention)")
+        cfg, m = self.cfg, layer.mla
+        nope, rope, vd, hq, lat = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, self.hq, cfg.kv_lora_rank
+        t = h.shape[0]
+        xq, xs = self._norm_quant(h, layer.attn_norm)
+        q = (m.q_b(*self._norm_quant(m.q_a(xq, xs), m.q_a_norm)) if m.q_a is not None else m.q_b(xq, xs)).view(t, hq, nope + rope)
+        ckv = m.kv_a(xq, xs)
+        c_n = ref.rmsnorm(ckv[:, :lat].contiguous(), m.kv_a_norm, cfg.rms_eps)  # bf16 [T, latent]
+        wk, wv = self._absorbed_weights(layer)
+        q_abs = torch.einsum("thn,hnl->thl", q[:, :, :nope].float(), wk).to(torch.bfloat16)
+        d = rope + lat
+        qkv = torch.zeros((t, hq + 2, d), dtype=torch.bfloat16)
+        qkv[:, :hq, :rope] = q[:, :, nope:]
+        qkv[:, :hq, rope:] = q_abs
+        qkv[:, hq, :rope] = ckv[:, lat:]
+        qkv[:, hq, rope:] = c_n
+        qkv[:, hq + 1, :lat] = c_n  # value row = the latent (the cache class keeps keys and values the same width)
+        o_lat = self._attention(qkv.view(t, (hq + 2) * d), kv, step, prefill).view(t, hq, d)[:, :, :lat]
+        return torch.einsum("thl,hvl->thv", o_lat.float(), wv).to(torch.bfloat16).reshape(t, hq * vd)
 
     def _mla_heads(self, h, layer):
         """Per-head (query, key, value) in the padded 256-wide layout: ``[T, 3 * Hq, 256]`` bf16, rows q | k | v."""
@@ -118,7 +164,7 @@ class MlaModel(MoeDecoderModel):
     def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
         if getattr(layer, "mla", None) is None:
             return super()._block(h, layer, kv, step, prefill)
-        attn = self._mla_attention(h, layer, kv, step, prefill)
+        attn = (self._mla_absorbed if self.cfg.absorbed else self._mla_attention)(h, layer, kv, step, prefill)
         h = self._row_parallel(layer.o_proj, *self._in_plain(attn, layer.o_proj), h=h)
         return self._ffn(h, layer)
 

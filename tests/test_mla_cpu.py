@@ -112,3 +112,39 @@ def test_checkpoint_round_trip_serves_the_same_model(tmp_path):
     direct = LLMEngine(MlaModel(cfg, mla_weights_from_tensors(cfg, tensors, "cpu")), max_batch=1, max_seq_len=64, device="cpu")
     prompt = torch.randint(0, cfg.vocab_size, (15,), generator=torch.Generator().manual_seed(1))
     assert torch.equal(eng.generate([prompt], 4).tokens, direct.generate([prompt], 4).tokens)
+
+
+def test_absorbed_latent_cache_path_matches_the_direct_path():
+    """Same weights, two executions: expanded per-head K/V in the cache vs one latent row per token with the kv_b
+    matrices absorbed into the query and the output.  Rounding points differ (FP8 cache rows, bf16 latent), the
+    function does not.  At the V3 geometry the latent rows are 57x smaller than the expanded heads (114x once a
+    dedicated cache stops storing the latent twice, as key and as value)."""
+    import dataclasses
+    cfg = dataclasses.replace(MlaConfig.tiny(), first_dense_layers=3)  # dense: no routing flips in the comparison
+    w = random_mla_weights(cfg, "cpu", seed=6, std=0.05, expert_chunk=3)
+    cfg_abs = dataclasses.replace(cfg, absorbed=True)
+    assert (cfg_abs.head_dim, cfg_abs.num_kv_heads) == (cfg.kv_lora_rank + cfg.qk_rope_head_dim, 1)
+    direct = LLMEngine(MlaModel(cfg, w), max_batch=1, max_seq_len=96, device="cpu")
+    latent = LLMEngine(MlaModel(cfg_abs, w), max_batch=1, max_seq_len=96, device="cpu")
+    per_token = lambda e: e.cache.kv_heads * 2 * e.cache.head_dim
+    assert per_token(direct) == 2 * 2 * 256 and per_token(latent) == 2 * 192
+    prompt = torch.randint(0, cfg.vocab_size, (31,), generator=torch.Generator().manual_seed(4))
+
+    def logits(eng):
+        n = prompt.numel()
+        eng.cache.assign(0, 9, n)
+        step = StepBuffers(input_ids=prompt.to(torch.int32), positions=torch.arange(n, dtype=torch.int32),
+                           slots=eng.cache.slots(9, 0, n), cu_seqlens=[0, n])
+        out = eng.model.forward(step, eng.cache, prefill=True).float()
+        eng.cache.release(9)
+        return out
+    a, b = logits(direct), logits(latent)
+    cos = float(torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0))
+    # measured 0.9943: the FP8 rounding level of a three-layer model (GPU vs CPU of the direct path: 0.9954)
+    assert cos > 0.99 and float((a - b).abs().mean()) <= 0.03 * float(a.abs().max()), cos
+    # decode over the latent cache continues its own prefill consistently
+    toks = latent.generate([prompt], 5).tokens[0]
+    again = LLMEngine(MlaModel(cfg_abs, w), max_batch=1, max_seq_len=96, device="cpu")
+    assert again.prefill(0, torch.cat([prompt, toks[:2].to(prompt.dtype)])) == int(toks[2])
+    v3 = MlaConfig.v3_style()
+    assert (2 * 256 * v3.num_heads) / (2 * (v3.kv_lora_rank + v3.qk_rope_head_dim)) > 50
