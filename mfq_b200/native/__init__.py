@@ -144,6 +144,25 @@ class NintRows:
         return q.value, k.value
 
 
+def nvq_decode(t, threads: int = 8) -> np.ndarray:
+    """Rows of a plain (non-JSC) :class:`~mfq_b200.formats.nvq.NvqTensor` as float32 ``[out, neuron_len]``."""
+    from ..formats.nvq import codebook as lattice
+    table = np.ascontiguousarray(lattice(t.spec) if t.codebook is None else t.codebook, dtype=np.float32)
+    rows, n = int(t.neuron_scale.size), int(t.neuron_len)
+    idx = np.ascontiguousarray(t.indices, dtype=np.uint16)
+    sg, sub = np.ascontiguousarray(t.signs, dtype=np.uint8), np.ascontiguousarray(t.sub_scale, dtype=np.uint8)
+    anchors = np.ascontiguousarray(t.neuron_scale, dtype=np.float32)
+    out = np.empty((rows, n), dtype=np.float32)
+    fn = lib().mfq_nvq_decode
+    fn.argtypes = [C.c_void_p] * 5 + [C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+    fn.restype = C.c_int
+    rc = fn(_np_ptr(idx), _np_ptr(sg), _np_ptr(sub), _np_ptr(anchors), _np_ptr(table), rows, n, t.spec.groupsize,
+            t.spec.vector_size, table.shape[0], int(t.spec.sign_mode == "index_parity"), _np_ptr(out), threads)
+    if rc != 0:
+        raise ValueError(_err())
+    return out
+
+
 def mxfp4_decode(codes: np.ndarray, scales: np.ndarray, rows: int, cols: int, threads: int = 8) -> np.ndarray:
     out = np.empty((rows, cols), dtype=np.float32)
     codes, scales = np.ascontiguousarray(codes, np.uint8), np.ascontiguousarray(scales, np.uint8)

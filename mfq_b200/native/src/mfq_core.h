@@ -45,6 +45,9 @@ int mfq_nint_row_bits(void* h, int64_t row, int* q_bits, int* k_bits);
 int mfq_nint_gemv(void* h, int64_t row_begin, int64_t row_end, const float* x, float* y, int threads);
 int mfq_mxfp4_decode(const uint8_t* codes, const uint8_t* scales_e8m0, int64_t rows, int64_t cols, float* out, int threads);
 int mfq_fp8_block_decode(const uint8_t* codes, const float* scales, int64_t rows, int64_t cols, int block, float* out, int threads);
+// NVQ rows from the unpacked index / sign / sub-scale streams (see packed_rows.cpp); out [rows, n]
+int mfq_nvq_decode(const uint16_t* indices, const uint8_t* signs, const uint8_t* sub, const float* anchors, const float* table,
+                   int64_t rows, int64_t n, int gs, int vec, int entries, int index_parity, float* out, int threads);
 void mfq_f32_to_bf16(const float* in, uint16_t* out, int64_t n);
 
 // ---- prefix cache -------------------------------------------------------------------------------------------

@@ -235,6 +235,42 @@ int mfq_mxfp4_decode(const uint8_t* codes, const uint8_t* scales, int64_t rows, 
   return 0;
 }
 
+// NVQ rows from their unpacked streams: w = anchor[row] * sub[row, group] * table[index][i] * sign.
+//   indices [rows, nvec] (u16), signs [rows, ceil(n/8)]: 7 stored sign bits per 8 weights, the eighth is their parity
+//   (XOR bit 7 of the index when index_parity != 0, which needs vec == 8), sub [rows, ceil(n/gs)] (u8),
+//   anchors [rows] f32, table [entries, vec] f32 magnitudes.
+int mfq_nvq_decode(const uint16_t* indices, const uint8_t* signs, const uint8_t* sub, const float* anchors, const float* table,
+                   int64_t rows, int64_t n, int gs, int vec, int entries, int index_parity, float* out, int threads) {
+  if (rows <= 0 || n <= 0 || gs <= 0 || (vec != 4 && vec != 8) || entries <= 0) return fail(-1, "bad NVQ geometry");
+  if (index_parity && vec != 8) return fail(-1, "index-parity signs need 8-wide vectors");
+  const int64_t nvec = (n + vec - 1) / vec, nsign = (n + 7) / 8, ng = (n + gs - 1) / gs;
+  int bad = 0;
+  mfqn::parallel_for(rows, threads, [&](int64_t b, int64_t e) {
+    for (int64_t r = b; r < e; ++r) {
+      const uint16_t* ir = indices + r * nvec;
+      const uint8_t* sr = signs + r * nsign;
+      const uint8_t* gr = sub + r * ng;
+      float* dst = out + r * n;
+      for (int64_t i = 0; i < n; ++i) {
+        const uint16_t idx = ir[i / vec];
+        if (idx >= entries) { bad = 1; dst[i] = 0.f; continue; }
+        const uint8_t m = sr[i / 8];
+        const int bit = int(i % 8);
+        int neg;
+        if (bit < 7) {
+          neg = (m >> bit) & 1;
+        } else {
+          neg = __builtin_popcount(m & 0x7F) & 1;
+          if (index_parity) neg ^= (ir[i / 8] >> 7) & 1;
+        }
+        const float v = table[int64_t(idx) * vec + i % vec] * anchors[r] * float(gr[i / gs]);
+        dst[i] = neg ? -v : v;
+      }
+    }
+  });
+  return bad ? fail(-2, "NVQ index outside the codebook") : 0;
+}
+
 static float e4m3_to_float(uint8_t c) {
   const int sign = c >> 7, exp = (c >> 3) & 0xF, man = c & 7;
   float v;

@@ -147,3 +147,22 @@ def test_planners():
     book.pin(12)
     with pytest.raises(MemoryError):
         book.acquire(13)
+
+
+def test_native_nvq_rows_match_the_python_decoder():
+    import numpy as np
+    from mfq_b200 import formats as F
+    from mfq_b200 import native
+    from mfq_b200.formats.nvq import dequantize_nvq_rows
+    from mfq_b200.quantize.nvq import quantize_nvq
+    rng = np.random.default_rng(0)
+    for cb, cols in (("e8_1024", 200), ("d4_512", 96), ("e8_256", 72)):
+        w = rng.standard_normal((12, cols)).astype(np.float32)
+        t = quantize_nvq(w, F.NvqSpec(cb))
+        got = native.nvq_decode(t, threads=3)
+        assert got.shape == (12, cols) and np.array_equal(got, dequantize_nvq_rows(t).astype(np.float32))
+    t.indices = t.indices.astype(np.uint16)
+    t.indices[0, 0] = 60000
+    import pytest
+    with pytest.raises(ValueError):
+        native.nvq_decode(t)
