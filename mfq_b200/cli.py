@@ -319,7 +319,12 @@ def _cmd_serve(args) -> int:
     if args.cluster_peer:
         from .server.cluster import ClusterBackend
         cluster = ClusterBackend(args.cluster_peer)
-    uvicorn.run(create_app(service, api_key=key, cluster=cluster), host=args.host, port=args.port, access_log=args.access_log)
+    app = create_app(service, api_key=key, cluster=cluster)
+    if args.anthropic_port and args.anthropic_port != args.port:
+        from .server.listen import Listeners
+        Listeners(app, args.host, [args.port, args.anthropic_port], access_log=args.access_log).start().wait()
+    else:
+        uvicorn.run(app, host=args.host, port=args.port, access_log=args.access_log)
     return 0
 
 
@@ -428,6 +433,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--anthropic-port", type=int, default=0,
+                   help="second listener for Anthropic-style clients (the reference uses 8091); 0: one port serves both")
     s.add_argument("--api-keys-file", default=None,
                    help="JSON store of API keys with scopes (inference / read / admin); keys are kept as SHA-256 digests")
     s.add_argument("--kv-budget-gb", type=float, default=0.0,
