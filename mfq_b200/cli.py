@@ -328,6 +328,28 @@ def _cmd_serve(args) -> int:
     return 0
 
 
+def _cmd_runtime(args) -> int:
+    """One model behind the newline-delimited JSON protocol on stdin / stdout (what a benchmark harness or a parent
+    process drives; reference: the ``mfq-runtime --transport stdio`` executable, cpp_runtime/main.cpp)."""
+    import torch
+    from .checkpoint import load_engine
+    from .server import ModelService
+    from .server.stdio import StdioTransport
+    device = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    out = sys.stdout
+    sys.stdout = sys.stderr  # anything printed while serving must not corrupt the frame stream
+    service = ModelService(max_queue=args.max_queue, queue_timeout=args.queue_timeout)
+    engine, tok, _cfg = load_engine(args.model, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size,
+                                    native_4bit=args.native_4bit)
+    service.add_model(args.model_name or Path(args.model).stem, engine, tok)
+    try:
+        StdioTransport(service, sys.stdin, out).serve()
+    finally:
+        service.shutdown()
+        sys.stdout = out
+    return 0
+
+
 def _cmd_bench(args) -> int:
     os.execv(sys.executable, [sys.executable, str(Path(__file__).resolve().parents[1] / "bench.py"), *args.rest])
 
@@ -447,6 +469,17 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--prefix-cache-ram-gb", type=float, default=4.0)
     s.add_argument("--prefix-cache-disk-gb", type=float, default=64.0)
     s.set_defaults(fn=_cmd_serve)
+    rt = sub.add_parser("runtime", help="serve one model over newline-delimited JSON frames on stdin / stdout")
+    rt.add_argument("--model", required=True)
+    rt.add_argument("--model-name")
+    rt.add_argument("--transport", choices=["stdio"], default="stdio")
+    rt.add_argument("--continuous-batching", type=int, default=32)
+    rt.add_argument("--ctx-size", type=int, default=8192)
+    rt.add_argument("--max-queue", type=int, default=256)
+    rt.add_argument("--queue-timeout", type=float, default=30.0)
+    rt.add_argument("--native-4bit", action="store_true")
+    rt.add_argument("--device")
+    rt.set_defaults(fn=_cmd_runtime)
     be = sub.add_parser("bench", help="run the flagship benchmark (arguments are passed through to bench.py)")
     be.add_argument("rest", nargs=argparse.REMAINDER)
     be.set_defaults(fn=_cmd_bench)
