@@ -350,6 +350,20 @@ def _cmd_runtime(args) -> int:
     return 0
 
 
+def _cmd_profile(args) -> int:
+    """Per-op time split of one prefill and a few eager decode steps (named scopes, CUDA events on a GPU)."""
+    import torch
+    from .checkpoint import load_engine
+    from .utils.profiler import PROFILER, profile_engine
+    device = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    engine, _tok, cfg = load_engine(args.model, device, max_batch=1, max_seq_len=args.prompt_tokens + args.decode_tokens + 8)
+    vocab = int(cfg.vocab_size)
+    ids = torch.tensor([3 + (i * 7919) % (vocab - 8) for i in range(args.prompt_tokens)], dtype=torch.int32)
+    profile_engine(engine, ids, args.decode_tokens, args.filter)
+    PROFILER.report(sys.stdout)
+    return 0
+
+
 def _cmd_bench(args) -> int:
     os.execv(sys.executable, [sys.executable, str(Path(__file__).resolve().parents[1] / "bench.py"), *args.rest])
 
@@ -469,6 +483,13 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--prefix-cache-ram-gb", type=float, default=4.0)
     s.add_argument("--prefix-cache-disk-gb", type=float, default=64.0)
     s.set_defaults(fn=_cmd_serve)
+    pf = sub.add_parser("profile", help="per-op time split of a prefill and a few eager decode steps")
+    pf.add_argument("--model", required=True)
+    pf.add_argument("--prompt-tokens", type=int, default=128)
+    pf.add_argument("--decode-tokens", type=int, default=8)
+    pf.add_argument("--filter", default="", help="comma separated name pieces to keep (e.g. attn,ffn.down)")
+    pf.add_argument("--device")
+    pf.set_defaults(fn=_cmd_profile)
     rt = sub.add_parser("runtime", help="serve one model over newline-delimited JSON frames on stdin / stdout")
     rt.add_argument("--model", required=True)
     rt.add_argument("--model-name")

@@ -20,9 +20,11 @@ import torch
 
 from .. import ops
 from ..models.llama import LlamaModel, StepBuffers
+from ..utils.profiler import scope
 from .kv_cache import PAGE_SIZE, PagedKVCache
 
 BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+_PROFILE_DECODE = __import__("os").environ.get("MFQ_PROFILE_DECODE", "0") == "1"  # one stderr line per decode call
 
 
 def bucket_for(n: int) -> int:
@@ -301,6 +303,10 @@ class LLMEngine:
             self.prefix_stats["blocks_stored"] += 1
 
     def _prefill_span(self, row: int, seq_id: int, ids: torch.Tensor, start: int, end: int, state_slots):
+        with scope("prefill.span", self.device):
+            return self._prefill_span_body(row, seq_id, ids, start, end, state_slots)
+
+    def _prefill_span_body(self, row: int, seq_id: int, ids: torch.Tensor, start: int, end: int, state_slots):
         """Run tokens ``[start, end)`` of the row's sequence (``ids`` holds the whole prompt, on the device) through
         the model in chunks of at most ``prefill_chunk``; tokens before ``start`` must already be in the KV pages.
         Returns (logits of the last token, hidden states of the span if an MTP head needs them)."""
@@ -496,6 +502,18 @@ class LLMEngine:
     def decode(self, rows: list[int]) -> dict:
         """Scheduler entry: advance each of ``rows`` (other rows are masked off).  Returns ``{row: token}``, or
         ``{row: [tokens]}`` when the rows decode through MTP cycles."""
+        if _PROFILE_DECODE:
+            import sys
+            import time
+            t0 = time.perf_counter()
+            out = self._decode_rows(rows)
+            print(f"decode_profile rows={len(rows)} tokens={sum(len(v) if isinstance(v, list) else 1 for v in out.values())} "
+                  f"wall_ms={(time.perf_counter() - t0) * 1e3:.3f}", file=sys.stderr)
+            return out
+        with scope("decode.step", self.device):
+            return self._decode_rows(rows)
+
+    def _decode_rows(self, rows: list[int]) -> dict:
         b = bucket_for(max(rows) + 1)
         b = min(b, self.max_batch)
         mask = torch.zeros(self.max_batch, dtype=torch.int32)

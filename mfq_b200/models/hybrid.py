@@ -26,6 +26,7 @@ import torch
 from .. import ops
 from ..ops import gdn
 from ..ops import reference as ref
+from ..utils.profiler import scope
 from .llama import Fp8Linear, LlamaLayer, StepBuffers
 from .moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeFfn, MoeLayer, MoeWeights, _to_float
 
@@ -447,9 +448,11 @@ class HybridModel(MoeDecoderModel):
     def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
         li = self._layer_index.get(id(layer))  # None: a block outside the stack (the MTP head's attention block)
         if getattr(layer, "gdn", None) is not None:
-            h = self._gdn_mixer(h, layer, li, step)
+            with scope("mixer.gdn", h.device):
+                h = self._gdn_mixer(h, layer, li, step)
         elif isinstance(layer, HybridLayer):
-            h = self._gated_attention(h, layer, kv, step, prefill)
+            with scope("mixer.gated_attn", h.device):
+                h = self._gated_attention(h, layer, kv, step, prefill)
         else:
             return super()._block(h, layer, kv, step, prefill)
         return self._ffn(h, layer)

@@ -23,6 +23,7 @@ import torch
 from .. import ops
 from ..ops import reference as ref
 from ..quantize.fp8_block import quantize_fp8_block_torch
+from ..utils.profiler import scope
 
 FP8 = torch.float8_e4m3fn
 
@@ -342,24 +343,30 @@ class LlamaModel:
     # -- feed-forward -------------------------------------------------------------------------------------------
     def _ffn(self, h, layer):
         """Dense SwiGLU block: ``h + down(silu(gate(x)) * up(x))`` with ``x = rmsnorm(h)``."""
-        gu = layer.gate_up(*self._in_norm(h, layer.mlp_norm, layer.gate_up))
-        return self._row_parallel(layer.down, *self._in_silu(gu, layer.down), h=h)
+        with scope("ffn.gate_up", h.device):
+            gu = layer.gate_up(*self._in_norm(h, layer.mlp_norm, layer.gate_up))
+        with scope("ffn.down", h.device):
+            return self._row_parallel(layer.down, *self._in_silu(gu, layer.down), h=h)
 
     # -- forward ------------------------------------------------------------------------------------------------
     def _embed(self, ids):
         return ops.embed(ids, self.w.embed) if self.w.embed.is_cuda else self.w.embed[ids.long()].clone()
 
     def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
-        qkv = layer.qkv(*self._in_norm(h, layer.attn_norm, layer.qkv))
-        attn = self._attention(qkv, kv, step, prefill)
-        h = self._row_parallel(layer.o_proj, *self._in_plain(attn, layer.o_proj), h=h)
+        with scope("attn.qkv", h.device):
+            qkv = layer.qkv(*self._in_norm(h, layer.attn_norm, layer.qkv))
+        with scope("attn.core", h.device):
+            attn = self._attention(qkv, kv, step, prefill)
+        with scope("attn.o_proj", h.device):
+            h = self._row_parallel(layer.o_proj, *self._in_plain(attn, layer.o_proj), h=h)
         return self._ffn(h, layer)
 
     def _head(self, h, norm, gather_logits: bool):
-        xq, xs = self._norm_quant(h, norm)
-        logits = self.w.lm_head(xq, xs)
-        if self.tp > 1 and gather_logits:
-            logits = self.collective.gather_columns(logits)
+        with scope("head", h.device):
+            xq, xs = self._norm_quant(h, norm)
+            logits = self.w.lm_head(xq, xs)
+            if self.tp > 1 and gather_logits:
+                logits = self.collective.gather_columns(logits)
         return logits
 
     def forward(self, step: StepBuffers, cache, *, prefill: bool, logits_rows: torch.Tensor | None = None,

@@ -24,6 +24,7 @@ from .. import ops
 from ..ops import moe as moe_ops
 from ..ops import reference as ref
 from ..quantize.fp8_block import quantize_fp8_block_torch
+from ..utils.profiler import scope
 from .llama import kv_head_rows, Fp8Linear, LlamaConfig, LlamaLayer, LlamaModel, LlamaWeights
 
 
@@ -192,6 +193,10 @@ class MoeDecoderModel(LlamaModel):
         ffn = getattr(layer, "moe", None)
         if ffn is None:
             return super()._ffn(h, layer)
+        with scope("ffn.moe", h.device):
+            return self._ffn_moe(h, layer, ffn)
+
+    def _ffn_moe(self, h, layer, ffn: MoeFfn):
         cfg = self.cfg
         if not h.is_cuda:
             return self._ffn_reference(h, layer, ffn)
