@@ -59,12 +59,16 @@ def read_hf_directory(path) -> tuple[dict, dict[str, np.ndarray], dict[str, byte
 
 def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", expert_mix: str = "", seed: int = 20260908,
                      device: str = "cpu", progress=None, widths: dict[str, int | None] | None = None,
-                     imatrix: dict[str, np.ndarray] | None = None, scheme: dict | None = None) -> dict[str, object]:
+                     imatrix: dict[str, np.ndarray] | None = None, scheme: dict | None = None, resume=None) -> dict[str, object]:
     """Apply the quantization plan: routed experts by the seeded mix (or the dense rule), 2-D weights by ``dense``
     (nint2..8 / nvq3 / mxfp4 / fp8 / bf16), norms / router / embeddings-as-requested stay bf16.
     ``widths`` (a preset plan: tensor -> NINT width, None = keep) overrides ``dense`` per tensor; ``imatrix`` supplies
     per-input-channel importance to the NINT search; ``scheme`` (``mfq.calibration-scheme.v3``, expert-wise) fixes the
-    family of every routed expert projection."""
+    family of every routed expert projection.  ``resume`` (a :class:`~mfq_b200.quantize.resume.ResumeStore`) parks
+    every finished tensor and hands back the ones a previous, interrupted run finished for the same source and plan."""
+    if resume is not None:
+        return _quantize_resumable(tensors, resume, dense=dense, expert_mix=expert_mix, seed=seed, device=device,
+                                   progress=progress, widths=widths, imatrix=imatrix, scheme=scheme)
     from .quantize import balanced_expert_mix, parse_profiles, quantize_expertwise, quantize_matrix
     profiles = parse_profiles(expert_mix) if expert_mix else ()
     dense_profile = None if dense == "bf16" else parse_profiles({"fp8": "FP8", "mxfp4": "MXFP4", "nvq3": "NVQ3"}.get(dense, dense.upper()))[0]
@@ -101,6 +105,28 @@ def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", ex
                 from .calibration.imatrix import input_importance
                 imp = input_importance(imatrix, name)
             out[name] = quantize_matrix(a, profile, device=device, importance=imp) if imp is not None else quantize_matrix(a, profile, device=device)
+    return out
+
+
+def _quantize_resumable(tensors, store, *, dense, expert_mix, seed, device, progress, widths, imatrix, scheme):
+    """One tensor at a time through :func:`quantize_tensors`, with the resume store in front of it."""
+    import hashlib
+    out: dict[str, object] = {}
+    for name, t in tensors.items():
+        a = np.asarray(t, dtype=np.float32)
+        label = {"dense": dense, "mix": expert_mix, "seed": seed, "width": (widths or {}).get(name, "-") if widths is not None else "-",
+                 "scheme": [x for x in (scheme or {}).get("assignments", []) if x["tensor"] == name]}
+        if imatrix is not None:
+            from .calibration.imatrix import input_importance
+            imp = input_importance(imatrix, name)
+            label["imatrix"] = None if imp is None else hashlib.sha256(np.ascontiguousarray(imp, dtype=np.float32).data).hexdigest()
+        key = store.key(name, a, json.dumps(label, sort_keys=True))
+        got = store.get(name, key)
+        if got is None:
+            got = quantize_tensors({name: a}, dense=dense, expert_mix=expert_mix, seed=seed, device=device, progress=progress,
+                                   widths=widths, imatrix=imatrix, scheme=scheme)[name]
+            store.put(name, key, got)
+        out[name] = got
     return out
 
 

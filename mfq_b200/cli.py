@@ -66,7 +66,15 @@ def _cmd_quantize(args) -> int:
     from . import formats as F
     from .checkpoint import quantize_tensors, save_checkpoint
     out = Path(args.output)
-    if out.exists() and not args.overwrite and not args.dry_run:
+    if out.exists() and args.resume_completed and not args.dry_run:
+        try:  # a finished output from an earlier run: nothing to do
+            with F.open_mfq(out) as done:
+                n = sum(1 for k in done if not k.startswith("__mfq_asset__/"))
+            print(json.dumps({"output": str(out), "already_complete": True, "tensors": n}))
+            return 0
+        except Exception:
+            pass  # unreadable (cut short): quantize again over it
+    elif out.exists() and not args.overwrite and not args.dry_run:
         raise SystemExit(f"{out} exists (use --overwrite)")
     cfg, tensors, assets = _load_source(args)
     dense = "bf16" if args.full_precision else (args.format or f"nint{args.bits}")
@@ -98,16 +106,23 @@ def _cmd_quantize(args) -> int:
         bits = int(dense[4:])
         gs, k = expertwise._NINT_PRESETS[bits]
         expertwise._NINT_PRESETS[bits] = (args.groupsize or gs, args.sub_bits or k)
+    store = None
+    if not args.no_temp:
+        from .quantize.resume import ResumeStore
+        store = ResumeStore(str(out) + ".tmp", resume=args.resume, keep=args.keep_temp)
     q = quantize_tensors(tensors, dense=dense, expert_mix=args.random_expert_mix, seed=args.random_expert_mix_seed,
-                         widths=widths, imatrix=imatrix, scheme=scheme, device=args.device, progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
+                         widths=widths, imatrix=imatrix, scheme=scheme, device=args.device, resume=store,
+                         progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
     extra = {"quantization": {"dense": dense, "preset": args.preset or None, "imatrix": bool(imatrix), "ew_scheme": bool(scheme), "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
                               "random_expert_mix_seed": args.random_expert_mix_seed if args.random_expert_mix else None}}
     paths = save_checkpoint(out, cfg, q, assets, extra=extra,
                             shard_bytes=int(args.shard_size_gb * (1 << 30)) if args.shard_size_gb else None)
     size = sum(Path(p).stat().st_size for p in paths)
     weights = sum(int(t.size) for t in tensors.values())
+    if store is not None:
+        store.finish()
     print(json.dumps({"output": str(paths[0]), "shards": len(paths), "bytes": size, "weights": weights,
-                      "bits_per_weight": round(8 * size / weights, 3)}))
+                      "bits_per_weight": round(8 * size / weights, 3), "resumed_tensors": len(store.reused) if store else 0}))
     return 0
 
 
@@ -392,6 +407,10 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--device", default="cpu")
     q.add_argument("--seed", type=int, default=0)
     q.add_argument("--dry-run", action="store_true")
+    q.add_argument("--resume", action="store_true", help="reuse the validated per-tensor blobs an interrupted run left in <output>.tmp/")
+    q.add_argument("--resume-completed", action="store_true", help="exit at once when the output already exists and opens")
+    q.add_argument("--keep-temp", action="store_true", help="keep <output>.tmp/ after a successful run")
+    q.add_argument("--no-temp", action="store_true", help="do not park finished tensors on disk while quantizing")
     q.add_argument("--overwrite", action="store_true")
     q.add_argument("--verbose", action="store_true")
     q.add_argument("--shard-size-gb", type=float, default=0.0, help="write name-0000i-of-0000N.mfq shards of at most this size")
