@@ -105,6 +105,11 @@ def config_from_hf(hf: dict) -> dict:
         "rope_theta": float(hf.get("rope_theta", 1e4)), "rms_eps": float(hf.get("rms_norm_eps", 1e-5)),
         "name": hf.get("_name_or_path") or hf.get("model_type", "model"),
     }
+    from .models.rope_scaling import YarnScaling
+    yarn = YarnScaling.from_hf(hf)
+    if yarn is not None:
+        cfg["rope_scaling"] = yarn.to_dict()
+        cfg["max_position"] = int(hf.get("max_position_embeddings") or yarn.max_position())
     if hf.get("kv_lora_rank"):  # latent attention (DeepSeek-V2/V3 style)
         cfg.update(q_lora_rank=int(hf.get("q_lora_rank") or 0), kv_lora_rank=int(hf["kv_lora_rank"]),
                    qk_nope_head_dim=int(hf.get("qk_nope_head_dim", 128)), qk_rope_head_dim=int(hf.get("qk_rope_head_dim", 64)),

@@ -150,15 +150,21 @@ def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict
 
 def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots: int | None = None, max_batch: int = 64,
                 max_seq_len: int = 8192, tp_rank: int = 0, tp_size: int = 1,
-                collective=None, use_graphs: bool = True, kv_budget_bytes: int | None = None):
+                collective=None, use_graphs: bool = True, kv_budget_bytes: int | None = None,
+                yarn_context_extension: float | None = None):
     """``.mfq`` -> (engine, tokenizer, config).  ``kv_budget_bytes`` caps the paged KV pool (see ``engine/kv_budget.py``);
-    on a GPU it defaults to 90 % of the memory that is free once the weights are resident."""
+    on a GPU it defaults to 90 % of the memory that is free once the weights are resident.  ``yarn_context_extension``
+    (> 1) runs the model on that multiple of its trained context with YaRN-scaled rotary frequencies."""
     from .engine.llm_engine import LLMEngine
     from .models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
     from .server.tokenizer import tokenizer_from_assets
     with F.open_mfq(path) as store:
         assets = store.assets()
         raw = json.loads(assets["model_config.json"])
+        if yarn_context_extension and yarn_context_extension > 1.0:
+            trained = int((raw.get("rope_scaling") or {}).get("original_max_position") or raw.get("max_position") or 8192)
+            raw["rope_scaling"] = dict(raw.get("rope_scaling") or {}, factor=float(yarn_context_extension), original_max_position=trained)
+            raw["max_position"] = int(trained * yarn_context_extension)
         if raw.get("kv_lora_rank"):  # latent attention family
             from .models.mla import MlaConfig, MlaModel, mla_weights_from_tensors
             if tp_size != 1:

@@ -309,7 +309,8 @@ def _cmd_serve(args) -> int:
         path = name_or_path if Path(name_or_path).exists() else args.model
         engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size,
                                         native_4bit=args.native_4bit, expert_slots=args.moe_gpu_cache_slots,
-                                        kv_budget_bytes=int(args.kv_budget_gb * (1 << 30)) if args.kv_budget_gb else None)
+                                        kv_budget_bytes=int(args.kv_budget_gb * (1 << 30)) if args.kv_budget_gb else None,
+                                        yarn_context_extension=args.yarn_context_extension)
         if args.session_cache_gb > 0:
             from .engine.session_cache import SessionSnapshotCache
             engine.session_cache = SessionSnapshotCache(int(args.session_cache_gb * (1 << 30)))
@@ -355,7 +356,7 @@ def _cmd_runtime(args) -> int:
     sys.stdout = sys.stderr  # anything printed while serving must not corrupt the frame stream
     service = ModelService(max_queue=args.max_queue, queue_timeout=args.queue_timeout)
     engine, tok, _cfg = load_engine(args.model, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size,
-                                    native_4bit=args.native_4bit)
+                                    native_4bit=args.native_4bit, yarn_context_extension=args.yarn_context_extension)
     service.add_model(args.model_name or Path(args.model).stem, engine, tok)
     try:
         StdioTransport(service, sys.stdin, out).serve()
@@ -488,6 +489,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--yarn-context-extension", type=float, default=None,
+                   help="run on this multiple (> 1) of the trained context with YaRN-scaled rotary frequencies")
     s.add_argument("--anthropic-port", type=int, default=0,
                    help="second listener for Anthropic-style clients (the reference uses 8091); 0: one port serves both")
     s.add_argument("--api-keys-file", default=None,
@@ -518,6 +521,7 @@ def build_parser() -> argparse.ArgumentParser:
     rt.add_argument("--max-queue", type=int, default=256)
     rt.add_argument("--queue-timeout", type=float, default=30.0)
     rt.add_argument("--native-4bit", action="store_true")
+    rt.add_argument("--yarn-context-extension", type=float, default=None)
     rt.add_argument("--device")
     rt.set_defaults(fn=_cmd_runtime)
     be = sub.add_parser("bench", help="run the flagship benchmark (arguments are passed through to bench.py)")

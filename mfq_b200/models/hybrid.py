@@ -416,7 +416,7 @@ class HybridModel(MoeDecoderModel):
                 vd = torch.empty_like(kd)
             q = ops.rope_kv_write(qkv, step.positions, step.slots, kv, n_q=self.hq, n_kv=self.hk, head_dim=d, theta=cfg.rope_theta,
                                   rot=self.rot, kd_out=kd, vd_out=vd, q_norm=layer.q_norm, k_norm=layer.k_norm,
-                                  norm_eps=cfg.rms_eps)
+                                  norm_eps=cfg.rms_eps, scaling=self.rope_scaling)
             if prefill:
                 o = self._prefill_attention(q, kd, vd, kv, step)
             else:
@@ -432,8 +432,8 @@ class HybridModel(MoeDecoderModel):
                     return x
                 xf = x.float()
                 return (xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + cfg.rms_eps) * w).to(torch.bfloat16)
-            q = ref.rope(headnorm(q3[:, : self.hq], layer.q_norm), step.positions, cfg.rope_theta, self.rot)
-            k = ref.rope(headnorm(q3[:, self.hq : self.hq + self.hk], layer.k_norm), step.positions, cfg.rope_theta, self.rot)
+            q = ref.rope(headnorm(q3[:, : self.hq], layer.q_norm), step.positions, cfg.rope_theta, self.rot, self.rope_scaling)
+            k = ref.rope(headnorm(q3[:, self.hq : self.hq + self.hk], layer.k_norm), step.positions, cfg.rope_theta, self.rot, self.rope_scaling)
             ref.write_kv(kv, k, q3[:, self.hq + self.hk :], step.slots)
             if prefill:
                 o = self._prefill_attention(q, None, None, kv, step)

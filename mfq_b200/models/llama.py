@@ -24,6 +24,7 @@ from .. import ops
 from ..ops import reference as ref
 from ..quantize.fp8_block import quantize_fp8_block_torch
 from ..utils.profiler import scope
+from .rope_scaling import YarnScaling
 
 FP8 = torch.float8_e4m3fn
 
@@ -41,6 +42,7 @@ class LlamaConfig:
     rms_eps: float = 1e-5
     max_position: int = 8192
     name: str = "llama-8b-fp8"
+    rope_scaling: dict | None = None  # YaRN context extension: the fields of models.rope_scaling.YarnScaling
 
     @classmethod
     def llama_8b(cls) -> "LlamaConfig":
@@ -249,6 +251,9 @@ class LlamaModel:
         self.hq = cfg.num_heads // self.tp
         self.hk = max(1, cfg.num_kv_heads // self.tp)
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.rope_scaling = YarnScaling.from_dict(getattr(cfg, "rope_scaling", None))
+        if self.rope_scaling is not None:
+            self.sm_scale *= self.rope_scaling.softmax_scale_factor
         self.attn_splits = 1
         self.attn_rot = None  # leading dims of a head that are rotated (None: all of them)
 
@@ -302,11 +307,11 @@ class LlamaModel:
                 kd = torch.empty((t, self.hk, d), dtype=torch.bfloat16, device=qkv.device)
                 vd = torch.empty_like(kd)
             q = ops.rope_kv_write(qkv, step.positions, step.slots, kv, n_q=self.hq, n_kv=self.hk, head_dim=d,
-                                  theta=cfg.rope_theta, rot=self.attn_rot, kd_out=kd, vd_out=vd)
+                                  theta=cfg.rope_theta, rot=self.attn_rot, kd_out=kd, vd_out=vd, scaling=self.rope_scaling)
         else:
             q3 = qkv.view(t, self.hq + 2 * self.hk, d)
-            q = ref.rope(q3[:, : self.hq], step.positions, cfg.rope_theta, self.attn_rot)
-            k = ref.rope(q3[:, self.hq : self.hq + self.hk], step.positions, cfg.rope_theta, self.attn_rot)
+            q = ref.rope(q3[:, : self.hq], step.positions, cfg.rope_theta, self.attn_rot, self.rope_scaling)
+            k = ref.rope(q3[:, self.hq : self.hq + self.hk], step.positions, cfg.rope_theta, self.attn_rot, self.rope_scaling)
             ref.write_kv(kv, k, q3[:, self.hq + self.hk :], step.slots)
         if not prefill:
             if qkv.is_cuda:

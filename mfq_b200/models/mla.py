@@ -92,6 +92,8 @@ class MlaModel(MoeDecoderModel):
         if self.tp != 1:
             raise NotImplementedError("latent attention is single-rank for now")
         self.sm_scale = 1.0 / math.sqrt(cfg.qk_nope_head_dim + cfg.qk_rope_head_dim)
+        if self.rope_scaling is not None:
+            self.sm_scale *= self.rope_scaling.softmax_scale_factor
         self.attn_rot = cfg.qk_rope_head_dim
         if cfg.absorbed:
             self.hk = 1  # all query heads attend to the one latent row per token

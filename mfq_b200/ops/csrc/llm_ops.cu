@@ -200,6 +200,21 @@ __global__ void quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* 
 // qkv: [T, (Hq + 2 Hk) * D] bf16.  One warp per (token, head).  Cache page layout [page][Hk][page_size][D]
 // with one fp32 multiplier per (page, head, slot).  slots[t] = physical page * page_size + offset (< 0: skip).
 // ---------------------------------------------------------------------------------------------
+// YaRN context extension: rotary pair `fi` keeps its frequency below `low`, is slowed down by `factor` above `high`,
+// blended linearly in between; cos / sin carry `mscale`.  factor == 1 leaves the frequencies bit-identical.
+struct RopeScale {
+  float factor, low, high, mscale;
+};
+
+__device__ __forceinline__ float rope_inv_freq(float log2_theta, int fi, int rot, const RopeScale& y) {
+  float f = exp2f(-log2_theta * (2.f * fi) / float(rot));
+  if (y.factor != 1.f) {
+    const float ramp = fminf(fmaxf((float(fi) - y.low) / (y.high - y.low), 0.f), 1.f);
+    f *= (1.f - ramp) + ramp / y.factor;
+  }
+  return f;
+}
+
 template <int D>
 __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
                                      const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
@@ -207,7 +222,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
                                      float* __restrict__ k_scale, float* __restrict__ v_scale, int T, int Hq, int Hk,
                                      int page_size, int rot, float log2_theta, __nv_bfloat16* __restrict__ kd_out,
                                      __nv_bfloat16* __restrict__ vd_out, const float* __restrict__ q_norm_w,
-                                     const float* __restrict__ k_norm_w, float norm_eps, int row_stride) {
+                                     const float* __restrict__ k_norm_w, float norm_eps, int row_stride,
+                                     const RopeScale ys) {
   pdl_trigger();
   pdl_wait();
   constexpr int EPL = D / 32;  // elements per lane
@@ -266,9 +282,11 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
 #pragma unroll
       for (int j = 0; j < HP; ++j) {
         const int idx = lane * HP + j;
-        const float inv_freq = exp2f(-log2_theta * (2.f * idx) / float(rot));
+        const float inv_freq = rope_inv_freq(log2_theta, idx, rot, ys);
         float s, c;
         sincosf(pos * inv_freq, &s, &c);
+        s *= ys.mscale;
+        c *= ys.mscale;
         const float a = lo[j], b = hi[j];
         lo[j] = a * c - b * s;
         hi[j] = b * c + a * s;
@@ -282,9 +300,11 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, cons
           const int idx = (part ? D / 2 : 0) + lane * HP + j;
           if (idx < rot) {
             const int fi = idx % half_rot;
-            const float inv_freq = exp2f(-log2_theta * (2.f * fi) / float(rot));
+            const float inv_freq = rope_inv_freq(log2_theta, fi, rot, ys);
             float s, c;
             sincosf(pos * inv_freq, &s, &c);
+            s *= ys.mscale;
+            c *= ys.mscale;
             const float self = part ? hi[j] : lo[j];
             const int pidx = idx < half_rot ? idx + half_rot : idx - half_rot;
             const float other = __bfloat162float(src[pidx]) * (nw ? inv_rms * nw[pidx] : 1.f);
@@ -507,26 +527,40 @@ extern "C" int mfq_gate_quant_rows(const void* x, const void* gate, void* q_out,
 
 // q_norm_w / k_norm_w ([D] fp32, may be null): per-head RMSNorm of q / k before the rotation; row_stride: elements
 // between token rows of qkv (>= (Hq + 2 Hk) * D; an attention output gate may follow the v heads).
-extern "C" int mfq_rope_kv_write_ex(const void* qkv, const int* positions, const int* slots, void* q_out, void* k_cache,
-                                    void* v_cache, float* k_scale, float* v_scale, int T, int Hq, int Hk, int D,
-                                    int page_size, int rot, float theta, void* kd_out, void* vd_out,
-                                    const float* q_norm_w, const float* k_norm_w, float norm_eps, int row_stride,
-                                    cudaStream_t stream) {
+// yarn_*: context extension (see RopeScale); factor 1 and mscale 1 are the plain rotation.
+extern "C" int mfq_rope_kv_write_yarn(const void* qkv, const int* positions, const int* slots, void* q_out, void* k_cache,
+                                      void* v_cache, float* k_scale, float* v_scale, int T, int Hq, int Hk, int D,
+                                      int page_size, int rot, float theta, void* kd_out, void* vd_out,
+                                      const float* q_norm_w, const float* k_norm_w, float norm_eps, int row_stride,
+                                      float yarn_factor, float yarn_low, float yarn_high, float yarn_mscale,
+                                      cudaStream_t stream) {
   if (T <= 0 || row_stride < (Hq + 2 * Hk) * D || row_stride % 8) return -1;
+  if (!(yarn_factor >= 1.f) || !(yarn_high > yarn_low) || !(yarn_mscale > 0.f)) return -1;
   const int warps = T * (Hq + 2 * Hk);
   const int blocks = (warps + 7) / 8;
   const float l2t = log2f(theta);
+  const RopeScale ys{yarn_factor, yarn_low, yarn_high, yarn_mscale};
 #define MFQ_ROPE(DD)                                                                                             \
   launch_kernel(rope_kv_write_kernel<DD>, dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(qkv), positions, slots, \
       static_cast<__nv_bfloat16*>(q_out), static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache),      \
       k_scale, v_scale, T, Hq, Hk, page_size, rot, l2t, static_cast<__nv_bfloat16*>(kd_out),                   \
-      static_cast<__nv_bfloat16*>(vd_out), q_norm_w, k_norm_w, norm_eps, row_stride)
+      static_cast<__nv_bfloat16*>(vd_out), q_norm_w, k_norm_w, norm_eps, row_stride, ys)
   if (D == 128) MFQ_ROPE(128);
   else if (D == 64) MFQ_ROPE(64);
   else if (D == 256) MFQ_ROPE(256);
   else return -1;
 #undef MFQ_ROPE
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+extern "C" int mfq_rope_kv_write_ex(const void* qkv, const int* positions, const int* slots, void* q_out, void* k_cache,
+                                    void* v_cache, float* k_scale, float* v_scale, int T, int Hq, int Hk, int D,
+                                    int page_size, int rot, float theta, void* kd_out, void* vd_out,
+                                    const float* q_norm_w, const float* k_norm_w, float norm_eps, int row_stride,
+                                    cudaStream_t stream) {
+  return mfq_rope_kv_write_yarn(qkv, positions, slots, q_out, k_cache, v_cache, k_scale, v_scale, T, Hq, Hk, D, page_size,
+                                rot, theta, kd_out, vd_out, q_norm_w, k_norm_w, norm_eps, row_stride, 1.f, 0.f, 1.f, 1.f,
+                                stream);
 }
 
 extern "C" int mfq_rope_kv_write(const void* qkv, const int* positions, const int* slots, void* q_out, void* k_cache,

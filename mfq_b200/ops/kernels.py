@@ -131,13 +131,21 @@ def gate_quant_rows(x: torch.Tensor, gate: torch.Tensor):
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, kv, *, n_q: int, n_kv: int,
                   head_dim: int, theta: float, rot: int | None = None, q_out=None, kd_out=None,
                   vd_out=None, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
-                  norm_eps: float = 1e-6) -> torch.Tensor:
-    """Rotate Q/K, write K/V of each token into the fp8 page pool ``kv`` (a :class:`LayerKV`).  ``kd_out`` /
+                  norm_eps: float = 1e-6, scaling=None) -> torch.Tensor:
+    """Rotate Q/K, write K/V of each token into the fp8 page pool ``kv`` (a :class:`LayerKV`).  ``scaling``: a
+    :class:`~mfq_b200.models.rope_scaling.YarnScaling` for context extension.  ``kd_out`` /
     ``vd_out`` (``[T, Hk, D]`` bf16) optionally receive the values the pages now hold, for the chunk's attention.
     ``q_norm`` / ``k_norm`` (``[D]`` fp32): per-head RMSNorm before the rotation; ``rot`` < D: partial rotary.
     Rows of ``qkv`` may be wider than the q|k|v heads (e.g. an output gate after v); the row stride is honoured."""
     t = qkv.shape[0]
     q_out = torch.empty((t, n_q, head_dim), dtype=torch.bfloat16, device=qkv.device) if q_out is None else q_out
+    if scaling is not None and (scaling.factor != 1.0 or scaling.mscale != 1.0):
+        rc = lib().mfq_rope_kv_write_yarn(ptr(qkv), ptr(positions), ptr(slots), ptr(q_out), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale),
+                                          ptr(kv.v_scale), t, n_q, n_kv, head_dim, kv.page_size, rot or head_dim, float(theta),
+                                          ptr(kd_out), ptr(vd_out), ptr(q_norm), ptr(k_norm), float(norm_eps), qkv.stride(0),
+                                          *scaling.kernel_args(rot or head_dim, float(theta)), stream_ptr())
+        check(rc, "rope_kv_write")
+        return q_out
     rc = lib().mfq_rope_kv_write_ex(ptr(qkv), ptr(positions), ptr(slots), ptr(q_out), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale),
                                     ptr(kv.v_scale), t, n_q, n_kv, head_dim, kv.page_size, rot or head_dim, float(theta),
                                     ptr(kd_out), ptr(vd_out), ptr(q_norm), ptr(k_norm), float(norm_eps), qkv.stride(0),

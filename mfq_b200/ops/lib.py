@@ -31,6 +31,8 @@ _SIGNATURES = {
     "mfq_silu_mul_bf16": [_vp, _vp, _i, _i, _i, _vp],
     "mfq_gate_quant_rows": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "mfq_rope_kv_write_ex": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _f, _i, _vp],
+    "mfq_rope_kv_write_yarn": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _f, _i,
+                               _f, _f, _f, _f, _vp],
     "mfq_rope_kv_write": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     
     "mfq_paged_attn_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp],

@@ -52,14 +52,18 @@ def fp8_gemm(x_q, x_scale, w_q, w_scale, residual=None) -> torch.Tensor:
     return y.to(torch.bfloat16)
 
 
-def rope(x: torch.Tensor, positions: torch.Tensor, theta: float, rot: int | None = None) -> torch.Tensor:
-    """``x [T, H, D]``; rotate-half pairing (i, i + rot/2) over the first ``rot`` dims."""
+def rope(x: torch.Tensor, positions: torch.Tensor, theta: float, rot: int | None = None, scaling=None) -> torch.Tensor:
+    """``x [T, H, D]``; rotate-half pairing (i, i + rot/2) over the first ``rot`` dims.  ``scaling``: a
+    :class:`~mfq_b200.models.rope_scaling.YarnScaling` (blended frequencies, cos / sin times its attention factor)."""
     d = x.shape[-1]
     rot = rot or d
     half = rot // 2
-    inv = torch.exp2(-math.log2(theta) * (2 * torch.arange(half, device=x.device, dtype=torch.float32)) / rot)
+    if scaling is not None:
+        inv, mscale = scaling.inv_freq(rot, theta, x.device), scaling.mscale
+    else:
+        inv, mscale = torch.exp2(-math.log2(theta) * (2 * torch.arange(half, device=x.device, dtype=torch.float32)) / rot), 1.0
     ang = positions.float()[:, None] * inv[None, :]
-    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    c, s = ang.cos()[:, None, :] * mscale, ang.sin()[:, None, :] * mscale
     xf = x.float()
     a, b = xf[..., :half], xf[..., half:rot]
     out = xf.clone()
