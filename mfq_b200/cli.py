@@ -380,6 +380,29 @@ def _cmd_profile(args) -> int:
     return 0
 
 
+def _cmd_bench_model(args) -> int:
+    """Prompt-length x concurrency matrix through the stdio runtime; JSON (+ Markdown / HTML) report."""
+    from .evaluation import model_bench as mb
+    ints = lambda text: [int(x) for x in text.split(",") if x]
+    if args.render:
+        report = json.loads(Path(args.render).read_text())
+    else:
+        if not args.model and not args.runtime_command:
+            raise SystemExit("--model (or --runtime-command) is required")
+        command = args.runtime_command.split() if args.runtime_command else [
+            sys.executable, "-m", "mfq_b200.cli", "runtime", "--model", args.model, "--continuous-batching",
+            str(max(ints(args.concurrency))), "--ctx-size", str(max(ints(args.prompt_tokens)) + args.new_tokens + 16),
+            *(["--device", args.device] if args.device else [])]
+        report = mb.benchmark(command, ints(args.prompt_tokens), args.new_tokens, ints(args.concurrency), args.repeats,
+                              args.warmup, mtp=args.mtp, label=args.label or (Path(args.model).stem if args.model else ""))
+    if args.output:
+        Path(args.output).write_text(json.dumps(report, indent=1))
+    if args.html:
+        Path(args.html).write_text(mb.render_html(report))
+    print(mb.render_markdown(report))
+    return 0
+
+
 def _cmd_bench(args) -> int:
     os.execv(sys.executable, [sys.executable, str(Path(__file__).resolve().parents[1] / "bench.py"), *args.rest])
 
@@ -505,6 +528,21 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--prefix-cache-ram-gb", type=float, default=4.0)
     s.add_argument("--prefix-cache-disk-gb", type=float, default=64.0)
     s.set_defaults(fn=_cmd_serve)
+    bm = sub.add_parser("bench-model", help="prefill / decode / TTFT over a prompt-length x concurrency matrix (stdio runtime)")
+    bm.add_argument("--model")
+    bm.add_argument("--runtime-command", help="another runtime that speaks the stdio frames (instead of --model)")
+    bm.add_argument("--prompt-tokens", default="128,1024")
+    bm.add_argument("--new-tokens", type=int, default=64)
+    bm.add_argument("--concurrency", default="1,8")
+    bm.add_argument("--repeats", type=int, default=3)
+    bm.add_argument("--warmup", type=int, default=1)
+    bm.add_argument("--mtp", action="store_true")
+    bm.add_argument("--device")
+    bm.add_argument("--label", default="")
+    bm.add_argument("--output", help="write the JSON report here")
+    bm.add_argument("--html", help="write a self-contained HTML report here")
+    bm.add_argument("--render", help="render an existing JSON report instead of running")
+    bm.set_defaults(fn=_cmd_bench_model)
     pf = sub.add_parser("profile", help="per-op time split of a prefill and a few eager decode steps")
     pf.add_argument("--model", required=True)
     pf.add_argument("--prompt-tokens", type=int, default=128)

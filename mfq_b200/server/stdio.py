@@ -95,8 +95,19 @@ class StdioTransport:
         self.send({"id": rid, "type": "result", "data": {
             "text": text, "finish_reason": finish or "stop",
             "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out), "total_tokens": len(ids) + len(out)},
-            "metrics": {"prefill_ms": (first - t0) * 1e3, "decode_ms": (end - first) * 1e3, "total_ms": (end - t0) * 1e3}}})
+            "metrics": self._metrics(len(ids), len(out), t0, first, end)}})
         self.send({"id": rid, "type": "done"})
+
+    @staticmethod
+    def _metrics(prompt: int, completion: int, t0: float, first: float, end: float) -> dict:
+        """Per-request timing as the reference runtime reports it (``InferenceMetrics``: ttft, prefill / decode ms and
+        rates).  The first generated token belongs to the prefill; decode covers the tokens after it."""
+        prefill_ms, decode_ms = (first - t0) * 1e3, (end - first) * 1e3
+        return {"prompt_tokens": prompt, "prefill_tokens": prompt, "completion_tokens": completion,
+                "ttft_ms": prefill_ms, "prefill_ms": prefill_ms, "decode_ms": decode_ms, "total_ms": (end - t0) * 1e3,
+                "prefill_tps": prompt / max(prefill_ms, 1e-6) * 1e3,
+                "decode_tps": max(completion - 1, 0) / max(decode_ms, 1e-6) * 1e3,
+                "generation_tps": completion / max((end - t0) * 1e3, 1e-6) * 1e3}
 
     def _fail(self, rid, code: str, message: str) -> None:
         self.send({"id": rid, "type": "error", "error": {"code": code, "message": message}})
