@@ -303,11 +303,29 @@ def _cmd_serve(args) -> int:
     from .checkpoint import load_engine
     from .server import ModelService, create_app
     device = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    ctx = None
+    if args.tensor_parallel > 1:
+        from .server import tp_serve
+        if not tp_serve.under_launcher():  # first invocation: become N ranks
+            import subprocess
+            return subprocess.call(tp_serve.launcher_argv(sys.argv[1:] if args._argv is None else args._argv, args.tensor_parallel))
+        ctx = tp_serve.RankContext(device)
+        device = ctx.device
+    tp = dict(tp_rank=ctx.rank, tp_size=ctx.world, collective=ctx.collective) if ctx else {}
+
+    if ctx is not None and ctx.rank != 0:  # follower: mirror rank 0's engine calls until it shuts down
+        from .parallel.spmd import follower_loop
+        engine, _tok, _cfg = load_engine(args.model, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size,
+                                         native_4bit=args.native_4bit, yarn_context_extension=args.yarn_context_extension, **tp)
+        why = follower_loop(engine, ctx.log)
+        print(f"rank={ctx.rank} follower_exit={why}", file=sys.stderr)
+        ctx.finish()
+        return 0 if why == "shutdown" else 1
     service = ModelService(max_instances=args.max_runtime_instances, max_queue=args.max_queue, queue_timeout=args.queue_timeout)
 
     def loader(name_or_path):
         path = name_or_path if Path(name_or_path).exists() else args.model
-        engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size,
+        engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size, **tp,
                                         native_4bit=args.native_4bit, expert_slots=args.moe_gpu_cache_slots,
                                         kv_budget_bytes=int(args.kv_budget_gb * (1 << 30)) if args.kv_budget_gb else None,
                                         yarn_context_extension=args.yarn_context_extension)
@@ -321,8 +339,11 @@ def _cmd_serve(args) -> int:
             engine.prefix_salt = f"{Path(path).name}:{Path(path).stat().st_size}"
         return engine, tok
 
-    service.loader = loader
+    service.loader = loader if ctx is None else None  # ranks load together at start; no loading on demand under TP
     engine, tok = loader(args.model)
+    if ctx is not None:
+        from .parallel.spmd import LeaderBackend
+        engine = LeaderBackend(engine, ctx.log)
     service.add_model(args.model_name or Path(args.model).stem, engine, tok)
     key = os.environ.get(args.api_key_env) if args.api_key_env else None
     if args.api_keys_file:
@@ -336,11 +357,17 @@ def _cmd_serve(args) -> int:
         from .server.cluster import ClusterBackend
         cluster = ClusterBackend(args.cluster_peer)
     app = create_app(service, api_key=key, cluster=cluster)
-    if args.anthropic_port and args.anthropic_port != args.port:
-        from .server.listen import Listeners
-        Listeners(app, args.host, [args.port, args.anthropic_port], access_log=args.access_log).start().wait()
-    else:
-        uvicorn.run(app, host=args.host, port=args.port, access_log=args.access_log)
+    try:
+        if args.anthropic_port and args.anthropic_port != args.port:
+            from .server.listen import Listeners
+            Listeners(app, args.host, [args.port, args.anthropic_port], access_log=args.access_log).start().wait()
+        else:
+            uvicorn.run(app, host=args.host, port=args.port, access_log=args.access_log)
+    finally:
+        if ctx is not None:  # the server is down: let the other ranks go
+            service.shutdown()
+            engine.shutdown_followers()
+            ctx.finish()
     return 0
 
 
@@ -512,6 +539,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--tensor-parallel", type=int, default=1,
+                   help="ranks (one process per GPU) that share every layer: attention heads, FFN columns and experts are sharded")
     s.add_argument("--yarn-context-extension", type=float, default=None,
                    help="run on this multiple (> 1) of the trained context with YaRN-scaled rotary frequencies")
     s.add_argument("--anthropic-port", type=int, default=0,
@@ -570,6 +599,7 @@ def build_parser() -> argparse.ArgumentParser:
 
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
+    args._argv = None if argv is None else list(argv)  # what a re-launch under the rank launcher repeats
     return int(args.fn(args) or 0)
 
 

@@ -118,6 +118,9 @@ def paged_attn_decode(q, kv, block_table, seq_lens, sm_scale, q_len: int = 1):
     b = q.shape[0] // q_len
     for i in range(b):
         n = int(seq_lens[i])
+        if n <= 0:  # an unused row of the batch bucket: nothing to attend to (the GPU kernel writes zeros too)
+            outs.append(torch.zeros_like(q[i * q_len : (i + 1) * q_len]))
+            continue
         k, v = gather_paged(kv, block_table[i], n)
         outs.append(attention(q[i * q_len : (i + 1) * q_len], k, v, sm_scale, causal_offset=n - q_len))
     return torch.cat(outs, 0)

@@ -103,3 +103,24 @@ class LocalCollective:
 
     def barrier(self) -> None:
         self.group.barrier.wait()
+
+
+class ProcessGroupCollective(LocalCollective):
+    """The same interface across PROCESSES, over a ``torch.distributed`` group of CPU tensors (``gloo``).
+
+    It exists so that the whole multi-rank serving path (launcher, command log, sharded checkpoint load, tensor- and
+    expert-parallel model code) runs end to end on machines without GPUs; GPU ranks use the fused peer-memory
+    collectives of :class:`~mfq_b200.parallel.tensor_parallel.TensorParallel` instead."""
+
+    def __init__(self, group=None) -> None:
+        import torch.distributed as dist
+        self._dist, self.pg = dist, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+
+    def _exchange(self, value):
+        out = [None] * self.world
+        self._dist.all_gather_object(out, value, group=self.pg)
+        return out
+
+    def barrier(self) -> None:
+        self._dist.barrier(group=self.pg)
