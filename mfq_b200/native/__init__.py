@@ -41,6 +41,10 @@ def lib():
             "mfq_tp_plan": ([_i64, _i, _vp, _i64, _vp, _vp], _i),
             "mfq_moe_rank_swaps": ([_vp, _vp, _i, _i, _d, _vp, _vp], _i),
             "mfq_moe_dispatch_plan": ([_vp, _vp, _i, _d, _d, _d, _d, _i, _vp], _i),
+            "mfq_json_vocab_open": ([_vp, _vp, _i64], _vp), "mfq_json_vocab_close": ([_vp], None),
+            "mfq_json_vocab_nodes": ([_vp], _i64), "mfq_json_state_init": ([_vp, _i], None),
+            "mfq_json_state_feed": ([_vp, _vp, _i64], _i), "mfq_json_state_complete": ([_vp], _i),
+            "mfq_json_mask": ([_vp, _vp, _vp], _i64),
             "mfq_slotbook_open": ([_i], _vp), "mfq_slotbook_close": ([_vp], None), "mfq_slotbook_lookup": ([_vp, _i64], _i),
             "mfq_slotbook_acquire": ([_vp, _i64, _vp], _i), "mfq_slotbook_pin": ([_vp, _i64, _i], _i),
         }
@@ -293,3 +297,57 @@ class SlotBook:
         if n < 0:
             raise KeyError(_err())
         return n
+
+
+class JsonVocabulary:
+    """Byte trie of a tokenizer's vocabulary for JSON-constrained decoding (``token_bytes[i]``: the bytes token ``i``
+    adds to the text; empty for special tokens, which then never match)."""
+
+    def __init__(self, token_bytes: list[bytes]) -> None:
+        self.size = len(token_bytes)
+        offsets = np.zeros(self.size + 1, dtype=np.int64)
+        np.cumsum([len(b) for b in token_bytes], out=offsets[1:])
+        blob = np.frombuffer(b"".join(token_bytes) or b"\0", dtype=np.uint8)
+        self._h = lib().mfq_json_vocab_open(_np_ptr(blob), _np_ptr(offsets), self.size)
+        if not self._h:
+            raise ValueError(_err())
+        self.token_bytes = token_bytes
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().mfq_json_vocab_close(self._h)
+            self._h = None
+
+    @property
+    def nodes(self) -> int:
+        return int(lib().mfq_json_vocab_nodes(self._h))
+
+
+class JsonState:
+    """Position of a partly generated JSON document in the grammar."""
+
+    def __init__(self, vocab: JsonVocabulary, need_object: bool = False) -> None:
+        self.vocab = vocab
+        self._s = np.zeros(16, dtype=np.uint8)
+        lib().mfq_json_state_init(_np_ptr(self._s), int(need_object))
+
+    def feed(self, data: bytes) -> bool:
+        """Consume bytes; False (state unchanged) if the grammar refuses them."""
+        if not data:
+            return True
+        buf = np.frombuffer(data, dtype=np.uint8)
+        return lib().mfq_json_state_feed(_np_ptr(self._s), _np_ptr(buf), len(data)) == 0
+
+    def feed_token(self, token: int) -> bool:
+        return self.feed(self.vocab.token_bytes[token])
+
+    @property
+    def complete(self) -> bool:
+        return bool(lib().mfq_json_state_complete(_np_ptr(self._s)))
+
+    def mask(self) -> np.ndarray:
+        """bool ``[vocab]``: tokens that keep the text a prefix of a valid document."""
+        words = np.zeros((self.vocab.size + 31) // 32, dtype=np.uint32)
+        if lib().mfq_json_mask(self.vocab._h, _np_ptr(self._s), _np_ptr(words)) < 0:
+            raise ValueError(_err())
+        return np.unpackbits(words.view(np.uint8), bitorder="little")[: self.vocab.size].astype(bool)

@@ -71,6 +71,16 @@ int mfq_moe_rank_swaps(const double* heat, const uint8_t* resident, int n_expert
 // per-expert execution tier for one step: 0 inactive, 1 GPU resident, 2 GPU after transfer, 3 CPU
 int mfq_moe_dispatch_plan(const int* tokens_per_expert, const uint8_t* resident, int n_experts, double bytes_per_expert,
                           double h2d_gbs, double gpu_tok_us, double cpu_tok_us, int cpu_available, int* tier_out);
+// ---- token constraints ----------------------------------------------------------------------------------------
+// JSON grammar over a byte trie of the vocabulary (json_constraint.cpp); state = 16 opaque bytes
+void* mfq_json_vocab_open(const uint8_t* bytes, const int64_t* offsets, int64_t vocab);
+void mfq_json_vocab_close(void* vocab);
+int64_t mfq_json_vocab_nodes(void* vocab);
+void mfq_json_state_init(void* state, int need_object);
+int mfq_json_state_feed(void* state, const uint8_t* bytes, int64_t n);
+int mfq_json_state_complete(const void* state);
+int64_t mfq_json_mask(void* vocab, const void* state, uint32_t* bits_out);
+
 void* mfq_slotbook_open(int slots);
 void mfq_slotbook_close(void* book);
 int mfq_slotbook_lookup(void* book, int64_t key);                 // slot or -1; refreshes recency
