@@ -188,4 +188,7 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
                          max_batch=max_batch, max_seq_len=max_seq_len).num_pages
     engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, num_pages=num_pages,
                        use_graphs=use_graphs and expert_slots is None)
-    return engine, tokenizer_from_assets(assets, cfg.vocab_size), cfg
+    tokenizer = tokenizer_from_assets(assets, cfg.vocab_size)
+    # structured output needs the vocabulary's byte strings; resolved on the first request that asks for it
+    engine.set_token_bytes(lambda: tokenizer.token_bytes(cfg.vocab_size), tokenizer.stop_ids)
+    return engine, tokenizer, cfg

@@ -84,6 +84,9 @@ class LLMEngine:
         self.row_seq: dict[int, int] = {}
         self.row_len: dict[int, int] = {}  # host mirror of seq_lens for page management
         self.row_stochastic: dict[int, bool] = {}
+        self.row_constraint: dict[int, object] = {}  # row -> grammar state of a structured-output request
+        self.logit_bias: torch.Tensor | None = None  # [max_batch, vocabulary] bf16, allocated by the first such request
+        self._token_bytes, self._constraint_vocab, self._constraint_stop = None, None, ()
         self._next_seq_id = 0
         # models with recurrent (linear-attention) state keep it per batch row
         self.rec_state = model.make_state(max_batch) if hasattr(model, "make_state") else None
@@ -106,6 +109,45 @@ class LLMEngine:
             self.mtp_counters = torch.zeros(2, dtype=torch.int64, device=dev)  # drafted, accepted
             self.mtp_graphs: dict[int, torch.cuda.CUDAGraph] = {}
             self.mtp_cycles = 0
+
+    # -- token constraints -------------------------------------------------------------------------------------------
+    def set_token_bytes(self, token_bytes, stop_ids=()) -> None:
+        """Give the engine the vocabulary's byte strings (see the tokenizers' ``token_bytes``); needed before a request
+        may ask for structured output.  The trie is built on first use."""
+        self._token_bytes, self._constraint_stop = token_bytes, tuple(stop_ids)
+        self._constraint_vocab = None
+
+    def _constraint_for(self, params):
+        fmt = getattr(params, "response_format", None) if params is not None else None
+        if not fmt or getattr(self, "_token_bytes", None) is None:
+            return None
+        if self._constraint_vocab is None:
+            from .. import native
+            table = self._token_bytes() if callable(self._token_bytes) else self._token_bytes
+            self._constraint_vocab = native.JsonVocabulary(list(table))
+        from .constraints import make_constraint
+        stops = tuple(getattr(params, "stop_token_ids", ()) or ()) or self._constraint_stop
+        return make_constraint(fmt, self._constraint_vocab, stops)
+
+    def _bias_rows(self, logits: torch.Tensor, b: int) -> torch.Tensor:
+        """The persistent ``[max_batch, vocabulary]`` bias, cut to this rank's vocabulary shard of ``logits``."""
+        v = logits.shape[1]
+        tp = self.model.tp
+        if self.logit_bias is None or self.logit_bias.shape[1] != v * tp:
+            self.logit_bias = torch.zeros((self.max_batch, v * tp), dtype=torch.bfloat16, device=self.device)
+        lo = self.model.w.tp_rank * v if tp > 1 else 0
+        return self.logit_bias[:b, lo : lo + v]
+
+    def _write_bias(self, rows) -> None:
+        """Refresh the bias rows of ``rows`` from their grammar states (zero for rows without one)."""
+        if self.logit_bias is None:
+            return
+        for r in rows:
+            c = self.row_constraint.get(r)
+            if c is None:
+                self.logit_bias[r].zero_()
+            else:
+                self.logit_bias[r].copy_(c.bias(self.logit_bias.shape[1]), non_blocking=True)
 
     # -- capacity (scheduler backend protocol) ------------------------------------------------------------------
     def free_tokens(self) -> int:
@@ -132,6 +174,7 @@ class LLMEngine:
             self.cache.release(seq)
         self.row_len.pop(row, None)
         self.row_stochastic.pop(row, None)
+        self.row_constraint.pop(row, None)
 
     # -- sampling ---------------------------------------------------------------------------------------------------
     def set_sampling(self, row: int, params) -> None:
@@ -190,11 +233,12 @@ class LLMEngine:
             self.sampled[r] = int(torch.multinomial(p / p.sum(), 1, generator=g))
 
     # -- prefill -------------------------------------------------------------------------------------------------
-    def prefill(self, row: int, token_ids, params=None, session: str | None = None) -> int:
+    def prefill(self, row: int, token_ids, params=None, session: str | None = None, generated: int = 0) -> int:
         """Run the prompt of batch row ``row`` through the model; returns the first generated token id and leaves
         the row ready for decode (``seq_lens[row]`` = prompt length, ``sampled[row]`` = first token).  With ``session``
         and a :attr:`session_cache`, the history of that conversation is restored from its snapshot when the prompt
-        extends it."""
+        extends it.  ``generated``: how many trailing tokens of ``token_ids`` the model itself produced earlier (a
+        replayed request); a token constraint re-reads them before it masks the next token."""
         dev = self.device
         self._bind_state()
         ids = torch.as_tensor(token_ids, dtype=torch.int32)
@@ -227,6 +271,14 @@ class LLMEngine:
         self._store_prefix(seq_id, keys, start)
         self.seq_lens[row] = n
         self.row_len[row] = n
+        constraint = self._constraint_for(params)
+        if constraint is not None:
+            for t in (ids[n - generated :].tolist() if generated else ()):
+                constraint.advance(int(t))
+            self.row_constraint[row] = constraint
+            bias = self._bias_rows(logits, self.max_batch)[row : row + 1]
+            self._write_bias([row])
+            logits = logits + bias
         if self.row_stochastic[row]:
             # sample row 0 of the one-row logits with this row's record
             saved_rows, saved_len = self.sample_rows[0].clone(), self.seq_lens[0].clone()
@@ -247,6 +299,8 @@ class LLMEngine:
             mlogits, mhid = self.model.mtp_forward(mstep, self.cache, hidden, prefill=True, logits_rows=last)
             self.draft[row, 0] = self.model.sample_greedy(mlogits)[0]
             self._mtp_chain(row, row + 1, mhid[n - 1 : n].contiguous(), masked=False)
+        if constraint is not None:
+            constraint.advance(int(tok))
         return int(tok)
 
     def save_session(self, row: int, session: str, tokens) -> None:
@@ -361,7 +415,7 @@ class LLMEngine:
         slots.copy_(torch.where(act, pages * self.cache.page_size + pos % self.cache.page_size, torch.full_like(pos, -1)))
         seq_lens.copy_(torch.where(act, pos + 1, pos))
 
-    def _decode_body(self, b: int, stochastic: bool = False) -> None:
+    def _decode_body(self, b: int, stochastic: bool = False, constrained: bool = False) -> None:
         dev = self.device
         self._advance(self.sampled[:b], self.input_ids[:b], self.positions[:b], self.seq_lens[:b], self.slots[:b],
                       self.cache.block_table[:b], self.active[:b])
@@ -374,6 +428,8 @@ class LLMEngine:
         if dev.type == "cuda":
             self.model.attn_splits = self._splits_now(b)
         logits = self.model.forward(step, self.cache, prefill=False, gather_logits=False)
+        if constrained:
+            logits += self._bias_rows(logits, b)
         self._sample(logits, b, stochastic)
 
     def _splits_now(self, b: int) -> int:
@@ -382,13 +438,14 @@ class LLMEngine:
         longest = max(self.row_len.values(), default=self.max_seq_len)
         return attn_splits_for(b, self.model.hk, min(self.max_seq_len, longest))
 
-    def decode_step(self, b: int, stochastic: bool = False) -> None:
-        """Advance the active rows among ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device)."""
+    def decode_step(self, b: int, stochastic: bool = False, constrained: bool = False) -> None:
+        """Advance the active rows among ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device).
+        ``constrained``: add the rows' token-constraint bias to the logits before sampling (a graph variant of its own)."""
         self._bind_state()
         if not self.use_graphs:
-            self._decode_body(b, stochastic)
+            self._decode_body(b, stochastic, constrained)
             return
-        key = (b, stochastic, self._splits_now(b))
+        key = (b, stochastic, self._splits_now(b)) + ((True,) if constrained else ())
         g = self.graphs.get(key)
         if g is None:
             ops.Workspace.get(self.device)
@@ -398,12 +455,12 @@ class LLMEngine:
             saved_rec = (self.rec_state.conv.clone(), self.rec_state.state.clone()) if self.rec_state is not None else None
             with torch.cuda.stream(side):
                 for _ in range(2):
-                    self._decode_body(b, stochastic)
+                    self._decode_body(b, stochastic, constrained)
             torch.cuda.current_stream().wait_stream(side)
             g = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             with torch.cuda.graph(g):
-                self._decode_body(b, stochastic)
+                self._decode_body(b, stochastic, constrained)
             self.launches_per_step[b] = ops.launch_count() - before
             # warm-up and capture ran real steps: roll the sequence state back (the KV rows they wrote get rewritten)
             self.seq_lens.copy_(saved[0])
@@ -519,7 +576,10 @@ class LLMEngine:
         mask = torch.zeros(self.max_batch, dtype=torch.int32)
         mask[rows] = 1
         self.active.copy_(mask.to(self.device), non_blocking=True)
-        if self.mtp_k and not any(self.row_stochastic.get(r, False) for r in rows):
+        constrained = any(r in self.row_constraint for r in rows)
+        if constrained:
+            self._write_bias(range(b))
+        if self.mtp_k and not constrained and not any(self.row_stochastic.get(r, False) for r in rows):
             self.mtp_step(b)
             toks, counts = self.out_tokens[:b].cpu(), self.n_out[:b].cpu()
             out = {}
@@ -528,10 +588,12 @@ class LLMEngine:
                 self.row_len[r] += n
                 out[r] = [int(t) for t in toks[r, :n]]
             return out
-        self.decode_step(b, any(self.row_stochastic.get(r, False) for r in rows))
+        self.decode_step(b, any(self.row_stochastic.get(r, False) for r in rows), constrained)
         toks = self.sampled[:b].cpu()
         for r in rows:
             self.row_len[r] += 1
+            if r in self.row_constraint:
+                self.row_constraint[r].advance(int(toks[r]))
         return {r: int(toks[r]) for r in rows}
 
     def step_host(self, host_in: torch.Tensor, host_out: torch.Tensor) -> None:

@@ -60,6 +60,7 @@ class SamplingParams:
     stop_token_ids: tuple[int, ...] = ()
     enable_mtp: bool = False
     mtp_max_draft_tokens: int = 3
+    response_format: dict | str | None = None  # {"type": "json_object"}: constrain the output to a JSON document
 
 
 @dataclass
@@ -277,10 +278,12 @@ class ContinuousBatchScheduler:
             self.running[row] = req
             self.stats.admitted += 1
             try:
+                extra = {}
                 if req.session is not None and hasattr(self.backend, "save_session"):
-                    tok = self.backend.prefill(row, req.context, req.params, session=req.session)
-                else:
-                    tok = self.backend.prefill(row, req.context, req.params)
+                    extra["session"] = req.session
+                if req.generated and req.params.response_format:  # replay after a retraction: the grammar has to
+                    extra["generated"] = len(req.generated)       # re-read what was generated before
+                tok = self.backend.prefill(row, req.context, req.params, **extra)
             except MemoryError:
                 self.running.pop(row, None)
                 self.backend.release(row)

@@ -48,7 +48,19 @@ def _params_from(body: dict, stop_ids: tuple[int, ...]) -> SamplingParams:
         frequency_penalty=float(body.get("frequency_penalty", 0.0) or 0.0),
         repetition_penalty=float(body.get("repetition_penalty", 1.0) or 1.0), seed=int(body.get("seed", 0) or 0),
         stop_token_ids=stop_ids, enable_mtp=bool(body.get("enable_mtp", False)),
-        mtp_max_draft_tokens=int(body.get("mtp_max_draft_tokens", 3) or 3))
+        mtp_max_draft_tokens=int(body.get("mtp_max_draft_tokens", 3) or 3),
+        response_format=_response_format(body.get("response_format")))
+
+
+def _response_format(value):
+    """OpenAI ``response_format``: ``{"type": "json_object" | "json_schema" | "text"}`` -> what the engine constrains
+    on (None for free text).  A schema is held to "a JSON object"; its keys are not enforced token by token."""
+    kind = value.get("type") if isinstance(value, dict) else value
+    if kind in (None, "", "text"):
+        return None
+    if kind not in ("json_object", "json_schema"):
+        raise ValueError(f"unsupported response_format type {kind!r}")
+    return {"type": kind}
 
 
 class _Stream:
@@ -180,7 +192,10 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
         ids = lm.tokenizer.encode(prompt)
         if not ids:
             return None, error_response(400, "invalid_request", "empty prompt")
-        params = _params_from(body, tuple(lm.tokenizer.stop_ids))
+        try:
+            params = _params_from(body, tuple(lm.tokenizer.stop_ids))
+        except (TypeError, ValueError) as exc:
+            return None, error_response(400, "invalid_request", str(exc))
         try:
             req, events = await asyncio.get_running_loop().run_in_executor(
                 None, lambda: service.submit(lm, ids, params, priority=int(body.get("priority", 0) or 0),

@@ -56,7 +56,8 @@ class StdioTransport:
             s = params.get("sampling") or {}
             sp = SamplingParams(max_tokens=int(s.get("max_new_tokens", 256)), temperature=float(s.get("temperature", 0.0)),
                                 top_p=float(s.get("top_p", 1.0)), top_k=int(s.get("top_k", 0)), seed=int(s.get("seed", 0)),
-                                stop_token_ids=tuple(lm.tokenizer.stop_ids), enable_mtp=bool(s.get("enable_mtp", False)))
+                                stop_token_ids=tuple(lm.tokenizer.stop_ids), enable_mtp=bool(s.get("enable_mtp", False)),
+                                response_format=params.get("response_format") or None)
             ids = self._prompt_ids(lm, params)
             t0 = time.monotonic()
             req, events = self.service.submit(lm, ids, sp, priority=int(params.get("priority", 0) or 0),

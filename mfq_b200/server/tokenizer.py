@@ -27,6 +27,11 @@ class ByteTokenizer:
         text = data.decode("utf-8", errors="ignore")
         return text + "?" * sum(1 for i in ids if i >= 259)
 
+    def token_bytes(self, vocab_size: int | None = None) -> list[bytes]:
+        """Bytes each token id adds to the text (empty for specials and unused ids); for token constraints."""
+        n = vocab_size or self.vocab_size
+        return [bytes([i - 3]) if 3 <= i < 259 else b"" for i in range(n)]
+
     def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True) -> str:
         parts = [f"<|{m['role']}|>\n{_content_text(m.get('content'))}\n" for m in messages]
         if add_generation_prompt:
@@ -52,6 +57,32 @@ class HfTokenizer:
     def decode(self, ids) -> str:
         return self.tk.decode(list(ids), skip_special_tokens=True)
 
+    def token_bytes(self, vocab_size: int | None = None) -> list[bytes]:
+        """Bytes each token id adds to the text; empty for special / added control tokens and ids past the vocabulary.
+        Byte-level BPE vocabularies are mapped back through the GPT-2 byte alphabet; sentencepiece-style ones through
+        the ``\u2581`` space marker and ``<0xNN>`` byte tokens; a piece that cannot be recovered exactly becomes 0xFF
+        placeholders (legal inside strings only)."""
+        n = vocab_size or self.vocab_size
+        spec = json.loads(self.tk.to_str())
+        special = {t["id"] for t in spec.get("added_tokens", []) if t.get("special")}
+        byte_level = "ByteLevel" in json.dumps(spec.get("decoder") or {}) or "ByteLevel" in json.dumps(spec.get("pre_tokenizer") or {})
+        alphabet = _gpt2_byte_alphabet() if byte_level else None
+        out = []
+        for i in range(n):
+            piece = self.tk.id_to_token(i) if i not in special else None
+            if piece is None:
+                out.append(b"")
+            elif alphabet is not None:
+                try:
+                    out.append(bytes(alphabet[ch] for ch in piece))
+                except KeyError:  # an added plain-text token
+                    out.append(piece.encode("utf-8"))
+            elif len(piece) == 6 and piece.startswith("<0x") and piece.endswith(">"):
+                out.append(bytes([int(piece[3:5], 16)]))
+            else:
+                out.append(piece.replace("\u2581", " ").encode("utf-8"))
+        return out
+
     def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True) -> str:
         if self.chat_template:
             import jinja2
@@ -62,6 +93,19 @@ class HfTokenizer:
     @property
     def stop_ids(self) -> tuple[int, ...]:
         return (self.eos_id,) if self.eos_id is not None else ()
+
+
+def _gpt2_byte_alphabet() -> dict[str, int]:
+    """Printable stand-in character -> byte, as byte-level BPE vocabularies spell their tokens."""
+    keep = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
+    table, extra = {}, 0
+    for b in range(256):
+        if b in keep:
+            table[chr(b)] = b
+        else:
+            table[chr(256 + extra)] = b
+            extra += 1
+    return table
 
 
 def _content_text(content) -> str:
