@@ -158,9 +158,16 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
     from .engine.llm_engine import LLMEngine
     from .models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
     from .server.tokenizer import tokenizer_from_assets
-    with F.open_mfq(path) as store:
-        assets = store.assets()
-        raw = json.loads(assets["model_config.json"])
+    import contextlib
+    if Path(path).is_dir():  # a Hugging Face directory served directly: float tensors, transcoded to FP8 on load
+        raw, hf_tensors, assets = read_hf_directory(path)
+        opened = contextlib.nullcontext(hf_tensors)
+    else:
+        opened = F.open_mfq(path)
+    with opened as store:
+        if not isinstance(store, dict):
+            assets = store.assets()
+            raw = json.loads(assets["model_config.json"])
         if yarn_context_extension and yarn_context_extension > 1.0:
             trained = int((raw.get("rope_scaling") or {}).get("original_max_position") or raw.get("max_position") or 8192)
             raw["rope_scaling"] = dict(raw.get("rope_scaling") or {}, factor=float(yarn_context_extension), original_max_position=trained)
