@@ -491,7 +491,7 @@ def build_parser() -> argparse.ArgumentParser:
     ci.set_defaults(fn=_cmd_calibrate)
 
     dg = sub.add_parser("diagnose", help="self-checks: formats anywhere, kernels and the engine on a GPU box")
-    dg.add_argument("--check", action="append", help="run only this check (repeatable): nint, fp8-block, container, fp8-gemm, attention, engine")
+    dg.add_argument("--check", action="append", help="run only this check (repeatable): nint, fp8-block, container, tp-linear, ep-moe, continuous-batching, json-constraint, fp8-gemm, attention, engine")
     from . import diagnostics as _diag
     dg.set_defaults(fn=_diag.main)
     i = sub.add_parser("inspect", help="summarise an .mfq container")

@@ -97,7 +97,100 @@ def check_engine_greedy() -> dict:
     return {"graph_equals_eager": bool(torch.equal(graph, eager)), "ok": bool(torch.equal(graph, eager))}
 
 
-CPU_CHECKS = {"nint": check_nint_roundtrip, "fp8-block": check_fp8_block_roundtrip}
+def _prefill_logits(model, prompt: torch.Tensor) -> torch.Tensor:
+    from .engine.llm_engine import LLMEngine
+    from .models.llama import StepBuffers
+    eng = LLMEngine(model, max_batch=1, max_seq_len=96, device="cpu")
+    n = prompt.numel()
+    eng.cache.assign(0, 7, n)
+    step = StepBuffers(input_ids=prompt.to(torch.int32), positions=torch.arange(n, dtype=torch.int32),
+                       slots=eng.cache.slots(7, 0, n), cu_seqlens=[0, n])
+    return model.forward(step, eng.cache, prefill=True).float()
+
+
+def _parallel_agreement(build, world: int, prompt: torch.Tensor) -> dict:
+    """Logits of ``world`` in-process ranks (threads, CPU tensors) against the single-rank model."""
+    from .parallel.local_collective import LocalGroup
+    single = _prefill_logits(build(0, 1, None), prompt)
+    ranks = LocalGroup(world).run(lambda rank, coll: _prefill_logits(build(rank, world, coll), prompt))
+    same = all(torch.equal(r, ranks[0]) for r in ranks[1:])
+    cos = float(torch.nn.functional.cosine_similarity(ranks[0].flatten(), single.flatten(), dim=0))
+    return {"world": world, "ranks_identical": same, "cosine_vs_single": round(cos, 4), "ok": same and cos > 0.97}
+
+
+def check_tp_linear() -> dict:
+    """Tensor-parallel dense model (attention heads, FFN columns, vocabulary sharded over 2 and 4 ranks; 4 ranks on 2 KV
+    heads replicate each head twice) against one rank.  Host-validated: ranks are threads over CPU tensors."""
+    from .models.llama import LlamaConfig, LlamaModel, LlamaWeights
+    cfg = LlamaConfig.tiny()
+    prompt = torch.randint(0, cfg.vocab_size, (33,), generator=torch.Generator().manual_seed(33))
+    build = lambda rank, w, coll: LlamaModel(cfg, LlamaWeights.random_init(cfg, "cpu", seed=3, std=0.05, tp_rank=rank, tp_size=w), collective=coll)
+    res = [_parallel_agreement(build, w, prompt) for w in (2, 4)]
+    return {"cases": res, "ok": all(r["ok"] for r in res)}
+
+
+def check_ep_moe() -> dict:
+    """Expert-parallel MoE decoder (experts split over 2 ranks, each adds its experts' partial) against one rank."""
+    from .models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from .models.moe_lm import MoeConfig, init_weights
+    cfg = MoeDecoderConfig.tiny()
+    tensors = {k: v.numpy() for k, v in init_weights(MoeConfig(
+        vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, num_layers=cfg.num_layers, num_heads=cfg.num_heads,
+        num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, num_experts=cfg.num_experts, top_k=cfg.top_k,
+        moe_intermediate=cfg.moe_intermediate, shared_intermediate=cfg.shared_intermediate), seed=4, std=0.05).items()}
+    prompt = torch.randint(0, cfg.vocab_size, (29,), generator=torch.Generator().manual_seed(2))
+    build = lambda rank, w, coll: MoeDecoderModel(cfg, MoeWeights.from_tensors(cfg, tensors, "cpu", rank, w), collective=coll)
+    return _parallel_agreement(build, 2, prompt)
+
+
+def check_continuous_batching(device: str | None = None) -> dict:
+    """Requests that join and leave a running batch must generate what they generate alone (greedy)."""
+    from .engine.llm_engine import LLMEngine
+    from .engine.scheduler import ContinuousBatchScheduler, Request, SamplingParams
+    from .models.llama import LlamaConfig, LlamaModel, LlamaWeights
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    cfg = LlamaConfig.tiny()
+    model = LlamaModel(cfg, LlamaWeights.random_init(cfg, device, seed=5, std=0.05))
+    prompts = [list(range(3 + i, 20 + 4 * i)) for i in range(5)]
+
+    def run(batch):
+        eng = LLMEngine(model, max_batch=4, max_seq_len=128, device=device)
+        sched = ContinuousBatchScheduler(eng, max_queue=16)
+        reqs = [Request(list(p), SamplingParams(max_tokens=5 + 2 * i)) for i, p in enumerate(batch)]
+        for r in reqs:
+            sched.submit(r)
+        for _ in range(400):
+            if not sched.step() and sched.idle:
+                break
+        return [r.generated for r in reqs]
+
+    together = run(prompts)  # five requests through four rows: the fifth joins when a row frees up
+    alone = [run([p])[0][: len(t)] for p, t in zip(prompts, together)]
+    same = sum(a == b[: len(a)] for a, b in zip(alone, together))
+    # on a GPU a batch bucket changes the GEMM tile shape, so a near-tie may flip late in a sequence: first tokens must agree
+    first = all(a[:1] == b[:1] for a, b in zip(alone, together))
+    return {"requests": len(prompts), "identical": same, "first_tokens_agree": first,
+            "ok": first and (same == len(prompts) or device != "cpu")}
+
+
+def check_json_constraint() -> dict:
+    """Grammar automaton + vocabulary mask (native library) on a byte vocabulary."""
+    import json as _json
+    from . import native
+    vocab = native.JsonVocabulary([bytes([b]) for b in range(256)] + [b'{"', b'":', b"true", b"}}"])
+    s = native.JsonState(vocab, need_object=True)
+    doc = b'{"k": [1, 2.5e-1, {"z": null}], "s": "a\\n"}'
+    ok = s.feed(doc) and s.complete and isinstance(_json.loads(doc), dict)
+    t = native.JsonState(vocab, need_object=True)
+    refused = not t.feed(b"[1]") and not t.feed(b'{"a" 1}')
+    t.feed(b'{"a"')
+    mask = t.mask()
+    only_colon = bool(mask[ord(":")]) and not mask[ord("}")] and not mask[256]
+    return {"accepts_valid": bool(ok), "refuses_invalid": refused, "mask": only_colon, "ok": bool(ok and refused and only_colon)}
+
+
+CPU_CHECKS = {"nint": check_nint_roundtrip, "fp8-block": check_fp8_block_roundtrip, "tp-linear": check_tp_linear,
+              "ep-moe": check_ep_moe, "continuous-batching": check_continuous_batching, "json-constraint": check_json_constraint}
 GPU_CHECKS = {"fp8-gemm": check_fp8_gemm, "attention": check_attention, "engine": check_engine_greedy}
 
 

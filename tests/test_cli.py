@@ -60,6 +60,10 @@ def test_diagnose_runs_the_format_checks_on_cpu(capsys):
     report = json.loads(capsys.readouterr().out)
     assert report["ok"] and set(report["checks"]) == {"nint", "container", "fp8-block"}
     assert report["checks"]["nint"]["snr_db"] > 18
+    assert main(["diagnose", "--check", "tp-linear", "--check", "ep-moe", "--check", "continuous-batching", "--check", "json-constraint"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    assert report["ok"] and report["checks"]["ep-moe"]["ranks_identical"] and report["checks"]["continuous-batching"]["identical"] == 5
+    assert [c["world"] for c in report["checks"]["tp-linear"]["cases"]] == [2, 4]
 
 
 def test_wt2_reference_and_eval_against_it(tmp_path, capsys):
