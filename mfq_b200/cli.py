@@ -430,6 +430,20 @@ def _cmd_bench_model(args) -> int:
     return 0
 
 
+def _cmd_config(args) -> int:
+    """The effective runtime configuration and the table of ``MFQ_*`` variables."""
+    from .config import RuntimeConfig
+    cfg = RuntimeConfig.from_env()
+    rows = cfg.describe()
+    if args.json:
+        print(json.dumps(rows, indent=1))
+        return 0
+    for r in rows:
+        mark = "" if r["value"] == r["default"] else "   (set)"
+        print(f"{r['variable']:<22} = {r['value']!s:<10} default {r['default']!s:<8}{mark}\n    {r['what']}")
+    return 0
+
+
 def _cmd_bench(args) -> int:
     os.execv(sys.executable, [sys.executable, str(Path(__file__).resolve().parents[1] / "bench.py"), *args.rest])
 
@@ -572,6 +586,9 @@ def build_parser() -> argparse.ArgumentParser:
     bm.add_argument("--html", help="write a self-contained HTML report here")
     bm.add_argument("--render", help="render an existing JSON report instead of running")
     bm.set_defaults(fn=_cmd_bench_model)
+    cf = sub.add_parser("config", help="effective runtime configuration and the MFQ_* environment variables")
+    cf.add_argument("--json", action="store_true")
+    cf.set_defaults(fn=_cmd_config)
     pf = sub.add_parser("profile", help="per-op time split of a prefill and a few eager decode steps")
     pf.add_argument("--model", required=True)
     pf.add_argument("--prompt-tokens", type=int, default=128)

@@ -24,7 +24,9 @@ from ..utils.profiler import scope
 from .kv_cache import PAGE_SIZE, PagedKVCache
 
 BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
-_PROFILE_DECODE = __import__("os").environ.get("MFQ_PROFILE_DECODE", "0") == "1"  # one stderr line per decode call
+from ..config import current as _config, trace
+
+_PROFILE_DECODE = _config().profile_decode  # one stderr line per decode call
 
 
 def bucket_for(n: int) -> int:
@@ -45,11 +47,13 @@ class GenerationResult:
 
 class LLMEngine:
     def __init__(self, model: LlamaModel, *, max_batch: int = 64, max_seq_len: int = 8192, num_pages: int | None = None,
-                 device=None, use_graphs: bool = True, mtp_draft_tokens: int = 0, prefill_chunk: int = 8192,
+                 device=None, use_graphs: bool | None = None, mtp_draft_tokens: int = 0, prefill_chunk: int | None = None,
                  prefix_cache=None, prefix_salt: str = "") -> None:
         """``mtp_draft_tokens`` (K, 0 = off): with a model that carries an MTP head, greedy rows decode by
         draft/verify cycles that confirm between 1 and K+1 tokens each (:meth:`mtp_step`)."""
         self.model = model
+        use_graphs = _config().cuda_graphs if use_graphs is None else use_graphs
+        prefill_chunk = _config().prefill_chunk if prefill_chunk is None else prefill_chunk
         self.prefill_chunk = prefill_chunk  # prompts longer than this are prefilled in chunks that attend to the cached past
         # content-addressed KV blocks (mfq_b200.native.PrefixCache): a prompt whose leading 256-token blocks are cached
         # gets their pages restored instead of recomputed.  `prefix_salt` must name the model (weights + KV format).
@@ -462,6 +466,8 @@ class LLMEngine:
             with torch.cuda.graph(g):
                 self._decode_body(b, stochastic, constrained)
             self.launches_per_step[b] = ops.launch_count() - before
+            trace("graph", "captured", rows=b, stochastic=int(stochastic), constrained=int(constrained),
+                  launches=self.launches_per_step[b], graphs=len(self.graphs) + 1)
             # warm-up and capture ran real steps: roll the sequence state back (the KV rows they wrote get rewritten)
             self.seq_lens.copy_(saved[0])
             self.sampled.copy_(saved[1])

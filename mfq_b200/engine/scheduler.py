@@ -26,6 +26,8 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, Protocol
 
+from ..config import trace
+
 INITIAL_NEW_TOKEN_RATIO = 0.7
 MIN_NEW_TOKEN_RATIO = 0.098
 RATIO_DECAY_STEPS = 600
@@ -181,12 +183,14 @@ class ContinuousBatchScheduler:
     def _finish(self, req: Request, reason: str) -> None:
         req.finished, req.finish_reason = True, reason
         self.stats.completed += 1
+        trace("scheduler", "finish", request=req.id, reason=reason, generated=len(req.generated), retractions=req.retractions)
         self._emit(req, Event("completed", req.id, finish_reason=reason, metrics=self._metrics(req)))
 
     def _fail(self, req: Request, exc: Exception) -> None:
         req.finished, req.error = True, exc
         req.finish_reason = getattr(exc, "code", "error")
         self.stats.failed += 1
+        trace("scheduler", "fail", request=req.id, code=req.finish_reason)
         self._emit(req, Event("failed", req.id, error_code=req.finish_reason, metrics=self._metrics(req)))
 
     def _snapshot(self, req: Request) -> None:
@@ -256,6 +260,7 @@ class ContinuousBatchScheduler:
         victim.row = -1
         victim.retractions += 1
         self.stats.retractions += 1
+        trace("scheduler", "retract", request=victim.id, row=row, generated=len(victim.generated))
         self.new_token_ratio = min(INITIAL_NEW_TOKEN_RATIO, self.new_token_ratio + 0.1)  # be less optimistic for a while
         self._emit(victim, Event("retracted", victim.id))
         self.waiting.insert(0, victim)
@@ -277,6 +282,8 @@ class ContinuousBatchScheduler:
             req.row, req.start_time = row, self.clock()
             self.running[row] = req
             self.stats.admitted += 1
+            trace("scheduler", "admit", request=req.id, row=row, context=len(req.context), waiting=len(self.waiting),
+                  running=len(self.running), replay=int(bool(req.generated)))
             try:
                 extra = {}
                 if req.session is not None and hasattr(self.backend, "save_session"):

@@ -18,7 +18,8 @@ GEMV_MAX_ROWS = 16  # up to this many rows the weight-streaming kernel (fp8_gemv
 def gemv_enabled() -> bool:
     """``MFQ_GEMV=0`` in the environment sends every shape through the tcgen05 GEMM (A/B measurements)."""
     import os
-    return os.environ.get("MFQ_GEMV", "1") != "0"
+    from ..config import current
+    return current().gemv
 
 
 def _token_tile(m: int) -> int:

@@ -123,7 +123,13 @@ class Profiler:
         self._items.clear()
 
 
-PROFILER = Profiler.from_env()
+def _from_config() -> Profiler:
+    from ..config import current
+    cfg = current()
+    return Profiler(cfg.profile, cfg.profile_filter)
+
+
+PROFILER = _from_config()
 
 
 def scope(name: str, device=None):
