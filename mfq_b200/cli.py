@@ -322,6 +322,8 @@ def _cmd_serve(args) -> int:
         ctx.finish()
         return 0 if why == "shutdown" else 1
     service = ModelService(max_instances=args.max_runtime_instances, max_queue=args.max_queue, queue_timeout=args.queue_timeout)
+    if args.worker_process and ctx is None:
+        return _serve_with_worker(args, service, device)
 
     def loader(name_or_path):
         path = name_or_path if Path(name_or_path).exists() else args.model
@@ -368,6 +370,31 @@ def _cmd_serve(args) -> int:
             service.shutdown()
             engine.shutdown_followers()
             ctx.finish()
+    return 0
+
+
+def _serve_with_worker(args, service, device) -> int:
+    """``mfq serve --worker-process``: the engine lives in a child ``mfq runtime``; this process keeps HTTP, the
+    tokenizer and the watch over the child (a dead child fails its requests at once and is restarted on demand)."""
+    import uvicorn
+    from . import formats as F
+    from .server import create_app
+    from .server.tokenizer import tokenizer_from_assets
+    with F.open_mfq(args.model) as store:
+        assets = store.assets()
+    vocab = int(json.loads(assets["model_config.json"]).get("vocab_size", 0))
+    command = [sys.executable, "-m", "mfq_b200.cli", "runtime", "--model", args.model, "--device", device,
+               "--continuous-batching", str(args.continuous_batching), "--ctx-size", str(args.ctx_size),
+               "--max-queue", str(args.max_queue), "--queue-timeout", str(args.queue_timeout),
+               *(["--native-4bit"] if args.native_4bit else []),
+               *(["--yarn-context-extension", str(args.yarn_context_extension)] if args.yarn_context_extension else [])]
+    service.add_worker_model(args.model_name or Path(args.model).stem, command, tokenizer_from_assets(assets, vocab),
+                             capacity=args.continuous_batching)
+    key = os.environ.get(args.api_key_env) if args.api_key_env else None
+    try:
+        uvicorn.run(create_app(service, api_key=key), host=args.host, port=args.port, access_log=args.access_log)
+    finally:
+        service.shutdown()
     return 0
 
 
@@ -553,6 +580,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--worker-process", action="store_true",
+                   help="run the engine in a child process that is watched and restarted on demand (the server survives a dead engine)")
     s.add_argument("--tensor-parallel", type=int, default=1,
                    help="ranks (one process per GPU) that share every layer: attention heads, FFN columns and experts are sharded")
     s.add_argument("--yarn-context-extension", type=float, default=None,

@@ -53,6 +53,19 @@ class ModelService:
         self.models[name] = lm
         return lm
 
+    def add_worker_model(self, name: str, command: list[str], tokenizer, *, capacity: int = 32, env: dict | None = None,
+                         **worker_kw) -> LoadedModel:
+        """A model that runs in a child runtime process (see ``server/worker.py``): the child owns the engine, this
+        process keeps the tokenizer, the queue limits and the watch over the child."""
+        from .worker import WorkerScheduler
+        while len(self.models) >= self.max_instances and name not in self.models:
+            victim, _ = next(iter(self.models.items()))
+            self.unload(victim)
+        sched = WorkerScheduler(command, capacity=capacity, max_queue=self.max_queue, env=env, **worker_kw)
+        lm = LoadedModel(name, None, tokenizer, sched, request_capacity=capacity, meta={"worker": True})
+        self.models[name] = lm
+        return lm
+
     def load(self, name: str) -> LoadedModel:
         if name in self.models:
             self.models.move_to_end(name)
@@ -66,6 +79,8 @@ class ModelService:
         lm = self.models.pop(name, None)
         if lm is None:
             return False
+        if hasattr(lm.scheduler, "shutdown"):  # a worker process: end the child with the model
+            lm.scheduler.shutdown()
         self.metrics.drop_instance(lm.name, lm.instance)
         return True
 
@@ -128,6 +143,9 @@ class ModelService:
     def shutdown(self) -> None:
         self._stop.set()
         self._thread.join(timeout=5)
+        for lm in self.models.values():
+            if hasattr(lm.scheduler, "shutdown"):
+                lm.scheduler.shutdown()
 
     # ---- observation ---------------------------------------------------------------------------------------------
     def record_completion(self, model: LoadedModel, req: Request, result: str) -> None:
@@ -145,7 +163,8 @@ class ModelService:
         out = []
         for lm in self.models.values():
             s = lm.scheduler
-            out.append({"model": lm.name, "instance": lm.instance, "healthy": s.healthy, "running": len(s.running),
+            extra = {"worker_restarts": s.restarts, "worker_failures": s.failures} if hasattr(s, "restarts") else {}
+            out.append({**extra, "model": lm.name, "instance": lm.instance, "healthy": s.healthy, "running": len(s.running),
                         "queued": len(s.waiting), "batch_capacity": lm.request_capacity, "stats": vars(s.stats),
                         "kv_free_tokens": lm.engine.free_tokens() if hasattr(lm.engine, "free_tokens") else None})
         return {"instances": out}

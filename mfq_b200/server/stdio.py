@@ -12,6 +12,10 @@ A driver that speaks to the reference's ``mfq-runtime --transport stdio`` (its b
     <- {"v": 1, "id": "r1", "type": "done"}
     -> {"op": "cancel", "params": {"target": "r1"}}, {"op": "status"}, {"op": "shutdown"}
 
+``input.token_ids`` gives an exact, already tokenized prompt; ``"stream_tokens": true`` adds one
+``{"type": "token", "data": {"id": N}}`` frame per generated token (stop tokens included), which is what a front-end
+process that owns the tokenizer and proxies requests to worker processes consumes (``server/worker.py``).
+
 ``benchmark_prompt_tokens`` replaces the prompt by exactly that many synthetic token ids (what benchmarks use to pin the
 prompt length).  Requests run concurrently: every ``generate`` gets a thread that forwards its events; one lock
 serialises the writes, so frames never interleave inside a line.
@@ -42,6 +46,8 @@ class StdioTransport:
     # ---- operations ------------------------------------------------------------------------------------------------
     def _prompt_ids(self, lm, params: dict) -> list[int]:
         inp = params.get("input") or {}
+        if inp.get("token_ids"):  # an exact prompt, already tokenized (a front end that owns the tokenizer)
+            return [int(t) for t in inp["token_ids"]]
         n = int(inp.get("benchmark_prompt_tokens") or 0)
         if n > 0:
             vocab = getattr(lm.tokenizer, "vocab_size", 256)
@@ -54,9 +60,12 @@ class StdioTransport:
         try:
             lm = self.service.resolve(params.get("model"))
             s = params.get("sampling") or {}
+            stops = tuple(int(t) for t in s["stop_token_ids"]) if "stop_token_ids" in s else tuple(lm.tokenizer.stop_ids)
             sp = SamplingParams(max_tokens=int(s.get("max_new_tokens", 256)), temperature=float(s.get("temperature", 0.0)),
                                 top_p=float(s.get("top_p", 1.0)), top_k=int(s.get("top_k", 0)), seed=int(s.get("seed", 0)),
-                                stop_token_ids=tuple(lm.tokenizer.stop_ids), enable_mtp=bool(s.get("enable_mtp", False)),
+                                presence_penalty=float(s.get("presence_penalty", 0.0)), frequency_penalty=float(s.get("frequency_penalty", 0.0)),
+                                repetition_penalty=float(s.get("repetition_penalty", 1.0)),
+                                stop_token_ids=stops, enable_mtp=bool(s.get("enable_mtp", False)),
                                 response_format=params.get("response_format") or None)
             ids = self._prompt_ids(lm, params)
             t0 = time.monotonic()
@@ -75,6 +84,8 @@ class StdioTransport:
                 continue
             if ev.kind == "token":
                 first = first or time.monotonic()
+                if params.get("stream_tokens"):  # raw ids, stop tokens included: the front end decodes
+                    self.send({"id": rid, "type": "token", "data": {"id": int(ev.token)}})
                 if ev.token in sp.stop_token_ids:
                     continue
                 out.append(ev.token)
