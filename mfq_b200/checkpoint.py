@@ -168,6 +168,8 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
         if not isinstance(store, dict):
             assets = store.assets()
             raw = json.loads(assets["model_config.json"])
+            from .formats.legacy_names import canonical_view
+            store = canonical_view(store)  # old artifacts kept source tensor paths
         if yarn_context_extension and yarn_context_extension > 1.0:
             trained = int((raw.get("rope_scaling") or {}).get("original_max_position") or raw.get("max_position") or 8192)
             raw["rope_scaling"] = dict(raw.get("rope_scaling") or {}, factor=float(yarn_context_extension), original_max_position=trained)
