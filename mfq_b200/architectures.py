@@ -51,21 +51,33 @@ LAYER_SUFFIX = {
 _EXPERT_RE = re.compile(r"^(?:mlp|block_sparse_moe)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj|w1|w2|w3)\.weight$")
 _EXPERT_PROJ = {"gate_proj": "gate", "w1": "gate", "up_proj": "up", "w3": "up", "down_proj": "down", "w2": "down"}
 _LAYER_RE = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
+# multi-token-prediction head as Qwen3-Next style checkpoints name it
+PREDICTOR_TOP = {
+    "mtp.fc.weight": "predictor.fusion.weight",
+    "mtp.pre_fc_norm_embedding.weight": "predictor.embedding_norm.weight",
+    "mtp.pre_fc_norm_hidden.weight": "predictor.hidden_norm.weight",
+    "mtp.norm.weight": "predictor.output_norm.weight",
+}
+_MTP_LAYER_RE = re.compile(r"^mtp\.layers\.(\d+)\.(.+)$")
 
 
 def canonical_name(hf_name: str) -> tuple[str, int | None] | None:
     """``hf_name`` -> (canonical name, expert index or None); None for tensors the runtime does not use."""
     if hf_name in TOP_LEVEL:
         return TOP_LEVEL[hf_name], None
-    m = _LAYER_RE.match(hf_name)
+    if hf_name in PREDICTOR_TOP:
+        return PREDICTOR_TOP[hf_name], None
+    m, root = _LAYER_RE.match(hf_name), "model"
+    if not m:
+        m, root = _MTP_LAYER_RE.match(hf_name), "predictor"
     if not m:
         return None
     layer, rest = int(m[1]), m[2]
     if rest in LAYER_SUFFIX:
-        return f"model.block.{layer}.{LAYER_SUFFIX[rest]}", None
+        return f"{root}.block.{layer}.{LAYER_SUFFIX[rest]}", None
     e = _EXPERT_RE.match(rest)
     if e:
-        return f"model.block.{layer}.mlp.experts.{_EXPERT_PROJ[e[2]]}.weight", int(e[1])
+        return f"{root}.block.{layer}.mlp.experts.{_EXPERT_PROJ[e[2]]}.weight", int(e[1])
     return None
 
 

@@ -151,10 +151,12 @@ def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict
 def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots: int | None = None, max_batch: int = 64,
                 max_seq_len: int = 8192, tp_rank: int = 0, tp_size: int = 1,
                 collective=None, use_graphs: bool = True, kv_budget_bytes: int | None = None,
-                yarn_context_extension: float | None = None):
+                yarn_context_extension: float | None = None, mtp_draft_tokens: int = 0, mtp_adaptive: bool = False):
     """``.mfq`` -> (engine, tokenizer, config).  ``kv_budget_bytes`` caps the paged KV pool (see ``engine/kv_budget.py``);
     on a GPU it defaults to 90 % of the memory that is free once the weights are resident.  ``yarn_context_extension``
-    (> 1) runs the model on that multiple of its trained context with YaRN-scaled rotary frequencies."""
+    (> 1) runs the model on that multiple of its trained context with YaRN-scaled rotary frequencies.
+    ``mtp_draft_tokens`` (K > 0, only with a checkpoint that carries a ``predictor.*`` head): greedy rows decode by
+    draft/verify cycles; ``mtp_adaptive`` parks the cycles while they are slower than plain decoding."""
     from .engine.llm_engine import LLMEngine
     from .models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
     from .server.tokenizer import tokenizer_from_assets
@@ -193,10 +195,13 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
         kv_budget_bytes = device_budget(device)
     if kv_budget_bytes is not None:
         from .engine.kv_budget import plan
-        num_pages = plan(budget_bytes=kv_budget_bytes, layers=cfg.num_layers, kv_heads=model.hk, head_dim=cfg.head_dim,
+        has_head = getattr(weights, "mtp", None) is not None
+        num_pages = plan(budget_bytes=kv_budget_bytes, layers=cfg.num_layers + int(has_head), kv_heads=model.hk, head_dim=cfg.head_dim,
                          max_batch=max_batch, max_seq_len=max_seq_len).num_pages
     engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, num_pages=num_pages,
-                       use_graphs=use_graphs and expert_slots is None)
+                       use_graphs=use_graphs and expert_slots is None,
+                       mtp_draft_tokens=mtp_draft_tokens if getattr(weights, "mtp", None) is not None else 0,
+                       mtp_adaptive=mtp_adaptive)
     tokenizer = tokenizer_from_assets(assets, cfg.vocab_size)
     # structured output needs the vocabulary's byte strings; resolved on the first request that asks for it
     engine.set_token_bytes(lambda: tokenizer.token_bytes(cfg.vocab_size), tokenizer.stop_ids)

@@ -330,7 +330,8 @@ def _cmd_serve(args) -> int:
         engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size, **tp,
                                         native_4bit=args.native_4bit, expert_slots=args.moe_gpu_cache_slots,
                                         kv_budget_bytes=int(args.kv_budget_gb * (1 << 30)) if args.kv_budget_gb else None,
-                                        yarn_context_extension=args.yarn_context_extension)
+                                        yarn_context_extension=args.yarn_context_extension,
+                                        mtp_draft_tokens=args.mtp_draft_tokens, mtp_adaptive=args.mtp_adaptive)
         if args.session_cache_gb > 0:
             from .engine.session_cache import SessionSnapshotCache
             engine.session_cache = SessionSnapshotCache(int(args.session_cache_gb * (1 << 30)))
@@ -580,6 +581,10 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--mtp-draft-tokens", type=int, default=0,
+                   help="draft this many tokens per cycle with the checkpoint's multi-token-prediction head (0: off)")
+    s.add_argument("--mtp-adaptive", action="store_true",
+                   help="measure cycles against plain decoding and park them while they lose (the head stays primed)")
     s.add_argument("--worker-process", action="store_true",
                    help="run the engine in a child process that is watched and restarted on demand (the server survives a dead engine)")
     s.add_argument("--tensor-parallel", type=int, default=1,

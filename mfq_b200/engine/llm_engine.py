@@ -14,6 +14,7 @@ The class also implements the backend protocol of :class:`~mfq_b200.engine.sched
 from __future__ import annotations
 
 import ctypes as C
+import time
 from dataclasses import dataclass
 
 import torch
@@ -48,10 +49,15 @@ class GenerationResult:
 class LLMEngine:
     def __init__(self, model: LlamaModel, *, max_batch: int = 64, max_seq_len: int = 8192, num_pages: int | None = None,
                  device=None, use_graphs: bool | None = None, mtp_draft_tokens: int = 0, prefill_chunk: int | None = None,
-                 prefix_cache=None, prefix_salt: str = "") -> None:
+                 prefix_cache=None, prefix_salt: str = "", mtp_adaptive: bool = False) -> None:
         """``mtp_draft_tokens`` (K, 0 = off): with a model that carries an MTP head, greedy rows decode by
         draft/verify cycles that confirm between 1 and K+1 tokens each (:meth:`mtp_step`)."""
         self.model = model
+        # adaptive speculation: cycles only while they beat plain decoding (see engine/mtp_policy.ParkingController)
+        self.mtp_controller = None
+        if mtp_adaptive and mtp_draft_tokens:
+            from .mtp_policy import ParkingController
+            self.mtp_controller = ParkingController()
         use_graphs = _config().cuda_graphs if use_graphs is None else use_graphs
         prefill_chunk = _config().prefill_chunk if prefill_chunk is None else prefill_chunk
         self.prefill_chunk = prefill_chunk  # prompts longer than this are prefilled in chunks that attend to the cached past
@@ -419,7 +425,7 @@ class LLMEngine:
         slots.copy_(torch.where(act, pages * self.cache.page_size + pos % self.cache.page_size, torch.full_like(pos, -1)))
         seq_lens.copy_(torch.where(act, pos + 1, pos))
 
-    def _decode_body(self, b: int, stochastic: bool = False, constrained: bool = False) -> None:
+    def _decode_body(self, b: int, stochastic: bool = False, constrained: bool = False, keep_head: bool = False) -> None:
         dev = self.device
         self._advance(self.sampled[:b], self.input_ids[:b], self.positions[:b], self.seq_lens[:b], self.slots[:b],
                       self.cache.block_table[:b], self.active[:b])
@@ -431,10 +437,21 @@ class LLMEngine:
                            block_table=self.cache.block_table[:b], seq_lens=self.seq_lens[:b], state_slots=state_slots)
         if dev.type == "cuda":
             self.model.attn_splits = self._splits_now(b)
-        logits = self.model.forward(step, self.cache, prefill=False, gather_logits=False)
+        if keep_head:
+            logits, hidden = self.model.forward(step, self.cache, prefill=False, gather_logits=False, return_hidden=True)
+        else:
+            logits = self.model.forward(step, self.cache, prefill=False, gather_logits=False)
         if constrained:
             logits += self._bias_rows(logits, b)
         self._sample(logits, b, stochastic)
+        if keep_head:
+            # parked speculation: the head still reads every position (its hidden state paired with the token that
+            # followed), so its KV rows stay complete and draft 1 is ready when cycles resume
+            mstep = StepBuffers(input_ids=self.sampled[:b], positions=self.positions[:b], slots=self.slots[:b],
+                                block_table=self.cache.block_table[:b], seq_lens=self.seq_lens[:b])
+            mlogits, _ = self.model.mtp_forward(mstep, self.cache, hidden, prefill=False)
+            self.model.sample_greedy(mlogits, out=self.c_tok[:b])
+            self.draft[:b, 0].copy_(torch.where(self.active[:b] > 0, self.c_tok[:b], self.draft[:b, 0]))  # masked rows keep theirs
 
     def _splits_now(self, b: int) -> int:
         """Attention KV splits for the current contexts (host mirror of the row lengths; a graph is kept per value)."""
@@ -442,35 +459,38 @@ class LLMEngine:
         longest = max(self.row_len.values(), default=self.max_seq_len)
         return attn_splits_for(b, self.model.hk, min(self.max_seq_len, longest))
 
-    def decode_step(self, b: int, stochastic: bool = False, constrained: bool = False) -> None:
+    def decode_step(self, b: int, stochastic: bool = False, constrained: bool = False, keep_head: bool = False) -> None:
         """Advance the active rows among ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device).
         ``constrained``: add the rows' token-constraint bias to the logits before sampling (a graph variant of its own)."""
         self._bind_state()
         if not self.use_graphs:
-            self._decode_body(b, stochastic, constrained)
+            self._decode_body(b, stochastic, constrained, keep_head)
             return
-        key = (b, stochastic, self._splits_now(b)) + ((True,) if constrained else ())
+        key = (b, stochastic, self._splits_now(b)) + ((True,) if constrained else ()) + (("head",) if keep_head else ())
         g = self.graphs.get(key)
         if g is None:
             ops.Workspace.get(self.device)
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream())
             saved = (self.seq_lens.clone(), self.sampled.clone())
+            saved_draft = self.draft.clone() if keep_head else None
             saved_rec = (self.rec_state.conv.clone(), self.rec_state.state.clone()) if self.rec_state is not None else None
             with torch.cuda.stream(side):
                 for _ in range(2):
-                    self._decode_body(b, stochastic, constrained)
+                    self._decode_body(b, stochastic, constrained, keep_head)
             torch.cuda.current_stream().wait_stream(side)
             g = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             with torch.cuda.graph(g):
-                self._decode_body(b, stochastic, constrained)
+                self._decode_body(b, stochastic, constrained, keep_head)
             self.launches_per_step[b] = ops.launch_count() - before
             trace("graph", "captured", rows=b, stochastic=int(stochastic), constrained=int(constrained),
                   launches=self.launches_per_step[b], graphs=len(self.graphs) + 1)
             # warm-up and capture ran real steps: roll the sequence state back (the KV rows they wrote get rewritten)
             self.seq_lens.copy_(saved[0])
             self.sampled.copy_(saved[1])
+            if saved_draft is not None:
+                self.draft.copy_(saved_draft)
             if saved_rec is not None:  # the recurrent state cannot be "rewritten later" like KV rows: put it back
                 self.rec_state.conv.copy_(saved_rec[0])
                 self.rec_state.state.copy_(saved_rec[1])
@@ -586,6 +606,16 @@ class LLMEngine:
         if constrained:
             self._write_bias(range(b))
         if self.mtp_k and not constrained and not any(self.row_stochastic.get(r, False) for r in rows):
+            ctl = self.mtp_controller
+            mode = ctl.mode() if ctl is not None else "mtp"
+            t0 = time.perf_counter()
+            if mode == "plain":  # parked: one token per row, the head kept primed
+                self.decode_step(b, False, False, keep_head=True)
+                toks = self.sampled[:b].cpu()
+                for r in rows:
+                    self.row_len[r] += 1
+                ctl.observe("plain", len(rows), len(rows), (time.perf_counter() - t0) * 1e3)
+                return {r: [int(toks[r])] for r in rows}
             self.mtp_step(b)
             toks, counts = self.out_tokens[:b].cpu(), self.n_out[:b].cpu()
             out = {}
@@ -593,6 +623,8 @@ class LLMEngine:
                 n = int(counts[r])
                 self.row_len[r] += n
                 out[r] = [int(t) for t in toks[r, :n]]
+            if ctl is not None:
+                ctl.observe("mtp", sum(len(v) for v in out.values()), len(rows), (time.perf_counter() - t0) * 1e3)
             return out
         self.decode_step(b, any(self.row_stochastic.get(r, False) for r in rows), constrained)
         toks = self.sampled[:b].cpu()

@@ -107,3 +107,65 @@ class DepthController:
     def state(self) -> dict:
         return {"acceptance": [round(a, 3) for a in self.acceptance], "cycle_ms": self.cycle_ms, "parked": self.parked,
                 "expected_tokens": [round(self.expected_tokens(d), 3) for d in range(self.max_depth + 1)]}
+
+
+class ParkingController:
+    """Run draft/verify cycles only while they pay: the engine-side reduction of :class:`DepthController` to the two
+    modes one captured graph geometry offers -- cycles at the depth the engine was built with, or plain decode steps
+    that keep the draft head primed ("parked").
+
+    Both modes are measured in tokens per row and millisecond (EMA).  After ``probe`` calls in each mode the controller
+    parks when cycles have been slower than ``exit_margin`` x plain decoding for ``park_after`` calls in a row, re-probes
+    cycles for ``probe`` calls every ``reprobe_every`` parked calls, and resumes when they win again.  Reference:
+    ``cpp_runtime/engine/include/mtp_depth_controller.h`` (adaptive depth with parking)."""
+
+    def __init__(self, *, ema: float = 0.2, exit_margin: float = 1.05, park_after: int = 8, reprobe_every: int = 64,
+                 probe: int = 4) -> None:
+        self.ema, self.exit_margin, self.park_after, self.reprobe_every, self.probe = ema, exit_margin, park_after, reprobe_every, probe
+        self.rate = {"mtp": None, "plain": None}  # tokens per row per ms
+        self.calls = {"mtp": 0, "plain": 0}
+        self.parked = False
+        self.losing = 0
+        self._parked_calls = 0
+        self._probe_left = 0
+
+    def mode(self) -> str:
+        if self.calls["mtp"] < self.probe:
+            return "mtp"
+        if self.calls["plain"] < self.probe:
+            return "plain"
+        if self.parked:
+            if self._probe_left > 0:
+                return "mtp"
+            if self._parked_calls >= self.reprobe_every:
+                self._probe_left = self.probe
+                self._parked_calls = 0
+                return "mtp"
+            return "plain"
+        return "mtp"
+
+    def observe(self, mode: str, tokens: int, rows: int, ms: float) -> None:
+        if rows <= 0 or ms <= 0:
+            return
+        r = tokens / rows / ms
+        old = self.rate[mode]
+        self.rate[mode] = r if old is None else old + self.ema * (r - old)
+        self.calls[mode] += 1
+        if self.parked:
+            if mode == "plain":
+                self._parked_calls += 1
+            else:
+                self._probe_left -= 1
+        if self.rate["mtp"] is None or self.rate["plain"] is None or self.calls["plain"] < self.probe:
+            return
+        wins = self.rate["mtp"] >= self.rate["plain"] * self.exit_margin
+        if self.parked:
+            if mode == "mtp" and self._probe_left <= 0 and wins:
+                self.parked, self.losing = False, 0
+        elif mode == "mtp":
+            self.losing = 0 if wins else self.losing + 1
+            if self.losing >= self.park_after:
+                self.parked, self._parked_calls, self._probe_left = True, 0, 0
+
+    def state(self) -> dict:
+        return {"parked": self.parked, "rate": dict(self.rate), "calls": dict(self.calls), "losing": self.losing}

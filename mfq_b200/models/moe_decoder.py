@@ -138,11 +138,9 @@ class MoeWeights(LlamaWeights):
                         pass
             return Fp8Linear.from_float(float_builder())
 
-        layers = []
         e_per = cfg.num_experts // w
         e_lo = tp_rank * e_per
-        for i in range(cfg.num_layers):
-            p = f"model.block.{i}."
+        def build_layer(p):
             qkv_names = [p + f"attention.{n}.weight" for n in ("query", "key", "value")]
             layer = MoeLayer(
                 attn_norm=norm(p + "attention.norm.weight"),
@@ -180,10 +178,20 @@ class MoeWeights(LlamaWeights):
                 layer.gate_up = linear([p + "mlp.gate.weight", p + "mlp.up.weight"],
                                        lambda: torch.cat([rows(get(p + "mlp.gate.weight"), i_), rows(get(p + "mlp.up.weight"), i_)], 0))
                 layer.down = linear([p + "mlp.down.weight"], lambda: cols(get(p + "mlp.down.weight"), i_))
-            layers.append(layer)
+            return layer
+
+        layers = [build_layer(f"model.block.{i}.") for i in range(cfg.num_layers)]
         head = rows(get("model.output.weight"), cfg.vocab_size)
-        return cls(get("model.token_embedding.weight").to(torch.bfloat16), layers, norm("model.output_norm.weight"),
-                   Fp8Linear.from_float(head), tp_rank, tp_size)
+        weights = cls(get("model.token_embedding.weight").to(torch.bfloat16), layers, norm("model.output_norm.weight"),
+                      Fp8Linear.from_float(head), tp_rank, tp_size)
+        if "predictor.fusion.weight" in tensors:  # multi-token-prediction head (one block; fusion = [embedding | hidden])
+            from .llama import MtpHead
+            out_norm = "predictor.output_norm.weight"
+            weights.mtp = MtpHead(enorm=norm("predictor.embedding_norm.weight"), hnorm=norm("predictor.hidden_norm.weight"),
+                                  eh_proj=Fp8Linear.from_float(get("predictor.fusion.weight")),
+                                  layer=build_layer("predictor.block.0."),
+                                  final_norm=norm(out_norm) if out_norm in tensors else None)
+        return weights
 
 
 class MoeDecoderModel(LlamaModel):
