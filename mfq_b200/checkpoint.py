@@ -131,7 +131,8 @@ def _quantize_resumable(tensors, store, *, dense, expert_mix, seed, device, prog
 
 
 def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict[str, bytes] | None = None,
-                    arch: str = "mfq_b200_decoder", extra: dict | None = None, shard_bytes: int | None = None):
+                    arch: str = "mfq_b200_decoder", extra: dict | None = None, shard_bytes: int | None = None,
+                    shard_tensors: int | None = None):
     """Write the checkpoint; with ``shard_bytes`` as ``stem-0000i-of-0000N.mfq`` files (returns their paths)."""
     records = {}
     from .formats import model_graph
@@ -142,8 +143,8 @@ def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict
         records[ASSET_PREFIX + k] = v
     records.update(tensors)
     header = F.FileHeader(model_arch=arch, extra={"runtime_assets": sorted(all_assets), **(extra or {})})
-    if shard_bytes:
-        return F.save_sharded(path, header, records, shard_bytes)
+    if shard_bytes or shard_tensors:
+        return F.save_sharded(path, header, records, shard_bytes, shard_tensors)
     F.save(path, header, records)
     return [path]
 

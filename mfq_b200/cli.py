@@ -85,6 +85,13 @@ def _cmd_quantize(args) -> int:
         dense = f"nint{presets.PRESETS[preset]}"
         topo = presets.Topology(int(cfg.get("num_layers", 0)), int(cfg.get("num_heads", 1)), int(cfg.get("num_kv_heads", 1)))
         widths = presets.plan(preset, {n: tuple(t.shape) for n, t in tensors.items()}, topo)
+    if args.recipe:
+        from .quantize.recipe import load_recipe
+        widths = dict(widths or {})
+        widths.update(load_recipe(args.recipe, list(tensors)))
+    if args.target_bpw:
+        widths = dict(widths or {})
+        widths.update(_alphaq_widths(tensors, args.target_bpw))
     imatrix = scheme = None
     if args.imatrix:
         from .calibration.imatrix import load as load_imatrix
@@ -115,8 +122,11 @@ def _cmd_quantize(args) -> int:
                          progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
     extra = {"quantization": {"dense": dense, "preset": args.preset or None, "imatrix": bool(imatrix), "ew_scheme": bool(scheme), "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
                               "random_expert_mix_seed": args.random_expert_mix_seed if args.random_expert_mix else None}}
-    paths = save_checkpoint(out, cfg, q, assets, extra=extra,
-                            shard_bytes=int(args.shard_size_gb * (1 << 30)) if args.shard_size_gb else None)
+    shard_bytes = int(args.shard_size_gb * (1 << 30)) if args.shard_size_gb else None
+    if args.split_max_size:
+        from .quantize.recipe import parse_size
+        shard_bytes = parse_size(args.split_max_size)
+    paths = save_checkpoint(out, cfg, q, assets, extra=extra, shard_bytes=shard_bytes, shard_tensors=args.split_max_tensors or None)
     size = sum(Path(p).stat().st_size for p in paths)
     weights = sum(int(t.size) for t in tensors.values())
     if store is not None:
@@ -124,6 +134,22 @@ def _cmd_quantize(args) -> int:
     print(json.dumps({"output": str(paths[0]), "shards": len(paths), "bytes": size, "weights": weights,
                       "bits_per_weight": round(8 * size / weights, 3), "resumed_tensors": len(store.reused) if store else 0}))
     return 0
+
+
+def _alphaq_widths(tensors, target_bpw: float) -> dict[str, int]:
+    """NINT width per 2-D weight from the AlphaQ allocation (heavier-tailed spectra get more bits) under the bit budget."""
+    from .calibration import alphaq
+    from .quantize import presets
+    stats, sizes = {}, {}
+    for name, t in tensors.items():
+        if t.ndim == 2 and presets.quantizable(name, t.shape):
+            stats[name] = alphaq.weight_statistics(t)
+            sizes[name] = int(t.size)
+    if not stats:
+        return {}
+    cands = {f"nint{b}": b + 0.3 for b in range(2, 9)}  # code bits + group parameters
+    choice = alphaq.allocate(alphaq.importance(stats), sizes, cands, target_bpw * sum(sizes.values()))
+    return {name: int(fam[4:]) for name, fam in choice.items()}
 
 
 def _cmd_calibrate(args) -> int:
@@ -497,8 +523,12 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--random-expert-mix", default="", help="comma separated families per routed expert projection")
     q.add_argument("--random-expert-mix-seed", type=int, default=20260908)
     q.add_argument("--full-precision", action="store_true")
-    q.add_argument("--device", default="cpu")
+    q.add_argument("--device", "--backend", dest="device", default="cpu")
     q.add_argument("--seed", type=int, default=0)
+    q.add_argument("--recipe", help="per-tensor precisions from a GGUF file's tensor table (.gguf) or a JSON rule list")
+    q.add_argument("--target-bpw", type=float, default=0.0, help="AlphaQ allocation of NINT widths over the 2-D weights under this budget")
+    q.add_argument("--split-max-size", help="limit of tensor payload per output shard, N[M|G]")
+    q.add_argument("--split-max-tensors", type=int, default=0, help="limit of tensors per output shard")
     q.add_argument("--dry-run", action="store_true")
     q.add_argument("--resume", action="store_true", help="reuse the validated per-tensor blobs an interrupted run left in <output>.tmp/")
     q.add_argument("--resume-completed", action="store_true", help="exit at once when the output already exists and opens")

@@ -152,17 +152,19 @@ def save(path, header: FileHeader, tensors: Mapping[str, Any]) -> None:
     os.replace(tmp, path)
 
 
-def save_sharded(path, header: FileHeader, tensors: Mapping[str, Any], max_bytes: int) -> list[Path]:
+def save_sharded(path, header: FileHeader, tensors: Mapping[str, Any], max_bytes: int | None,
+                 max_tensors: int | None = None) -> list[Path]:
     """Write ``tensors`` as ``stem-00001-of-0000N.mfq`` files of at most ``max_bytes`` of blobs each (a tensor is never
     split; one larger than the limit gets a shard of its own).  Every shard carries the header; the asset records go to
-    the first.  Returns the shard paths; ``open_mfq`` on any of them opens the whole checkpoint."""
+    the first.  ``max_tensors`` also limits the records per shard.  Returns the shard paths; ``open_mfq`` on any of them
+    opens the whole checkpoint."""
     p = Path(path)
     stem = p.name[: -len(".mfq")] if p.name.endswith(".mfq") else p.name
     packed = {name: pack_tensor(t) for name, t in tensors.items()}
     groups: list[list[str]] = [[]]
     size = 0
     for name, (_dt, blob) in packed.items():
-        if groups[-1] and size + len(blob) > max_bytes:
+        if groups[-1] and ((max_bytes and size + len(blob) > max_bytes) or (max_tensors and len(groups[-1]) >= max_tensors)):
             groups.append([])
             size = 0
         groups[-1].append(name)
