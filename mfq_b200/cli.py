@@ -328,7 +328,7 @@ def _cmd_serve(args) -> int:
     import uvicorn
     from .checkpoint import load_engine
     from .server import ModelService, create_app
-    device = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    device = args.device if args.device not in (None, "auto") else ("cuda" if torch.cuda.is_available() else "cpu")
     ctx = None
     if args.tensor_parallel > 1:
         from .server import tp_serve
@@ -347,24 +347,40 @@ def _cmd_serve(args) -> int:
         print(f"rank={ctx.rank} follower_exit={why}", file=sys.stderr)
         ctx.finish()
         return 0 if why == "shutdown" else 1
-    service = ModelService(max_instances=args.max_runtime_instances, max_queue=args.max_queue, queue_timeout=args.queue_timeout)
+    import logging
+    logging.basicConfig(level=getattr(logging, str(args.log_level).upper(), logging.INFO))
+    service = ModelService(max_instances=args.max_runtime_instances, max_queue=args.max_queue, queue_timeout=args.queue_timeout,
+                           idle_timeout=args.runtime_idle_timeout or None)
     if args.worker_process and ctx is None:
         return _serve_with_worker(args, service, device)
 
     def loader(name_or_path):
         path = name_or_path if Path(name_or_path).exists() else args.model
+        if not Path(name_or_path).exists() and args.model_dir:  # a model name: look it up in the model directory
+            for cand in (Path(args.model_dir) / name_or_path, Path(args.model_dir) / f"{name_or_path}.mfq"):
+                if cand.exists():
+                    path = str(cand)
+                    break
+        slots = args.moe_gpu_cache_slots
+        if slots is None and args.moe_gpu_cache_gb:
+            slots = _expert_slots_for(path, args.moe_gpu_cache_gb)
         engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size, **tp,
-                                        native_4bit=args.native_4bit, expert_slots=args.moe_gpu_cache_slots,
+                                        native_4bit=args.native_4bit, expert_slots=slots,
                                         kv_budget_bytes=int(args.kv_budget_gb * (1 << 30)) if args.kv_budget_gb else None,
                                         yarn_context_extension=args.yarn_context_extension,
                                         mtp_draft_tokens=args.mtp_draft_tokens, mtp_adaptive=args.mtp_adaptive)
+        if args.prefill_chunk_size not in (None, "auto"):
+            engine.prefill_chunk = max(16, int(args.prefill_chunk_size))
         if args.session_cache_gb > 0:
             from .engine.session_cache import SessionSnapshotCache
             engine.session_cache = SessionSnapshotCache(int(args.session_cache_gb * (1 << 30)))
-        if args.prefix_cache_dir:
+        if args.prefix_cache_dir and not args.no_prefix_cache:
             from . import native
-            engine.prefix_cache = native.PrefixCache(args.prefix_cache_dir, ram_budget=int(args.prefix_cache_ram_gb * (1 << 30)),
-                                                     disk_budget=int(args.prefix_cache_disk_gb * (1 << 30)))
+            from .quantize.recipe import parse_size
+            ram = parse_size(args.prefix_cache_hot_size) if args.prefix_cache_hot_size else int(args.prefix_cache_ram_gb * (1 << 30))
+            disk = parse_size(args.prefix_cache_disk_size) if args.prefix_cache_disk_size else int(args.prefix_cache_disk_gb * (1 << 30))
+            engine.prefix_cache = native.PrefixCache(args.prefix_cache_dir, ram_budget=ram, disk_budget=disk,
+                                                     block_tokens=args.prefix_cache_block_tokens)
             engine.prefix_salt = f"{Path(path).name}:{Path(path).stat().st_size}"
         return engine, tok
 
@@ -385,7 +401,13 @@ def _cmd_serve(args) -> int:
     if args.cluster_peer:
         from .server.cluster import ClusterBackend
         cluster = ClusterBackend(args.cluster_peer)
-    app = create_app(service, api_key=key, cluster=cluster)
+    sessions = None
+    if args.db or args.data_dir:
+        from .server.sessions import SessionStore
+        db = Path(args.db) if args.db else Path(args.data_dir) / "mfq-server.sqlite3"
+        db.parent.mkdir(parents=True, exist_ok=True)
+        sessions = SessionStore(db)
+    app = create_app(service, api_key=key, cluster=cluster, sessions=sessions)
     try:
         if args.anthropic_port and args.anthropic_port != args.port:
             from .server.listen import Listeners
@@ -398,6 +420,21 @@ def _cmd_serve(args) -> int:
             engine.shutdown_followers()
             ctx.finish()
     return 0
+
+
+def _expert_slots_for(path, gigabytes: float) -> int | None:
+    """``--moe-gpu-cache-gb``: how many routed experts per layer fit in that much HBM (FP8 gate_up + down + multipliers)."""
+    from . import formats as F
+    if Path(path).is_dir():
+        return None
+    with F.open_mfq(path) as store:
+        cfg = json.loads(store.assets()["model_config.json"])
+    h, i, layers = int(cfg.get("hidden_size", 0)), int(cfg.get("moe_intermediate", 0) or 0), int(cfg.get("num_layers", 1))
+    if not h or not i or not cfg.get("num_experts"):
+        return None
+    per_expert = 3 * h * i * (1 + 4 / (128 * 128))
+    slots = int(gigabytes * (1 << 30) / (layers * per_expert))
+    return max(1, slots) if slots < int(cfg["num_experts"]) else None
 
 
 def _serve_with_worker(args, service, device) -> int:
@@ -600,12 +637,23 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--host", default="127.0.0.1")
     s.add_argument("--port", type=int, default=8090)
     s.add_argument("--api-key-env")
-    s.add_argument("--continuous-batching", type=int, default=32)
-    s.add_argument("--ctx-size", type=int, default=8192)
+    s.add_argument("--continuous-batching", "--max-requests-per-runtime", dest="continuous_batching", type=int, default=32)
+    s.add_argument("--ctx-size", "--context-size", dest="ctx_size", type=int, default=8192)
+    s.add_argument("--prefill-chunk-size", default="auto", help="auto, or the longest prompt span prefilled in one pass")
     s.add_argument("--max-runtime-instances", type=int, default=1)
-    s.add_argument("--max-queue", type=int, default=256)
+    s.add_argument("--max-queue", "--max-queued-requests-per-runtime", dest="max_queue", type=int, default=256)
     s.add_argument("--queue-timeout", type=float, default=30.0)
-    s.add_argument("--device")
+    s.add_argument("--runtime-idle-timeout", type=float, default=0.0, help="unload a model idle for this many seconds (0: never)")
+    s.add_argument("--model-dir", help="directory in which model names given to /api/v1/models/load are looked up")
+    s.add_argument("--data-dir", help="directory of the server's own state (session database)")
+    s.add_argument("--db", help="SQLite file of the session store (default: in memory, or <data-dir>/mfq-server.sqlite3)")
+    s.add_argument("--moe-gpu-cache-gb", type=float, default=0.0, help="HBM for routed experts; the rest stay in pinned host memory")
+    s.add_argument("--prefix-cache-disk-size", help="N[M|G]; overrides --prefix-cache-disk-gb")
+    s.add_argument("--prefix-cache-hot-size", help="N[M|G]; overrides --prefix-cache-ram-gb")
+    s.add_argument("--prefix-cache-block-tokens", type=int, default=256)
+    s.add_argument("--no-prefix-cache", action="store_true")
+    s.add_argument("--log-level", default="info")
+    s.add_argument("--device", "--backend", dest="device")
     s.add_argument("--access-log", action="store_true")
     s.add_argument("--native-4bit", action="store_true",
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")

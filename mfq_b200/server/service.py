@@ -33,7 +33,8 @@ class LoadedModel:
 
 class ModelService:
     def __init__(self, *, max_instances: int = 1, max_queue: int = 256, queue_timeout: float | None = 30.0,
-                 loader=None) -> None:
+                 loader=None, idle_timeout: float | None = None) -> None:
+        self.idle_timeout = idle_timeout  # unload a model nobody used for this long (it loads again on demand)
         self.models: OrderedDict[str, LoadedModel] = OrderedDict()
         self.max_instances, self.max_queue, self.queue_timeout = max_instances, max_queue, queue_timeout
         self.metrics = Metrics()
@@ -100,6 +101,7 @@ class ModelService:
     def submit(self, model: LoadedModel, prompt_ids: list[int], params: SamplingParams, *, priority: int = 0,
                timeout_seconds: float | None = None, session: str | None = None) -> tuple[Request, "queue.Queue[Event]"]:
         events: "queue.Queue[Event]" = queue.Queue()
+        model.meta["last_used"] = time.monotonic()
         req = Request(prompt_ids, params, priority=priority, timeout_seconds=timeout_seconds, on_event=events.put,
                       session=str(session) if session else None)
         done = threading.Event()
@@ -138,7 +140,18 @@ class ModelService:
                     except Exception:  # scheduler bug: poison this model only
                         lm.scheduler.healthy = False
             if not busy:
+                self._reap_idle()
                 time.sleep(0.002)
+
+    def _reap_idle(self) -> None:
+        """Unload models that finished their work ``idle_timeout`` seconds ago; only when a loader can bring them back."""
+        if not self.idle_timeout or self.loader is None:
+            return
+        now = time.monotonic()
+        for name, lm in list(self.models.items()):
+            last = lm.meta.get("last_used", lm.meta.setdefault("last_used", now))
+            if lm.scheduler.idle and now - last > self.idle_timeout:
+                self.unload(name)
 
     def shutdown(self) -> None:
         self._stop.set()
