@@ -14,6 +14,7 @@ _HELP = {
     "mfq_runtime_queued_requests": ("gauge", "Requests waiting for a slot."),
     "mfq_runtime_rejected_requests_total": ("counter", "Requests refused with 429 runtime_queue_full."),
     "mfq_runtime_kv_bytes": ("gauge", "Resident KV bytes."),
+    "mfq_runtime_resident_bytes": ("gauge", "Resident memory of the runtime process."),
     "mfq_runtime_kv_usage_ratio": ("gauge", "KV bytes in use over the KV budget."),
     "mfq_runtime_mtp_acceptance_ratio": ("gauge", "Accepted MTP draft tokens over drafted tokens."),
     "mfq_requests_total": ("counter", "Requests served, by result."),
@@ -83,7 +84,12 @@ class Metrics:
                 total = (eng.cache.num_pages - 1) * eng.cache.page_size * eng.cache.bytes_per_token()
                 gauges["mfq_runtime_kv_bytes"].append((base, used))
                 gauges["mfq_runtime_kv_usage_ratio"].append((base, used / total if total else 0.0))
+            worker = getattr(getattr(s, "worker", None), "proc", None)  # a child runtime: report ITS memory
+            rss = _resident_bytes(worker.pid if worker is not None and worker.poll() is None else None)
+            if rss:
+                gauges["mfq_runtime_resident_bytes"].append((base, rss))
             mtp = getattr(eng, "mtp_stats", None)
+            mtp = mtp() if callable(mtp) else mtp
             if mtp and mtp.get("drafted"):
                 gauges["mfq_runtime_mtp_acceptance_ratio"].append((base, mtp["accepted"] / mtp["drafted"]))
         for name, rows in gauges.items():
@@ -108,3 +114,13 @@ class Metrics:
                     lines.append(f"{name}_sum{_labels(lb)} {h['sum']:g}")
                     lines.append(f"{name}_count{_labels(lb)} {h['count']}")
         return "\n".join(lines) + "\n"
+
+
+def _resident_bytes(pid: int | None = None) -> int:
+    """Resident set size of this process (or of ``pid``) from ``/proc``; 0 where that is not available."""
+    import os
+    try:
+        with open(f"/proc/{pid or os.getpid()}/statm") as f:
+            return int(f.read().split()[1]) * os.sysconf("SC_PAGE_SIZE")
+    except (OSError, ValueError, IndexError):
+        return 0

@@ -93,3 +93,18 @@ def test_server_parses_response_format():
     assert _params_from({}, ()).response_format is None
     with pytest.raises(ValueError):
         _params_from({"response_format": {"type": "xml"}}, ())
+
+
+def test_metrics_render_with_a_real_engine():
+    """/metrics over an LLMEngine (KV gauges, resident bytes, MTP ratio only once something was drafted)."""
+    from mfq_b200.server import ModelService
+    eng, tok = _engine()
+    service = ModelService()
+    try:
+        service.add_model("tiny", eng, tok)
+        text = service.metrics.render(service)
+        assert 'mfq_runtime_kv_bytes{' in text and "mfq_runtime_resident_bytes{" in text and "mfq_runtime_mtp_acceptance_ratio" not in text
+        rss = float([l for l in text.splitlines() if l.startswith("mfq_runtime_resident_bytes{")][0].split()[-1])
+        assert rss > 50e6
+    finally:
+        service.shutdown()
