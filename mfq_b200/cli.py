@@ -386,6 +386,13 @@ def _cmd_serve(args) -> int:
 
     service.loader = loader if ctx is None else None  # ranks load together at start; no loading on demand under TP
     engine, tok = loader(args.model)
+    profile_path = None
+    if args.moe_cache_profile:
+        from .engine import moe_cache_profile as mcp
+        profile_path = args.moe_cache_profile + (f".rank{ctx.rank}" if ctx is not None else "")
+        warmed = mcp.apply(engine.model, mcp.load(profile_path))
+        print(f"moe_cache_profile path={profile_path} warmed_experts={warmed}", file=sys.stderr)
+    served_engine = engine
     if ctx is not None:
         from .parallel.spmd import LeaderBackend
         engine = LeaderBackend(engine, ctx.log)
@@ -415,6 +422,8 @@ def _cmd_serve(args) -> int:
         else:
             uvicorn.run(app, host=args.host, port=args.port, access_log=args.access_log)
     finally:
+        if profile_path:
+            mcp.save(profile_path, mcp.collect(served_engine.model, args.model_name or Path(args.model).stem))
         if ctx is not None:  # the server is down: let the other ranks go
             service.shutdown()
             engine.shutdown_followers()
@@ -648,6 +657,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--data-dir", help="directory of the server's own state (session database)")
     s.add_argument("--db", help="SQLite file of the session store (default: in memory, or <data-dir>/mfq-server.sqlite3)")
     s.add_argument("--moe-gpu-cache-gb", type=float, default=0.0, help="HBM for routed experts; the rest stay in pinned host memory")
+    s.add_argument("--moe-cache-profile", help="JSON file of expert heat: warms the HBM expert arena at start, rewritten at shutdown")
     s.add_argument("--prefix-cache-disk-size", help="N[M|G]; overrides --prefix-cache-disk-gb")
     s.add_argument("--prefix-cache-hot-size", help="N[M|G]; overrides --prefix-cache-ram-gb")
     s.add_argument("--prefix-cache-block-tokens", type=int, default=256)

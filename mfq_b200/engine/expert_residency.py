@@ -117,6 +117,20 @@ class ExpertResidency:
             self._unpin(wave)
         return out
 
+    def warm(self, heat=None) -> list[int]:
+        """Make the hottest ``slots`` experts resident before traffic arrives (``heat``: a saved profile for this
+        layer; default: the heat gathered so far).  Returns the experts now resident."""
+        if heat is not None:
+            h = np.asarray(heat, dtype=np.float64)
+            if h.shape != self.heat.shape:
+                raise ValueError(f"heat profile has {h.shape[0]} entries, this layer has {self.n} experts")
+            self.heat = h.copy()
+        order = [int(e) for e in np.argsort(-self.heat, kind="stable")[: self.slots] if self.heat[e] > 0]
+        if order:
+            self._make_resident(order)
+            self._unpin(order)
+        return order
+
     # -- between steps ------------------------------------------------------------------------------------------
     def rebalance(self, max_swaps: int = 4, hysteresis: float = 0.25) -> list[tuple[int, int]]:
         """Swap cold residents for hotter absent experts; returns the (evicted, loaded) pairs."""

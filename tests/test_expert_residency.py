@@ -59,3 +59,40 @@ def test_rebalance_brings_hot_experts_in():
     assert resident == [2, 3, 5]
     for e in resident:  # arena contents follow the book
         assert torch.equal(res.arena.gate_up[res.slot_of[e]], res.host[0][e])
+
+
+def test_cache_profile_warms_a_fresh_arena(tmp_path):
+    """Heat gathered by one run is saved; a fresh residency warmed from it starts with the hot experts resident."""
+    from types import SimpleNamespace
+
+    from mfq_b200.engine import moe_cache_profile as mcp
+    n, slots = 10, 3
+
+    def model():
+        layers = []
+        for _ in range(2):
+            res = ExpertResidency(*_fake_experts(n), slots=slots, device="cpu")
+            layers.append(SimpleNamespace(moe=SimpleNamespace(residency=res)))
+        layers.insert(1, SimpleNamespace(moe=None))  # a dense layer in between
+        return SimpleNamespace(w=SimpleNamespace(layers=layers, tp_rank=0))
+
+    first = model()
+    hot = torch.tensor([[7, 2], [7, 5], [7, 2], [2, 5]], dtype=torch.int32)
+    for layer in (first.w.layers[0], first.w.layers[2]):
+        for _ in range(3):
+            layer.moe.residency.run(hot, lambda ids_slot, arena: torch.zeros(1))
+    path = tmp_path / "profile.json"
+    mcp.save(path, mcp.collect(first, "m"))
+    doc = mcp.load(path)
+    assert doc["format"] == mcp.FORMAT and set(doc["layers"]) == {"0", "2"} and doc["layers"]["0"]["heat"][7] > doc["layers"]["0"]["heat"][5] > 0
+    fresh = model()
+    assert mcp.apply(fresh, doc) == 6
+    for layer in (fresh.w.layers[0], fresh.w.layers[2]):
+        r = layer.moe.residency
+        assert sorted(int(e) for e in (r.slot_of >= 0).nonzero()[0]) == [2, 5, 7] and r.stats["uploads"] == 3
+        r.run(hot, lambda ids_slot, arena: torch.zeros(1))
+        assert r.stats["uploads"] == 3 and r.stats["hits"] == 3  # first traffic: no upload at all
+    # a profile of another model is ignored
+    other = model()
+    other.w.layers.pop()
+    assert mcp.apply(other, doc) == 0 and mcp.load(tmp_path / "missing.json") is None
