@@ -202,7 +202,8 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
     engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, num_pages=num_pages,
                        use_graphs=use_graphs and expert_slots is None,
                        mtp_draft_tokens=mtp_draft_tokens if getattr(weights, "mtp", None) is not None else 0,
-                       mtp_adaptive=mtp_adaptive)
+                       mtp_adaptive=mtp_adaptive and tp_size == 1)  # ranks time their steps separately: they would
+    #                                                                    park at different moments and fall out of lockstep
     tokenizer = tokenizer_from_assets(assets, cfg.vocab_size)
     # structured output needs the vocabulary's byte strings; resolved on the first request that asks for it
     engine.set_token_bytes(lambda: tokenizer.token_bytes(cfg.vocab_size), tokenizer.stop_ids)

@@ -371,6 +371,10 @@ def _cmd_serve(args) -> int:
                                         mtp_draft_tokens=args.mtp_draft_tokens, mtp_adaptive=args.mtp_adaptive)
         if args.prefill_chunk_size not in (None, "auto"):
             engine.prefill_chunk = max(16, int(args.prefill_chunk_size))
+        if ctx is not None:
+            # sharded serving: every rank must run the same kernels for a request, so the per-rank caches that let
+            # rank 0 skip part of a prefill (session snapshots, prefix blocks) stay off
+            return engine, tok
         if args.session_cache_gb > 0:
             from .engine.session_cache import SessionSnapshotCache
             engine.session_cache = SessionSnapshotCache(int(args.session_cache_gb * (1 << 30)))

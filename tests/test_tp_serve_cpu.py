@@ -34,7 +34,7 @@ def test_two_cpu_ranks_serve_a_completion(tmp_path):
     env.pop("WORLD_SIZE", None)
     log = open(tmp_path / "serve.log", "w")
     proc = subprocess.Popen([sys.executable, "-m", "mfq_b200.cli", "serve", "--model", str(ckpt), "--device", "cpu", "--port", str(port),
-                             "--tensor-parallel", "2", "--continuous-batching", "2", "--ctx-size", "96", "--session-cache-gb", "0"],
+                             "--tensor-parallel", "2", "--continuous-batching", "2", "--ctx-size", "96"],
                             env=env, stdout=log, stderr=subprocess.STDOUT, start_new_session=True)
     try:
         base = f"http://127.0.0.1:{port}"
@@ -48,7 +48,7 @@ def test_two_cpu_ranks_serve_a_completion(tmp_path):
                 assert proc.poll() is None, (tmp_path / "serve.log").read_text()[-3000:]
                 assert time.time() < deadline, (tmp_path / "serve.log").read_text()[-3000:]
                 time.sleep(1.0)
-        body = {"messages": [{"role": "user", "content": "hello there"}], "max_tokens": 6, "temperature": 0}
+        body = {"messages": [{"role": "user", "content": "hello there"}], "max_tokens": 6, "temperature": 0, "session_id": "s1"}
         a = _post(base + "/v1/chat/completions", body)
         b = _post(base + "/v1/chat/completions", body)
         assert a["usage"]["completion_tokens"] >= 1 and a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
