@@ -681,6 +681,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run the engine in a child process that is watched and restarted on demand (the server survives a dead engine)")
     s.add_argument("--tensor-parallel", type=int, default=1,
                    help="ranks (one process per GPU) that share every layer: attention heads, FFN columns and experts are sharded")
+    s.add_argument("--expert-parallel", action="store_true",
+                   help="accepted for compatibility: the ranks of --tensor-parallel always split the routed experts among themselves too")
     s.add_argument("--yarn-context-extension", type=float, default=None,
                    help="run on this multiple (> 1) of the trained context with YaRN-scaled rotary frequencies")
     s.add_argument("--anthropic-port", type=int, default=0,

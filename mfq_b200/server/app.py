@@ -187,8 +187,11 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
         except KeyError as exc:
             return None, error_response(404, "model_not_found", f"model {exc.args[0]!r} is not loaded")
         from . import tools as tool_ops
+        template_vars = dict(body.get("chat_template_kwargs") or {})
+        if body.get("enable_thinking") is not None:  # request-level switch of reasoning, as the templates spell it
+            template_vars["enable_thinking"] = bool(body["enable_thinking"])
         prompt = lm.tokenizer.apply_chat_template(tool_ops.with_tools(messages, tool_ops.normalise(body.get("tools"))),
-                                                  add_generation_prompt=True)
+                                                  add_generation_prompt=True, **template_vars)
         ids = lm.tokenizer.encode(prompt)
         if not ids:
             return None, error_response(400, "invalid_request", "empty prompt")

@@ -32,7 +32,7 @@ class ByteTokenizer:
         n = vocab_size or self.vocab_size
         return [bytes([i - 3]) if 3 <= i < 259 else b"" for i in range(n)]
 
-    def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True) -> str:
+    def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True, **_template_vars) -> str:
         parts = [f"<|{m['role']}|>\n{_content_text(m.get('content'))}\n" for m in messages]
         if add_generation_prompt:
             parts.append("<|assistant|>\n")
@@ -83,11 +83,13 @@ class HfTokenizer:
                 out.append(piece.replace("\u2581", " ").encode("utf-8"))
         return out
 
-    def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True) -> str:
+    def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True, **template_vars) -> str:
+        """``template_vars`` reach the Jinja template as variables (``enable_thinking``, ``tools`` ...)."""
         if self.chat_template:
             import jinja2
             env = jinja2.Environment(trim_blocks=True, lstrip_blocks=True)
-            return env.from_string(self.chat_template).render(messages=messages, add_generation_prompt=add_generation_prompt)
+            return env.from_string(self.chat_template).render(messages=messages, add_generation_prompt=add_generation_prompt,
+                                                              **template_vars)
         return ByteTokenizer.apply_chat_template(self, messages, add_generation_prompt)  # type: ignore[arg-type]
 
     @property

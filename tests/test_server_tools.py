@@ -76,3 +76,16 @@ def test_reasoning_block_is_split_from_the_answer(client):
     r = c.post("/v1/chat/completions", json={"model": "m", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 200})
     msg = r.json()["choices"][0]["message"]
     assert msg["content"] == "Hello!" and msg["reasoning_content"] == "the user greets me"
+
+
+def test_enable_thinking_reaches_the_chat_template():
+    import json as _json
+    from mfq_b200.server.tokenizer import HfTokenizer
+    spec = {"version": "1.0", "truncation": None, "padding": None, "added_tokens": [], "normalizer": None, "pre_tokenizer": None,
+            "post_processor": None, "decoder": None,
+            "model": {"type": "WordLevel", "vocab": {"<unk>": 0, "a": 1}, "unk_token": "<unk>"}}
+    template = "{% for m in messages %}{{ m.content }}{% endfor %}{% if enable_thinking is defined and not enable_thinking %}<think></think>{% endif %}"
+    tok = HfTokenizer(_json.dumps(spec).encode(), template)
+    msgs = [{"role": "user", "content": "a"}]
+    assert tok.apply_chat_template(msgs) == "a" and tok.apply_chat_template(msgs, enable_thinking=True) == "a"
+    assert tok.apply_chat_template(msgs, enable_thinking=False) == "a<think></think>"
