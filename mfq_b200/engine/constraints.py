@@ -50,6 +50,28 @@ class JsonTokenConstraint:
             self.finished = True
 
 
+class LogitBias:
+    """OpenAI ``logit_bias``: a fixed additive bias on chosen token ids for the whole request (values are clamped to
+    +-100 as the API defines them); optionally on top of a grammar constraint."""
+
+    def __init__(self, bias: dict, inner=None) -> None:
+        self.table = {int(t): max(-100.0, min(100.0, float(v))) for t, v in bias.items()}
+        self.inner = inner
+        self.finished = False
+
+    def bias(self, width: int) -> torch.Tensor:
+        out = self.inner.bias(width).float() if self.inner is not None else torch.zeros(width)
+        for t, v in self.table.items():
+            if 0 <= t < width:
+                out[t] += v
+        return out.to(torch.bfloat16)
+
+    def advance(self, token: int) -> None:
+        if self.inner is not None:
+            self.inner.advance(token)
+            self.finished = self.inner.finished
+
+
 def make_constraint(response_format, vocabulary, stop_ids):
     """``response_format`` as the request carried it (a dict, a type string or None) -> a constraint or None."""
     if not response_format or vocabulary is None:

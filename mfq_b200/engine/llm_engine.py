@@ -129,6 +129,13 @@ class LLMEngine:
 
     def _constraint_for(self, params):
         fmt = getattr(params, "response_format", None) if params is not None else None
+        bias = getattr(params, "logit_bias", None) if params is not None else None
+        if bias:
+            from .constraints import LogitBias
+            return LogitBias(bias, self._grammar_for(fmt, params))
+        return self._grammar_for(fmt, params)
+
+    def _grammar_for(self, fmt, params):
         if not fmt or getattr(self, "_token_bytes", None) is None:
             return None
         if self._constraint_vocab is None:

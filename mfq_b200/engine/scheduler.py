@@ -62,6 +62,7 @@ class SamplingParams:
     stop_token_ids: tuple[int, ...] = ()
     enable_mtp: bool = False
     mtp_max_draft_tokens: int = 3
+    logit_bias: dict | None = None  # token id -> additive bias in [-100, 100] (OpenAI semantics)
     response_format: dict | str | None = None  # {"type": "json_object"}: constrain the output to a JSON document
 
 
@@ -288,7 +289,7 @@ class ContinuousBatchScheduler:
                 extra = {}
                 if req.session is not None and hasattr(self.backend, "save_session"):
                     extra["session"] = req.session
-                if req.generated and req.params.response_format:  # replay after a retraction: the grammar has to
+                if req.generated and (req.params.response_format or req.params.logit_bias):  # replay after a retraction: the grammar has to
                     extra["generated"] = len(req.generated)       # re-read what was generated before
                 tok = self.backend.prefill(row, req.context, req.params, **extra)
             except MemoryError:

@@ -49,7 +49,8 @@ def _params_from(body: dict, stop_ids: tuple[int, ...]) -> SamplingParams:
         repetition_penalty=float(body.get("repetition_penalty", 1.0) or 1.0), seed=int(body.get("seed", 0) or 0),
         stop_token_ids=stop_ids, enable_mtp=bool(body.get("enable_mtp", False)),
         mtp_max_draft_tokens=int(body.get("mtp_max_draft_tokens", 3) or 3),
-        response_format=_response_format(body.get("response_format")))
+        response_format=_response_format(body.get("response_format")),
+        logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()} or None)
 
 
 def _response_format(value):

@@ -66,7 +66,8 @@ class StdioTransport:
                                 presence_penalty=float(s.get("presence_penalty", 0.0)), frequency_penalty=float(s.get("frequency_penalty", 0.0)),
                                 repetition_penalty=float(s.get("repetition_penalty", 1.0)),
                                 stop_token_ids=stops, enable_mtp=bool(s.get("enable_mtp", False)),
-                                response_format=params.get("response_format") or None)
+                                response_format=params.get("response_format") or None,
+                                logit_bias={int(k): float(v) for k, v in (params.get("logit_bias") or {}).items()} or None)
             ids = self._prompt_ids(lm, params)
             t0 = time.monotonic()
             req, events = self.service.submit(lm, ids, sp, priority=int(params.get("priority", 0) or 0),

@@ -168,7 +168,7 @@ class WorkerScheduler:
         p = req.params
         frame = {"id": f"w{req.id}", "op": "generate", "params": {
             "input": {"token_ids": list(req.prompt)}, "stream": False, "stream_tokens": True, "priority": req.priority,
-            "timeout_seconds": req.timeout_seconds, "response_format": p.response_format,
+            "timeout_seconds": req.timeout_seconds, "response_format": p.response_format, "logit_bias": p.logit_bias,
             "sampling": {"temperature": p.temperature, "top_p": p.top_p, "top_k": p.top_k, "max_new_tokens": p.max_tokens,
                          "seed": p.seed, "enable_mtp": p.enable_mtp, "presence_penalty": p.presence_penalty,
                          "frequency_penalty": p.frequency_penalty, "repetition_penalty": p.repetition_penalty,

@@ -108,3 +108,23 @@ def test_metrics_render_with_a_real_engine():
         assert rss > 50e6
     finally:
         service.shutdown()
+
+
+def test_logit_bias_bans_and_forces_tokens():
+    eng, tok = _engine()
+    prompt = tok.encode("abc")
+    free = [eng.prefill(0, prompt, SamplingParams(max_tokens=8))]
+    for _ in range(5):
+        free.append(eng.decode([0])[0])
+    eng.release(0)
+    banned = {t: -100 for t in set(free)}
+    got = [eng.prefill(0, prompt, SamplingParams(max_tokens=8, logit_bias=banned))]
+    for _ in range(5):
+        got.append(eng.decode([0])[0])
+    eng.release(0)
+    assert not set(got) & set(free)
+    forced = [eng.prefill(0, prompt, SamplingParams(max_tokens=8, logit_bias={77: 100}))]
+    forced.append(eng.decode([0])[0])
+    assert forced == [77, 77]
+    from mfq_b200.server.app import _params_from
+    assert _params_from({"logit_bias": {"12": -5, "13": 250}}, ()).logit_bias == {12: -5.0, 13: 250.0}
