@@ -418,7 +418,11 @@ def _cmd_serve(args) -> int:
         db = Path(args.db) if args.db else Path(args.data_dir) / "mfq-server.sqlite3"
         db.parent.mkdir(parents=True, exist_ok=True)
         sessions = SessionStore(db)
-    app = create_app(service, api_key=key, cluster=cluster, sessions=sessions)
+    policies = None
+    if args.data_dir:
+        from .server.policies import PolicyStore
+        policies = PolicyStore(Path(args.data_dir) / "policies.json")
+    app = create_app(service, api_key=key, cluster=cluster, sessions=sessions, policies=policies)
     try:
         if args.anthropic_port and args.anthropic_port != args.port:
             from .server.listen import Listeners

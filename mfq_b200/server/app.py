@@ -110,7 +110,7 @@ class _Stream:
                 return
 
 
-def create_app(service: ModelService, api_key=None, sessions=None, cluster=None, hardware=None) -> FastAPI:
+def create_app(service: ModelService, api_key=None, sessions=None, cluster=None, hardware=None, policies=None) -> FastAPI:
     """``api_key``: one key with every scope, or a :class:`~mfq_b200.server.auth.KeyStore`; ``sessions``: a :class:`~mfq_b200.server.sessions.SessionStore` (in-memory when omitted); ``cluster``: a
     :class:`~mfq_b200.server.cluster.ClusterBackend` whose peers serve models that are not loaded here; ``hardware``:
     a :class:`~mfq_b200.server.hardware.HardwareMonitor`."""
@@ -118,7 +118,11 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
     from .sessions import SessionStore
     from contextlib import asynccontextmanager
     from .jobs import JobManager
+    from .policies import PolicyStore
     jobs = JobManager()
+    policies = policies if policies is not None else PolicyStore()
+    for _lm in service.models.values():
+        policies.apply_concurrency(_lm.name, _lm.scheduler)
 
     @asynccontextmanager
     async def lifespan(_app):
@@ -197,7 +201,7 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
         if not ids:
             return None, error_response(400, "invalid_request", "empty prompt")
         try:
-            params = _params_from(body, tuple(lm.tokenizer.stop_ids))
+            params = _params_from(policies.request_defaults(lm.name, body), tuple(lm.tokenizer.stop_ids))
         except (TypeError, ValueError) as exc:
             return None, error_response(400, "invalid_request", str(exc))
         try:
@@ -437,6 +441,24 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
         return [{"model": lm.name, "batch_capacity": lm.request_capacity, "max_queue": lm.scheduler.max_queue,
                  "queue_timeout": lm.scheduler.queue_timeout} for lm in service.models.values()]
 
+    @app.get("/api/v1/runtime/policies")
+    async def list_policies():
+        return {"policies": policies.all(), "sections": {k: sorted(v) for k, v in __import__("mfq_b200.server.policies", fromlist=["SECTIONS"]).SECTIONS.items()}}
+
+    @app.get("/api/v1/runtime/policies/{model}")
+    async def get_policy(model: str):
+        return {"model": model, "policy": policies.get(model)}
+
+    @app.put("/api/v1/runtime/policies/{model}")
+    async def put_policy(model: str, request: HttpRequest):
+        try:
+            clean = policies.put(model, await request.json())
+        except ValueError as exc:
+            return error_response(400, "invalid_request", str(exc))
+        if model in service.models:
+            policies.apply_concurrency(model, service.models[model].scheduler)
+        return {"model": model, "policy": clean}
+
     @app.post("/api/v1/models/load")
     async def load_model(request: HttpRequest):
         body = await request.json()
@@ -444,6 +466,7 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
             lm = await asyncio.get_running_loop().run_in_executor(None, service.load, body.get("model", ""))
         except KeyError:
             return error_response(404, "model_not_found", "unknown model and no loader configured")
+        policies.apply_concurrency(lm.name, lm.scheduler)
         return {"model": lm.name, "instance": lm.instance}
 
     @app.post("/api/v1/models/unload")
