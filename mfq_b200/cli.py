@@ -354,19 +354,28 @@ def _cmd_serve(args) -> int:
     if args.worker_process and ctx is None:
         return _serve_with_worker(args, service, device)
 
+    policies = None
+    if args.data_dir:
+        from .server.policies import PolicyStore
+        policies = PolicyStore(Path(args.data_dir) / "policies.json")
+
     def loader(name_or_path):
         path = name_or_path if Path(name_or_path).exists() else args.model
+        pol = policies.get(args.model_name or Path(name_or_path).stem) if policies is not None else {}
+        ctx_size = int(pol.get("context", {}).get("max_context_tokens") or args.ctx_size)
+        kv_gb = float(pol.get("memory", {}).get("kv_budget_gb") or args.kv_budget_gb)
+        cache_gb = float(pol.get("memory", {}).get("moe_gpu_cache_gb") or args.moe_gpu_cache_gb)
         if not Path(name_or_path).exists() and args.model_dir:  # a model name: look it up in the model directory
             for cand in (Path(args.model_dir) / name_or_path, Path(args.model_dir) / f"{name_or_path}.mfq"):
                 if cand.exists():
                     path = str(cand)
                     break
         slots = args.moe_gpu_cache_slots
-        if slots is None and args.moe_gpu_cache_gb:
-            slots = _expert_slots_for(path, args.moe_gpu_cache_gb)
-        engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=args.ctx_size, **tp,
+        if slots is None and cache_gb:
+            slots = _expert_slots_for(path, cache_gb)
+        engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=ctx_size, **tp,
                                         native_4bit=args.native_4bit, expert_slots=slots,
-                                        kv_budget_bytes=int(args.kv_budget_gb * (1 << 30)) if args.kv_budget_gb else None,
+                                        kv_budget_bytes=int(kv_gb * (1 << 30)) if kv_gb else None,
                                         yarn_context_extension=args.yarn_context_extension,
                                         mtp_draft_tokens=args.mtp_draft_tokens, mtp_adaptive=args.mtp_adaptive)
         if args.prefill_chunk_size not in (None, "auto"):
@@ -418,10 +427,6 @@ def _cmd_serve(args) -> int:
         db = Path(args.db) if args.db else Path(args.data_dir) / "mfq-server.sqlite3"
         db.parent.mkdir(parents=True, exist_ok=True)
         sessions = SessionStore(db)
-    policies = None
-    if args.data_dir:
-        from .server.policies import PolicyStore
-        policies = PolicyStore(Path(args.data_dir) / "policies.json")
     app = create_app(service, api_key=key, cluster=cluster, sessions=sessions, policies=policies)
     try:
         if args.anthropic_port and args.anthropic_port != args.port:
