@@ -152,7 +152,8 @@ def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict
 def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots: int | None = None, max_batch: int = 64,
                 max_seq_len: int = 8192, tp_rank: int = 0, tp_size: int = 1,
                 collective=None, use_graphs: bool = True, kv_budget_bytes: int | None = None,
-                yarn_context_extension: float | None = None, mtp_draft_tokens: int = 0, mtp_adaptive: bool = False):
+                yarn_context_extension: float | None = None, mtp_draft_tokens: int = 0, mtp_adaptive: bool = False,
+                lp_rank: int = 0, lp_size: int = 1, layer_split=None):
     """``.mfq`` -> (engine, tokenizer, config).  ``kv_budget_bytes`` caps the paged KV pool (see ``engine/kv_budget.py``);
     on a GPU it defaults to 90 % of the memory that is free once the weights are resident.  ``yarn_context_extension``
     (> 1) runs the model on that multiple of its trained context with YaRN-scaled rotary frequencies.
@@ -187,7 +188,8 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
         else:
             fields = {f for f in MoeDecoderConfig.__dataclass_fields__}
             cfg = MoeDecoderConfig(**{k: v for k, v in raw.items() if k in fields})
-            weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size, expert_slots=expert_slots, native_4bit=native_4bit)
+            weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size, expert_slots=expert_slots, native_4bit=native_4bit,
+                                              lp_rank=lp_rank, lp_size=lp_size, layer_split=layer_split)
             model = MoeDecoderModel(cfg, weights, collective=collective)
     # host-tier experts read the routing on the host every step, which a captured graph cannot do
     num_pages = None
@@ -197,7 +199,7 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
     if kv_budget_bytes is not None:
         from .engine.kv_budget import plan
         has_head = getattr(weights, "mtp", None) is not None
-        num_pages = plan(budget_bytes=kv_budget_bytes, layers=cfg.num_layers + int(has_head), kv_heads=model.hk, head_dim=cfg.head_dim,
+        num_pages = plan(budget_bytes=kv_budget_bytes, layers=model.local_layers + int(has_head), kv_heads=model.hk, head_dim=cfg.head_dim,
                          max_batch=max_batch, max_seq_len=max_seq_len).num_pages
     engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, num_pages=num_pages,
                        use_graphs=use_graphs and expert_slots is None,

@@ -330,14 +330,22 @@ def _cmd_serve(args) -> int:
     from .server import ModelService, create_app
     device = args.device if args.device not in (None, "auto") else ("cuda" if torch.cuda.is_available() else "cpu")
     ctx = None
-    if args.tensor_parallel > 1:
+    if args.tensor_parallel > 1 and args.layer_parallel > 1:
+        raise SystemExit("--tensor-parallel and --layer-parallel are mutually exclusive")
+    ranks = max(args.tensor_parallel, args.layer_parallel)
+    if ranks > 1:
         from .server import tp_serve
         if not tp_serve.under_launcher():  # first invocation: become N ranks
             import subprocess
-            return subprocess.call(tp_serve.launcher_argv(sys.argv[1:] if args._argv is None else args._argv, args.tensor_parallel))
+            return subprocess.call(tp_serve.launcher_argv(sys.argv[1:] if args._argv is None else args._argv, ranks))
         ctx = tp_serve.RankContext(device)
         device = ctx.device
-    tp = dict(tp_rank=ctx.rank, tp_size=ctx.world, collective=ctx.collective) if ctx else {}
+    tp = {}
+    if ctx is not None and args.layer_parallel > 1:  # contiguous layer ranges per rank, run one after the other
+        split = [float(x) for x in args.layer_split.split(",")] if args.layer_split else None
+        tp = dict(lp_rank=ctx.rank, lp_size=ctx.world, layer_split=split, collective=ctx.collective)
+    elif ctx is not None:
+        tp = dict(tp_rank=ctx.rank, tp_size=ctx.world, collective=ctx.collective)
 
     if ctx is not None and ctx.rank != 0:  # follower: mirror rank 0's engine calls until it shuts down
         from .parallel.spmd import follower_loop
@@ -690,6 +698,9 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run the engine in a child process that is watched and restarted on demand (the server survives a dead engine)")
     s.add_argument("--tensor-parallel", type=int, default=1,
                    help="ranks (one process per GPU) that share every layer: attention heads, FFN columns and experts are sharded")
+    s.add_argument("--layer-parallel", type=int, default=1,
+                   help="ranks that each hold a contiguous range of layers (weights and KV) and run one after the other")
+    s.add_argument("--layer-split", help="comma separated weights of the layer ranges, e.g. 3,1")
     s.add_argument("--expert-parallel", action="store_true",
                    help="accepted for compatibility: the ranks of --tensor-parallel always split the routed experts among themselves too")
     s.add_argument("--yarn-context-extension", type=float, default=None,

@@ -75,7 +75,7 @@ class LLMEngine:
         pages_per_seq = (max_seq_len + PAGE_SIZE - 1) // PAGE_SIZE
         if num_pages is None:
             num_pages = max_batch * pages_per_seq + 1
-        self.cache = PagedKVCache(layers=cfg.num_layers + (1 if has_head else 0), kv_heads=model.hk, head_dim=cfg.head_dim, num_pages=num_pages,
+        self.cache = PagedKVCache(layers=getattr(model, "local_layers", cfg.num_layers) + (1 if has_head else 0), kv_heads=model.hk, head_dim=cfg.head_dim, num_pages=num_pages,
                                   max_seqs=max_batch, max_pages_per_seq=pages_per_seq, device=self.device)
         dev = self.device
         self.input_ids = torch.zeros(max_batch, dtype=torch.int32, device=dev)

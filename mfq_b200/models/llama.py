@@ -374,15 +374,37 @@ class LlamaModel:
                 logits = self.collective.gather_columns(logits)
         return logits
 
+    @property
+    def local_layers(self) -> int:
+        """Layers whose weights and KV pages this rank holds (all of them unless layers are placed across ranks)."""
+        ranges = getattr(self.w, "lp_ranges", None)
+        if not ranges:
+            return len(self.w.layers)
+        l0, l1 = ranges[self.w.lp_rank]
+        return l1 - l0
+
+    def _run_layers(self, h, step: StepBuffers, cache, prefill: bool):
+        w = self.w
+        ranges = getattr(w, "lp_ranges", None)
+        if not ranges:
+            for li, layer in enumerate(w.layers):
+                h = self._block(h, layer, cache.layer(li), step, prefill)
+            return h
+        # layer placement: stages run one after the other; the owner's result reaches every rank
+        for stage, (l0, l1) in enumerate(ranges):
+            if stage == w.lp_rank:
+                for li in range(l0, l1):
+                    h = self._block(h, w.layers[li], cache.layer(li - l0), step, prefill)
+            h = self.collective.broadcast_rows(h, stage)
+        return h
+
     def forward(self, step: StepBuffers, cache, *, prefill: bool, logits_rows: torch.Tensor | None = None,
                 gather_logits: bool = True, return_hidden: bool = False):
         """Returns bf16 logits ``[rows, vocab]`` (all tokens, or ``logits_rows`` of them).  With tensor parallelism
         and ``gather_logits=False`` the result is this rank's vocabulary shard, for :meth:`sample_greedy`.
         ``return_hidden`` adds the residual stream of every token before the output norm (the MTP head's input)."""
         w = self.w
-        h = self._embed(step.input_ids)
-        for li, layer in enumerate(w.layers):
-            h = self._block(h, layer, cache.layer(li), step, prefill)
+        h = self._run_layers(self._embed(step.input_ids), step, cache, prefill)
         hidden = h
         if logits_rows is not None:
             h = h[logits_rows.long()] if not h.is_cuda else h.index_select(0, logits_rows.long())

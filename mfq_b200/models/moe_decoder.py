@@ -82,7 +82,8 @@ def _to_float(t, device) -> torch.Tensor:
 class MoeWeights(LlamaWeights):
     @classmethod
     def from_tensors(cls, cfg: MoeDecoderConfig, tensors, device, tp_rank: int = 0, tp_size: int = 1,
-                     expert_slots: int | None = None, native_4bit: bool = False) -> "MoeWeights":
+                     expert_slots: int | None = None, native_4bit: bool = False, lp_rank: int = 0, lp_size: int = 1,
+                     layer_split=None) -> "MoeWeights":
         """Build rank-local FP8 weights from checkpoint tensors under canonical names (a dict or an ``MfqStore``).
         ``expert_slots`` < experts per rank keeps the routed experts in (pinned) host memory behind an HBM arena of
         that many slots (:class:`~mfq_b200.engine.expert_residency.ExpertResidency`); such a model decodes eagerly.
@@ -180,11 +181,19 @@ class MoeWeights(LlamaWeights):
                 layer.down = linear([p + "mlp.down.weight"], lambda: cols(get(p + "mlp.down.weight"), i_))
             return layer
 
-        layers = [build_layer(f"model.block.{i}.") for i in range(cfg.num_layers)]
+        lp_ranges = None
+        if lp_size > 1:  # layer placement: only this rank's contiguous range is built (None keeps the global index)
+            if tp_size != 1:
+                raise ValueError("layer placement and tensor / expert parallelism are mutually exclusive")
+            from ..parallel.layer_parallel import plan_layers
+            lp_ranges = plan_layers(cfg.num_layers, lp_size, layer_split)
+        mine = range(*lp_ranges[lp_rank]) if lp_ranges else range(cfg.num_layers)
+        layers = [build_layer(f"model.block.{i}.") if i in mine else None for i in range(cfg.num_layers)]
         head = rows(get("model.output.weight"), cfg.vocab_size)
         weights = cls(get("model.token_embedding.weight").to(torch.bfloat16), layers, norm("model.output_norm.weight"),
                       Fp8Linear.from_float(head), tp_rank, tp_size)
-        if "predictor.fusion.weight" in tensors:  # multi-token-prediction head (one block; fusion = [embedding | hidden])
+        weights.lp_rank, weights.lp_size, weights.lp_ranges = lp_rank, lp_size, lp_ranges
+        if "predictor.fusion.weight" in tensors and lp_ranges is None:  # multi-token-prediction head (one block; fusion = [embedding | hidden])
             from .llama import MtpHead
             out_norm = "predictor.output_norm.weight"
             weights.mtp = MtpHead(enorm=norm("predictor.embedding_norm.weight"), hnorm=norm("predictor.hidden_norm.weight"),

@@ -101,6 +101,11 @@ class LocalCollective:
             return out
         return res
 
+    def broadcast_rows(self, h: torch.Tensor, src: int) -> torch.Tensor:
+        """Every rank gets rank ``src``'s tensor (layer placement: the stage owner hands the residual stream on)."""
+        got = self._exchange(h)[src]
+        return got if src == self.rank else got.clone()
+
     def barrier(self) -> None:
         self.group.barrier.wait()
 

@@ -149,6 +149,13 @@ class TensorParallel:
                  stream_ptr()), "allgather_rows", 2)
         return out
 
+    def broadcast_rows(self, h: torch.Tensor, src: int) -> torch.Tensor:
+        """Layer placement hand-off: every rank receives rank ``src``'s rows (in place; a few KB per step, so the
+        library broadcast over NVLink is used -- it is capturable in a CUDA graph)."""
+        import torch.distributed as dist
+        dist.broadcast(h, src=dist.get_global_rank(self.group, src) if hasattr(dist, "get_global_rank") else src, group=self.group)
+        return h
+
     def barrier(self) -> None:
         """Device-side barrier of all ranks on the current stream (bounded wait, no host synchronisation)."""
         if not hasattr(self, "_bar"):

@@ -25,7 +25,11 @@ def test_launcher_command_line():
     assert argv[-7:] == ["-m", "mfq_b200.cli", "serve", "--model", "m.mfq", "--tensor-parallel", "4"]
 
 
-def test_two_cpu_ranks_serve_a_completion(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("mode", [["--tensor-parallel", "2"], ["--layer-parallel", "2"]])
+def test_two_cpu_ranks_serve_a_completion(tmp_path, mode):
     ckpt = tmp_path / "tiny.mfq"
     assert main(["quantize", "synthetic:tiny-moe-128", str(ckpt), "--full-precision"]) == 0
     port = free_port()
@@ -34,7 +38,7 @@ def test_two_cpu_ranks_serve_a_completion(tmp_path):
     env.pop("WORLD_SIZE", None)
     log = open(tmp_path / "serve.log", "w")
     proc = subprocess.Popen([sys.executable, "-m", "mfq_b200.cli", "serve", "--model", str(ckpt), "--device", "cpu", "--port", str(port),
-                             "--tensor-parallel", "2", "--continuous-batching", "2", "--ctx-size", "96"],
+                             *mode, "--continuous-batching", "2", "--ctx-size", "96"],
                             env=env, stdout=log, stderr=subprocess.STDOUT, start_new_session=True)
     try:
         base = f"http://127.0.0.1:{port}"
