@@ -77,6 +77,19 @@ def _cmd_quantize(args) -> int:
     elif out.exists() and not args.overwrite and not args.dry_run:
         raise SystemExit(f"{out} exists (use --overwrite)")
     cfg, tensors, assets = _load_source(args)
+    base_records = None
+    if args.base_mfq:
+        # add a multi-token-prediction head to an existing checkpoint: everything the base holds is carried over as it is
+        # (no re-quantization), only the source's predictor.* tensors are quantized and added
+        with F.open_mfq(args.base_mfq) as base:
+            base_records = {n: base[n] for n in base if not n.startswith("__mfq_asset__/")}
+            base_assets = base.assets()
+            cfg = json.loads(base_assets.pop("model_config.json"))
+            base_assets.pop("model_graph.json", None)
+            assets = {**base_assets, **assets}
+        tensors = {n: t for n, t in tensors.items() if n.startswith("predictor.")}
+        if not tensors:
+            raise SystemExit(f"{args.input} has no multi-token-prediction head (predictor.* / mtp.* tensors) to add")
     dense = "bf16" if args.full_precision else (args.format or f"nint{args.bits}")
     widths = None
     if args.preset:
@@ -126,6 +139,9 @@ def _cmd_quantize(args) -> int:
     if args.split_max_size:
         from .quantize.recipe import parse_size
         shard_bytes = parse_size(args.split_max_size)
+    if base_records is not None:
+        q = {**base_records, **q}
+        extra["quantization"]["base_mfq"] = Path(args.base_mfq).name
     paths = save_checkpoint(out, cfg, q, assets, extra=extra, shard_bytes=shard_bytes, shard_tensors=args.split_max_tensors or None)
     size = sum(Path(p).stat().st_size for p in paths)
     weights = sum(int(t.size) for t in tensors.values())
@@ -543,12 +559,15 @@ def _cmd_bench_model(args) -> int:
             *(["--device", args.device] if args.device else [])]
         report = mb.benchmark(command, ints(args.prompt_tokens), args.new_tokens, ints(args.concurrency), args.repeats,
                               args.warmup, mtp=args.mtp, label=args.label or (Path(args.model).stem if args.model else ""))
+    problems = mb.validate_report(report)
+    for line in problems:
+        print(f"invalid report: {line}", file=sys.stderr)
     if args.output:
         Path(args.output).write_text(json.dumps(report, indent=1))
     if args.html:
         Path(args.html).write_text(mb.render_html(report))
     print(mb.render_markdown(report))
-    return 0
+    return 1 if problems else 0
 
 
 def _cmd_config(args) -> int:
@@ -592,6 +611,7 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--full-precision", action="store_true")
     q.add_argument("--device", "--backend", dest="device", default="cpu")
     q.add_argument("--seed", type=int, default=0)
+    q.add_argument("--base-mfq", help="existing checkpoint to extend: its records are kept as they are and the source's multi-token-prediction head is added")
     q.add_argument("--recipe", help="per-tensor precisions from a GGUF file's tensor table (.gguf) or a JSON rule list")
     q.add_argument("--target-bpw", type=float, default=0.0, help="AlphaQ allocation of NINT widths over the 2-D weights under this budget")
     q.add_argument("--split-max-size", help="limit of tensor payload per output shard, N[M|G]")
@@ -646,7 +666,7 @@ def build_parser() -> argparse.ArgumentParser:
     kl.add_argument("--ctx", type=int, default=128)
     kl.add_argument("--seed", type=int, default=0)
     kl.set_defaults(fn=_cmd_eval)
-    ol = sub.add_parser("optimize-layout", help="rewrite a checkpoint into the runtime's native execution layout")
+    ol = sub.add_parser("optimize-layout", aliases=["optimize"], help="rewrite a checkpoint into the runtime's native execution layout")
     ol.add_argument("--input", required=True)
     ol.add_argument("--output", required=True)
     ol.add_argument("--overwrite", action="store_true")

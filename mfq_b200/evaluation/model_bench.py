@@ -136,6 +136,30 @@ def benchmark(command: list[str], prompt_lengths, new_tokens, concurrency, repea
             "mtp": mtp, "rows": rows}
 
 
+def validate_report(report: dict) -> list[str]:
+    """Problems that make a benchmark report unusable (empty list: fine).  Checked before a report is rendered or
+    compared: every cell present once, positive rates, completions within what was asked for."""
+    problems = []
+    if report.get("format") != "mfq.model-bench.v1":
+        problems.append(f"unknown format {report.get('format')!r}")
+    seen = set()
+    for i, r in enumerate(report.get("rows") or []):
+        cell = (r.get("prompt_tokens"), r.get("concurrency"), r.get("new_tokens"))
+        if cell in seen:
+            problems.append(f"row {i}: cell {cell} appears twice")
+        seen.add(cell)
+        for key in ("ttft_ms", "prefill_tps", "aggregate_tps"):
+            v = r.get(key)
+            if not isinstance(v, (int, float)) or not v > 0 or v != v or v == float("inf"):
+                problems.append(f"row {i}: {key} = {v!r}")
+        done, asked = r.get("completion_tokens", 0), (r.get("new_tokens") or 0) * (r.get("concurrency") or 0)
+        if not 0 < done <= asked:
+            problems.append(f"row {i}: {done} completion tokens for {asked} asked")
+    if not report.get("rows"):
+        problems.append("no rows")
+    return problems
+
+
 # ---- reports ---------------------------------------------------------------------------------------------------------
 _COLUMNS = (("prompt_tokens", "prompt", "{:d}"), ("concurrency", "streams", "{:d}"), ("new_tokens", "new", "{:d}"),
             ("ttft_ms", "TTFT ms", "{:.1f}"), ("prefill_tps", "prefill tok/s", "{:.0f}"),

@@ -27,6 +27,16 @@ def test_matrix_over_the_stdio_runtime_and_reports(tmp_path, capsys):
     assert "TTFT ms" in capsys.readouterr().out
 
 
+def test_report_validation():
+    good = {"format": "mfq.model-bench.v1", "rows": [{"prompt_tokens": 8, "concurrency": 2, "new_tokens": 4, "ttft_ms": 1.0,
+                                                      "prefill_tps": 10.0, "decode_tps": 5.0, "aggregate_tps": 5.0, "completion_tokens": 8}]}
+    assert mb.validate_report(good) == []
+    bad = {"format": "x", "rows": [dict(good["rows"][0], ttft_ms=0.0, completion_tokens=9), good["rows"][0], good["rows"][0]]}
+    msgs = " | ".join(mb.validate_report(bad))
+    assert "unknown format" in msgs and "ttft_ms" in msgs and "9 completion tokens for 8" in msgs and "appears twice" in msgs
+    assert mb.validate_report({"format": "mfq.model-bench.v1", "rows": []}) == ["no rows"]
+
+
 def test_renderers_escape_and_scale():
     report = {"label": "<x>", "command": ["a", "<b>"], "rows": [
         {"prompt_tokens": 1, "concurrency": 1, "new_tokens": 2, "ttft_ms": 1.0, "prefill_tps": 10.0, "decode_tps": 5.0, "aggregate_tps": 5.0},

@@ -48,3 +48,33 @@ def test_checkpoint_with_a_head_decodes_by_cycles(tmp_path):
         agree += 1
     assert agree >= 12  # verify windows and one-token steps sum in different orders; a late near-tie may flip
     assert spec.mtp_stats()["drafted"] > 0
+
+
+def test_base_mfq_gets_a_head_added_without_requantizing(tmp_path, capsys):
+    from mfq_b200.cli import main
+    kw = dict(_SYNTHETIC["tiny-moe-128"])
+    body = {k: v.numpy().astype(np.float32) for k, v in init_weights(MoeConfig(**kw), seed=2, std=0.05).items()}
+    base = tmp_path / "base.mfq"
+    assert main(["quantize", "synthetic:tiny-moe-128", str(base), "--format", "nint4", "--seed", "2"]) == 0
+    # the source of the head: a full-precision checkpoint that carries predictor.* tensors
+    rng = np.random.default_rng(1)
+    h = kw["hidden_size"]
+    head = {"predictor.block.0." + n[len("model.block.1."):]: (np.ones_like(t) if "norm" in n else (rng.standard_normal(t.shape) * 0.05).astype(np.float32))
+            for n, t in body.items() if n.startswith("model.block.1.")}
+    head.update({"predictor.embedding_norm.weight": np.ones(h, np.float32), "predictor.hidden_norm.weight": np.ones(h, np.float32),
+                 "predictor.fusion.weight": (rng.standard_normal((h, 2 * h)) * 0.05).astype(np.float32)})
+    src = tmp_path / "with_head_fp.mfq"
+    save_checkpoint(src, dict(kw, name="src"), {k: F.to_bf16(v) for k, v in {**body, **head}.items()})
+    out = tmp_path / "base_plus_head.mfq"
+    assert main(["quantize", str(src), str(out), "--base-mfq", str(base), "--format", "nint8"]) == 0
+    capsys.readouterr()
+    with F.open_mfq(base) as b, F.open_mfq(out) as o:
+        for name in b:
+            if not name.startswith("__mfq_asset__/"):
+                assert bytes(o.raw(name)) == bytes(b.raw(name)), name  # carried over byte for byte
+        assert "predictor.fusion.weight" in o and "predictor.fusion.weight" not in b
+    eng, _, _ = load_engine(out, "cpu", max_batch=1, max_seq_len=64, mtp_draft_tokens=2)
+    assert eng.mtp_k == 2
+    import pytest
+    with pytest.raises(SystemExit, match="no multi-token-prediction head"):
+        main(["quantize", str(base), str(tmp_path / "x.mfq"), "--base-mfq", str(base)])
