@@ -37,11 +37,20 @@ class JsonTokenConstraint:
     def bias(self, width: int) -> torch.Tensor:
         """bf16 ``[width]``: 0 where a token may come next, a large negative number elsewhere (ids past the
         vocabulary, e.g. padding columns of the output projection, are never allowed)."""
+        cache = self.vocabulary.__dict__.setdefault("_bias_cache", {})
+        key = (self.state.key, self.state.complete, self.stop_ids, width)
+        hit = cache.get(key)
+        if hit is not None:  # e.g. every step inside a string value: same state, same 256 KB row
+            return hit
         out = np.full(width, NEG, dtype=np.float32)
         mask = self.allowed()
         n = min(width, mask.size)
         out[:n][mask[:n]] = 0.0
-        return torch.from_numpy(out).to(torch.bfloat16)
+        row = torch.from_numpy(out).to(torch.bfloat16)
+        if len(cache) >= 128:
+            cache.pop(next(iter(cache)))
+        cache[key] = row
+        return row
 
     def advance(self, token: int) -> None:
         if self.finished:

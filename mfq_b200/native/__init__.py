@@ -347,7 +347,21 @@ class JsonState:
 
     def mask(self) -> np.ndarray:
         """bool ``[vocab]``: tokens that keep the text a prefix of a valid document."""
+        key = self.key
+        cache = self.vocab.__dict__.setdefault("_mask_cache", {})
+        hit = cache.get(key)
+        if hit is not None:
+            return hit.copy()
         words = np.zeros((self.vocab.size + 31) // 32, dtype=np.uint32)
         if lib().mfq_json_mask(self.vocab._h, _np_ptr(self._s), _np_ptr(words)) < 0:
             raise ValueError(_err())
-        return np.unpackbits(words.view(np.uint8), bitorder="little")[: self.vocab.size].astype(bool)
+        mask = np.unpackbits(words.view(np.uint8), bitorder="little")[: self.vocab.size].astype(bool)
+        if len(cache) >= 256:  # the mask is a function of the 16 state bytes alone; text inside a string keeps one state
+            cache.pop(next(iter(cache)))
+        cache[key] = mask
+        return mask.copy()
+
+    @property
+    def key(self) -> bytes:
+        """The grammar position as bytes: equal keys have equal masks."""
+        return self._s.tobytes()
