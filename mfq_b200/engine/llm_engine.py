@@ -159,12 +159,17 @@ class LLMEngine:
         """Refresh the bias rows of ``rows`` from their grammar states (zero for rows without one)."""
         if self.logit_bias is None:
             return
+        held = self.__dict__.setdefault("_bias_held", {})  # row -> the host row its device copy came from (None: zeros)
         for r in rows:
             c = self.row_constraint.get(r)
-            if c is None:
+            src = None if c is None else c.bias(self.logit_bias.shape[1])
+            if r in held and held[r] is src:
+                continue  # same grammar state as last step (e.g. inside a string): the device row is already right
+            if src is None:
                 self.logit_bias[r].zero_()
             else:
-                self.logit_bias[r].copy_(c.bias(self.logit_bias.shape[1]), non_blocking=True)
+                self.logit_bias[r].copy_(src, non_blocking=True)
+            held[r] = src
 
     # -- capacity (scheduler backend protocol) ------------------------------------------------------------------
     def free_tokens(self) -> int:
