@@ -14,7 +14,10 @@ Failure handling (all on the host):
 * the next ``submit`` revives the worker -- a fresh child, waited for until its ``ready`` frame -- unless the last
   start is more recent than the back-off (1 s, doubling per consecutive failure up to 60 s), in which case the request
   is refused with ``backend_failure``; a worker that served a request successfully resets the back-off;
-* a child that starts but never says ``ready`` within ``ready_timeout`` counts as a failed start and is killed.
+* a child that starts but never says ``ready`` within ``ready_timeout`` counts as a failed start and is killed;
+* a child that is alive but sends no frame for ``stall_timeout`` seconds while requests are in flight is taken for hung:
+  it is killed and handled like a dead one; a request whose own deadline passed without an answer fails with
+  ``runtime_deadline_exceeded`` and is cancelled at the child.
 
 Reference: the Python runtime pool launches native workers, polls them until healthy, detects their death with
 ``process.poll()`` and revives dead or unhealthy runtimes on the next request with a per-model back-off
@@ -97,10 +100,12 @@ class WorkerProcess:
 class WorkerScheduler:
     def __init__(self, command: list[str], *, capacity: int = 32, max_queue: int = 256, env: dict | None = None,
                  ready_timeout: float = 600.0, backoff: float = 1.0, max_backoff: float = 60.0,
-                 clock=time.monotonic, start: bool = True) -> None:
+                 clock=time.monotonic, start: bool = True, stall_timeout: float | None = 300.0) -> None:
         self.command, self.env, self.ready_timeout = list(command), env, ready_timeout
         self.capacity, self.max_queue, self.clock = capacity, max_queue, clock
         self.backoff0, self.max_backoff = backoff, max_backoff
+        self.stall_timeout = stall_timeout  # requests in flight and no frame for this long: the child hangs -> kill it
+        self._last_frame = clock()
         self.stats = SchedulerStats()
         self.running: dict[int, Request] = {}  # request id -> request in flight at the worker
         self.waiting: list[Request] = []       # kept for the status view; the worker queues for itself
@@ -173,6 +178,10 @@ class WorkerScheduler:
                          "seed": p.seed, "enable_mtp": p.enable_mtp, "presence_penalty": p.presence_penalty,
                          "frequency_penalty": p.frequency_penalty, "repetition_penalty": p.repetition_penalty,
                          "stop_token_ids": list(p.stop_token_ids)}}}
+        if not self.running:
+            self._last_frame = self.clock()  # the silence before this request does not count against the child
+        if req.timeout_seconds:
+            req.deadline = req.arrival + float(req.timeout_seconds)
         self.running[req.id] = req
         if not self.worker.send(frame):
             self._worker_died()
@@ -197,6 +206,7 @@ class WorkerScheduler:
             except queue.Empty:
                 break
             busy = True
+            self._last_frame = self.clock()
             if frame is None:  # end of the child's output
                 if self.healthy:
                     self._worker_died()
@@ -232,6 +242,20 @@ class WorkerScheduler:
                     if req.on_event:
                         req.on_event(Event("completed", req.id, finish_reason=req.finish_reason or "stop"))
         if self.healthy and not w.alive and w.frames.empty():
+            self._worker_died()
+            busy = True
+        now = self.clock()
+        for req in [r for r in self.running.values() if r.deadline is not None and now > r.deadline + 1.0]:
+            # the child enforces deadlines itself; this is the front end's own bound in case it does not answer
+            self.running.pop(req.id, None)
+            self.worker.send({"op": "cancel", "params": {"target": f"w{req.id}"}})
+            req.finished, req.finish_reason = True, "runtime_deadline_exceeded"
+            self.stats.failed += 1
+            if req.on_event:
+                req.on_event(Event("failed", req.id, error_code="runtime_deadline_exceeded"))
+            busy = True
+        if self.healthy and self.running and self.stall_timeout and now - self._last_frame > self.stall_timeout:
+            w.kill()  # alive but silent with work in flight: a hung engine; the next request starts a fresh child
             self._worker_died()
             busy = True
         return busy

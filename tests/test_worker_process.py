@@ -85,3 +85,32 @@ def test_failed_starts_back_off():
     now[0] += 5.0  # the back-off doubled to 8 s
     with pytest.raises(BackendFailure, match="next start in 3.0 s"):
         sched.submit(Request([1, 2, 3]))
+
+
+_SILENT_CHILD = (
+    "import sys, json, time\n"
+    "print(json.dumps({'v': 1, 'type': 'ready', 'data': {'models': ['m']}}), flush=True)\n"
+    "for line in sys.stdin:\n"
+    "    pass\n"  # reads requests, never answers
+)
+
+
+def test_a_silent_child_is_killed_and_deadlines_are_enforced_by_the_front_end():
+    from mfq_b200.engine.scheduler import Request
+    events = []
+    sched = WorkerScheduler([sys.executable, "-c", _SILENT_CHILD], ready_timeout=60, stall_timeout=3.0, backoff=0.0)
+    try:
+        late = Request([1, 2, 3], timeout_seconds=0.2, on_event=events.append)
+        stuck = Request([4, 5, 6], on_event=events.append)
+        sched.submit(late)
+        sched.submit(stuck)
+        deadline = time.time() + 20
+        while sched.running and time.time() < deadline:
+            sched.step()
+            time.sleep(0.05)
+        kinds = [(e.request_id, e.kind, e.error_code) for e in events]
+        assert (late.id, "failed", "runtime_deadline_exceeded") in kinds
+        assert (stuck.id, "failed", "backend_failure") in kinds
+        assert not sched.healthy and sched.failures == 1 and sched.worker.proc.poll() is not None  # the hung child was killed
+    finally:
+        sched.shutdown()
