@@ -499,7 +499,8 @@ def _serve_with_worker(args, service, device) -> int:
                *(["--native-4bit"] if args.native_4bit else []),
                *(["--yarn-context-extension", str(args.yarn_context_extension)] if args.yarn_context_extension else [])]
     service.add_worker_model(args.model_name or Path(args.model).stem, command, tokenizer_from_assets(assets, vocab),
-                             capacity=args.continuous_batching)
+                             capacity=args.continuous_batching, ready_timeout=args.runtime_startup_timeout,
+                             stall_timeout=args.runtime_stall_timeout or None)
     key = os.environ.get(args.api_key_env) if args.api_key_env else None
     try:
         uvicorn.run(create_app(service, api_key=key), host=args.host, port=args.port, access_log=args.access_log)
@@ -714,6 +715,9 @@ def build_parser() -> argparse.ArgumentParser:
                    help="draft this many tokens per cycle with the checkpoint's multi-token-prediction head (0: off)")
     s.add_argument("--mtp-adaptive", action="store_true",
                    help="measure cycles against plain decoding and park them while they lose (the head stays primed)")
+    s.add_argument("--runtime-startup-timeout", type=float, default=600.0, help="seconds a worker process may take to announce itself")
+    s.add_argument("--runtime-stall-timeout", type=float, default=300.0,
+                   help="a worker with requests in flight that sends nothing for this long is killed as hung (0: never)")
     s.add_argument("--worker-process", action="store_true",
                    help="run the engine in a child process that is watched and restarted on demand (the server survives a dead engine)")
     s.add_argument("--tensor-parallel", type=int, default=1,
