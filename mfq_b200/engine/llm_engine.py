@@ -608,9 +608,24 @@ class LLMEngine:
         with scope("decode.step", self.device):
             return self._decode_rows(rows)
 
+    def _check_pages(self, rows) -> None:
+        """A row that decodes past its reserved pages would read and write the shared null page (block-table entry 0)
+        and corrupt every other row doing the same: refuse before launching."""
+        ps = self.cache.page_size
+        owned = self.cache.allocator.owned
+        for r in rows:
+            if r not in self.row_seq:
+                raise RuntimeError(f"row {r} was never prefilled")
+            need = self.row_len[r] + 1 + self.mtp_k
+            have = len(owned.get(self.row_seq[r], ())) * ps
+            if need > have:
+                raise RuntimeError(f"row {r} needs KV room for {need} tokens but holds pages for {have}: "
+                                   "call can_grow() / grow() before decode()")
+
     def _decode_rows(self, rows: list[int]) -> dict:
         b = bucket_for(max(rows) + 1)
         b = min(b, self.max_batch)
+        self._check_pages(rows)
         mask = torch.zeros(self.max_batch, dtype=torch.int32)
         mask[rows] = 1
         self.active.copy_(mask.to(self.device), non_blocking=True)

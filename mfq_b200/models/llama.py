@@ -383,6 +383,37 @@ class LlamaModel:
         l0, l1 = ranges[self.w.lp_rank]
         return l1 - l0
 
+    def _fused_tp(self, rows: int) -> bool:
+        """Whether this pass takes the fused tensor-parallel pipeline: the plain dense block, FP8 linears, a collective
+        that offers the fused reduce, and a row count within its buffers."""
+        col = self.collective
+        return (self.tp > 1 and type(self)._block is LlamaModel._block and type(self)._ffn is LlamaModel._ffn
+                and hasattr(col, "row_parallel_fused") and getattr(col, "fused", True)
+                and not getattr(self.w, "lp_ranges", None) and rows <= col.fused_rows(self.cfg.hidden_size)
+                and all(l.qkv.input_kind == "fp8" for l in self.w.layers[:1]))
+
+    def _run_layers_fused(self, h, step: StepBuffers, cache, prefill: bool):
+        """Tensor-parallel layer stack with every all-reduce fused with the residual add, the FOLLOWING RMSNorm and
+        its FP8 quantization (one kernel per row-parallel projection).  Returns the residual stream and the rows
+        already normalised with the output norm and quantised: the LM head's input."""
+        w, eps, col = self.w, self.cfg.rms_eps, self.collective
+        x = self._norm_quant(h, w.layers[0].attn_norm)
+        last = len(w.layers) - 1
+        for li, layer in enumerate(w.layers):
+            with scope("attn.qkv", h.device):
+                qkv = layer.qkv(*x)
+            with scope("attn.core", h.device):
+                attn = self._attention(qkv, cache.layer(li), step, prefill)
+            with scope("attn.o_proj", h.device):
+                h, xq, xs = col.row_parallel_fused(layer.o_proj, *self._quant(attn), h, layer.mlp_norm, eps)
+            with scope("ffn.gate_up", h.device):
+                gu = layer.gate_up(xq, xs)
+            with scope("ffn.down", h.device):
+                nxt = w.layers[li + 1].attn_norm if li < last else w.final_norm
+                h, xq, xs = col.row_parallel_fused(layer.down, *self._silu_quant(gu), h, nxt, eps)
+            x = (xq, xs)
+        return h, x
+
     def _run_layers(self, h, step: StepBuffers, cache, prefill: bool):
         w = self.w
         ranges = getattr(w, "lp_ranges", None)
@@ -404,12 +435,34 @@ class LlamaModel:
         and ``gather_logits=False`` the result is this rank's vocabulary shard, for :meth:`sample_greedy`.
         ``return_hidden`` adds the residual stream of every token before the output norm (the MTP head's input)."""
         w = self.w
-        h = self._run_layers(self._embed(step.input_ids), step, cache, prefill)
-        hidden = h
+        self._begin_step()
+        rows = step.input_ids.numel()
+        if self._fused_tp(rows):
+            # the residual stream lives in the collective's peer-mapped buffer, so finished rows can be pushed to it
+            h0 = self.collective.stream_rows(self.cfg.hidden_size, rows)
+            if h0.is_cuda:
+                ops.embed(step.input_ids, w.embed, out=h0)
+            else:
+                h0.copy_(w.embed[step.input_ids.long()])
+            h, x_head = self._run_layers_fused(h0, step, cache, prefill)
+            hidden = h
+            if logits_rows is None:
+                with scope("head", h.device):
+                    logits = w.lm_head(*x_head)
+                    if gather_logits:
+                        logits = self.collective.gather_columns(logits)
+                return (logits, hidden) if return_hidden else logits
+        else:
+            h = self._run_layers(self._embed(step.input_ids), step, cache, prefill)
+            hidden = h
         if logits_rows is not None:
             h = h[logits_rows.long()] if not h.is_cuda else h.index_select(0, logits_rows.long())
         logits = self._head(h, w.final_norm, gather_logits)
         return (logits, hidden) if return_hidden else logits
+
+    def _begin_step(self) -> None:
+        if self.tp > 1 and hasattr(self.collective, "begin_step"):
+            self.collective.begin_step()
 
     def mtp_forward(self, step: StepBuffers, cache, hidden: torch.Tensor, *, prefill: bool,
                     logits_rows: torch.Tensor | None = None):
@@ -419,6 +472,7 @@ class LlamaModel:
         ``num_layers`` at ``step.slots``.  Returns (vocabulary-shard logits, the head's output hidden states)."""
         m = self.w.mtp
         eps = self.cfg.rms_eps
+        self._begin_step()
         e = self._embed(step.input_ids)
         if e.is_cuda:
             _, _, ye, _ = ops.rmsnorm_quant(e, m.enorm, eps, want_q=False, want_y=True)

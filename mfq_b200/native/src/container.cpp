@@ -8,6 +8,8 @@
 #include "mfq_core.h"
 
 #include <cstring>
+#include <exception>
+#include <memory>
 #include <fcntl.h>
 #include <string>
 #include <sys/mman.h>
@@ -113,6 +115,8 @@ int parse_into(Store& s, int file_index, bool first) {
   }
   const uint32_t n_tensors = c.get<uint32_t>();
   if (!c.ok) return fail(-2, "shard %d: truncated header", file_index);
+  // sizes in the file are not trusted: a record takes at least 16 bytes of table (two length words + the blob size)
+  if (uint64_t(n_tensors) > uint64_t(c.left) / 16) return fail(-2, "shard %d: tensor count exceeds the file size", file_index);
   std::vector<Record> recs;
   recs.reserve(n_tensors);
   for (uint32_t i = 0; i < n_tensors; ++i) {
@@ -126,10 +130,12 @@ int parse_into(Store& s, int file_index, bool first) {
   }
   int64_t off = int64_t(c.p - m.base);
   for (auto& r : recs) {
+    // checked per record, against what is left, so that a crafted size cannot wrap the running offset
+    if (uint64_t(r.nbytes) > uint64_t(m.size) - uint64_t(off))
+      return fail(-2, "shard %d: blobs run past the end of the file", file_index);
     r.offset = off;
     off += r.nbytes;
   }
-  if (size_t(off) > m.size) return fail(-2, "shard %d: blobs run past the end of the file", file_index);
   if (first) {
     s.version = int(version);
     s.arch = arch;
@@ -148,8 +154,8 @@ extern "C" {
 
 const char* mfq_last_error() { return mfqn::error_slot().c_str(); }
 
-void* mfq_store_open(const char* path) {
-  auto s = new Store();
+void* mfq_store_open(const char* path) try {
+  std::unique_ptr<Store> s(new Store());
   std::string stem;
   int index = 0, count = 0;
   std::vector<std::string> paths;
@@ -166,15 +172,16 @@ void* mfq_store_open(const char* path) {
     s->files.emplace_back();
     if (!map_file(paths[i], s->files.back())) {
       fail(-1, "cannot map '%s'", paths[i].c_str());
-      delete s;
       return nullptr;
     }
     if (parse_into(*s, int(i), i == 0) != 0) {
-      delete s;
       return nullptr;
     }
   }
-  return s;
+  return s.release();
+} catch (const std::exception& e) {  // nothing may unwind through the C boundary
+  fail(-3, "opening the container failed: %s", e.what());
+  return nullptr;
 }
 
 void mfq_store_close(void* store) { delete static_cast<Store*>(store); }

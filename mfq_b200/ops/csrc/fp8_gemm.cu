@@ -546,12 +546,15 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
     if (size_t(n_tiles) * t_tiles * BT * kTileN > ar->half_elems) return -8;
     p.ar = *ar;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
+  // the shared-memory opt-in is a per-device property of the function: set it once on every device that launches
+  static bool attr_set[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -6;
+  if (!attr_set[dev]) {
     if (cudaFuncSetAttribute(fp8_gemm_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
         cudaSuccess)
       return -6;
-    attr_set = true;
+    attr_set[dev] = true;
   }
   if (ag) p.ag = *ag;
   const int extra_x = ag ? ag->push_ctas : 0;
@@ -760,7 +763,8 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[MFQ_NOALLOC_SCR
 namespace {
 constexpr int kMaxDevices = 64;
 // Device address of g_noalloc_scratch per device ordinal.  In host code the array's name is only a handle for
-// cudaGetSymbolAddress; the address a kernel can use has to be asked for, per device.
+// cudaGetSymbolAddress; the address a kernel can use has to be asked for, per device.  Filled without a lock: two
+// host threads that race here both look up, and store, the same address.
 unsigned char* g_noalloc_ptr[kMaxDevices] = {};
 
 int noalloc_fail(int code, const char* why) {
@@ -803,5 +807,21 @@ extern "C" int mfq_fp8_gemm_noalloc(const void* w, const float* w_scale, const v
   const int rc = mfq_fp8_gemm(w, w_scale, x, x_scale, out, residual, partials, MFQ_NOALLOC_PARTIAL_BYTES, counters,
                               MFQ_NOALLOC_MAX_TILES, status, M, N, K, token_tile, splits, stream);
   if (rc != 0) return noalloc_fail(rc, "launch failed");
+  return MFQ_NOALLOC_OK;
+}
+
+extern "C" int mfq_fp8_gemm_noalloc_status(int* status_out, cudaStream_t stream) {
+  if (!status_out) return noalloc_fail(MFQ_NOALLOC_BAD_ARGUMENT, "status_out is null");
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return noalloc_fail(MFQ_NOALLOC_SETUP_FAILED, "no current CUDA device");
+  if (!g_noalloc_ptr[dev]) {  // nothing has run on this device yet
+    *status_out = 0;
+    return MFQ_NOALLOC_OK;
+  }
+  const int* status = reinterpret_cast<const int*>(g_noalloc_ptr[dev] + MFQ_NOALLOC_PARTIAL_BYTES) + MFQ_NOALLOC_MAX_TILES;
+  if (cudaMemcpyAsync(status_out, status, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess)
+    return noalloc_fail(MFQ_NOALLOC_SETUP_FAILED, "could not read the status word");
   return MFQ_NOALLOC_OK;
 }

@@ -40,8 +40,9 @@ extern "C" {
 //
 // Allocation: none.  No cudaMalloc, cudaFree or allocating library routine is called, here or in the kernel.
 //
-// First call on a device: looks up the device address of the scratch array (once per device, with that device
-// current) before launching.  Make that first call outside of any stream capture.
+// First call on a device: looks up the device address of the scratch array and opts the kernel into its large
+// dynamic shared memory (both once per device, with that device current) before launching.  Make that first call
+// outside of any stream capture.
 //
 // Sharing: all calls on a device use the same scratch, which keeps whatever the previous call left there.  The
 // counters and the status word are cleared on `stream` at the start of every call; the partial tiles need no
@@ -53,6 +54,14 @@ extern "C" {
 // is also written to stderr).
 int mfq_fp8_gemm_noalloc(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
                          const void* residual, int M, int N, int K, int token_tile, int splits, cudaStream_t stream);
+
+// The kernel's waits are bounded; one that runs out (a protocol fault, never expected) leaves a non-zero code in the
+// status word inside the scratch instead of hanging, and the output of that call is then incomplete.  This reads the
+// word left by the calls queued so far on `stream` of the current device: it waits for `stream`, copies the word to
+// *status_out (0 = every call completed normally; 1 producer, 2 tensor-core issuer, 3 epilogue wait ran out) and
+// allocates nothing.  The word is cleared at the start of every mfq_fp8_gemm_noalloc call, so read it after the call
+// you care about and before the next one.
+int mfq_fp8_gemm_noalloc_status(int* status_out, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -69,6 +69,31 @@ class LocalCollective:
         h.copy_(total.to(h.dtype))
         return h
 
+    # the fused reduce of the GPU path (ops/csrc/tp_reduce.cu): bf16 partials, summed in rank order in fp32, plus the
+    # residual, stored as bf16; then RMSNorm + FP8 row quantization of the stored rows
+    fused = True
+
+    def begin_step(self) -> None:
+        pass
+
+    def fused_rows(self, hidden: int) -> int:
+        return 1024
+
+    def stream_rows(self, hidden: int, rows: int) -> torch.Tensor:
+        return torch.empty((rows, hidden), dtype=torch.bfloat16)
+
+    def row_parallel_fused(self, lin, x_q, x_scale, h, norm_w=None, eps: float = 0.0):
+        from ..ops import reference as ref
+        parts = self._exchange(lin(x_q, x_scale).to(torch.bfloat16).float())
+        total = torch.zeros_like(parts[0])
+        for p in parts:
+            total = total + p
+        h.copy_((total + h.float()).to(h.dtype))
+        if norm_w is None:
+            return h, None, None
+        q, s, _, _ = ref.rmsnorm_quant(h, norm_w, eps)
+        return h, q, s
+
     def allreduce_rows(self, partial: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
         parts = self._exchange(partial.float())
         total = h.float()

@@ -35,20 +35,119 @@ class _ReduceContext:
         self.flag_table = self.flags.table()
 
 
+class FusedStream:
+    """Peer-mapped buffers of the decode-sized residual stream of one hidden size, and the fused
+    all-reduce + residual + RMSNorm + FP8-quantization kernel over them (``ops/csrc/tp_reduce.cu``).
+
+    ``partial_out(m)`` is where a row-parallel GEMM writes this rank's bf16 partial (two halves used alternately);
+    :meth:`reduce` then sums all ranks' partials into the residual stream ``h`` and, given norm weights, leaves the
+    next GEMM's input ``(xq, xs)``.  With ``h`` inside this object's own buffer (:meth:`h_rows`) and enough rows the
+    two-shot mode is used: each rank finishes 1/W of the rows and pushes them to the others."""
+
+    TWO_SHOT_MIN_ROWS = 64
+
+    def __init__(self, tp: "TensorParallel", hidden: int, rows_cap: int = 1024) -> None:
+        self.tp, self.hidden, self.rows_cap = tp, hidden, rows_cap
+        g, dev = tp.group, tp.device
+        self.partials = PeerBuffer(g, 2 * rows_cap * hidden * 2, dev)
+        self.h = PeerBuffer(g, rows_cap * hidden * 2, dev)
+        self.xq = PeerBuffer(g, rows_cap * hidden, dev)
+        self.xs = PeerBuffer(g, rows_cap * 4, dev)
+        self.flags = PeerBuffer(g, 256, dev)
+        self.state = torch.zeros(4, dtype=torch.int32, device=dev)
+        self._partial_t = self.partials.local_tensor().view(torch.bfloat16).view(2, rows_cap, hidden)
+        self._h_t = self.h.local_tensor().view(torch.bfloat16).view(rows_cap, hidden)
+        self._xq_t = self.xq.local_tensor().view(FP8_DTYPE).view(rows_cap, hidden)
+        self._xs_t = self.xs.local_tensor().view(torch.float32)
+        self._tables = (self.partials.table(), self.h.table(), self.xq.table(), self.xs.table(), self.flags.table())
+        self.half = 0
+
+    def h_rows(self, m: int) -> torch.Tensor:
+        """The first ``m`` rows of the peer-mapped residual stream (keep the model's ``h`` here to enable two-shot)."""
+        return self._h_t[:m]
+
+    def partial_out(self, m: int) -> torch.Tensor:
+        return self._partial_t[self.half, :m]
+
+    def reduce(self, m: int, h: torch.Tensor, norm_w: torch.Tensor | None, eps: float = 0.0, add_residual: bool = True):
+        """``h += sum_r partial_r`` (the partials of the half :meth:`partial_out` last returned); with ``norm_w`` also
+        returns ``(xq, xs) = quant(rmsnorm(h) * norm_w)``.  ``h`` may be any ``[m, hidden]`` bf16 tensor of this rank;
+        rows inside :meth:`h_rows` allow the two-shot mode."""
+        tp = self.tp
+        own = h.data_ptr() == self._h_t.data_ptr()
+        two_shot = int(own and m >= self.TWO_SHOT_MIN_ROWS and m >= 2 * tp.world)
+        tables = self._tables
+        if not own:  # one-shot only: the residual stream is read and written locally at the caller's address
+            h_table = (C.c_void_p * tp.world)(*[h.data_ptr()] * tp.world)
+            tables = (tables[0], h_table, *tables[2:])
+        fn = lib().mfq_tp_reduce_norm_quant
+        fn.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 6 + \
+                      [C.c_int, C.c_void_p, C.c_void_p]
+        ws = Workspace.get(tp.device)
+        rc = fn(m, self.hidden, self.half, ptr(norm_w), float(eps), two_shot, int(add_residual), tp.world, tp.rank, *tables,
+                ptr(self.state), self.rows_cap, ptr(ws.status), stream_ptr())
+        check(rc, "tp_reduce_norm_quant")
+        self.half ^= 1
+        if norm_w is None:
+            return h, None, None
+        return h, self._xq_t[:m], self._xs_t[:m]
+
+
+FP8_DTYPE = torch.float8_e4m3fn
+
+
 class TensorParallel:
     def __init__(self, group, device: torch.device, max_rows: int = 8192) -> None:
         self.group, self.device = group, device
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self._ctx: dict[tuple[int, int, int], _ReduceContext] = {}
+        self._streams: dict[int, FusedStream] = {}
         self.rows_cap = max_rows
+        self.fused = True  # False: the GEMM-epilogue exchange (per-tile flags) also for decode-sized batches
         self._slots = PeerBuffer(group, 2 * self.world * max_rows * 8, device)
         self._slot_flags = PeerBuffer(group, max_rows * 4, device)
         self._slot_expected = torch.zeros(max_rows, dtype=torch.int32, device=device)
+
+    def stream(self, hidden: int) -> FusedStream:
+        """The fused-reduce buffers of one hidden size (created on first use: a collective call)."""
+        st = self._streams.get(hidden)
+        if st is None:
+            st = self._streams[hidden] = FusedStream(self, hidden)
+        return st
+
+    def begin_step(self) -> None:
+        """Call at the start of every forward pass: a device-side barrier of all ranks, after which the fused reduce
+        starts again at half 0 of its partial buffers.  The halves are chosen on the host (and frozen into captured
+        graphs), so without this two consecutive passes could use the same half back to back."""
+        self.barrier()
+        for st in self._streams.values():
+            st.half = 0
+
+    def row_parallel_fused(self, lin, x_q: torch.Tensor, x_scale: torch.Tensor, h: torch.Tensor,
+                           norm_w: torch.Tensor | None = None, eps: float = 0.0):
+        """``h += all_reduce(x_q @ lin^T)``, then ``(xq, xs) = quant(rmsnorm(h) * norm_w)`` for the next GEMM: the local
+        GEMM writes its bf16 partial into peer-mapped memory and ONE kernel does the exchange, the residual add, the
+        norm and the quantization.  Returns ``(h, xq, xs)`` (the latter None without ``norm_w``).  ``m`` must not
+        exceed the stream's row capacity."""
+        m = x_q.shape[0]
+        st = self.stream(lin.q.shape[0])
+        K.fp8_gemm(x_q, x_scale, lin.q, lin.scale, out=st.partial_out(m))
+        return st.reduce(m, h, norm_w, eps)
+
+    def stream_rows(self, hidden: int, rows: int) -> torch.Tensor:
+        """``[rows, hidden]`` bf16 view of the peer-mapped residual stream (where the model keeps ``h``)."""
+        return self.stream(hidden).h_rows(rows)
+
+    def fused_rows(self, hidden: int) -> int:
+        """Largest row count the fused reduce of this hidden size accepts."""
+        return self.stream(hidden).rows_cap
 
     def row_parallel_linear(self, lin, x_q: torch.Tensor, x_scale: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
         """``h += all_reduce(x_q @ lin^T)`` in place; ``x_q`` holds this rank's input shard."""
         m, k = x_q.shape
         n = lin.q.shape[0]
+        if m <= self.fused_rows(n) and self.fused:
+            return self.row_parallel_fused(lin, x_q, x_scale, h)[0]
         if m % (self.world * 128) == 0:
             # wide batches: two-shot (reduce-scatter in the GEMM epilogue, then all-gather of the bf16 rows) moves
             # 2(W-1)/W of the output per rank instead of the (W-1)x of the one-shot exchange
@@ -177,6 +276,10 @@ class TensorParallel:
     def allreduce_rows(self, partial: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
         """``h += sum over ranks of partial`` in place (one fused kernel over peer memory)."""
         rows, width = partial.shape
+        if self.fused and rows <= self.fused_rows(width):
+            st = self.stream(width)
+            st.partial_out(rows).copy_(partial)
+            return st.reduce(rows, h, None)[0]
         key = ("rows", width)
         ctx = self._ctx.get(key)
         if ctx is None:
@@ -207,6 +310,13 @@ class TensorParallel:
 
 class NcclTensorParallel(TensorParallel):
     """Baseline: unfused GEMM followed by NCCL all-reduce / all-gather (what a library-only port would do)."""
+
+    def __init__(self, group, device, max_rows: int = 8192) -> None:
+        super().__init__(group, device, max_rows)
+        self.fused = False
+
+    def begin_step(self) -> None:
+        pass
 
     def allreduce_rows(self, partial, h):
         total = partial.float()

@@ -146,7 +146,7 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
     @app.middleware("http")
     async def auth(request: HttpRequest, call_next):
         scope = required_scope(request.method, request.url.path)
-        if scope is not None and keys.keys:
+        if scope is not None and keys.enforce:
             supplied = request.headers.get("x-api-key")
             header = request.headers.get("authorization", "")
             if header.lower().startswith("bearer "):
@@ -401,7 +401,10 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
 
     @app.delete("/api/v1/auth/keys/{key_id}")
     async def revoke_key(key_id: str):
-        return {"revoked": keys.revoke(key_id)}
+        try:
+            return {"revoked": keys.revoke(key_id)}
+        except ValueError as exc:
+            return error_response(409, "last_admin_key", str(exc))
 
     @app.get("/api/v1/hardware")
     async def hardware_snapshot():

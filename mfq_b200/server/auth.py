@@ -3,7 +3,10 @@
 Three scopes: ``inference`` (the OpenAI / Anthropic routes), ``read`` (GET on the control API, metrics), ``admin``
 (everything, including changing the server: loading models, jobs, cache purges, key management).  Keys are kept as
 SHA-256 digests, so the store can be written to disk and listed without revealing a key; a key is shown once, when it is
-created.  With no keys configured the server is open (the default for a loopback deployment).  Reference:
+created.  Whether credentials are enforced is decided once, when the store is made: a store that was given a key or a
+key file enforces them from then on, also when its table later becomes empty (every request is then refused, and the
+last admin key cannot be revoked); a store made with neither leaves the server open (the default for a loopback
+deployment).  Reference:
 ``mfq/server/api/auth.py`` (bearer / ``x-api-key`` credentials with scopes) and the auth-key routes of the control API.
 """
 
@@ -38,11 +41,13 @@ def _digest(key: str) -> str:
 
 
 class KeyStore:
-    def __init__(self, path=None) -> None:
+    def __init__(self, path=None, enforce: bool | None = None) -> None:
         self.path = Path(path) if path else None
         self.keys: dict[str, dict] = {}  # digest -> {"id", "name", "scopes", "created"}
         if self.path and self.path.exists():
             self.keys = json.loads(self.path.read_text())
+        # auth on or off is a property of the deployment, not of how many keys happen to be in the table
+        self.enforce = bool(self.path is not None or self.keys) if enforce is None else bool(enforce)
 
     def _save(self) -> None:
         if self.path:
@@ -56,6 +61,7 @@ class KeyStore:
             raise ValueError(f"a key needs at least one scope of {SCOPES}")
         rec = {"id": secrets.token_hex(6), "name": name, "scopes": scopes, "created": time.time()}
         self.keys[_digest(key)] = rec
+        self.enforce = True
         self._save()
         return rec
 
@@ -64,8 +70,11 @@ class KeyStore:
         return key, self.add(key, scopes, name)
 
     def revoke(self, key_id: str) -> bool:
+        """Remove a key.  The last key with the ``admin`` scope stays (ValueError): without it nobody could manage keys."""
         for d, rec in list(self.keys.items()):
             if rec["id"] == key_id:
+                if "admin" in rec["scopes"] and sum("admin" in r["scopes"] for r in self.keys.values()) == 1:
+                    raise ValueError("the last admin key cannot be revoked")
                 del self.keys[d]
                 self._save()
                 return True
@@ -84,7 +93,7 @@ class KeyStore:
         return None
 
     def allows(self, key: str | None, scope: str | None) -> bool:
-        if scope is None or not self.keys:
+        if scope is None or not self.enforce:
             return True
         have = self.scopes_of(key)
         return have is not None and ("admin" in have or scope in have)

@@ -43,10 +43,15 @@ class Job:
 
     def describe(self, tail_bytes: int = 4096) -> dict:
         state = self.state
-        try:
-            data = self.log_path.read_bytes()[-tail_bytes:].decode("utf-8", errors="replace")
-        except OSError:
-            data = ""
+        data = ""
+        if tail_bytes > 0:  # 0 = no log text at all (the listing route); never read more than the tail
+            try:
+                with open(self.log_path, "rb") as f:
+                    f.seek(0, 2)
+                    f.seek(max(0, f.tell() - tail_bytes))
+                    data = f.read(tail_bytes).decode("utf-8", errors="replace")
+            except OSError:
+                data = ""
         return {"id": self.id, "kind": self.kind, "argv": self.argv, "state": state, "created": self.created,
                 "finished": self.finished, "exit_code": self.proc.poll() if self.proc else None, "log_tail": data}
 

@@ -25,7 +25,9 @@ def test_constrained_decode_graph_matches_eager_and_stays_in_the_grammar():
         eng = LLMEngine(LlamaModel(cfg, w), max_batch=4, max_seq_len=128, use_graphs=graphs)
         eng.set_token_bytes(lambda: tok.token_bytes(cfg.vocab_size), tok.stop_ids)
         free = eng.prefill(1, prompt, SamplingParams(max_tokens=8))  # an unconstrained neighbour in the same batch
+        eng.grow(1, len(prompt) + 48)  # pages for every token the loop below may write
         seq = [eng.prefill(0, prompt, fmt)]
+        eng.grow(0, len(prompt) + 48)
         neighbour = [free]
         for _ in range(40):
             if eng.row_constraint[0].finished:
@@ -37,9 +39,11 @@ def test_constrained_decode_graph_matches_eager_and_stays_in_the_grammar():
         text = bytes(t - 3 for t in seq if 3 <= t < 259)
         state = native.JsonState(eng._constraint_vocab, need_object=True)
         assert state.feed(text), text
-        # the neighbour decodes as if alone
+        # the neighbour decodes as if alone: a row's tokens depend on the batch bucket (which fixes the kernels and
+        # their summation order), not on what the other rows of the bucket hold
         alone = LLMEngine(LlamaModel(cfg, w), max_batch=4, max_seq_len=128, use_graphs=graphs)
         ref = [alone.prefill(1, prompt, SamplingParams(max_tokens=8))]
+        alone.grow(1, len(prompt) + 48)
         for _ in range(len(neighbour) - 1):
             ref.append(alone.decode([1])[1])
         assert ref == neighbour

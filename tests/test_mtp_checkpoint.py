@@ -38,9 +38,11 @@ def test_checkpoint_with_a_head_decodes_by_cycles(tmp_path):
     assert spec.mtp_k == 2 and spec.mtp_controller is not None
     prompt = list(range(9, 31))
     want = [plain.prefill(0, prompt)]
+    plain.grow(0, 96)
     for _ in range(20):
         want.append(plain.decode([0])[0])
     got = [spec.prefill(0, prompt)]
+    spec.grow(0, 96)
     while len(got) < 18:
         got.extend(spec.decode([0])[0])
     agree = 0

@@ -119,9 +119,11 @@ def test_adaptive_engine_is_lossless_and_parks_when_cycles_lose():
     adaptive.mtp_controller = ParkingController(probe=2, park_after=2, reprobe_every=3)
     prompt = list(range(7, 30))
     want = [plain_eng.prefill(0, prompt)]
+    plain_eng.grow(0, 128)
     for _ in range(40):
         want.append(plain_eng.decode([0])[0])
     got, modes = [adaptive.prefill(0, prompt)], []
+    adaptive.grow(0, 128)
     while len(got) < 36:
         before = dict(adaptive.mtp_controller.calls)
         out = adaptive.decode([0])[0]

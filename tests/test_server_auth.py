@@ -43,3 +43,33 @@ def test_keys_and_scopes_over_http(tmp_path):
     on_disk = json.loads((tmp_path / "keys.json").read_text())
     assert "root-secret" not in json.dumps(on_disk) and len(on_disk) == 1  # digests only
     assert KeyStore(tmp_path / "keys.json").allows("root-secret", "admin")
+
+
+def test_empty_key_table_does_not_reopen_the_server(tmp_path):
+    """A server started with a key or a key file keeps refusing requests when its table is empty."""
+    service = ModelService(max_queue=2, queue_timeout=5.0)
+    service.add_model("echo", EchoBackend(max_batch=2), ByteTokenizer())
+    chat = {"model": "echo", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 8}
+    with TestClient(create_app(service, api_key="only-key")) as c:
+        admin = {"authorization": "Bearer only-key"}
+        kid = c.get("/api/v1/auth/keys", headers=admin).json()["keys"][0]["id"]
+        assert c.delete(f"/api/v1/auth/keys/{kid}", headers=admin).status_code == 409  # the last admin key stays
+        assert c.post("/v1/chat/completions", json=chat).status_code == 401
+        c.app.state.keys.keys.clear()  # a table emptied behind the API's back still enforces
+        assert c.post("/v1/chat/completions", json=chat).status_code == 401
+        assert c.post("/api/v1/jobs", json={"kind": "inspect", "args": []}).status_code == 401
+    (tmp_path / "keys.json").write_text("{}")
+    with TestClient(create_app(service, api_key=KeyStore(tmp_path / "keys.json"))) as c:
+        assert c.post("/v1/chat/completions", json=chat).status_code == 401
+    with TestClient(create_app(service)) as c:  # no key, no key file: open
+        assert c.post("/v1/chat/completions", json=chat).status_code == 200
+    service.shutdown()
+
+
+def test_job_listing_carries_no_log_text(tmp_path):
+    from mfq_b200.server.jobs import Job
+    log = tmp_path / "j.log"
+    log.write_text("x" * 10000 + "END")
+    job = Job("j", "inspect", ["inspect"], log)
+    assert job.describe(0)["log_tail"] == ""
+    assert job.describe(8)["log_tail"] == "xxxxxEND"

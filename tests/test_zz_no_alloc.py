@@ -3,9 +3,8 @@
 Some users of the library cannot allocate device memory at the point where they need the GEMM (inside a stream
 capture, inside a serving loop that must not synchronize, or because they gave the library a fixed memory budget),
 so ``mfq_fp8_gemm_noalloc`` keeps its split-K scratch in a device array inside the library.  This test checks that
-it gives the same answer as the regular entry point, twice in a row (the second call reuses the scratch the first
-one left behind).  It lives in the last-collected file so that a run stopping at the first failure has already
-run everything else.
+it gives the same answer as the regular entry point and as the fp32 reference, twice in a row (the second call
+reuses the scratch the first one left behind), and that the status word reads back clean.
 """
 
 import ctypes as C
@@ -49,6 +48,12 @@ def test_noalloc_entry_matches_regular_entry_twice():
         assert torch.cuda.memory_allocated() == before
         assert_close(got, want, rel=2e-2, what=f"no-alloc call {call}")
         assert torch.equal(got, want), "same kernel, same split order: results must be identical"
+        exact = ref.fp8_gemm(xq.cpu(), xs.cpu(), wq.cpu(), wsc.cpu(), residual=res.cpu())
+        assert_close(got.cpu(), exact, rel=2e-2, what=f"no-alloc call {call} vs fp32 reference")
+        status = C.c_int(-1)
+        st = lib.mfq_fp8_gemm_noalloc_status
+        st.restype, st.argtypes = C.c_int, [C.POINTER(C.c_int), C.c_void_p]
+        assert st(C.byref(status), torch.cuda.current_stream().cuda_stream) == 0 and status.value == 0
 
 
 def test_noalloc_entry_rejects_oversized_problem():

@@ -100,6 +100,36 @@ def main() -> None:
     torch.cuda.synchronize()
     Workspace.get(dev).check()
 
+    # fused all-reduce + residual + RMSNorm + FP8 quantization over peer memory, one-shot and two-shot, eager and replayed
+    hid = 512
+    st = tp.stream(hid)
+    norm_w = (torch.rand(hid, generator=g, device=dev) + 0.5).to(torch.bfloat16)
+    fr_h_exact, fr_q_err = True, 0.0
+    for m_rows in (1, 24, 8 * world + 3, 200):
+        for it in range(3):
+            gr = torch.Generator(device=dev).manual_seed(100 * m_rows + 10 * it + rank)
+            part = torch.randn((m_rows, hid), generator=gr, device=dev).to(torch.bfloat16)
+            h0 = torch.randn((m_rows, hid), generator=torch.Generator(device=dev).manual_seed(7 + it), device=dev).to(torch.bfloat16)
+            hbuf = st.h_rows(m_rows)
+            hbuf.copy_(h0)
+            tp.barrier()  # every rank's residual rows are in place before a peer may push into them
+            st.partial_out(m_rows).copy_(part)
+            _, xq_f, xs_f = st.reduce(m_rows, hbuf, norm_w, 1e-5)
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part)
+            total = torch.zeros((m_rows, hid), device=dev)
+            for p_ in parts:
+                total = total + p_.float()
+            h_want = (total + h0.float()).to(torch.bfloat16)
+            fr_h_exact = fr_h_exact and bool(torch.equal(hbuf, h_want))
+            q_w, s_w, _, _ = ref.rmsnorm_quant(h_want, norm_w, 1e-5)
+            got_x = xq_f.float() * xs_f[:, None]
+            want_x = q_w.float() * s_w[:, None]
+            fr_q_err = max(fr_q_err, float((got_x - want_x).abs().max() / want_x.abs().max()))
+    result["fused_reduce_h_exact"], result["fused_reduce_q_err"] = fr_h_exact, fr_q_err
+    torch.cuda.synchronize()
+    Workspace.get(dev).check()
+
     # expert parallelism: routed experts split over the ranks, shared expert and attention tensor-parallel
     from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
     from mfq_b200.models.moe_lm import MoeConfig, init_weights, quantize_moe_checkpoint
