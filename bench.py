@@ -117,6 +117,11 @@ def run_ours(args) -> dict:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def phase(name: str) -> None:  # progress on stderr: a run that stops shows where
+        if rank == 0:
+            print(f"[bench] {name} t={time.time() - t_start:.1f}s", file=sys.stderr, flush=True)
+    t_start = time.time()
+
     def max_over_ranks(ms: float) -> float:
         if world == 1:
             return ms
@@ -129,8 +134,10 @@ def run_ours(args) -> dict:
     prompts = [torch.randint(0, cfg.vocab_size, (ctx,), generator=gen) for _ in range(batch)]
 
     # ---- prefill: warm once on row 0, time one 4096-token prompt, then fill every row ----
+    phase("weights ready")
     engine.prefill(0, prompts[0])
     barrier()
+    phase("first prefill done")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     engine.prefill(0, prompts[0])
@@ -143,6 +150,7 @@ def run_ours(args) -> dict:
         engine.grow(row, ctx + 2 * new + 8)
     barrier()
     ops.Workspace.get(dev).check()
+    phase("all rows prefilled")
 
     def timed_decode(b: int, steps: int, warmup: int):
         for _ in range(warmup):
@@ -159,8 +167,12 @@ def run_ours(args) -> dict:
         return max_over_ranks(a.elapsed_time(z)), clocks.summary()
 
     ms64, clocks = timed_decode(batch, args.steps, args.warmup)
+    ops.Workspace.get(dev).check()
+    phase("batched decode timed")
     launches = engine.launches_per_step.get(batch, 0) * args.steps
     ms1, _ = timed_decode(1, args.steps, args.warmup)
+    ops.Workspace.get(dev).check()
+    phase("single-stream decode timed")
     engine_launches = dict(engine.launches_per_step)
 
     # ---- end to end through the public step API: pinned H2D of the inputs + D2H of the result every step ----
@@ -180,6 +192,7 @@ def run_ours(args) -> dict:
     barrier()
     e2e_ms = max_over_ranks(a.elapsed_time(z))
     ops.Workspace.get(dev).check()
+    phase("end-to-end timed")
 
     # ---- the same tensor-parallel model with library collectives (unfused GEMM + NCCL all-reduce), for comparison ----
     nccl = {}
@@ -188,8 +201,10 @@ def run_ours(args) -> dict:
             from mfq_b200.parallel.tensor_parallel import NcclTensorParallel
             del engine
             torch.cuda.empty_cache()
+            # eager launches: library collectives are kept out of CUDA-graph capture here
             base = LLMEngine(LlamaModel(cfg, weights, collective=NcclTensorParallel(dist.group.WORLD, dev)), max_batch=batch,
-                             max_seq_len=ctx + 2 * new + 16)
+                             max_seq_len=ctx + 2 * new + 16, use_graphs=False)
+            phase("library-collective engine built")
             for row in range(batch):
                 base.prefill(row, prompts[row][: min(ctx, 512)])  # timing only: a short context fills the rows faster
                 base.grow(row, ctx + 2 * new + 8)
@@ -201,7 +216,8 @@ def run_ours(args) -> dict:
             n1, _ = timed_decode(1, args.steps, args.warmup)
             nccl = {"nccl_baseline_decode_tok_s_bs64": round(batch * args.steps / (n64 / 1e3), 2),
                     "nccl_baseline_decode_tok_s_bs1": round(args.steps / (n1 / 1e3), 2),
-                    "nccl_baseline_note": "same model and kernels, row-parallel sums through ncclAllReduce after an unfused GEMM"}
+                    "nccl_baseline_note": "same model and kernels, row-parallel sums through ncclAllReduce after an unfused "
+                                          "GEMM, eager launches (no CUDA graph)"}
         except Exception as exc:  # the comparison is optional: report why it is missing
             nccl = {"nccl_baseline_error": repr(exc)[:200]}
 

@@ -37,7 +37,9 @@ struct GemmCfg {
   static constexpr int kCols = BT / (kEpiWarps / 4);   // token columns per epilogue thread
   static constexpr int kThreads = 64 + 32 * kEpiWarps;
   static constexpr int kXsBytes = kEpiWarps * kCols * 4;  // per-warp copy of the row multipliers of its token columns
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kXsBytes;
+  static constexpr int kWsMax = 256;                      // weight-block multipliers of a CTA's K range kept in smem, per warp
+  static constexpr int kWsBytes = kEpiWarps * kWsMax * 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kXsBytes + kWsBytes;
 };
 
 // Cross-rank all-reduce context of the fused epilogue (world == 1: disabled).
@@ -296,6 +298,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     if (!gather) {
       for (int j = lane; j < CW; j += 32) xs_w[j] = (t0 + col0 + j < row_end) ? __ldg(p.x_scale + t0 + col0 + j) : 0.f;
     }
+    // The weight-block multipliers of this CTA's K range, likewise: a global load per K block would sit, exposed, on
+    // the chain wait -> TMEM load -> FMA that every block goes through (it was the longest link of that chain).
+    float* ws_w = xs_smem + Cfg::kEpiWarps * CW + (warp - 2) * Cfg::kWsMax;
+    const bool ws_cached = nkb <= Cfg::kWsMax;
+    if (ws_cached) {
+      for (int j = lane; j < nkb; j += 32) ws_w[j] = __ldg(wsc + kb0 + j);
+    }
+    __syncwarp();
     bool ok = true;
     for (int i = 0; i < nkb; ++i) {
       const int buf = i % Cfg::kAcc;
@@ -303,7 +313,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const float s = __ldg(wsc + kb0 + i);
+      const float s = ws_cached ? ws_w[i] : __ldg(wsc + kb0 + i);
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * BT + col0;
       if constexpr (CW == 64) {
         uint32_t r0[32], r1[32];
@@ -568,7 +578,7 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
     if (forced > 0) p.stages = forced < Cfg::kStages ? (forced < 2 ? 2 : forced) : Cfg::kStages;
     else if (ctas > 148 && BT <= 64) p.stages = kb_per < 4 ? (kb_per < 2 ? 2 : kb_per) : 4;
   }
-  const int smem_bytes = p.stages * Cfg::kStageBytes + 1024 + 256 + Cfg::kXsBytes;
+  const int smem_bytes = p.stages * Cfg::kStageBytes + 1024 + 256 + Cfg::kXsBytes + Cfg::kWsBytes;
   launch_kernel(fp8_gemm_kernel<BT>, dim3(n_tiles + extra_x, t_tiles, splits), dim3(Cfg::kThreads), smem_bytes, stream, tw, tx, tx_alt, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }

@@ -65,4 +65,6 @@ def test_moe_ffn_matches_reference(t, e, k, e_lo, e_hi):
         hq, hs = ref.silu_mul_quant(gu)
         y = ((hq.float() * hs[:, None]) @ ref.dequant_block(dn_q[le], dn_s[le]).T).to(torch.bfloat16).float()
         want.index_add_(0, tok, y * wt[tok, slot][:, None])
-    assert_close(got, want, rel=2e-2, what="moe ffn")
+    # the SwiGLU output is re-quantized to E4M3 between the two GEMMs: a bf16 ulp of difference there flips a code now
+    # and then, which moves single outputs by more than the element-wise bound
+    assert_close(got, want, rel=2e-2, what="moe ffn", outliers=5e-3)
