@@ -65,7 +65,7 @@ def bench_gemm(m: int, n: int, k: int, reps: int, splits=None, tile=None) -> dic
     out = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
     ms = time_ms(lambda i: K.fp8_gemm(x, xs, w[i % copies], ws, out=out, splits=splits, token_tile=tile), reps)
     byt = n * k + m * k + 2 * m * n
-    gemv = m <= K.GEMV_MAX_ROWS and n % 16 == 0 and splits is None and tile is None and K.gemv_enabled()
+    gemv = splits is None and tile is None and K.use_gemv(m, n, k)
     return {"kernel": "fp8_gemv" if gemv else "fp8_gemm", "m": m, "n": n, "k": k, "us": ms * 1e3, "gbs": byt / ms / 1e6,
             "tflops": 2 * m * n * k / ms / 1e9, "splits": splits if splits else K.pick_splits(m, n, k)}
 
@@ -144,12 +144,15 @@ def main() -> None:
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--only", default="", help="comma separated kernel families: gemm,w4,attn,small,prefill")
+    ap.add_argument("--tp", type=int, default=1, help="time one rank's shard of a tensor-parallel group of this size")
     args = ap.parse_args()
     pk = peaks()
     rows = []
     only = set(filter(None, args.only.split(",")))
     want = lambda family: not only or family in only
-    shapes = [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336), ("lm_head", 128256, 4096)]
+    tp = args.tp
+    shapes = [("qkv", 6144 // tp, 4096), ("o_proj", 4096, 4096 // tp), ("gate_up", 28672 // tp, 4096), ("down", 4096, 14336 // tp),
+              ("lm_head", 128256 // tp, 4096)]
     for m in ((1, 64) if args.quick else (1, 16, 64, 512, 4096)) if want("gemm") else ():
         for name, n, k in shapes:
             if name == "lm_head" and m > 64:
@@ -158,7 +161,7 @@ def main() -> None:
             r["name"] = name
             rows.append(r)
             if r["kernel"] == "fp8_gemv":  # the tcgen05 GEMM on the same shape, for comparison
-                r = bench_gemm(m, n, k, args.reps, splits=K.pick_splits(m, n, k), tile=16)
+                r = bench_gemm(m, n, k, args.reps, splits=K.pick_splits(m, n, k), tile=K._token_tile(m))
                 r["name"] = name
                 rows.append(r)
     for m in ((1, 64) if args.quick else (1, 16, 64, 512, 4096)) if want("w4") else ():
@@ -167,8 +170,8 @@ def main() -> None:
             r["name"] = name
             rows.append(r)
     for batch, ctx in ((1, 4096), (64, 4096)) if want("attn") else ():
-        for splits in (1, 4, K.attn_splits_for(batch, 8, ctx)):
-            rows.append(bench_attn(batch, ctx, 32, 8, 128, splits, args.reps))
+        for splits in sorted({1, 4, K.attn_splits_for(batch, max(1, 8 // tp), ctx)}):
+            rows.append(bench_attn(batch, ctx, 32 // tp, max(1, 8 // tp), 128, splits, args.reps))
         # 256-wide heads of the hybrid model: 16 query heads on 2 KV heads
         rows.append(bench_attn(batch, ctx, 16, 2, 256, K.attn_splits_for(batch, 2, ctx), args.reps))
     for m in (1, 64, 4096) if want("small") else ():

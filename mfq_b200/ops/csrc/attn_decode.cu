@@ -23,7 +23,6 @@
 
 namespace mfq {
 
-constexpr int kAttnStages = 3;
 constexpr float kNeg = -1e30f;
 
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -48,16 +47,17 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int D>
+template <int D, int kAttnStages>
 struct AttnSmem {
   static constexpr int kPageBytes = 16 * D;                    // one head's K (or V) page
   static constexpr int kStageBytes = 2 * kPageBytes + 128;     // K, V, k scales, v scales
-  static constexpr int kWarpBytes = kAttnStages * kStageBytes;
+  static constexpr int kWarpBytes = kAttnStages * kStageBytes;  // also the merge scratch: needs >= 16*D*4 + 128
   static constexpr int kTotal = 4 * kWarpBytes + 4 * kAttnStages * 8 + 16;
 };
 
-template <int D>
-__global__ void __launch_bounds__(128)
+// kAttnStages: pages in flight per warp; kMinBlocks: CTAs per SM the register allocation is held to.
+template <int D, int kAttnStages, int kMinBlocks>
+__global__ void __launch_bounds__(128, kMinBlocks)
 paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t* __restrict__ k_cache,
                              const uint8_t* __restrict__ v_cache, const float* __restrict__ k_scale,
                              const float* __restrict__ v_scale, const int* __restrict__ block_table,
@@ -66,7 +66,7 @@ paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t*
                              float scale_log2, int q_len, int* status) {
   pdl_trigger();
   pdl_wait();
-  using L = AttnSmem<D>;
+  using L = AttnSmem<D, kAttnStages>;
   constexpr int KSTEPS = D / 16, NBD = D / 8;
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -114,7 +114,8 @@ paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t*
   for (int half = 0; half < 2; ++half) {
     const int r = g8 + 8 * half;
     const int qr = r / G, g = r % G;
-    row_len[half] = r < R ? len - (q_len - 1 - qr) : 0;
+    // rows beyond R carry a zero query and are never stored: leaving them unmasked keeps `full` below warp-uniform
+    row_len[half] = r < R ? len - (q_len - 1 - qr) : 0x7fffffff;
     const __nv_bfloat16* qp = q + ((size_t(seq) * q_len + qr) * Hq + kvh * G + g) * D;
 #pragma unroll
     for (int s = 0; s < KSTEPS; ++s) {
@@ -165,19 +166,19 @@ paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t*
       }
     }
     // ---- scales, causal mask, online softmax (rows g8 and g8+8; columns nb*8 + 2c, +1) ----
+    // A page that lies wholly inside both rows' causal ranges (every page but the last one or two) needs no mask.
+    const bool full = tok0 + 16 <= min(row_len[0], row_len[1]);
     float p[2][4];
     float mx[2] = {kNeg, kNeg};
-    bool valid[2][4];
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb) {
       const int tk = nb * 8 + 2 * c;
-      const float ks0 = sKs[tk], ks1 = sKs[tk + 1];
+      const float2 ks = *reinterpret_cast<const float2*>(sKs + tk);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int half = e >> 1;
-        const int t = tok0 + tk + (e & 1);
-        valid[nb][e] = t < row_len[half];
-        sc[nb][e] = valid[nb][e] ? sc[nb][e] * ((e & 1) ? ks1 : ks0) : kNeg;
+        sc[nb][e] *= (e & 1) ? ks.y : ks.x;
+        if (!full && tok0 + tk + (e & 1) >= row_len[half]) sc[nb][e] = kNeg;
         mx[half] = fmaxf(mx[half], sc[nb][e]);
       }
     }
@@ -194,23 +195,29 @@ paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t*
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb) {
       const int tk = nb * 8 + 2 * c;
-      const float vs0 = sVs[tk], vs1 = sVs[tk + 1];
+      const float2 vs = *reinterpret_cast<const float2*>(sVs + tk);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int half = e >> 1;
-        const float pe = valid[nb][e] ? exp2f(sc[nb][e] - m_run[half]) : 0.f;
+        // a masked score is kNeg: exp2 gives 0 unless the whole row is still empty (m_run == kNeg), hence the test
+        const float pe = sc[nb][e] > 0.5f * kNeg ? exp2f(sc[nb][e] - m_run[half]) : 0.f;
         psum[half] += pe;
-        p[nb][e] = pe * ((e & 1) ? vs1 : vs0);  // fold the V multiplier of that token into P
+        p[nb][e] = pe * ((e & 1) ? vs.y : vs.x);  // fold the V multiplier of that token into P
       }
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) l_run[half] = l_run[half] * corr[half] + psum[half];
     const uint32_t pa[4] = {pack_f16x2(p[0][0], p[0][1]), pack_f16x2(p[0][2], p[0][3]),
                             pack_f16x2(p[1][0], p[1][1]), pack_f16x2(p[1][2], p[1][3])};
-    // ---- O = O * corr + P V ----
+    // ---- O = O * corr + P V; the rescale is skipped (warp-uniformly) while no row maximum moved, the usual case
+    //      once the first pages of a long context have been seen ----
+    const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
+    if (rescale) {
+#pragma unroll
+      for (int j = 0; j < NBD; ++j) { o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1]; }
+    }
 #pragma unroll
     for (int j = 0; j < NBD; ++j) {
-      o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
       const uint32_t vw = *reinterpret_cast<const uint32_t*>(sV + (8 * j + g8) * 16 + 4 * c);
       mma_f16(o[j], pa, e4m3x2_to_f16x2(uint16_t(vw & 0xffffu)), e4m3x2_to_f16x2(uint16_t(vw >> 16)));
     }
@@ -282,20 +289,23 @@ __global__ void attn_reduce_log2_kernel(const float* __restrict__ part_acc, cons
   out[hq * D + d] = __float2bfloat16(ll > 0.f ? a / ll : 0.f);
 }
 
-template <int D>
-static int launch_attn(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
-                       const float* v_scale, const int* block_table, const int* seq_lens, void* out, float* part_acc,
-                       float* part_ml, int B, int Hq, int Hk, int max_pages, float sm_scale, int splits, int q_len,
-                       int* status, cudaStream_t stream) {
-  using L = AttnSmem<D>;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(paged_attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
+template <int D, int kAttnStages, int kMinBlocks>
+static int launch_attn_v(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                         const float* v_scale, const int* block_table, const int* seq_lens, void* out, float* part_acc,
+                         float* part_ml, int B, int Hq, int Hk, int max_pages, float sm_scale, int splits, int q_len,
+                         int* status, cudaStream_t stream) {
+  using L = AttnSmem<D, kAttnStages>;
+  static_assert(L::kWarpBytes >= 16 * D * 4 + 128, "the per-warp ring doubles as the merge scratch");
+  static bool attr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -6;
+  if (!attr[dev]) {
+    if (cudaFuncSetAttribute(paged_attn_decode_mma_kernel<D, kAttnStages, kMinBlocks>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
       return -6;
-    attr = true;
+    attr[dev] = true;
   }
   const float scale_log2 = sm_scale * 1.4426950408889634f;
-  launch_kernel(paged_attn_decode_mma_kernel<D>, dim3(B, Hk, splits), dim3(128), L::kTotal, stream, 
+  launch_kernel(paged_attn_decode_mma_kernel<D, kAttnStages, kMinBlocks>, dim3(B, Hk, splits), dim3(128), L::kTotal, stream, 
       static_cast<const __nv_bfloat16*>(q), static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache),
       k_scale, v_scale, block_table, seq_lens, static_cast<__nv_bfloat16*>(out), part_acc, part_ml, Hq, Hk, max_pages,
       scale_log2, q_len, status);
@@ -305,6 +315,24 @@ static int launch_attn(const void* q, const void* k_cache, const void* v_cache, 
     if (cudaGetLastError() != cudaSuccess) return -7;
   }
   return 0;
+}
+
+template <int D>
+static int launch_attn(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                       const float* v_scale, const int* block_table, const int* seq_lens, void* out, float* part_acc,
+                       float* part_ml, int B, int Hq, int Hk, int max_pages, float sm_scale, int splits, int q_len,
+                       int* status, cudaStream_t stream) {
+  // MFQ_ATTN_VARIANT (measurement switch): 0 = 3 pages in flight per warp, 3 CTAs per SM; 1 = 4 pages, 3 CTAs;
+  // 2 = 3 pages, 4 CTAs (128 registers); 3 = 6 pages, 2 CTAs
+  static const int variant = [] { const char* e = getenv("MFQ_ATTN_VARIANT"); return e ? atoi(e) : 0; }();
+#define MFQ_ATTN_ARGS q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_acc, part_ml, B, Hq, Hk, max_pages, sm_scale, splits, q_len, status, stream
+  if constexpr (D <= 128) {
+    if (variant == 1) return launch_attn_v<D, 4, 3>(MFQ_ATTN_ARGS);
+    if (variant == 2) return launch_attn_v<D, 3, 4>(MFQ_ATTN_ARGS);
+    if (variant == 3) return launch_attn_v<D, 6, 2>(MFQ_ATTN_ARGS);
+  }
+  return launch_attn_v<D, 3, (D <= 128 ? 3 : 1)>(MFQ_ATTN_ARGS);
+#undef MFQ_ATTN_ARGS
 }
 
 }  // namespace mfq

@@ -1,5 +1,6 @@
-// Weight-streaming block-scaled FP8 GEMV / skinny GEMM for 1..16 token rows (single-stream decode, speculative
-// verify windows, and the per-expert tiles of a decode-sized MoE step).
+// Weight-streaming block-scaled FP8 GEMV / skinny GEMM for 1..64 token rows (single-stream decode, speculative
+// verify windows, the per-expert tiles of a decode-sized MoE step, and -- with 32 or 64 rows -- the small per-rank
+// projections of a tensor-parallel decode step, where a tcgen05 pipeline would spend longer filling than working).
 //
 // With this few rows the product is pure weight streaming and what counts is latency: no tensor maps, no TMEM, no
 // pipeline to fill.  A CTA owns 16 output rows; its eight warps split the K range by 128-wide blocks.  A thread reads
@@ -45,7 +46,7 @@ constexpr int kWarps = 8;  // K-split inside a CTA
 // the kWarps / RG warps of a group split K.  Expert tiles use RG = 2: a CTA's life is a chain of dependent loads
 // (tile map, offsets, weights), so it has to carry enough bytes to be worth that latency.
 template <int NB, int RG>
-__global__ void __launch_bounds__(kWarps * 32, 2) fp8_gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kWarps * 32, (NB <= 2 ? 2 : 1)) fp8_gemv_kernel(const GemvParams p) {
   pdl_trigger();
   constexpr int kSplit = kWarps / RG;
   __shared__ float part[kWarps][16][NB * 8];
@@ -161,20 +162,22 @@ static int launch_gemv(const GemvParams& p, int tiles, int nb, cudaStream_t stre
   } else {
     const dim3 grid(p.N / 16, tiles);
     if (nb == 1) launch_kernel(fp8_gemv_kernel<1, 1>, grid, dim3(kWarps * 32), 0, stream, p);
-    else launch_kernel(fp8_gemv_kernel<2, 1>, grid, dim3(kWarps * 32), 0, stream, p);
+    else if (nb == 2) launch_kernel(fp8_gemv_kernel<2, 1>, grid, dim3(kWarps * 32), 0, stream, p);
+    else if (nb <= 4) launch_kernel(fp8_gemv_kernel<4, 1>, grid, dim3(kWarps * 32), 0, stream, p);
+    else launch_kernel(fp8_gemv_kernel<8, 1>, grid, dim3(kWarps * 32), 0, stream, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 
 }  // namespace mfq
 
-// out[M, N] = x_scale[m] * sum over 128-blocks of w_scale * (x_q . w_q) (+ residual), M <= 16, N % 16 == 0, K % 128 == 0.
+// out[M, N] = x_scale[m] * sum over 128-blocks of w_scale * (x_q . w_q) (+ residual), M <= 64, N % 16 == 0, K % 128 == 0.
 extern "C" int mfq_fp8_gemv(const void* w, const float* w_scale, const void* x, const float* x_scale, void* out,
                             const void* residual, int M, int N, int K, cudaStream_t stream) {
-  if (M <= 0 || M > 16 || N % 16 || K % 128 || N <= 0) return -1;
+  if (M <= 0 || M > 64 || N % 16 || K % 128 || N <= 0) return -1;
   mfq::GemvParams p{static_cast<const uint8_t*>(w), w_scale, static_cast<const uint8_t*>(x), x_scale,
                     static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(residual), M, N, K, nullptr, nullptr, nullptr};
-  return mfq::launch_gemv(p, 1, M <= 8 ? 1 : 2, stream);
+  return mfq::launch_gemv(p, 1, (M + 7) / 8, stream);
 }
 
 // Grouped form for expert-sorted rows: tile_map entries are (expert, 16-row tile) as the route plan writes them with a

@@ -12,14 +12,21 @@ from .lib import Workspace, check, lib, ptr, stream_ptr
 FP8 = torch.float8_e4m3fn
 
 
-GEMV_MAX_ROWS = 16  # up to this many rows the weight-streaming kernel (fp8_gemv.cu) replaces the tcgen05 GEMM
+GEMV_MAX_ROWS = 16  # up to this many rows the weight-streaming kernel (fp8_gemv.cu) always replaces the tcgen05 GEMM
+GEMV_WIDE_ROWS = 64  # ... and up to this many when the weight matrix is small (see use_gemv)
 
 
-def gemv_enabled() -> bool:
-    """``MFQ_GEMV=0`` in the environment sends every shape through the tcgen05 GEMM (A/B measurements)."""
-    import os
-    from ..config import current
-    return current().gemv
+def use_gemv(m: int, n: int, k: int) -> bool:
+    """Whether ``[m, k] x [n, k]^T`` goes to the weight-streaming kernel: always for up to 16 rows; for up to 64 rows
+    only when the output is a few tiles wide and the matrix small (a tensor-parallel rank's q/k/v shard), where the
+    tcgen05 path would need a deep split-K whose reduction costs more than the product.  Measured on B200 at 64 rows:
+    768 x 4096 takes 11.1 us here against 14.7 us there; from 3072 x 4096 up the tcgen05 path wins (the legacy
+    ``mma.sync`` pipe this kernel uses runs at a fraction of the tcgen05 rate)."""
+    if n % 16 or not gemv_enabled():
+        return False
+    if m <= GEMV_MAX_ROWS:
+        return True
+    return m <= GEMV_WIDE_ROWS and n <= 1024 and n * k <= (4 << 20)
 
 
 def _token_tile(m: int) -> int:
@@ -59,7 +66,7 @@ def fp8_gemm(x_q: torch.Tensor, x_scale: torch.Tensor, w_q: torch.Tensor, w_scal
     assert w_scale.shape == (math.ceil(n / 128), k // 128) and w_scale.is_contiguous()
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=x_q.device)
-    if m <= GEMV_MAX_ROWS and n % 16 == 0 and splits is None and token_tile is None and gemv_enabled():
+    if splits is None and token_tile is None and use_gemv(m, n, k):
         rc = lib().mfq_fp8_gemv(ptr(w_q), ptr(w_scale), ptr(x_q), ptr(x_scale), ptr(out), ptr(residual), m, n, k, stream_ptr())
         check(rc, "fp8_gemv")
         return out

@@ -62,10 +62,13 @@ def test_fp8_gemm_all_token_tiles():
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 128), (1, 4096, 4096), (4, 6144, 2048), (8, 2048, 14336), (9, 272, 1024),
-                                   (16, 1040, 512), (2, 151936, 256)])
+                                   (16, 1040, 512), (2, 151936, 256), (17, 768, 4096), (32, 1024, 512), (47, 512, 1024),
+                                   (64, 768, 4096), (64, 16, 128)])
 def test_weight_streaming_gemv_matches_reference(m, n, k):
-    """Rows <= 16 without explicit tiling take the mma.sync weight-streaming kernel (residual add in place included)."""
+    """Rows <= 16 (and up to 64 rows on small matrices) without explicit tiling take the mma.sync weight-streaming
+    kernel (residual add in place included)."""
     require_gpu_lib()
+    assert ops.kernels.use_gemv(m, n, k)
     xq, xs, wq, ws = make(m, n, k, seed=3 * m + n)
     res = torch.randn((m, n), device="cuda").to(torch.bfloat16)
     want = ref.fp8_gemm(xq, xs, wq, ws, residual=res)
