@@ -16,6 +16,12 @@ GEMV_MAX_ROWS = 16  # up to this many rows the weight-streaming kernel (fp8_gemv
 GEMV_WIDE_ROWS = 64  # ... and up to this many when the weight matrix is small (see use_gemv)
 
 
+def gemv_enabled() -> bool:
+    """``MFQ_GEMV=0`` in the environment sends every shape through the tcgen05 GEMM (A/B measurements)."""
+    from ..config import current
+    return current().gemv
+
+
 def use_gemv(m: int, n: int, k: int) -> bool:
     """Whether ``[m, k] x [n, k]^T`` goes to the weight-streaming kernel: always for up to 16 rows; for up to 64 rows
     only when the output is a few tiles wide and the matrix small (a tensor-parallel rank's q/k/v shard), where the
