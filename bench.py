@@ -278,7 +278,8 @@ def run_hybrid(args) -> dict:
     batch, ctx, new = args.batch, args.context, args.steps + args.warmup + 8
     use_mtp = world == 1  # draft/verify cycles are measured on one GPU only
     t0 = time.time()
-    weights = random_hybrid_weights(cfg, dev, seed=0, mtp=use_mtp, tp_rank=rank, tp_size=world)
+    weights = random_hybrid_weights(cfg, dev, seed=0, mtp=use_mtp, tp_rank=rank, tp_size=world,
+                                    expert_format="packed" if args.weights == "packed" else "fp8")
     torch.cuda.synchronize()
     build_s = time.time() - t0
     engine = LLMEngine(HybridModel(cfg, weights, collective=collective), max_batch=batch, max_seq_len=ctx + 4 * new + 16,
@@ -347,6 +348,7 @@ def run_hybrid(args) -> dict:
         "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)", "impl": "ours",
         "config": {"model": cfg.name, "global_batch": batch, "seq_len": ctx, "parallelism": f"tp{world}+ep{world}" if world > 1 else "dp1",
                    "weights_gb": round(weights.nbytes() / 1e9, 1) if hasattr(weights, "nbytes") else None,
+                   "experts": "packed NINT2-5 / MXFP4 mix, decoded in registers" if args.weights == "packed" else "block FP8",
                    "l2": "inputs larger than L2 (the routed experts of a step alone exceed it)"},
         "clocks": clocks,
         "extra": {"decode_tok_s_bs1": round(args.steps / (ms1 / 1e3), 2), "ms_per_step_bs1": round(ms1 / args.steps, 4),
@@ -385,8 +387,10 @@ def main() -> None:
                          "batch fixed (strong scaling); dp = one replica per GPU, batch per GPU fixed (weak scaling)")
     ap.add_argument("--nccl-baseline", action="store_true",
                     help="tp: also time the same model with library (NCCL) collectives after unfused GEMMs (under extra)")
-    ap.add_argument("--weights", choices=["fp8", "w4"], default="fp8",
-                    help="block linears in block-scaled FP8 (default) or in the 4-bit NINT-native format (single GPU)")
+    ap.add_argument("--weights", choices=["fp8", "w4", "packed"], default="fp8",
+                    help="block linears in block-scaled FP8 (default) or in the 4-bit NINT-native format (single GPU); "
+                         "hybrid80b: 'packed' keeps the routed experts in a seeded mix of packed NINT 2-5 bit / MXFP4 "
+                         "codes (about 3.4 bits per weight) decoded inside the expert kernels")
     ap.add_argument("--tiny", action="store_true", help="tiny model, for checking the harness itself")
     ap.add_argument("--model", choices=["llama8b", "hybrid80b"], default="llama8b",
                     help="llama8b: the flagship; hybrid80b: the Gated-DeltaNet + MoE hybrid with an MTP head (one GPU)")

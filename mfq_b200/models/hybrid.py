@@ -21,6 +21,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -202,12 +203,16 @@ def _quant_stack(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
 
 
 def random_hybrid_weights(cfg: HybridConfig, device, seed: int = 0, std: float = 0.02, mtp: bool = False,
-                          expert_chunk: int = 64, tp_rank: int = 0, tp_size: int = 1) -> HybridWeights:
+                          expert_chunk: int = 64, tp_rank: int = 0, tp_size: int = 1, expert_format: str = "fp8") -> HybridWeights:
     """N(0, std) weights drawn and quantized to block FP8 on ``device``, layer by layer.  Only one chunk of
     ``expert_chunk`` experts exists in float at a time, so the 80B configuration builds inside its FP8 footprint.
     Under tensor / expert parallelism every rank draws the (small) dense matrices in full from the common stream and keeps
     its slice, and draws only its own experts, each chunk from a generator seeded by the chunk's global position: all
-    ranks hold shards of one and the same model, whatever ``tp_size`` is."""
+    ranks hold shards of one and the same model, whatever ``tp_size`` is.
+
+    ``expert_format="packed"``: the routed experts are random payloads in the packed run-time layout instead
+    (``ops.packed.PackedExperts.synthetic``): every (expert, projection) draws its family from a seeded allocation
+    over NINT 2 / 3 / 4 / 5 bit and MXFP4 averaging about 3.4 bits per weight, and stays packed in HBM."""
     from .llama import MtpHead, kv_head_rows
     dev = torch.device(device)
     gen = torch.Generator(device=dev)
@@ -250,11 +255,26 @@ def random_hybrid_weights(cfg: HybridConfig, device, seed: int = 0, std: float =
             counter[0] += 1
         return torch.cat(qs), torch.cat(ss)
 
+    layer_no = [0]
+
+    def packed_experts(n, k, salt):
+        from ..ops import packed as packed_ops
+        # seeded allocation per (layer, expert, projection): 30 % NINT2, 30 % NINT3, 20 % NINT4, 10 % NINT5, 10 % MXFP4
+        rng = np.random.default_rng(seed * 1_000_003 + 101 * layer_no[0] + salt)
+        alloc = rng.choice([2, 3, 4, 5, 16], size=e, p=[0.3, 0.3, 0.2, 0.1, 0.1])
+        return packed_ops.PackedExperts.synthetic(e_per, n, k, alloc[r * e_per : (r + 1) * e_per], dev, gs=32,
+                                                  seed=seed * 7919 + 13 * layer_no[0] + salt, std=std)
+
     def moe():
-        gu_q, gu_s = experts(2 * mi, h)
-        dn_q, dn_s = experts(h, mi)
-        ffn = MoeFfn(router=rnd(e, h), router_bias=None, gate_up=gu_q, gate_up_scale=gu_s, down=dn_q, down_scale=dn_s,
-                     e_lo=r * e_per)
+        layer_no[0] += 1
+        if expert_format == "packed":
+            ffn = MoeFfn(router=rnd(e, h), router_bias=None, gate_up=None, gate_up_scale=None, down=None, down_scale=None,
+                         e_lo=r * e_per, packed_gate_up=packed_experts(2 * mi, h, 1), packed_down=packed_experts(h, mi, 2))
+        else:
+            gu_q, gu_s = experts(2 * mi, h)
+            dn_q, dn_s = experts(h, mi)
+            ffn = MoeFfn(router=rnd(e, h), router_bias=None, gate_up=gu_q, gate_up_scale=gu_s, down=dn_q, down_scale=dn_s,
+                         e_lo=r * e_per)
         if si:
             sg, su, sd = rnd(si, h), rnd(si, h), rnd(h, si)
             if w > 1 and (si // w) % 128 == 0:

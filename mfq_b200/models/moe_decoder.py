@@ -62,6 +62,9 @@ class MoeFfn:
     e_lo: int = 0
     residency: object | None = None  # ExpertResidency: experts live on the host, `gate_up`/`down` are its HBM arena
     shared_replicated: bool = False  # shared expert too narrow to shard on 128-wide blocks: every rank holds all of it
+    # routed experts kept in their packed checkpoint codes (ops.packed.PackedExperts); gate_up / down are then unused
+    packed_gate_up: object | None = None
+    packed_down: object | None = None
 
 
 @dataclass
@@ -83,12 +86,15 @@ class MoeWeights(LlamaWeights):
     @classmethod
     def from_tensors(cls, cfg: MoeDecoderConfig, tensors, device, tp_rank: int = 0, tp_size: int = 1,
                      expert_slots: int | None = None, native_4bit: bool = False, lp_rank: int = 0, lp_size: int = 1,
-                     layer_split=None) -> "MoeWeights":
+                     layer_split=None, packed_experts: bool = False) -> "MoeWeights":
         """Build rank-local FP8 weights from checkpoint tensors under canonical names (a dict or an ``MfqStore``).
         ``expert_slots`` < experts per rank keeps the routed experts in (pinned) host memory behind an HBM arena of
         that many slots (:class:`~mfq_b200.engine.expert_residency.ExpertResidency`); such a model decodes eagerly.
         ``native_4bit`` (single GPU): attention and dense-FFN projections stored as NINT (<= 4 code bits) or MXFP4 keep
-        their 4-bit codes and run through the in-pipeline-decode GEMM instead of being transcoded to FP8."""
+        their 4-bit codes and run through the in-pipeline-decode GEMM instead of being transcoded to FP8.
+        ``packed_experts`` (GPU): routed experts stored as MFE pools of NINT (group size 24 / 32) or MXFP4 keep their
+        packed codes in HBM and are decoded inside the expert kernels (``ops/packed.py``); a layer that holds an expert
+        of another family falls back to the FP8 transcode."""
         dev = torch.device(device)
         h, d, w = cfg.hidden_size, cfg.head_dim, tp_size
         hq, hk = cfg.num_heads, cfg.num_kv_heads
@@ -149,7 +155,19 @@ class MoeWeights(LlamaWeights):
                                                          kv_head_rows(get(qkv_names[2]), hk, d, tp_rank, w)], 0)),
                 o_proj=linear([p + "attention.output.weight"], lambda: cols(get(p + "attention.output.weight"), hq * d)),
                 mlp_norm=norm(p + "mlp.norm.weight"), gate_up=None, down=None)
-            if (p + "mlp.router.weight") in tensors:
+            packed_pair = None
+            if (p + "mlp.router.weight") in tensors and packed_experts and dev.type == "cuda" and expert_slots is None:
+                from ..ops import packed as packed_ops
+                mine = range(e_lo, e_lo + e_per)
+                pgu = packed_ops.pack_moe_projection([tensors[p + "mlp.experts.gate.weight"], tensors[p + "mlp.experts.up.weight"]], mine, dev)
+                pdn = packed_ops.pack_moe_projection([tensors[p + "mlp.experts.down.weight"]], mine, dev) if pgu is not None else None
+                packed_pair = (pgu, pdn) if pdn is not None else None
+            if packed_pair is not None:
+                bias_name = p + "mlp.router.bias"
+                ffn = MoeFfn(router=norm(p + "mlp.router.weight"), router_bias=get(bias_name) if bias_name in tensors else None,
+                             gate_up=None, gate_up_scale=None, down=None, down_scale=None, e_lo=e_lo,
+                             packed_gate_up=packed_pair[0], packed_down=packed_pair[1])
+            elif (p + "mlp.router.weight") in tensors:
                 gate = get(p + "mlp.experts.gate.weight")[e_lo : e_lo + e_per]
                 up = get(p + "mlp.experts.up.weight")[e_lo : e_lo + e_per]
                 down = get(p + "mlp.experts.down.weight")[e_lo : e_lo + e_per]
@@ -159,7 +177,8 @@ class MoeWeights(LlamaWeights):
                 ffn = MoeFfn(router=norm(p + "mlp.router.weight"),
                              router_bias=get(bias_name) if bias_name in tensors else None,
                              gate_up=gu_q, gate_up_scale=gu_s, down=dn_q, down_scale=dn_s, e_lo=e_lo)
-                if expert_slots is not None and expert_slots < e_per:
+            if (p + "mlp.router.weight") in tensors:
+                if packed_pair is None and expert_slots is not None and expert_slots < e_per:
                     from ..engine.expert_residency import ExpertResidency
                     ffn.residency = ExpertResidency(gu_q.cpu(), gu_s.cpu(), dn_q.cpu(), dn_s.cpu(), expert_slots, dev)
                     arena = ffn.residency.arena
@@ -206,6 +225,37 @@ class MoeWeights(LlamaWeights):
 class MoeDecoderModel(LlamaModel):
     """:class:`LlamaModel` whose FFN is a routed mixture of experts wherever the layer carries one."""
 
+    expert_parallel = None  # an ExpertParallel: token-sharded dispatch / combine for wide batches (see below)
+    ep_min_tokens = 0
+
+    def enable_expert_all_to_all(self, group, max_tokens: int, min_tokens: int | None = None) -> None:
+        """Route batches of at least ``min_tokens`` tokens (default 16 per rank) through the all-to-all: every rank
+        dispatches ITS slice of the tokens to the ranks that own their experts (FP8 rows pushed into the owners'
+        receive tables), runs its experts on what arrives and returns the weighted sums, instead of every rank gathering
+        rows of ALL tokens for its experts and the partial outputs being all-reduced.  Collective: call on every rank.
+        ``max_tokens``: the largest batch (tokens of the whole step) that will take this path."""
+        from ..parallel.expert_parallel import ExpertParallel
+        cfg = self.cfg
+        per_rank = -(-max_tokens // self.tp)
+        self.expert_parallel = ExpertParallel(group, self.w.embed.device, num_experts=cfg.num_experts, top_k=cfg.top_k,
+                                              hidden=cfg.hidden_size, max_tokens=per_rank)
+        self.ep_min_tokens = 16 * self.tp if min_tokens is None else min_tokens
+
+    def _ffn_all_to_all(self, h, ffn: MoeFfn, xq, xs, ids, wt, shared):
+        """Token-sharded expert layer: my slice of the rows goes through dispatch -> local experts -> combine, the
+        finished slices are gathered back into the replicated residual stream; the (tensor-parallel) shared expert's
+        partial sums are reduced as before."""
+        t, w, r = h.shape[0], self.tp, self.w.tp_rank
+        per = t // w
+        lo, hi = r * per, (r + 1) * per
+        ep = self.expert_parallel
+        mine = ep.moe_ffn(xq[lo:hi], xs[lo:hi], ids[lo:hi].contiguous(), wt[lo:hi].contiguous(), ffn.gate_up, ffn.gate_up_scale,
+                          ffn.down, ffn.down_scale, base=h[lo:hi], cap=per)
+        self.collective.allgather_rows(mine, out=h)
+        if shared is not None:
+            h = self.collective.allreduce_rows(shared, h)
+        return h
+
     def _ffn(self, h, layer):
         ffn = getattr(layer, "moe", None)
         if ffn is None:
@@ -225,6 +275,15 @@ class MoeDecoderModel(LlamaModel):
         if ffn.shared_gate_up is not None and not (ffn.shared_replicated and self.w.tp_rank != 0):
             sq, ss = ops.silu_mul_quant(ffn.shared_gate_up(xq, xs))
             shared = ffn.shared_down(sq, ss)  # this rank's partial of the shared expert (rank 0's whole, if replicated)
+        if ffn.packed_gate_up is not None:
+            # experts in their packed checkpoint codes: decoded in registers inside the expert products
+            from ..ops import packed as packed_ops
+            if self.tp == 1:
+                return packed_ops.moe_ffn_packed(y, ids, wt, ffn.packed_gate_up, ffn.packed_down, e_lo=ffn.e_lo, base=h,
+                                                 extra=shared, out=h)
+            partial = packed_ops.moe_ffn_packed(y, ids, wt, ffn.packed_gate_up, ffn.packed_down, e_lo=ffn.e_lo, base=None,
+                                                extra=shared)
+            return self.collective.allreduce_rows(partial, h)
         if ffn.residency is not None:
             # host-tier experts: translate expert -> arena slot (uploading what is missing), in waves if needed
             local = ids - ffn.e_lo
@@ -242,6 +301,10 @@ class MoeDecoderModel(LlamaModel):
         if self.tp == 1:
             return moe_ops.moe_ffn_fp8(xq, xs, ids, wt, ffn.gate_up, ffn.gate_up_scale, ffn.down, ffn.down_scale,
                                        e_lo=ffn.e_lo, base=h, extra=shared, out=h)
+        t = h.shape[0]
+        ep = self.expert_parallel
+        if ep is not None and t >= self.ep_min_tokens and t % self.tp == 0 and t // self.tp <= ep.cap_max:
+            return self._ffn_all_to_all(h, ffn, xq, xs, ids, wt, shared)
         partial = moe_ops.moe_ffn_fp8(xq, xs, ids, wt, ffn.gate_up, ffn.gate_up_scale, ffn.down, ffn.down_scale,
                                       e_lo=ffn.e_lo, base=None, extra=shared)
         return self.collective.allreduce_rows(partial, h)

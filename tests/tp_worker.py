@@ -150,6 +150,13 @@ def main() -> None:
     gathered = [torch.empty_like(ep_toks) for _ in range(world)]
     dist.all_gather(gathered, ep_toks)
     result["ep_ranks_agree"] = all(torch.equal(g, gathered[0]) for g in gathered)
+    # the same model with wide batches routed through the all-to-all (48 prompt tokens: 48 / world per rank)
+    a2a_model = MoeDecoderModel(mcfg, MoeWeights.from_tensors(mcfg, ck, dev, rank, world), collective=tp)
+    a2a_model.enable_expert_all_to_all(dist.group.WORLD, max_tokens=64, min_tokens=world)
+    a2a_engine = LLMEngine(a2a_model, max_batch=4, max_seq_len=128, use_graphs=False)
+    a2a_logits = prefill_logits(a2a_model, a2a_engine, prompt, dev)
+    result["ep_a2a_vs_replicated_max_err"] = float((a2a_logits - ep_logits).abs().max())
+    result["ep_a2a_vs_replicated_mean_err"] = float((a2a_logits - ep_logits).abs().mean())
     if world == 2:
         # hybrid model (Gated DeltaNet + gated attention + experts) with every head kind split over the two ranks
         from mfq_b200.models.hybrid import HybridConfig, HybridModel, HybridWeights, init_hybrid_weights
