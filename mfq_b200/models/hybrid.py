@@ -212,7 +212,7 @@ def random_hybrid_weights(cfg: HybridConfig, device, seed: int = 0, std: float =
 
     ``expert_format="packed"``: the routed experts are random payloads in the packed run-time layout instead
     (``ops.packed.PackedExperts.synthetic``): every (expert, projection) draws its family from a seeded allocation
-    over NINT 2 / 3 / 4 / 5 bit and MXFP4 averaging about 3.4 bits per weight, and stays packed in HBM."""
+    over NINT 2 / 3 / 4 / 5 bit and MXFP4 averaging about 3.4 bits per weight in HBM (2.9 code bits), and stays packed."""
     from .llama import MtpHead, kv_head_rows
     dev = torch.device(device)
     gen = torch.Generator(device=dev)
@@ -259,9 +259,10 @@ def random_hybrid_weights(cfg: HybridConfig, device, seed: int = 0, std: float =
 
     def packed_experts(n, k, salt):
         from ..ops import packed as packed_ops
-        # seeded allocation per (layer, expert, projection): 30 % NINT2, 30 % NINT3, 20 % NINT4, 10 % NINT5, 10 % MXFP4
+        # seeded allocation per (layer, expert, projection): 40 % NINT2, 35 % NINT3, 15 % NINT4, 5 % NINT5, 5 % MXFP4
+        # (2.9 code bits on average; with group codes and anchors about 3.4 bits per weight in HBM)
         rng = np.random.default_rng(seed * 1_000_003 + 101 * layer_no[0] + salt)
-        alloc = rng.choice([2, 3, 4, 5, 16], size=e, p=[0.3, 0.3, 0.2, 0.1, 0.1])
+        alloc = rng.choice([2, 3, 4, 5, 16], size=e, p=[0.4, 0.35, 0.15, 0.05, 0.05])
         return packed_ops.PackedExperts.synthetic(e_per, n, k, alloc[r * e_per : (r + 1) * e_per], dev, gs=32,
                                                   seed=seed * 7919 + 13 * layer_no[0] + salt, std=std)
 

@@ -15,9 +15,11 @@
 //     consecutive codes (aligned to their own size, a warp's loads of a plane being contiguous).  Inside those words code 2i sits in the low
 //     half-word and code 2i+1 at the same position of the high half-word, so ONE shift + ONE 3-input logic op pull a
 //     pair of codes out of a plane straight into the mantissa bits of two bf16 numbers (128 + q, exact), pre-shifted
-//     planes OR-ing on top; one bf16x2 subtract and one bf16x2 FMA (q * s - m) finish two weights;
+//     planes OR-ing on top; one bf16x2 subtract and one bf16x2 FMA ((q - z) * s - (m - z s)) finish two weights;
 //   * group parameters are one byte each (ls, lm), four groups per aligned word: with 16- and 24-wide groups a thread's
 //     32 codes always fall into two neighbouring groups of ONE such word; with 32-wide groups into exactly one group.
+//     Every int -> float and float -> bf16 step of the parameter arithmetic is done with integer / FMA-pipe instructions
+//     (magic-number conversions): the conversion unit runs at a quarter of the rate and bounded an earlier version;
 //
 // A warp owns 16 weight rows (one tile) and a slice of K; `mma.sync.m16n8k16` (bf16) takes the decoded pairs as its A
 // fragment and the token rows -- read with the same slot assignment, so any k order is the right one -- as B.  The
@@ -113,35 +115,97 @@ __device__ __forceinline__ uint32_t code_pair(const uint32_t (&w4)[4], const uin
   return q;
 }
 
-// Decodes the 16 pairs of one (row, unit) slice of a NINT row of width B into bf16x2 weights.  `unit_base`: first word
-// of the tile's unit, `slot` = row * 4 + quad thread.  s2[g] / nm2[g]: (s, s) and (-m, -m) of the thread's two groups;
-// runs u < n_first use group 0.
+// Where the group parameters of a thread's n-th run of 32 codes live: the aligned 4-group word `word4`, the first group
+// inside it `lg`, and how many of the run's four 8-code pieces belong to that first group (the rest to the next one).
+//   32-wide groups: run n is group n.   16-wide: groups 2n, 2n + 1.   24-wide: the run starts in group floor(4n / 3).
+__host__ __device__ inline int group_words(int gs, int units) {  // 4-group parameter words per row
+  return gs == 32 ? units : gs == 16 ? units * 2 : (units * 4 - 1) / 3 + 1;
+}
+__device__ __forceinline__ void group_of_run(int gs, int n, int& word4, int& lg, int& n_first) {
+  if (gs == 32) { word4 = n >> 2; lg = n & 3; n_first = 4; }
+  else if (gs == 16) { word4 = n >> 1; lg = (n & 1) * 2; n_first = 2; }
+  else { word4 = n / 3; lg = n % 3; n_first = 3 - lg; }
+}
+
+// Small unsigned integer (< 2^23) -> float without the conversion unit: the integer lands in the mantissa of 2^23.
+__device__ __forceinline__ float u2f(uint32_t v) { return __uint_as_float(0x4B000000u | v) - 8388608.f; }
+// float -> bf16 (round half up on the dropped bits) replicated into both halves, integer pipe only.
+__device__ __forceinline__ uint32_t bf16_twice(float f) {
+  const uint32_t u = __float_as_uint(f) + 0x8000u;
+  return __byte_perm(u, u, 0x3232);
+}
+
+// A group's affine terms.  w = q s - m is evaluated as (q - z) s - (m - z s) with the integer zero point z = round(m / s):
+// z is subtracted exactly together with the 128 of the bf16 trick, so the constant that is left is at most half a code
+// step and its bf16 rounding (like that of s, now multiplied by |q - z| instead of q) stays far below the step.  Any
+// integer z gives the same weight in exact arithmetic, so the approximate reciprocal only costs precision at ties.
+__device__ __forceinline__ void group_terms(float d, float dm, uint32_t ls, uint32_t lm, uint32_t& s2, uint32_t& nm2,
+                                            uint32_t& kz2) {
+  const float s = d * u2f(ls), m = dm * u2f(lm);
+  float zf = s > 0.f ? __fdividef(m, s) : 0.f;
+  zf = fminf(fmaxf(zf, 0.f), 127.f) + 12582912.f;  // 1.5 * 2^23: the add rounds to an integer in the low mantissa bits
+  const uint32_t z = __float_as_uint(zf) & 0x7Fu;
+  s2 = bf16_twice(s);
+  nm2 = bf16_twice(fmaf(zf - 12582912.f, s, -m));
+  kz2 = (0x4300u | z) * 0x10001u;  // bf16 128 + z, twice
+}
+
+// A thread's raw share of one unit: the plane words of its two rows (rows g8 and g8 + 8 of the tile) and their group
+// parameter words.  Loading is separate from decoding so that the next unit's loads are in flight while this one is
+// decoded and multiplied.  B: 1..8 = NINT code width, 16 = MXFP4.
 template <int B>
-__device__ __forceinline__ void decode_nint(const uint32_t* __restrict__ unit_base, int slot, const uint32_t (&s2)[2],
-                                            const uint32_t (&nm2)[2], int n_first, uint32_t (&wp)[16]) {
+struct RawUnit {
+  static constexpr int kWords = B == 16 ? 4 : B;
+  uint32_t w[2][kWords];
+  uint2 pw[2];  // NINT: (ls word, lm word) of the 4-group block; MXFP4: x = the unit's four E8M0 bytes
+};
+
+template <int B>
+__device__ __forceinline__ void load_unit(RawUnit<B>& r, const uint32_t* __restrict__ unit_base, const uint8_t* __restrict__ gp,
+                                          int g8, int c, int unit, int units, int gs, int g4) {
+  constexpr int P4 = B == 16 ? 1 : (B >= 4 ? (B == 8 ? 2 : 1) : 0);
+  constexpr int P2 = (B != 16 && B != 8 && (B & 2)) ? 1 : 0, P1 = (B != 16 && B != 8 && (B & 1)) ? 1 : 0;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = h * 8 + g8, slot = row * 4 + c;
+    const uint32_t* plane = unit_base;
+    int o = 0;
+    if constexpr (P4 >= 1) { const uint4 v = *reinterpret_cast<const uint4*>(plane + slot * 4); r.w[h][0] = v.x; r.w[h][1] = v.y; r.w[h][2] = v.z; r.w[h][3] = v.w; plane += 256; o = 4; }
+    if constexpr (P4 == 2) { const uint4 v = *reinterpret_cast<const uint4*>(plane + slot * 4); r.w[h][4] = v.x; r.w[h][5] = v.y; r.w[h][6] = v.z; r.w[h][7] = v.w; plane += 256; o = 8; }
+    if constexpr (P2 == 1) { const uint2 v = *reinterpret_cast<const uint2*>(plane + slot * 2); r.w[h][o] = v.x; r.w[h][o + 1] = v.y; plane += 128; o += 2; }
+    if constexpr (P1 == 1) { r.w[h][o] = plane[slot]; }
+    if constexpr (B == 16) {
+      r.pw[h] = make_uint2(*reinterpret_cast<const uint32_t*>(gp + (size_t(row) * units + unit) * 4), 0u);
+    } else {
+      int word4, lg, n_first;
+      group_of_run(gs, unit * 4 + c, word4, lg, n_first);
+      r.pw[h] = *reinterpret_cast<const uint2*>(gp + (size_t(row) * g4 + word4) * 8);
+    }
+  }
+}
+
+// Decodes the 16 pairs of one row's share of a unit into bf16x2 weights.  Per 8-code piece u (4 pairs) of the run:
+// s2[u] = (s, s), kz2[u] = (128 + z, 128 + z), nm2[u] = (z s - m, z s - m) of the piece's group -- see group_terms().
+template <int B>
+__device__ __forceinline__ void decode_nint(const uint32_t (&w)[B], const uint32_t (&s2)[4], const uint32_t (&nm2)[4],
+                                            const uint32_t (&kz2)[4], uint32_t (&wp)[16]) {
   constexpr int P4 = B >= 4 ? (B == 8 ? 2 : 1) : 0, P2 = ((B & 2) && B != 8) ? 1 : 0, P1 = ((B & 1) && B != 8) ? 1 : 0;
   uint32_t w4[4] = {0, 0, 0, 0}, w4b[4] = {0, 0, 0, 0}, w2[2] = {0, 0}, w1 = 0;
-  const uint32_t* plane = unit_base;
-  if constexpr (P4 >= 1) { const uint4 v = *reinterpret_cast<const uint4*>(plane + slot * 4); w4[0] = v.x; w4[1] = v.y; w4[2] = v.z; w4[3] = v.w; plane += 256; }
-  if constexpr (P4 == 2) { const uint4 v = *reinterpret_cast<const uint4*>(plane + slot * 4); w4b[0] = v.x; w4b[1] = v.y; w4b[2] = v.z; w4b[3] = v.w; plane += 256; }
-  if constexpr (P2 == 1) { const uint2 v = *reinterpret_cast<const uint2*>(plane + slot * 2); w2[0] = v.x; w2[1] = v.y; plane += 128; }
-  if constexpr (P1 == 1) { w1 = plane[slot]; }
-  uint32_t s16[2] = {0, 0};
-  if constexpr (B == 8) {  // high nibble: q = lo + 16 hi  ->  w = lo s - m + hi (16 s)
-    const uint32_t sixteen = 0x41804180u;  // bf16 16.0
-    s16[0] = bf16x2_mul(s2[0], sixteen);
-    s16[1] = bf16x2_mul(s2[1], sixteen);
-  }
+  int o = 0;
+  if constexpr (P4 >= 1) { w4[0] = w[0]; w4[1] = w[1]; w4[2] = w[2]; w4[3] = w[3]; o = 4; }
+  if constexpr (P4 == 2) { w4b[0] = w[4]; w4b[1] = w[5]; w4b[2] = w[6]; w4b[3] = w[7]; o = 8; }
+  if constexpr (P2 == 1) { w2[0] = w[o]; w2[1] = w[o + 1]; o += 2; }
+  if constexpr (P1 == 1) { w1 = w[o]; }
   auto one = [&](auto idx) {
     constexpr int I = decltype(idx)::value;
-    const int g = (I / 4) < n_first ? 0 : 1;
-    if constexpr (B == 8) {
-      const uint32_t lo = bf16x2_sub((shift<4 * (I % 4)>(w4[I / 4]) & 0x000F000Fu) | kMagic, kMagic);
+    constexpr int u = I / 4;
+    if constexpr (B == 8) {  // high nibble: q = lo + 16 hi  ->  w = (lo - z) s - rest + hi (16 s)
+      const uint32_t lo = bf16x2_sub((shift<4 * (I % 4)>(w4[I / 4]) & 0x000F000Fu) | kMagic, kz2[u]);
       const uint32_t hi = bf16x2_sub((shift<4 * (I % 4)>(w4b[I / 4]) & 0x000F000Fu) | kMagic, kMagic);
-      wp[I] = bf16x2_fma(hi, s16[g], bf16x2_fma(lo, s2[g], nm2[g]));
+      wp[I] = bf16x2_fma(hi, bf16x2_mul(s2[u], 0x41804180u /* 16.0 */), bf16x2_fma(lo, s2[u], nm2[u]));
     } else {
-      const uint32_t q = bf16x2_sub(code_pair<B, I>(w4, w2, w1), kMagic);
-      wp[I] = bf16x2_fma(q, s2[g], nm2[g]);
+      const uint32_t q = bf16x2_sub(code_pair<B, I>(w4, w2, w1), kz2[u]);
+      wp[I] = bf16x2_fma(q, s2[u], nm2[u]);
     }
   };
 #define MFQ_ONE(i) one(std::integral_constant<int, i>{});
@@ -157,10 +221,7 @@ __device__ __forceinline__ uint32_t mxfp4_scale2(uint32_t e8m0) {
   const uint32_t field = min(e8m0 + 126u, 254u);  // scales of 4 and more do not occur in weights; clamped, not wrapped
   return (field << 7) | (field << 23);
 }
-__device__ __forceinline__ void decode_mxfp4(const uint32_t* __restrict__ unit_base, int slot, uint32_t scale2,
-                                             uint32_t (&wp)[16]) {
-  const uint4 v = *reinterpret_cast<const uint4*>(unit_base + slot * 4);
-  const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+__device__ __forceinline__ void decode_mxfp4(const uint32_t (&w4)[4], uint32_t scale2, uint32_t (&wp)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const uint32_t t = w4[i / 4] >> (4 * (i % 4));
@@ -169,24 +230,88 @@ __device__ __forceinline__ void decode_mxfp4(const uint32_t* __restrict__ unit_b
   }
 }
 
-// Where the group parameters of a thread's n-th run of 32 codes live: the aligned 4-group word `word4`, the first group
-// inside it `lg`, and how many of the run's four 8-code pieces belong to that first group (the rest to the next one).
-//   32-wide groups: run n is group n.   16-wide: groups 2n, 2n + 1.   24-wide: the run starts in group floor(4n / 3).
-__host__ __device__ inline int group_words(int gs, int units) {  // 4-group parameter words per row
-  return gs == 32 ? units : gs == 16 ? units * 2 : (units * 4 - 1) / 3 + 1;
-}
-__device__ __forceinline__ void group_of_run(int gs, int n, int& word4, int& lg, int& n_first) {
-  if (gs == 32) { word4 = n >> 2; lg = n & 3; n_first = 4; }
-  else if (gs == 16) { word4 = n >> 1; lg = (n & 1) * 2; n_first = 2; }
-  else { word4 = n / 3; lg = n % 3; n_first = 3 - lg; }
+// Both rows of a raw unit -> bf16x2 weight pairs.
+template <int B>
+__device__ __forceinline__ void decode_unit(const RawUnit<B>& r, const float (&d)[2], const float (&dm)[2], int gs, int unit,
+                                            int c, uint32_t (&wp)[2][16]) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if constexpr (B == 16) {
+      decode_mxfp4(r.w[h], mxfp4_scale2((r.pw[h].x >> (8 * c)) & 0xFFu), wp[h]);
+    } else {
+      uint32_t s2[4], nm2[4], kz2[4];
+      if (gs == 32) {  // the run is one group: no per-piece selection at all
+        const int sh = 8 * ((unit * 4 + c) & 3);
+        group_terms(d[h], dm[h], (r.pw[h].x >> sh) & 0xFFu, (r.pw[h].y >> sh) & 0xFFu, s2[0], nm2[0], kz2[0]);
+#pragma unroll
+        for (int u = 1; u < 4; ++u) { s2[u] = s2[0]; nm2[u] = nm2[0]; kz2[u] = kz2[0]; }
+      } else {  // the run crosses from group lg into lg + 1 after n_first of its four 8-code pieces
+        int word4, lg, n_first;
+        group_of_run(gs, unit * 4 + c, word4, lg, n_first);
+        uint32_t sa, ma, za, sb, mb, zb;
+        group_terms(d[h], dm[h], (r.pw[h].x >> (8 * lg)) & 0xFFu, (r.pw[h].y >> (8 * lg)) & 0xFFu, sa, ma, za);
+        group_terms(d[h], dm[h], (r.pw[h].x >> (8 * lg + 8)) & 0xFFu, (r.pw[h].y >> (8 * lg + 8)) & 0xFFu, sb, mb, zb);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const bool first = u < n_first;
+          s2[u] = first ? sa : sb; nm2[u] = first ? ma : mb; kz2[u] = first ? za : zb;
+        }
+      }
+      decode_nint<B>(r.w[h], s2, nm2, kz2, wp[h]);
+    }
+  }
 }
 
 // Words a thread owns per unit for width code `bits` (its 32 codes of every plane).
 __host__ __device__ inline int words_per_thread(int bits) { return bits == 16 ? 4 : bits; }  // unit = 64 x this many words
 
+// The K slice of one warp over one tile: units ks, ks + KS, ...  The next unit's raw words are requested before this
+// unit is decoded and multiplied, the activations right after (they are cache-resident): two units of weights in flight.
+template <int B, int KS, int NB, bool kPrefetch>
+__device__ __forceinline__ void tile_product(const PackedParams& p, const uint32_t* __restrict__ tile_codes,
+                                             const uint8_t* __restrict__ gp, int gs, const float (&d)[2], const float (&dm)[2],
+                                             const __nv_bfloat16* const (&xr)[NB], const bool (&live)[NB], int ks, int g8, int c,
+                                             float (&acc)[NB][4]) {
+  constexpr size_t unit_words = size_t(64) * (B == 16 ? 4 : B);
+  const int g4 = group_words(gs, p.units);
+  RawUnit<B> cur;
+  if (kPrefetch && ks < p.units) load_unit<B>(cur, tile_codes + size_t(ks) * unit_words, gp, g8, c, ks, p.units, gs, g4);
+  for (int unit = ks; unit < p.units; unit += KS) {
+    RawUnit<B> nxt;
+    if constexpr (kPrefetch) {
+      nxt = cur;
+      if (unit + KS < p.units) load_unit<B>(nxt, tile_codes + size_t(unit + KS) * unit_words, gp, g8, c, unit + KS, p.units, gs, g4);
+    } else {
+      load_unit<B>(cur, tile_codes + size_t(unit) * unit_words, gp, g8, c, unit, p.units, gs, g4);
+    }
+    const int k0 = unit * 128 + c * 32;  // this thread's first input of the unit
+    uint32_t xb[NB][16];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (live[nb] && k0 + v * 8 + 8 <= p.K_x) val = *reinterpret_cast<const uint4*>(xr[nb] + k0 + v * 8);
+        xb[nb][4 * v] = val.x; xb[nb][4 * v + 1] = val.y; xb[nb][4 * v + 2] = val.z; xb[nb][4 * v + 3] = val.w;
+      }
+    }
+    uint32_t wp[2][16];
+    decode_unit<B>(cur, d, dm, gs, unit, c, wp);
+    // 8 MMAs per token block: MMA j takes pairs 2j and 2j+1 of both rows, and the same slots of the tokens
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+        mma_bf16(acc[nb], wp[0][2 * j], wp[1][2 * j], wp[0][2 * j + 1], wp[1][2 * j + 1], xb[nb][2 * j], xb[nb][2 * j + 1]);
+    }
+    if constexpr (kPrefetch) cur = nxt;
+  }
+}
+
 // KS: warps that split the K range of one tile; a CTA of 8 warps covers 8 / KS tiles.  NB: 8-token blocks (1 | 2).
-template <int KS, int NB>
-__global__ void __launch_bounds__(256) packed_gemv_kernel(const PackedParams p) {
+// PF: request the next unit's words before decoding this one (two units of weights in flight per warp).
+template <int KS, int NB, bool PF>
+__global__ void __launch_bounds__(256, 2) packed_gemv_kernel(const PackedParams p) {
   pdl_trigger();
   constexpr int kTilesPerCta = 8 / KS;
   __shared__ float part[8][16][NB * 8];
@@ -198,22 +323,20 @@ __global__ void __launch_bounds__(256) packed_gemv_kernel(const PackedParams p) 
   const int2 tm = p.tile_map[blockIdx.y];
   if (tm.x < 0) return;
   const int expert = tm.x;
-  const int row0 = p.offsets[expert] + tm.y * (NB * 8);
+  const int row0 = p.offsets[expert] + tm.y * 16;  // the route plan's token tile is 16 rows
   const int rows = min(NB * 8, p.offsets[expert + 1] - row0);
-  const bool active = tile < p.tiles && p.tile_meta[size_t(expert) * p.tiles + tile].x != 0;
+  int4 meta = make_int4(0, 0, 0, 0);
+  if (tile < p.tiles) meta = p.tile_meta[size_t(expert) * p.tiles + tile];
+  const int bits = meta.x;
 
   float acc[NB][4];
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f;
 
-  if (active) {
-    const int4 meta = p.tile_meta[size_t(expert) * p.tiles + tile];
-    const int bits = meta.x;
+  if (bits != 0) {
     const uint32_t* tile_codes = p.codes + p.code_base[expert] + meta.y;
-    const size_t unit_words = size_t(64) * words_per_thread(bits);
     const size_t trow = size_t(expert) * p.tiles * 16 + size_t(tile) * 16;  // row index into anchors / out_row
     const uint8_t* gp = p.gparams + p.gparam_base[expert] + meta.z;
-    const int gs = meta.w, g4 = group_words(meta.w, p.units);
     float d[2] = {0.f, 0.f}, dm[2] = {0.f, 0.f};
     if (bits != 16) {
 #pragma unroll
@@ -233,61 +356,16 @@ __global__ void __launch_bounds__(256) packed_gemv_kernel(const PackedParams p) 
       if (p.src_token && live[nb]) xrow = p.src_token[xrow];
       xr[nb] = p.x + size_t(live[nb] ? xrow : 0) * p.x_stride;
     }
-    for (int unit = ks; unit < p.units; unit += KS) {
-      const int k0 = unit * 128 + c * 32;  // this thread's first input of the unit
-      // ---- activations: 32 consecutive inputs of each token row (zero past the end of the row) ----
-      uint32_t xb[NB][16];
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 val = make_uint4(0u, 0u, 0u, 0u);
-          if (live[nb] && k0 + v * 8 + 8 <= p.K_x) val = *reinterpret_cast<const uint4*>(xr[nb] + k0 + v * 8);
-          xb[nb][4 * v] = val.x; xb[nb][4 * v + 1] = val.y; xb[nb][4 * v + 2] = val.z; xb[nb][4 * v + 3] = val.w;
-        }
-      }
-      // ---- weights of rows g8 and g8 + 8 ----
-      uint32_t wp[2][16];
-      const uint32_t* unit_base = tile_codes + size_t(unit) * unit_words;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int row = h * 8 + g8, slot = row * 4 + c;
-        if (bits == 16) {
-          const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(gp + (size_t(row) * p.units + unit) * 4);
-          decode_mxfp4(unit_base, slot, mxfp4_scale2((sc4 >> (8 * c)) & 0xFFu), wp[h]);
-        } else {
-          // group parameters: the thread's 32 codes lie in groups g0 and g0 + 1 of one aligned 4-group word
-          int word4, lg, n_first;
-          group_of_run(gs, unit * 4 + c, word4, lg, n_first);
-          const uint2 pw = *reinterpret_cast<const uint2*>(gp + (size_t(row) * g4 + word4) * 8);
-          uint32_t s2[2], nm2[2];
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int sh = 8 * min(lg + j, 3);
-            const float s = d[h] * float((pw.x >> sh) & 0xFFu);
-            const float m = dm[h] * float((pw.y >> sh) & 0xFFu);
-            s2[j] = pack_bf16x2(s, s);
-            nm2[j] = pack_bf16x2(-m, -m);
-          }
-          switch (bits) {
-            case 1: decode_nint<1>(unit_base, slot, s2, nm2, n_first, wp[h]); break;
-            case 2: decode_nint<2>(unit_base, slot, s2, nm2, n_first, wp[h]); break;
-            case 3: decode_nint<3>(unit_base, slot, s2, nm2, n_first, wp[h]); break;
-            case 4: decode_nint<4>(unit_base, slot, s2, nm2, n_first, wp[h]); break;
-            case 5: decode_nint<5>(unit_base, slot, s2, nm2, n_first, wp[h]); break;
-            case 6: decode_nint<6>(unit_base, slot, s2, nm2, n_first, wp[h]); break;
-            case 7: decode_nint<7>(unit_base, slot, s2, nm2, n_first, wp[h]); break;
-            default: decode_nint<8>(unit_base, slot, s2, nm2, n_first, wp[h]); break;
-          }
-        }
-      }
-      // ---- 8 MMAs per token block: MMA j takes pairs 2j and 2j+1 of both rows, and the same slots of the tokens ----
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-          mma_bf16(acc[nb], wp[0][2 * j], wp[1][2 * j], wp[0][2 * j + 1], wp[1][2 * j + 1], xb[nb][2 * j], xb[nb][2 * j + 1]);
-      }
+    switch (bits) {  // uniform over the warp: a tile holds rows of one width
+      case 1: tile_product<1, KS, NB, PF>(p, tile_codes, gp, meta.w, d, dm, xr, live, ks, g8, c, acc); break;
+      case 2: tile_product<2, KS, NB, PF>(p, tile_codes, gp, meta.w, d, dm, xr, live, ks, g8, c, acc); break;
+      case 3: tile_product<3, KS, NB, PF>(p, tile_codes, gp, meta.w, d, dm, xr, live, ks, g8, c, acc); break;
+      case 4: tile_product<4, KS, NB, PF>(p, tile_codes, gp, meta.w, d, dm, xr, live, ks, g8, c, acc); break;
+      case 5: tile_product<5, KS, NB, PF>(p, tile_codes, gp, meta.w, d, dm, xr, live, ks, g8, c, acc); break;
+      case 6: tile_product<6, KS, NB, PF>(p, tile_codes, gp, meta.w, d, dm, xr, live, ks, g8, c, acc); break;
+      case 7: tile_product<7, KS, NB, PF>(p, tile_codes, gp, meta.w, d, dm, xr, live, ks, g8, c, acc); break;
+      case 8: tile_product<8, KS, NB, PF>(p, tile_codes, gp, meta.w, d, dm, xr, live, ks, g8, c, acc); break;
+      default: tile_product<16, KS, NB, PF>(p, tile_codes, gp, meta.w, d, dm, xr, live, ks, g8, c, acc); break;
     }
   }
   // ---- add the K slices of a tile, write bf16 rows ----
@@ -315,7 +393,39 @@ __global__ void __launch_bounds__(256) packed_gemv_kernel(const PackedParams p) 
 }
 
 // Dense reconstruction of one expert's matrix from the packed layout: out[n, k] bf16 (n = output feature).  One warp per
-// (tile, unit); the same decode routines as the product kernel, so it doubles as their direct test.
+// (tile, unit); the same load / decode routines as the product kernel, so it doubles as their direct test.
+template <int B>
+__device__ __forceinline__ void dequant_unit(const PackedParams& p, const int4& meta, size_t trow, int expert, int unit, int g8,
+                                             int c, __nv_bfloat16* __restrict__ dense, int K_out) {
+  const uint32_t* unit_base = p.codes + p.code_base[expert] + meta.y + size_t(unit) * 64 * (B == 16 ? 4 : B);
+  const uint8_t* gp = p.gparams + p.gparam_base[expert] + meta.z;
+  float d[2] = {0.f, 0.f}, dm[2] = {0.f, 0.f};
+  if constexpr (B != 16) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __half2 a = *reinterpret_cast<const __half2*>(p.anchors + (trow + g8 + 8 * h) * 2);
+      d[h] = __low2float(a);
+      dm[h] = __high2float(a);
+    }
+  }
+  RawUnit<B> raw;
+  load_unit<B>(raw, unit_base, gp, g8, c, unit, p.units, meta.w, group_words(meta.w, p.units));
+  uint32_t wp[2][16];
+  decode_unit<B>(raw, d, dm, meta.w, unit, c, wp);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int n = p.out_row[trow + g8 + 8 * h];
+    if (n < 0) continue;
+    const int k0 = unit * 128 + c * 32;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int k = k0 + 2 * i;
+      if (k + 1 < K_out) *reinterpret_cast<uint32_t*>(dense + size_t(n) * K_out + k) = wp[h][i];
+      else if (k < K_out) dense[size_t(n) * K_out + k] = __ushort_as_bfloat16(uint16_t(wp[h][i] & 0xFFFFu));
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) packed_dequant_kernel(const PackedParams p, int expert, __nv_bfloat16* __restrict__ dense,
                                                              int K_out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -324,52 +434,18 @@ __global__ void __launch_bounds__(256) packed_dequant_kernel(const PackedParams 
   if (item >= p.tiles * p.units) return;
   const int tile = item / p.units, unit = item % p.units;
   const int4 meta = p.tile_meta[size_t(expert) * p.tiles + tile];
-  const int bits = meta.x;
-  if (bits == 0) return;
-  const uint32_t* unit_base = p.codes + p.code_base[expert] + meta.y + size_t(unit) * 64 * words_per_thread(bits);
   const size_t trow = size_t(expert) * p.tiles * 16 + size_t(tile) * 16;
-  const uint8_t* gp = p.gparams + p.gparam_base[expert] + meta.z;
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    uint32_t wp[16];
-    const int row = h * 8 + g8, slot = row * 4 + c;
-    if (bits == 16) {
-      const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(gp + (size_t(row) * p.units + unit) * 4);
-      decode_mxfp4(unit_base, slot, mxfp4_scale2((sc4 >> (8 * c)) & 0xFFu), wp);
-    } else {
-      const __half2 a = *reinterpret_cast<const __half2*>(p.anchors + (trow + row) * 2);
-      const float d = __low2float(a), dm = __high2float(a);
-      int word4, lg, n_first;
-      group_of_run(meta.w, unit * 4 + c, word4, lg, n_first);
-      const uint2 pw = *reinterpret_cast<const uint2*>(gp + (size_t(row) * group_words(meta.w, p.units) + word4) * 8);
-      uint32_t s2[2], nm2[2];
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int sh = 8 * min(lg + j, 3);
-        const float s = d * float((pw.x >> sh) & 0xFFu), m = dm * float((pw.y >> sh) & 0xFFu);
-        s2[j] = pack_bf16x2(s, s);
-        nm2[j] = pack_bf16x2(-m, -m);
-      }
-      switch (bits) {
-        case 1: decode_nint<1>(unit_base, slot, s2, nm2, n_first, wp); break;
-        case 2: decode_nint<2>(unit_base, slot, s2, nm2, n_first, wp); break;
-        case 3: decode_nint<3>(unit_base, slot, s2, nm2, n_first, wp); break;
-        case 4: decode_nint<4>(unit_base, slot, s2, nm2, n_first, wp); break;
-        case 5: decode_nint<5>(unit_base, slot, s2, nm2, n_first, wp); break;
-        case 6: decode_nint<6>(unit_base, slot, s2, nm2, n_first, wp); break;
-        case 7: decode_nint<7>(unit_base, slot, s2, nm2, n_first, wp); break;
-        default: decode_nint<8>(unit_base, slot, s2, nm2, n_first, wp); break;
-      }
-    }
-    const int n = p.out_row[trow + g8 + 8 * h];
-    if (n < 0) continue;
-    const int k0 = unit * 128 + c * 32;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int k = k0 + 2 * i;
-      if (k + 1 < K_out) *reinterpret_cast<uint32_t*>(dense + size_t(n) * K_out + k) = wp[i];
-      else if (k < K_out) dense[size_t(n) * K_out + k] = __ushort_as_bfloat16(uint16_t(wp[i] & 0xFFFFu));
-    }
+  switch (meta.x) {
+    case 0: break;
+    case 1: dequant_unit<1>(p, meta, trow, expert, unit, g8, c, dense, K_out); break;
+    case 2: dequant_unit<2>(p, meta, trow, expert, unit, g8, c, dense, K_out); break;
+    case 3: dequant_unit<3>(p, meta, trow, expert, unit, g8, c, dense, K_out); break;
+    case 4: dequant_unit<4>(p, meta, trow, expert, unit, g8, c, dense, K_out); break;
+    case 5: dequant_unit<5>(p, meta, trow, expert, unit, g8, c, dense, K_out); break;
+    case 6: dequant_unit<6>(p, meta, trow, expert, unit, g8, c, dense, K_out); break;
+    case 7: dequant_unit<7>(p, meta, trow, expert, unit, g8, c, dense, K_out); break;
+    case 8: dequant_unit<8>(p, meta, trow, expert, unit, g8, c, dense, K_out); break;
+    default: dequant_unit<16>(p, meta, trow, expert, unit, g8, c, dense, K_out); break;
   }
 }
 
@@ -391,11 +467,13 @@ static PackedParams make_params(const void* codes, const void* code_base, const 
 
 // Grouped product over the (expert, 16-token tile) pairs of a route plan.  x: bf16 rows (the unsorted token rows with
 // src_token, else the expert-sorted rows), K_x valid inputs each (K_x % 8 == 0); out: [sorted rows, N_out] bf16.
-// Packed arrays: see PackedParams and mfq_b200/ops/packed.py.  token_tile must be 16 (the plan's tile).
+// Packed arrays: see PackedParams and mfq_b200/ops/packed.py.  The plan's token tile must be 16.  max_rows_per_expert: an
+// upper bound on the rows any expert receives (0: unknown).
 extern "C" int mfq_packed_gemv_grouped(const void* codes, const void* code_base, const void* tile_meta, const void* gparams,
                                        const void* gparam_base, const void* anchors, const void* out_row, int tiles, int units,
                                        const void* x, int x_stride, int K_x, void* out, int N_out, const void* tile_map,
-                                       int map_cap, const int* offsets, const int* src_token, cudaStream_t stream) {
+                                       int map_cap, const int* offsets, const int* src_token, int max_rows_per_expert,
+                                       cudaStream_t stream) {
   if (tiles <= 0 || units <= 0 || K_x <= 0 || K_x % 8 || x_stride % 8 || map_cap <= 0 || N_out <= 0)
     return -1;
   mfq::PackedParams p = mfq::make_params(codes, code_base, tile_meta, gparams, gparam_base, anchors, out_row, tiles, units);
@@ -407,14 +485,27 @@ extern "C" int mfq_packed_gemv_grouped(const void* codes, const void* code_base,
   p.tile_map = static_cast<const int2*>(tile_map);
   p.offsets = offsets;
   p.src_token = src_token;
-  // long rows: four warps share a tile's K range; short rows: one warp per tile
-  if (units >= 12) {
-    mfq::launch_kernel(mfq::packed_gemv_kernel<4, 2>, dim3((tiles + 1) / 2, map_cap), dim3(256), 0, stream, p);
-  } else if (units >= 6) {
-    mfq::launch_kernel(mfq::packed_gemv_kernel<2, 2>, dim3((tiles + 3) / 4, map_cap), dim3(256), 0, stream, p);
-  } else {
-    mfq::launch_kernel(mfq::packed_gemv_kernel<1, 2>, dim3((tiles + 7) / 8, map_cap), dim3(256), 0, stream, p);
-  }
+  // Few tokens (no expert sees more than 8 rows): the step is latency-bound, so up to four warps split a tile's K range
+  // and every warp keeps two units in flight.  More tokens: thousands of CTAs exist anyway, a warp then walks a whole
+  // row range by itself (its start-up latencies -- tile map, offsets, descriptors -- are paid once per 16 units).
+  const bool narrow = max_rows_per_expert > 0 && max_rows_per_expert <= 8;
+  static const int force_ks = [] { const char* e = getenv("MFQ_PACKED_KS"); return e ? atoi(e) : 0; }();
+  static const int force_pf = [] { const char* e = getenv("MFQ_PACKED_PF"); return e ? atoi(e) : -1; }();
+  int ks = narrow ? (units >= 12 ? 4 : units >= 6 ? 2 : 1) : 1;
+  if (force_ks == 1 || force_ks == 2 || force_ks == 4) ks = force_ks;
+  const bool pf = force_pf >= 0 ? force_pf != 0 : true;
+  const dim3 grid((tiles + 8 / ks - 1) / (8 / ks), map_cap);
+#define MFQ_LAUNCH(KS_, NB_, PF_) mfq::launch_kernel(mfq::packed_gemv_kernel<KS_, NB_, PF_>, grid, dim3(256), 0, stream, p)
+#define MFQ_PICK(KS_) \
+  do { \
+    if (narrow) { if (pf) MFQ_LAUNCH(KS_, 1, true); else MFQ_LAUNCH(KS_, 1, false); } \
+    else { if (pf) MFQ_LAUNCH(KS_, 2, true); else MFQ_LAUNCH(KS_, 2, false); } \
+  } while (0)
+  if (ks == 4) MFQ_PICK(4);
+  else if (ks == 2) MFQ_PICK(2);
+  else MFQ_PICK(1);
+#undef MFQ_PICK
+#undef MFQ_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 

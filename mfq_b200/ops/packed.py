@@ -411,9 +411,10 @@ def packed_gemv_grouped(w: PackedExperts, x: torch.Tensor, plan, gather: bool) -
     fn = lib().mfq_packed_gemv_grouped
     fn.restype = C.c_int
     fn.argtypes = [C.c_void_p] * 7 + [C.c_int] * 2 + [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
-                                                      C.c_void_p, C.c_void_p, C.c_void_p]
+                                                      C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    tokens = plan.dest.shape[0]  # an expert receives each token at most once
     rc = fn(*w._args(), ptr(x), x.stride(0), min(w.k_in, x.shape[1]), ptr(out), w.n_out, ptr(plan.tile_map),
-            plan.tile_map.shape[0], ptr(plan.offsets), ptr(plan.src_token) if gather else None, stream_ptr())
+            plan.tile_map.shape[0], ptr(plan.offsets), ptr(plan.src_token) if gather else None, tokens, stream_ptr())
     check(rc, "packed_gemv_grouped")
     return out
 

@@ -6,7 +6,8 @@ for a multi-pass capture to finish in about a minute) and exits.  Cases: ``gemm_
 ``w4_decode`` / ``w4_prefill`` (the 4-bit in-pipeline-decode GEMM at the same shapes), ``gdn_decode`` (Gated DeltaNet step,
 64 sequences), ``moe_dispatch`` (expert-parallel dispatch + combine kernels at world 1, 4096 tokens), ``gemv_decode``
 (the weight-streaming FP8 kernel, M=1, N=28672, K=4096), ``attn_prefill_d256`` (T=2048, 16 query / 2 KV heads of 256),
-``gdn_prefill`` (the long-row Gated DeltaNet path, 2048 tokens, 32 heads).
+``gdn_prefill`` (the long-row Gated DeltaNet path, 2048 tokens, 32 heads), ``packed_decode`` / ``packed_decode_bs1`` (the
+packed-expert product at 64 tokens / one token, 512 experts).
 """
 
 from __future__ import annotations
@@ -132,10 +133,25 @@ def moe_dispatch() -> None:
         ep.combine(y, plan, recv)
 
 
+def packed_decode(tokens: int = 64) -> None:
+    """Packed expert gate/up product of the 512-expert hybrid model: `tokens` tokens x top-10 routes over synthetic NINT 2-5
+    bit / MXFP4 payloads ([1024, 2048] per expert, about 0.5 GB in all)."""
+    from . import moe, packed
+    e, k = 512, 10
+    rng = torch.Generator().manual_seed(0)
+    bits = [int(b) for b in torch.tensor([2, 3, 4, 5, 16])[torch.randint(0, 5, (e,), generator=rng)]]
+    pe = packed.PackedExperts.synthetic(e, 1024, 2048, bits, "cuda", gs=32, seed=1)
+    x = torch.randn((tokens, 2048), device="cuda").to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(e, device="cuda")[:k] for _ in range(tokens)]).to(torch.int32)
+    plan = moe.plan_routes(ids, 0, e, token_tile=16)
+    for _ in range(3):
+        packed.packed_gemv_grouped(pe, x, plan, gather=True)
+
+
 CASES = {"gemm_prefill": lambda: gemm(4096, 4096, 4096), "gemm_decode": lambda: gemm(64, 28672, 4096),
          "attn_decode": attn_decode, "attn_prefill": attn_prefill, "w4_decode": lambda: w4_gemm(64, 28672, 4096),
          "w4_prefill": lambda: w4_gemm(4096, 4096, 4096), "gdn_decode": gdn_decode, "moe_dispatch": moe_dispatch,
-         "gemv_decode": lambda: gemm(1, 28672, 4096), "attn_prefill_d256": attn_prefill_d256, "gdn_prefill": gdn_prefill}
+         "gemv_decode": lambda: gemm(1, 28672, 4096), "packed_decode": packed_decode, "packed_decode_bs1": lambda: packed_decode(1), "attn_prefill_d256": attn_prefill_d256, "gdn_prefill": gdn_prefill}
 
 if __name__ == "__main__":
     CASES[sys.argv[1]]()
