@@ -173,6 +173,9 @@ def run_ours(args) -> dict:
     ms1, _ = timed_decode(1, args.steps, args.warmup)
     ops.Workspace.get(dev).check()
     phase("single-stream decode timed")
+    ms32 = None
+    if batch >= 32:  # the reference accepts at most 32 concurrent sequences: one pair of figures at the same batch
+        ms32, _ = timed_decode(32, args.steps, args.warmup)
     engine_launches = dict(engine.launches_per_step)
 
     # ---- end to end through the public step API: pinned H2D of the inputs + D2H of the result every step ----
@@ -238,6 +241,7 @@ def run_ours(args) -> dict:
         "gpu_launches": launches * replicas,
         "extra": {"decode_tok_s_bs1": round(replicas * args.steps / (ms1 / 1e3), 2), "ms_per_step_bs1": round(ms1 / args.steps, 4),
                   "prefill_tok_s": round(replicas * ctx / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 2),
+                  "decode_tok_s_bs32": round(replicas * 32 * args.steps / (ms32 / 1e3), 2) if ms32 else None,
                   "launches_per_step_bs64": engine_launches.get(batch), "launches_per_step_bs1": engine_launches.get(1),
                   "vs_published_bs64": round(value / PUBLISHED_BATCHED_DECODE_TOK_S, 2),
                   "vs_published_bs1": round(args.steps / (ms1 / 1e3) / PUBLISHED_SINGLE_DECODE_TOK_S, 2),

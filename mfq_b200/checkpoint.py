@@ -59,14 +59,19 @@ def read_hf_directory(path) -> tuple[dict, dict[str, np.ndarray], dict[str, byte
 
 def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", expert_mix: str = "", seed: int = 20260908,
                      device: str = "cpu", progress=None, widths: dict[str, int | None] | None = None,
-                     imatrix: dict[str, np.ndarray] | None = None, scheme: dict | None = None, resume=None) -> dict[str, object]:
+                     imatrix: dict[str, np.ndarray] | None = None, scheme: dict | None = None, resume=None,
+                     fp8_sq_bits: float = 0.0) -> dict[str, object]:
     """Apply the quantization plan: routed experts by the seeded mix (or the dense rule), 2-D weights by ``dense``
     (nint2..8 / nvq3 / mxfp4 / fp8 / bf16), norms / router / embeddings-as-requested stay bf16.
     ``widths`` (a preset plan: tensor -> NINT width, None = keep) overrides ``dense`` per tensor; ``imatrix`` supplies
     per-input-channel importance to the NINT search; ``scheme`` (``mfq.calibration-scheme.v3``, expert-wise) fixes the
     family of every routed expert projection.  ``resume`` (a :class:`~mfq_b200.quantize.resume.ResumeStore`) parks
-    every finished tensor and hands back the ones a previous, interrupted run finished for the same source and plan."""
+    every finished tensor and hands back the ones a previous, interrupted run finished for the same source and plan.
+    ``fp8_sq_bits`` (1..8, 0 = off): dense FP8 tensors are re-encoded with per-row scalar palettes averaging that many
+    code bits per weight (``quantize/fp8_sq.py``; the imatrix, if given, weights the palette fit)."""
     if resume is not None:
+        if fp8_sq_bits:
+            raise ValueError("--fp8-sq-bits cannot be combined with a resumable run yet")
         return _quantize_resumable(tensors, resume, dense=dense, expert_mix=expert_mix, seed=seed, device=device,
                                    progress=progress, widths=widths, imatrix=imatrix, scheme=scheme)
     from .quantize import balanced_expert_mix, parse_profiles, quantize_expertwise, quantize_matrix
@@ -105,6 +110,11 @@ def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", ex
                 from .calibration.imatrix import input_importance
                 imp = input_importance(imatrix, name)
             out[name] = quantize_matrix(a, profile, device=device, importance=imp) if imp is not None else quantize_matrix(a, profile, device=device)
+            if fp8_sq_bits and profile.family == "FP8":
+                from .calibration.imatrix import input_importance
+                from .quantize.fp8_sq import quantize_fp8_sq
+                weight = input_importance(imatrix, name) if imatrix is not None else None
+                out[name] = quantize_fp8_sq(out[name], float(fp8_sq_bits), weight)
     return out
 
 

@@ -127,11 +127,12 @@ def _cmd_quantize(args) -> int:
         gs, k = expertwise._NINT_PRESETS[bits]
         expertwise._NINT_PRESETS[bits] = (args.groupsize or gs, args.sub_bits or k)
     store = None
-    if not args.no_temp:
+    if not args.no_temp and not args.fp8_sq_bits:
         from .quantize.resume import ResumeStore
         store = ResumeStore(str(out) + ".tmp", resume=args.resume, keep=args.keep_temp)
     q = quantize_tensors(tensors, dense=dense, expert_mix=args.random_expert_mix, seed=args.random_expert_mix_seed,
                          widths=widths, imatrix=imatrix, scheme=scheme, device=args.device, resume=store,
+                         fp8_sq_bits=args.fp8_sq_bits,
                          progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
     extra = {"quantization": {"dense": dense, "preset": args.preset or None, "imatrix": bool(imatrix), "ew_scheme": bool(scheme), "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
                               "random_expert_mix_seed": args.random_expert_mix_seed if args.random_expert_mix else None}}
@@ -615,6 +616,9 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--base-mfq", help="existing checkpoint to extend: its records are kept as they are and the source's multi-token-prediction head is added")
     q.add_argument("--recipe", help="per-tensor precisions from a GGUF file's tensor table (.gguf) or a JSON rule list")
     q.add_argument("--target-bpw", type=float, default=0.0, help="AlphaQ allocation of NINT widths over the 2-D weights under this budget")
+    q.add_argument("--fp8-sq-bits", type=float, default=0.0,
+                   help="with --format fp8: re-encode the E4M3 tensors with per-row scalar palettes (FP8-128SQ rows SQ1..SQ8) "
+                        "averaging this many code bits per weight")
     q.add_argument("--split-max-size", help="limit of tensor payload per output shard, N[M|G]")
     q.add_argument("--split-max-tensors", type=int, default=0, help="limit of tensors per output shard")
     q.add_argument("--dry-run", action="store_true")

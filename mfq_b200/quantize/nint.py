@@ -11,6 +11,13 @@ itself the k-quant ``make_qkx2`` search of llama.cpp), restated batched over
 3. anchors ``d = f16(max_g scale / (2^k-1))``, ``dmin = f16(max_g -min / (2^k-1))``;
    group codes ``rint((2^k-1) * scale / max scale)``;
 4. re-round element codes against the *effective* (anchored) scale and min.
+
+With an importance vector (an imatrix) the search is the weighted variant (reference:
+``mfq/quantize/nint_quant.py:102-139,141-217,310-480``): element weights ``imp * sqrt(sigma2 + x^2)`` with ``sigma2``
+taken over 256-value blocks, a finer candidate grid (37 inverse scales from ``qmax - 0.9`` in steps of 0.05), and a
+final coordinate descent on what is actually stored -- the integer group codes are re-solved against the anchored row
+scale / minimum and the element codes re-rounded, a step being kept only when the weighted error of the stored
+reconstruction falls.
 """
 
 from __future__ import annotations
@@ -20,15 +27,19 @@ import torch
 
 from ..formats.nint import NintSpec, NintTensor
 
-__all__ = ["quantize_nint", "fit_groups"]
+__all__ = ["quantize_nint", "fit_groups", "importance_weights", "refine_stored"]
 
 
-def fit_groups(x: torch.Tensor, w: torch.Tensor, qmax: int) -> tuple[torch.Tensor, torch.Tensor]:
+def fit_groups(x: torch.Tensor, w: torch.Tensor, qmax: int, fine: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """Best ``(scale, zero)`` per group with ``recon = zero + scale * L``, ``L in [0, qmax]``.
 
-    ``x``/``w`` are ``[..., gs]``; returns two ``[...]`` tensors (``zero <= 0``).
+    ``x``/``w`` are ``[..., gs]``; returns two ``[...]`` tensors (``zero <= 0``).  ``fine``: the denser candidate grid of
+    the importance-weighted search.
     """
-    rmin, rdelta, nstep = (-1.0, 0.1, 20) if qmax <= 15 else (-0.5, 0.1, 15)
+    if fine:
+        rmin, rdelta, nstep = -0.9, 0.05, 36
+    else:
+        rmin, rdelta, nstep = (-1.0, 0.1, 20) if qmax <= 15 else (-0.5, 0.1, 15)
     lo = torch.clamp(x.amin(-1), max=0.0)
     hi = x.amax(-1)
     sw = w.sum(-1)
@@ -72,6 +83,56 @@ def _f16(x: torch.Tensor) -> torch.Tensor:
     return x.to(torch.float16).to(torch.float32)
 
 
+IMATRIX_BLOCK = 256  # sigma^2 of the importance weights is taken over blocks of this many inputs
+
+
+def importance_weights(rows: torch.Tensor, importance: torch.Tensor) -> torch.Tensor:
+    """Element weights of the importance-weighted search: ``imp[k] * sqrt(sigma2[block(k)] + x^2)`` with
+    ``sigma2 = 2 * mean(x^2)`` over blocks of 256 inputs (the last block over what it holds)."""
+    out, n = rows.shape
+    pad = (-n) % IMATRIX_BLOCK
+    blocks = torch.nn.functional.pad(rows, (0, pad)).reshape(out, -1, IMATRIX_BLOCK)
+    counts = torch.full((blocks.shape[1],), float(IMATRIX_BLOCK), device=rows.device)
+    if pad:
+        counts[-1] -= pad
+    sigma2 = 2.0 * blocks.pow(2).sum(-1) / counts[None, :]
+    sigma2 = sigma2.repeat_interleave(IMATRIX_BLOCK, dim=1)[:, :n]
+    return importance.expand(out, n) * torch.sqrt(sigma2 + rows * rows)
+
+
+def refine_stored(x, w, q, d, dm, ls, lm, qmax: int, kmax: int, passes: int = 2):
+    """Coordinate descent on the stored reconstruction ``d * ls * q - dm * lm`` (weighted squared error): with the element
+    codes fixed each group's best integer ``ls`` and ``lm`` have closed forms; then the element codes are re-rounded
+    against the new effective values.  A pass is kept per row only where the row's weighted error fell."""
+    def row_error(q_, ls_, lm_):
+        rec = (d[:, None] * ls_)[..., None] * q_ - (dm[:, None] * lm_)[..., None]
+        return (w * (rec - x) ** 2).sum((-1, -2))
+    best = row_error(q, ls, lm)
+    for _ in range(passes):
+        cls, clm, cq = ls.clone(), lm.clone(), q.clone()
+        for _inner in range(2):
+            sw, sx = w.sum(-1), (w * x).sum(-1)
+            sq, sq2, sqx = (w * cq).sum(-1), (w * cq * cq).sum(-1), (w * cq * x).sum(-1)
+            em = dm[:, None] * clm
+            den = d[:, None] * sq2
+            new_ls = torch.where(den > 0, torch.clamp(torch.round((sqx + em * sq) / den.clamp_min(1e-30)), 0, kmax), cls)
+            es = d[:, None] * new_ls
+            den_m = dm[:, None] * sw
+            new_lm = torch.where(den_m > 0, torch.clamp(torch.round((es * sq - sx) / den_m.clamp_min(1e-30)), 0, kmax), clm)
+            cls, clm = new_ls, new_lm
+        es, em = d[:, None] * cls, dm[:, None] * clm
+        cq = torch.clamp(torch.round((x + em[..., None]) / torch.where(es > 0, es, torch.ones_like(es))[..., None]), 0, qmax)
+        err = row_error(cq, cls, clm)
+        better = err < best
+        if not bool(better.any()):
+            break
+        q = torch.where(better[:, None, None], cq, q)
+        ls = torch.where(better[:, None], cls, ls)
+        lm = torch.where(better[:, None], clm, lm)
+        best = torch.where(better, err, best)
+    return q, ls, lm
+
+
 def _quantize_uniform(rows: torch.Tensor, bits: int, gs: int, k: int, importance: torch.Tensor | None):
     out, n = rows.shape
     pad = (-n) % gs
@@ -79,11 +140,11 @@ def _quantize_uniform(rows: torch.Tensor, bits: int, gs: int, k: int, importance
     if importance is None:
         w = x.pow(2).mean(-1, keepdim=True).sqrt() + x.abs()
     else:
-        w = torch.nn.functional.pad(importance.expand(out, n), (0, pad)).reshape(out, -1, gs).clone()
+        w = torch.nn.functional.pad(importance_weights(rows, importance), (0, pad)).reshape(out, -1, gs).clone()
     if pad:
         w[:, -1, gs - pad:] = 0.0
     qmax, kmax = (1 << bits) - 1, (1 << k) - 1
-    scale, zero = fit_groups(x, w, qmax)
+    scale, zero = fit_groups(x, w, qmax, fine=importance is not None)
     mins = -zero
     top_s = scale.amax(-1)
     top_m = mins.amax(-1)
@@ -94,6 +155,8 @@ def _quantize_uniform(rows: torch.Tensor, bits: int, gs: int, k: int, importance
     eff_s = d[:, None] * ls
     eff_m = dm[:, None] * lm
     q = torch.clamp(torch.round((x + eff_m[..., None]) / torch.where(eff_s > 0, eff_s, torch.ones_like(eff_s))[..., None]), 0, qmax)
+    if importance is not None:
+        q, ls, lm = refine_stored(x, w, q, d, dm, ls, lm, qmax, kmax)
     return q.to(torch.uint8), d, dm, ls.to(torch.uint8), lm.to(torch.uint8)
 
 
