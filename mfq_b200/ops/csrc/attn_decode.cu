@@ -1,11 +1,9 @@
 // Paged GQA decode / verify attention over FP8 pages, built to run at HBM speed.
 //
-// A work item = (sequence, KV head, KV split); the 4 warps of a CTA take its pages round-robin.  The grid is persistent:
-// CTAs draw items from a device counter until none is left, and a CTA always knows its NEXT item, so each warp keeps
-// its page ring full across the item boundary (no pipeline bubble per item, no idle SMs in a last partial wave).
-// Every warp owns a private ring of page buffers in shared memory that it fills with bulk async copies (one 2 KB K
-// block, one 2 KB V block and two 64 B scale rows per page and head; completion on an mbarrier), so dozens of KB are
-// in flight per SM without any CTA-wide synchronisation inside an item.  The math is tensor-core `mma.sync.m16n8k16` in f16 with fp32
+// One CTA = (sequence, KV head, KV split); its 4 warps take pages round-robin.  Every warp owns a private
+// ring of page buffers in shared memory that it fills with bulk async copies (one 2 KB K block, one 2 KB V
+// block and two 64 B scale rows per page and head; completion on an mbarrier), so dozens of KB are in flight
+// per SM without any CTA-wide synchronisation.  The math is tensor-core `mma.sync.m16n8k16` in f16 with fp32
 // accumulation: the 16 MMA rows hold the (query row, head-of-group) pairs that share this KV head -- G heads
 // x q_len query tokens <= 16 -- so a 4-head group or a 4-token speculative verify window costs the same KV
 // traffic as one head.  FP8 codes are expanded to f16 with `cvt.f16x2.e4m3x2` straight into MMA fragments.
@@ -53,23 +51,19 @@ template <int D, int kAttnStages>
 struct AttnSmem {
   static constexpr int kPageBytes = 16 * D;                    // one head's K (or V) page
   static constexpr int kStageBytes = 2 * kPageBytes + 128;     // K, V, k scales, v scales
-  static constexpr int kWarpBytes = kAttnStages * kStageBytes;
-  static constexpr int kFixed = 4 * kWarpBytes + 4 * kAttnStages * 8 + 32;  // rings, barriers, abort flag + next-item word
-  // merge scratch of the four warps, for `rows` live MMA rows: [rows][D] partial outputs + [16][2] (max, sum)
-  static constexpr int scratch_bytes(int rows) { return rows * D * 4 + 128; }
-  static constexpr int total(int rows) { return kFixed + 4 * scratch_bytes(rows); }
+  static constexpr int kWarpBytes = kAttnStages * kStageBytes;  // also the merge scratch: needs >= 16*D*4 + 128
+  static constexpr int kTotal = 4 * kWarpBytes + 4 * kAttnStages * 8 + 16;
 };
 
 // kAttnStages: pages in flight per warp; kMinBlocks: CTAs per SM the register allocation is held to.
-// work[0]: next item to hand out, work[1]: CTAs that have finished (the last one zeroes both for the next launch).
 template <int D, int kAttnStages, int kMinBlocks>
 __global__ void __launch_bounds__(128, kMinBlocks)
 paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t* __restrict__ k_cache,
                              const uint8_t* __restrict__ v_cache, const float* __restrict__ k_scale,
                              const float* __restrict__ v_scale, const int* __restrict__ block_table,
                              const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out,
-                             float* __restrict__ part_acc, float* __restrict__ part_ml, int B, int Hq, int Hk, int nsplit,
-                             int max_pages, float scale_log2, int q_len, int* __restrict__ work, int* status) {
+                             float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hk, int max_pages,
+                             float scale_log2, int q_len, int* status) {
   pdl_trigger();
   pdl_wait();
   using L = AttnSmem<D, kAttnStages>;
@@ -80,79 +74,38 @@ paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t*
   uint8_t* ring = smem + warp * L::kWarpBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * L::kWarpBytes) + warp * kAttnStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 4 * L::kWarpBytes + 4 * kAttnStages * 8);
-  volatile int* s_item = abort_flag + 1;  // [2]: the item after the current one, and a spare for the first fetch
+
+  const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
   const int G = Hq / Hk;
   const int R = G * q_len;  // live MMA rows
-  const int scratch_bytes = L::scratch_bytes(R);
-  uint8_t* scratch0 = smem + L::kFixed;
-  const int total_items = B * Hk * nsplit;
+  const int len = seq_lens[seq];
+  const int pages_total = (len + 15) >> 4;
+  const int per_split = (pages_total + nsplit - 1) / nsplit;
+  const int page_begin = split * per_split;
+  const int page_end = min(pages_total, page_begin + per_split);
+  const int my_pages = page_end > page_begin + warp ? (page_end - page_begin - warp + 3) / 4 : 0;
 
-  // An item's geometry: which pages of which sequence this warp walks.
-  struct Item { int seq, kvh, split, len, page_begin, my_pages; bool valid; };
-  auto decode_item = [&](int idx) {
-    Item it;
-    it.valid = idx < total_items;
-    it.seq = it.kvh = it.split = it.len = it.page_begin = it.my_pages = 0;
-    if (it.valid) {
-      it.split = idx % nsplit;
-      it.kvh = (idx / nsplit) % Hk;
-      it.seq = idx / (nsplit * Hk);
-      it.len = seq_lens[it.seq];
-      const int pages_total = (it.len + 15) >> 4;
-      const int per_split = (pages_total + nsplit - 1) / nsplit;
-      it.page_begin = it.split * per_split;
-      const int page_end = min(pages_total, it.page_begin + per_split);
-      it.my_pages = page_end > it.page_begin + warp ? (page_end - it.page_begin - warp + 3) / 4 : 0;
-    }
-    return it;
-  };
-
-  if (threadIdx.x == 0) {
-    *abort_flag = 0;
-    s_item[0] = atomicAdd(work, 1);
-    s_item[1] = atomicAdd(work, 1);
-  }
+  if (threadIdx.x == 0) *abort_flag = 0;
   if (lane == 0) {
     for (int s = 0; s < kAttnStages; ++s) mbar_init(&bars[s], 1);
     mbar_fence_init();
   }
   __syncthreads();
-  Item cur = decode_item(s_item[0]), nxt = decode_item(s_item[1]);
-  __syncthreads();  // both words read before thread 0 reuses s_item[0] for the following fetches
 
-  auto issue = [&](const Item& it, int i, int stage) {  // lane 0 only: start the copies of this warp's i-th page of `it`
-    const int page = block_table[size_t(it.seq) * max_pages + it.page_begin + warp + 4 * i];
-    const size_t ph = size_t(page) * Hk + it.kvh;
-    uint8_t* st = ring + stage * L::kStageBytes;
-    mbar_expect_tx(&bars[stage], L::kStageBytes);
-    bulk_load(st, k_cache + ph * L::kPageBytes, L::kPageBytes, &bars[stage]);
-    bulk_load(st + L::kPageBytes, v_cache + ph * L::kPageBytes, L::kPageBytes, &bars[stage]);
-    bulk_load(st + 2 * L::kPageBytes, k_scale + ph * 16, 64, &bars[stage]);
-    bulk_load(st + 2 * L::kPageBytes + 64, v_scale + ph * 16, 64, &bars[stage]);
+  const int* bt = block_table + size_t(seq) * max_pages;
+  auto issue = [&](int i) {  // lane 0 only: start the copies of this warp's i-th page
+    const int s = i % kAttnStages;
+    const int page = bt[page_begin + warp + 4 * i];
+    const size_t ph = size_t(page) * Hk + kvh;
+    uint8_t* st = ring + s * L::kStageBytes;
+    mbar_expect_tx(&bars[s], L::kStageBytes);
+    bulk_load(st, k_cache + ph * L::kPageBytes, L::kPageBytes, &bars[s]);
+    bulk_load(st + L::kPageBytes, v_cache + ph * L::kPageBytes, L::kPageBytes, &bars[s]);
+    bulk_load(st + 2 * L::kPageBytes, k_scale + ph * 16, 64, &bars[s]);
+    bulk_load(st + 2 * L::kPageBytes + 64, v_scale + ph * 16, 64, &bars[s]);
   };
-  // Ring bookkeeping, identical on all lanes: pages issued / consumed so far, and where the issue cursor stands
-  // (inside the current item or already inside the next one).
-  int issued = 0, consumed = 0, iss_in_next = 0, iss_i = 0;
-  auto top_up = [&]() {
-    while (issued - consumed < kAttnStages) {
-      const Item& it = iss_in_next ? nxt : cur;
-      if (!it.valid) break;
-      if (iss_i >= it.my_pages) {
-        if (iss_in_next) break;
-        iss_in_next = 1;
-        iss_i = 0;
-        continue;
-      }
-      if (lane == 0) issue(it, iss_i, issued % kAttnStages);
-      ++iss_i;
-      ++issued;
-    }
-  };
-  bool ok = true;
-
-  while (cur.valid) {
-  const int seq = cur.seq, kvh = cur.kvh, split = cur.split, len = cur.len, page_begin = cur.page_begin, my_pages = cur.my_pages;
-  top_up();
+  if (lane == 0)
+    for (int i = 0; i < min(my_pages, kAttnStages); ++i) issue(i);
 
   // ---- Q fragments (rows r = qr * G + g; dims permuted to match the K page layout) ----
   uint32_t qa[KSTEPS][4];
@@ -183,10 +136,11 @@ paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t*
 #pragma unroll
   for (int j = 0; j < NBD; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
   float m_run[2] = {kNeg, kNeg}, l_run[2] = {0.f, 0.f};
+  bool ok = true;
 
   for (int i = 0; i < my_pages; ++i) {
-    const int s = consumed % kAttnStages;
-    ok = mbar_wait(&bars[s], (consumed / kAttnStages) & 1, abort_flag, status, kStatusTimeoutEpilogue);
+    const int s = i % kAttnStages;
+    ok = mbar_wait(&bars[s], (i / kAttnStages) & 1, abort_flag, status, kStatusTimeoutEpilogue);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
     const uint8_t* st = ring + s * L::kStageBytes;
@@ -268,70 +222,51 @@ paged_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t*
       mma_f16(o[j], pa, e4m3x2_to_f16x2(uint16_t(vw & 0xffffu)), e4m3x2_to_f16x2(uint16_t(vw >> 16)));
     }
     __syncwarp();
-    ++consumed;
-    top_up();  // the freed slot takes this item's next page -- or already the first pages of the next item
+    if (lane == 0 && i + kAttnStages < my_pages) issue(i + kAttnStages);
   }
 
-  // ---- merge: lanes of a row, then the four warps (through a scratch area of its own: the rings stay in flight) ----
+  // ---- merge: lanes of a row, then the four warps (the page ring is reused as scratch) ----
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 1);
     l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 2);
   }
-  float* w_o = reinterpret_cast<float*>(scratch0 + warp * scratch_bytes);  // [R rows][D]
-  float* w_ml = w_o + R * D;                                               // [16][2]
+  float* w_o = reinterpret_cast<float*>(ring);          // [16 rows][D]
+  float* w_ml = w_o + 16 * D;                           // [16][2]   (fits: kWarpBytes >= 16*D*4 + 128)
+  __syncwarp();
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int r = g8 + 8 * half;
-    if (r < R) {
 #pragma unroll
-      for (int j = 0; j < NBD; ++j) {
-        w_o[r * D + 8 * j + 2 * c] = o[j][2 * half];
-        w_o[r * D + 8 * j + 2 * c + 1] = o[j][2 * half + 1];
-      }
-      if (c == 0) { w_ml[2 * r] = m_run[half]; w_ml[2 * r + 1] = l_run[half]; }
+    for (int j = 0; j < NBD; ++j) {
+      w_o[r * D + 8 * j + 2 * c] = o[j][2 * half];
+      w_o[r * D + 8 * j + 2 * c + 1] = o[j][2 * half + 1];
     }
+    if (c == 0) { w_ml[2 * r] = m_run[half]; w_ml[2 * r + 1] = l_run[half]; }
   }
-  if (threadIdx.x == 0) s_item[0] = atomicAdd(work, 1);  // the item after `nxt`; published by the barrier below
   __syncthreads();
-  if (ok && !*abort_flag) {
-    for (int idx = threadIdx.x; idx < R * D; idx += blockDim.x) {
-      const int r = idx / D, d = idx % D;
-      float mm = kNeg;
+  if (!ok || *abort_flag) return;
+  for (int idx = threadIdx.x; idx < R * D; idx += blockDim.x) {
+    const int r = idx / D, d = idx % D;
+    float mm = kNeg;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, reinterpret_cast<const float*>(scratch0 + w * scratch_bytes)[R * D + 2 * r]);
-      float ll = 0.f, a = 0.f;
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, reinterpret_cast<const float*>(smem + w * L::kWarpBytes)[16 * D + 2 * r]);
+    float ll = 0.f, a = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float* wo = reinterpret_cast<const float*>(scratch0 + w * scratch_bytes);
-        const float cw = exp2f(wo[R * D + 2 * r] - mm);
-        ll += wo[R * D + 2 * r + 1] * cw;
-        a += wo[r * D + d] * cw;
-      }
-      const int qr = r / G, g = r % G;
-      const size_t hq = (size_t(seq) * q_len + qr) * Hq + kvh * G + g;
-      if (nsplit == 1) {
-        out[hq * D + d] = __float2bfloat16(ll > 0.f ? a / ll : 0.f);
-      } else {
-        part_acc[(hq * nsplit + split) * D + d] = a;
-        if (d == 0) { part_ml[(hq * nsplit + split) * 2] = mm; part_ml[(hq * nsplit + split) * 2 + 1] = ll; }
-      }
+    for (int w = 0; w < 4; ++w) {
+      const float* wo = reinterpret_cast<const float*>(smem + w * L::kWarpBytes);
+      const float cw = exp2f(wo[16 * D + 2 * r] - mm);
+      ll += wo[16 * D + 2 * r + 1] * cw;
+      a += wo[r * D + d] * cw;
     }
-  }
-  const int following = s_item[0];
-  const bool aborted = *abort_flag != 0;
-  __syncthreads();  // scratch and s_item[0] are free again
-  if (aborted) break;  // a wait ran out somewhere in this CTA: every warp leaves together
-  cur = nxt;
-  nxt = decode_item(following);
-  if (iss_in_next) iss_in_next = 0;  // the cursor stood inside what is now the current item: same index
-  else iss_i = 0;                    // nothing of it was requested yet
-  }  // item loop
-
-  // the last CTA to leave re-arms the counters for the next launch
-  if (threadIdx.x == 0) {
-    const int done = atomicAdd(work + 1, 1);
-    if (done == int(gridDim.x) - 1) { work[0] = 0; work[1] = 0; __threadfence(); }
+    const int qr = r / G, g = r % G;
+    const size_t hq = (size_t(seq) * q_len + qr) * Hq + kvh * G + g;
+    if (nsplit == 1) {
+      out[hq * D + d] = __float2bfloat16(ll > 0.f ? a / ll : 0.f);
+    } else {
+      part_acc[(hq * nsplit + split) * D + d] = a;
+      if (d == 0) { part_ml[(hq * nsplit + split) * 2] = mm; part_ml[(hq * nsplit + split) * 2 + 1] = ll; }
+    }
   }
 }
 
@@ -358,29 +293,22 @@ template <int D, int kAttnStages, int kMinBlocks>
 static int launch_attn_v(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
                          const float* v_scale, const int* block_table, const int* seq_lens, void* out, float* part_acc,
                          float* part_ml, int B, int Hq, int Hk, int max_pages, float sm_scale, int splits, int q_len,
-                         int* work, int* status, cudaStream_t stream) {
+                         int* status, cudaStream_t stream) {
   using L = AttnSmem<D, kAttnStages>;
-  const int rows = (Hq / Hk) * q_len;
-  const int smem_bytes = L::total(rows);
+  static_assert(L::kWarpBytes >= 16 * D * 4 + 128, "the per-warp ring doubles as the merge scratch");
   static bool attr[64] = {};
-  static int sms[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -6;
   if (!attr[dev]) {
-    if (cudaFuncSetAttribute(paged_attn_decode_mma_kernel<D, kAttnStages, kMinBlocks>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(16)) != cudaSuccess)
+    if (cudaFuncSetAttribute(paged_attn_decode_mma_kernel<D, kAttnStages, kMinBlocks>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
       return -6;
-    if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -6;
     attr[dev] = true;
   }
   const float scale_log2 = sm_scale * 1.4426950408889634f;
-  // persistent grid: as many CTAs as fit at once (shared memory decides), never more than there are items
-  const int per_sm = max(1, min(kMinBlocks, (227 * 1024) / (smem_bytes + 1024)));
-  const int items = B * Hk * splits;
-  const int grid = min(items, sms[dev] * per_sm);
-  launch_kernel(paged_attn_decode_mma_kernel<D, kAttnStages, kMinBlocks>, dim3(grid), dim3(128), smem_bytes, stream,
+  launch_kernel(paged_attn_decode_mma_kernel<D, kAttnStages, kMinBlocks>, dim3(B, Hk, splits), dim3(128), L::kTotal, stream, 
       static_cast<const __nv_bfloat16*>(q), static_cast<const uint8_t*>(k_cache), static_cast<const uint8_t*>(v_cache),
-      k_scale, v_scale, block_table, seq_lens, static_cast<__nv_bfloat16*>(out), part_acc, part_ml, B, Hq, Hk, splits, max_pages,
-      scale_log2, q_len, work, status);
+      k_scale, v_scale, block_table, seq_lens, static_cast<__nv_bfloat16*>(out), part_acc, part_ml, Hq, Hk, max_pages,
+      scale_log2, q_len, status);
   if (cudaGetLastError() != cudaSuccess) return -7;
   if (splits > 1) {
     launch_kernel(attn_reduce_log2_kernel<D>, dim3(B * q_len * Hq), dim3(D), 0, stream, part_acc, part_ml, static_cast<__nv_bfloat16*>(out), splits);
@@ -393,11 +321,11 @@ template <int D>
 static int launch_attn(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
                        const float* v_scale, const int* block_table, const int* seq_lens, void* out, float* part_acc,
                        float* part_ml, int B, int Hq, int Hk, int max_pages, float sm_scale, int splits, int q_len,
-                       int* work, int* status, cudaStream_t stream) {
+                       int* status, cudaStream_t stream) {
   // MFQ_ATTN_VARIANT (measurement switch): 0 = 3 pages in flight per warp, 3 CTAs per SM; 1 = 4 pages, 3 CTAs;
   // 2 = 3 pages, 4 CTAs (128 registers); 3 = 6 pages, 2 CTAs
   static const int variant = [] { const char* e = getenv("MFQ_ATTN_VARIANT"); return e ? atoi(e) : 0; }();
-#define MFQ_ATTN_ARGS q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_acc, part_ml, B, Hq, Hk, max_pages, sm_scale, splits, q_len, work, status, stream
+#define MFQ_ATTN_ARGS q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_acc, part_ml, B, Hq, Hk, max_pages, sm_scale, splits, q_len, status, stream
   if constexpr (D <= 128) {
     if (variant == 1) return launch_attn_v<D, 4, 3>(MFQ_ATTN_ARGS);
     if (variant == 2) return launch_attn_v<D, 3, 4>(MFQ_ATTN_ARGS);
@@ -410,21 +338,20 @@ static int launch_attn(const void* q, const void* k_cache, const void* v_cache, 
 }  // namespace mfq
 
 // q: [B * q_len, Hq, D] bf16; caches in the fragment-friendly page layout described at the top of this file;
-// seq_lens count every token visible to the last query row.  (Hq / Hk) * q_len must be <= 16.  work: two ints, zero
-// before the first launch (the kernel returns them to zero); launches that share them must not overlap.
+// seq_lens count every token visible to the last query row.  (Hq / Hk) * q_len must be <= 16.
 extern "C" int mfq_paged_attn_decode_mma(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
                                          const float* v_scale, const int* block_table, const int* seq_lens, void* out,
                                          float* part_acc, float* part_ml, int B, int Hq, int Hk, int D, int max_pages,
-                                         float sm_scale, int splits, int q_len, int* work, int* status, cudaStream_t stream) {
+                                         float sm_scale, int splits, int q_len, int* status, cudaStream_t stream) {
   if (B <= 0 || Hk <= 0 || Hq % Hk || (Hq / Hk) * q_len > 16 || splits < 1) return -1;
   if (D == 128)
     return mfq::launch_attn<128>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_acc, part_ml,
-                                 B, Hq, Hk, max_pages, sm_scale, splits, q_len, work, status, stream);
+                                 B, Hq, Hk, max_pages, sm_scale, splits, q_len, status, stream);
   if (D == 256)
     return mfq::launch_attn<256>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_acc, part_ml,
-                                 B, Hq, Hk, max_pages, sm_scale, splits, q_len, work, status, stream);
+                                 B, Hq, Hk, max_pages, sm_scale, splits, q_len, status, stream);
   if (D == 64)
     return mfq::launch_attn<64>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_acc, part_ml, B,
-                                Hq, Hk, max_pages, sm_scale, splits, q_len, work, status, stream);
+                                Hq, Hk, max_pages, sm_scale, splits, q_len, status, stream);
   return -1;
 }

@@ -190,7 +190,7 @@ def paged_attn_decode(q: torch.Tensor, kv, block_table: torch.Tensor, seq_lens: 
     rc = lib().mfq_paged_attn_decode_mma(ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
                                          ptr(block_table), ptr(seq_lens), ptr(out), ptr(ws.attn_acc), ptr(ws.attn_ml), b,
                                          hq, hk, d, block_table.shape[1], float(sm_scale), splits, q_len,
-                                         ptr(ws.attn_work), ptr(ws.status), stream_ptr())
+                                         ptr(ws.status), stream_ptr())
     check(rc, "paged_attn_decode", 2 if splits > 1 else 1)
     return out
 

@@ -35,7 +35,7 @@ _SIGNATURES = {
                                _f, _f, _f, _f, _vp],
     "mfq_rope_kv_write": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     
-    "mfq_paged_attn_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp],
+    "mfq_paged_attn_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp],
     "mfq_argmax": [_vp, _vp, _i, _i, _i, _vp],
     "mfq_embed": [_vp, _vp, _vp, _i, _i, _vp],
     "mfq_decode_advance": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
@@ -89,7 +89,6 @@ class Workspace:
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.attn_acc = torch.empty(attn_floats, dtype=torch.float32, device=device)
         self.attn_ml = torch.empty(attn_floats // 32, dtype=torch.float32, device=device)
-        self.attn_work = torch.zeros(2, dtype=torch.int32, device=device)  # item / finished-CTA counters of the persistent attention
 
     @classmethod
     def get(cls, device: torch.device) -> "Workspace":
