@@ -241,19 +241,26 @@ class MoeDecoderModel(LlamaModel):
                                               hidden=cfg.hidden_size, max_tokens=per_rank)
         self.ep_min_tokens = 16 * self.tp if min_tokens is None else min_tokens
 
-    def _ffn_all_to_all(self, h, ffn: MoeFfn, xq, xs, ids, wt, shared):
+    def _ffn_all_to_all(self, h, ffn: MoeFfn, xq, xs, ids, wt):
         """Token-sharded expert layer: my slice of the rows goes through dispatch -> local experts -> combine, the
-        finished slices are gathered back into the replicated residual stream; the (tensor-parallel) shared expert's
-        partial sums are reduced as before."""
+        finished slices are gathered back into the replicated residual stream.  A replicated shared expert runs on my
+        slice only and rides along in the combine; a tensor-parallel one runs on all rows and its partial sums are
+        reduced afterwards (by every rank: the collectives must be issued in the same order everywhere)."""
         t, w, r = h.shape[0], self.tp, self.w.tp_rank
         per = t // w
         lo, hi = r * per, (r + 1) * per
         ep = self.expert_parallel
+        extra = partial = None
+        if ffn.shared_gate_up is not None:
+            if ffn.shared_replicated:
+                extra = ffn.shared_down(*ops.silu_mul_quant(ffn.shared_gate_up(xq[lo:hi], xs[lo:hi])))
+            else:
+                partial = ffn.shared_down(*ops.silu_mul_quant(ffn.shared_gate_up(xq, xs)))
         mine = ep.moe_ffn(xq[lo:hi], xs[lo:hi], ids[lo:hi].contiguous(), wt[lo:hi].contiguous(), ffn.gate_up, ffn.gate_up_scale,
-                          ffn.down, ffn.down_scale, base=h[lo:hi], cap=per)
+                          ffn.down, ffn.down_scale, base=h[lo:hi], extra=extra, cap=per)
         self.collective.allgather_rows(mine, out=h)
-        if shared is not None:
-            h = self.collective.allreduce_rows(shared, h)
+        if partial is not None:
+            h = self.collective.allreduce_rows(partial, h)
         return h
 
     def _ffn(self, h, layer):
@@ -271,6 +278,11 @@ class MoeDecoderModel(LlamaModel):
         ids, wt = moe_ops.router_topk(y, ffn.router, cfg.top_k, bias=ffn.router_bias, sigmoid=cfg.router == "sigmoid",
                                       norm_topk=cfg.norm_topk, scale=cfg.routed_scale, n_group=cfg.n_group,
                                       topk_group=cfg.topk_group)
+        t = h.shape[0]
+        ep = self.expert_parallel
+        if (ep is not None and ffn.packed_gate_up is None and ffn.residency is None and self.tp > 1
+                and t >= self.ep_min_tokens and t % self.tp == 0 and t // self.tp <= ep.cap_max):
+            return self._ffn_all_to_all(h, ffn, xq, xs, ids, wt)
         shared = None
         if ffn.shared_gate_up is not None and not (ffn.shared_replicated and self.w.tp_rank != 0):
             sq, ss = ops.silu_mul_quant(ffn.shared_gate_up(xq, xs))
@@ -301,10 +313,6 @@ class MoeDecoderModel(LlamaModel):
         if self.tp == 1:
             return moe_ops.moe_ffn_fp8(xq, xs, ids, wt, ffn.gate_up, ffn.gate_up_scale, ffn.down, ffn.down_scale,
                                        e_lo=ffn.e_lo, base=h, extra=shared, out=h)
-        t = h.shape[0]
-        ep = self.expert_parallel
-        if ep is not None and t >= self.ep_min_tokens and t % self.tp == 0 and t // self.tp <= ep.cap_max:
-            return self._ffn_all_to_all(h, ffn, xq, xs, ids, wt, shared)
         partial = moe_ops.moe_ffn_fp8(xq, xs, ids, wt, ffn.gate_up, ffn.gate_up_scale, ffn.down, ffn.down_scale,
                                       e_lo=ffn.e_lo, base=None, extra=shared)
         return self.collective.allreduce_rows(partial, h)

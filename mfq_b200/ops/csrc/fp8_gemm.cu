@@ -236,7 +236,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             if (int32_t(seen - (ag_epoch + 1u)) >= 0) break;
             if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t_start > kWaitBudgetNs)) {
               *abort_flag = 1;
-              atomicCAS(p.status, 0, kStatusTimeoutPeer);
+              atomicCAS(p.status, 0, kStatusTimeoutPeer | (1 << 8));
               shard_ready = false;
               break;
             }
@@ -459,7 +459,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
               if (int32_t(seen - target) >= 0) break;
               if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t_start > kWaitBudgetNs)) {
                 *abort_flag = 1;
-                atomicCAS(p.status, 0, kStatusTimeoutPeer);
+                atomicCAS(p.status, 0, kStatusTimeoutPeer | (2 << 8));
                 break;
               }
             }

@@ -42,14 +42,15 @@ __device__ __forceinline__ void flag_add_sys(uint32_t* p) {
   asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
 }
 
-__device__ __forceinline__ bool flag_wait_sys(const uint32_t* p, uint32_t target, int* status) {
+__device__ __forceinline__ bool flag_wait_sys(const uint32_t* p, uint32_t target, int* status, int site = 3) {
   const unsigned long long t0 = globaltimer_ns();
   uint32_t seen, spins = 0;
   while (true) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p) : "memory");
     if (int32_t(seen - target) >= 0) return true;
     if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
-      atomicCAS(status, 0, kStatusTimeoutPeer);
+      // status[1..3]: the word's last value, the value awaited and the waiting thread (= source rank), for the report
+      if (atomicCAS(status, 0, kStatusTimeoutPeer | (site << 8)) == 0) { status[1] = int(seen); status[2] = int(target); status[3] = int(threadIdx.x); }
       return false;
     }
   }
@@ -174,7 +175,7 @@ moe_combine_reduce_kernel(const int* __restrict__ send_slot, const __nv_bfloat16
                           A2aParams p, int* status) {
   const int t = blockIdx.x;
   const uint32_t target = p.words[0];
-  if (int(threadIdx.x) < p.world) flag_wait_sys(p.flags[p.rank] + p.world + threadIdx.x, target, status);
+  if (int(threadIdx.x) < p.world) flag_wait_sys(p.flags[p.rank] + p.world + threadIdx.x, target, status, 10);
   __syncthreads();
   if (t >= T) return;  // a rank without tokens still waits, so that it cannot run ahead of its peers
   const __nv_bfloat16* comb = p.comb[p.rank];

@@ -72,7 +72,7 @@ argmax_allgather_kernel(const __nv_bfloat16* __restrict__ logits, int* __restric
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
     if (int32_t(seen - target) >= 0) break;
     if ((++spins & 0x3F) == 0 && globaltimer_ns() - t_start > kWaitBudgetNs) {
-      atomicCAS(status, 0, kStatusTimeoutPeer);
+      atomicCAS(status, 0, kStatusTimeoutPeer | (4 << 8));
       ok = false;
       break;
     }
@@ -154,7 +154,7 @@ allreduce_rows_kernel(const __nv_bfloat16* __restrict__ partial, const __nv_bflo
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
       if (int32_t(seen - target) >= 0) break;
       if ((++spins & 0x3F) == 0 && globaltimer_ns() - t_start > kWaitBudgetNs) {
-        atomicCAS(status, 0, kStatusTimeoutPeer);
+        atomicCAS(status, 0, kStatusTimeoutPeer | (5 << 8));
         ok = 0;
         break;
       }
@@ -239,7 +239,7 @@ __global__ void peer_barrier_kernel(int world, int rank, uint32_t* f0, uint32_t*
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags[rank]) : "memory");
     if (int32_t(seen - target) >= 0) break;
     if ((++spins & 0x3F) == 0 && globaltimer_ns() - t_start > kWaitBudgetNs) {
-      atomicCAS(status, 0, kStatusTimeoutPeer);
+      atomicCAS(status, 0, kStatusTimeoutPeer | (6 << 8));
       break;
     }
   }
@@ -312,7 +312,7 @@ allgather_collect_kernel(uint8_t* __restrict__ out, size_t total_bytes, GatherPa
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
       if (int32_t(seen - target) >= 0) break;
       if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
-        atomicCAS(status, 0, kStatusTimeoutPeer);
+        atomicCAS(status, 0, kStatusTimeoutPeer | (7 << 8));
         s_ok = 0;
         break;
       }

@@ -110,7 +110,7 @@ tp_reduce_norm_quant_kernel(const ReduceParams p, int M, int H, int half, const 
   }
   if (tid < p.world && tid != p.rank) {
     if (!wait_word(p.flags[p.rank] + tid, want)) {
-      atomicCAS(status, 0, kStatusTimeoutPeer);
+      atomicCAS(status, 0, kStatusTimeoutPeer | (8 << 8));
       s_flag = 0;
     }
   }
@@ -241,7 +241,7 @@ tp_reduce_norm_quant_kernel(const ReduceParams p, int M, int H, int half, const 
     if (tid < p.world && tid != p.rank) {
       __threadfence_system();
       st_release_sys(p.flags[tid] + 8 + p.rank, want);
-      if (ready && !wait_word(p.flags[p.rank] + 8 + tid, want)) atomicCAS(status, 0, kStatusTimeoutPeer);
+      if (ready && !wait_word(p.flags[p.rank] + 8 + tid, want)) atomicCAS(status, 0, kStatusTimeoutPeer | (9 << 8));
     }
     __syncthreads();
   }

@@ -76,6 +76,12 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+# the wait on another rank that ran out, as tagged by the kernels (status word bits 8 and up)
+_PEER_WAIT_SITES = {1: "all-gather GEMM: shard flag", 2: "GEMM all-reduce epilogue: tile flags", 3: "expert all-to-all: dispatched rows", 10: "expert all-to-all: combined rows",
+                    4: "arg-max all-gather", 5: "row all-reduce", 6: "peer barrier", 7: "row all-gather",
+                    8: "fused reduce: partials ready", 9: "fused reduce: rows pushed"}
+
+
 class Workspace:
     """Per-device scratch shared by the kernels (sized once; grows never during graph capture)."""
 
@@ -101,10 +107,13 @@ class Workspace:
 
     def check(self) -> None:
         """Raise if any kernel recorded a timed-out wait since the last check (synchronizes)."""
-        code = int(self.status[0].item())
-        if code:
+        word = int(self.status[0].item())
+        if word:
+            detail = self.status[1:].tolist()
             self.status.zero_()
-            raise RuntimeError(f"a kernel gave up waiting (status code {code}); results are invalid")
+            code, site = word & 0xFF, word >> 8
+            where = f", wait site {site} ({_PEER_WAIT_SITES.get(site, '?')}; detail {detail})" if site else ""
+            raise RuntimeError(f"a kernel gave up waiting (status code {code}{where}); results are invalid")
 
 
 _LAUNCHES = [0]

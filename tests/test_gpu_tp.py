@@ -30,7 +30,7 @@ def test_tp_matches_single_gpu_and_nccl_baseline(world):
     # both paths re-quantize activations to FP8 after every block, so rounding differences move a few codes
     assert r["fused_vs_nccl_max_err"] <= 0.12 * r["logit_scale"], r
     assert r["tp_vs_single_max_err"] <= 0.15 * r["logit_scale"], r
-    assert r["tp_vs_single_top1"] >= 0.6, r  # near-flat random-init logits flip their arg-max easily
+    assert r["tp_vs_single_top1"] >= 0.75, r  # near-flat random-init logits: FP8 re-rounding flips about one arg-max in seven
     assert r["fused_reduce_h_exact"] and r["fused_reduce_q_err"] <= 0.07, r  # one E4M3 step at most (2^-3 relative)
     assert r["rs_max_err"] <= 0.02 and r["ag_max_err"] <= 0.02 and r["ar2_max_err"] <= 0.02, r
     # a routed token whose top-k changes under FP8 rounding moves whole logit rows: bound the mean tightly, the max loosely
