@@ -379,6 +379,14 @@ __global__ void gdn_select_kernel(const float* __restrict__ ckpt, const float* _
   }
 }
 
+// Host entry of the post-pass for the other translation units of the library (the chunked prefill).
+int launch_gdn_gated_norm(const float* o_raw, const void* z, const float* norm_w, void* y, size_t pairs, int Hv, float eps,
+                          int z_stride, cudaStream_t stream) {
+  gdn_gated_norm_kernel<<<unsigned((pairs + 7) / 8), 256, 0, stream>>>(o_raw, static_cast<const __nv_bfloat16*>(z), norm_w,
+                                                                       static_cast<__nv_bfloat16*>(y), pairs, Hv, eps, z_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
 }  // namespace mfq
 
 using namespace mfq;

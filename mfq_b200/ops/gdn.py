@@ -19,6 +19,8 @@ from .lib import check, lib, ptr, stream_ptr
 _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
 _bound = False
 PREFILL_MIN_TOKENS = 8  # rows longer than this take the prefill kernels
+CHUNKED_MIN_TOKENS = 64  # rows at least this long take the chunked (WY) prefill; shorter ones the token-serial one
+_scratch: dict[int, torch.Tensor] = {}
 
 
 def _lib():
@@ -29,6 +31,9 @@ def _lib():
         L.mfq_gdn_recurrent.argtypes = [_vp] * 11 + [_i] * 6 + [_f, _i, _i, _vp]
         L.mfq_gdn_select.argtypes = [_vp] * 6 + [_i] * 6 + [_vp]
         L.mfq_gdn_prefill.argtypes = [_vp] * 12 + [_i] * 6 + [_f, _i, _i, _vp]
+        L.mfq_gdn_prefill_chunked.argtypes = [_vp] * 12 + [C.c_longlong] + [_i] * 6 + [_f, _i, _i, _vp, _vp]
+        L.mfq_gdn_chunk_scratch_floats.argtypes = [_i] * 4
+        L.mfq_gdn_chunk_scratch_floats.restype = C.c_longlong
         _bound = True
     return L
 
@@ -70,6 +75,22 @@ def recurrent(qkv: torch.Tensor, z: torch.Tensor, a: torch.Tensor, b: torch.Tens
     rows = n // L
     dk, dv = state.shape[2], state.shape[3]
     y = torch.empty((n, Hv * dv), dtype=torch.bfloat16, device=qkv.device)
+    if qkv.is_cuda and ckpt is None and L >= CHUNKED_MIN_TOKENS:
+        # 64-token chunks: a parallel pre-pass solves each chunk's triangular system, a scan carries the state
+        # over the chunks on tensor cores (``csrc/gdn_chunk.cu``); ``qkv`` is left as it is
+        lb = _lib()
+        need = int(lb.mfq_gdn_chunk_scratch_floats(rows, L, Hk, Hv))
+        dev = qkv.device.index or 0
+        scratch = _scratch.get(dev)
+        if scratch is None or scratch.numel() < need:
+            scratch = _scratch[dev] = torch.empty(need, dtype=torch.float32, device=qkv.device)
+        o_raw = torch.empty((n, Hv * dv), dtype=torch.float32, device=qkv.device)
+        from .lib import Workspace
+        check(lb.mfq_gdn_prefill_chunked(ptr(qkv), ptr(z), ptr(a), ptr(b), ptr(A_log), ptr(dt_bias), ptr(norm_w), ptr(state),
+                                         ptr(slot), ptr(y), ptr(o_raw), ptr(scratch), scratch.numel(), rows, L, Hk, Hv, dk, dv,
+                                         float(eps), z.stride(0), a.stride(0), ptr(Workspace.get(qkv.device).status),
+                                         stream_ptr()), "gdn_prefill_chunked", 3)
+        return y
     if qkv.is_cuda and ckpt is None and L > PREFILL_MIN_TOKENS:
         # long rows: pre-pass / 4-threads-per-column recurrence / post-pass (normalises q and k inside ``qkv`` in place)
         o_raw = torch.empty((n, Hv * dv), dtype=torch.float32, device=qkv.device)

@@ -42,7 +42,8 @@ def _run(t, dev, L, hk, hv, ckpt=False):
     return conv_out, y, d, cck, sck
 
 
-@pytest.mark.parametrize("b,L,hk,hv", [(5, 1, 2, 4), (1, 67, 2, 2), (3, 4, 1, 2), (1, 9, 1, 2), (3, 300, 2, 4), (1, 1024, 1, 1)])
+@pytest.mark.parametrize("b,L,hk,hv", [(5, 1, 2, 4), (1, 67, 2, 2), (3, 4, 1, 2), (1, 9, 1, 2), (3, 300, 2, 4), (1, 1024, 1, 1),
+                                       (1, 64, 1, 2), (2, 2048, 2, 4)])
 def test_gdn_matches_reference(b, L, hk, hv):
     require_gpu_lib()
     t, _ = _problem(b, L, hk, hv, slots=b + 2, seed=b * 10 + L)
@@ -55,6 +56,31 @@ def test_gdn_matches_reference(b, L, hk, hv):
     assert_close(yg.float().cpu()[live], yc.float()[live], rel=2e-2, what="gdn output")
     assert_close(dg["state"].cpu(), dc["state"], rel=1e-3, what="state")
     assert_close(dg["conv_state"].cpu(), dc["conv_state"], rel=1e-6, what="conv state")
+
+
+def test_gdn_token_serial_prefill_still_matches(monkeypatch):
+    """Rows shorter than a chunk keep the token-serial long-row kernels; force them for a longer row too."""
+    require_gpu_lib()
+    monkeypatch.setattr(gdn, "CHUNKED_MIN_TOKENS", 1 << 30)
+    t, _ = _problem(2, 150, 2, 4, slots=3, seed=5)
+    _, yg, dg, _, _ = _run(t, "cuda", 150, 2, 4)
+    _, yc, dc, _, _ = _run(t, "cpu", 150, 2, 4)
+    check_status()
+    assert_close(yg.float().cpu(), yc.float(), rel=2e-2, what="gdn output")
+    assert_close(dg["state"].cpu(), dc["state"], rel=1e-3, what="state")
+
+
+def test_gdn_chunked_prefill_equals_token_serial_kernels(monkeypatch):
+    """The chunked scan runs its products in tf32; against the fp32 token-serial kernels on the same device the raw
+    state differs by about a tf32 step (2^-11) of its largest entry."""
+    require_gpu_lib()
+    t, _ = _problem(1, 1000, 2, 4, slots=2, seed=9)
+    _, y_chunk, d_chunk, _, _ = _run(t, "cuda", 1000, 2, 4)
+    monkeypatch.setattr(gdn, "CHUNKED_MIN_TOKENS", 1 << 30)
+    _, y_serial, d_serial, _, _ = _run(t, "cuda", 1000, 2, 4)
+    check_status()
+    assert_close(d_chunk["state"].cpu(), d_serial["state"].cpu(), rel=1.5e-3, what="state")
+    assert_close(y_chunk.float().cpu(), y_serial.float().cpu(), rel=1e-2, what="gdn output")
 
 
 def test_gdn_verify_window_checkpoints_and_select():
