@@ -55,6 +55,43 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, float* __re
   }
 }
 
+// Long rows (prefill): a thread owns two adjacent channels and a run of kConvRun consecutive tokens, slides the 4-tap window
+// through registers (every input is read once, as a 4-byte pair) and keeps eight independent loads in flight.
+constexpr int kConvRun = 32;
+__global__ void __launch_bounds__(128) gdn_conv_long_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ conv_state,
+                                                            const float* __restrict__ w, const int* __restrict__ slot,
+                                                            float* __restrict__ out, int L, int C, int xs) {
+  const int b = blockIdx.y;
+  const int s = slot[b];
+  if (s < 0) return;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= C) return;
+  const float4 wa = *reinterpret_cast<const float4*>(w + c * 4), wb = *reinterpret_cast<const float4*>(w + c * 4 + 4);
+  const float* st = conv_state + size_t(s) * 3 * C;
+  const int t0 = blockIdx.z * kConvRun;
+  auto in = [&](int t) -> float2 {
+    if (t >= 0) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + (size_t(b) * L + t) * xs + c));
+    return *reinterpret_cast<const float2*>(st + (3 + t) * C + c);  // t = -3, -2, -1: history rows 0, 1, 2
+  };
+  float2 p3 = in(t0 - 3), p2 = in(t0 - 2), p1 = in(t0 - 1);
+  const int n = min(kConvRun, L - t0);
+  for (int i = 0; i < n; i += 8) {
+    float2 cur[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) cur[e] = (i + e < n) ? in(t0 + i + e) : make_float2(0.f, 0.f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      if (i + e < n) {
+        const float ya = wa.x * p3.x + wa.y * p2.x + wa.z * p1.x + wa.w * cur[e].x;
+        const float yb = wb.x * p3.y + wb.y * p2.y + wb.z * p1.y + wb.w * cur[e].y;
+        *reinterpret_cast<float2*>(out + (size_t(b) * L + t0 + i + e) * C + c) =
+            make_float2(ya / (1.f + __expf(-ya)), yb / (1.f + __expf(-yb)));
+      }
+      p3 = p2; p2 = p1; p1 = cur[e];
+    }
+  }
+}
+
 // History update, as a launch of its own AFTER the convolution: blocks of the convolution that handle the first
 // tokens still read the old history, so it cannot be overwritten by a sibling block of the same grid.
 __global__ void gdn_conv_state_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ conv_state,
@@ -394,6 +431,12 @@ using namespace mfq;
 extern "C" int mfq_gdn_conv(const void* x, float* conv_state, const float* w, const int* slot, float* out, float* conv_ckpt,
                             int B, int L, int C, int x_stride, cudaStream_t stream) {
   if (B <= 0 || L <= 0 || C <= 0 || x_stride < C) return -1;
+  if (!conv_ckpt && L >= 2 * kConvRun && C % 2 == 0 && x_stride % 2 == 0) {
+    gdn_conv_long_kernel<<<dim3((C / 2 + 127) / 128, B, (L + kConvRun - 1) / kConvRun), 128, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), conv_state, w, slot, out, L, C, x_stride);
+    launch_kernel(gdn_conv_state_kernel, dim3((C + 255) / 256, B), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), conv_state, slot, L, C, x_stride);
+    return cudaGetLastError() == cudaSuccess ? 0 : -7;
+  }
   dim3 grid((C + 255) / 256, B, min(L, 64));
   const int fused_state = (!conv_ckpt && grid.z == 1) ? 1 : 0;  // decode: no second launch
   launch_kernel(gdn_conv_kernel, grid, dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), conv_state, w, slot, out, conv_ckpt, L, C, x_stride, fused_state);
