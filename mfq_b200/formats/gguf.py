@@ -5,7 +5,8 @@ Face directory.  A small writer exists for tests and fixtures.
 File layout (little endian): ``"GGUF"``, version u32 (2 or 3), tensor count u64, key/value count u64; the key/value
 pairs (string key, u32 type, value; arrays carry an element type and a u64 count); the tensor infos (name, u32 rank,
 u64 dims with the innermost first, u32 ggml type, u64 offset into the data section); padding to ``general.alignment``
-(default 32); tensor data.  Decoded here: F32, F16, BF16, Q8_0, Q4_0, Q4_1, Q5_0, Q5_1 (blocks of 32).  Reference:
+(default 32); tensor data.  Decoded here: F32, F16, BF16, Q8_0, Q4_0, Q4_1, Q5_0, Q5_1 (blocks of 32), the 256-value super-block
+types Q2_K .. Q6_K, IQ4_NL and IQ4_XS.  Reference:
 ``mfq/tools/quantize_gguf_to_mfq.py`` (the reference's GGUF front end) and ``mfq/commands/quantize.py:308-322``
 (source detection).
 """
@@ -113,8 +114,11 @@ def decode(buf: np.ndarray, start: int, n: int, kind: int) -> np.ndarray:
     if kind == GGML_BF16:
         raw = np.frombuffer(buf, dtype="<u2", count=n, offset=start).astype(np.uint32) << 16
         return raw.view(np.float32)
+    if kind in _SUPER_BLOCK_BYTES or kind == GGML_IQ4_NL:
+        return _decode_k(buf, start, n, kind)
     if kind not in _BLOCK_BYTES:
-        raise NotImplementedError(f"ggml tensor type {kind} is not decoded here (F32, F16, BF16, Q8_0, Q4_0/1, Q5_0/1 are)")
+        raise NotImplementedError(f"ggml tensor type {kind} is not decoded here (F32, F16, BF16, Q8_0, Q4_0/1, Q5_0/1, "
+                                  "Q2_K .. Q6_K, IQ4_NL and IQ4_XS are)")
     if n % 32:
         raise ValueError("block-quantized tensors hold a multiple of 32 values")
     nb, bb = n // 32, _BLOCK_BYTES[kind]
@@ -142,6 +146,96 @@ def decode(buf: np.ndarray, start: int, n: int, kind: int) -> np.ndarray:
     if has_min:
         return (q * d + m).reshape(-1)
     return ((q - (16.0 if high is not None else 8.0)) * d).reshape(-1)
+
+
+# ---- 256-value super-blocks (the "K" family) and the 4-bit non-linear types ---------------------------------------------
+GGML_Q2_K, GGML_Q3_K, GGML_Q4_K, GGML_Q5_K, GGML_Q6_K, GGML_IQ4_NL, GGML_IQ4_XS = 10, 11, 12, 13, 14, 20, 23
+_SUPER_BLOCK_BYTES = {GGML_Q2_K: 84, GGML_Q3_K: 110, GGML_Q4_K: 144, GGML_Q5_K: 176, GGML_Q6_K: 210, GGML_IQ4_XS: 136}
+_IQ4_VALUES = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.float32)
+
+
+def _scale_min_6bit(sc: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """The eight 6-bit (scale, min) pairs packed in 12 bytes of a Q4_K / Q5_K block: ``[blocks, 8]`` each."""
+    lo, mid, hi = sc[:, 0:4], sc[:, 4:8], sc[:, 8:12]
+    scale = np.concatenate([lo & 63, (hi & 0x0F) | ((lo >> 6) << 4)], axis=1)
+    mins = np.concatenate([mid & 63, (hi >> 4) | ((mid >> 6) << 4)], axis=1)
+    return scale.astype(np.float32), mins.astype(np.float32)
+
+
+def _decode_k(buf: np.ndarray, start: int, n: int, kind: int) -> np.ndarray:
+    """Super-block types: every block of 256 values (32 for IQ4_NL) carries an fp16 multiplier and packed sub-block
+    scales; the sub-block order below is the one ggml's reference dequantizers walk."""
+    if kind == GGML_IQ4_NL:
+        if n % 32:
+            raise ValueError("IQ4_NL tensors hold a multiple of 32 values")
+        blocks = np.frombuffer(buf, dtype=np.uint8, count=n // 32 * 18, offset=start).reshape(-1, 18)
+        d = _f16(np.ascontiguousarray(blocks[:, :2]))
+        nib = blocks[:, 2:]
+        q = np.concatenate([nib & 0x0F, nib >> 4], axis=1)
+        return (_IQ4_VALUES[q] * d).reshape(-1)
+    if n % 256:
+        raise ValueError("super-block tensors hold a multiple of 256 values")
+    nb, bb = n // 256, _SUPER_BLOCK_BYTES[kind]
+    blk = np.frombuffer(buf, dtype=np.uint8, count=nb * bb, offset=start).reshape(nb, bb)
+
+    def f16(a, b):
+        return _f16(np.ascontiguousarray(blk[:, a:b]))
+
+    if kind == GGML_Q2_K:
+        scales, qs, d, dmin = blk[:, :16], blk[:, 16:80], f16(80, 82), f16(82, 84)
+        # value (half, shift j, l) reads byte qs[32 half + l], bits 2j..2j+1; its scale is number 8 half + 2 j + l // 16
+        q = qs.reshape(nb, 2, 1, 32) >> (2 * np.arange(4, dtype=np.uint8)).reshape(1, 1, 4, 1) & 3
+        sc = scales.reshape(nb, 2, 4, 2).repeat(16, axis=3)
+        out = d[:, :, None, None] * (sc & 0x0F) * q - dmin[:, :, None, None] * (sc >> 4)
+        return out.astype(np.float32).reshape(-1)
+    if kind == GGML_Q3_K:
+        hmask, qs, packed, d = blk[:, :32], blk[:, 32:96], blk[:, 96:108], f16(108, 110)
+        aux = np.ascontiguousarray(packed).view("<u4").astype(np.uint32)  # [nb, 3]
+        k1, k2 = np.uint32(0x03030303), np.uint32(0x0F0F0F0F)
+        tmp = aux[:, 2]
+        words = np.stack([(aux[:, 0] & k2) | ((tmp & k1) << 4), (aux[:, 1] & k2) | (((tmp >> 2) & k1) << 4),
+                          ((aux[:, 0] >> 4) & k2) | (((tmp >> 4) & k1) << 4),
+                          ((aux[:, 1] >> 4) & k2) | (((tmp >> 6) & k1) << 4)], axis=1).astype("<u4")
+        sc = np.ascontiguousarray(words).view(np.uint8).reshape(nb, 16).astype(np.float32) - 32.0
+        low = (qs.reshape(nb, 2, 1, 32) >> (2 * np.arange(4, dtype=np.uint8)).reshape(1, 1, 4, 1) & 3).astype(np.float32)
+        bit = (hmask.reshape(nb, 1, 1, 32) >> np.arange(8, dtype=np.uint8).reshape(1, 2, 4, 1)) & 1  # bit 4 half + j
+        q = low - np.where(bit == 1, 0.0, 4.0)
+        out = d[:, :, None, None] * sc.reshape(nb, 2, 4, 2).repeat(16, axis=3) * q
+        return out.astype(np.float32).reshape(-1)
+    if kind in (GGML_Q4_K, GGML_Q5_K):
+        d, dmin = f16(0, 2), f16(2, 4)
+        scale, mins = _scale_min_6bit(blk[:, 4:16])
+        if kind == GGML_Q4_K:
+            ql = blk[:, 16:144].reshape(nb, 4, 32)
+            high = np.zeros((nb, 4, 2, 32), dtype=np.uint8)
+        else:
+            qh, ql = blk[:, 16:48], blk[:, 48:176].reshape(nb, 4, 32)
+            # values 64 j + l take bit 2 j of qh[l], values 64 j + 32 + l bit 2 j + 1
+            high = ((qh.reshape(nb, 1, 1, 32) >> np.arange(8, dtype=np.uint8).reshape(1, 4, 2, 1)) & 1) << 4
+        q = np.stack([ql & 0x0F, ql >> 4], axis=2) | high  # [nb, 4, 2, 32]
+        out = (d * scale).reshape(nb, 4, 2, 1) * q - (dmin * mins).reshape(nb, 4, 2, 1)
+        return out.astype(np.float32).reshape(-1)
+    if kind == GGML_Q6_K:
+        ql, qh = blk[:, :128].reshape(nb, 2, 2, 32), blk[:, 128:192].reshape(nb, 2, 1, 32)
+        sc = blk[:, 192:208].view(np.int8).astype(np.float32).reshape(nb, 2, 4, 2)
+        d = f16(208, 210)
+        # per half: values l, l + 32 take the low nibbles of ql[l], ql[l + 32]; l + 64, l + 96 the high ones;
+        # two more bits each come from qh[l] at shifts 0, 2, 4, 6
+        nib = np.concatenate([ql & 0x0F, ql >> 4], axis=2)  # [nb, 2, 4, 32]
+        top = (qh >> (2 * np.arange(4, dtype=np.uint8)).reshape(1, 1, 4, 1)) & 3
+        q = (nib | (top << 4)).astype(np.float32) - 32.0
+        out = d[:, :, None, None] * sc.repeat(16, axis=3) * q
+        return out.astype(np.float32).reshape(-1)
+    if kind == GGML_IQ4_XS:
+        d = f16(0, 2)
+        sh = np.ascontiguousarray(blk[:, 2:4]).view("<u2").astype(np.uint32)  # [nb, 1]
+        sl, qs = blk[:, 4:8], blk[:, 8:136].reshape(nb, 8, 16)
+        ib = np.arange(8)
+        ls = ((sl[:, ib // 2] >> (4 * (ib % 2)).astype(np.uint8)) & 0x0F).astype(np.uint32) | (((sh >> (2 * ib).astype(np.uint32)) & 3) << 4)
+        q = np.concatenate([qs & 0x0F, qs >> 4], axis=2)  # [nb, 8, 32]
+        out = (d * (ls.astype(np.float32) - 32.0))[:, :, None] * _IQ4_VALUES[q]
+        return out.astype(np.float32).reshape(-1)
+    raise NotImplementedError(kind)
 
 
 # ---- names and config -------------------------------------------------------------------------------------------

@@ -4,6 +4,7 @@ contiguous; outputs may be preallocated (needed under CUDA-graph capture) or are
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -61,10 +62,27 @@ def pick_splits(m: int, n: int, k: int, sms: int = 148) -> int:
     return best
 
 
+PAIR_MIN_ROWS = 1024  # batches at least this wide take the two-SM GEMM (``csrc/fp8_gemm_2cta.cu``)
+
+
+def pair_tile(m: int, n: int) -> int:
+    """Token tile of the two-SM GEMM for this shape, 0 = use the one-SM kernel.  ``MFQ_GEMM_PAIR`` = 0 / 128 / 256
+    overrides the choice."""
+    forced = os.environ.get("MFQ_GEMM_PAIR")
+    tile = int(forced) if forced not in (None, "") else _PAIR_DEFAULT
+    if tile not in (128, 256) or n % 256 or m < PAIR_MIN_ROWS:
+        return 0
+    return tile
+
+
+_PAIR_DEFAULT = 0
+
+
 def fp8_gemm(x_q: torch.Tensor, x_scale: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor, *,
              out: torch.Tensor | None = None, residual: torch.Tensor | None = None, splits: int | None = None,
-             token_tile: int | None = None) -> torch.Tensor:
-    """``out[M, N] = (x_q * x_scale[:, None]) @ (w_q * blockscale(w_scale)).T`` in bf16 (+ residual)."""
+             token_tile: int | None = None, pair: int | None = None) -> torch.Tensor:
+    """``out[M, N] = (x_q * x_scale[:, None]) @ (w_q * blockscale(w_scale)).T`` in bf16 (+ residual).
+    ``pair``: token tile (128 / 256) of the two-SM kernel, 0 = never, None = by shape (:func:`pair_tile`)."""
     m, k = x_q.shape
     n = w_q.shape[0]
     assert w_q.shape[1] == k and k % 128 == 0 and x_q.dtype == FP8 and w_q.dtype == FP8
@@ -77,6 +95,14 @@ def fp8_gemm(x_q: torch.Tensor, x_scale: torch.Tensor, w_q: torch.Tensor, w_scal
         check(rc, "fp8_gemv")
         return out
     ws = Workspace.get(x_q.device)
+    if pair is None:
+        pair = pair_tile(m, n) if splits is None and token_tile is None else 0
+    if pair:
+        assert pair in (128, 256) and n % 256 == 0
+        rc = lib().mfq_fp8_gemm_pair(ptr(w_q), ptr(w_scale), ptr(x_q), ptr(x_scale), ptr(out), ptr(residual), ptr(ws.status),
+                                     m, n, k, pair, stream_ptr())
+        check(rc, "fp8_gemm_pair")
+        return out
     bt = token_tile or _token_tile(m)
     sp = pick_splits(m, n, k) if splits is None else splits
     rc = lib().mfq_fp8_gemm(ptr(w_q), ptr(w_scale), ptr(x_q), ptr(x_scale), ptr(out), ptr(residual), ptr(ws.splitk),

@@ -19,6 +19,7 @@ _vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
 
 _SIGNATURES = {
     "mfq_fp8_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
+    "mfq_fp8_gemm_pair": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "mfq_fp8_gemm_allreduce": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp,
                                _vp, _sz, _i, _vp],
     "mfq_fp8_gemm_allgather": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp],

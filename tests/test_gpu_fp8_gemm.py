@@ -80,3 +80,17 @@ def test_weight_streaming_gemv_matches_reference(m, n, k):
     h = res.clone()
     ops.fp8_gemm(xq, xs, wq, ws, residual=h, out=h)
     assert_close(h, want, what="gemv residual in place")
+
+
+@pytest.mark.parametrize("tile", [128, 256])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (300, 512, 1024), (1024, 768, 2048)])
+def test_fp8_gemm_on_sm_pairs_matches_reference(m, n, k, tile):
+    """The two-SM kernel (a CTA pair per 256 weight rows, tokens shared through the tensor core's peer read)."""
+    require_gpu_lib()
+    xq, xs, wq, ws = make(m, n, k, seed=m + n + tile)
+    res = torch.randn((m, n), device="cuda").to(torch.bfloat16)
+    got = ops.fp8_gemm(xq, xs, wq, ws, pair=tile, residual=res)
+    check_status()
+    assert_close(got, ref.fp8_gemm(xq, xs, wq, ws, residual=res), what=f"pair gemm {m}x{n}x{k} tile {tile}")
+    again = ops.fp8_gemm(xq, xs, wq, ws, pair=tile, residual=res)
+    assert torch.equal(got, again)
