@@ -54,7 +54,7 @@ def read_hf_directory(path) -> tuple[dict, dict[str, np.ndarray], dict[str, byte
     for fname in ("tokenizer.json", "tokenizer_config.json", "generation_config.json", "chat_template.jinja"):
         if (p / fname).exists():
             assets[f"hf/{fname}"] = (p / fname).read_bytes()
-    return config_from_hf(hf_cfg), to_canonical(tensors), assets
+    return config_from_hf(hf_cfg), to_canonical(tensors, hf_cfg), assets
 
 
 def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", expert_mix: str = "", seed: int = 20260908,

@@ -248,6 +248,20 @@ _BLOCK = {
     "ffn_gate_exps.weight": "mlp.experts.gate.weight", "ffn_up_exps.weight": "mlp.experts.up.weight",
     "ffn_down_exps.weight": "mlp.experts.down.weight", "ffn_gate_shexp.weight": "mlp.shared_expert.gate.weight",
     "ffn_up_shexp.weight": "mlp.shared_expert.up.weight", "ffn_down_shexp.weight": "mlp.shared_expert.down.weight",
+    "ffn_gate_inp_shexp.weight": "mlp.shared_expert.router.weight", "ffn_gate_up_exps.weight": "mlp.experts.gate_up.weight",
+    "post_attention_norm.weight": "mlp.norm.weight", "exp_probs_b.bias": "mlp.router.bias",
+    # hybrid family (Gated DeltaNet layers), llama.cpp's names for them (mfq/architectures/tensor_schema.py:584-595)
+    "attn_qkv.weight": "linear_attention.qkv.weight", "attn_gate.weight": "linear_attention.gate.weight",
+    "ssm_alpha.weight": "linear_attention.alpha.weight", "ssm_beta.weight": "linear_attention.beta.weight",
+    "ssm_conv1d.weight": "linear_attention.conv.weight", "ssm_dt.bias": "linear_attention.dt_bias",
+    "ssm_a": "linear_attention.a", "ssm_norm.weight": "linear_attention.norm.weight", "ssm_out.weight": "linear_attention.output.weight",
+    # latent attention (DeepSeek style)
+    "attn_q_a.weight": "attention.query_a.weight", "attn_q_a_norm.weight": "attention.query_a_norm.weight",
+    "attn_q_b.weight": "attention.query_b.weight", "attn_kv_a_mqa.weight": "attention.key_value_a.weight",
+    "attn_kv_a_norm.weight": "attention.key_value_a_norm.weight", "attn_kv_b.weight": "attention.key_value_b.source.weight",
+    # appended next-token-prediction layer
+    "nextn.eh_proj.weight": "predictor.fusion.weight", "nextn.enorm.weight": "predictor.embedding_norm.weight",
+    "nextn.hnorm.weight": "predictor.hidden_norm.weight", "nextn.shared_head_norm.weight": "predictor.output_norm.weight",
 }
 _TOP = {"token_embd.weight": "model.token_embedding.weight", "output_norm.weight": "model.output_norm.weight",
         "output.weight": "model.output.weight"}
@@ -259,7 +273,8 @@ def canonical_name(name: str) -> str | None:
     if name.startswith("blk."):
         _, idx, rest = name.split(".", 2)
         if rest in _BLOCK:
-            return f"model.block.{idx}.{_BLOCK[rest]}"
+            target = _BLOCK[rest]
+            return target if target.startswith("predictor.") else f"model.block.{idx}.{target}"
     return None
 
 
