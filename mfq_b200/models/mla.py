@@ -22,6 +22,7 @@ from dataclasses import dataclass
 
 import torch
 
+from .. import ops
 from ..ops import reference as ref
 from .llama import Fp8Linear, StepBuffers
 from .moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeFfn, MoeLayer, MoeWeights
@@ -36,7 +37,7 @@ class MlaConfig(MoeDecoderConfig):
     qk_nope_head_dim: int = 128
     qk_rope_head_dim: int = 64
     v_head_dim: int = 128
-    absorbed: bool = False  # latent cache + weight-absorbed attention (reference path on CPU tensors only)
+    absorbed: bool = False  # latent cache + weight-absorbed attention (GPU kernels need latent 512 + rotary 64)
     name: str = "mla-moe-fp8"
 
     def __post_init__(self):
@@ -114,7 +115,7 @@ class MlaModel(MoeDecoderModel):
         values instead of ``2 * Hq * 256``), queries are mapped into the latent space, attention runs as Hq query heads
         over one shared key/value row, and the latent output is expanded by ``W_v`` afterwards."""
         if h.is_cuda:
-            raise NotImplementedError("the latent-cache path has no GPU kernel yet (576-wide shared-row attention)")
+            return self._mla_absorbed_gpu(h, layer, kv, step, prefill)
         cfg, m = self.cfg, layer.mla
         nope, rope, vd, hq, lat = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, self.hq, cfg.kv_lora_rank
         t = h.shape[0]
@@ -133,6 +134,48 @@ class MlaModel(MoeDecoderModel):
         qkv[:, hq + 1, :lat] = c_n  # value row = the latent (the cache class keeps keys and values the same width)
         o_lat = self._attention(qkv.view(t, (hq + 2) * d), kv, step, prefill).view(t, hq, d)[:, :, :lat]
         return torch.einsum("thl,hvl->thv", o_lat.float(), wv).to(torch.bfloat16).reshape(t, hq * vd)
+
+    def _mla_absorbed_gpu(self, h, layer, kv, step: StepBuffers, prefill: bool):
+        """The same on the GPU.  Every token's ``[k_rope | latent]`` row goes to the FP8 latent cache; decode steps run
+        the shared-row attention kernel over it (``ops/mla.py``) between two small per-head products (``W_k^T q`` in,
+        ``W_v o`` out); a prefill chunk attends to itself in the direct per-head form on the 256-wide prefill kernel
+        (keys and values expanded from the chunk's own latents, never stored)."""
+        from ..ops import mla as mla_ops
+        cfg, m = self.cfg, layer.mla
+        nope, rope, vd, hq, lat = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, self.hq, cfg.kv_lora_rank
+        if lat != mla_ops.LATENT or rope + lat != mla_ops.ROW_WIDTH:
+            raise NotImplementedError("the latent-cache kernels are built for a 512-wide latent and a 64-wide rotary part")
+        t = h.shape[0]
+        xq, xs = self._norm_quant(h, layer.attn_norm)
+        q = (m.q_b(*self._norm_quant(m.q_a(xq, xs), m.q_a_norm)) if m.q_a is not None else m.q_b(xq, xs)).view(t, hq, nope + rope)
+        ckv = m.kv_a(xq, xs)
+        c_n = ops.rmsnorm_quant(ckv[:, :lat].contiguous(), m.kv_a_norm, cfg.rms_eps, want_q=False, want_y=True)[2]
+        k_rope = ref.rope(ckv[:, None, lat:], step.positions, cfg.rope_theta, rope, self.rope_scaling)[:, 0]
+        q_rope = ref.rope(q[:, :, nope:], step.positions, cfg.rope_theta, rope, self.rope_scaling)
+        mla_ops.latent_write(torch.cat([k_rope, c_n], 1), step.slots, kv)
+        if prefill:
+            if step.past_len > 0:
+                raise NotImplementedError("a prefill chunk after cached tokens needs keys expanded from cached latents: "
+                                          "use one chunk per prompt with the latent cache")
+            kvb = m.kv_b(*self._quant(c_n)).view(t, hq, nope + vd)
+            qh = torch.zeros((t, hq, PADDED_HEAD), dtype=torch.bfloat16, device=h.device)
+            kh, vh = torch.zeros_like(qh), torch.zeros_like(qh)
+            qh[:, :, :rope], qh[:, :, rope : rope + nope] = q_rope, q[:, :, :nope]
+            kh[:, :, :rope], kh[:, :, rope : rope + nope] = k_rope[:, None, :], kvb[:, :, :nope]
+            vh[:, :, :vd] = kvb[:, :, nope:]
+            o = ops.attn_prefill(qh, kh, vh, step.cu_seqlens, self.sm_scale)
+            return o.view(t, hq, PADDED_HEAD)[:, :, :vd].reshape(t, hq * vd)
+        if step.q_len != 1:
+            raise NotImplementedError("verify windows over the latent cache are not built")
+        key = ("bf16", id(layer))
+        if key not in self._absorb:
+            wk, wv = self._absorbed_weights(layer)
+            self._absorb[key] = (wk.to(torch.bfloat16).contiguous(), wv.transpose(1, 2).to(torch.bfloat16).contiguous())
+        wk, wv_t = self._absorb[key]  # [Hq, nope, latent], [Hq, latent, v]
+        q_abs = torch.bmm(q[:, :, :nope].transpose(0, 1), wk).transpose(0, 1)  # [T, Hq, latent]
+        o_lat = mla_ops.decode(torch.cat([q_rope, q_abs], -1), kv, step.block_table, step.seq_lens, sm_scale=self.sm_scale,
+                               splits=getattr(self, "attn_splits", 1) or 1)
+        return torch.bmm(o_lat.transpose(0, 1), wv_t).transpose(0, 1).reshape(t, hq * vd)
 
     def _mla_heads(self, h, layer):
         """Per-head (query, key, value) in the padded 256-wide layout: ``[T, 3 * Hq, 256]`` bf16, rows q | k | v."""

@@ -103,6 +103,29 @@ def bench_attn(batch: int, ctx: int, hq: int, hk: int, d: int, splits: int, reps
     return {"kernel": "paged_attn_decode", "batch": batch, "ctx": ctx, "hq": hq, "hk": hk, "d": d, "splits": splits, "us": ms * 1e3, "gbs": byt / ms / 1e6}
 
 
+def bench_mla_decode(batch: int, ctx: int, heads: int, splits: int, reps: int) -> dict:
+    """Shared-row latent attention: 576-wide key rows and their 512-wide latent as values, one row per token."""
+    from . import mla as mla_ops
+    pages_per = math.ceil(ctx / 16)
+    layers = max(1, math.ceil(4 * L2_BYTES / (batch * ctx * 2 * 576)))
+    cache = PagedKVCache(layers=layers, kv_heads=1, head_dim=576, num_pages=batch * pages_per + 1, max_seqs=batch,
+                         max_pages_per_seq=pages_per, device="cuda")
+    cache.k.view(torch.int8).random_(-100, 100)
+    cache.v.view(torch.int8).random_(-100, 100)
+    cache.k_scale.fill_(0.01)
+    cache.v_scale.fill_(0.01)
+    for b in range(batch):
+        cache.assign(b, b, ctx)
+    q = torch.randn((batch, heads, 576), device="cuda").to(torch.bfloat16)
+    sl = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+    out = torch.empty((batch, heads, 512), dtype=torch.bfloat16, device="cuda")
+    kvs = [cache.layer(i) for i in range(layers)]
+    ms = time_ms(lambda i: mla_ops.decode(q, kvs[i % layers], cache.block_table, sl, sm_scale=0.07, splits=splits, out=out), reps)
+    byt = batch * ctx * (576 + 512 + 8) * math.ceil(heads / 16)  # every 16-head tile streams the rows once
+    return {"kernel": "mla_decode", "batch": batch, "ctx": ctx, "heads": heads, "splits": splits, "us": ms * 1e3,
+            "gbs": byt / ms / 1e6, "unique_gbs": batch * ctx * (576 + 512 + 8) / ms / 1e6}
+
+
 def bench_prefill(t: int, hq: int, hk: int, reps: int, d: int = 128) -> list[dict]:
     q = torch.randn((t, hq, d), device="cuda").to(torch.bfloat16)
     k = torch.randn((t, hk, d), device="cuda").to(torch.bfloat16)
@@ -143,7 +166,7 @@ def main() -> None:
     ap.add_argument("--json", default="")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--only", default="", help="comma separated kernel families: gemm,w4,attn,small,prefill")
+    ap.add_argument("--only", default="", help="comma separated kernel families: gemm,w4,attn,mla,small,prefill")
     ap.add_argument("--tp", type=int, default=1, help="time one rank's shard of a tensor-parallel group of this size")
     args = ap.parse_args()
     pk = peaks()
@@ -174,6 +197,9 @@ def main() -> None:
             rows.append(bench_attn(batch, ctx, 32 // tp, max(1, 8 // tp), 128, splits, args.reps))
         # 256-wide heads of the hybrid model: 16 query heads on 2 KV heads
         rows.append(bench_attn(batch, ctx, 16, 2, 256, K.attn_splits_for(batch, 2, ctx), args.reps))
+    for batch, ctx in ((1, 4096), (64, 4096)) if want("mla") else ():
+        for splits in ((1, 8, 16) if batch == 1 else (1, 2, 4)):
+            rows.append(bench_mla_decode(batch, ctx, max(16, 128 // tp), splits, args.reps))
     for m in (1, 64, 4096) if want("small") else ():
         rows += bench_small(m, 4096, 14336, args.reps)
     for t in (1024, 4096) if want("prefill") else ():

@@ -82,3 +82,85 @@ def test_mla_gpu_matches_cpu_and_graph_decode():
     parts = LLMEngine(MlaModel(cfg, gpu.model.w), max_batch=4, max_seq_len=128, prefill_chunk=16)
     assert torch.equal(parts.generate(prompts, 8).tokens[:, 0], toks[:, 0])
     check_status()
+
+
+def _latent_cfg(**kw):
+    import dataclasses
+    base = MlaConfig(vocab_size=1024, hidden_size=256, intermediate_size=512, num_layers=2, num_heads=4, num_kv_heads=4,
+                     head_dim=256, rope_theta=1e4, rms_eps=1e-6, num_experts=8, top_k=2, moe_intermediate=128,
+                     shared_intermediate=128, router="sigmoid", n_group=2, topk_group=1, routed_scale=2.5,
+                     first_dense_layers=2, q_lora_rank=128, kv_lora_rank=512, absorbed=True, name="latent-cache-test")
+    return dataclasses.replace(base, **kw) if kw else base
+
+
+def test_latent_cache_kernels_match_reference():
+    """The 576-wide shared-row decode attention and its cache writer against the fp32 restatement over the same pages
+    (16 and 20 heads: a full and a ragged head tile; one and several KV splits; ragged sequence lengths)."""
+    from mfq_b200.engine.kv_cache import PagedKVCache
+    from mfq_b200.ops import mla as mla_ops
+    from mfq_b200.ops import reference as ref
+    require_gpu_lib()
+    g = torch.Generator().manual_seed(0)
+    lens = [1, 16, 77, 300]
+    b, ps = len(lens), 16
+    for heads, splits in ((16, 1), (20, 3)):
+        cache = PagedKVCache(layers=1, kv_heads=1, head_dim=576, num_pages=128, max_seqs=b, max_pages_per_seq=24, device="cuda")
+        kv = cache.layer(0)
+        for r, n in enumerate(lens):
+            cache.assign(r, 900 + r, n)
+            rows = (torch.randn((n, 576), generator=g) * 0.7).to(torch.bfloat16).cuda()
+            mla_ops.latent_write(rows, cache.slots(900 + r, 0, n).cuda(), kv)
+        q = (torch.randn((b, heads, 576), generator=g) * 0.3).to(torch.bfloat16).cuda()
+        seq_lens = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        got = mla_ops.decode(q, kv, cache.block_table[:b], seq_lens, sm_scale=0.07, splits=splits).float().cpu()
+        check_status()
+        # reference: the dequantized pages as one KV head, values = latent part of the same row
+        want = ref.paged_attn_decode(q.cpu(), _cpu_layer(kv), cache.block_table[:b].cpu(), seq_lens.cpu(), 0.07, 1).float()[:, :, :512]
+        err = (got - want).abs().max() / want.abs().max()
+        assert float(err) < 2e-2, (heads, splits, float(err))
+
+
+def _cpu_layer(kv):
+    from mfq_b200.engine.kv_cache import LayerKV
+    return LayerKV(kv.k.cpu(), kv.v.cpu(), kv.k_scale.cpu(), kv.v_scale.cpu(), kv.page_size)
+
+
+def test_latent_cache_model_matches_cpu_and_decodes_under_graphs():
+    """The weight-absorbed model on the GPU (latent cache, shared-row decode kernel) against its CPU restatement."""
+    require_gpu_lib()
+    cfg = _latent_cfg()
+    w_cpu = random_mla_weights(cfg, "cpu", seed=5, std=0.05, expert_chunk=3)
+    gpu = LLMEngine(MlaModel(cfg, _to(w_cpu, "cuda")), max_batch=4, max_seq_len=160)
+    cpu = LLMEngine(MlaModel(cfg, w_cpu), max_batch=4, max_seq_len=160, device="cpu")
+    assert gpu.cache.bytes_per_token() < 2 * 1300 * cfg.num_layers  # ~1.2 KB per token and layer, whatever the head count
+    prompt = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(3))
+    lg, lc = _logits(gpu, prompt, "cuda"), _logits(cpu, prompt, "cpu")
+    check_status()
+    scale = float(lc.abs().max())
+    cos = float(torch.nn.functional.cosine_similarity(lg.flatten(), lc.flatten(), dim=0))
+    assert cos > 0.99 and float((lg - lc).abs().mean()) <= 0.03 * scale, (cos, float((lg - lc).abs().mean()), scale)
+    # teacher-forced decode steps: the same tokens through both, so the step logits can be compared number by number
+    def forced(eng, dev):
+        n = prompt.numel()
+        eng.cache.assign(0, 777, n + 6)
+        step = StepBuffers(input_ids=prompt.to(dev, torch.int32), positions=torch.arange(n, dtype=torch.int32, device=dev),
+                           slots=eng.cache.slots(777, 0, n).to(dev), cu_seqlens=[0, n])
+        eng.model.forward(step, eng.cache, prefill=True)
+        outs = []
+        for j, tok in enumerate((5, 900, 17, 333, 64)):
+            step = StepBuffers(input_ids=torch.tensor([tok], dtype=torch.int32, device=dev),
+                               positions=torch.tensor([n + j], dtype=torch.int32, device=dev),
+                               slots=eng.cache.slots(777, n + j, 1).to(dev), block_table=eng.cache.block_table[:1],
+                               seq_lens=torch.tensor([n + j + 1], dtype=torch.int32, device=dev))
+            outs.append(eng.model.forward(step, eng.cache, prefill=False).float().cpu())
+        eng.cache.release(777)
+        return torch.cat(outs, 0)
+    dg, dc = forced(gpu, "cuda"), forced(cpu, "cpu")
+    check_status()
+    dcos = float(torch.nn.functional.cosine_similarity(dg.flatten(), dc.flatten(), dim=0))
+    assert dcos > 0.99 and float((dg - dc).abs().mean()) <= 0.03 * float(dc.abs().max()), (dcos, float((dg - dc).abs().mean()))
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)) for n in (11, 23, 30)]
+    toks = gpu.generate(prompts, 8).tokens
+    check_status()
+    eager = LLMEngine(MlaModel(cfg, gpu.model.w), max_batch=4, max_seq_len=160, use_graphs=False)
+    assert torch.equal(eager.generate(prompts, 8).tokens, toks)
