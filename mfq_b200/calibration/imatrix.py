@@ -43,6 +43,7 @@ class ImatrixCollector:
         for name, s in self.sum_in.items():
             n = max(1, self.count[name])
             out[name + ".in"] = (s / n).cpu().numpy().astype(np.float32)
+            out[name + ".count"] = np.array(self.count[name], dtype=np.int64)  # rows seen: an expert's exposure
             if name in self.sum_out:
                 out[name + ".out"] = (self.sum_out[name] / n).cpu().numpy().astype(np.float32)
         return out

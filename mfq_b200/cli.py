@@ -195,6 +195,40 @@ def _cmd_calibrate(args) -> int:
         used = sum(sizes[k] * cands[c] for k, c in choice.items()) / max(1, sum(sizes.values()))
         print(json.dumps({"output": args.output, "tensors": len(stats), "bits_per_weight": round(used, 3)}))
         return 0
+    if args.calibrate_cmd in ("candidates", "allocate", "natscale"):
+        from .calibration import natscale
+        from .calibration.imatrix import load as load_imatrix
+        im = load_imatrix(args.imatrix) if args.imatrix else None
+        layers = None
+        if getattr(args, "layers", ""):
+            layers = set()
+            for part in args.layers.split(","):
+                lo, _, hi = part.partition("-")
+                layers.update(range(int(lo), int(hi or lo) + 1))
+        if getattr(args, "candidates_file", None):
+            cands = json.loads(Path(args.candidates_file).read_text())
+        else:
+            cands = natscale.expert_candidates(tensors, [f.strip().upper() for f in args.families.split(",") if f.strip()], imatrix=im,
+                                               layers=layers)
+        if args.calibrate_cmd == "candidates":
+            Path(args.output).write_text(json.dumps(cands))
+            print(json.dumps({"output": args.output, "banks": len(cands["tensors"]), "families": cands["families"]}))
+            return 0
+        if args.calibrate_cmd == "allocate" and args.method == "milp":
+            # the exact joint solver over the same candidates; every expert weighs the same without an importance file
+            from .calibration.ew_solver import solve
+            total = sum(ex["weights"] for t in cands["tensors"] for ex in t["experts"])
+            from .calibration.ew_solver import IMPORTANCE_FORMAT
+            scheme, report = solve({"format": IMPORTANCE_FORMAT, "mode": "score", "entries": []}, cands,
+                                   args.target_bpw * total)
+        else:
+            sens = args.sensitivity or ("imatrix-energy" if im is not None else "uniform")
+            scheme, report = natscale.allocate(cands, args.target_bpw, imatrix=im, tensors=tensors, tau=args.tau, sensitivity=sens)
+        Path(args.output).write_text(json.dumps(scheme, indent=1))
+        if args.report:
+            Path(args.report).write_text(json.dumps(report, indent=1))
+        print(json.dumps({"output": args.output, **{k: v for k, v in report.items() if not isinstance(v, (dict, list))}}))
+        return 0
     # imatrix: run the fp32 reference model with recording linears
     import torch
     from .calibration.imatrix import ImatrixCollector
@@ -644,6 +678,28 @@ def build_parser() -> argparse.ArgumentParser:
     ci.add_argument("--chunks", type=int, default=4)
     ci.add_argument("--ctx", type=int, default=128)
     ci.add_argument("--seed", type=int, default=0)
+    def _candidate_args(p, target=True):
+        p.add_argument("input")
+        p.add_argument("--families", default="NINT2,NINT3,NINT4,NINT5,NINT6,NINT8", help="NINT families scored per expert matrix")
+        p.add_argument("--imatrix", help="importance matrix with per-expert statistics (`mfq calibrate imatrix`)")
+        p.add_argument("--layers", default="", help="comma-separated layers or ranges (default: all)")
+        p.add_argument("--seed", type=int, default=0)
+        p.add_argument("--output", required=True)
+        if target:
+            p.add_argument("--candidates-file", help="reuse a table written by `mfq calibrate candidates`")
+            p.add_argument("--target-bpw", type=float, required=True, help="mean bits per routed-expert weight")
+            p.add_argument("--tau", type=float, default=1.0, help="NatScale contrast in nats")
+            p.add_argument("--sensitivity", choices=("uniform", "imatrix-energy"), default=None)
+            p.add_argument("--report")
+    cc = cs.add_parser("candidates", help="quantize every routed expert matrix under every family: error and size table")
+    _candidate_args(cc, target=False)
+    cl = cs.add_parser("allocate", help="score candidates and allocate a family per expert matrix under a budget")
+    _candidate_args(cl)
+    cl.add_argument("--method", choices=("natscale", "milp"), default="natscale")
+    cn = cs.add_parser("natscale", help="NatScale allocation (contrast-normalised sensitivities, convex-hull budget solver)")
+    _candidate_args(cn)
+    for p_ in (cc, cl, cn):
+        p_.set_defaults(fn=_cmd_calibrate)
     se = sub.add_parser("solve-ew", help="expert-wise joint budget solver (MILP) -> calibration scheme")
     se.add_argument("--importance", required=True)
     se.add_argument("--candidates", required=True)

@@ -147,6 +147,10 @@ class MoeLM:
             tok, slot = (idx == e).nonzero(as_tuple=True)
             xe = x[tok]
             he = torch.nn.functional.silu(xe @ gate[e].T) * (xe @ up[e].T)
+            if self.observer is not None:  # per-expert statistics: "<tensor>#<expert>", inputs only
+                self.observer(f"{p}mlp.experts.gate.weight#{e}", xe, None)
+                self.observer(f"{p}mlp.experts.up.weight#{e}", xe, None)
+                self.observer(f"{p}mlp.experts.down.weight#{e}", he, None)
             out.index_add_(0, tok, (he @ down[e].T) * wt[tok, slot][:, None])
         if cfg.shared_intermediate:
             hs = torch.nn.functional.silu(self._lin(p + "mlp.shared_expert.gate.weight", x)) * self._lin(p + "mlp.shared_expert.up.weight", x)
