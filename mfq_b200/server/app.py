@@ -23,7 +23,7 @@ import queue
 import time
 import uuid
 
-from fastapi import FastAPI, Request as HttpRequest
+from fastapi import FastAPI, Request as HttpRequest, WebSocket, WebSocketDisconnect
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from ..engine.scheduler import BackendFailure, QueueFull, SamplingParams
@@ -110,10 +110,12 @@ class _Stream:
                 return
 
 
-def create_app(service: ModelService, api_key=None, sessions=None, cluster=None, hardware=None, policies=None) -> FastAPI:
+def create_app(service: ModelService, api_key=None, sessions=None, cluster=None, hardware=None, policies=None,
+               catalog=None) -> FastAPI:
     """``api_key``: one key with every scope, or a :class:`~mfq_b200.server.auth.KeyStore`; ``sessions``: a :class:`~mfq_b200.server.sessions.SessionStore` (in-memory when omitted); ``cluster``: a
     :class:`~mfq_b200.server.cluster.ClusterBackend` whose peers serve models that are not loaded here; ``hardware``:
-    a :class:`~mfq_b200.server.hardware.HardwareMonitor`."""
+    a :class:`~mfq_b200.server.hardware.HardwareMonitor`; ``catalog``: a :class:`~mfq_b200.server.catalog.ModelCatalog`
+    of artifacts on disk (the ``/api/v1/catalog`` routes)."""
     from .hardware import HardwareMonitor
     from .sessions import SessionStore
     from contextlib import asynccontextmanager
@@ -476,6 +478,106 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
     async def unload_model(request: HttpRequest):
         body = await request.json()
         return {"unloaded": service.unload(body.get("model", ""))}
+
+    # ---- catalog of artifacts on disk ----------------------------------------------------------------------------
+    from .catalog import ArtifactNotFound, ModelCatalog
+    cat = catalog if catalog is not None else ModelCatalog()
+    app.state.catalog = cat
+
+    @app.get("/api/v1/catalog")
+    async def catalog_list():
+        return {"roots": cat.roots, "models": cat.listing()}
+
+    @app.post("/api/v1/catalog/scan")
+    async def catalog_scan(request: HttpRequest):
+        body = await request.json() if await request.body() else {}
+        for root in body.get("roots", []):
+            cat.add_root(root)
+        return await asyncio.get_running_loop().run_in_executor(None, cat.scan)
+
+    @app.put("/api/v1/catalog/{ident}/aliases/{name}")
+    async def catalog_alias(ident: str, name: str):
+        try:
+            cat.alias(name, ident)
+        except ArtifactNotFound:
+            return error_response(404, "model_not_found", f"no catalog entry {ident!r}")
+        return {"id": ident, "aliases": cat.resolve(ident).aliases}
+
+    @app.delete("/api/v1/catalog/{ident}")
+    async def catalog_remove(ident: str):
+        return {"removed": cat.remove(ident)}
+
+    # ---- realtime: one WebSocket, many generations ------------------------------------------------------------------
+
+    @app.websocket("/api/v1/realtime")
+    async def realtime(ws: WebSocket):
+        """Frames in: ``{"type": "generate", "id", "model", "messages", sampling fields...}``, ``{"type": "cancel", "id"}``,
+        ``{"type": "ping"}``.  Frames out: ``started``, ``delta`` (text pieces), ``done`` (finish reason + usage), ``error``,
+        ``pong``.  Several generations may run at once on one socket; closing the socket cancels them all."""
+        if keys.enforce:
+            supplied = ws.headers.get("x-api-key") or ws.query_params.get("api_key")
+            header = ws.headers.get("authorization", "")
+            if header.lower().startswith("bearer "):
+                supplied = header[7:].strip()
+            if keys.scopes_of(supplied) is None or not keys.allows(supplied, "inference"):
+                await ws.close(code=4401)
+                return
+        await ws.accept()
+        running: dict[str, tuple] = {}
+        send_lock = asyncio.Lock()
+
+        async def send(frame: dict) -> None:
+            async with send_lock:
+                await ws.send_text(json.dumps(frame))
+
+        async def pump(rid: str, stream, lm, ids) -> None:
+            try:
+                async for piece in stream.pieces():
+                    await send({"type": "delta", "id": rid, "text": piece})
+                if stream.error_code:
+                    await send({"type": "error", "id": rid, "code": stream.error_code})
+                else:
+                    await send({"type": "done", "id": rid, "finish_reason": stream.finish or "stop", "text": stream.text,
+                                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(stream.ids)}})
+            finally:
+                running.pop(rid, None)
+
+        try:
+            while True:
+                try:
+                    frame = json.loads(await ws.receive_text())
+                except json.JSONDecodeError:
+                    await send({"type": "error", "code": "invalid_request", "message": "frames are JSON objects"})
+                    continue
+                kind, rid = frame.get("type"), str(frame.get("id", ""))
+                if kind == "ping":
+                    await send({"type": "pong"})
+                elif kind == "cancel":
+                    entry = running.get(rid)
+                    if entry is not None:
+                        service.cancel(entry[1], entry[2].id)
+                    await send({"type": "cancelling" if entry else "error", "id": rid, **({} if entry else {"code": "unknown_id"})})
+                elif kind == "generate":
+                    if not rid or rid in running:
+                        await send({"type": "error", "id": rid, "code": "invalid_request", "message": "id missing or in use"})
+                        continue
+                    stop = frame.get("stop") or []
+                    started, err = await _start(frame, frame.get("messages") or [], [stop] if isinstance(stop, str) else list(stop))
+                    if err is not None:
+                        payload = json.loads(err.body)
+                        await send({"type": "error", "id": rid, **payload.get("error", {})})
+                        continue
+                    stream, lm, ids = started
+                    running[rid] = (asyncio.create_task(pump(rid, stream, lm, ids)), lm, stream.req)
+                    await send({"type": "started", "id": rid, "model": lm.name, "prompt_tokens": len(ids)})
+                else:
+                    await send({"type": "error", "id": rid, "code": "invalid_request", "message": f"unknown frame type {kind!r}"})
+        except WebSocketDisconnect:
+            pass
+        finally:
+            for task, lm, req in list(running.values()):
+                service.cancel(lm, req.id)
+                task.cancel()
 
     # ---- sessions (chat history kept by the server for its clients) ----------------------------------------------
     @app.get("/api/v1/sessions")

@@ -1,0 +1,145 @@
+"""Model catalog (discovery, aliases, persistence, routes), pool memory budgets, and the realtime WebSocket."""
+
+import json
+
+import numpy as np
+import pytest
+from fastapi.testclient import TestClient
+
+from mfq_b200.server import ModelService, create_app
+from mfq_b200.server.catalog import ArtifactNotFound, ModelCatalog
+from mfq_b200.server.pool import RuntimePool
+from mfq_b200.server.tokenizer import ByteTokenizer
+from test_server import EchoBackend
+
+
+def _artifacts(root):
+    from mfq_b200.cli import main
+    (root / "packed").mkdir()
+    assert main(["quantize", "synthetic:tiny-moe", str(root / "packed" / "tiny.mfq"), "--random-expert-mix", "NINT4,MXFP4"]) == 0
+    hf = root / "hf-model"
+    hf.mkdir()
+    (hf / "config.json").write_text(json.dumps({"model_type": "llama"}))
+    (hf / "model.safetensors").write_bytes(b"\0" * 64)
+    (root / "other.gguf").write_bytes(b"GGUF" + b"\0" * 60)
+
+
+def test_catalog_discovers_persists_and_resolves(tmp_path):
+    _artifacts(tmp_path)
+    state = tmp_path / "catalog.json"
+    cat = ModelCatalog(state, roots=[tmp_path])
+    rep = cat.scan()
+    assert rep["entries"] == 3 and set(rep["added"]) == {"tiny", "hf-model", "other"}
+    tiny = cat.resolve("tiny")
+    assert tiny.kind == "mfq" and tiny.bytes > 0 and "MFE" in tiny.quantization["tensor_dtypes"]
+    cat.alias("prod", "tiny")
+    assert cat.resolve("prod").id == "tiny"
+    with pytest.raises(ArtifactNotFound):
+        cat.resolve("missing")
+    again = ModelCatalog(state)  # restart: entries, roots and aliases come back
+    assert again.resolve("prod").path == tiny.path and again.roots == cat.roots
+    (tmp_path / "other.gguf").unlink()
+    rep = again.scan()
+    assert rep["removed"] == ["other"] and again.resolve("prod").id == "tiny"  # aliases survive a rescan
+
+
+def test_catalog_routes(tmp_path):
+    _artifacts(tmp_path)
+    service = ModelService()
+    service.add_model("echo", EchoBackend(max_batch=2), ByteTokenizer())
+    with TestClient(create_app(service, catalog=ModelCatalog(tmp_path / "c.json"))) as c:
+        assert c.get("/api/v1/catalog").json()["models"] == []
+        rep = c.post("/api/v1/catalog/scan", json={"roots": [str(tmp_path)]}).json()
+        assert rep["entries"] == 3
+        assert c.put("/api/v1/catalog/tiny/aliases/prod").json()["aliases"] == ["prod"]
+        assert c.put("/api/v1/catalog/nope/aliases/x").status_code == 404
+        ids = [m["id"] for m in c.get("/api/v1/catalog").json()["models"]]
+        assert ids == ["hf-model", "other", "tiny"]
+        assert c.delete("/api/v1/catalog/other").json()["removed"] is True
+    service.shutdown()
+
+
+class _Runtime:
+    def __init__(self, name):
+        self.name, self.kv = name, None
+
+    def set_kv_budget(self, b):
+        self.kv = b
+
+
+def test_pool_memory_budget_evicts_rebalances_and_remembers_failures():
+    now = [0.0]
+    sizes = {"a": 40, "b": 30, "c": 50, "huge": 500, "broken": 0}
+    loads = []
+
+    def loader(name):
+        loads.append(name)
+        if name == "broken":
+            raise OSError("cannot open")
+        return _Runtime(name)
+    pool = RuntimePool(loader, max_instances=4, max_memory_bytes=100, sizer=lambda n: sizes.get(n, 10), min_kv_bytes=5,
+                       clock=lambda: now[0], load_failure_cooldown=30.0)
+    a = pool.get("a")
+    assert a.kv_budget_bytes == 60 and a.runtime.kv == 60  # everything the weights leave
+    now[0] = 1.0
+    b = pool.get("b")
+    assert pool.rebalance() == {"a": 15, "b": 15} and a.runtime.kv == 15
+    pool.configure("a", kv_share=2.0)
+    assert pool.rebalance() == {"a": 20, "b": 10}
+    now[0] = 2.0
+    pool.get("c")  # 40 + 30 + 50 > 100: the least recently used idle model goes
+    assert set(pool.instances) == {"b", "c"} and pool.evictions == 1
+    with pytest.raises(MemoryError):
+        pool.get("huge")
+    with pytest.raises(OSError):
+        pool.get("broken")
+    with pytest.raises(OSError):
+        pool.get("broken")  # inside the cool-down: the loader is not called again
+    assert loads.count("broken") == 1
+    now[0] = 40.0
+    with pytest.raises(OSError):
+        pool.get("broken")
+    assert loads.count("broken") == 2
+    pool.configure("b", idle_ttl=5.0)  # per-model idle time-out
+    assert pool.reap() == ["b"]
+    snap = pool.snapshot()
+    assert snap["weight_bytes"] == 50 and snap["instances"][0]["kv_budget_bytes"] == 50
+
+
+def test_realtime_socket_generates_pings_and_reports_errors():
+    service = ModelService(max_queue=4, queue_timeout=5.0)
+    service.add_model("echo", EchoBackend(max_batch=2), ByteTokenizer())
+    with TestClient(create_app(service)) as c:
+        with c.websocket_connect("/api/v1/realtime") as ws:
+            ws.send_text(json.dumps({"type": "ping"}))
+            assert json.loads(ws.receive_text()) == {"type": "pong"}
+            ws.send_text(json.dumps({"type": "generate", "id": "g1", "model": "echo", "messages": [{"role": "user", "content": "hi"}],
+                                     "max_tokens": 8}))
+            frames = []
+            while not frames or frames[-1]["type"] not in ("done", "error"):
+                frames.append(json.loads(ws.receive_text()))
+            assert frames[0]["type"] == "started" and frames[0]["model"] == "echo"
+            assert "".join(f["text"] for f in frames if f["type"] == "delta") == "ok!"
+            assert frames[-1]["type"] == "done" and frames[-1]["text"] == "ok!" and frames[-1]["usage"]["completion_tokens"] == 3
+            ws.send_text(json.dumps({"type": "generate", "id": "g2", "model": "nope", "messages": [{"role": "user", "content": "x"}]}))
+            err = json.loads(ws.receive_text())
+            assert err["type"] == "error" and err["id"] == "g2" and err["code"] == "model_not_found"
+            ws.send_text("not json")
+            assert json.loads(ws.receive_text())["code"] == "invalid_request"
+            ws.send_text(json.dumps({"type": "cancel", "id": "unknown"}))
+            assert json.loads(ws.receive_text())["code"] == "unknown_id"
+    service.shutdown()
+
+
+def test_realtime_socket_needs_an_inference_key():
+    from starlette.websockets import WebSocketDisconnect
+    service = ModelService()
+    service.add_model("echo", EchoBackend(max_batch=2), ByteTokenizer())
+    with TestClient(create_app(service, api_key="secret")) as c:
+        with pytest.raises(WebSocketDisconnect):
+            with c.websocket_connect("/api/v1/realtime") as ws:
+                ws.receive_text()
+        with c.websocket_connect("/api/v1/realtime", headers={"authorization": "Bearer secret"}) as ws:
+            ws.send_text(json.dumps({"type": "ping"}))
+            assert json.loads(ws.receive_text())["type"] == "pong"
+    service.shutdown()
