@@ -162,7 +162,7 @@ def save_checkpoint(path, config: dict, tensors: dict[str, object], assets: dict
 def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots: int | None = None, max_batch: int = 64,
                 max_seq_len: int = 8192, tp_rank: int = 0, tp_size: int = 1,
                 collective=None, use_graphs: bool = True, kv_budget_bytes: int | None = None,
-                yarn_context_extension: float | None = None, mtp_draft_tokens: int = 0, mtp_adaptive: bool = False,
+                yarn_context_extension: float | None = None, mtp_draft_tokens: int = 0, mtp_adaptive: bool = False, mtp_dynamic_depth: bool = False,
                 lp_rank: int = 0, lp_size: int = 1, layer_split=None):
     """``.mfq`` -> (engine, tokenizer, config).  ``kv_budget_bytes`` caps the paged KV pool (see ``engine/kv_budget.py``);
     on a GPU it defaults to 90 % of the memory that is free once the weights are resident.  ``yarn_context_extension``
@@ -214,7 +214,7 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
     engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, num_pages=num_pages,
                        use_graphs=use_graphs and expert_slots is None,
                        mtp_draft_tokens=mtp_draft_tokens if getattr(weights, "mtp", None) is not None else 0,
-                       mtp_adaptive=mtp_adaptive and tp_size == 1)  # ranks time their steps separately: they would
+                       mtp_adaptive=mtp_adaptive and tp_size == 1, mtp_dynamic_depth=mtp_dynamic_depth and tp_size == 1)  # ranks time their steps separately: they would
     #                                                                    park at different moments and fall out of lockstep
     tokenizer = tokenizer_from_assets(assets, cfg.vocab_size)
     # structured output needs the vocabulary's byte strings; resolved on the first request that asks for it

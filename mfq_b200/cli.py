@@ -436,7 +436,8 @@ def _cmd_serve(args) -> int:
                                         native_4bit=args.native_4bit, expert_slots=slots,
                                         kv_budget_bytes=int(kv_gb * (1 << 30)) if kv_gb else None,
                                         yarn_context_extension=args.yarn_context_extension,
-                                        mtp_draft_tokens=args.mtp_draft_tokens, mtp_adaptive=args.mtp_adaptive)
+                                        mtp_draft_tokens=args.mtp_draft_tokens, mtp_adaptive=args.mtp_adaptive,
+                                        mtp_dynamic_depth=args.mtp_dynamic_depth)
         if args.prefill_chunk_size not in (None, "auto"):
             engine.prefill_chunk = max(16, int(args.prefill_chunk_size))
         if ctx is not None:
@@ -773,6 +774,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
     s.add_argument("--mtp-draft-tokens", type=int, default=0,
                    help="draft this many tokens per cycle with the checkpoint's multi-token-prediction head (0: off)")
+    s.add_argument("--mtp-dynamic-depth", action="store_true",
+                   help="choose the number of drafts (1 .. --mtp-draft-tokens) per cycle from measured tokens per millisecond")
     s.add_argument("--mtp-adaptive", action="store_true",
                    help="measure cycles against plain decoding and park them while they lose (the head stays primed)")
     s.add_argument("--runtime-startup-timeout", type=float, default=600.0, help="seconds a worker process may take to announce itself")

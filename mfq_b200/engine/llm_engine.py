@@ -49,9 +49,11 @@ class GenerationResult:
 class LLMEngine:
     def __init__(self, model: LlamaModel, *, max_batch: int = 64, max_seq_len: int = 8192, num_pages: int | None = None,
                  device=None, use_graphs: bool | None = None, mtp_draft_tokens: int = 0, prefill_chunk: int | None = None,
-                 prefix_cache=None, prefix_salt: str = "", mtp_adaptive: bool = False) -> None:
+                 prefix_cache=None, prefix_salt: str = "", mtp_adaptive: bool = False, mtp_dynamic_depth: bool = False) -> None:
         """``mtp_draft_tokens`` (K, 0 = off): with a model that carries an MTP head, greedy rows decode by
-        draft/verify cycles that confirm between 1 and K+1 tokens each (:meth:`mtp_step`)."""
+        draft/verify cycles that confirm between 1 and K+1 tokens each (:meth:`mtp_step`).  ``mtp_dynamic_depth``: every
+        cycle runs at the depth (1 .. K drafts) whose measured tokens per millisecond is best
+        (:class:`~mfq_b200.engine.mtp_policy.CycleDepthController`); one graph per (bucket, depth, next depth)."""
         self.model = model
         # adaptive speculation: cycles only while they beat plain decoding (see engine/mtp_policy.ParkingController)
         self.mtp_controller = None
@@ -69,6 +71,11 @@ class LLMEngine:
         cfg = model.cfg
         has_head = getattr(model.w, "mtp", None) is not None
         self.mtp_k = mtp_draft_tokens if has_head else 0
+        self.mtp_depth = self.mtp_k  # drafts the next cycle verifies (columns 0 .. depth-1 of `draft` are primed)
+        self.depth_controller = None
+        if mtp_dynamic_depth and self.mtp_k > 1:
+            from .mtp_policy import CycleDepthController
+            self.depth_controller = CycleDepthController(self.mtp_k)
         self.device = torch.device(device) if device is not None else model.w.embed.device
         self.max_batch = max_batch
         self.max_seq_len = max_seq_len
@@ -117,8 +124,12 @@ class LLMEngine:
             self.c_tok, self.c_ids, self.c_pos, self.c_lens = i32(max_batch), i32(max_batch), i32(max_batch), i32(max_batch)
             self.c_slots = i32(max_batch, fill=-1)
             self.mtp_counters = torch.zeros(2, dtype=torch.int64, device=dev)  # drafted, accepted
-            self.mtp_graphs: dict[int, torch.cuda.CUDAGraph] = {}
+            self.mtp_graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
             self.mtp_cycles = 0
+            # cycles at a depth d < K work on contiguous [batch, d] / [batch, d + 1] copies (the kernels index by depth)
+            self.draft_d = {d: (self.draft if d == k else i32(max_batch, d)) for d in range(1, k + 1)}
+            self.out_tokens_d = {d: (self.out_tokens if d == k else i32(max_batch, d + 1, fill=-1)) for d in range(1, k + 1)}
+            self.last_depth = k
 
     # -- token constraints -------------------------------------------------------------------------------------------
     def set_token_bytes(self, token_bytes, stop_ids=()) -> None:
@@ -510,15 +521,16 @@ class LLMEngine:
         g.replay()
 
     # -- MTP draft / verify ---------------------------------------------------------------------------------------
-    def _mtp_chain(self, r0: int, r1: int, hid: torch.Tensor, masked: bool = True) -> None:
-        """Drafts 2..K of rows ``[r0, r1)``: the head runs on its own previous output and draft, one position at a
-        time past the confirmed sequence (those KV rows are provisional and get rewritten by the next cycle)."""
-        if self.mtp_k < 2:
+    def _mtp_chain(self, r0: int, r1: int, hid: torch.Tensor, masked: bool = True, depth: int | None = None) -> None:
+        """Drafts 2..``depth`` (default K) of rows ``[r0, r1)``: the head runs on its own previous output and draft, one
+        position at a time past the confirmed sequence (those KV rows are provisional and get rewritten by the next cycle)."""
+        depth = self.mtp_k if depth is None else depth
+        if depth < 2:
             return
         table = self.cache.block_table[r0:r1]
         tok, ids, pos, lens, slots = (t[r0:r1] for t in (self.c_tok, self.c_ids, self.c_pos, self.c_lens, self.c_slots))
         lens.copy_(self.seq_lens[r0:r1])
-        for j in range(2, self.mtp_k + 1):
+        for j in range(2, depth + 1):
             tok.copy_(self.draft[r0:r1, j - 2])
             self._advance(tok, ids, pos, lens, slots, table, self.active[r0:r1] if masked else None)
             step = StepBuffers(input_ids=ids, positions=pos, slots=slots, block_table=table, seq_lens=lens)
@@ -526,12 +538,18 @@ class LLMEngine:
             self.model.sample_greedy(logits, out=tok)
             self.draft[r0:r1, j - 1].copy_(tok)
 
-    def _mtp_body(self, b: int) -> None:
+    def _mtp_body(self, b: int, depth: int | None = None, next_depth: int | None = None) -> None:
+        """One cycle verifying ``depth`` drafts (default K) and leaving ``next_depth`` drafts for the following one."""
         from ..ops import mtp as mtp_ops
-        k, w = self.mtp_k, self.mtp_k + 1
+        k = self.mtp_k if depth is None else depth
+        next_depth = k if next_depth is None else next_depth
+        w = k + 1
+        draft, out_tokens = self.draft_d[k], self.out_tokens_d[k]
+        if draft is not self.draft:
+            draft[:b].copy_(self.draft[:b, :k])
         table = self.cache.block_table[:b]
         ids, pos, slots, lens = self.v_ids[: b * w], self.v_pos[: b * w], self.v_slots[: b * w], self.v_lens[:b]
-        mtp_ops.prepare(self.sampled[:b], self.draft[:b], self.seq_lens[:b], table, self.active[:b], ids, pos, slots, lens,
+        mtp_ops.prepare(self.sampled[:b], draft[:b], self.seq_lens[:b], table, self.active[:b], ids, pos, slots, lens,
                         self.cache.page_size)
         if self.device.type == "cuda":
             self.model.attn_splits = self._splits_now(b)
@@ -548,22 +566,28 @@ class LLMEngine:
         mstep = StepBuffers(input_ids=targets, positions=pos, slots=slots, block_table=table, seq_lens=lens, q_len=w)
         mlogits, mhid = self.model.mtp_forward(mstep, self.cache, hidden, prefill=False)
         head_next = self.model.sample_greedy(mlogits, out=self.head_next[: b * w])
-        mtp_ops.accept(targets, head_next, self.active[:b], self.draft[:b], self.sampled[:b], self.seq_lens[:b],
-                       self.out_tokens[:b], self.n_out[:b], self.accept_row[:b], self.mtp_counters)
+        mtp_ops.accept(targets, head_next, self.active[:b], draft[:b], self.sampled[:b], self.seq_lens[:b],
+                       out_tokens[:b], self.n_out[:b], self.accept_row[:b], self.mtp_counters)
+        if draft is not self.draft:
+            self.draft[:b, 0].copy_(draft[:b, 0])  # the first draft of the next cycle
         if self.rec_state is not None:  # recurrent layers keep the state after the last accepted window position
             self.model.commit_verify(b, w, state_slots, self.accept_row[:b])
-        if k > 1:
-            self._mtp_chain(0, b, mtp_ops.select_rows(mhid, self.accept_row[:b], w))
+        if next_depth > 1:
+            self._mtp_chain(0, b, mtp_ops.select_rows(mhid, self.accept_row[:b], w), depth=next_depth)
 
     def mtp_step(self, b: int) -> None:
         """One draft/verify cycle for the active rows among ``[0, b)``: confirms ``n_out[r]`` in 1..K+1 tokens per
         row (``out_tokens[r, :n_out[r]]``), all state stays on the device (one CUDA graph per batch bucket)."""
         self.mtp_cycles += 1
         self._bind_state()
+        depth = self.mtp_depth
+        nxt = self.depth_controller.next_depth() if self.depth_controller is not None else depth
+        self.last_depth, self.mtp_depth = depth, nxt
         if not self.use_graphs:
-            self._mtp_body(b)
+            self._mtp_body(b, depth, nxt)
             return
-        g = self.mtp_graphs.get(b)
+        key = (b, depth, nxt)
+        g = self.mtp_graphs.get(key)
         if g is None:
             ops.Workspace.get(self.device)
             side = torch.cuda.Stream(device=self.device)
@@ -572,20 +596,24 @@ class LLMEngine:
             saved_rec = (self.rec_state.conv.clone(), self.rec_state.state.clone()) if self.rec_state is not None else None
             with torch.cuda.stream(side):
                 for _ in range(2):
-                    self._mtp_body(b)
+                    self._mtp_body(b, depth, nxt)
             torch.cuda.current_stream().wait_stream(side)
             g = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             with torch.cuda.graph(g):
-                self._mtp_body(b)
-            self.launches_per_step[("mtp", b)] = ops.launch_count() - before
+                self._mtp_body(b, depth, nxt)
+            self.launches_per_step[("mtp", b) if depth == nxt == self.mtp_k else ("mtp", b, depth, nxt)] = ops.launch_count() - before
             for dst, src in zip((self.seq_lens, self.sampled, self.draft, self.mtp_counters), saved):
                 dst.copy_(src)
             if saved_rec is not None:
                 self.rec_state.conv.copy_(saved_rec[0])
                 self.rec_state.state.copy_(saved_rec[1])
-            self.mtp_graphs[b] = g
+            self.mtp_graphs[key] = g
         g.replay()
+
+    def mtp_result(self, b: int):
+        """``(out_tokens [b, depth + 1], n_out [b])`` of the cycle :meth:`mtp_step` just ran (device tensors)."""
+        return self.out_tokens_d[self.last_depth][:b], self.n_out[:b]
 
     def mtp_stats(self) -> dict:
         """Draft acceptance so far (the reference reports the same through its ``mtp_stats`` frame)."""
@@ -644,14 +672,18 @@ class LLMEngine:
                 ctl.observe("plain", len(rows), len(rows), (time.perf_counter() - t0) * 1e3)
                 return {r: [int(toks[r])] for r in rows}
             self.mtp_step(b)
-            toks, counts = self.out_tokens[:b].cpu(), self.n_out[:b].cpu()
+            toks, counts = (t.cpu() for t in self.mtp_result(b))
             out = {}
             for r in rows:
                 n = int(counts[r])
                 self.row_len[r] += n
                 out[r] = [int(t) for t in toks[r, :n]]
+            ms = (time.perf_counter() - t0) * 1e3
             if ctl is not None:
-                ctl.observe("mtp", sum(len(v) for v in out.values()), len(rows), (time.perf_counter() - t0) * 1e3)
+                ctl.observe("mtp", sum(len(v) for v in out.values()), len(rows), ms)
+            if self.depth_controller is not None:  # acceptance of the typical row, cost of the whole cycle
+                accepted = sorted(len(v) - 1 for v in out.values())[len(out) // 2]
+                self.depth_controller.observe(self.last_depth, accepted, ms)
             return out
         self.decode_step(b, any(self.row_stochastic.get(r, False) for r in rows), constrained)
         toks = self.sampled[:b].cpu()
@@ -694,7 +726,7 @@ class LLMEngine:
             host = out.cpu()
             while min(got) < max_new_tokens:
                 self.mtp_step(b)
-                toks, counts = self.out_tokens[:b].cpu(), self.n_out[:b].cpu()
+                toks, counts = (t.cpu() for t in self.mtp_result(b))
                 for r in range(b):
                     n = min(int(counts[r]), max_new_tokens - got[r])
                     host[r, got[r] : got[r] + n] = toks[r, :n]

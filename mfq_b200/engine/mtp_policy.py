@@ -109,6 +109,20 @@ class DepthController:
                 "expected_tokens": [round(self.expected_tokens(d), 3) for d in range(self.max_depth + 1)]}
 
 
+class CycleDepthController(DepthController):
+    """Depth choice among draft/verify cycles only (depths 1 .. max): what the engine uses when parking is off or is
+    decided elsewhere (:class:`ParkingController`).  Plain decoding (depth 0) is never probed or chosen."""
+
+    def next_depth(self) -> int:
+        for d in range(self.max_depth, 0, -1):  # measure every depth once, widest first
+            if self.cycle_ms[d] is None:
+                return d
+        stale = max(range(1, self.max_depth + 1), key=lambda d: self.age[d])
+        if self.age[stale] >= self.reprobe_every:
+            return stale
+        return max(range(1, self.max_depth + 1), key=lambda d: self.score(d) or 0.0)
+
+
 class ParkingController:
     """Run draft/verify cycles only while they pay: the engine-side reduction of :class:`DepthController` to the two
     modes one captured graph geometry offers -- cycles at the depth the engine was built with, or plain decode steps

@@ -9,10 +9,10 @@ from mfq_b200.models.llama import LlamaConfig, LlamaModel, LlamaWeights
 from mfq_b200.ops import mtp as mtp_ops
 
 
-def _engine(k, max_batch=2, mtp=True):
+def _engine(k, max_batch=2, mtp=True, **kw):
     cfg = LlamaConfig.tiny()
     w = LlamaWeights.random_init(cfg, "cpu", seed=5, std=0.05, mtp=mtp)
-    return cfg, LLMEngine(LlamaModel(cfg, w), max_batch=max_batch, max_seq_len=96, device="cpu", mtp_draft_tokens=k)
+    return cfg, LLMEngine(LlamaModel(cfg, w), max_batch=max_batch, max_seq_len=96, device="cpu", mtp_draft_tokens=k, **kw)
 
 
 def _agree(a, b):
@@ -146,3 +146,29 @@ def test_adaptive_engine_is_lossless_and_parks_when_cycles_lose():
     assert first_park <= 8 and seen[first_park : first_park + 4] == ["plain"] * 4  # parked, then a re-probe
     assert "mtp" in seen[first_park + 4 : first_park + 7]
     assert not c.parked and seen[-3:] == ["mtp"] * 3  # 2 tokens/ms beats 1 token/ms: resumed
+
+
+def test_dynamic_depth_is_lossless_and_visits_every_depth():
+    """Per-cycle depth choice: cycles at 3, 2 and 1 drafts interleave (the controller measures each depth first) and the
+    confirmed tokens stay those of plain greedy decoding."""
+    cfg, eng = _engine(3, mtp_dynamic_depth=True)
+    assert eng.depth_controller is not None
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)) for n in (9, 14)]
+    plain = eng.generate(prompts, 14).tokens
+    for r in range(2):
+        eng.release(r)
+    for r, p in enumerate(prompts):
+        eng.prefill(r, p)
+        eng.grow(r, int(p.numel()) + 40)
+    got = {0: [int(eng.sampled[0])], 1: [int(eng.sampled[1])]}
+    depths = []
+    while min(len(v) for v in got.values()) < 14:
+        out = eng.decode([0, 1])
+        depths.append(eng.last_depth)
+        for r, toks in out.items():
+            assert 1 <= len(toks) <= eng.last_depth + 1
+            got[r] += toks
+    assert set(depths[:6]) == {1, 2, 3}  # every depth gets measured (the next depth is chosen before a cycle is timed)
+    assert min(_agree(plain[r].tolist(), got[r][:14]) for r in range(2)) >= 0.75
+    st = eng.depth_controller.state()
+    assert all(ms is not None for ms in st["cycle_ms"][1:])
