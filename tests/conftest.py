@@ -26,3 +26,14 @@ def reference_pkg():
     except Exception as exc:  # pragma: no cover
         pytest.skip(f"reference package not importable: {exc}")
     return ref
+
+
+@pytest.fixture(autouse=True)
+def _seeded(request):
+    """Every test starts from the same generator state (CPU and, when present, CUDA): tests that draw their data from the
+    global generators see the same data in every run, so a tolerance that holds once holds always."""
+    import zlib
+
+    import torch
+    torch.manual_seed(zlib.crc32(request.node.nodeid.encode()) & 0x7FFFFFFF)
+    yield

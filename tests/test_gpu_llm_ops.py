@@ -35,17 +35,20 @@ def test_rmsnorm_quant(m, h):
 
 def test_quant_rows_and_swiglu():
     require_gpu_lib()
-    x = torch.randn((9, 1024), device="cuda").to(torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn((9, 1024), device="cuda", generator=g).to(torch.bfloat16)
     q, s = ops.quant_rows(x)
     q2, s2 = ref.quant_rows(x)
     assert_close(s, s2, rel=1e-5, what="row scale")
     assert (q.float() - q2.float()).abs().max() <= 32, "codes may differ by at most one step"
-    assert_close(deq(q, s), x, rel=0.07)
-    gu = torch.randn((9, 2 * 1536), device="cuda").to(torch.bfloat16)
+    assert_close(deq(q, s), x, rel=0.07)  # E4M3 keeps three mantissa bits: at most 6.25 % off per element
+    gu = torch.randn((9, 2 * 1536), device="cuda", generator=g).to(torch.bfloat16)
     q, s = ops.silu_mul_quant(gu)
     q2, s2 = ref.silu_mul_quant(gu)
     assert_close(s, s2, rel=1e-2)
-    assert_close(deq(q, s), deq(q2, s2), rel=0.07)
+    # the kernel rounds silu(g) * u once, the restatement goes through bf16 first: a product that lands on a rounding
+    # boundary takes the neighbouring code (one step = 12.5 %), so a small share of the elements may differ by a step
+    assert_close(deq(q, s), deq(q2, s2), rel=0.07, outliers=3e-2)
 
 
 def make_cache(hk, d, batch, max_len):
