@@ -60,7 +60,7 @@ def read_hf_directory(path) -> tuple[dict, dict[str, np.ndarray], dict[str, byte
 def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", expert_mix: str = "", seed: int = 20260908,
                      device: str = "cpu", progress=None, widths: dict[str, int | None] | None = None,
                      imatrix: dict[str, np.ndarray] | None = None, scheme: dict | None = None, resume=None,
-                     fp8_sq_bits: float = 0.0) -> dict[str, object]:
+                     fp8_sq_bits: float = 0.0, row_widths: dict | None = None) -> dict[str, object]:
     """Apply the quantization plan: routed experts by the seeded mix (or the dense rule), 2-D weights by ``dense``
     (nint2..8 / nvq3 / mxfp4 / fp8 / bf16), norms / router / embeddings-as-requested stay bf16.
     ``widths`` (a preset plan: tensor -> NINT width, None = keep) overrides ``dense`` per tensor; ``imatrix`` supplies
@@ -68,10 +68,11 @@ def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", ex
     family of every routed expert projection.  ``resume`` (a :class:`~mfq_b200.quantize.resume.ResumeStore`) parks
     every finished tensor and hands back the ones a previous, interrupted run finished for the same source and plan.
     ``fp8_sq_bits`` (1..8, 0 = off): dense FP8 tensors are re-encoded with per-row scalar palettes averaging that many
-    code bits per weight (``quantize/fp8_sq.py``; the imatrix, if given, weights the palette fit)."""
+    code bits per weight (``quantize/fp8_sq.py``; the imatrix, if given, weights the palette fit).  ``row_widths``
+    (``mfq.inint-rows.v1`` from ``mfq calibrate inint``): the listed tensors become NINT with a code width per output row."""
     if resume is not None:
-        if fp8_sq_bits:
-            raise ValueError("--fp8-sq-bits cannot be combined with a resumable run yet")
+        if fp8_sq_bits or row_widths is not None:
+            raise ValueError("--fp8-sq-bits / --row-widths cannot be combined with a resumable run yet")
         return _quantize_resumable(tensors, resume, dense=dense, expert_mix=expert_mix, seed=seed, device=device,
                                    progress=progress, widths=widths, imatrix=imatrix, scheme=scheme)
     from .quantize import balanced_expert_mix, parse_profiles, quantize_expertwise, quantize_matrix
@@ -104,6 +105,13 @@ def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", ex
             out[name] = quantize_expertwise(a, assign, tuple(use), device=device)
         elif keep or profile is None or (profile.family in ("FP8", "MXFP4") and a.shape[-1] % 128):
             out[name] = F.to_bf16(a)
+        elif row_widths is not None and name in row_widths.get("tensors", {}):
+            from .calibration.imatrix import input_importance
+            from .calibration.inint import row_bits
+            from .quantize.nint import quantize_nint
+            spec = parse_profiles(f"NINT{int(row_widths['low'])}")[0].nint
+            imp = input_importance(imatrix, name) if imatrix is not None else None
+            out[name] = quantize_nint(a, spec, row_q_bits=row_bits(row_widths, name), importance=imp, device=device)
         else:
             imp = None
             if imatrix is not None and profile.nint is not None:

@@ -111,6 +111,7 @@ def _cmd_quantize(args) -> int:
         imatrix = load_imatrix(args.imatrix)
     if args.ew_scheme:
         scheme = json.loads(Path(args.ew_scheme).read_text())
+    row_widths = json.loads(Path(args.row_widths).read_text()) if getattr(args, "row_widths", None) else None
     def _label(n, t):
         if ".mlp.experts." in n and t.ndim == 3 and (args.random_expert_mix or scheme or dense != "bf16"):
             return "MFE"
@@ -127,12 +128,12 @@ def _cmd_quantize(args) -> int:
         gs, k = expertwise._NINT_PRESETS[bits]
         expertwise._NINT_PRESETS[bits] = (args.groupsize or gs, args.sub_bits or k)
     store = None
-    if not args.no_temp and not args.fp8_sq_bits:
+    if not args.no_temp and not args.fp8_sq_bits and row_widths is None:
         from .quantize.resume import ResumeStore
         store = ResumeStore(str(out) + ".tmp", resume=args.resume, keep=args.keep_temp)
     q = quantize_tensors(tensors, dense=dense, expert_mix=args.random_expert_mix, seed=args.random_expert_mix_seed,
                          widths=widths, imatrix=imatrix, scheme=scheme, device=args.device, resume=store,
-                         fp8_sq_bits=args.fp8_sq_bits,
+                         fp8_sq_bits=args.fp8_sq_bits, row_widths=row_widths,
                          progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
     extra = {"quantization": {"dense": dense, "preset": args.preset or None, "imatrix": bool(imatrix), "ew_scheme": bool(scheme), "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
                               "random_expert_mix_seed": args.random_expert_mix_seed if args.random_expert_mix else None}}
@@ -194,6 +195,14 @@ def _cmd_calibrate(args) -> int:
         Path(args.output).write_text(json.dumps(doc, indent=1))
         used = sum(sizes[k] * cands[c] for k, c in choice.items()) / max(1, sum(sizes.values()))
         print(json.dumps({"output": args.output, "tensors": len(stats), "bits_per_weight": round(used, 3)}))
+        return 0
+    if args.calibrate_cmd == "inint":
+        from .calibration import inint
+        from .calibration.imatrix import load as load_imatrix
+        doc = inint.select_rows(tensors, args.target_bpw, imatrix=load_imatrix(args.imatrix) if args.imatrix else None,
+                                low=args.low, high=args.high, device=args.device)
+        Path(args.output).write_text(json.dumps(doc))
+        print(json.dumps({"output": args.output, "tensors": len(doc["tensors"]), **doc["report"]}))
         return 0
     if args.calibrate_cmd in ("candidates", "allocate", "natscale"):
         from .calibration import natscale
@@ -643,6 +652,7 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--preset", help="role-based mixed-width NINT preset: S2-S S2-M S3-S S3-M S3-L S4-S S4-M S5-S S5-M S6 S8")
     q.add_argument("--imatrix", help="importance matrix (.npz from `mfq calibrate imatrix`) for the NINT search")
     q.add_argument("--ew-scheme", "--scheme", dest="ew_scheme", help="mfq.calibration-scheme.v3 from `mfq solve-ew`")
+    q.add_argument("--row-widths", help="per-neuron NINT widths (mfq.inint-rows.v1 from `mfq calibrate inint`)")
     q.add_argument("--random-expert-mix", default="", help="comma separated families per routed expert projection")
     q.add_argument("--random-expert-mix-seed", type=int, default=20260908)
     q.add_argument("--full-precision", action="store_true")
@@ -699,7 +709,16 @@ def build_parser() -> argparse.ArgumentParser:
     cl.add_argument("--method", choices=("natscale", "milp"), default="natscale")
     cn = cs.add_parser("natscale", help="NatScale allocation (contrast-normalised sensitivities, convex-hull budget solver)")
     _candidate_args(cn)
-    for p_ in (cc, cl, cn):
+    cr = cs.add_parser("inint", help="per-neuron NINT widths: every row of every dense projection narrow or wide under a budget")
+    cr.add_argument("input")
+    cr.add_argument("--imatrix")
+    cr.add_argument("--target-bpw", type=float, required=True)
+    cr.add_argument("--low", type=int, default=4)
+    cr.add_argument("--high", type=int, default=8)
+    cr.add_argument("--device", default="cpu")
+    cr.add_argument("--seed", type=int, default=0)
+    cr.add_argument("--output", required=True)
+    for p_ in (cc, cl, cn, cr):
         p_.set_defaults(fn=_cmd_calibrate)
     se = sub.add_parser("solve-ew", help="expert-wise joint budget solver (MILP) -> calibration scheme")
     se.add_argument("--importance", required=True)

@@ -92,3 +92,34 @@ def test_calibrate_subcommands(tmp_path, capsys):
     capsys.readouterr()
     assert main(["quantize", "synthetic:tiny-moe", str(out), "--ew-scheme", str(scheme)]) == 0
     assert out.exists()
+
+
+def test_per_neuron_widths_end_to_end(tmp_path, capsys):
+    """`mfq calibrate inint` -> `mfq quantize --row-widths`: rows that matter get eight bits, the mean stays in budget, and the
+    mixed matrix reconstructs better than the all-narrow one."""
+    import json
+
+    from mfq_b200 import formats as F
+    from mfq_b200.calibration import inint
+    from mfq_b200.cli import main
+    rng = np.random.default_rng(0)
+    w = rng.normal(size=(64, 256)).astype(np.float32) * 0.05
+    w[:8] *= 20.0  # a few loud neurons: their rows cost most at four bits
+    doc = inint.select_rows({"model.block.0.attention.query.weight": w}, 5.6)
+    rep = doc["report"]
+    assert rep["bits_per_weight"] <= 5.6 and 0 < rep["high_rows"] < 64 and rep["loss_vs_all_low"] < 0.5
+    assert set(range(8)) <= set(doc["tensors"]["model.block.0.attention.query.weight"]["high_rows"])
+    bits = inint.row_bits(doc, "model.block.0.attention.query.weight")
+    assert bits.dtype == np.uint8 and set(bits.tolist()) == {4, 8}
+    with pytest.raises(ValueError):
+        inint.select_rows({"model.block.0.attention.query.weight": w}, 3.0)  # below the all-narrow size
+    im, rows, out = tmp_path / "im.npz", tmp_path / "rows.json", tmp_path / "m.mfq"
+    assert main(["calibrate", "imatrix", "synthetic:tiny-moe", "--output", str(im), "--chunks", "1", "--ctx", "48"]) == 0
+    assert main(["calibrate", "inint", "synthetic:tiny-moe", "--imatrix", str(im), "--target-bpw", "6.0", "--output", str(rows)]) == 0
+    capsys.readouterr()
+    assert main(["quantize", "synthetic:tiny-moe", str(out), "--row-widths", str(rows), "--imatrix", str(im)]) == 0
+    listed = json.loads(rows.read_text())["tensors"]
+    with F.open_mfq(out) as store:
+        name = next(n for n in listed if listed[n]["high_rows"])
+        t = store[name]
+        assert sorted(set(np.asarray(t.row_q_bits).tolist())) == [4, 8]
