@@ -195,6 +195,71 @@ __global__ void quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* 
   }
 }
 
+
+// SwiGLU + row quantization for decode-sized batches, one ROW PER CLUSTER of kSplit CTAs: with one CTA per row a batch
+// of 64 rows occupies 64 of 148 SMs and every thread walks its slice twice (amax, then encode, the SiLU evaluated both
+// times).  Here a CTA owns 1/kSplit of the row, keeps its products in registers, and the row maximum is met through
+// distributed shared memory (one float per CTA, two cluster barriers).
+constexpr int kSwigluSplit = 4;
+constexpr int kSwigluVecs = 2;  // 16-byte vectors per thread: covers K <= 8 * 256 * kSwigluVecs * kSwigluSplit
+__global__ void __cluster_dims__(kSwigluSplit, 1, 1) __launch_bounds__(256)
+silu_mul_quant_split_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q_out, float* __restrict__ scale_out,
+                            int K, int in_stride) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[33];
+  __shared__ float part_max;
+  const size_t row = blockIdx.x / kSwigluSplit;
+  const int part = blockIdx.x % kSwigluSplit;
+  const __nv_bfloat16* xr = x + row * in_stride;
+  const int nvec = K / 8 / kSwigluSplit, v0 = part * nvec;
+  float y[kSwigluVecs][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < kSwigluVecs; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      const uint4 a = *reinterpret_cast<const uint4*>(xr + (v0 + vi) * 8);
+      const uint4 b = *reinterpret_cast<const uint4*>(xr + K + (v0 + vi) * 8);
+      const __nv_bfloat16* ab = reinterpret_cast<const __nv_bfloat16*>(&a);
+      const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float g = __bfloat162float(ab[j]);
+        y[i][j] = __bfloat162float(__float2bfloat16(g / (1.f + __expf(-g)) * __bfloat162float(bb[j])));
+        amax = fmaxf(amax, fabsf(y[i][j]));
+      }
+    }
+  }
+  amax = block_reduce<true>(amax, red);
+  if (threadIdx.x == 0) part_max = amax;
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  float row_max = 0.f;
+#pragma unroll
+  for (int r = 0; r < kSwigluSplit; ++r) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&part_max)), "r"(r));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    row_max = fmaxf(row_max, v);
+  }
+  // nobody leaves (and gives up its shared memory) while a peer may still read it
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  const float scale = fmaxf(row_max, 1e-12f) / kE4M3Max, inv = 1.f / scale;
+  if (part == 0 && threadIdx.x == 0) scale_out[row] = scale;
+#pragma unroll
+  for (int i = 0; i < kSwigluVecs; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      uint2 o;
+      uint8_t* ob = reinterpret_cast<uint8_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ob[j] = to_e4m3(y[i][j] * inv);
+      *reinterpret_cast<uint2*>(q_out + row * K + (v0 + vi) * 8) = o;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // RoPE (rotate-half pairing i <-> i + rot/2 over the first `rot` dims) on Q and K, then K/V -> FP8 pages.
 // qkv: [T, (Hq + 2 Hk) * D] bf16.  One warp per (token, head).  Cache page layout [page][Hk][page_size][D]
@@ -508,6 +573,11 @@ extern "C" int mfq_quant_rows(const void* x, void* q_out, float* scale_out, int 
                               cudaStream_t stream) {
   if (K % 8 || in_stride % 8 || M <= 0) return -1;
   const int threads = K >= 4096 ? 512 : 256;
+  if (swiglu && M <= 256 && K % (8 * kSwigluSplit) == 0 && K / 8 / kSwigluSplit <= 256 * kSwigluVecs && K >= 4096) {
+    launch_kernel(silu_mul_quant_split_kernel, dim3(M * kSwigluSplit), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x),
+                  static_cast<uint8_t*>(q_out), scale_out, K, in_stride);
+    return cudaGetLastError() == cudaSuccess ? 0 : -7;
+  }
   if (swiglu)
     launch_kernel(quant_rows_kernel<1>, dim3(M), dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out), scale_out, K, in_stride, static_cast<const __nv_bfloat16*>(nullptr), 0);
   else

@@ -6,7 +6,7 @@ for a multi-pass capture to finish in about a minute) and exits.  Cases: ``gemm_
 ``w4_decode`` / ``w4_prefill`` (the 4-bit in-pipeline-decode GEMM at the same shapes), ``gdn_decode`` (Gated DeltaNet step,
 64 sequences), ``moe_dispatch`` (expert-parallel dispatch + combine kernels at world 1, 4096 tokens), ``gemv_decode``
 (the weight-streaming FP8 kernel, M=1, N=28672, K=4096), ``attn_prefill_d256`` (T=2048, 16 query / 2 KV heads of 256),
-``gdn_prefill`` (the long-row Gated DeltaNet path, 2048 tokens, 32 heads), ``packed_decode`` / ``packed_decode_bs1`` (the
+``gdn_prefill`` (the long-row Gated DeltaNet path, 2048 tokens, 32 heads), ``mla_decode`` (latent-cache decode attention), ``packed_decode`` / ``packed_decode_bs1`` (the
 packed-expert product at 64 tokens / one token, 512 experts).
 """
 
@@ -87,6 +87,28 @@ def gdn_prefill() -> None:
         gdn.recurrent(qkv, z, a, b, A_log, dt_bias, norm_w, state, slot, L, hk, hv)
 
 
+def mla_decode() -> None:
+    """Shared-row latent attention, 64 sequences x 4096 tokens, 16 heads (one rank's share of 128): 285 MB of rows."""
+    import math
+
+    from ..engine.kv_cache import PagedKVCache
+    from . import mla as mla_ops
+    batch, ctx, heads = 64, 4096, 16
+    pages_per = math.ceil(ctx / 16)
+    cache = PagedKVCache(layers=2, kv_heads=1, head_dim=576, num_pages=batch * pages_per + 1, max_seqs=batch,
+                         max_pages_per_seq=pages_per, device="cuda")
+    cache.k.view(torch.int8).random_(-100, 100)
+    cache.v.view(torch.int8).random_(-100, 100)
+    cache.k_scale.fill_(0.01)
+    cache.v_scale.fill_(0.01)
+    for b in range(batch):
+        cache.assign(b, b, ctx)
+    q = torch.randn((batch, heads, 576), device="cuda").to(torch.bfloat16)
+    sl = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+    for i in range(3):
+        mla_ops.decode(q, cache.layer(i % 2), cache.block_table, sl, sm_scale=0.07, splits=2)
+
+
 def w4_gemm(m: int, n: int, k: int) -> None:
     from . import w4
     base = w4.quantize_torch(torch.randn((n, k), device="cuda") * 0.02)
@@ -151,7 +173,7 @@ def packed_decode(tokens: int = 64) -> None:
 CASES = {"gemm_prefill": lambda: gemm(4096, 4096, 4096), "gemm_decode": lambda: gemm(64, 28672, 4096),
          "attn_decode": attn_decode, "attn_prefill": attn_prefill, "w4_decode": lambda: w4_gemm(64, 28672, 4096),
          "w4_prefill": lambda: w4_gemm(4096, 4096, 4096), "gdn_decode": gdn_decode, "moe_dispatch": moe_dispatch,
-         "gemv_decode": lambda: gemm(1, 28672, 4096), "packed_decode": packed_decode, "packed_decode_bs1": lambda: packed_decode(1), "attn_prefill_d256": attn_prefill_d256, "gdn_prefill": gdn_prefill}
+         "gemv_decode": lambda: gemm(1, 28672, 4096), "packed_decode": packed_decode, "packed_decode_bs1": lambda: packed_decode(1), "attn_prefill_d256": attn_prefill_d256, "gdn_prefill": gdn_prefill, "mla_decode": mla_decode}
 
 if __name__ == "__main__":
     CASES[sys.argv[1]]()

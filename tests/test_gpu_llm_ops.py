@@ -49,6 +49,13 @@ def test_quant_rows_and_swiglu():
     # the kernel rounds silu(g) * u once, the restatement goes through bf16 first: a product that lands on a rounding
     # boundary takes the neighbouring code (one step = 12.5 %), so a small share of the elements may differ by a step
     assert_close(deq(q, s), deq(q2, s2), rel=0.07, outliers=3e-2)
+    # decode-sized batches of wide rows take the kernel that splits a row over a cluster of four CTAs
+    for m, i in ((64, 14336), (5, 4096), (3, 5120)):
+        gu = torch.randn((m, 2 * i), device="cuda", generator=g).to(torch.bfloat16)
+        q, s = ops.silu_mul_quant(gu)
+        q2, s2 = ref.silu_mul_quant(gu)
+        assert_close(s, s2, rel=1e-2, what=f"swiglu scale {m}x{i}")
+        assert_close(deq(q, s), deq(q2, s2), rel=0.07, outliers=3e-2, what=f"swiglu rows {m}x{i}")
 
 
 def make_cache(hk, d, batch, max_len):
