@@ -42,3 +42,12 @@ def test_tp_matches_single_gpu_and_nccl_baseline(world):
     assert r["ep_vs_single_mean_err"] <= 0.03 * r["ep_logit_scale"], r
     if world == 2:  # the tiny hybrid model has two linear-attention key heads: one per rank
         assert r["hybrid_ranks_agree"] and r["hybrid_tp_cos"] > 0.95 and r["hybrid_tp_row_cos"] > 0.97, r
+
+
+def test_two_gpu_ranks_serve_a_completion(tmp_path):
+    """`mfq serve --tensor-parallel 2` on two GPUs: launcher, sharded load, fused collectives, command log, HTTP on rank 0."""
+    require_gpu_lib()
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from test_tp_serve_cpu import serve_and_complete
+    serve_and_complete(tmp_path, ["--tensor-parallel", "2"], [], {"NCCL_NVLS_ENABLE": "0"})

@@ -30,14 +30,20 @@ import pytest
 
 @pytest.mark.parametrize("mode", [["--tensor-parallel", "2"], ["--layer-parallel", "2"]])
 def test_two_cpu_ranks_serve_a_completion(tmp_path, mode):
+    serve_and_complete(tmp_path, mode, ["--device", "cpu"], {"OMP_NUM_THREADS": "2"})
+
+
+def serve_and_complete(tmp_path, mode, device_args, env_extra):
+    """Start `mfq serve` with ``mode`` on a tiny checkpoint, wait for /health, run the same greedy completion twice (the second
+    one resumes the session), check the runtime status, stop the server."""
     ckpt = tmp_path / "tiny.mfq"
     assert main(["quantize", "synthetic:tiny-moe-128", str(ckpt), "--full-precision"]) == 0
     port = free_port()
-    env = dict(os.environ, OMP_NUM_THREADS="2")
+    env = dict(os.environ, **env_extra)
     env.pop("RANK", None)
     env.pop("WORLD_SIZE", None)
     log = open(tmp_path / "serve.log", "w")
-    proc = subprocess.Popen([sys.executable, "-m", "mfq_b200.cli", "serve", "--model", str(ckpt), "--device", "cpu", "--port", str(port),
+    proc = subprocess.Popen([sys.executable, "-m", "mfq_b200.cli", "serve", "--model", str(ckpt), *device_args, "--port", str(port),
                              *mode, "--continuous-batching", "2", "--ctx-size", "96"],
                             env=env, stdout=log, stderr=subprocess.STDOUT, start_new_session=True)
     try:
