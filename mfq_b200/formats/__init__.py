@@ -15,6 +15,9 @@ def dequantize(t):
     """Any family tensor -> float32 ndarray in its logical shape."""
     import numpy as np
     from . import mxfp4sq as _sq
+    from .npq0 import Npq0Tensor, dequantize_npq0
+    if isinstance(t, Npq0Tensor):
+        return dequantize_npq0(t)
     from .nint8zero import Nint8ZeroTensor, dequantize_nint8_zero
     if isinstance(t, Nint8ZeroTensor):
         return dequantize_nint8_zero(t)

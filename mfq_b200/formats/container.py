@@ -28,7 +28,7 @@ from typing import Any
 
 import numpy as np
 
-from . import fp8sq, mfe, mx, mxfp4sq, nint, nint8zero, nvq
+from . import fp8sq, mfe, mx, mxfp4sq, nint, nint8zero, npq0, nvq
 from .dense import DENSE_DTYPES, pack_dense, unpack_dense
 
 MFQ_MAGIC = b"MFQ1"
@@ -86,6 +86,8 @@ def pack_tensor(t) -> tuple[str, bytes]:
         return t.dtype, fp8sq.pack_fp8sq(t)
     if isinstance(t, nint8zero.Nint8ZeroTensor):
         return nint8zero.NINT8_ZERO_DTYPE, nint8zero.pack_nint8_zero(t)
+    if isinstance(t, npq0.Npq0Tensor):
+        return t.variant.label, npq0.pack_npq0(t)
     if isinstance(t, nint.NintTensor):
         return nint.NINT_DTYPE, nint.pack_nint(t)
     if isinstance(t, (nvq.NvqTensor, nvq.NvqJscTensor)):
@@ -104,6 +106,8 @@ def unpack_tensor(dtype: str, blob):
         return mx.unpack_mx(dtype, blob)
     if dtype == nint8zero.NINT8_ZERO_DTYPE:
         return nint8zero.unpack_nint8_zero(blob)
+    if dtype in npq0.VARIANTS:
+        return npq0.unpack_npq0(blob)
     dtype = canonical_dtype(dtype)
     if dtype == MFE_DTYPE:
         return mfe.unpack_mfe(blob, unpack_tensor)

@@ -45,7 +45,7 @@ class ExpertProfile:
             return self.nint.bpw(4096)
         if self.nvq is not None:
             return self.nvq.bpw(4096, out=4096)
-        return {"MXFP4": 4.25, "FP8": 8.0, "BF16": 16.0}[self.family]
+        return {"MXFP4": 4.25, "FP8": 8.0, "BF16": 16.0, "NPQ0-S": 0.84, "NPQ0-L": 1.0}[self.family]
 
 
 def parse_profiles(text: str) -> tuple[ExpertProfile, ...]:
@@ -60,7 +60,7 @@ def parse_profiles(text: str) -> tuple[ExpertProfile, ...]:
             out.append(ExpertProfile(name, nint=NintSpec(bits, gs, k)))
         elif name in _NVQ_FAMILIES:
             out.append(ExpertProfile(name, nvq=NvqSpec(_NVQ_FAMILIES[name])))
-        elif name in ("MXFP4", "FP8", "BF16"):
+        elif name in ("MXFP4", "FP8", "BF16", "NPQ0-S", "NPQ0-L"):
             out.append(ExpertProfile(name))
         else:
             raise ValueError(f"unsupported expert precision {name!r}")
@@ -85,6 +85,9 @@ def quantize_matrix(w, profile: ExpertProfile, device="cpu", importance=None):
         return quantize_mxfp4(w, device=device)
     if profile.family == "FP8":
         return quantize_fp8_block(w, device=device)
+    if profile.family in ("NPQ0-S", "NPQ0-L"):
+        from ..formats.npq0 import quantize_npq0
+        return quantize_npq0(np.asarray(w, dtype=np.float32), profile.family)
     if profile.family == "BF16":
         from ..formats.dense import to_bf16
         return to_bf16(np.asarray(w, dtype=np.float32))
