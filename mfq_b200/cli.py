@@ -731,7 +731,8 @@ def build_parser() -> argparse.ArgumentParser:
     ci.set_defaults(fn=_cmd_calibrate)
 
     dg = sub.add_parser("diagnose", help="self-checks: formats anywhere, kernels and the engine on a GPU box")
-    dg.add_argument("--check", action="append", help="run only this check (repeatable): nint, fp8-block, container, tp-linear, ep-moe, continuous-batching, json-constraint, fp8-gemm, attention, engine")
+    dg.add_argument("--check", action="append", help="run only this check (repeatable); `mfq diagnose --list` prints the names")
+    dg.add_argument("--list", action="store_true", help="print the names of all checks and exit")
     from . import diagnostics as _diag
     dg.set_defaults(fn=_diag.main)
     i = sub.add_parser("inspect", help="summarise an .mfq container")

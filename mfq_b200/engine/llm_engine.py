@@ -476,11 +476,13 @@ class LLMEngine:
             self.model.sample_greedy(mlogits, out=self.c_tok[:b])
             self.draft[:b, 0].copy_(torch.where(self.active[:b] > 0, self.c_tok[:b], self.draft[:b, 0]))  # masked rows keep theirs
 
-    def _splits_now(self, b: int) -> int:
+    def _splits_now(self, b: int, q_len: int = 1) -> int:
         """Attention KV splits for the current contexts (host mirror of the row lengths; a graph is kept per value)."""
         from ..ops.kernels import attn_splits_for
         longest = max(self.row_len.values(), default=self.max_seq_len)
-        return attn_splits_for(b, self.model.hk, min(self.max_seq_len, longest))
+        hk = self.model.hk
+        rows = max(1, getattr(self.model, "hq", hk) // hk) * q_len
+        return attn_splits_for(b, hk, min(self.max_seq_len, longest), getattr(self.model.cfg, "head_dim", 128), rows)
 
     def decode_step(self, b: int, stochastic: bool = False, constrained: bool = False, keep_head: bool = False) -> None:
         """Advance the active rows among ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device).
@@ -552,7 +554,7 @@ class LLMEngine:
         mtp_ops.prepare(self.sampled[:b], draft[:b], self.seq_lens[:b], table, self.active[:b], ids, pos, slots, lens,
                         self.cache.page_size)
         if self.device.type == "cuda":
-            self.model.attn_splits = self._splits_now(b)
+            self.model.attn_splits = self._splits_now(b, w)
         state_slots = None
         if self.rec_state is not None:
             state_slots = self.state_slots[:b]

@@ -194,13 +194,20 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tenso
     return q_out
 
 
-def attn_splits_for(batch: int, kv_heads: int, ctx_len: int) -> int:
-    """KV splits per (sequence, KV head) for the decode attention, fitted to a sweep on B200 (batch 8..128, contexts
-    1k/4k): enough CTAs to occupy the GPU (~256) when the batch is small, about 1300 tokens per split when the
-    context is long, never below 256 tokens per split."""
-    by_ctas = -(-256 // max(1, batch * kv_heads))
-    by_len = int(ctx_len / 1300 + 0.5)
-    return max(1, min(max(by_ctas, by_len), max(1, ctx_len // 256), 64))
+def attn_splits_for(batch: int, kv_heads: int, ctx_len: int, head_dim: int = 128, rows: int = 1) -> int:
+    """KV splits per (sequence, KV head) for the decode attention, fitted to sweeps on B200 (batch 1..128, contexts
+    1k/4k/16k, 8 and 2 KV heads, head widths 128 and 256).  ``rows`` = query heads per KV head x query tokens per
+    sequence.  Up to 8 rows run the tokens-as-rows kernel, 4 CTAs per SM (2 at width 256): the best split count is the
+    largest one whose grid still fits one wave, with at least 256 tokens per split and at most 32 splits -- partial
+    waves cost more than short splits, and a batch that fills the GPU by itself is not split at all.  Wider windows run
+    the 16-row kernel at 3 CTAs per SM, where several waves of shorter CTAs (about 1300 tokens each) measured best."""
+    n = max(1, batch * kv_heads)
+    if rows > 8:
+        by_ctas = -(-256 // n)
+        by_len = int(ctx_len / 1300 + 0.5)
+        return max(1, min(max(by_ctas, by_len), max(1, ctx_len // 256), 64))
+    slots = 148 * (4 if head_dim <= 128 else 2)
+    return max(1, min(slots // n, ctx_len // 256, 32))
 
 
 def paged_attn_decode(q: torch.Tensor, kv, block_table: torch.Tensor, seq_lens: torch.Tensor, *, sm_scale: float,

@@ -101,9 +101,11 @@ def test_rope_kv_write_and_decode_attention(hq, hk, d):
         assert_close(got, want, rel=2e-2, what=f"decode attention splits={splits}")
 
 
-def test_decode_attention_verify_window():
+@pytest.mark.parametrize("hq,hk,d,ql", [(8, 2, 128, 4), (8, 2, 128, 2), (4, 4, 128, 3), (8, 1, 256, 1), (16, 2, 256, 2)])
+def test_decode_attention_verify_window(hq, hk, d, ql):
+    """Windows of several query tokens: 16 (row, head) pairs take the 16-row kernel, up to 8 the tokens-as-rows one."""
     require_gpu_lib()
-    hq, hk, d, n, ql = 8, 2, 128, 100, 4
+    n = 100
     cache = make_cache(hk, d, 1, 256)
     kv = cache.layer(0)
     cache.assign(0, 0, n)
@@ -143,4 +145,5 @@ def test_diagnose_kernel_checks_pass():
     report = diagnostics.run()
     failed = {k: v for k, v in report["checks"].items() if not v["ok"]}
     assert report["ok"], (failed, report.get("device_status"))
-    assert {"fp8-gemm", "attention", "engine"} <= set(report["checks"])
+    assert {"fp8-gemm", "attention", "engine", "gdn-chunked", "packed-experts", "mla-latent-cache", "moe-grouped", "codecs",
+            "native"} <= set(report["checks"])
