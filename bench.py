@@ -169,6 +169,13 @@ def run_ours(args) -> dict:
     ms64, clocks = timed_decode(batch, args.steps, args.warmup)
     ops.Workspace.get(dev).check()
     phase("batched decode timed")
+    if args.profile_steps:  # a profiler started with its collection off sees exactly these steps
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for _ in range(args.profile_steps):
+            engine.decode_step(batch)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     launches = engine.launches_per_step.get(batch, 0) * args.steps
     ms1, _ = timed_decode(1, args.steps, args.warmup)
     ops.Workspace.get(dev).check()
@@ -395,6 +402,8 @@ def main() -> None:
                     help="block linears in block-scaled FP8 (default) or in the 4-bit NINT-native format (single GPU); "
                          "hybrid80b: 'packed' keeps the routed experts in a seeded mix of packed NINT 2-5 bit / MXFP4 "
                          "codes (about 3.4 bits per weight) decoded inside the expert kernels")
+    ap.add_argument("--profile-steps", type=int, default=0,
+                    help="after the timed region, run this many batched decode steps between cudaProfilerStart/Stop")
     ap.add_argument("--tiny", action="store_true", help="tiny model, for checking the harness itself")
     ap.add_argument("--model", choices=["llama8b", "hybrid80b"], default="llama8b",
                     help="llama8b: the flagship; hybrid80b: the Gated-DeltaNet + MoE hybrid with an MTP head (one GPU)")

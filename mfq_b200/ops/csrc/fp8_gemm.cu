@@ -216,12 +216,30 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (!early_inputs) pdl_wait();
+  // Weights are never written by a kernel of the same stream, so the plain GEMM starts the weight tiles of its first
+  // ring pass BEFORE it waits for its predecessor: under programmatic dependent launch this CTA is resident while the
+  // short kernel that produces its activations (a norm, a quantization) still runs, and the weight stream -- all of it
+  // for a short K range -- arrives under that kernel instead of after it.  The activation tiles follow the wait.
+  int w_ahead = 0;
+  if (!early_inputs) {
+    if (warp == 0 && lane == 0) {
+      tma_prefetch_desc(&tmap_w);
+      tma_prefetch_desc(&tmap_x);
+      w_ahead = min(nkb, stages);
+      for (int i = 0; i < w_ahead; ++i) {
+        mbar_expect_tx(&full[i], Cfg::kStageBytes);
+        tma_load_2d(tiles + i * Cfg::kStageBytes, &tmap_w, &full[i], (kb0 + i) * kBlockK, n0);
+      }
+    }
+    pdl_wait();
+  }
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_w);
-      tma_prefetch_desc(&tmap_x);
+      if (early_inputs) {
+        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
+      }
       const CUtensorMap* xmap = (gather && (ag_epoch & 1u)) ? &tmap_x_alt : &tmap_x;
       bool shard_ready = true;
       if (gather) {
@@ -248,12 +266,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       int s = 0;
       uint32_t ring_phase = 0;  // ring position and wrap parity, kept incrementally: the depth is a run-time value
       for (int i = 0; shard_ready && i < nkb; ++i, s = (s + 1 == stages ? 0 : s + 1), ring_phase ^= (s == 0 ? 1u : 0u)) {
-        if (!mbar_wait(&empty[s], ring_phase ^ 1u, abort_flag, p.status, kStatusTimeoutProducer)) break;
         uint8_t* a = tiles + s * Cfg::kStageBytes;
         uint8_t* b = a + kTileN * kBlockK;
-        mbar_expect_tx(&full[s], Cfg::kStageBytes);
-        if (p.tile_map) tma_load_3d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0, expert);
-        else tma_load_2d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0);
+        if (i >= w_ahead) {  // the first pass of the plain mode is armed and its weight tile on the way already
+          if (!mbar_wait(&empty[s], ring_phase ^ 1u, abort_flag, p.status, kStatusTimeoutProducer)) break;
+          mbar_expect_tx(&full[s], Cfg::kStageBytes);
+          if (p.tile_map) tma_load_3d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0, expert);
+          else tma_load_2d(a, &tmap_w, &full[s], (kb0 + i) * kBlockK, n0);
+        }
         tma_load_2d(b, xmap, &full[s], (kb0 + i) * kBlockK, t0);
       }
     }
@@ -497,14 +517,21 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           }  // all-reduce
         }
         if (owner && n < p.N) {
+          // The residual may be the output buffer itself (in-place add), so the compiler keeps every load behind the
+          // store before it: one exposed memory round trip per token column.  All loads of the thread are issued
+          // first (each element is read and written by this thread only), then the sums are stored.
+          if (p.residual) {
+            unsigned short res[CW];
+            const unsigned short* rp = reinterpret_cast<const unsigned short*>(p.residual);
+#pragma unroll
+            for (int tt = 0; tt < CW; ++tt)
+              res[tt] = (col0 + tt < tl) ? __ldcg(rp + size_t(t0 + col0 + tt) * p.N + n) : (unsigned short)0;
+#pragma unroll
+            for (int tt = 0; tt < CW; ++tt) acc[tt] += __uint_as_float(uint32_t(res[tt]) << 16);
+          }
 #pragma unroll
           for (int tt = 0; tt < CW; ++tt) {
-            if (col0 + tt < tl) {
-              float v = acc[tt];
-              const size_t o = size_t(t0 + col0 + tt) * p.N + n;
-              if (p.residual) v += __bfloat162float(p.residual[o]);
-              p.out[o] = __float2bfloat16(v);
-            }
+            if (col0 + tt < tl) p.out[size_t(t0 + col0 + tt) * p.N + n] = __float2bfloat16(acc[tt]);
           }
         }
       }
@@ -639,13 +666,15 @@ rs_reduce_kernel(ArParams ar, __nv_bfloat16* __restrict__ out, const __nv_bfloat
         for (int rr = 0; rr < 4; ++rr) v[j] += part[j][rr];  // rank order
     }
     if (n < N) {
+      if (residual) {  // may be the output buffer: all loads before the first store
+        float res[kBatch];
 #pragma unroll
-      for (int j = 0; j < kBatch; ++j) {
-        const size_t o = size_t(t_local * BT + c0 + j) * N + n;
-        float val = v[j];
-        if (residual) val += __bfloat162float(residual[o]);
-        out[o] = __float2bfloat16(val);
+        for (int j = 0; j < kBatch; ++j) res[j] = __bfloat162float(residual[size_t(t_local * BT + c0 + j) * N + n]);
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) v[j] += res[j];
       }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) out[size_t(t_local * BT + c0 + j) * N + n] = __float2bfloat16(v[j]);
     }
   }
 }

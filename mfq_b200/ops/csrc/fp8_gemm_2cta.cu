@@ -354,14 +354,22 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       }
       if (ok && n < p.N) {
         const int tl = min(BT, p.M - t0);
+        // residual and output may be one buffer: all loads first, or every load would wait behind the store before it
+        if (p.residual) {
+          unsigned short res[CW];
+          const unsigned short* rp = reinterpret_cast<const unsigned short*>(p.residual);
+#pragma unroll
+          for (int tt = 0; tt < CW; ++tt)
+            res[tt] = (col0 + tt < tl) ? __ldcg(rp + size_t(t0 + col0 + tt) * p.N + n) : (unsigned short)0;
+#pragma unroll
+          for (int tt = 0; tt < CW; ++tt) acc[tt] = fmaf(acc[tt], xs_w[tt], __uint_as_float(uint32_t(res[tt]) << 16));
+        } else {
+#pragma unroll
+          for (int tt = 0; tt < CW; ++tt) acc[tt] *= xs_w[tt];
+        }
 #pragma unroll
         for (int tt = 0; tt < CW; ++tt) {
-          if (col0 + tt < tl) {
-            float v = acc[tt] * xs_w[tt];
-            const size_t o = size_t(t0 + col0 + tt) * p.N + n;
-            if (p.residual) v += __bfloat162float(p.residual[o]);
-            p.out[o] = __float2bfloat16(v);
-          }
+          if (col0 + tt < tl) p.out[size_t(t0 + col0 + tt) * p.N + n] = __float2bfloat16(acc[tt]);
         }
       }
     }

@@ -277,14 +277,18 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) {
         }
       }
       if (owner && n < p.N) {
+        // residual and output may be one buffer: all loads first, or every load would wait behind the store before it
+        if (p.residual) {
+          unsigned short res[BT];
+          const unsigned short* rp = reinterpret_cast<const unsigned short*>(p.residual);
+#pragma unroll
+          for (int c = 0; c < BT; ++c) res[c] = (c < tl) ? __ldcg(rp + size_t(t0 + c) * p.N + n) : (unsigned short)0;
+#pragma unroll
+          for (int c = 0; c < BT; ++c) acc[c] += __uint_as_float(uint32_t(res[c]) << 16);
+        }
 #pragma unroll
         for (int c = 0; c < BT; ++c) {
-          if (c < tl) {
-            const size_t o = size_t(t0 + c) * p.N + n;
-            float v = acc[c];
-            if (p.residual) v += __bfloat162float(p.residual[o]);
-            p.out[o] = __float2bfloat16(v);
-          }
+          if (c < tl) p.out[size_t(t0 + c) * p.N + n] = __float2bfloat16(acc[c]);
         }
       }
     }
