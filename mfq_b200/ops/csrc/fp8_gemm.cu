@@ -88,7 +88,31 @@ struct GemmParams {
   const int* expert_offsets = nullptr;
   AgParams ag;
   int stages = 0;  // depth of the shared-memory ring actually used (<= GemmCfg::kStages); fewer stages = more CTAs per SM
+  // Split-K with the splits of a tile launched as one thread-block cluster: the partial sums meet in distributed shared
+  // memory instead of a global scratch buffer with an arrival counter, and every CTA of the cluster finishes a share of
+  // the token columns instead of the last arriver finishing all of them.
+  int cluster_reduce = 0;
 };
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+  return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 template <int BT>
 __global__ void __launch_bounds__(GemmCfg<BT>::kThreads, (BT <= 64 ? 2 : 1))
@@ -366,7 +390,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const int tiles_nt = n_tiles_x * gridDim.y;
       const int tile_id = t_tile * n_tiles_x + n_tile;
       bool owner = true;  // this CTA holds the tile's complete local sum in `acc`
-      if (gridDim.z > 1) {
+      if (p.cluster_reduce) {
+        // The ring is free (the last MMA has completed, so every tile that was loaded has been read): the partial
+        // goes there as [token column][128 rows] fp32 and is summed after the cluster barrier below.
+        owner = false;
+        float* stage = reinterpret_cast<float*>(tiles);
+#pragma unroll
+        for (int tt = 0; tt < CW; ++tt) stage[(col0 + tt) * kTileN + row] = acc[tt];
+      } else if (gridDim.z > 1) {
         owner = false;
         float* mine = p.ws + (size_t(split) * tiles_nt + tile_id) * (BT * kTileN);
 #pragma unroll
@@ -538,6 +569,54 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
   }
 
+  if (p.cluster_reduce) {
+    // Every thread of every CTA of the cluster gets here (all waits above are bounded), so the barriers cannot hang.
+    __syncwarp();
+    cluster_barrier();  // all partials are in place
+    if (warp >= 2 && !*abort_flag) {
+      // CTA r of S finishes the token columns c = r (mod S); a thread owns one output row and every kSel-th of those
+      // columns.  The S partials of a column are summed in split order whichever CTA does it, so results do not depend
+      // on scheduling.  All loads of a group of columns (S remote partials, multiplier, residual) leave before the
+      // first sum, so their round trips overlap.  (Fetching multipliers and residuals ahead of the barrier measured
+      // slower: the values have to be held across it, and the registers for that spill.)
+      constexpr int kSel = Cfg::kEpiWarps / 4;
+      constexpr int kGroup = 4;
+      const int e = int(threadIdx.x) - 64, row = e & 127, sel = e >> 7;
+      const int S = int(gridDim.z), r = int(cluster_cta_rank());
+      const int tl = min(BT, row_end - t0), n = n0 + row;
+      const uint32_t mine = smem_u32(tiles) + uint32_t(row) * 4u;
+      uint32_t base[8];
+#pragma unroll
+      for (int z = 0; z < 8; ++z) base[z] = map_to_cta(mine, uint32_t(z < S ? z : 0));
+      const unsigned short* rp = reinterpret_cast<const unsigned short*>(p.residual);
+      const int step = S * kSel;
+      for (int c0 = r + S * sel; c0 < tl; c0 += step * kGroup) {
+        float v[kGroup][8], xm[kGroup];
+        unsigned short res[kGroup];
+#pragma unroll
+        for (int j = 0; j < kGroup; ++j) {
+          const int c = c0 + j * step;
+          const bool live = c < tl;
+          xm[j] = live ? __ldg(p.x_scale + t0 + c) : 0.f;
+          res[j] = (live && rp && n < p.N) ? __ldcg(rp + size_t(t0 + c) * p.N + n) : (unsigned short)0;
+#pragma unroll
+          for (int z = 0; z < 8; ++z) v[j][z] = (live && z < S) ? ld_cluster_f32(base[z] + uint32_t(c) * (kTileN * 4u)) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < kGroup; ++j) {
+          const int c = c0 + j * step;
+          float sum = 0.f;
+#pragma unroll
+          for (int z = 0; z < 8; ++z) sum += v[j][z];  // split order; zeros beyond S
+          sum = sum * xm[j] + __uint_as_float(uint32_t(res[j]) << 16);
+          if (c < tl && n < p.N) p.out[size_t(t0 + c) * p.N + n] = __float2bfloat16(sum);
+        }
+      }
+    }
+    __syncwarp();
+    cluster_barrier();  // nobody's shared memory goes away while a peer still reads it
+  }
+
   // ----- teardown: every thread arrives here, also after an aborted wait -----
   tc_fence_before();
   __syncthreads();
@@ -606,6 +685,43 @@ static int launch_gemm(const void* w, const float* w_scale, const void* x, const
     else if (ctas > 148 && BT <= 64) p.stages = kb_per < 4 ? (kb_per < 2 ? 2 : kb_per) : 4;
   }
   const int smem_bytes = p.stages * Cfg::kStageBytes + 1024 + 256 + Cfg::kXsBytes + Cfg::kWsBytes;
+  static const bool cluster_ok = [] { const char* e = getenv("MFQ_GEMM_CLUSTER_REDUCE"); return !e || atoi(e) != 0; }();
+  if (cluster_ok && !ar && !ag && !tile_map && splits > 1 && splits <= 8) {
+    // A cluster is placed inside one GPC, so a grid that needs nearly every SM (144 CTAs in clusters of 3, one CTA per
+    // SM) does not fit in one wave although the CTA count says it would; the driver is asked how many clusters of this
+    // shape can be resident, and the ring is made shallower (more CTAs per SM) until the whole grid is.
+    static int resident[64][9][Cfg::kStages + 1] = {};  // [device][cluster size][stages]: 0 = not asked yet
+    const int clusters = n_tiles * t_tiles;
+    const int min_stages = (BT * kTileN * 4 + Cfg::kStageBytes - 1) / Cfg::kStageBytes < 2 ? 2 : (BT * kTileN * 4 + Cfg::kStageBytes - 1) / Cfg::kStageBytes;
+    auto smem_for = [](int st) { return st * Cfg::kStageBytes + 1024 + 256 + Cfg::kXsBytes + Cfg::kWsBytes; };
+    auto fits = [&](int st) {
+      int& known = resident[dev][splits][st];
+      if (known == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(n_tiles, t_tiles, splits);
+        cfg.blockDim = dim3(Cfg::kThreads);
+        cfg.dynamicSmemBytes = smem_for(st);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = splits;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        known = (cudaOccupancyMaxActiveClusters(&n, fp8_gemm_kernel<BT>, &cfg) == cudaSuccess && n > 0) ? n : -1;
+        (void)cudaGetLastError();
+      }
+      return known >= clusters;
+    };
+    int st = p.stages;
+    while (st > min_stages && st > 2 && !fits(st)) st = st > 4 ? 4 : st - 1;
+    if (st >= min_stages) {
+      p.stages = st;
+      p.cluster_reduce = 1;
+      launch_kernel_clustered(fp8_gemm_kernel<BT>, dim3(n_tiles, t_tiles, splits), dim3(Cfg::kThreads), dim3(1, 1, splits),
+                              smem_for(st), stream, tw, tx, tx_alt, p);
+      return cudaGetLastError() == cudaSuccess ? 0 : -7;
+    }
+  }
   launch_kernel(fp8_gemm_kernel<BT>, dim3(n_tiles + extra_x, t_tiles, splits), dim3(Cfg::kThreads), smem_bytes, stream, tw, tx, tx_alt, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }

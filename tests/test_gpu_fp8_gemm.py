@@ -24,6 +24,8 @@ def make(m, n, k, seed=0):
     (1, 128, 128, 1), (16, 256, 512, 1), (5, 384, 1024, 1), (40, 512, 512, 1), (64, 1024, 2048, 1),
     (128, 256, 1024, 1), (300, 640, 1536, 1), (512, 1024, 4096, 1),
     (1, 256, 2048, 4), (33, 384, 4096, 8), (64, 512, 14336, 7), (130, 256, 1024, 2),
+    # up to 8 splits meet in distributed shared memory (one cluster per tile), more go through the global scratch buffer
+    (20, 320, 2048, 3), (64, 256, 4096, 16), (100, 4096, 4096, 4), (64, 6144, 4096, 3), (7, 384, 1536, 6),
 ])
 def test_fp8_gemm_matches_reference(m, n, k, splits):
     require_gpu_lib()
