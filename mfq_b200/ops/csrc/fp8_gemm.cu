@@ -303,25 +303,32 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // This one thread's loop is the pace of a weight-streaming CTA whose tiles are already in shared memory, so it
+      // carries no work that can be left out: descriptors advance by a constant per stage (the ring is contiguous and
+      // stays inside the 14-bit address field), a fresh accumulator is not waited for, and a stage that no later K
+      // block reuses is not handed back.
       constexpr uint32_t idesc = umma_idesc(kTileN, BT, 0, 0);
+      constexpr uint64_t kStageStep = uint64_t(Cfg::kStageBytes >> 4);
+      const uint64_t a_desc0 = umma_desc_k_sw128(smem_u32(tiles));
+      const uint64_t b_desc0 = umma_desc_k_sw128(smem_u32(tiles) + kTileN * kBlockK);
       int s = 0;
       uint32_t ring_phase = 0;
       for (int i = 0; i < nkb; ++i, s = (s + 1 == stages ? 0 : s + 1), ring_phase ^= (s == 0 ? 1u : 0u)) {
         const int buf = i % Cfg::kAcc;
-        if (!mbar_wait(&acc_empty[buf], ((i / Cfg::kAcc) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutMma)) break;
+        if (i >= Cfg::kAcc &&
+            !mbar_wait(&acc_empty[buf], ((i / Cfg::kAcc) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutMma)) break;
         if (!mbar_wait(&full[s], ring_phase, abort_flag, p.status, kStatusTimeoutMma)) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(tiles + s * Cfg::kStageBytes);
-        const uint64_t a_desc = umma_desc_k_sw128(a_addr);
-        const uint64_t b_desc = umma_desc_k_sw128(a_addr + kTileN * kBlockK);
+        const uint64_t a_desc = a_desc0 + uint64_t(s) * kStageStep;
+        const uint64_t b_desc = b_desc0 + uint64_t(s) * kStageStep;
         const uint32_t d = tmem_base + buf * BT;
 #pragma unroll
         for (int k = 0; k < kBlockK / 32; ++k) {
           // advancing 32 bytes along K inside the swizzle row = +2 in the 16-byte address field
           umma_f8f6f4(d, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2), idesc, k > 0 ? 1u : 0u);
         }
-        tc_commit(&empty[s]);      // smem stage reusable once these MMAs have read it
-        tc_commit(&acc_full[buf]); // accumulator block complete
+        if (i + stages < nkb) tc_commit(&empty[s]);  // smem stage reusable once these MMAs have read it
+        tc_commit(&acc_full[buf]);                   // accumulator block complete
       }
     }
   } else {
