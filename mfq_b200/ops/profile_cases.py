@@ -171,6 +171,7 @@ def packed_decode(tokens: int = 64) -> None:
 
 
 CASES = {"gemm_prefill": lambda: gemm(4096, 4096, 4096), "gemm_decode": lambda: gemm(64, 28672, 4096),
+         "gemm_decode_splitk": lambda: gemm(64, 4096, 14336),
          "attn_decode": attn_decode, "attn_prefill": attn_prefill, "w4_decode": lambda: w4_gemm(64, 28672, 4096),
          "w4_prefill": lambda: w4_gemm(4096, 4096, 4096), "gdn_decode": gdn_decode, "moe_dispatch": moe_dispatch,
          "gemv_decode": lambda: gemm(1, 28672, 4096), "packed_decode": packed_decode, "packed_decode_bs1": lambda: packed_decode(1), "attn_prefill_d256": attn_prefill_d256, "gdn_prefill": gdn_prefill, "mla_decode": mla_decode}
