@@ -154,26 +154,46 @@ class MlaModel(MoeDecoderModel):
         q_rope = ref.rope(q[:, :, nope:], step.positions, cfg.rope_theta, rope, self.rope_scaling)
         mla_ops.latent_write(torch.cat([k_rope, c_n], 1), step.slots, kv)
         if prefill:
-            if step.past_len > 0:
-                raise NotImplementedError("a prefill chunk after cached tokens needs keys expanded from cached latents: "
-                                          "use one chunk per prompt with the latent cache")
-            kvb = m.kv_b(*self._quant(c_n)).view(t, hq, nope + vd)
+            past = step.past_len
+            rows_k, rows_c = k_rope, c_n
+            if past > 0:
+                # A chunk after cached tokens: the past rows come back from the latent cache (the FP8 values that decode
+                # steps will read) and their per-head keys and values are expanded again -- the cache never holds them.
+                from ..engine.kv_cache import k_logical
+                pages = step.block_table[0][: (past + kv.page_size - 1) // kv.page_size].long()
+                cached = k_logical(kv.k[pages]).float() * kv.k_scale[pages][..., None]  # [pages, 1, 16, 576]
+                cached = cached.reshape(-1, rope + lat)[:past].to(torch.bfloat16)
+                rows_k = torch.cat([cached[:, :rope], k_rope], 0)
+                rows_c = torch.cat([cached[:, rope:], c_n], 0)
+            tk = rows_c.shape[0]
+            kvb = m.kv_b(*self._quant(rows_c.contiguous())).view(tk, hq, nope + vd)
             qh = torch.zeros((t, hq, PADDED_HEAD), dtype=torch.bfloat16, device=h.device)
-            kh, vh = torch.zeros_like(qh), torch.zeros_like(qh)
+            kh = torch.zeros((tk, hq, PADDED_HEAD), dtype=torch.bfloat16, device=h.device)
+            vh = torch.zeros_like(kh)
             qh[:, :, :rope], qh[:, :, rope : rope + nope] = q_rope, q[:, :, :nope]
-            kh[:, :, :rope], kh[:, :, rope : rope + nope] = k_rope[:, None, :], kvb[:, :, :nope]
+            kh[:, :, :rope], kh[:, :, rope : rope + nope] = rows_k[:, None, :], kvb[:, :, :nope]
             vh[:, :, :vd] = kvb[:, :, nope:]
-            o = ops.attn_prefill(qh, kh, vh, step.cu_seqlens, self.sm_scale)
+            if past > 0:
+                o = ops.kernels.attn_prefill_bf16(qh, kh, vh, self.sm_scale)
+            else:
+                o = ops.attn_prefill(qh, kh, vh, step.cu_seqlens, self.sm_scale)
             return o.view(t, hq, PADDED_HEAD)[:, :, :vd].reshape(t, hq * vd)
+        block_table, seq_lens = step.block_table, step.seq_lens
         if step.q_len != 1:
-            raise NotImplementedError("verify windows over the latent cache are not built")
+            # A window of w query tokens per sequence (speculative verification): every window position becomes a row
+            # of its own over the same pages, seeing the context up to itself -- the window's latent rows are in the
+            # cache already, so causality is a matter of row lengths.
+            w = step.q_len
+            back = torch.arange(w - 1, -1, -1, dtype=seq_lens.dtype, device=seq_lens.device)
+            seq_lens = (seq_lens[:, None] - back[None, :]).reshape(-1).contiguous()
+            block_table = block_table.repeat_interleave(w, 0).contiguous()
         key = ("bf16", id(layer))
         if key not in self._absorb:
             wk, wv = self._absorbed_weights(layer)
             self._absorb[key] = (wk.to(torch.bfloat16).contiguous(), wv.transpose(1, 2).to(torch.bfloat16).contiguous())
         wk, wv_t = self._absorb[key]  # [Hq, nope, latent], [Hq, latent, v]
         q_abs = torch.bmm(q[:, :, :nope].transpose(0, 1), wk).transpose(0, 1)  # [T, Hq, latent]
-        o_lat = mla_ops.decode(torch.cat([q_rope, q_abs], -1), kv, step.block_table, step.seq_lens, sm_scale=self.sm_scale,
+        o_lat = mla_ops.decode(torch.cat([q_rope, q_abs], -1), kv, block_table, seq_lens, sm_scale=self.sm_scale,
                                splits=getattr(self, "attn_splits", 1) or 1)
         return torch.bmm(o_lat.transpose(0, 1), wv_t).transpose(0, 1).reshape(t, hq * vd)
 

@@ -164,3 +164,49 @@ def test_latent_cache_model_matches_cpu_and_decodes_under_graphs():
     check_status()
     eager = LLMEngine(MlaModel(cfg, gpu.model.w), max_batch=4, max_seq_len=160, use_graphs=False)
     assert torch.equal(eager.generate(prompts, 8).tokens, toks)
+
+
+def test_latent_cache_chunked_prefill_and_verify_window():
+    """A prompt prefilled in chunks (later chunks attend to latents read back from the cache) and a three-token verify
+    window over the latent cache, each against the CPU restatement of the same call."""
+    require_gpu_lib()
+    cfg = _latent_cfg()
+    w_cpu = random_mla_weights(cfg, "cpu", seed=6, std=0.05, expert_chunk=3)
+    gpu = LLMEngine(MlaModel(cfg, _to(w_cpu, "cuda")), max_batch=2, max_seq_len=160, prefill_chunk=16, use_graphs=False)
+    whole = LLMEngine(MlaModel(cfg, gpu.model.w), max_batch=2, max_seq_len=160, use_graphs=False)
+    cpu = LLMEngine(MlaModel(cfg, w_cpu), max_batch=2, max_seq_len=160, device="cpu")
+    prompt = torch.randint(0, cfg.vocab_size, (45,), generator=torch.Generator().manual_seed(8))
+
+    def chunked_logits(eng, dev, chunk):
+        n = prompt.numel()
+        eng.cache.assign(0, 321, n + 4)
+        last = None
+        for a in range(0, n, chunk):
+            b = min(n, a + chunk)
+            step = StepBuffers(input_ids=prompt[a:b].to(dev, torch.int32), positions=torch.arange(a, b, dtype=torch.int32, device=dev),
+                               slots=eng.cache.slots(321, a, b - a).to(dev), cu_seqlens=[0, b - a], past_len=a,
+                               block_table=eng.cache.block_table[:1])
+            last = eng.model.forward(step, eng.cache, prefill=True).float().cpu()
+        return last, n
+
+    lc, n = chunked_logits(gpu, "cuda", 16)
+    lw, _ = chunked_logits(whole, "cuda", 64)
+    check_status()
+    cos = float(torch.nn.functional.cosine_similarity(lc.flatten(), lw[-lc.shape[0]:].flatten(), dim=0))
+    assert cos > 0.995, cos  # the past seen through its FP8 cache rows instead of the bf16 values of the same chunk
+    lr, _ = chunked_logits(cpu, "cpu", 16)
+    cos = float(torch.nn.functional.cosine_similarity(lc.flatten(), lr.flatten(), dim=0))
+    assert cos > 0.99, cos
+
+    # three-token window after the prompt (rows 0 of both engines still hold it)
+    def window(eng, dev):
+        toks = torch.tensor([7, 300, 41], dtype=torch.int32, device=dev)
+        step = StepBuffers(input_ids=toks, positions=torch.arange(n, n + 3, dtype=torch.int32, device=dev),
+                           slots=eng.cache.slots(321, n, 3).to(dev), block_table=eng.cache.block_table[:1],
+                           seq_lens=torch.tensor([n + 3], dtype=torch.int32, device=dev), q_len=3)
+        return eng.model.forward(step, eng.cache, prefill=False, gather_logits=False).float().cpu()
+    wg, wc = window(gpu, "cuda"), window(cpu, "cpu")
+    check_status()
+    assert wg.shape == wc.shape and wg.shape[0] == 3
+    cos = float(torch.nn.functional.cosine_similarity(wg.flatten(), wc.flatten(), dim=0))
+    assert cos > 0.99 and float((wg - wc).abs().mean()) <= 0.03 * float(wc.abs().max()), cos
