@@ -95,6 +95,7 @@ class LLMEngine:
         # repetition f32, seed u64 (the layout the sampling kernel reads)
         self.sample_rows = torch.zeros((max_batch, 8), dtype=torch.int32, device=dev)
         self.sample_work: torch.Tensor | None = None
+        self.verify_work: torch.Tensor | None = None  # scratch of the speculative verification draw
         self.use_graphs = use_graphs and dev.type == "cuda"
         self.graphs: dict[tuple[int, bool, int], torch.cuda.CUDAGraph] = {}
         self.launches_per_step: dict[int, int] = {}
@@ -540,8 +541,62 @@ class LLMEngine:
             self.model.sample_greedy(logits, out=tok)
             self.draft[r0:r1, j - 1].copy_(tok)
 
-    def _mtp_body(self, b: int, depth: int | None = None, next_depth: int | None = None) -> None:
-        """One cycle verifying ``depth`` drafts (default K) and leaving ``next_depth`` drafts for the following one."""
+    def _verify_targets(self, logits: torch.Tensor, draft: torch.Tensor, b: int, w: int) -> torch.Tensor:
+        """The token every window position emits under the rows' sampling parameters (speculative sampling with the
+        deterministic proposal of the draft head: a draft is kept with its target probability, otherwise replaced by a
+        draw from the target distribution without it, so the emitted tokens follow the target distribution exactly;
+        greedy rows get the arg-max).  ``logits [b * w, V]``, ``draft [b, w - 1]``; returns ``targets [b * w]``."""
+        if self.model.tp > 1:
+            logits = self.model.collective.gather_columns(logits)
+        out = self.targets[: b * w]
+        v = logits.shape[1]
+        if not logits.is_cuda:
+            return self._verify_targets_reference(logits, draft, b, w, out)
+        if self.verify_work is None or self.verify_work.shape[1] != v:
+            self.verify_work = torch.empty((self.max_batch * (self.mtp_k + 1), v), dtype=torch.float32, device=self.device)
+        fn = ops.lib.lib().mfq_sample_verify
+        fn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 6
+        fn.restype = C.c_int
+        rc = fn(logits.data_ptr(), b, w, v, logits.stride(0), self.sample_rows.data_ptr(), self.seq_lens.data_ptr(),
+                draft.data_ptr(), self.verify_work.data_ptr(), out.data_ptr(), ops.lib.stream_ptr())
+        ops.lib.check(rc, "sample_verify")
+        return out
+
+    def _verify_targets_reference(self, logits, draft, b: int, w: int, out: torch.Tensor) -> torch.Tensor:
+        for r in range(b):
+            rec = self.sample_rows[r].cpu()
+            temp, top_p = rec[:1].view(torch.float32).item(), rec[2:3].view(torch.float32).item()
+            top_k = int(rec[1])
+            for i in range(w):
+                l = logits[r * w + i].float()
+                if temp <= 0:
+                    out[r * w + i] = int(l.argmax())
+                    continue
+                l = l / temp
+                if 0 < top_k < l.numel():
+                    l = l.masked_fill(l < l.topk(top_k).values[-1], float("-inf"))
+                p = torch.softmax(l, -1)
+                if top_p < 1:
+                    sp, si = p.sort(descending=True)
+                    keep = (sp.cumsum(0) - sp) < top_p
+                    mask = torch.zeros_like(p, dtype=torch.bool).scatter_(0, si[keep], True)
+                    p = torch.where(mask, p, torch.zeros_like(p))
+                p = p / p.sum()
+                g = torch.Generator().manual_seed(int(rec[6:8].view(torch.int64)) + int(self.seq_lens[r]) + i)
+                if i < w - 1:
+                    x = int(draft[r, i])
+                    if float(torch.rand((), generator=g)) < float(p[x]):
+                        out[r * w + i] = x
+                        continue
+                    p = p.clone()
+                    p[x] = 0
+                    p = p / p.sum()
+                out[r * w + i] = int(torch.multinomial(p, 1, generator=g))
+        return out
+
+    def _mtp_body(self, b: int, depth: int | None = None, next_depth: int | None = None, stochastic: bool = False) -> None:
+        """One cycle verifying ``depth`` drafts (default K) and leaving ``next_depth`` drafts for the following one.
+        ``stochastic``: rows with a temperature verify by speculative sampling instead of arg-max comparison."""
         from ..ops import mtp as mtp_ops
         k = self.mtp_k if depth is None else depth
         next_depth = k if next_depth is None else next_depth
@@ -562,7 +617,10 @@ class LLMEngine:
         step = StepBuffers(input_ids=ids, positions=pos, slots=slots, block_table=table, seq_lens=lens, q_len=w,
                            state_slots=state_slots, verify=self.rec_state is not None)
         logits, hidden = self.model.forward(step, self.cache, prefill=False, gather_logits=False, return_hidden=True)
-        targets = self.model.sample_greedy(logits, out=self.targets[: b * w])
+        if stochastic:
+            targets = self._verify_targets(logits, draft, b, w)
+        else:
+            targets = self.model.sample_greedy(logits, out=self.targets[: b * w])
         # the head sees the TRUE successor of every window position, so whatever prefix is accepted its KV rows and
         # its prediction at the last confirmed position are exact
         mstep = StepBuffers(input_ids=targets, positions=pos, slots=slots, block_table=table, seq_lens=lens, q_len=w)
@@ -577,7 +635,7 @@ class LLMEngine:
         if next_depth > 1:
             self._mtp_chain(0, b, mtp_ops.select_rows(mhid, self.accept_row[:b], w), depth=next_depth)
 
-    def mtp_step(self, b: int) -> None:
+    def mtp_step(self, b: int, stochastic: bool = False) -> None:
         """One draft/verify cycle for the active rows among ``[0, b)``: confirms ``n_out[r]`` in 1..K+1 tokens per
         row (``out_tokens[r, :n_out[r]]``), all state stays on the device (one CUDA graph per batch bucket)."""
         self.mtp_cycles += 1
@@ -586,9 +644,9 @@ class LLMEngine:
         nxt = self.depth_controller.next_depth() if self.depth_controller is not None else depth
         self.last_depth, self.mtp_depth = depth, nxt
         if not self.use_graphs:
-            self._mtp_body(b, depth, nxt)
+            self._mtp_body(b, depth, nxt, stochastic)
             return
-        key = (b, depth, nxt)
+        key = (b, depth, nxt) + ((True,) if stochastic else ())
         g = self.mtp_graphs.get(key)
         if g is None:
             ops.Workspace.get(self.device)
@@ -598,12 +656,12 @@ class LLMEngine:
             saved_rec = (self.rec_state.conv.clone(), self.rec_state.state.clone()) if self.rec_state is not None else None
             with torch.cuda.stream(side):
                 for _ in range(2):
-                    self._mtp_body(b, depth, nxt)
+                    self._mtp_body(b, depth, nxt, stochastic)
             torch.cuda.current_stream().wait_stream(side)
             g = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             with torch.cuda.graph(g):
-                self._mtp_body(b, depth, nxt)
+                self._mtp_body(b, depth, nxt, stochastic)
             self.launches_per_step[("mtp", b) if depth == nxt == self.mtp_k else ("mtp", b, depth, nxt)] = ops.launch_count() - before
             for dst, src in zip((self.seq_lens, self.sampled, self.draft, self.mtp_counters), saved):
                 dst.copy_(src)
@@ -662,18 +720,19 @@ class LLMEngine:
         constrained = any(r in self.row_constraint for r in rows)
         if constrained:
             self._write_bias(range(b))
-        if self.mtp_k and not constrained and not any(self.row_stochastic.get(r, False) for r in rows):
+        stochastic = any(self.row_stochastic.get(r, False) for r in rows)
+        if self.mtp_k and not constrained:
             ctl = self.mtp_controller
             mode = ctl.mode() if ctl is not None else "mtp"
             t0 = time.perf_counter()
             if mode == "plain":  # parked: one token per row, the head kept primed
-                self.decode_step(b, False, False, keep_head=True)
+                self.decode_step(b, stochastic, False, keep_head=True)
                 toks = self.sampled[:b].cpu()
                 for r in rows:
                     self.row_len[r] += 1
                 ctl.observe("plain", len(rows), len(rows), (time.perf_counter() - t0) * 1e3)
                 return {r: [int(toks[r])] for r in rows}
-            self.mtp_step(b)
+            self.mtp_step(b, stochastic)
             toks, counts = (t.cpu() for t in self.mtp_result(b))
             out = {}
             for r in rows:
@@ -687,7 +746,7 @@ class LLMEngine:
                 accepted = sorted(len(v) - 1 for v in out.values())[len(out) // 2]
                 self.depth_controller.observe(self.last_depth, accepted, ms)
             return out
-        self.decode_step(b, any(self.row_stochastic.get(r, False) for r in rows), constrained)
+        self.decode_step(b, stochastic, constrained)
         toks = self.sampled[:b].cpu()
         for r in rows:
             self.row_len[r] += 1

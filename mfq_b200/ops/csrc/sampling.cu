@@ -49,14 +49,24 @@ __device__ __forceinline__ float uniform01(unsigned long long seed, unsigned lon
 
 // logits [B, V] bf16 (row stride `stride`); counts [B, V] uint16 occurrences of each token in the row's sequence
 // (may be null); work [B, V] fp32 scratch; out [B] sampled ids; steps [B] per-row draw counter (read only).
+//
+// Speculative verification (`window` > 1, `draft` given): the B rows are `window` consecutive positions of B / window
+// sequences; `rows` / `steps` are per SEQUENCE, position i draws with counter steps[seq] + i.  Positions 0 .. window-2
+// carry a draft token x = draft[seq][i] that was proposed deterministically (the draft head's arg-max), i.e. from a
+// one-hot proposal, so speculative sampling keeps it with probability p(x) under this row's processed target
+// distribution and otherwise draws from p with x removed -- the emitted token is then distributed exactly as p.  The
+// last position has no draft and is a plain draw.  Greedy rows return the arg-max either way, so comparing `out` with
+// the draft (what the accept kernel does) is the verification in both modes.
 __global__ void __launch_bounds__(1024)
 sample_kernel(const __nv_bfloat16* __restrict__ logits, int V, int stride, const unsigned short* __restrict__ counts,
               const SampleRow* __restrict__ rows, const int* __restrict__ steps, float* __restrict__ work,
-              int* __restrict__ out) {
+              int* __restrict__ out, int window, const int* __restrict__ draft) {
   __shared__ float red[32];
   __shared__ float s_scan[33];
   const int b = blockIdx.x, tid = threadIdx.x;
-  const SampleRow r = rows[b];
+  const int seq = b / window, pos = b - seq * window;
+  const SampleRow r = rows[seq];
+  const int x = (draft && pos < window - 1) ? draft[seq * (window - 1) + pos] : -1;
   const __nv_bfloat16* lr = logits + size_t(b) * stride;
   float* w = work + size_t(b) * V;
   const unsigned short* cr = counts ? counts + size_t(b) * V : nullptr;
@@ -123,13 +133,13 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, int V, int stride, const
     }
     cut = lo;
   }
-  float kept = 0.f;
-  for (int i = tid; i < V; i += blockDim.x) kept += w[i] >= cut ? __expf(w[i] - gmax) : 0.f;
-  // ---- draw: inverse CDF over index order; each thread owns a contiguous slice ----
+  // mass of the draft token inside the kept set (0: no draft, or the cuts removed it -> it can only be rejected)
+  const float e_x = (x >= 0 && x < V && w[x] >= cut) ? __expf(w[x] - gmax) : 0.f;
+  // ---- draw: inverse CDF over index order, the draft token left out; each thread owns a contiguous slice ----
   const int per = (V + blockDim.x - 1) / blockDim.x;
   const int i0 = tid * per, i1 = min(V, i0 + per);
   float mine = 0.f;
-  for (int i = i0; i < i1; ++i) mine += w[i] >= cut ? __expf(w[i] - gmax) : 0.f;
+  for (int i = i0; i < i1; ++i) mine += (w[i] >= cut && i != x) ? __expf(w[i] - gmax) : 0.f;
   // block exclusive scan of `mine`
   float incl = mine;
 #pragma unroll
@@ -146,15 +156,23 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, int V, int stride, const
     s_scan[32] = run;
   }
   __syncthreads();
-  const float total = s_scan[32];
+  const float total = s_scan[32];  // without the draft token
+  const unsigned long long step = (unsigned long long)(steps[seq] + pos);
+  if (x >= 0) {
+    // keep the draft with probability p(x) = e_x / (total + e_x); every thread takes the same branch
+    const float ua = uniform01(r.seed ^ 0x5DEECE66Dull, step);
+    if (ua * (total + e_x) < e_x || total <= 0.f) {
+      if (tid == 0) out[b] = x;
+      return;
+    }
+  }
   const float before = s_scan[tid >> 5] + incl - mine;
-  const float target = uniform01(r.seed, (unsigned long long)steps[b]) * total;
-  (void)kept;
+  const float target = uniform01(r.seed, step) * total;
   if (target >= before && (target < before + mine || (tid == blockDim.x - 1))) {
     float run = before;
     int pick = -1;
     for (int i = i0; i < i1; ++i) {
-      if (w[i] >= cut) {
+      if (w[i] >= cut && i != x) {
         run += __expf(w[i] - gmax);
         pick = i;
         if (run > target) break;
@@ -172,6 +190,18 @@ extern "C" int mfq_sample(const void* logits, int B, int V, int stride, const vo
   if (B <= 0 || V <= 0) return -1;
   mfq::sample_kernel<<<B, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), V, stride,
                                              static_cast<const unsigned short*>(counts),
-                                             static_cast<const mfq::SampleRow*>(rows), steps, work, out);
+                                             static_cast<const mfq::SampleRow*>(rows), steps, work, out, 1, nullptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+// Verification draw for speculative decoding: logits [B * window, V] (window consecutive positions per sequence), rows /
+// steps [B] per sequence, draft [B, window - 1] proposed tokens; out [B * window] = the token each position emits (the
+// draft where it was kept).  See sample_kernel.
+extern "C" int mfq_sample_verify(const void* logits, int B, int window, int V, int stride, const void* rows, const int* steps,
+                                 const int* draft, float* work, int* out, cudaStream_t stream) {
+  if (B <= 0 || V <= 0 || window < 1) return -1;
+  mfq::sample_kernel<<<B * window, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), V, stride, nullptr,
+                                                      static_cast<const mfq::SampleRow*>(rows), steps, work, out, window,
+                                                      window > 1 ? draft : nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }

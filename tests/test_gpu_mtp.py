@@ -81,3 +81,46 @@ def test_mtp_cycles_match_plain_greedy(k):
     assert eng.out_tokens[0, :n].tolist() == truth[1 : 1 + n] and n >= max(1, k)
     check_status()
     assert eng.mtp_stats()["drafted"] > 0
+
+
+def test_verification_draw_follows_the_target_distribution():
+    """The sampling kernel in verification mode: 6000 sequences x 3 window positions with one set of logits -- the emitted
+    token is distributed as the processed target distribution whatever the draft is, a draft is kept exactly as often as
+    the target would have emitted it, and greedy rows return the arg-max."""
+    import ctypes as C
+    from mfq_b200 import ops
+    require_gpu_lib()
+    b, w, v = 6000, 3, 512
+    base = torch.full((v,), -9.0)
+    base[:6] = torch.tensor([2.0, 1.5, 1.0, 0.5, 0.0, -0.5])
+    logits = base.to(torch.bfloat16).repeat(b * w, 1).cuda()
+    temp, top_k = 0.8, 5
+    p = torch.softmax(base[:5] / temp, -1)
+    rec = torch.zeros((b, 8), dtype=torch.int32)
+    rec[:, 0] = torch.tensor([temp]).view(torch.int32)[0]
+    rec[:, 1] = top_k
+    rec[:, 2] = torch.tensor([1.0]).view(torch.int32)[0]
+    rec[:, 5] = torch.tensor([1.0]).view(torch.int32)[0]
+    rec[:, 6:8] = torch.arange(1, b + 1, dtype=torch.int64).mul(7919).view(-1, 1).view(torch.int32).view(b, 2)
+    rec[-100:, 0] = 0  # the last hundred sequences are greedy
+    rows = rec.cuda()
+    steps = torch.randint(1, 1000, (b,), dtype=torch.int32).cuda()
+    draft = torch.tensor([[0, 3]], dtype=torch.int32).repeat(b, 1).cuda()  # a likely draft, then an unlikely one
+    work = torch.empty((b * w, v), dtype=torch.float32, device="cuda")
+    out = torch.empty(b * w, dtype=torch.int32, device="cuda")
+    fn = ops.lib.lib().mfq_sample_verify
+    fn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 6
+    fn.restype = C.c_int
+    assert fn(logits.data_ptr(), b, w, v, logits.stride(0), rows.data_ptr(), steps.data_ptr(), draft.data_ptr(),
+              work.data_ptr(), out.data_ptr(), ops.lib.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    got = out.cpu().view(b, w)
+    assert (got[-100:] == 0).all()
+    s = got[:-100]
+    n = s.shape[0]
+    for pos, x in ((0, 0), (1, 3), (2, None)):
+        freq = torch.bincount(s[:, pos], minlength=v).float() / n
+        assert float(freq[5:].sum()) == 0.0
+        assert float((freq[:5] - p).abs().max()) < 0.025, (pos, freq[:5].tolist(), p.tolist())
+    # positions draw independently of each other (distinct counters)
+    assert float(((s[:, 0] == s[:, 2]).float().mean() - float((p * p).sum())).abs()) < 0.03

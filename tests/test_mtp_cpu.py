@@ -172,3 +172,56 @@ def test_dynamic_depth_is_lossless_and_visits_every_depth():
     assert min(_agree(plain[r].tolist(), got[r][:14]) for r in range(2)) >= 0.75
     st = eng.depth_controller.state()
     assert all(ms is not None for ms in st["cycle_ms"][1:])
+
+
+def test_stochastic_verification_follows_the_target_distribution():
+    """Speculative sampling with the draft head's deterministic proposal: whatever the draft token is, the emitted token
+    is distributed as the (temperature / top-k processed) target distribution."""
+    cfg, eng = _engine(2, max_batch=1)
+    eng.set_sampling(0, SamplingParams(max_tokens=8, temperature=0.8, top_k=5, seed=123))
+    v = cfg.vocab_size
+    logits = torch.full((3, v), -9.0)
+    logits[:, :6] = torch.tensor([2.0, 1.5, 1.0, 0.5, 0.0, -0.5])  # the sixth falls to top-k
+    p = torch.softmax(logits[0, :5] / 0.8, -1)
+    for draft_tok in (0, 3, 5):  # a likely, an unlikely and an impossible draft
+        counts = torch.zeros(v)
+        kept = 0
+        n = 3000
+        for trial in range(n):
+            eng.seq_lens[0] = 10 + 3 * trial  # the draw counter: a fresh random number per trial and position
+            out = eng._verify_targets(logits, torch.tensor([[draft_tok, 1]], dtype=torch.int32), 1, 3)
+            counts[int(out[0])] += 1
+            kept += int(out[0]) == draft_tok
+        freq = counts[:5] / n
+        assert counts[5:].sum() == 0
+        assert float((freq - p).abs().max()) < 0.03, (draft_tok, freq.tolist(), p.tolist())
+        if draft_tok == 5:
+            assert kept == 0
+        else:
+            assert abs(kept / n - float(p[draft_tok])) < 0.03  # a draft is kept exactly as often as the target would emit it
+
+
+def test_stochastic_rows_decode_through_mtp_cycles():
+    def run():
+        cfg, eng = _engine(2, max_batch=2)
+        sched = ContinuousBatchScheduler(eng)
+        got = {}
+        for i, n in enumerate((7, 12)):
+            p = torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)).tolist()
+            r = Request(prompt=p, params=SamplingParams(max_tokens=10, temperature=0.9, top_p=0.9, seed=7 + i))
+            toks = got.setdefault(i, [])
+            def on_event(ev, toks=toks):
+                if ev.kind == "token":
+                    toks.append(ev.token if hasattr(ev, "token") else ev.data)
+                elif ev.kind == "completed":
+                    toks.append(("done", ev.metrics["completion_tokens"]))
+            r.on_event = on_event
+            sched.submit(r)
+        sched.run_until_idle()
+        return eng, got
+    eng, got = run()
+    assert all(v[-1] == ("done", 10) for v in got.values())
+    st = eng.mtp_stats()
+    assert st["cycles"] > 0 and st["drafted"] > 0  # the sampled rows went through draft/verify cycles, not plain steps
+    _, again = run()
+    assert again == got  # the same seeds replay the same tokens
