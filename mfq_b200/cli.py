@@ -170,8 +170,72 @@ def _alphaq_widths(tensors, target_bpw: float) -> dict[str, int]:
     return {name: int(fam[4:]) for name, fam in choice.items()}
 
 
+def _calibration_tokenizer(spec: str):
+    """``byte`` = the byte-level tokenizer; else a ``tokenizer.json`` file or a directory that holds one (its
+    ``tokenizer_config.json``, when present, supplies the chat template)."""
+    from .server.tokenizer import ByteTokenizer, HfTokenizer
+    if spec in ("", "byte"):
+        return ByteTokenizer()
+    p = Path(spec)
+    root = p if p.is_dir() else p.parent
+    blob = (root / "tokenizer.json" if p.is_dir() else p).read_bytes()
+    template = eos = None
+    if (root / "tokenizer_config.json").exists():
+        tc = json.loads((root / "tokenizer_config.json").read_text())
+        template, eos = tc.get("chat_template"), tc.get("eos_token") if isinstance(tc.get("eos_token"), str) else None
+    return HfTokenizer(blob, chat_template=template, eos_token=eos)
+
+
+def _cmd_calibrate_corpus(args) -> int:
+    from .calibration import dataset
+    tok = _calibration_tokenizer(args.tokenizer)
+    if args.calibrate_cmd == "data":
+        sources, files = {}, []
+        for item in args.source:
+            domain, _, path = item.rpartition("=")
+            path = Path(path)
+            files.append(path)
+            sources.setdefault(domain or path.stem, []).extend(dataset.read_records(path))
+        weights = {k: float(v) for k, v in (w.split("=") for w in args.domain_weight)} if args.domain_weight else None
+        corpus = dataset.build_text_corpus(tok, args.output, sources, train_tokens=args.train_tokens,
+                                           validation_tokens=args.validation_tokens, sequence_length=args.sequence_length,
+                                           seed=args.seed, render_mode=args.render_mode, domain_weights=weights, source_files=files)
+        event = "calibration_corpus_ready"
+    else:
+        rows, files = [], []
+        for f in args.source_file:
+            files.append(Path(f))
+            rows.extend(dataset.read_records(f))
+        corpus = dataset.build_trace_corpus(tok, args.output, rows, train_tokens=args.train_tokens,
+                                            validation_tokens=args.validation_tokens, sequence_length=args.sequence_length,
+                                            seed=args.seed, expected_generator_model=args.expected_generator_model or None,
+                                            source_files=files)
+        event = "trace_calibration_corpus_ready"
+    print(json.dumps({"event": event, "path": str(corpus.root), "train_tokens": corpus.token_count("train"),
+                      "validation_tokens": corpus.token_count("validation"), "windows": corpus.chunks,
+                      "token_sha256": corpus.manifest["token_sha256"]}))
+    return 0
+
+
 def _cmd_calibrate(args) -> int:
+    if args.calibrate_cmd in ("data", "trace-data"):
+        return _cmd_calibrate_corpus(args)
     cfg, tensors, _assets = _load_source(args)
+    if args.calibrate_cmd == "collect":
+        from .calibration.dataset import load_corpus
+        from .calibration.statistics import collect_statistics
+        from .models.moe_lm import MoeConfig
+        fields = MoeConfig.__dataclass_fields__
+        mcfg = MoeConfig(**{k: v for k, v in cfg.items() if k in fields})
+        stats = collect_statistics(mcfg, tensors, load_corpus(args.corpus), args.output, device=args.device,
+                                   train_input_tokens=args.train_input_tokens, validation_input_tokens=args.validation_input_tokens,
+                                   train_fisher_tokens=args.train_fisher_tokens, validation_fisher_tokens=args.validation_fisher_tokens,
+                                   window=args.input_window or None, seed=args.seed)
+        if args.imatrix_output:  # the input statistics in the form `mfq quantize --imatrix` reads
+            np.savez(Path(args.imatrix_output), **stats.as_imatrix("train"))
+        print(json.dumps({"event": "calibration_statistics_ready", "output": args.output, "tensors": len(stats.entries),
+                          "mean_scored_loss": stats.metadata.get("mean_scored_loss")}))
+        return 0
     if args.calibrate_cmd == "alphaq":
         from .calibration import alphaq
         from .quantize import presets
@@ -689,6 +753,35 @@ def build_parser() -> argparse.ArgumentParser:
     ci.add_argument("--chunks", type=int, default=4)
     ci.add_argument("--ctx", type=int, default=128)
     ci.add_argument("--seed", type=int, default=0)
+    cd = cs.add_parser("data", help="tokenize local text / JSONL records into a train + validation calibration corpus")
+    cd.add_argument("--source", action="append", required=True, metavar="[DOMAIN=]FILE",
+                    help="JSONL ({\"text\"} or {\"messages\"} per line) or plain text (paragraphs); repeatable")
+    cd.add_argument("--domain-weight", action="append", default=[], metavar="DOMAIN=W", help="share of a domain in both splits (default equal)")
+    cd.add_argument("--render-mode", choices=("auto", "plain"), default="auto", help="plain: never apply the chat template")
+    ct = cs.add_parser("trace-data", help="tokenize model-generated JSONL traces; only generated positions are scored")
+    ct.add_argument("--source-file", action="append", required=True)
+    ct.add_argument("--expected-generator-model", default="", help="reject rows whose `model` differs")
+    for p_ in (cd, ct):
+        p_.add_argument("--tokenizer", default="byte", help="tokenizer.json, a directory holding one, or `byte`")
+        p_.add_argument("--output", required=True, help="corpus directory to create")
+        p_.add_argument("--train-tokens", type=int, default=1 << 20)
+        p_.add_argument("--validation-tokens", type=int, default=1 << 17)
+        p_.add_argument("--sequence-length", type=int, default=2048)
+        p_.add_argument("--seed", type=int, default=0)
+        p_.set_defaults(fn=_cmd_calibrate)
+    cc = cs.add_parser("collect", help="activation second moments and row Fisher of every linear layer over a corpus")
+    cc.add_argument("input")
+    cc.add_argument("--corpus", required=True, help="directory written by `calibrate data` / `calibrate trace-data`")
+    cc.add_argument("--output", required=True, help=".npz statistics file to create")
+    cc.add_argument("--imatrix-output", default="", help="also write the input statistics as an importance matrix")
+    cc.add_argument("--device", default="cpu")
+    cc.add_argument("--input-window", type=int, default=0, help="truncate every window to this many tokens (0: whole windows)")
+    cc.add_argument("--train-input-tokens", type=int, default=1 << 16)
+    cc.add_argument("--validation-input-tokens", type=int, default=1 << 14)
+    cc.add_argument("--train-fisher-tokens", type=int, default=1 << 14)
+    cc.add_argument("--validation-fisher-tokens", type=int, default=1 << 12)
+    cc.add_argument("--seed", type=int, default=0)
+    cc.set_defaults(fn=_cmd_calibrate)
     def _candidate_args(p, target=True):
         p.add_argument("input")
         p.add_argument("--families", default="NINT2,NINT3,NINT4,NINT5,NINT6,NINT8", help="NINT families scored per expert matrix")
