@@ -207,7 +207,7 @@ def check_codecs() -> dict:
     w = _w()
     out, ok = {}, True
     limits = {"NINT2": 0.6, "NINT3": 0.3, "NINT4": 0.15, "NINT5": 0.08, "NINT6": 0.04, "NINT8": 0.02, "NVQ3": 0.5, "MXFP4": 0.2,
-              "FP8": 0.07, "NPQ0-S": 1.5, "NPQ0-L": 1.5}
+              "FP8": 0.07, "NPQ0-S": 1.5, "NPQ0-L": 1.5, "NVQ1-L": 1.2, "NVQ1-S": 1.2}
     for fam, lim in limits.items():
         t = quantize_matrix(w, parse_profiles(fam)[0])
         dtype, blob = F.pack_tensor(t)

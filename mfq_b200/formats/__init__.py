@@ -18,6 +18,9 @@ def dequantize(t):
     from .npq0 import Npq0Tensor, dequantize_npq0
     if isinstance(t, Npq0Tensor):
         return dequantize_npq0(t)
+    from .nvq1 import Nvq1Tensor, dequantize_nvq1
+    if isinstance(t, Nvq1Tensor):
+        return dequantize_nvq1(t)
     from .nint8zero import Nint8ZeroTensor, dequantize_nint8_zero
     if isinstance(t, Nint8ZeroTensor):
         return dequantize_nint8_zero(t)

@@ -45,7 +45,8 @@ class ExpertProfile:
             return self.nint.bpw(4096)
         if self.nvq is not None:
             return self.nvq.bpw(4096, out=4096)
-        return {"MXFP4": 4.25, "FP8": 8.0, "BF16": 16.0, "NPQ0-S": 0.84, "NPQ0-L": 1.0}[self.family]
+        return {"MXFP4": 4.25, "FP8": 8.0, "BF16": 16.0, "NPQ0-S": 0.84, "NPQ0-L": 1.0, "NVQ1-L": 1.55, "NVQ1-L-S4": 1.59,
+                "NVQ1-S": 1.34}[self.family]
 
 
 def parse_profiles(text: str) -> tuple[ExpertProfile, ...]:
@@ -60,7 +61,7 @@ def parse_profiles(text: str) -> tuple[ExpertProfile, ...]:
             out.append(ExpertProfile(name, nint=NintSpec(bits, gs, k)))
         elif name in _NVQ_FAMILIES:
             out.append(ExpertProfile(name, nvq=NvqSpec(_NVQ_FAMILIES[name])))
-        elif name in ("MXFP4", "FP8", "BF16", "NPQ0-S", "NPQ0-L"):
+        elif name in ("MXFP4", "FP8", "BF16", "NPQ0-S", "NPQ0-L", "NVQ1-L", "NVQ1-L-S4", "NVQ1-S"):
             out.append(ExpertProfile(name))
         else:
             raise ValueError(f"unsupported expert precision {name!r}")
@@ -88,6 +89,10 @@ def quantize_matrix(w, profile: ExpertProfile, device="cpu", importance=None):
     if profile.family in ("NPQ0-S", "NPQ0-L"):
         from ..formats.npq0 import quantize_npq0
         return quantize_npq0(np.asarray(w, dtype=np.float32), profile.family)
+    if profile.family.startswith("NVQ1-"):
+        from ..formats.nvq1 import quantize_nvq1
+        w = np.asarray(w, dtype=np.float32)
+        return quantize_nvq1(w, profile.family, axis=w.ndim - 2, importance=importance, device=str(device))
     if profile.family == "BF16":
         from ..formats.dense import to_bf16
         return to_bf16(np.asarray(w, dtype=np.float32))
