@@ -1,4 +1,4 @@
-"""Background jobs of the control API: quantize / evaluate / inspect / diagnose runs as child processes of the server.
+"""Background jobs of the control API: quantize / evaluate / benchmark / calibrate / inspect / diagnose runs as child processes of the server.
 
 A job is one ``mfq`` command line.  Its combined output goes to a log file whose tail the API returns; a job is stopped
 by signalling exactly the process the manager started (never by name).  Finished jobs stay listed until they are
@@ -16,7 +16,7 @@ import uuid
 from dataclasses import dataclass, field
 from pathlib import Path
 
-ALLOWED = ("quantize", "eval", "inspect", "diagnose", "calibrate", "solve-ew")
+ALLOWED = ("quantize", "eval", "inspect", "diagnose", "calibrate", "solve-ew", "bench", "optimize-layout", "wt2-reference")
 
 
 @dataclass
