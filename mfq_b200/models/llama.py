@@ -345,12 +345,25 @@ class LlamaModel:
             outs.append(ref.attention(q[a:b], kk, vv, self.sm_scale, causal_offset=0))
         return torch.cat(outs, 0)
 
+    def _self_prepared(self, lin, rows: int) -> bool:
+        """Whether ``lin`` takes bf16 rows and prepares its FP8 activations inside its own kernel: a few rows on one GPU
+        (``ops.fp8_gemv_act``) -- four kernels less per layer in a single-stream decode step, same bits."""
+        return (self.tp == 1 and isinstance(lin, Fp8Linear) and lin.q.is_cuda and lin.q.ndim == 2
+                and ops.act_gemv_ok(rows, lin.q.shape[0], lin.q.shape[1]))
+
     # -- feed-forward -------------------------------------------------------------------------------------------
     def _ffn(self, h, layer):
         """Dense SwiGLU block: ``h + down(silu(gate(x)) * up(x))`` with ``x = rmsnorm(h)``."""
+        rows = h.shape[0]
         with scope("ffn.gate_up", h.device):
-            gu = layer.gate_up(*self._in_norm(h, layer.mlp_norm, layer.gate_up))
+            if self._self_prepared(layer.gate_up, rows):
+                gu = ops.fp8_gemv_act(h, layer.gate_up.q, layer.gate_up.scale, ops.ACT_NORM, norm_w=layer.mlp_norm,
+                                      eps=self.cfg.rms_eps)
+            else:
+                gu = layer.gate_up(*self._in_norm(h, layer.mlp_norm, layer.gate_up))
         with scope("ffn.down", h.device):
+            if self._self_prepared(layer.down, rows) and gu.shape[1] == 2 * layer.down.q.shape[1]:
+                return ops.fp8_gemv_act(gu, layer.down.q, layer.down.scale, ops.ACT_SWIGLU, residual=h, out=h)
             return self._row_parallel(layer.down, *self._in_silu(gu, layer.down), h=h)
 
     # -- forward ------------------------------------------------------------------------------------------------
@@ -358,12 +371,19 @@ class LlamaModel:
         return ops.embed(ids, self.w.embed) if self.w.embed.is_cuda else self.w.embed[ids.long()].clone()
 
     def _block(self, h, layer, kv, step: StepBuffers, prefill: bool):
+        rows = h.shape[0]
         with scope("attn.qkv", h.device):
-            qkv = layer.qkv(*self._in_norm(h, layer.attn_norm, layer.qkv))
+            if self._self_prepared(layer.qkv, rows):
+                qkv = ops.fp8_gemv_act(h, layer.qkv.q, layer.qkv.scale, ops.ACT_NORM, norm_w=layer.attn_norm, eps=self.cfg.rms_eps)
+            else:
+                qkv = layer.qkv(*self._in_norm(h, layer.attn_norm, layer.qkv))
         with scope("attn.core", h.device):
             attn = self._attention(qkv, kv, step, prefill)
         with scope("attn.o_proj", h.device):
-            h = self._row_parallel(layer.o_proj, *self._in_plain(attn, layer.o_proj), h=h)
+            if self._self_prepared(layer.o_proj, rows) and attn.is_contiguous():
+                h = ops.fp8_gemv_act(attn, layer.o_proj.q, layer.o_proj.scale, ops.ACT_PLAIN, residual=h, out=h)
+            else:
+                h = self._row_parallel(layer.o_proj, *self._in_plain(attn, layer.o_proj), h=h)
         return self._ffn(h, layer)
 
     def _head(self, h, norm, gather_logits: bool):

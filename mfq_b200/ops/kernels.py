@@ -131,6 +131,34 @@ def rmsnorm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, *, residual
     return q_out, scale_out, y_out, residual_out
 
 
+ACT_GEMV_MAX_ROWS = 4  # rows up to which a projection rebuilds its FP8 activations itself (fp8_gemv_act_kernel)
+ACT_NORM, ACT_PLAIN, ACT_SWIGLU = 0, 1, 2
+
+
+def act_gemv_ok(m: int, n: int, k: int) -> bool:
+    """Whether ``fp8_gemv_act`` takes this shape: a handful of rows, rows of at most 16384 values (64 KB of FP8 rows
+    in shared memory), and the standalone norm kernel's layout must be one this kernel can replay (<= 512 threads)."""
+    return gemv_enabled() and 0 < m <= ACT_GEMV_MAX_ROWS and n % 16 == 0 and k % 128 == 0 and k <= 16384
+
+
+def fp8_gemv_act(x: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor, mode: int, *, norm_w: torch.Tensor | None = None,
+                 eps: float = 0.0, residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out = W . quant(prep(x))`` (+ residual) for up to 4 bf16 rows, the preparation -- RMSNorm * ``norm_w``
+    (``ACT_NORM``), nothing (``ACT_PLAIN``) or ``silu(x[:, :K]) * x[:, K:]`` (``ACT_SWIGLU``) -- and the per-row FP8
+    quantization done inside the product kernel, bit-identical to the standalone kernels followed by ``fp8_gemm``'s
+    weight-streaming path."""
+    m = x.shape[0]
+    n, k = w_q.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.shape[1] == (2 * k if mode == ACT_SWIGLU else k)
+    assert act_gemv_ok(m, n, k) and (mode != ACT_NORM or norm_w is not None)
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    rc = lib().mfq_fp8_gemv_act(ptr(w_q), ptr(w_scale), ptr(x), x.stride(0), ptr(norm_w), float(eps), ptr(out), ptr(residual),
+                                m, n, k, mode, stream_ptr())
+    check(rc, "fp8_gemv_act")
+    return out
+
+
 def quant_rows(x: torch.Tensor, *, q_out=None, scale_out=None):
     m, k = x.shape
     q_out = torch.empty((m, k), dtype=FP8, device=x.device) if q_out is None else q_out

@@ -45,6 +45,7 @@ _SIGNATURES = {
     "mfq_mtp_select_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "mfq_nvq_assign": [_vp, _vp, _vp, _vp, _vp, C.c_longlong, _i, _i, _vp],
     "mfq_fp8_gemv": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "mfq_fp8_gemv_act": [_vp, _vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _i, _vp],
     "mfq_fp8_gemv_grouped": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp],
     "mfq_attn_prefill_d256": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp, _vp],
     "mfq_attn_prefill_bf16": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp, _vp],

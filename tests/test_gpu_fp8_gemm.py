@@ -96,3 +96,36 @@ def test_fp8_gemm_on_sm_pairs_matches_reference(m, n, k, tile):
     assert_close(got, ref.fp8_gemm(xq, xs, wq, ws, residual=res), what=f"pair gemm {m}x{n}x{k} tile {tile}")
     again = ops.fp8_gemm(xq, xs, wq, ws, pair=tile, residual=res)
     assert torch.equal(got, again)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 6144, 4096), (3, 256, 2048), (4, 4096, 8192), (2, 512, 1024), (1, 4096, 14336)])
+def test_gemv_with_folded_activation_preparation_is_bit_identical(m, n, k):
+    """RMSNorm + quantization, plain quantization and SwiGLU + quantization done inside the product kernel give the bits
+    of the standalone kernels followed by the weight-streaming product (the sum of squares replays the norm kernel's
+    summation tree), with and without an in-place residual."""
+    require_gpu_lib()
+    g = torch.Generator(device="cuda").manual_seed(m * 31 + n)
+    w = (torch.randn((n, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    wq, ws = quantize_fp8_block_torch(w)
+    x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(k, generator=g, device="cuda")).to(torch.bfloat16)
+    res = torch.randn((m, n), generator=g, device="cuda").to(torch.bfloat16)
+    # norm
+    xq, xs, _, _ = ops.rmsnorm_quant(x, nw, 1e-5)
+    want = ops.fp8_gemm(xq, xs, wq, ws)
+    got = ops.fp8_gemv_act(x, wq, ws, ops.ACT_NORM, norm_w=nw, eps=1e-5)
+    assert torch.equal(got, want), float((got.float() - want.float()).abs().max())
+    # plain, residual added in place
+    xq, xs = ops.quant_rows(x)
+    want = ops.fp8_gemm(xq, xs, wq, ws, residual=res)
+    h = res.clone()
+    ops.fp8_gemv_act(x, wq, ws, ops.ACT_PLAIN, residual=h, out=h)
+    assert torch.equal(h, want)
+    # SwiGLU
+    gu = torch.randn((m, 2 * k), generator=g, device="cuda").to(torch.bfloat16)
+    hq, hs = ops.silu_mul_quant(gu)
+    want = ops.fp8_gemm(hq, hs, wq, ws, residual=res)
+    got = ops.fp8_gemv_act(gu, wq, ws, ops.ACT_SWIGLU, residual=res)
+    assert torch.equal(got, want)
+    check_status()
+    assert_close(got, ref.fp8_gemm(*ref.silu_mul_quant(gu), wq, ws, residual=res), what="against the fp32 restatement")
