@@ -52,6 +52,7 @@ TRACE_TOPICS = ("scheduler", "graph", "prefix", "session", "spmd")
 # field -> (environment variable, parser, what it does)
 _ENV = {
     "gemv": ("MFQ_GEMV", _flag, "weight-streaming FP8 GEMV for <= 16 token rows (0: always the tcgen05 GEMM)"),
+    "act_gemv": ("MFQ_ACT_GEMV", _flag, "fold norm / quantization / SwiGLU into the product kernel for <= 4 rows (measured slower: off)"),
     "pdl": ("MFQ_PDL", _flag, "programmatic dependent launch on the decode kernels (read by the CUDA library)"),
     "gemm_stages": ("MFQ_GEMM_STAGES", _stages, "force the TMA ring depth of the FP8 GEMM, 0 = chosen per shape (read by the CUDA library)"),
     "cuda_graphs": ("MFQ_CUDA_GRAPHS", _flag, "capture decode / MTP steps into CUDA graphs (0: eager launches)"),
@@ -67,6 +68,7 @@ _ENV = {
 @dataclass(frozen=True)
 class RuntimeConfig:
     gemv: bool = True
+    act_gemv: bool = False
     pdl: bool = True
     gemm_stages: int = 0
     cuda_graphs: bool = True

@@ -349,7 +349,7 @@ class LlamaModel:
         """Whether ``lin`` takes bf16 rows and prepares its FP8 activations inside its own kernel: a few rows on one GPU
         (``ops.fp8_gemv_act``) -- four kernels less per layer in a single-stream decode step, same bits."""
         return (self.tp == 1 and isinstance(lin, Fp8Linear) and lin.q.is_cuda and lin.q.ndim == 2
-                and ops.act_gemv_ok(rows, lin.q.shape[0], lin.q.shape[1]))
+                and ops.act_gemv_pays(rows, lin.q.shape[0], lin.q.shape[1]))
 
     # -- feed-forward -------------------------------------------------------------------------------------------
     def _ffn(self, h, layer):

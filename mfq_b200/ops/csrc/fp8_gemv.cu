@@ -208,6 +208,29 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fp8_gemv_act_kernel(const Gemv
     for (int kb = wid; kb < kblocks; kb += kWarps)
       if (lane < 16) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + size_t(lane) * p.K + kb * 128));
   }
+  // The first batch of this warp's weight loads is issued BEFORE the dependency wait as well, into registers: its DRAM / L2
+  // round trip then runs under the wait and under the activation preparation instead of after them.
+  const uint8_t* w_lo = p.w + size_t(n0 + g8) * p.K + 16 * c;
+  const uint8_t* w_hi = w_lo + size_t(8) * p.K;
+  const float* ws_row = p.w_scale + size_t(n0 >> 7) * kblocks;
+  constexpr int kBatch = 4;
+  uint4 a_lo0[kBatch], a_hi0[kBatch], a_lo1[kBatch], a_hi1[kBatch];
+  float wscale[kBatch];
+  auto load_batch = [&](int kb0) {
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int kb = kb0 + u * kWarps;
+      if (kb < kblocks) {
+        const int k = kb * 128;
+        a_lo0[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
+        a_hi0[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
+        a_lo1[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k + 64));
+        a_hi1[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k + 64));
+        wscale[u] = __ldg(ws_row + kb);
+      }
+    }
+  };
+  load_batch(wid);
   pdl_wait();
   const int nvec = p.K >> 3;
   // one element vector of the prepared (pre-quantization) row, as the standalone kernels compute it
@@ -299,28 +322,11 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fp8_gemv_act_kernel(const Gemv
   __syncthreads();
 
   // ---- the product, as in fp8_gemv_kernel<1, 1>, the activation fragments coming from shared memory ----
-  const uint8_t* w_lo = p.w + size_t(n0 + g8) * p.K + 16 * c;
-  const uint8_t* w_hi = w_lo + size_t(8) * p.K;
-  const float* ws_row = p.w_scale + size_t(n0 >> 7) * kblocks;
   const bool live = g8 < p.M;
   const uint8_t* xq = act_smem + size_t(live ? g8 : 0) * p.K + 16 * c;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  constexpr int kBatch = 4;
   for (int kb0 = wid; kb0 < kblocks; kb0 += kWarps * kBatch) {
-    uint4 a_lo0[kBatch], a_hi0[kBatch], a_lo1[kBatch], a_hi1[kBatch];
-    float wscale[kBatch];
-#pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-      const int kb = kb0 + u * kWarps;
-      if (kb < kblocks) {
-        const int k = kb * 128;
-        a_lo0[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
-        a_hi0[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
-        a_lo1[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k + 64));
-        a_hi1[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k + 64));
-        wscale[u] = __ldg(ws_row + kb);
-      }
-    }
+    if (kb0 != wid) load_batch(kb0);
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
       const int kb = kb0 + u * kWarps;

@@ -141,6 +141,20 @@ def act_gemv_ok(m: int, n: int, k: int) -> bool:
     return gemv_enabled() and 0 < m <= ACT_GEMV_MAX_ROWS and n % 16 == 0 and k % 128 == 0 and k <= 16384
 
 
+ACT_GEMV_MAX_CTAS = 296  # one wave at two CTAs per SM
+
+
+def act_gemv_pays(m: int, n: int, k: int) -> bool:
+    """Whether a model should fold the preparation in.  Measured on B200 with one row (Llama-8B, 2.75 ms per step with
+    the standalone kernels): all four projections of a layer folded 3.23 ms -- every CTA repeats the preparation, so the
+    1792-CTA gate/up product pays it once per wave, six times; only the single-wave projections (o_proj, down) folded
+    2.92 ms -- three dependent passes over the row with block-wide reductions in between cost more inside every CTA than
+    the hand-over to a separate one-CTA kernel.  So the answer is no unless ``MFQ_ACT_GEMV=1`` asks for it; the kernel
+    stays for shapes and parts where the balance differs."""
+    from ..config import current
+    return current().act_gemv and act_gemv_ok(m, n, k) and n // 16 <= ACT_GEMV_MAX_CTAS
+
+
 def fp8_gemv_act(x: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor, mode: int, *, norm_w: torch.Tensor | None = None,
                  eps: float = 0.0, residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """``out = W . quant(prep(x))`` (+ residual) for up to 4 bf16 rows, the preparation -- RMSNorm * ``norm_w``
