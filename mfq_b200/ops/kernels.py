@@ -13,7 +13,9 @@ from .lib import Workspace, check, lib, ptr, stream_ptr
 FP8 = torch.float8_e4m3fn
 
 
-GEMV_MAX_ROWS = 16  # up to this many rows the weight-streaming kernel (fp8_gemv.cu) always replaces the tcgen05 GEMM
+GEMV_MAX_ROWS = 8   # up to this many rows the weight-streaming kernel (fp8_gemv.cu) always replaces the tcgen05 GEMM
+GEMV_MID_ROWS = 16  # ... up to this many when the matrix is at most GEMV_MID_WEIGHTS values
+GEMV_MID_WEIGHTS = 20 << 20
 GEMV_WIDE_ROWS = 64  # ... and up to this many when the weight matrix is small (see use_gemv)
 
 
@@ -24,14 +26,18 @@ def gemv_enabled() -> bool:
 
 
 def use_gemv(m: int, n: int, k: int) -> bool:
-    """Whether ``[m, k] x [n, k]^T`` goes to the weight-streaming kernel: always for up to 16 rows; for up to 64 rows
-    only when the output is a few tiles wide and the matrix small (a tensor-parallel rank's q/k/v shard), where the
-    tcgen05 path would need a deep split-K whose reduction costs more than the product.  Measured on B200 at 64 rows:
-    768 x 4096 takes 11.1 us here against 14.7 us there; from 3072 x 4096 up the tcgen05 path wins (the legacy
-    ``mma.sync`` pipe this kernel uses runs at a fraction of the tcgen05 rate)."""
+    """Whether ``[m, k] x [n, k]^T`` goes to the weight-streaming kernel: always for up to 8 rows; for 9..16 rows only
+    for matrices up to 20 M values (measured at 16 rows on B200, this kernel / tcgen05: o_proj 4096 x 4096 7.0 / 10.4 us,
+    but gate_up 28672 x 4096 44.5 / 22.7, down 24.0 / 18.3, LM head 168 / 92 -- a second 8-column block doubles its MMA
+    work while the tcgen05 tile is still nearly free); for up to 64 rows only when the output is a few tiles wide and the
+    matrix small (a tensor-parallel rank's q/k/v shard), where the tcgen05 path would need a deep split-K whose reduction
+    costs more than the product: 768 x 4096 at 64 rows takes 11.1 us here against 14.7 us there; from 3072 x 4096 up the
+    tcgen05 path wins (the legacy ``mma.sync`` pipe this kernel uses runs at a fraction of the tcgen05 rate)."""
     if n % 16 or not gemv_enabled():
         return False
     if m <= GEMV_MAX_ROWS:
+        return True
+    if m <= GEMV_MID_ROWS and n * k <= GEMV_MID_WEIGHTS:
         return True
     return m <= GEMV_WIDE_ROWS and n <= 1024 and n * k <= (4 << 20)
 
