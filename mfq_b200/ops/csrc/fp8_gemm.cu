@@ -114,6 +114,51 @@ __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Cluster split-K: CTA r of S finishes the token columns c = r (mod S); a thread owns one output row and every kSel-th
+// of those columns.  The S partials of a column are summed in split order whichever CTA does it, so results do not
+// depend on scheduling.  Every load of the thread -- S remote partials per column, multipliers, residual values -- leaves
+// before the first sum, so the round trips through the cluster's shared memory overlap (in groups of at most kLoads
+// partials to bound the registers).  Fetching multipliers and residuals ahead of the barrier measured slower: the values
+// have to be held across it, and the registers for that spill.
+template <int BT, int S>
+__device__ __forceinline__ void cluster_sum_columns(const GemmParams& p, const uint8_t* tiles, int t0, int tl, int n0) {
+  using Cfg = GemmCfg<BT>;
+  constexpr int kSel = Cfg::kEpiWarps / 4;
+  constexpr int kLoads = 32;
+  constexpr int kGroup = kLoads / S < 1 ? 1 : kLoads / S;
+  const int e = int(threadIdx.x) - 64, row = e & 127, sel = e >> 7;
+  const int r = int(cluster_cta_rank());
+  const int n = n0 + row;
+  const uint32_t mine = smem_u32(tiles) + uint32_t(row) * 4u;
+  uint32_t base[S];
+#pragma unroll
+  for (int z = 0; z < S; ++z) base[z] = map_to_cta(mine, uint32_t(z));
+  const unsigned short* rp = reinterpret_cast<const unsigned short*>(p.residual);
+  constexpr int step = S * kSel;
+  for (int c0 = r + S * sel; c0 < tl; c0 += step * kGroup) {
+    float v[kGroup][S], xm[kGroup];
+    unsigned short res[kGroup];
+#pragma unroll
+    for (int j = 0; j < kGroup; ++j) {
+      const int c = c0 + j * step;
+      const bool live = c < tl;
+      xm[j] = live ? __ldg(p.x_scale + t0 + c) : 0.f;
+      res[j] = (live && rp && n < p.N) ? __ldcg(rp + size_t(t0 + c) * p.N + n) : (unsigned short)0;
+#pragma unroll
+      for (int z = 0; z < S; ++z) v[j][z] = live ? ld_cluster_f32(base[z] + uint32_t(c) * (kTileN * 4u)) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kGroup; ++j) {
+      const int c = c0 + j * step;
+      float sum = 0.f;
+#pragma unroll
+      for (int z = 0; z < S; ++z) sum += v[j][z];  // split order
+      sum = sum * xm[j] + __uint_as_float(uint32_t(res[j]) << 16);
+      if (c < tl && n < p.N) p.out[size_t(t0 + c) * p.N + n] = __float2bfloat16(sum);
+    }
+  }
+}
+
 template <int BT>
 __global__ void __launch_bounds__(GemmCfg<BT>::kThreads, (BT <= 64 ? 2 : 1))
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -581,43 +626,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     __syncwarp();
     cluster_barrier();  // all partials are in place
     if (warp >= 2 && !*abort_flag) {
-      // CTA r of S finishes the token columns c = r (mod S); a thread owns one output row and every kSel-th of those
-      // columns.  The S partials of a column are summed in split order whichever CTA does it, so results do not depend
-      // on scheduling.  All loads of a group of columns (S remote partials, multiplier, residual) leave before the
-      // first sum, so their round trips overlap.  (Fetching multipliers and residuals ahead of the barrier measured
-      // slower: the values have to be held across it, and the registers for that spill.)
-      constexpr int kSel = Cfg::kEpiWarps / 4;
-      constexpr int kGroup = 4;
-      const int e = int(threadIdx.x) - 64, row = e & 127, sel = e >> 7;
-      const int S = int(gridDim.z), r = int(cluster_cta_rank());
-      const int tl = min(BT, row_end - t0), n = n0 + row;
-      const uint32_t mine = smem_u32(tiles) + uint32_t(row) * 4u;
-      uint32_t base[8];
-#pragma unroll
-      for (int z = 0; z < 8; ++z) base[z] = map_to_cta(mine, uint32_t(z < S ? z : 0));
-      const unsigned short* rp = reinterpret_cast<const unsigned short*>(p.residual);
-      const int step = S * kSel;
-      for (int c0 = r + S * sel; c0 < tl; c0 += step * kGroup) {
-        float v[kGroup][8], xm[kGroup];
-        unsigned short res[kGroup];
-#pragma unroll
-        for (int j = 0; j < kGroup; ++j) {
-          const int c = c0 + j * step;
-          const bool live = c < tl;
-          xm[j] = live ? __ldg(p.x_scale + t0 + c) : 0.f;
-          res[j] = (live && rp && n < p.N) ? __ldcg(rp + size_t(t0 + c) * p.N + n) : (unsigned short)0;
-#pragma unroll
-          for (int z = 0; z < 8; ++z) v[j][z] = (live && z < S) ? ld_cluster_f32(base[z] + uint32_t(c) * (kTileN * 4u)) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < kGroup; ++j) {
-          const int c = c0 + j * step;
-          float sum = 0.f;
-#pragma unroll
-          for (int z = 0; z < 8; ++z) sum += v[j][z];  // split order; zeros beyond S
-          sum = sum * xm[j] + __uint_as_float(uint32_t(res[j]) << 16);
-          if (c < tl && n < p.N) p.out[size_t(t0 + c) * p.N + n] = __float2bfloat16(sum);
-        }
+      const int tl = min(BT, row_end - t0);
+      switch (int(gridDim.z)) {  // the split count as a constant: all partials of a thread's columns are loaded at once
+        case 2: cluster_sum_columns<BT, 2>(p, tiles, t0, tl, n0); break;
+        case 3: cluster_sum_columns<BT, 3>(p, tiles, t0, tl, n0); break;
+        case 4: cluster_sum_columns<BT, 4>(p, tiles, t0, tl, n0); break;
+        case 5: cluster_sum_columns<BT, 5>(p, tiles, t0, tl, n0); break;
+        case 6: cluster_sum_columns<BT, 6>(p, tiles, t0, tl, n0); break;
+        case 7: cluster_sum_columns<BT, 7>(p, tiles, t0, tl, n0); break;
+        default: cluster_sum_columns<BT, 8>(p, tiles, t0, tl, n0); break;
       }
     }
     __syncwarp();

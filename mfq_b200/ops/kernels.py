@@ -56,6 +56,8 @@ def pick_splits(m: int, n: int, k: int, sms: int = 148) -> int:
     kb = k // 128
     if tiles >= 4 * sms or kb <= 1:
         return 1
+    if m <= 64 and (tiles, kb) in _MEASURED_SPLITS:
+        return _MEASURED_SPLITS[(tiles, kb)]
     best, best_cost = 1, None
     for s in range(1, min(kb, 16) + 1):
         per = math.ceil(kb / s)
@@ -67,6 +69,11 @@ def pick_splits(m: int, n: int, k: int, sms: int = 148) -> int:
             best, best_cost = s, cost
     return best
 
+
+# Decode shapes where a sweep inside a decode step disagrees with the wave model, (output tiles, K blocks) -> splits:
+# 48 tiles x 32 blocks (6144 x 4096, the fused q/k/v projection of an 8B model) takes 17.4 us with the model's 3 splits --
+# 144 CTAs in clusters of 3 leave no slack for cluster placement -- and 14.6 us with 4.
+_MEASURED_SPLITS = {(48, 32): 4}
 
 PAIR_MIN_ROWS = 1024  # batches at least this wide take the two-SM GEMM (``csrc/fp8_gemm_2cta.cu``)
 
