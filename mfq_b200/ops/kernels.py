@@ -59,12 +59,19 @@ def pick_splits(m: int, n: int, k: int, sms: int = 148) -> int:
     if m <= 64 and (tiles, kb) in _MEASURED_SPLITS:
         return _MEASURED_SPLITS[(tiles, kb)]
     best, best_cost = 1, None
-    for s in range(1, min(kb, 16) + 1):
+    # Up to 8 splits meet in a cluster's shared memory; more would fall back to the global scratch buffer with a
+    # last-arriver sum, which costs several microseconds (1536 x 4096 at 64 rows: 14.7 us with 11 splits, 9.1 with 8), so
+    # decode-sized tiles never ask for more.  A cluster grid that needs nearly every SM (129..148 CTAs) does not place
+    # well -- clusters stay inside a GPC -- and is charged for it.
+    small = _token_tile(m) <= 64
+    for s in range(1, min(kb, 8 if small else 16) + 1):
         per = math.ceil(kb / s)
         if s > 1 and per < 2:
             break
         ctas = tiles * math.ceil(kb / per)
         cost = math.ceil(ctas / sms) * (per + 4) + (1.5 if s > 1 else 0.0)
+        if small and s > 1 and 128 < ctas <= sms:
+            cost += 3.0
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
