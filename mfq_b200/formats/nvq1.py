@@ -316,8 +316,17 @@ def _basis(q, sbit, idx, tables, v: Nvq1Variant, nv: int):
 
 
 def quantize_nvq1(w, variant="NVQ1-L", *, axis: int = 0, importance=None, iterations: int = 3, table_steps: int = 2,
-                  device: str | None = None, chunk_rows: int = 64) -> Nvq1Tensor:
-    """``w``: any-rank array whose ``axis`` indexes the rows; ``importance [row length]``: optional column weights."""
+                  device: str | None = None, chunk_rows: int = 64, train_table: bool = False,
+                  validation_fraction: float = 0.125, _fixed_table=None) -> Nvq1Tensor:
+    """``w``: any-rank array whose ``axis`` indexes the rows; ``importance [row length]``: optional column weights.
+
+    ``train_table`` (NVQ1-L): also fit a tensor-local 2048-entry ternary table (Lloyd steps from the grid, entries kept
+    distinct) on all but every ``1 / validation_fraction``-th row, and keep it -- 4096 more bytes in the blob, profile
+    2 -- only if it lowers the error on the held-out rows; otherwise the tensor is encoded with the grid."""
+    if train_table and not (VARIANTS[variant] if isinstance(variant, str) else variant).banked:
+        return _quantize_with_tensor_table(w, variant, axis=axis, importance=importance, iterations=iterations,
+                                           table_steps=max(1, table_steps), device=device, chunk_rows=chunk_rows,
+                                           validation_fraction=validation_fraction)
     import torch
     v = VARIANTS[variant] if isinstance(variant, str) else variant
     w = np.asarray(w, dtype=np.float32)
@@ -333,7 +342,8 @@ def quantize_nvq1(w, variant="NVQ1-L", *, axis: int = 0, importance=None, iterat
     wg = torch.zeros_like(x)
     wg[:, :row_len] = 1.0 if importance is None else torch.as_tensor(np.asarray(importance, dtype=np.float32), device=dev).clamp_min(1e-12)
     x, wg = x.reshape(rows, nv, 8), wg.reshape(rows, nv, 8)
-    tables = torch.as_tensor(np.asarray(v.default_table(), dtype=np.float32), device=dev)
+    start = v.default_table() if _fixed_table is None else _fixed_table
+    tables = torch.as_tensor(np.asarray(start, dtype=np.float32), device=dev)
     if not v.banked:
         tables = torch.stack([tables, tables])
     qmax = (1 << v.sub_bits) - 1
@@ -355,6 +365,8 @@ def quantize_nvq1(w, variant="NVQ1-L", *, axis: int = 0, importance=None, iterat
     table = None
     if v.banked:
         table = tables.round().to(torch.int8).cpu().numpy()
+    elif _fixed_table is not None:
+        table = np.asarray(_fixed_table, dtype=np.int8)
     return Nvq1Tensor(v, shape, axis, row_len, anchors.cpu().numpy().astype(np.float32), q.cpu().numpy().astype(np.uint8),
                       idx.cpu().numpy().astype(np.uint16), sbit.cpu().numpy().astype(np.uint8), table)
 
@@ -403,3 +415,79 @@ def _refit_banks(x, wg, anchors, q, sbit, idx, tables, v: Nvq1Variant):
             new = torch.as_tensor(rows_np.astype(np.float32), device=x.device)
         out.append(new)
     return torch.stack(out)
+
+
+def _refit_single_table(x, wg, anchors, q, sbit, idx, table, v: Nvq1Variant):
+    """Lloyd step for the one table of NVQ1-L: both signs use it, each with its own delta."""
+    import torch
+    rows, nv, _ = x.shape
+    per = v.groupsize // 8
+    vs = sbit.repeat_interleave(per, 1)[:, :nv]
+    s = anchors[:, None] * q.repeat_interleave(per, 1)[:, :nv].float()
+    live = s > 0
+    xs, ws, ss, ids = x[live], wg[live], s[live][:, None], idx[live]
+    dl = torch.where(vs[live] != 0, -v.delta, v.delta)[:, None]
+    new = table.clone()
+    if ids.numel():
+        levels = torch.tensor([-1.0, 0.0, 1.0], device=x.device)
+        cost = torch.zeros((v.entries, 8, 3), device=x.device)
+        for li, l in enumerate(levels):
+            cost[:, :, li].index_add_(0, ids, ws * (xs - ss * (l + dl)) ** 2)
+        used = torch.zeros(v.entries, dtype=torch.bool, device=x.device)
+        used[ids.unique()] = True
+        new[used] = levels[cost[used].argmin(-1)]
+    rows_np = new.round().to(torch.int8).cpu().numpy()
+    seen, fresh = set(), []
+    for e in range(v.entries):
+        key = rows_np[e].tobytes()
+        if key in seen:
+            fresh.append(e)
+        else:
+            seen.add(key)
+    if fresh:  # duplicates take unused vectors of the ternary cube, walked in a fixed order
+        g = 0
+        for e in fresh:
+            while True:
+                cand = (np.array([(g // 3 ** c) % 3 for c in range(8)], dtype=np.int8) - 1)
+                g += 1
+                if cand.tobytes() not in seen:
+                    break
+            rows_np[e] = cand
+            seen.add(cand.tobytes())
+    return torch.as_tensor(rows_np.astype(np.float32), device=x.device)
+
+
+def _quantize_with_tensor_table(w, variant, *, axis, importance, iterations, table_steps, device, chunk_rows, validation_fraction):
+    import torch
+    v = VARIANTS[variant] if isinstance(variant, str) else variant
+    w = np.asarray(w, dtype=np.float32)
+    rows_first = np.moveaxis(w, axis, 0).reshape(w.shape[axis], -1)
+    rows = rows_first.shape[0]
+    every = max(2, int(round(1.0 / max(validation_fraction, 1e-6))))
+    held = np.arange(rows) % every == every - 1
+    if held.all() or not held.any():
+        return quantize_nvq1(w, v, axis=axis, importance=importance, iterations=iterations, device=device, chunk_rows=chunk_rows)
+    train, valid = rows_first[~held], rows_first[held]
+    dev = torch.device(device or "cpu")
+    table = np.asarray(IQ1S_GRID, dtype=np.int8)
+    for _ in range(table_steps):
+        t = quantize_nvq1(train, v, importance=importance, iterations=iterations, device=device, chunk_rows=chunk_rows, _fixed_table=table)
+        nv = t.indices.shape[1]
+        x = torch.zeros((train.shape[0], nv * 8), dtype=torch.float32, device=dev)
+        x[:, : train.shape[1]] = torch.from_numpy(train).to(dev)
+        wg = torch.zeros_like(x)
+        wg[:, : train.shape[1]] = 1.0 if importance is None else torch.as_tensor(np.asarray(importance, dtype=np.float32), device=dev).clamp_min(1e-12)
+        new = _refit_single_table(x.reshape(-1, nv, 8), wg.reshape(-1, nv, 8), torch.from_numpy(t.anchors).to(dev),
+                                  torch.from_numpy(t.sub_scale.astype(np.int64)).to(dev), torch.from_numpy(t.sign.astype(np.int64)).to(dev),
+                                  torch.from_numpy(t.indices.astype(np.int64)).to(dev), torch.as_tensor(table.astype(np.float32), device=dev), v)
+        table = new.round().to(torch.int8).cpu().numpy()
+
+    def held_error(tab):
+        t = quantize_nvq1(valid, v, importance=importance, iterations=iterations, device=device, chunk_rows=chunk_rows, _fixed_table=tab)
+        d = dequantize_nvq1(t) - valid
+        return float((d * d * (1.0 if importance is None else np.asarray(importance, dtype=np.float32))).sum())
+
+    if held_error(table) < held_error(None):
+        return quantize_nvq1(w, v, axis=axis, importance=importance, iterations=iterations, device=device, chunk_rows=chunk_rows,
+                             _fixed_table=table)
+    return quantize_nvq1(w, v, axis=axis, importance=importance, iterations=iterations, device=device, chunk_rows=chunk_rows)

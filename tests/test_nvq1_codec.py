@@ -110,3 +110,29 @@ def test_bytes_and_values_equal_the_reference_package(reference_pkg):
     sblob = nvq1.pack_nvq1(s)
     theirs = rs.unpack_nvq1_s(sblob)
     assert rs.pack_nvq1_s(theirs) == sblob
+
+
+def test_tensor_local_table_is_kept_only_when_it_helps():
+    rng = np.random.default_rng(11)
+    # weights whose 8-vectors come from a small set of patterns the IQ1_S grid does not contain: a trained table wins
+    patterns = rng.choice([-1.0, 0.0, 1.0], size=(40, 8), p=[0.45, 0.1, 0.45])
+    rows = []
+    for _ in range(64):
+        pick = patterns[rng.integers(0, 40, size=12)].reshape(-1)
+        rows.append(pick * 0.05 * (1 + 0.05 * rng.normal(size=96)))
+    w = np.asarray(rows, dtype=np.float32)
+    plain = nvq1.quantize_nvq1(w, "NVQ1-L")
+    tuned = nvq1.quantize_nvq1(w, "NVQ1-L", train_table=True)
+    err = lambda t: float(((nvq1.dequantize_nvq1(t) - w) ** 2).sum())
+    assert tuned.table is not None and tuned.table.shape == (2048, 8) and err(tuned) < 0.8 * err(plain), (err(tuned), err(plain))
+    assert np.unique(tuned.table, axis=0).shape[0] == 2048 and set(np.unique(tuned.table).tolist()) <= {-1, 0, 1}
+    blob = nvq1.pack_nvq1(tuned)
+    assert blob[4] == 2 and np.array_equal(nvq1.dequantize_nvq1(nvq1.unpack_nvq1(blob)), nvq1.dequantize_nvq1(tuned))
+    # Gaussian weights: the grid is already a good table, the trained one is dropped unless it wins on held-out rows
+    g = _weights(48, 96, seed=12)
+    t = nvq1.quantize_nvq1(g, "NVQ1-L", train_table=True)
+    assert t.table is None or err_of(t, g) <= err_of(nvq1.quantize_nvq1(g, "NVQ1-L"), g) * 1.05
+
+
+def err_of(t, w):
+    return float(((nvq1.dequantize_nvq1(t) - w) ** 2).sum())
