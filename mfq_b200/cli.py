@@ -712,7 +712,9 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--bits", type=int, default=4)
     q.add_argument("--groupsize", type=int, default=0)
     q.add_argument("--sub-bits", type=int, default=0)
-    q.add_argument("--format", choices=["nint2", "nint3", "nint4", "nint5", "nint6", "nint8", "nvq3", "mxfp4", "fp8", "bf16"])
+    q.add_argument("--format", choices=["nint2", "nint3", "nint4", "nint5", "nint6", "nint8", "nvq3", "mxfp4", "fp8", "bf16", "npq0-s", "npq0-l",
+                                        "nvq1-l", "nvq1-l-s4", "nvq1-s"],
+                   help="family of every 2-D weight (and of routed experts without a mix): NINT widths, lattice / product codes, MX, FP8")
     q.add_argument("--preset", help="role-based mixed-width NINT preset: S2-S S2-M S3-S S3-M S3-L S4-S S4-M S5-S S5-M S6 S8")
     q.add_argument("--imatrix", help="importance matrix (.npz from `mfq calibrate imatrix`) for the NINT search")
     q.add_argument("--ew-scheme", "--scheme", dest="ew_scheme", help="mfq.calibration-scheme.v3 from `mfq solve-ew`")
