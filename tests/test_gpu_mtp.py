@@ -124,3 +124,81 @@ def test_verification_draw_follows_the_target_distribution():
         assert float((freq[:5] - p).abs().max()) < 0.025, (pos, freq[:5].tolist(), p.tolist())
     # positions draw independently of each other (distinct counters)
     assert float(((s[:, 0] == s[:, 2]).float().mean() - float((p * p).sum())).abs()) < 0.03
+
+
+def _gpu_engine(k, **kw):
+    cfg = LlamaConfig.tiny()
+    w = LlamaWeights.random_init(cfg, "cuda", seed=5, std=0.05, mtp=True)
+    return cfg, LLMEngine(LlamaModel(cfg, w), max_batch=4, max_seq_len=128, mtp_draft_tokens=k, **kw)
+
+
+def _prefix(a, b):
+    n = 0
+    while n < min(len(a), len(b)) and a[n] == b[n]:
+        n += 1
+    return n / max(1, min(len(a), len(b)))
+
+
+def test_dynamic_depth_and_parked_steps_under_graphs():
+    """Per-cycle depth choice (one captured graph per (bucket, depth, next depth)) and parked plain steps that keep the
+    head primed, on the device: the confirmed tokens stay those of plain greedy decoding."""
+    require_gpu_lib()
+    cfg, eng = _gpu_engine(3, mtp_dynamic_depth=True)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)) for n in (9, 14)]
+    plain = eng.generate(prompts, 14).tokens
+    for r in range(2):
+        eng.release(r)
+    for r, p in enumerate(prompts):
+        eng.prefill(r, p)
+        eng.grow(r, int(p.numel()) + 40)
+    got = {0: [int(eng.sampled[0])], 1: [int(eng.sampled[1])]}
+    depths = []
+    while min(len(v) for v in got.values()) < 14:
+        out = eng.decode([0, 1])
+        depths.append(eng.last_depth)
+        for r, toks in out.items():
+            assert 1 <= len(toks) <= eng.last_depth + 1
+            got[r] += toks
+    check_status()
+    assert set(depths[:6]) == {1, 2, 3}
+    assert min(_prefix(plain[r].tolist(), got[r][:14]) for r in range(2)) >= 0.5
+    assert len(eng.mtp_graphs) >= 3  # several (depth, next depth) variants were captured
+    # parked mode: plain steps with the head kept primed, then cycles again
+    from mfq_b200.engine.mtp_policy import ParkingController
+    cfg, ad = _gpu_engine(2, mtp_adaptive=True)
+    ad.mtp_controller = ParkingController(probe=2, park_after=2, reprobe_every=3)
+    first = ad.prefill(0, prompts[0])
+    ad.grow(0, 80)
+    toks, modes = [first], []
+    while len(toks) < 24:
+        before = dict(ad.mtp_controller.calls)
+        toks.extend(ad.decode([0])[0])
+        modes.append("mtp" if ad.mtp_controller.calls["mtp"] > before["mtp"] else "plain")
+    check_status()
+    assert "plain" in modes and "mtp" in modes
+    ref_eng = LLMEngine(LlamaModel(cfg, ad.model.w), max_batch=4, max_seq_len=128)
+    want = ref_eng.generate([prompts[0]], 24).tokens[0].tolist()
+    assert _prefix(want, toks) >= 0.5
+
+
+def test_sampled_rows_go_through_cycles_and_replay():
+    """Rows with a temperature decode through draft / verify cycles (speculative sampling in the verify pass); the same
+    seeds give the same tokens, another seed gives others."""
+    from mfq_b200.engine.scheduler import SamplingParams
+    require_gpu_lib()
+
+    def run(seed):
+        cfg, eng = _gpu_engine(2)
+        p = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(3))
+        eng.set_sampling(0, SamplingParams(max_tokens=20, temperature=1.0, top_p=0.95, seed=seed))
+        toks = [eng.prefill(0, p, params=SamplingParams(max_tokens=20, temperature=1.0, top_p=0.95, seed=seed))]
+        eng.grow(0, 80)
+        while len(toks) < 20:
+            toks.extend(eng.decode([0])[0])
+        check_status()
+        return toks[:20], eng.mtp_stats()
+    a, st = run(11)
+    b, _ = run(11)
+    c, _ = run(12)
+    assert st["cycles"] > 0 and st["drafted"] > 0
+    assert a == b and a != c
