@@ -504,8 +504,41 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
         return {"id": ident, "aliases": cat.resolve(ident).aliases}
 
     @app.delete("/api/v1/catalog/{ident}")
-    async def catalog_remove(ident: str):
-        return {"removed": cat.remove(ident)}
+    async def catalog_remove(ident: str, purge: bool = False):
+        """Forget an entry; ``purge=true`` also deletes its files, which must lie under one of the catalog's roots."""
+        if not purge:
+            return {"removed": cat.remove(ident)}
+        try:
+            art = cat.resolve(ident)
+        except ArtifactNotFound:
+            return error_response(404, "model_not_found", f"no catalog entry {ident!r}")
+        if any(name in (art.id, *art.aliases) for name in service.models):
+            return error_response(409, "model_loaded", f"{ident!r} is loaded; unload it first")
+        try:
+            freed = cat.purge(art.id)
+        except PermissionError as exc:
+            return error_response(403, "outside_catalog_roots", str(exc))
+        return {"removed": True, "purged": True, "freed_bytes": freed}
+
+    @app.get("/api/v1/catalog/{ident}/analysis")
+    async def catalog_analysis(ident: str, batch: int = 1, context: int = 4096, tensor_parallel: int = 1):
+        """Composition of a checkpoint (bytes and bits per weight per family and group), parameter counts (total and
+        active per token) and the device memory a deployment of ``batch`` x ``context`` needs per GPU."""
+        from .analysis import analyse_artifact
+        try:
+            art = cat.resolve(ident)
+        except ArtifactNotFound:
+            return error_response(404, "model_not_found", f"no catalog entry {ident!r}")
+        if batch < 1 or context < 1 or tensor_parallel < 1:
+            return error_response(400, "invalid_request", "batch, context and tensor_parallel must be positive")
+        fn = lambda: analyse_artifact(art, batch=batch, context=context, tensor_parallel=tensor_parallel)
+        return await asyncio.get_running_loop().run_in_executor(None, fn)
+
+    @app.get("/api/v1/runtime/stats")
+    async def runtime_stats():
+        """Request counters and latency / throughput quantiles per model, from the metrics histograms."""
+        from .analysis import serving_stats
+        return serving_stats(service.metrics)
 
     # ---- realtime: one WebSocket, many generations ------------------------------------------------------------------
 

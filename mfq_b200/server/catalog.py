@@ -160,6 +160,25 @@ class ModelCatalog:
                 self._save()
             return gone
 
+    def purge(self, ident: str) -> int:
+        """Delete the files of an entry and forget it; returns the bytes freed.  Only paths below one of the catalog's
+        roots may be deleted (an entry added by hand from elsewhere is refused)."""
+        import shutil
+        art = self.resolve(ident)
+        path = Path(art.path).resolve()
+        if not any(path == Path(r).resolve() or Path(r).resolve() in path.parents for r in self.roots):
+            raise PermissionError(f"{path} is not below a catalog root")
+        freed = art.bytes
+        if path.is_dir():
+            shutil.rmtree(path)
+        else:
+            m = _SHARD_RE.match(path.name)
+            files = sorted(path.parent.glob(f"{m.group('stem')}-*-of-{m.group('count')}.mfq")) if m else [path]
+            for f in files:
+                f.unlink(missing_ok=True)
+        self.remove(art.id)
+        return freed
+
     def resolve(self, name: str) -> Artifact:
         with self._lock:
             if name in self.entries:

@@ -143,3 +143,50 @@ def test_realtime_socket_needs_an_inference_key():
             ws.send_text(json.dumps({"type": "ping"}))
             assert json.loads(ws.receive_text())["type"] == "pong"
     service.shutdown()
+
+
+def test_analysis_stats_and_purge_routes(tmp_path):
+    _artifacts(tmp_path)
+    service = ModelService()
+    service.add_model("echo", EchoBackend(), ByteTokenizer())
+    cat = ModelCatalog(tmp_path / "c.json", roots=[tmp_path])
+    cat.scan()
+    with TestClient(create_app(service, catalog=cat)) as c:
+        r = c.get("/api/v1/catalog/tiny/analysis", params={"batch": 8, "context": 2048, "tensor_parallel": 2})
+        assert r.status_code == 200
+        doc = r.json()
+        a = doc["analysis"]
+        assert a["tensors"] > 10 and a["by_dtype"]["MFE"]["tensors"] == 6 and a["bytes"] == sum(v["bytes"] for v in a["by_dtype"].values())
+        g = a["by_group"]["routed_experts"]
+        assert g["weights"] == 2 * 8 * 3 * 256 * 128 and 4.0 < g["bits_per_weight"] < 5.2  # NINT4 / MXFP4 mix
+        p = doc["parameters"]
+        assert p["experts"] == 8 and p["top_k"] == 2 and p["active_per_token"] < p["total"]
+        assert p["total"] - p["active_per_token"] == 2 * (8 - 2) * 3 * 256 * 128
+        m = doc["memory"]
+        assert m["gpus"] == 2 and m["per_gpu"]["total"] == sum(v for k, v in m["per_gpu"].items() if k != "total")
+        # 16-token pages, (2 * 64 + 8) bytes per token, head and layer, one KV head per rank of two
+        assert m["per_gpu"]["kv_cache"] == (8 * 128 + 1) * 2 * 1 * (2 * 64 + 8) * 16
+        assert c.get("/api/v1/catalog/tiny/analysis", params={"batch": 0}).status_code == 400
+        assert c.get("/api/v1/catalog/nope/analysis").status_code == 404
+        hf = c.get("/api/v1/catalog/hf-model/analysis").json()
+        assert hf["kind"] == "hf" and "analysis" not in hf
+        # serving statistics: quantiles out of the histograms
+        c.post("/v1/chat/completions", json={"model": "echo", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4})
+        st = c.get("/api/v1/runtime/stats").json()["models"]["echo"]
+        assert any(k.startswith("mfq_requests_total") or "request" in k for k in st["counters"])
+        h = next(iter(st["histograms"].values()))
+        assert h["count"] >= 1 and h["p50"] is not None and h["p95"] >= h["p50"]
+        # purge deletes files below a root only
+        gguf = tmp_path / "other.gguf"
+        assert gguf.exists()
+        r = c.delete("/api/v1/catalog/other", params={"purge": "true"})
+        assert r.status_code == 200 and r.json()["purged"] and not gguf.exists()
+        assert c.delete("/api/v1/catalog/other", params={"purge": "true"}).status_code == 404
+        outside = tmp_path.parent / "outside.gguf"
+        outside.write_bytes(b"GGUF" + b"\\0" * 8)
+        try:
+            from mfq_b200.server.catalog import Artifact
+            cat.entries["outside"] = Artifact("outside", str(outside), "gguf", 12, 0.0)
+            assert c.delete("/api/v1/catalog/outside", params={"purge": "true"}).status_code == 403 and outside.exists()
+        finally:
+            outside.unlink(missing_ok=True)
