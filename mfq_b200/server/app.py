@@ -128,7 +128,9 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
 
     @asynccontextmanager
     async def lifespan(_app):
+        history.start()
         yield
+        history.stop()
         jobs.shutdown()  # child processes started through the jobs API end with the server
 
     app = FastAPI(title="mfq-b200", version="0.1.0", lifespan=lifespan)
@@ -136,6 +138,9 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
     app.state.jobs = jobs
     app.state.cluster = cluster
     monitor = hardware if hardware is not None else HardwareMonitor()
+    from .hardware import ResourceHistory
+    history = ResourceHistory(monitor)
+    app.state.resource_history = history
     store = sessions if sessions is not None else SessionStore()
     app.state.sessions = store
 
@@ -411,6 +416,13 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
     @app.get("/api/v1/hardware")
     async def hardware_snapshot():
         return monitor.snapshot()
+
+    @app.get("/api/v1/hardware/history")
+    async def hardware_history(last: int | None = None):
+        """Timeline of GPU and host usage (one sample per second while the server runs; a first call takes one)."""
+        if not history.samples:
+            history.sample()
+        return history.history(last)
 
     @app.get("/api/v1/cluster")
     async def cluster_status():

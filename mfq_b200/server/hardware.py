@@ -2,7 +2,9 @@
 
 Only queries are issued (name, memory, utilisation, clocks, power, temperature, throttle reasons); nothing here changes
 a setting of the GPU.  ``nvml`` can be any object with the ``pynvml`` functions used below, which is how the tests run
-without a GPU.  Reference: ``mfq/server/services/hardware.py`` (NVML with a 1 s cache).
+without a GPU.  :class:`ResourceHistory` keeps a bounded timeline of those snapshots plus the host's CPU load and memory
+(``psutil``), filled by a sampler thread or by explicit :meth:`ResourceHistory.sample` calls.
+Reference: ``mfq/server/services/hardware.py`` (NVML with a 1 s cache), ``resource_monitor.py`` (usage timeline).
 """
 
 from __future__ import annotations
@@ -63,3 +65,72 @@ class HardwareMonitor:
         self._cache = {"gpus": gpus, "error": self.error if n is None else None, "sampled_at": time.time()}
         self._stamp = now
         return self._cache
+
+
+class ResourceHistory:
+    """The last ``capacity`` samples of GPU and host usage, one every ``interval`` seconds while the sampler runs."""
+
+    def __init__(self, monitor: HardwareMonitor, capacity: int = 600, interval: float = 1.0, host=None) -> None:
+        import collections
+        import threading
+        self.monitor, self.interval = monitor, interval
+        self.samples = collections.deque(maxlen=capacity)
+        self._host = host  # an object with cpu_percent() and virtual_memory() (psutil by default)
+        self._stop = threading.Event()
+        self._thread: threading.Thread | None = None
+        self._lock = threading.Lock()
+
+    def _host_usage(self) -> dict:
+        h = self._host
+        if h is None:
+            try:
+                import psutil
+                h = self._host = psutil
+            except Exception:
+                return {}
+        try:
+            vm = h.virtual_memory()
+            return {"cpu_percent": float(h.cpu_percent(interval=None)), "memory_total": int(vm.total), "memory_used": int(vm.total - vm.available)}
+        except Exception:
+            return {}
+
+    def sample(self) -> dict:
+        snap = self.monitor.snapshot()
+        row = {"t": time.time(), "host": self._host_usage(),
+               "gpus": [{k: g.get(k) for k in ("index", "memory_used", "utilization", "sm_clock_mhz", "power_w", "temperature_c")}
+                        for g in snap.get("gpus", [])]}
+        with self._lock:
+            self.samples.append(row)
+        return row
+
+    def start(self) -> None:
+        import threading
+        if self._thread is not None:
+            return
+        self._stop.clear()
+
+        def loop():
+            while not self._stop.wait(self.interval):
+                self.sample()
+        self._thread = threading.Thread(target=loop, name="mfq-resource-history", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2 * self.interval + 1)
+            self._thread = None
+
+    def history(self, last: int | None = None) -> dict:
+        with self._lock:
+            rows = list(self.samples)
+        if last is not None:
+            rows = rows[-max(0, int(last)):]
+        peak = {}
+        for r in rows:
+            for g in r["gpus"]:
+                p = peak.setdefault(g["index"], {"memory_used": 0, "utilization": 0, "power_w": 0.0})
+                for k in p:
+                    if g.get(k) is not None:
+                        p[k] = max(p[k], g[k])
+        return {"interval": self.interval, "capacity": self.samples.maxlen, "samples": rows, "peak": {str(k): v for k, v in peak.items()}}

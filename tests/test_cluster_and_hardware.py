@@ -141,3 +141,32 @@ def test_hardware_snapshot_is_cached_and_read_only():
         assert len(c.get("/api/v1/hardware").json()["gpus"]) == 2
         assert c.get("/api/v1/runtime/cache").json() == {"caches": []}
     service.shutdown()
+
+
+def test_resource_history_keeps_a_bounded_timeline():
+    from mfq_b200.server.hardware import ResourceHistory
+    now = [0.0]
+    mon = HardwareMonitor(nvml=FakeNvml(), ttl=0.0, clock=lambda: now[0])
+    host = SimpleNamespace(cpu_percent=lambda interval=None: 12.5,
+                           virtual_memory=lambda: SimpleNamespace(total=64 << 30, available=48 << 30))
+    hist = ResourceHistory(mon, capacity=3, interval=0.01, host=host)
+    for _ in range(5):
+        now[0] += 1
+        hist.sample()
+    doc = hist.history()
+    assert len(doc["samples"]) == 3 and doc["capacity"] == 3
+    row = doc["samples"][-1]
+    assert row["host"] == {"cpu_percent": 12.5, "memory_total": 64 << 30, "memory_used": 16 << 30}
+    assert [g["memory_used"] for g in row["gpus"]] == [1 << 30, 2 << 30] and row["gpus"][0]["power_w"] == 412.0
+    assert doc["peak"]["1"] == {"memory_used": 2 << 30, "utilization": 37, "power_w": 412.0}
+    assert len(hist.history(last=2)["samples"]) == 2
+    hist.start()  # the sampler thread adds rows by itself and stops on request
+    import time as _t
+    _t.sleep(0.08)
+    hist.stop()
+    assert hist._thread is None and len(hist.samples) == 3
+    service = ModelService()
+    with TestClient(create_app(service, hardware=mon)) as c:
+        r = c.get("/api/v1/hardware/history", params={"last": 1}).json()
+        assert len(r["samples"]) == 1 and len(r["samples"][0]["gpus"]) == 2
+    service.shutdown()
