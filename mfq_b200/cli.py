@@ -311,10 +311,24 @@ def _cmd_calibrate(args) -> int:
     col = ImatrixCollector()
     model = MoeLM(mcfg, {k: torch.from_numpy(np.asarray(v, dtype=np.float32)) for k, v in tensors.items()}, observer=col.observe)
     g = torch.Generator().manual_seed(args.seed)
-    for _ in range(args.chunks):
-        model.forward(torch.randint(0, mcfg.vocab_size, (args.ctx,), generator=g))
+    tokens = 0
+    if getattr(args, "corpus", ""):
+        # windows of a calibration corpus (`mfq calibrate data` / `trace-data`) instead of random ids
+        from .calibration.dataset import load_corpus
+        for toks, _mask in load_corpus(args.corpus).iter_chunks("train", max_tokens=args.chunks * args.ctx):
+            ids = torch.from_numpy(np.ascontiguousarray(toks[: args.ctx])).long()
+            if int(ids.max()) >= mcfg.vocab_size:
+                raise SystemExit(f"the corpus holds token id {int(ids.max())}, the model's vocabulary ends at {mcfg.vocab_size - 1}")
+            model.reset()
+            model.forward(ids)
+            tokens += int(ids.numel())
+    else:
+        for _ in range(args.chunks):
+            model.reset()
+            model.forward(torch.randint(0, mcfg.vocab_size, (args.ctx,), generator=g))
+            tokens += args.ctx
     col.save(args.output)
-    print(json.dumps({"output": args.output, "layers": len(col.sum_in)}))
+    print(json.dumps({"output": args.output, "layers": len(col.sum_in), "tokens": tokens}))
     return 0
 
 
@@ -754,6 +768,7 @@ def build_parser() -> argparse.ArgumentParser:
     ci.add_argument("--output", required=True)
     ci.add_argument("--chunks", type=int, default=4)
     ci.add_argument("--ctx", type=int, default=128)
+    ci.add_argument("--corpus", default="", help="calibration corpus directory (`mfq calibrate data`); default: random token ids")
     ci.add_argument("--seed", type=int, default=0)
     cd = cs.add_parser("data", help="tokenize local text / JSONL records into a train + validation calibration corpus")
     cd.add_argument("--source", action="append", required=True, metavar="[DOMAIN=]FILE",

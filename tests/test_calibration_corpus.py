@@ -171,3 +171,17 @@ def test_cli_data_trace_collect(tmp_path, capsys):
     assert ev["event"] == "calibration_statistics_ready" and ev["tensors"] > 10
     from mfq_b200.calibration.imatrix import load
     assert any(k.endswith(".in") for k in load(tmp_path / "im.npz"))
+
+
+def test_imatrix_over_a_corpus(tmp_path, capsys):
+    _sources(tmp_path)
+    assert cli.main(["calibrate", "data", "--source", str(tmp_path / "a.jsonl"), "--output", str(tmp_path / "corpus"),
+                     "--train-tokens", "900", "--validation-tokens", "100", "--sequence-length", "64"]) == 0
+    capsys.readouterr()
+    assert cli.main(["calibrate", "imatrix", "synthetic:tiny-moe", "--output", str(tmp_path / "im.npz"), "--corpus",
+                     str(tmp_path / "corpus"), "--chunks", "6", "--ctx", "64"]) == 0
+    ev = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert ev["tokens"] == 6 * 64 and ev["layers"] > 5
+    from mfq_b200.calibration.imatrix import load
+    im = load(tmp_path / "im.npz")
+    assert int(im["model.block.0.attention.query.weight.count"]) == 6 * 64
