@@ -19,6 +19,8 @@ class ImatrixCollector:
         self.sum_in: dict[str, torch.Tensor] = {}
         self.sum_out: dict[str, torch.Tensor] = {}
         self.count: dict[str, int] = {}
+        self.sum_reap: dict[str, float] = {}
+        self.n_reap: dict[str, int] = {}
 
     def observe(self, name: str, x: torch.Tensor, y: torch.Tensor | None = None) -> None:
         """``x [tokens, in]`` the input of linear ``name`` (``y [tokens, out]`` its output, optional)."""
@@ -29,6 +31,15 @@ class ImatrixCollector:
         if y is not None:
             y = y.detach().reshape(-1, y.shape[-1]).float()
             self.sum_out[name] = self.sum_out.get(name, 0) + (y * y).sum(0)
+
+    def observe_reap(self, name: str, route_weight: torch.Tensor, y: torch.Tensor) -> None:
+        """Router-weighted activation norm of one expert (``name`` = ``<down tensor>#<expert>``): ``route_weight [n]`` of
+        the tokens routed to it and its outputs ``y [n, hidden]`` before the weighting.  The mean of ``weight * |y|`` over
+        the expert's tokens is its REAP saliency: how much it moves the residual stream when it is called."""
+        y = y.detach().reshape(-1, y.shape[-1]).float()
+        s = float((route_weight.detach().reshape(-1).float() * y.norm(dim=-1)).sum())
+        self.sum_reap[name] = self.sum_reap.get(name, 0.0) + s
+        self.n_reap[name] = self.n_reap.get(name, 0) + y.shape[0]
 
     def hook_linear(self, weights: dict[str, torch.Tensor]):
         """Returns ``linear(name, x)`` that multiplies by ``weights[name]`` and records the statistics."""
@@ -46,6 +57,8 @@ class ImatrixCollector:
             out[name + ".count"] = np.array(self.count[name], dtype=np.int64)  # rows seen: an expert's exposure
             if name in self.sum_out:
                 out[name + ".out"] = (self.sum_out[name] / n).cpu().numpy().astype(np.float32)
+        for name, s in self.sum_reap.items():
+            out[name + ".reap"] = np.array(s / max(1, self.n_reap[name]), dtype=np.float64)
         return out
 
     def save(self, path) -> None:

@@ -186,8 +186,9 @@ def allocate(candidates: dict, target_bpw: float, *, imatrix: dict | None = None
              sensitivity: str = "imatrix-energy") -> tuple[dict, dict]:
     """Joint gate / up / down family per routed expert under ``target_bpw`` mean bits per expert weight.
 
-    ``sensitivity``: ``uniform`` (all experts weigh the same) or ``imatrix-energy`` (weights ``P_down ** beta`` with the
-    NatScale exponent; needs ``imatrix`` and ``tensors``).  Exposure is the fraction of calibration rows an expert saw
+    ``sensitivity``: ``uniform`` (all experts weigh the same), ``imatrix-energy`` (weights ``P_down ** beta`` with the
+    NatScale exponent; needs ``imatrix`` and ``tensors``) or ``reap`` (the expert's router-weighted activation norm,
+    ``<down>#e.reap`` of an importance matrix collected with expert saliencies, in place of the output energy).  Exposure is the fraction of calibration rows an expert saw
     (1 without an importance matrix).  Returns ``(scheme, report)``."""
     if candidates.get("format") != CANDIDATES_FORMAT:
         raise ValueError(f"expected {CANDIDATES_FORMAT}")
@@ -225,6 +226,11 @@ def allocate(candidates: dict, target_bpw: float, *, imatrix: dict | None = None
                 w = np.asarray(tensors[banks["down"]["name"]][e], dtype=np.float64)
                 second = np.asarray(imatrix.get(f"{banks['down']['name']}#{e}.in", np.zeros(w.shape[1])), dtype=np.float64)
                 p_down = float((second[None, :] * w * w).sum()) / w.shape[0]  # output energy of the down projection per channel
+            elif sensitivity == "reap":
+                if imatrix is None:
+                    raise ValueError("reap sensitivity needs an importance matrix collected with expert saliencies")
+                reap = float(np.asarray(imatrix.get(f"{banks['down']['name']}#{e}.reap", 0.0)))
+                p_down = reap * reap  # the loss below takes the square root: an expert weighs by its saliency itself
             f = counts[e] / denom
             loss = f * np.sqrt(p_down * (rel[0, combos[:, 0]] + rel[1, combos[:, 1]] + rel[2, combos[:, 2]]))
             rows_cost.append(loss)
@@ -234,7 +240,7 @@ def allocate(candidates: dict, target_bpw: float, *, imatrix: dict | None = None
             exposure.append(f)
     costs = np.stack(rows_cost)
     beta, contrast = 0.0, 0.0
-    if sensitivity == "imatrix-energy":
+    if sensitivity in ("imatrix-energy", "reap"):
         g = np.asarray(scores)
         beta = natscale_exponent(g, tau)
         contrast = realized_contrast(g, beta)
@@ -244,7 +250,7 @@ def allocate(candidates: dict, target_bpw: float, *, imatrix: dict | None = None
         wts[pos] = np.exp(beta * (lg - lg.max()))
         costs = costs * wts[:, None]
     elif sensitivity != "uniform":
-        raise ValueError("sensitivity must be uniform or imatrix-energy")
+        raise ValueError("sensitivity must be uniform, imatrix-energy or reap")
     budget = int(target_bpw * total_weights / 8)
     sol = allocate_hulls(np.stack(rows_bytes), costs, budget)
     assignments, hist = [], {}

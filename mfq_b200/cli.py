@@ -309,7 +309,8 @@ def _cmd_calibrate(args) -> int:
     fields = MoeConfig.__dataclass_fields__
     mcfg = MoeConfig(**{k: v for k, v in cfg.items() if k in fields})
     col = ImatrixCollector()
-    model = MoeLM(mcfg, {k: torch.from_numpy(np.asarray(v, dtype=np.float32)) for k, v in tensors.items()}, observer=col.observe)
+    model = MoeLM(mcfg, {k: torch.from_numpy(np.asarray(v, dtype=np.float32)) for k, v in tensors.items()}, observer=col.observe,
+                  reap_observer=col.observe_reap)
     g = torch.Generator().manual_seed(args.seed)
     tokens = 0
     if getattr(args, "corpus", ""):
@@ -810,7 +811,7 @@ def build_parser() -> argparse.ArgumentParser:
             p.add_argument("--candidates-file", help="reuse a table written by `mfq calibrate candidates`")
             p.add_argument("--target-bpw", type=float, required=True, help="mean bits per routed-expert weight")
             p.add_argument("--tau", type=float, default=1.0, help="NatScale contrast in nats")
-            p.add_argument("--sensitivity", choices=("uniform", "imatrix-energy"), default=None)
+            p.add_argument("--sensitivity", choices=("uniform", "imatrix-energy", "reap"), default=None)
             p.add_argument("--report")
     cc = cs.add_parser("candidates", help="quantize every routed expert matrix under every family: error and size table")
     _candidate_args(cc, target=False)

@@ -121,11 +121,13 @@ def route(logits: torch.Tensor, cfg: MoeConfig) -> tuple[torch.Tensor, torch.Ten
 class MoeLM:
     """fp32 forward with a plain KV list (no paging): prefill a prompt, then decode token by token."""
 
-    def __init__(self, cfg: MoeConfig, weights: dict[str, torch.Tensor], observer=None) -> None:
+    def __init__(self, cfg: MoeConfig, weights: dict[str, torch.Tensor], observer=None, reap_observer=None) -> None:
         """``observer(name, x, y)`` (optional) sees input and output of every named 2-D projection: the hook the
-        importance-matrix collection uses."""
+        importance-matrix collection uses.  ``reap_observer(name, route_weights, y)`` (optional) sees every routed
+        expert's outputs and the router weights of its tokens (``name`` = ``<down tensor>#<expert>``)."""
         self.cfg, self.w = cfg, weights
         self.observer = observer
+        self.reap_observer = reap_observer
         self.k_cache: list[torch.Tensor] = []
         self.v_cache: list[torch.Tensor] = []
 
@@ -151,7 +153,10 @@ class MoeLM:
                 self.observer(f"{p}mlp.experts.gate.weight#{e}", xe, None)
                 self.observer(f"{p}mlp.experts.up.weight#{e}", xe, None)
                 self.observer(f"{p}mlp.experts.down.weight#{e}", he, None)
-            out.index_add_(0, tok, (he @ down[e].T) * wt[tok, slot][:, None])
+            ye = he @ down[e].T
+            if self.reap_observer is not None:
+                self.reap_observer(f"{p}mlp.experts.down.weight#{e}", wt[tok, slot], ye)
+            out.index_add_(0, tok, ye * wt[tok, slot][:, None])
         if cfg.shared_intermediate:
             hs = torch.nn.functional.silu(self._lin(p + "mlp.shared_expert.gate.weight", x)) * self._lin(p + "mlp.shared_expert.up.weight", x)
             out = out + self._lin(p + "mlp.shared_expert.down.weight", hs)

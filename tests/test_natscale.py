@@ -123,3 +123,40 @@ def test_per_neuron_widths_end_to_end(tmp_path, capsys):
         name = next(n for n in listed if listed[n]["high_rows"])
         t = store[name]
         assert sorted(set(np.asarray(t.row_q_bits).tolist())) == [4, 8]
+
+
+def test_reap_saliency_is_collected_and_steers_the_allocation(tmp_path):
+    """Expert saliency = mean router weight x output norm over the tokens routed to it; with ``sensitivity="reap"`` the
+    experts that move the residual stream most keep the most bits."""
+    import json
+    import numpy as np
+    import torch
+    from mfq_b200 import cli
+    from mfq_b200.calibration import natscale
+    from mfq_b200.calibration.imatrix import ImatrixCollector, load
+    from mfq_b200.models.moe_lm import MoeConfig, MoeLM, init_weights
+    cfg = MoeConfig(**cli._SYNTHETIC["tiny-moe"])
+    w = init_weights(cfg, seed=3)
+    for e in range(cfg.num_experts):  # expert e answers (e + 1) times louder than expert 0
+        w["model.block.0.mlp.experts.down.weight"][e] *= (e + 1)
+    col = ImatrixCollector()
+    model = MoeLM(cfg, w, observer=col.observe, reap_observer=col.observe_reap)
+    g = torch.Generator().manual_seed(0)
+    for _ in range(4):
+        model.reset()
+        model.forward(torch.randint(0, cfg.vocab_size, (96,), generator=g))
+    col.save(tmp_path / "im.npz")
+    im = load(tmp_path / "im.npz")
+    reap = np.array([float(im[f"model.block.0.mlp.experts.down.weight#{e}.reap"]) for e in range(cfg.num_experts)])
+    assert (reap > 0).all() and np.corrcoef(reap, np.arange(1, cfg.num_experts + 1))[0, 1] > 0.9
+    tensors = {k: v.numpy() for k, v in w.items()}
+    cands = natscale.expert_candidates(tensors, ["NINT2", "NINT4", "NINT6"], imatrix=im, layers={0})
+    scheme, report = natscale.allocate(cands, 4.2, imatrix=im, tensors=tensors, sensitivity="reap")
+    bits = {}
+    for a in scheme["assignments"]:
+        bits.setdefault(a["expert_id"], []).append(int(a["family"][4:]))
+    mean_bits = np.array([np.mean(bits[e]) for e in sorted(bits)])
+    assert mean_bits[-3:].mean() >= mean_bits[:3].mean()  # the loud experts keep more bits than the quiet ones
+    assert report["sensitivity"] == "reap" and report["bits_per_weight"] <= 4.2 + 1e-6
+    with pytest.raises(ValueError):
+        natscale.allocate(cands, 4.2, sensitivity="reap")
