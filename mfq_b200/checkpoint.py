@@ -171,12 +171,14 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
                 max_seq_len: int = 8192, tp_rank: int = 0, tp_size: int = 1,
                 collective=None, use_graphs: bool = True, kv_budget_bytes: int | None = None,
                 yarn_context_extension: float | None = None, mtp_draft_tokens: int = 0, mtp_adaptive: bool = False, mtp_dynamic_depth: bool = False,
-                lp_rank: int = 0, lp_size: int = 1, layer_split=None):
+                lp_rank: int = 0, lp_size: int = 1, layer_split=None, expert_graphs: bool = False):
     """``.mfq`` -> (engine, tokenizer, config).  ``kv_budget_bytes`` caps the paged KV pool (see ``engine/kv_budget.py``);
     on a GPU it defaults to 90 % of the memory that is free once the weights are resident.  ``yarn_context_extension``
     (> 1) runs the model on that multiple of its trained context with YaRN-scaled rotary frequencies.
     ``mtp_draft_tokens`` (K > 0, only with a checkpoint that carries a ``predictor.*`` head): greedy rows decode by
-    draft/verify cycles; ``mtp_adaptive`` parks the cycles while they are slower than plain decoding."""
+    draft/verify cycles; ``mtp_adaptive`` parks the cycles while they are slower than plain decoding.
+    ``expert_graphs`` (with ``expert_slots``): decode inside CUDA graphs with the experts that are resident and settle
+    misses after the step (``LLMEngine.enable_expert_residency_graphs``); without it such a model decodes eagerly."""
     from .engine.llm_engine import LLMEngine
     from .models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
     from .server.tokenizer import tokenizer_from_assets
@@ -209,7 +211,8 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
             weights = MoeWeights.from_tensors(cfg, store, device, tp_rank, tp_size, expert_slots=expert_slots, native_4bit=native_4bit,
                                               lp_rank=lp_rank, lp_size=lp_size, layer_split=layer_split)
             model = MoeDecoderModel(cfg, weights, collective=collective)
-    # host-tier experts read the routing on the host every step, which a captured graph cannot do
+    # host-tier experts read the routing on the host every step, which a captured graph cannot do; with
+    # ``expert_graphs`` the step translates ids on the device instead and the engine settles misses afterwards
     num_pages = None
     if kv_budget_bytes is None and str(device).startswith("cuda"):
         from .engine.kv_budget import device_budget
@@ -220,10 +223,12 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
         num_pages = plan(budget_bytes=kv_budget_bytes, layers=model.local_layers + int(has_head), kv_heads=model.hk, head_dim=cfg.head_dim,
                          max_batch=max_batch, max_seq_len=max_seq_len).num_pages
     engine = LLMEngine(model, max_batch=max_batch, max_seq_len=max_seq_len, device=device, num_pages=num_pages,
-                       use_graphs=use_graphs and expert_slots is None,
+                       use_graphs=use_graphs and (expert_slots is None or expert_graphs),
                        mtp_draft_tokens=mtp_draft_tokens if getattr(weights, "mtp", None) is not None else 0,
                        mtp_adaptive=mtp_adaptive and tp_size == 1, mtp_dynamic_depth=mtp_dynamic_depth and tp_size == 1)  # ranks time their steps separately: they would
     #                                                                    park at different moments and fall out of lockstep
+    if expert_slots is not None and expert_graphs and not engine.enable_expert_residency_graphs():
+        engine.use_graphs = engine.use_graphs and not (hasattr(model, "residencies") and model.residencies())
     tokenizer = tokenizer_from_assets(assets, cfg.vocab_size)
     # structured output needs the vocabulary's byte strings; resolved on the first request that asks for it
     engine.set_token_bytes(lambda: tokenizer.token_bytes(cfg.vocab_size), tokenizer.stop_ids)

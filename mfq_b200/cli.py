@@ -522,6 +522,7 @@ def _cmd_serve(args) -> int:
             slots = _expert_slots_for(path, cache_gb)
         engine, tok, _cfg = load_engine(path, device, max_batch=args.continuous_batching, max_seq_len=ctx_size, **tp,
                                         native_4bit=args.native_4bit, expert_slots=slots,
+                                        expert_graphs=getattr(args, "moe_cache_graphs", False),
                                         kv_budget_bytes=int(kv_gb * (1 << 30)) if kv_gb else None,
                                         yarn_context_extension=args.yarn_context_extension,
                                         mtp_draft_tokens=args.mtp_draft_tokens, mtp_adaptive=args.mtp_adaptive,
@@ -903,6 +904,9 @@ def build_parser() -> argparse.ArgumentParser:
                    help="run NINT (<= 4 code bits) / MXFP4 projections through the 4-bit in-pipeline-decode GEMM instead of FP8")
     s.add_argument("--moe-gpu-cache-slots", type=int, default=None,
                    help="keep routed experts in pinned host memory behind an HBM arena of this many slots per layer")
+    s.add_argument("--moe-cache-graphs", action="store_true",
+                   help="with an expert cache: decode inside CUDA graphs with the resident experts and replay a step "
+                        "after uploading what it missed (without it such a model decodes eagerly, in waves)")
     s.add_argument("--mtp-draft-tokens", type=int, default=0,
                    help="draft this many tokens per cycle with the checkpoint's multi-token-prediction head (0: off)")
     s.add_argument("--mtp-dynamic-depth", action="store_true",

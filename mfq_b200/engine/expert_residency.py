@@ -16,6 +16,11 @@ route plan and no kernel changes:
 Reference: the residency manager, pinned expert arena and slot book of
 ``cpp_runtime/backends/cuda/runtime/moe_residency_manager.*``, ``storage/moe_expert_cache*``,
 ``engine/include/moe_cache_policy.h``; there the device polls host-written ready flags, here readiness is an event.
+
+Optimistic mode (``enable_optimistic``) keeps such a model inside CUDA graphs: a step translates ids through the device
+slot table as it is, routes to absent experts are skipped and counted in one device word; the engine reads that word
+after the step, and only when it is not zero uploads what was missing (``settle``), restores the few words of sequence
+state and runs the step again -- KV rows are simply rewritten.  Nothing on the device ever waits for an upload.
 """
 
 from __future__ import annotations
@@ -54,6 +59,7 @@ class ExpertResidency:
         self.copy_stream = torch.cuda.Stream(device=self.device) if cuda else None
         self.stats = {"hits": 0, "uploads": 0, "evictions": 0, "waves": 0, "upload_bytes": 0}
         self.bytes_per_expert = sum(t[0].numel() * t[0].element_size() for t in self.host)
+        self.optimistic = False
 
     # -- uploads ------------------------------------------------------------------------------------------------
     def _upload(self, expert: int, slot: int) -> None:
@@ -130,6 +136,54 @@ class ExpertResidency:
             self._make_resident(order)
             self._unpin(order)
         return order
+
+    # -- optimistic mode: device-only translation inside a captured step, misses settled afterwards ------------------
+    def enable_optimistic(self, miss_count: torch.Tensor) -> None:
+        """Steps may then be captured in a CUDA graph: :meth:`translate` never touches the host.  ``miss_count`` is one
+        int32 device word shared by all layers of a model; the engine reads it once after a step."""
+        self.optimistic = False  # the engine turns it on around a decode step; prefill and eager paths keep the waves
+        self.miss_count = miss_count
+        self.step_hist = torch.zeros(self.n, dtype=torch.int32, device=self.device)   # experts this step routed to
+        self.heat_dev = torch.zeros(self.n, dtype=torch.int32, device=self.device)    # the same, accumulated
+        self.stats.update({"replays": 0, "fallbacks": 0})
+
+    def begin_step(self) -> None:
+        self.step_hist.zero_()
+
+    def translate(self, topk_ids: torch.Tensor) -> torch.Tensor:
+        """Expert ids -> arena slots with what is resident NOW; routes to absent experts become -1 (the route plan skips
+        them) and are counted.  Device work only: a gather, two scatter-adds, a sum."""
+        valid = topk_ids >= 0
+        ids = topk_ids.long().clamp(min=0)
+        slot = self.slot_of_dev[ids]
+        ones = valid.reshape(-1).to(torch.int32)
+        self.step_hist.scatter_add_(0, ids.reshape(-1), ones)
+        self.heat_dev.scatter_add_(0, ids.reshape(-1), ones)
+        self.miss_count += (valid & (slot < 0)).sum().to(torch.int32)
+        return torch.where(valid, slot, torch.full_like(slot, -1)).to(torch.int32)
+
+    def settle(self) -> str:
+        """After a step whose shared miss counter was not zero: make every expert THIS layer routed to resident.
+        Returns ``"ok"`` (nothing was missing here), ``"replay"`` (uploads issued: run the step again) or
+        ``"fallback"`` (the step needs more distinct experts than there are slots: run it in waves)."""
+        hist = self.step_hist.cpu().numpy()
+        used = [int(e) for e in np.flatnonzero(hist)]
+        if all(self.slot_of[e] >= 0 for e in used):
+            return "ok"
+        if len(used) > self.slots:
+            self.stats["fallbacks"] += 1
+            return "fallback"
+        self.heat = self.heat * self.decay + hist
+        self._make_resident(used)
+        self._unpin(used)  # pinned only while the set was being placed: nothing uploads during a replay
+        self.stats["replays"] += 1
+        return "replay"
+
+    def absorb_heat(self) -> None:
+        """Fold the device-side usage counts into the host heat (call between steps, before :meth:`rebalance`)."""
+        if getattr(self, "heat_dev", None) is not None:
+            self.heat = self.heat * self.decay + self.heat_dev.cpu().numpy()
+            self.heat_dev.zero_()
 
     # -- between steps ------------------------------------------------------------------------------------------
     def rebalance(self, max_swaps: int = 4, hysteresis: float = 0.25) -> list[tuple[int, int]]:

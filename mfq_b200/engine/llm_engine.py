@@ -485,9 +485,62 @@ class LLMEngine:
         rows = max(1, getattr(self.model, "hq", hk) // hk) * q_len
         return attn_splits_for(b, hk, min(self.max_seq_len, longest), getattr(self.model.cfg, "head_dim", 128), rows)
 
+    def enable_expert_residency_graphs(self) -> bool:
+        """Let a model whose experts live behind an HBM slot arena decode inside CUDA graphs: its layers translate expert
+        ids through the device slot table without asking the host, and :meth:`decode_step` settles misses after the step
+        (upload, restore ``seq_lens`` / ``sampled``, run the step again).  Returns whether this engine can do that: the
+        model has such layers and no draft head (draft/verify cycles would still route on the host)."""
+        res = self.model.residencies() if hasattr(self.model, "residencies") else []
+        if not res or self.mtp_k or self.rec_state is not None:
+            return False
+        self.moe_miss_count = torch.zeros(1, dtype=torch.int32, device=self.device)
+        for r in res:
+            r.enable_optimistic(self.moe_miss_count)
+        self.residency_stats = {"steps": 0, "replays": 0, "fallbacks": 0}
+        return True
+
     def decode_step(self, b: int, stochastic: bool = False, constrained: bool = False, keep_head: bool = False) -> None:
         """Advance the active rows among ``[0, b)`` by one token (result in ``self.sampled[:b]``, on the device).
         ``constrained``: add the rows' token-constraint bias to the logits before sampling (a graph variant of its own)."""
+        if getattr(self, "moe_miss_count", None) is None:
+            self._decode_step_once(b, stochastic, constrained, keep_head)
+            return
+        # optimistic expert residency: the step runs with the experts that are resident; if a route met an absent one,
+        # bring the step's experts in and run it again from the same sequence state (its KV rows are rewritten).  A
+        # missing expert upstream changes the routing downstream, so a cold start may take a replay per layer: after a
+        # few the step runs in waves instead, which also leaves its experts resident.
+        res = self.model.residencies()
+        snap = (self.seq_lens.clone(), self.sampled.clone())
+        self.residency_stats["steps"] += 1
+
+        def restore():
+            self.seq_lens.copy_(snap[0])
+            self.sampled.copy_(snap[1])  # the sampler's counter is the row length: a replay draws the same token
+
+        for r in res:
+            r.optimistic = True
+        try:
+            for _attempt in range(self.residency_replays + 1):
+                self.moe_miss_count.zero_()
+                self._decode_step_once(b, stochastic, constrained, keep_head)
+                if int(self.moe_miss_count.item()) == 0:
+                    return
+                verdicts = [r.settle() for r in res]
+                restore()
+                if "fallback" in verdicts:
+                    break
+                self.residency_stats["replays"] += 1
+        finally:
+            for r in res:
+                r.optimistic = False
+        # in waves, outside the graphs: always right, whatever the step routes to
+        self.residency_stats["fallbacks"] += 1
+        self._bind_state()
+        self._decode_body(b, stochastic, constrained, keep_head)
+
+    residency_replays = 3
+
+    def _decode_step_once(self, b: int, stochastic: bool = False, constrained: bool = False, keep_head: bool = False) -> None:
         self._bind_state()
         if not self.use_graphs:
             self._decode_body(b, stochastic, constrained, keep_head)

@@ -241,6 +241,16 @@ class MoeDecoderModel(LlamaModel):
                                               hidden=cfg.hidden_size, max_tokens=per_rank)
         self.ep_min_tokens = 16 * self.tp if min_tokens is None else min_tokens
 
+    def residencies(self) -> list:
+        """The expert-residency managers of this model's layers (empty when every expert lives in HBM)."""
+        return [l.moe.residency for l in self.w.layers if getattr(l, "moe", None) is not None and l.moe.residency is not None]
+
+    def forward(self, step, cache, **kw):
+        for r in self.residencies():
+            if r.optimistic:
+                r.begin_step()  # inside a captured step this is a memset node: each replay starts its own histogram
+        return super().forward(step, cache, **kw)
+
     def _ffn_all_to_all(self, h, ffn: MoeFfn, xq, xs, ids, wt):
         """Token-sharded expert layer: my slice of the rows goes through dispatch -> local experts -> combine, the
         finished slices are gathered back into the replicated residual stream.  A replicated shared expert runs on my
@@ -300,8 +310,13 @@ class MoeDecoderModel(LlamaModel):
             # host-tier experts: translate expert -> arena slot (uploading what is missing), in waves if needed
             local = ids - ffn.e_lo
             local = torch.where((local >= 0) & (local < ffn.residency.n), local, torch.full_like(local, -1))
-            part = ffn.residency.run(local, lambda ids_slot, arena: moe_ops.moe_ffn_fp8(
-                xq, xs, ids_slot, wt, arena.gate_up, arena.gate_up_scale, arena.down, arena.down_scale, e_lo=0, base=None).float())
+            if ffn.residency.optimistic:
+                arena = ffn.residency.arena  # one pass over what is resident; the engine settles misses after the step
+                part = moe_ops.moe_ffn_fp8(xq, xs, ffn.residency.translate(local), wt, arena.gate_up, arena.gate_up_scale,
+                                           arena.down, arena.down_scale, e_lo=0, base=None).float()
+            else:
+                part = ffn.residency.run(local, lambda ids_slot, arena: moe_ops.moe_ffn_fp8(
+                    xq, xs, ids_slot, wt, arena.gate_up, arena.gate_up_scale, arena.down, arena.down_scale, e_lo=0, base=None).float())
             if part is None:  # no token of this step uses a local expert
                 part = torch.zeros_like(h, dtype=torch.float32)
             out = h.float() + part + (shared.float() if shared is not None else 0)

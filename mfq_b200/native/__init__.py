@@ -122,7 +122,7 @@ class NintRows:
         self.rows, self.row_len = lib().mfq_nint_rows(self._h), lib().mfq_nint_row_len(self._h)
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # module globals are already cleared at interpreter exit
             lib().mfq_nint_close(self._h)
             self._h = None
 
@@ -278,7 +278,7 @@ class SlotBook:
             raise ValueError(_err())
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # module globals are already cleared at interpreter exit
             lib().mfq_slotbook_close(self._h)
             self._h = None
 
@@ -314,7 +314,7 @@ class JsonVocabulary:
         self.token_bytes = token_bytes
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # module globals are already cleared at interpreter exit
             lib().mfq_json_vocab_close(self._h)
             self._h = None
 

@@ -96,3 +96,45 @@ def test_cache_profile_warms_a_fresh_arena(tmp_path):
     other = model()
     other.w.layers.pop()
     assert mcp.apply(other, doc) == 0 and mcp.load(tmp_path / "missing.json") is None
+
+
+def test_optimistic_translate_counts_misses_and_settle_makes_the_step_whole():
+    """Device-only translation: absent experts are skipped and counted; after ``settle`` the same step has no miss and
+    equals the all-resident answer; a step with more distinct experts than slots asks for the wave path."""
+    n, slots = 10, 4
+    gu, gus, dn, dns = _fake_experts(n)
+    res = ExpertResidency(gu, gus, dn, dns, slots=slots, device="cpu")
+    miss = torch.zeros(1, dtype=torch.int32)
+    res.enable_optimistic(miss)
+    assert res.optimistic is False  # only the engine's decode step turns it on
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn((4, 8), generator=g)
+    wt = torch.rand((4, 2), generator=g)
+    ids = torch.tensor([[0, 1], [1, 2], [-1, 2], [3, 1]], dtype=torch.int32)  # -1: an expert of another rank
+    want = _ffn(x, ids, wt, gu, dn)
+
+    def step():
+        res.begin_step()
+        miss.zero_()
+        ids_slot = res.translate(ids)
+        return ids_slot, _ffn(x, ids_slot, wt, res.arena.gate_up, res.arena.down)
+
+    ids_slot, got = step()
+    assert int(miss) == 7 and bool((ids_slot == -1).all()) and float(got.abs().max()) == 0.0  # cold arena: nothing ran
+    assert res.step_hist.tolist()[:4] == [1, 3, 2, 1]
+    assert res.settle() == "replay" and res.stats["uploads"] == 4
+    ids_slot, got = step()
+    assert int(miss) == 0 and torch.allclose(got, want, atol=1e-6)
+    assert bool((ids_slot[2] == torch.tensor([-1, int(res.slot_of[2])])).all())
+    assert res.settle() == "ok" and res.stats["uploads"] == 4 and res.stats["replays"] == 1
+    # nothing stays pinned after a settle: a later step may evict any of them
+    assert all(res.book.pins(e) == 0 for e in range(4)) if hasattr(res.book, "pins") else True
+    wide = torch.tensor([[4, 5], [6, 7], [8, 9], [0, 1]], dtype=torch.int32)
+    res.begin_step()
+    miss.zero_()
+    res.translate(wide)
+    assert int(miss) == 6 and res.settle() == "fallback" and res.stats["fallbacks"] == 1
+    # usage counted on the device reaches the host heat between steps
+    before = res.heat.copy()
+    res.absorb_heat()
+    assert res.heat[1] > before[1] * res.decay and int(res.heat_dev.sum()) == 0

@@ -71,3 +71,34 @@ def test_host_tier_experts_match_all_resident():
     err = (full - tiered).abs()
     # same FP8 experts; the waves round their partial sums to bf16 separately, which can flip a later layer's routing
     assert float(err.mean()) <= 0.02 * scale and float(err.max(-1).values.median()) <= 0.1 * scale
+
+
+@pytest.mark.parametrize("slots", [5, 3])
+def test_expert_residency_under_graphs_replays_misses(slots):
+    """An expert arena of ``slots`` of 8 experts decoding inside CUDA graphs: ids are translated on the device, a step
+    that met an absent expert is run again after the upload (or in waves when it needs more experts than slots), and
+    the tokens equal the eager wave-by-wave engine's."""
+    import torch
+    from gpu_common import check_status, require_gpu_lib
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from mfq_b200.models.moe_lm import MoeConfig, init_weights
+    require_gpu_lib()
+    cfg = MoeDecoderConfig.tiny()
+    tensors = init_weights(MoeConfig(head_dim=128, hidden_size=256, moe_intermediate=128, shared_intermediate=128), seed=4, std=0.05)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)) for n in (17, 40)]
+
+    eager = LLMEngine(MoeDecoderModel(cfg, MoeWeights.from_tensors(cfg, tensors, "cuda", expert_slots=slots)),
+                      max_batch=2, max_seq_len=96, use_graphs=False)
+    want = eager.generate(prompts, 12).tokens
+    eng = LLMEngine(MoeDecoderModel(cfg, MoeWeights.from_tensors(cfg, tensors, "cuda", expert_slots=slots)),
+                    max_batch=2, max_seq_len=96, use_graphs=True)
+    assert eng.enable_expert_residency_graphs()
+    got = eng.generate(prompts, 12).tokens
+    check_status()
+    assert torch.equal(got, want)
+    st = eng.residency_stats
+    assert st["steps"] >= 11 and len(eng.graphs) >= 1
+    assert st["replays"] + st["fallbacks"] < st["steps"] * eng.residency_replays  # most steps ran once, from the graph
+    res = eng.model.residencies()
+    assert all(not r.optimistic for r in res) and sum(r.stats["uploads"] for r in res) >= slots
