@@ -207,12 +207,13 @@ def check_codecs() -> dict:
     w = _w()
     out, ok = {}, True
     limits = {"NINT2": 0.6, "NINT3": 0.3, "NINT4": 0.15, "NINT5": 0.08, "NINT6": 0.04, "NINT8": 0.02, "NVQ3": 0.5, "MXFP4": 0.2,
-              "FP8": 0.07, "NPQ0-S": 1.5, "NPQ0-L": 1.5, "NVQ1-L": 1.2, "NVQ1-S": 1.2}
+              "FP8": 0.07, "NPQ0-S": 1.5, "NPQ0-L": 1.5, "NVQ1-L": 1.2, "NVQ1-S": 1.2,
+              "NEPQ0-S": 1.5, "NEPQ1-S": 1.2, "NEPQ1-A": 1.2}
     for fam, lim in limits.items():
         t = quantize_matrix(w, parse_profiles(fam)[0])
         dtype, blob = F.pack_tensor(t)
         again = F.pack_tensor(F.unpack_tensor(dtype, blob))[1]
-        err = _rel_np(F.dequantize(F.unpack_tensor(dtype, blob)), w)
+        err = _rel_np(F.dequantize(F.unpack_tensor(dtype, blob)).reshape(w.shape), w)
         good = again == blob and err <= lim
         ok &= good
         out[fam] = {"bytes": len(blob), "bits_per_weight": round(8 * len(blob) / w.size, 3), "max_rel_err": round(err, 4), "ok": good}

@@ -188,6 +188,7 @@ class ExpertResidency:
     # -- between steps ------------------------------------------------------------------------------------------
     def rebalance(self, max_swaps: int = 4, hysteresis: float = 0.25) -> list[tuple[int, int]]:
         """Swap cold residents for hotter absent experts; returns the (evicted, loaded) pairs."""
+        self.absorb_heat()
         swaps = native.moe_rank_swaps(self.heat, (self.slot_of >= 0).astype(np.uint8), max_swaps, hysteresis)
         done = []
         for evict, load in swaps:

@@ -28,6 +28,8 @@ def _residencies(model) -> dict[int, object]:
 
 
 def collect(model, name: str = "") -> dict:
+    for r in _residencies(model).values():
+        r.absorb_heat()  # usage counted on the device by graph-captured steps
     layers = {str(i): {"heat": [round(float(h), 4) for h in r.heat], "slots": r.slots, "stats": dict(r.stats)}
               for i, r in _residencies(model).items()}
     return {"format": FORMAT, "model": name, "rank": getattr(model.w, "tp_rank", 0), "layers": layers}

@@ -21,6 +21,9 @@ def dequantize(t):
     from .nvq1 import Nvq1Tensor, dequantize_nvq1
     if isinstance(t, Nvq1Tensor):
         return dequantize_nvq1(t)
+    from .nepq import NepqTensor, dequantize_nepq
+    if isinstance(t, NepqTensor):
+        return dequantize_nepq(t)  # logical coordinates: a rotation is undone
     from .nint8zero import Nint8ZeroTensor, dequantize_nint8_zero
     if isinstance(t, Nint8ZeroTensor):
         return dequantize_nint8_zero(t)

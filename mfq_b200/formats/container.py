@@ -28,7 +28,7 @@ from typing import Any
 
 import numpy as np
 
-from . import fp8sq, mfe, mx, mxfp4sq, nint, nint8zero, npq0, nvq, nvq1
+from . import fp8sq, mfe, mx, mxfp4sq, nepq, nint, nint8zero, npq0, nvq, nvq1
 from .dense import DENSE_DTYPES, pack_dense, unpack_dense
 
 MFQ_MAGIC = b"MFQ1"
@@ -90,6 +90,8 @@ def pack_tensor(t) -> tuple[str, bytes]:
         return t.variant.label, npq0.pack_npq0(t)
     if isinstance(t, nvq1.Nvq1Tensor):
         return t.variant.label, nvq1.pack_nvq1(t)
+    if isinstance(t, nepq.NepqTensor):
+        return nepq.NEPQ_DTYPE, nepq.pack_nepq(t)
     if isinstance(t, nint.NintTensor):
         return nint.NINT_DTYPE, nint.pack_nint(t)
     if isinstance(t, (nvq.NvqTensor, nvq.NvqJscTensor)):
@@ -112,6 +114,8 @@ def unpack_tensor(dtype: str, blob):
         return npq0.unpack_npq0(blob)
     if dtype in nvq1.DTYPES:
         return nvq1.unpack_nvq1(blob)
+    if dtype == nepq.NEPQ_DTYPE:
+        return nepq.unpack_nepq(blob)
     dtype = canonical_dtype(dtype)
     if dtype == MFE_DTYPE:
         return mfe.unpack_mfe(blob, unpack_tensor)

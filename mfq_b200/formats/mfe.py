@@ -48,6 +48,21 @@ class MfeTensor:
         return where
 
 
+_ROTATION = struct.Struct("<4sIIQ")
+
+
+def rotation_runtime(tensor) -> bytes:
+    """The runtime record of a pool whose tensor is a rotated NEPQ cohort: ``"HSG1" u32 K, u32 block, u64 seed`` and the
+    +-1 diagonal as K int8 values, so that a runtime can rotate activations without deriving the diagonal
+    (``mfq/formats/io.py:675-696`` of the reference); empty for every other pool."""
+    from .nepq import NepqTensor, rotation_signs
+    if not isinstance(tensor, NepqTensor) or not tensor.rotation_block:
+        return b""
+    k = int(tensor.shape[2])
+    return _ROTATION.pack(b"HSG1", k, int(tensor.rotation_block), int(tensor.rotation_seed)) + \
+        rotation_signs(k, tensor.rotation_block, tensor.rotation_seed).tobytes()
+
+
 def pack_mfe(t: MfeTensor, pack_tensor: Callable[[Any], tuple[str, bytes]]) -> bytes:
     n, out, k = t.shape
     parts = [_HEAD.pack(_MAGIC, n, out, k, len(t.pools))]
@@ -59,7 +74,8 @@ def pack_mfe(t: MfeTensor, pack_tensor: Callable[[Any], tuple[str, bytes]]) -> b
         name = dtype.encode("ascii")
         if not 0 < len(name) <= 32:
             raise ValueError(f"invalid MFE pool dtype {dtype!r}")
-        parts += [_POOL.pack(ids.size, len(name), len(payload), len(p.runtime)), ids.tobytes(), name, p.runtime, payload]
+        runtime = p.runtime or rotation_runtime(p.tensor)
+        parts += [_POOL.pack(ids.size, len(name), len(payload), len(runtime)), ids.tobytes(), name, runtime, payload]
     return b"".join(parts)
 
 
@@ -86,6 +102,8 @@ def unpack_mfe(blob, unpack_tensor: Callable[[str, Any], Any]) -> MfeTensor:
         off += plen
         if isinstance(tensor, MfeTensor):
             raise ValueError("nested MFE pool")
+        if runtime[:4] == b"HSG1" and runtime != rotation_runtime(tensor):
+            raise ValueError("MFE pool: the rotation record does not match its NEPQ tensor")
         pools.append(MfePool(ids, tensor, runtime))
     if off != len(blob):
         raise ValueError(f"MFE blob has {len(blob) - off} trailing bytes")

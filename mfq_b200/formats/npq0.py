@@ -112,12 +112,32 @@ def _check(t: Npq0Tensor) -> tuple[int, int, int]:
     return rows, groups, vecs
 
 
-def _pack_tables(t: Npq0Tensor) -> bytes:
-    v = t.variant
+def pack_tables(v: Npq0Variant, scale_lut, first, second) -> bytes:
+    """One table set as it sits in a blob: the 64-byte header with the scale ladder, then both int8 codebooks."""
     head = bytearray(_TABLE_HEADER)
     head[0:6] = bytes([v.table_version, v.states, v.first_bits, v.second_bits, GROUP, VEC])
-    head[8 : 8 + 2 * v.states] = np.asarray(t.scale_lut, dtype="<f2").tobytes()
-    return bytes(head) + np.asarray(t.first_codebooks, dtype=np.int8).tobytes() + np.asarray(t.second_codebooks, dtype=np.int8).tobytes()
+    head[8 : 8 + 2 * v.states] = np.asarray(scale_lut, dtype=np.float32).astype("<f2").tobytes()
+    return bytes(head) + np.asarray(first, dtype=np.int8).tobytes() + np.asarray(second, dtype=np.int8).tobytes()
+
+
+def unpack_tables(v: Npq0Variant, raw) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """Inverse of :func:`pack_tables` over exactly ``v.table_bytes`` bytes: (scale ladder fp32, first, second)."""
+    raw = bytes(raw)
+    if len(raw) != v.table_bytes:
+        raise ValueError(f"{v.label}: a table set is {v.table_bytes} bytes, got {len(raw)}")
+    head = raw[:_TABLE_HEADER]
+    if tuple(head[:6]) != (v.table_version, v.states, v.first_bits, v.second_bits, GROUP, VEC) or any(head[6:8]) or \
+            any(head[8 + 2 * v.states :]):
+        raise ValueError(f"{v.label}: unsupported table profile")
+    lut = np.frombuffer(head, dtype="<f2", count=v.states, offset=8).astype(np.float32)
+    n1 = v.states * (1 << v.first_bits) * SUB
+    first = np.frombuffer(raw, dtype=np.int8, count=n1, offset=_TABLE_HEADER).reshape(v.states, 1 << v.first_bits, SUB).copy()
+    second = np.frombuffer(raw, dtype=np.int8, offset=_TABLE_HEADER + n1).reshape(v.states, 1 << v.second_bits, SUB).copy()
+    return lut, first, second
+
+
+def _pack_tables(t: Npq0Tensor) -> bytes:
+    return pack_tables(t.variant, t.scale_lut, t.first_codebooks, t.second_codebooks)
 
 
 def pack_npq0(t: Npq0Tensor) -> bytes:
@@ -147,17 +167,10 @@ def unpack_npq0(blob) -> Npq0Tensor:
     off += 8 * ndim
     rows = struct.unpack_from("<I", blob, off)[0]
     off += 4
-    head = bytes(blob[off : off + _TABLE_HEADER])
-    if tuple(head[:6]) != (v.table_version, v.states, v.first_bits, v.second_bits, GROUP, VEC) or any(head[6:8]) or \
-            any(head[8 + 2 * v.states :]):
-        raise ValueError(f"{v.label}: unsupported table profile")
-    lut = np.frombuffer(head, dtype="<f2", count=v.states, offset=8).astype(np.float32)
-    off += _TABLE_HEADER
-    n1, n2 = v.states * (1 << v.first_bits) * SUB, v.states * (1 << v.second_bits) * SUB
-    first = np.frombuffer(blob, dtype=np.int8, count=n1, offset=off).reshape(v.states, 1 << v.first_bits, SUB).copy()
-    off += n1
-    second = np.frombuffer(blob, dtype=np.int8, count=n2, offset=off).reshape(v.states, 1 << v.second_bits, SUB).copy()
-    off += n2
+    if off + v.table_bytes > len(blob):
+        raise ValueError(f"{v.label}: truncated tables")
+    lut, first, second = unpack_tables(v, blob[off : off + v.table_bytes])
+    off += v.table_bytes
     anchors = np.frombuffer(blob, dtype="<f2", count=rows, offset=off).astype(np.float32)
     off += 2 * rows
     groups, vecs = math.ceil(neuron_len / GROUP), neuron_len // VEC

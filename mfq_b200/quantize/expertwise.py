@@ -46,7 +46,8 @@ class ExpertProfile:
         if self.nvq is not None:
             return self.nvq.bpw(4096, out=4096)
         return {"MXFP4": 4.25, "FP8": 8.0, "BF16": 16.0, "NPQ0-S": 0.84, "NPQ0-L": 1.0, "NVQ1-L": 1.55, "NVQ1-L-S4": 1.59,
-                "NVQ1-S": 1.34}[self.family]
+                "NVQ1-S": 1.34, "NEPQ0-S": 0.88, "NEPQ0-L": 1.04, "NEPQ1-S": 1.42, "NEPQ1-L": 1.63, "NEPQ0-A": 0.96,
+                "NEPQ1-A": 1.61}[self.family]
 
 
 def parse_profiles(text: str) -> tuple[ExpertProfile, ...]:
@@ -61,7 +62,8 @@ def parse_profiles(text: str) -> tuple[ExpertProfile, ...]:
             out.append(ExpertProfile(name, nint=NintSpec(bits, gs, k)))
         elif name in _NVQ_FAMILIES:
             out.append(ExpertProfile(name, nvq=NvqSpec(_NVQ_FAMILIES[name])))
-        elif name in ("MXFP4", "FP8", "BF16", "NPQ0-S", "NPQ0-L", "NVQ1-L", "NVQ1-L-S4", "NVQ1-S"):
+        elif name in ("MXFP4", "FP8", "BF16", "NPQ0-S", "NPQ0-L", "NVQ1-L", "NVQ1-L-S4", "NVQ1-S", "NEPQ0-S", "NEPQ0-L", "NEPQ1-S",
+                      "NEPQ1-L", "NEPQ0-A", "NEPQ1-A"):
             out.append(ExpertProfile(name))
         else:
             raise ValueError(f"unsupported expert precision {name!r}")
@@ -93,6 +95,10 @@ def quantize_matrix(w, profile: ExpertProfile, device="cpu", importance=None):
         from ..formats.nvq1 import quantize_nvq1
         w = np.asarray(w, dtype=np.float32)
         return quantize_nvq1(w, profile.family, axis=w.ndim - 2, importance=importance, device=str(device))
+    if profile.family.startswith("NEPQ"):
+        from ..formats.nepq import quantize_nepq
+        w = np.asarray(w, dtype=np.float32)
+        return quantize_nepq(w if w.ndim == 3 else w[None], profile.family, device=str(device))  # the experts share one table pool
     if profile.family == "BF16":
         from ..formats.dense import to_bf16
         return to_bf16(np.asarray(w, dtype=np.float32))
@@ -107,5 +113,6 @@ def quantize_expertwise(weights, assignment: np.ndarray, profiles: tuple[ExpertP
     for pi, profile in enumerate(profiles):
         ids = np.flatnonzero(assignment == pi).astype(np.int32)
         if ids.size:
-            pools.append(MfePool(ids, quantize_matrix(w[ids].reshape(ids.size * out, k), profile, device)))
+            stacked = profile.family.startswith("NEPQ")  # coded as [experts, out, K]: bank ids and anchors are per expert row
+            pools.append(MfePool(ids, quantize_matrix(w[ids] if stacked else w[ids].reshape(ids.size * out, k), profile, device)))
     return MfeTensor((n, out, k), tuple(pools))
