@@ -60,7 +60,7 @@ def read_hf_directory(path) -> tuple[dict, dict[str, np.ndarray], dict[str, byte
 def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", expert_mix: str = "", seed: int = 20260908,
                      device: str = "cpu", progress=None, widths: dict[str, int | None] | None = None,
                      imatrix: dict[str, np.ndarray] | None = None, scheme: dict | None = None, resume=None,
-                     fp8_sq_bits: float = 0.0, row_widths: dict | None = None) -> dict[str, object]:
+                     fp8_sq_bits: float = 0.0, row_widths: dict | None = None, mxfp4_sq_bits: float = 0.0) -> dict[str, object]:
     """Apply the quantization plan: routed experts by the seeded mix (or the dense rule), 2-D weights by ``dense``
     (nint2..8 / nvq3 / mxfp4 / fp8 / bf16), norms / router / embeddings-as-requested stay bf16.
     ``widths`` (a preset plan: tensor -> NINT width, None = keep) overrides ``dense`` per tensor; ``imatrix`` supplies
@@ -69,9 +69,11 @@ def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", ex
     every finished tensor and hands back the ones a previous, interrupted run finished for the same source and plan.
     ``fp8_sq_bits`` (1..8, 0 = off): dense FP8 tensors are re-encoded with per-row scalar palettes averaging that many
     code bits per weight (``quantize/fp8_sq.py``; the imatrix, if given, weights the palette fit).  ``row_widths``
-    (``mfq.inint-rows.v1`` from ``mfq calibrate inint``): the listed tensors become NINT with a code width per output row."""
+    (``mfq.inint-rows.v1`` from ``mfq calibrate inint``): the listed tensors become NINT with a code width per output row.
+    ``mxfp4_sq_bits`` (about 1.3 .. 4.25, 0 = off): every MXFP4 matrix -- dense, or a pool of routed experts -- is re-coded
+    as MXFP4-SQ with per-row widths averaging that many stored bits per weight (``quantize/mxfp4_sq.py``)."""
     if resume is not None:
-        if fp8_sq_bits or row_widths is not None:
+        if fp8_sq_bits or mxfp4_sq_bits or row_widths is not None:
             raise ValueError("--fp8-sq-bits / --row-widths cannot be combined with a resumable run yet")
         return _quantize_resumable(tensors, resume, dense=dense, expert_mix=expert_mix, seed=seed, device=device,
                                    progress=progress, widths=widths, imatrix=imatrix, scheme=scheme)
@@ -123,6 +125,20 @@ def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", ex
                 from .quantize.fp8_sq import quantize_fp8_sq
                 weight = input_importance(imatrix, name) if imatrix is not None else None
                 out[name] = quantize_fp8_sq(out[name], float(fp8_sq_bits), weight)
+    if mxfp4_sq_bits:
+        from .formats.mfe import MfePool, MfeTensor
+        from .formats.mx import MXFP4_DTYPE, MxTensor
+        from .quantize.mxfp4_sq import quantize_mxfp4_sq
+        is_mx = lambda t: isinstance(t, MxTensor) and t.dtype == MXFP4_DTYPE
+        for name, t in list(out.items()):
+            if progress and (is_mx(t) or isinstance(t, MfeTensor)):
+                progress(name + " [mxfp4-sq]")
+            if is_mx(t):
+                out[name] = quantize_mxfp4_sq(t, target_bits=float(mxfp4_sq_bits))
+            elif isinstance(t, MfeTensor) and any(is_mx(p.tensor) for p in t.pools):
+                out[name] = MfeTensor(t.shape, tuple(
+                    MfePool(p.expert_ids, quantize_mxfp4_sq(p.tensor, target_bits=float(mxfp4_sq_bits)), p.runtime) if is_mx(p.tensor) else p
+                    for p in t.pools))
     return out
 
 

@@ -128,12 +128,12 @@ def _cmd_quantize(args) -> int:
         gs, k = expertwise._NINT_PRESETS[bits]
         expertwise._NINT_PRESETS[bits] = (args.groupsize or gs, args.sub_bits or k)
     store = None
-    if not args.no_temp and not args.fp8_sq_bits and row_widths is None:
+    if not args.no_temp and not args.fp8_sq_bits and not args.mxfp4_sq_bits and row_widths is None:
         from .quantize.resume import ResumeStore
         store = ResumeStore(str(out) + ".tmp", resume=args.resume, keep=args.keep_temp)
     q = quantize_tensors(tensors, dense=dense, expert_mix=args.random_expert_mix, seed=args.random_expert_mix_seed,
                          widths=widths, imatrix=imatrix, scheme=scheme, device=args.device, resume=store,
-                         fp8_sq_bits=args.fp8_sq_bits, row_widths=row_widths,
+                         fp8_sq_bits=args.fp8_sq_bits, row_widths=row_widths, mxfp4_sq_bits=args.mxfp4_sq_bits,
                          progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
     extra = {"quantization": {"dense": dense, "preset": args.preset or None, "imatrix": bool(imatrix), "ew_scheme": bool(scheme), "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
                               "random_expert_mix_seed": args.random_expert_mix_seed if args.random_expert_mix else None}}
@@ -746,6 +746,9 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--fp8-sq-bits", type=float, default=0.0,
                    help="with --format fp8: re-encode the E4M3 tensors with per-row scalar palettes (FP8-128SQ rows SQ1..SQ8) "
                         "averaging this many code bits per weight")
+    q.add_argument("--mxfp4-sq-bits", type=float, default=0.0,
+                   help="re-code every MXFP4 matrix (dense with --format mxfp4, expert pools of a mix) as MXFP4-SQ: rows of 1..4 "
+                        "symbol bits over catalogue palettes, averaging this many stored bits per weight; still legal MXFP4 once decoded")
     q.add_argument("--split-max-size", help="limit of tensor payload per output shard, N[M|G]")
     q.add_argument("--split-max-tensors", type=int, default=0, help="limit of tensors per output shard")
     q.add_argument("--dry-run", action="store_true")

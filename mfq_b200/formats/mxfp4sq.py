@@ -13,10 +13,18 @@ Layout (parity: ``mfq/formats/mxfp4_sq.py:161-197,275-360`` of the reference)::
     block selectors (sq_rows*cols/32 x 1 bit), state scales (sq_rows*8 x 2 bit),
     state palettes (sq_rows*8 x 5 bit), native E8M0 scales (sq4_rows x cols/32)
 
-This module reads and writes the container and decodes the ``q = 4`` rows (what the
-tensor-core MXFP4 path consumes).  Rows with ``q < 4`` are carried through
-byte-exactly; expanding them needs the palette catalogue of the offline
-re-quantizer, which is outside the serving path.
+Decoding a ``q < 4`` row (``mfq/kernels/cuda/mxfp4_sq.cu:43-99`` of the reference).  A block of
+32 symbols names one of the row's eight STATES with three bits: the block's selector bit is
+bit 2, and bits 0-1 are the XOR of the low two bits of the block's symbols (for ``q = 1`` the
+XOR of the 16 two-bit pairs of neighbouring symbols) -- two bits of side information that cost
+no storage; the encoder steers them by nudging a symbol.  State ``s`` gives the block its
+E8M0 exponent ``matrix_scale_base + state_scale[s]`` and its palette ``state_palette[s]``, one
+of 32 catalogue palettes for that ``q``; a palette maps a symbol to an E2M1 nibble.  So every
+row expands to legal native MXFP4 (:func:`to_mxfp4`), which the tensor-core MXFP4 path runs.
+
+The catalogue: a palette is a ``2**q``-subset of the 15 distinct E2M1 values in ascending
+order; the subsets are numbered in lexicographic order of their positions and 32 numbers per
+``q`` are fixed by the format (``mfq/quantize/mxfp4_sq.py:47-153``).
 """
 
 from __future__ import annotations
@@ -29,7 +37,49 @@ import numpy as np
 from .bitstream import pack_bits, unpack_bits, packed_nbytes
 from .mx import E2M1_VALUES, MXFP4_DTYPE, MxTensor, e8m0_to_float
 
+import itertools
+
 MXFP4_SQ_DTYPE = "MXFP4-SQ"
+# E2M1 nibbles of the 15 distinct values in ascending order: -6 .. -0.5, 0, 0.5 .. 6
+ORDERED_NIBBLES = np.array([0xF, 0xE, 0xD, 0xC, 0xB, 0xA, 0x9, 0x0, 0x1, 0x2, 0x3, 0x4, 0x5, 0x6, 0x7], dtype=np.uint8)
+_CATALOGUE_IDS = {
+    1: (12, 26, 38, 11, 13, 58, 22, 48, 25, 23, 67, 21, 37, 24, 75, 20, 8, 59, 68, 9, 76, 7, 19, 36, 46, 55, 63, 70, 35, 47, 56, 45),
+    2: (120, 127, 187, 504, 512, 518, 547, 548, 558, 562, 592, 767, 806, 833, 966, 967, 192, 1112, 971, 802, 559, 240, 112,
+        226, 232, 182, 188, 121, 505, 848, 0, 1),
+    3: (499, 2407, 523, 5738, 1196, 2001, 5497, 4705, 1087, 2400, 2402, 1077, 1078, 4116, 5503, 2002, 3726, 2010, 5498, 4117,
+        5552, 4706, 500, 1483, 3717, 3727, 1478, 4818, 5811, 2003, 2989, 2035),
+}
+
+
+def _catalogue(q: int) -> np.ndarray:
+    """[32, 2**q] E2M1 nibbles: palette ``i`` is the ``_CATALOGUE_IDS[q][i]``-th ``2**q``-subset of the ordered values."""
+    want = {cid: slot for slot, cid in enumerate(_CATALOGUE_IDS[q])}
+    out = np.zeros((32, 1 << q), dtype=np.uint8)
+    last = max(want)
+    for number, positions in enumerate(itertools.combinations(range(15), 1 << q)):
+        slot = want.get(number)
+        if slot is not None:
+            out[slot] = ORDERED_NIBBLES[list(positions)]
+        if number >= last:
+            break
+    out.setflags(write=False)
+    return out
+
+
+PALETTES = {q: _catalogue(q) for q in (1, 2, 3)}
+
+
+def unpack_symbols(stream: bytes, cols: int, q: int) -> np.ndarray:
+    """One row's symbol stream -> [cols] uint8 (LSB first)."""
+    return unpack_bits(stream, 0, cols, q)[0].astype(np.uint8)
+
+
+def block_tags(symbols: np.ndarray, q: int) -> np.ndarray:
+    """``symbols [..., blocks, 32]`` -> the two tag bits every block carries in its symbols."""
+    s = np.asarray(symbols, dtype=np.uint8)
+    if q == 1:
+        return np.bitwise_xor.reduce(s[..., 0::2], axis=-1) | (np.bitwise_xor.reduce(s[..., 1::2], axis=-1) << 1)
+    return np.bitwise_xor.reduce(s & 3, axis=-1)
 _HEAD = struct.Struct("<4sBBHQQ")
 _MAGIC = b"SQV2"
 
@@ -115,11 +165,39 @@ def unpack_mxfp4sq(blob) -> Mxfp4SqTensor:
 
 
 def to_mxfp4(t: Mxfp4SqTensor) -> MxTensor:
-    if not t.is_native:
-        raise NotImplementedError("only all-SQ4 MXFP4-SQ tensors expand to native MXFP4 here")
+    """The native MXFP4 matrix every row decodes to (exactly the source for ``q = 4`` rows)."""
     rows, cols = t.shape
-    values = np.frombuffer(b"".join(t.row_symbols), dtype=np.uint8).reshape(rows, cols // 2).copy()
-    return MxTensor(MXFP4_DTYPE, (rows, cols), values, np.asarray(t.native_scales, dtype=np.uint8))
+    blocks = cols // 32
+    values = np.zeros((rows, cols // 2), dtype=np.uint8)
+    scales = np.zeros((rows, blocks), dtype=np.uint8)
+    q_of = np.asarray(t.row_q_bits, dtype=np.uint8)
+    sq = native = 0
+    for r in range(rows):
+        q = int(q_of[r])
+        if q == 4:
+            values[r] = np.frombuffer(t.row_symbols[r], dtype=np.uint8)
+            scales[r] = t.native_scales[native]
+            native += 1
+            continue
+        sym = unpack_symbols(t.row_symbols[r], cols, q).reshape(blocks, 32)
+        state = block_tags(sym, q) | (np.asarray(t.block_selectors[sq], dtype=np.uint8) << 2)
+        exponent = int(t.matrix_scale_base) + np.asarray(t.state_scales[sq], dtype=np.int64)[state]
+        if exponent.max() > 254:
+            raise ValueError("MXFP4-SQ row decodes to an invalid E8M0 exponent")
+        nib = PALETTES[q][np.asarray(t.state_palettes[sq], dtype=np.int64)[state][:, None], sym].reshape(cols)
+        values[r] = nib[0::2] | (nib[1::2] << 4)
+        scales[r] = exponent
+        sq += 1
+    return MxTensor(MXFP4_DTYPE, (rows, cols), values, scales)
+
+
+def expanded(t: Mxfp4SqTensor) -> MxTensor:
+    """:func:`to_mxfp4`, computed once per tensor object (loaders slice it expert by expert)."""
+    cached = getattr(t, "_expanded", None)
+    if cached is None:
+        cached = to_mxfp4(t)
+        object.__setattr__(t, "_expanded", cached)
+    return cached
 
 
 def dequantize_mxfp4sq(t: Mxfp4SqTensor) -> np.ndarray:

@@ -251,7 +251,10 @@ def _expert_slice(tensor, pos: int, out: int):
     """Rows ``[pos * out, (pos + 1) * out)`` of a pool's stacked family tensor, as a tensor of the same family (or None
     when the family has no packed kernel)."""
     from ..formats.mx import MXFP4_DTYPE, MxTensor
+    from ..formats.mxfp4sq import Mxfp4SqTensor, expanded
     from ..formats.nint import NintTensor
+    if isinstance(tensor, Mxfp4SqTensor):
+        tensor = expanded(tensor)  # every palette-coded row is a legal MXFP4 row
     r = slice(pos * out, (pos + 1) * out)
     if isinstance(tensor, NintTensor) and int(tensor.spec.groupsize) in (16, 24, 32) and tensor.axis == 0:
         return NintTensor(spec=tensor.spec, shape=(out, tensor.neuron_len), axis=0, neuron_len=tensor.neuron_len, q=tensor.q[r],

@@ -147,9 +147,12 @@ def concat_rows(parts: list[W4Weight]) -> W4Weight:
 
 def from_checkpoint_tensor(t) -> W4Weight | None:
     """:class:`W4Weight` for a checkpoint tensor the 4-bit GEMM can run natively (2-D NINT with at most 4 code bits
-    and a group size that is a multiple of 8, or MXFP4), else None."""
+    and a group size that is a multiple of 8, MXFP4, or MXFP4-SQ expanded to MXFP4), else None."""
     from ..formats.mx import MxTensor
+    from ..formats.mxfp4sq import Mxfp4SqTensor, expanded
     from ..formats.nint import NintTensor
+    if isinstance(t, Mxfp4SqTensor):
+        t = expanded(t)  # palette-coded rows decode to legal E2M1 nibbles under E8M0 scales: the same kernel runs them
     try:
         if isinstance(t, NintTensor) and len(t.shape) == 2 and t.axis == 0:
             return from_nint(t)
