@@ -387,9 +387,13 @@ def _cmd_eval(args) -> int:
     _, test = load(args.model)
     g = torch.Generator().manual_seed(args.seed)
     reports = []
+    rounding = None
+    if getattr(args, "activation_q8", False):
+        from .formats.nint8one import fake_quantize_nint8_one
+        rounding = fake_quantize_nint8_one  # the tested model sees Q8_1-rounded projection inputs, the baseline does not
     for _ in range(args.chunks):
         ids = torch.randint(0, cfg.vocab_size, (args.ctx,), generator=g)
-        lb, lt = MoeLM(cfg, base).forward(ids), MoeLM(cfg, test).forward(ids)
+        lb, lt = MoeLM(cfg, base).forward(ids), MoeLM(cfg, test, input_transform=rounding).forward(ids)
         half = args.ctx // 2  # score the second half of each window, like the reference protocol
         reports.append(compare_logits(lb[half:], lt[half:]))
     n = len(reports)
@@ -729,7 +733,7 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--groupsize", type=int, default=0)
     q.add_argument("--sub-bits", type=int, default=0)
     q.add_argument("--format", choices=["nint2", "nint3", "nint4", "nint5", "nint6", "nint8", "nvq3", "mxfp4", "fp8", "bf16", "npq0-s", "npq0-l",
-                                        "nvq1-l", "nvq1-l-s4", "nvq1-s"],
+                                        "nvq1-l", "nvq1-l-s4", "nvq1-s", "nvq2j", "nvq2j-l", "nvq2j-xl", "nvq3j", "nvq3j-512", "nvq3j-l"],
                    help="family of every 2-D weight (and of routed experts without a mix): NINT widths, lattice / product codes, MX, FP8")
     q.add_argument("--preset", help="role-based mixed-width NINT preset: S2-S S2-M S3-S S3-M S3-L S4-S S4-M S5-S S5-M S6 S8")
     q.add_argument("--imatrix", help="importance matrix (.npz from `mfq calibrate imatrix`) for the NINT search")
@@ -862,6 +866,8 @@ def build_parser() -> argparse.ArgumentParser:
     kl.add_argument("--chunks", "--kl-chunks", dest="chunks", type=int, default=4)
     kl.add_argument("--ctx", type=int, default=128)
     kl.add_argument("--seed", type=int, default=0)
+    kl.add_argument("--activation-q8", action="store_true",
+                    help="round the inputs of the tested model's projections to NINT8-1 (Q8_1) blocks, as an int8-activation runtime does")
     kl.set_defaults(fn=_cmd_eval)
     ol = sub.add_parser("optimize-layout", aliases=["optimize"], help="rewrite a checkpoint into the runtime's native execution layout")
     ol.add_argument("--input", required=True)

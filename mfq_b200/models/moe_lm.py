@@ -121,17 +121,23 @@ def route(logits: torch.Tensor, cfg: MoeConfig) -> tuple[torch.Tensor, torch.Ten
 class MoeLM:
     """fp32 forward with a plain KV list (no paging): prefill a prompt, then decode token by token."""
 
-    def __init__(self, cfg: MoeConfig, weights: dict[str, torch.Tensor], observer=None, reap_observer=None) -> None:
+    def __init__(self, cfg: MoeConfig, weights: dict[str, torch.Tensor], observer=None, reap_observer=None,
+                 input_transform=None) -> None:
         """``observer(name, x, y)`` (optional) sees input and output of every named 2-D projection: the hook the
         importance-matrix collection uses.  ``reap_observer(name, route_weights, y)`` (optional) sees every routed
         expert's outputs and the router weights of its tokens (``name`` = ``<down tensor>#<expert>``)."""
         self.cfg, self.w = cfg, weights
         self.observer = observer
         self.reap_observer = reap_observer
+        # ``input_transform(x)`` (optional) replaces the input of every named 2-D projection, e.g. by its NINT8-1
+        # reconstruction, to measure a checkpoint under the activation rounding of an int8-activation runtime
+        self.input_transform = input_transform
         self.k_cache: list[torch.Tensor] = []
         self.v_cache: list[torch.Tensor] = []
 
     def _lin(self, name: str, x: torch.Tensor) -> torch.Tensor:
+        if self.input_transform is not None:
+            x = self.input_transform(x).to(x.dtype)
         y = x @ self.w[name].T
         if self.observer is not None:
             self.observer(name, x, y)

@@ -29,6 +29,11 @@ _NINT_PRESETS = {2: (16, 4), 3: (16, 6), 4: (24, 6), 5: (28, 7), 6: (16, 8), 8: 
 _NVQ_FAMILIES = {"NVQ2": "e8_256", "NVQ3": "d4_256", "NVQ3-512": "d4_512", "NVQ3-L": "d4_1024",
                  "NVQ2-1024": "e8_1024", "NVQ2-4096": "e8_4096"}
 
+# joint scale/codebook-state lattice families: base grid, banks, learned scale table, storage layout
+_NVQ_JSC_FAMILIES = {"NVQ2J": ("e8_256", 2, True, "streams"), "NVQ2J-L": ("e8_1024", 2, True, "streams"),
+                     "NVQ2J-XL": ("e8_4096", 4, True, "group64"), "NVQ3J": ("d4_256", 2, False, "streams"),
+                     "NVQ3J-512": ("d4_512", 2, False, "streams"), "NVQ3J-L": ("d4_1024", 2, False, "streams")}
+
 __all__ = ["ExpertProfile", "parse_profiles", "balanced_expert_mix", "quantize_expertwise", "quantize_matrix",
            "DEFAULT_MIX_SEED"]
 
@@ -45,6 +50,8 @@ class ExpertProfile:
             return self.nint.bpw(4096)
         if self.nvq is not None:
             return self.nvq.bpw(4096, out=4096)
+        if self.family in _NVQ_JSC_FAMILIES:
+            return NvqSpec(_NVQ_JSC_FAMILIES[self.family][0]).bpw(4096, out=4096)
         return {"MXFP4": 4.25, "FP8": 8.0, "BF16": 16.0, "NPQ0-S": 0.84, "NPQ0-L": 1.0, "NVQ1-L": 1.55, "NVQ1-L-S4": 1.59,
                 "NVQ1-S": 1.34, "NEPQ0-S": 0.88, "NEPQ0-L": 1.04, "NEPQ1-S": 1.42, "NEPQ1-L": 1.63, "NEPQ0-A": 0.96,
                 "NEPQ1-A": 1.61}[self.family]
@@ -62,6 +69,8 @@ def parse_profiles(text: str) -> tuple[ExpertProfile, ...]:
             out.append(ExpertProfile(name, nint=NintSpec(bits, gs, k)))
         elif name in _NVQ_FAMILIES:
             out.append(ExpertProfile(name, nvq=NvqSpec(_NVQ_FAMILIES[name])))
+        elif name in _NVQ_JSC_FAMILIES:
+            out.append(ExpertProfile(name))
         elif name in ("MXFP4", "FP8", "BF16", "NPQ0-S", "NPQ0-L", "NVQ1-L", "NVQ1-L-S4", "NVQ1-S", "NEPQ0-S", "NEPQ0-L", "NEPQ1-S",
                       "NEPQ1-L", "NEPQ0-A", "NEPQ1-A"):
             out.append(ExpertProfile(name))
@@ -95,6 +104,12 @@ def quantize_matrix(w, profile: ExpertProfile, device="cpu", importance=None):
         from ..formats.nvq1 import quantize_nvq1
         w = np.asarray(w, dtype=np.float32)
         return quantize_nvq1(w, profile.family, axis=w.ndim - 2, importance=importance, device=str(device))
+    if profile.family in _NVQ_JSC_FAMILIES:
+        from .nvq_jsc import quantize_nvq_jsc
+        grid, banks, learned, layout = _NVQ_JSC_FAMILIES[profile.family]
+        w = np.asarray(w, dtype=np.float32)
+        return quantize_nvq_jsc(w, grid, banks=banks, axis=w.ndim - 2, importance=importance, learn_scales=learned,
+                                storage_layout=layout, device=device)
     if profile.family.startswith("NEPQ"):
         from ..formats.nepq import quantize_nepq
         w = np.asarray(w, dtype=np.float32)
