@@ -139,3 +139,44 @@ def test_checkpoint_experts_stay_packed_and_match_the_fp8_transcode():
     pgu = w.layers[0].moe.packed_gate_up
     assert pgu.bits_per_weight() < 7.5, pgu.bits_per_weight()  # 256-wide rows padded to whole 128-code units
     check_status()
+
+
+def test_palette_coded_mxfp4_experts_run_on_the_packed_mxfp4_path():
+    """MXFP4-SQ expert pools (rows of 1..4 symbol bits over catalogue palettes) decode to legal MXFP4 at load: the
+    packed kernels run them, and the logits are bit-equal to those of the same checkpoint with the pools expanded to
+    plain MXFP4 beforehand."""
+    require_gpu_lib()
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.formats.mfe import MfePool, MfeTensor
+    from mfq_b200.formats.mx import MxTensor
+    from mfq_b200.formats.mxfp4sq import Mxfp4SqTensor, to_mxfp4
+    from mfq_b200.models.llama import StepBuffers
+    from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from mfq_b200.models.moe_lm import MoeConfig, init_weights, quantize_moe_checkpoint
+    from mfq_b200.quantize.mxfp4_sq import quantize_mxfp4_sq
+    cfg = MoeDecoderConfig.tiny()
+    ck = quantize_moe_checkpoint(init_weights(MoeConfig(head_dim=128, hidden_size=256, moe_intermediate=128,
+                                                        shared_intermediate=128), seed=11, std=0.05), "MXFP4")
+    coded, plain = dict(ck), dict(ck)
+    pools = 0
+    for name, t in ck.items():
+        if isinstance(t, MfeTensor):
+            sq = tuple(MfePool(p.expert_ids, quantize_mxfp4_sq(p.tensor, target_bits=3.0), p.runtime) for p in t.pools)
+            coded[name] = MfeTensor(t.shape, sq)
+            plain[name] = MfeTensor(t.shape, tuple(MfePool(p.expert_ids, to_mxfp4(p.tensor), p.runtime) for p in sq))
+            pools += len(sq)
+            assert all(isinstance(p.tensor, Mxfp4SqTensor) for p in sq) and all(isinstance(p.tensor, MxTensor) for p in plain[name].pools)
+    assert pools > 0
+    prompt = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(5))
+    outs = []
+    for tensors in (coded, plain):
+        w = MoeWeights.from_tensors(cfg, tensors, "cuda", packed_experts=True)
+        assert w.layers[0].moe.packed_gate_up is not None
+        model = MoeDecoderModel(cfg, w)
+        eng = LLMEngine(model, max_batch=2, max_seq_len=96, use_graphs=False)
+        eng.cache.assign(0, 0, 40)
+        step = StepBuffers(input_ids=prompt.cuda().int(), positions=torch.arange(40, dtype=torch.int32, device="cuda"),
+                           slots=eng.cache.slots(0, 0, 40).cuda(), cu_seqlens=[0, 40])
+        outs.append(model.forward(step, eng.cache, prefill=True).float().cpu())
+    check_status()
+    assert torch.equal(outs[0], outs[1])
