@@ -23,7 +23,7 @@ import torch
 
 from ..formats.nvq import NvqSpec, NvqTensor, codebook as lattice
 
-__all__ = ["quantize_nvq", "encode_even_parity"]
+__all__ = ["quantize_nvq", "encode_even_parity", "train_tensor_codebook"]
 
 
 def encode_even_parity(rows: torch.Tensor, w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -108,8 +108,87 @@ def _search(xg: torch.Tensor, wg: torch.Tensor, table: torch.Tensor, vec: int, s
     return best_scale, best_idx, assign
 
 
+def train_tensor_codebook(weight, spec: NvqSpec, *, axis: int = 0, importance=None, rounds: int = 3, sample_rows: int = 2048,
+                          search_steps: int = 7, seed: int = 0, device: str | torch.device = "cpu") -> np.ndarray:
+    """A codebook of ``spec.entries`` magnitude vectors fitted to ONE tensor (stored in its blob, 2 bytes per entry).
+    Entries stay on the format's alphabet -- odd integers up to 7 (8-wide) or 15 (4-wide).  Lloyd rounds from the
+    standard grid on at most ``sample_rows`` rows: assign with the joint index / scale search, move every coordinate of
+    every entry to the odd level with the least weighted error over its vectors, and give entries that ended up unused
+    or duplicated the most frequent rounded target vectors the book does not hold yet.
+    Reference: ``mfq/quantize/nvq_tensor_codebook.py`` (tensor-local codebooks), ``nvq_codebook.py`` (alphabet rules)."""
+    w_full = torch.as_tensor(np.asarray(weight, dtype=np.float32))
+    axis %= w_full.ndim
+    rows_all = w_full.movedim(axis, 0).reshape(w_full.shape[axis], -1)
+    out, n = rows_all.shape
+    gs, vec = spec.groupsize, spec.vector_size
+    ng = math.ceil(n / gs)
+    g = torch.Generator().manual_seed(seed)
+    pick = torch.randperm(out, generator=g)[:sample_rows].sort().values
+    rows = torch.nn.functional.pad(rows_all[pick], (0, ng * gs - n)).to(device)
+    o = rows.shape[0]
+    wobj = torch.ones_like(rows) if importance is None else \
+        torch.nn.functional.pad(torch.as_tensor(np.asarray(importance, dtype=np.float32)).reshape(1, n).expand(o, n), (0, ng * gs - n)).to(device).clone()
+    wobj[:, n:] = 0.0
+    target, _ = encode_even_parity(rows, torch.where(wobj > 0, wobj, torch.full_like(wobj, 1e-12)))
+    xg, wg = target.reshape(o * ng, gs), wobj.reshape(o * ng, gs)
+    vpg = gs // vec
+    top = 7 if vec == 8 else 15
+    levels = torch.arange(1, top + 1, 2, dtype=torch.float32, device=rows.device)
+    table = torch.as_tensor(lattice(spec).astype(np.float32), device=rows.device)
+
+    def total_error(tab):
+        scale, idx, _ = _search(xg, wg, tab, vec, search_steps)
+        diff = scale[:, None] * tab[idx].reshape(xg.shape) - xg
+        return float((wg * diff * diff).sum()), scale, idx
+
+    best_err, scale, idx = total_error(table)
+    best = table.clone()
+    for _ in range(max(1, rounds)):
+        sv = scale.repeat_interleave(vpg)                                     # [V]
+        xv, wv, iv = xg.reshape(-1, vec), wg.reshape(-1, vec), idx.reshape(-1)
+        live = sv > 0
+        xv, wv, iv, sv = xv[live], wv[live], iv[live], sv[live]
+        cost = torch.zeros((spec.entries, vec, levels.numel()), device=rows.device)
+        for li, level in enumerate(levels):
+            cost[:, :, li].index_add_(0, iv, wv * (xv - sv[:, None] * level) ** 2)
+        used = torch.zeros(spec.entries, dtype=torch.bool, device=rows.device)
+        used[iv.unique()] = True
+        new = table.clone()
+        new[used] = levels[cost[used].argmin(-1)]
+        # unused and duplicate slots: the most frequent rounded targets that are not in the book yet
+        snapped = levels[((xv / sv[:, None]).clamp(1, top)[..., None] - levels).abs().argmin(-1)]
+        uniq, counts = torch.unique(snapped, dim=0, return_counts=True)
+        order = counts.argsort(descending=True)
+        held, free = set(), []
+        rows_np = new.cpu().numpy().astype(np.int8)
+        for e in range(spec.entries):
+            key = rows_np[e].tobytes()
+            if key in held or not bool(used[e]):
+                free.append(e)
+            else:
+                held.add(key)
+        cand = uniq[order].cpu().numpy().astype(np.int8)
+        c = 0
+        spare = lattice(spec).astype(np.int8)
+        for e in free:
+            while c < cand.shape[0] and cand[c].tobytes() in held:
+                c += 1
+            if c < cand.shape[0]:
+                rows_np[e] = cand[c]
+            else:  # nothing left to add from the data: keep a grid entry that is not held (a book may not repeat itself)
+                rows_np[e] = next(sp for sp in spare if sp.tobytes() not in held)
+            held.add(rows_np[e].tobytes())
+        table = torch.as_tensor(rows_np.astype(np.float32), device=rows.device)
+        err, scale, idx = total_error(table)
+        if err < best_err:
+            best_err, best = err, table.clone()
+    return best.cpu().numpy().astype(np.int8)
+
+
 def quantize_nvq(weight, spec: NvqSpec, *, axis: int = 0, importance=None, search_steps: int = 19,
-                 refit_anchor: bool = True, device: str | torch.device = "cpu", row_chunk: int = 256) -> NvqTensor:
+                 refit_anchor: bool = True, device: str | torch.device = "cpu", row_chunk: int = 256,
+                 codebook: np.ndarray | None = None) -> NvqTensor:
+    """``codebook``: a tensor-local table (``train_tensor_codebook``) carried in the blob instead of the standard grid."""
     if spec.sign_mode != "even":
         raise NotImplementedError("the quantizer emits even-parity signs only")
     w_full = torch.as_tensor(np.asarray(weight, dtype=np.float32) if not torch.is_tensor(weight) else weight).to(torch.float32)
@@ -120,7 +199,7 @@ def quantize_nvq(weight, spec: NvqSpec, *, axis: int = 0, importance=None, searc
     gs, vec = spec.groupsize, spec.vector_size
     ng = math.ceil(n / gs)
     padded = ng * gs
-    table = torch.as_tensor(lattice(spec).astype(np.float32), device=device)
+    table = torch.as_tensor((lattice(spec) if codebook is None else np.asarray(codebook)).astype(np.float32), device=device)
     levels = (1 << spec.sub_bits) - 1
     nvec, nsign = math.ceil(n / vec), math.ceil(n / 8)
     d_all = np.zeros(out, np.float32)
@@ -166,4 +245,4 @@ def quantize_nvq(weight, spec: NvqSpec, *, axis: int = 0, importance=None, searc
         i_all[sl] = idx.reshape(o, ng * vpg)[:, :nvec].cpu().numpy().astype(i_all.dtype)
         m_all[sl] = masks[:, :nsign].cpu().numpy()
     return NvqTensor(spec=spec, shape=shape, axis=axis, neuron_len=n, neuron_scale=d_all, sub_scale=s_all,
-                     indices=i_all, signs=m_all)
+                     indices=i_all, signs=m_all, codebook=None if codebook is None else np.asarray(codebook, dtype=np.int8))

@@ -88,3 +88,34 @@ def test_reference_package_reads_and_decodes_it(reference_pkg):
         theirs = R.unpack_nvq(blob)
         assert type(theirs).__name__ == "NvqJscTensor" and R.pack_nvq(theirs) == blob
         assert np.array_equal(dequantize_nvq_jsc(theirs), F.dequantize(t))
+
+
+def test_tensor_local_codebook_for_plain_nvq(reference_pkg):
+    """A codebook fitted to the tensor stays on the format's alphabet, has no repeated entry, travels in the blob, lowers
+    the error on rows it was not fitted on, and the reference package reads the result."""
+    from mfq.formats import nvq as R  # type: ignore
+    from mfq_b200.quantize.nvq import train_tensor_codebook
+    rng = np.random.default_rng(7)
+    # magnitudes drawn from a small set of shapes the standard grid does not favour
+    shapes = rng.choice([1.0, 3.0, 5.0, 7.0], size=(24, 8), p=[0.1, 0.2, 0.3, 0.4])
+    rows = []
+    for _ in range(160):
+        mag = shapes[rng.integers(0, 24, size=24)].reshape(-1)
+        rows.append(mag * rng.choice([-1.0, 1.0], size=192) * 0.01 * (1 + 0.03 * rng.normal(size=192)))
+    w = np.asarray(rows, dtype=np.float32)
+    spec = NvqSpec("e8_256")
+    table = train_tensor_codebook(w[:96], spec)
+    assert table.shape == (256, 8) and table.dtype == np.int8 and set(np.unique(table).tolist()) <= {1, 3, 5, 7}
+    assert np.unique(table, axis=0).shape[0] == 256
+    plain, own = quantize_nvq(w[96:], spec), quantize_nvq(w[96:], spec, codebook=table)
+    assert _rel_on(own, w[96:]) < 0.7 * _rel_on(plain, w[96:])
+    dtype, blob = F.pack_tensor(own)
+    back = F.unpack_tensor(dtype, blob)
+    assert len(blob) == len(F.pack_tensor(plain)[1]) + 512 and np.array_equal(back.codebook, table)
+    assert np.array_equal(F.dequantize(back), F.dequantize(own))
+    theirs = R.unpack_nvq(blob)
+    assert R.pack_nvq(theirs) == blob
+
+
+def _rel_on(t, w):
+    return float(((F.dequantize(t) - w) ** 2).sum() / (w ** 2).sum())
