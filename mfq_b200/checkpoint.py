@@ -50,11 +50,61 @@ def read_hf_directory(path) -> tuple[dict, dict[str, np.ndarray], dict[str, byte
     tensors: dict[str, np.ndarray] = {}
     for shard in sorted(p.glob("*.safetensors")):
         tensors.update(read_safetensors(shard))
+    tensors = fold_source_quantization(tensors, hf_cfg)
     assets = {}
     for fname in ("tokenizer.json", "tokenizer_config.json", "generation_config.json", "chat_template.jinja"):
         if (p / fname).exists():
             assets[f"hf/{fname}"] = (p / fname).read_bytes()
     return config_from_hf(hf_cfg), to_canonical(tensors, hf_cfg), assets
+
+
+def fold_source_quantization(tensors: dict[str, np.ndarray], hf_cfg: dict | None = None) -> dict[str, np.ndarray]:
+    """Sources that ship already-quantized weights, folded to plain float32 matrices under their plain names:
+
+    * block-scaled FP8 (``<w>`` in E4M3 with ``<w>_scale_inv`` of shape ``[ceil(out / b0), ceil(in / b1)]``; the block
+      comes from ``quantization_config.weight_block_size``, default 128 x 128): ``w * scale_inv`` per block;
+    * tensor- or channel-scaled FP8 (``<w>`` with ``<w>_scale`` holding one value, or one per output row);
+      ``input_scale`` / ``activation_scale`` companions (static activation ranges) are dropped;
+    * MXFP4 in the ``<name>_blocks`` / ``<name>_scales`` layout (``[..., groups, 16]`` bytes of two E2M1 nibbles, low
+      first, and one E8M0 exponent per 32 values): ``<name>`` becomes ``[..., groups * 32]`` float32.
+
+    Reference: the scaled-FP8 and MXFP4 source readers of ``mfq/formats/hf_source.py`` and ``mfq/convert/``."""
+    from .formats.mx import E2M1_VALUES
+    qc = (hf_cfg or {}).get("quantization_config") or {}
+    block = tuple(qc.get("weight_block_size") or (128, 128))
+    out = dict(tensors)
+    for name in list(out):
+        if name.endswith("_scale_inv") and name[: -len("_scale_inv")] in out:
+            base = name[: -len("_scale_inv")]
+            w, sc = np.asarray(out[base], dtype=np.float32), np.asarray(out.pop(name), dtype=np.float32)
+            lead = w.shape[:-2]
+            rows, cols = w.shape[-2:]
+            if sc.shape != lead + (-(-rows // block[0]), -(-cols // block[1])):
+                raise ValueError(f"{name}: scale grid {sc.shape} does not cover {w.shape} in {block[0]}x{block[1]} blocks")
+            full = np.repeat(np.repeat(sc, block[0], axis=-2), block[1], axis=-1)[..., :rows, :cols]
+            out[base] = w * full
+        elif name.endswith(".weight_scale") and name[: -len("_scale")] in out:
+            base = name[: -len("_scale")]
+            w, sc = np.asarray(out[base], dtype=np.float32), np.asarray(out.pop(name), dtype=np.float32)
+            if sc.size == 1:
+                out[base] = w * sc.reshape(())
+            elif sc.size == int(np.prod(w.shape[:-1])):
+                out[base] = w * sc.reshape(w.shape[:-1] + (1,))
+            else:
+                raise ValueError(f"{name}: {sc.shape} is neither one scale nor one per output row of {w.shape}")
+        elif name.endswith((".input_scale", ".activation_scale")):
+            out.pop(name)
+    for name in list(out):
+        if name.endswith("_blocks") and name[: -len("_blocks")] + "_scales" in out:
+            base = name[: -len("_blocks")]
+            blocks, scales = np.asarray(out.pop(name)), np.asarray(out.pop(base + "_scales"))
+            if blocks.dtype != np.uint8 or scales.dtype != np.uint8 or blocks.shape[-1] != 16 or blocks.shape[:-1] != scales.shape:
+                raise ValueError(f"{name}: expected uint8 [..., groups, 16] with uint8 exponents [..., groups]")
+            nib = np.stack([blocks & 15, blocks >> 4], -1).reshape(blocks.shape[:-1] + (32,))
+            val = np.where(nib & 8, -E2M1_VALUES[nib & 7], E2M1_VALUES[nib & 7]).astype(np.float32)
+            val = val * np.ldexp(np.float32(1.0), scales.astype(np.int32) - 127)[..., None]
+            out[base] = val.reshape(blocks.shape[:-2] + (blocks.shape[-2] * 32,)).astype(np.float32)
+    return out
 
 
 def quantize_tensors(tensors: dict[str, np.ndarray], *, dense: str = "nint4", expert_mix: str = "", seed: int = 20260908,
