@@ -255,8 +255,10 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
     else:
         opened = F.open_mfq(path)
     with opened as store:
+        header = None
         if not isinstance(store, dict):
             assets = store.assets()
+            header = store.header
             raw = json.loads(assets["model_config.json"])
             from .formats.legacy_names import canonical_view
             store = canonical_view(store)  # old artifacts kept source tensor paths
@@ -295,6 +297,11 @@ def load_engine(path, device="cuda", *, native_4bit: bool = False, expert_slots:
     #                                                                    park at different moments and fall out of lockstep
     if expert_slots is not None and expert_graphs and not engine.enable_expert_residency_graphs():
         engine.use_graphs = engine.use_graphs and not (hasattr(model, "residencies") and model.residencies())
+    # what the checkpoint says about itself, for the server's sampling-profile resolution
+    engine.checkpoint_meta = {
+        "path": str(path), "header_extra": dict(getattr(header, "extra", None) or {}),
+        "architecture": raw.get("model_type") or raw.get("family") or getattr(header, "model_arch", "") or "",
+        "assets": {k: v for k, v in assets.items() if k == "hf/generation_config.json"}}
     tokenizer = tokenizer_from_assets(assets, cfg.vocab_size)
     # structured output needs the vocabulary's byte strings; resolved on the first request that asks for it
     engine.set_token_bytes(lambda: tokenizer.token_bytes(cfg.vocab_size), tokenizer.stop_ids)

@@ -137,6 +137,16 @@ def _cmd_quantize(args) -> int:
                          progress=(lambda n: print(f"quantize {n}", file=sys.stderr)) if args.verbose else None)
     extra = {"quantization": {"dense": dense, "preset": args.preset or None, "imatrix": bool(imatrix), "ew_scheme": bool(scheme), "random_expert_mix": args.random_expert_mix.split(",") if args.random_expert_mix else [],
                               "random_expert_mix_seed": args.random_expert_mix_seed if args.random_expert_mix else None}}
+    from .formats import runtime_profile as rp
+    inherited = None
+    if str(args.input).endswith(".mfq") and Path(args.input).is_file():
+        with F.open_mfq(args.input) as src_store:
+            inherited = (src_store.header.extra or {}).get(rp.HEADER_KEY)
+    sampling = rp.profile_for_new_checkpoint(args.input if Path(str(args.input)).is_dir() else None,
+                                             {"model_type": cfg.get("model_type") or cfg.get("family"), "_name_or_path": Path(str(args.input)).name},
+                                             assets=assets, explicit=args.runtime_profile, inherited=inherited)
+    if sampling is not None:
+        extra[rp.HEADER_KEY] = sampling
     shard_bytes = int(args.shard_size_gb * (1 << 30)) if args.shard_size_gb else None
     if args.split_max_size:
         from .quantize.recipe import parse_size
@@ -750,6 +760,8 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--fp8-sq-bits", type=float, default=0.0,
                    help="with --format fp8: re-encode the E4M3 tensors with per-row scalar palettes (FP8-128SQ rows SQ1..SQ8) "
                         "averaging this many code bits per weight")
+    q.add_argument("--runtime-profile", help="runtime.sampling.v1 JSON whose sampling defaults are embedded in the output "
+                                             "(over the architecture registry, the source's generation config and its mfq-runtime.json)")
     q.add_argument("--mxfp4-sq-bits", type=float, default=0.0,
                    help="re-code every MXFP4 matrix (dense with --format mxfp4, expert pools of a mix) as MXFP4-SQ: rows of 1..4 "
                         "symbol bits over catalogue palettes, averaging this many stored bits per weight; still legal MXFP4 once decoded")

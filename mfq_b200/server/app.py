@@ -208,7 +208,15 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
         if not ids:
             return None, error_response(400, "invalid_request", "empty prompt")
         try:
-            params = _params_from(policies.request_defaults(lm.name, body), tuple(lm.tokenizer.stop_ids))
+            merged = policies.request_defaults(lm.name, body)
+            if "profile_defaults" not in lm.meta:
+                from ..formats import runtime_profile as rp
+                try:
+                    lm.meta["profile_defaults"] = rp.checkpoint_defaults(lm.meta)
+                except (ValueError, OSError):
+                    lm.meta["profile_defaults"] = {}
+            merged = {**lm.meta["profile_defaults"], **{k: v for k, v in merged.items() if v is not None}}
+            params = _params_from(merged, tuple(lm.tokenizer.stop_ids))
         except (TypeError, ValueError) as exc:
             return None, error_response(400, "invalid_request", str(exc))
         try:
@@ -667,6 +675,6 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
         except KeyError:
             return error_response(404, "model_not_found", f"model {model!r} is not loaded")
         meta = getattr(lm, "meta", None) or {}
-        return rp.resolve(meta.get("header_extra"), meta.get("assets"), meta.get("architecture"))
+        return rp.resolve(meta.get("header_extra"), meta.get("assets"), meta.get("architecture"), meta.get("path"))
 
     return app

@@ -51,6 +51,9 @@ class ModelService:
             self.unload(victim)
         sched = ContinuousBatchScheduler(engine, max_queue=self.max_queue, queue_timeout=self.queue_timeout)
         lm = LoadedModel(name, engine, tokenizer, sched, request_capacity=getattr(engine, "max_batch", 1))
+        about = getattr(engine, "checkpoint_meta", None) or getattr(getattr(engine, "engine", None), "checkpoint_meta", None)
+        if about:
+            lm.meta.update(about)
         self.models[name] = lm
         return lm
 
