@@ -28,7 +28,7 @@ import numpy as np
 import torch
 
 from ..formats.nvq import NvqJscTensor, NvqSpec, analytic_jsc_tables, codebook as lattice
-from .nvq import encode_even_parity
+from .nvq import assign_fused, encode_even_parity, fused_assign_available
 
 __all__ = ["quantize_nvq_jsc"]
 
@@ -38,17 +38,25 @@ def _assign_states(xv, wv, anchors_v, lut, bank_of, tables, vpg: int):
     error [G]) -- exhaustive over the 16 states, nearest entry per vector inside each."""
     v = xv.shape[0]
     g = v // vpg
-    cross = [(wv * xv) @ t.T for t in tables]
-    quad = [wv @ (t * t).T for t in tables]
-    x2 = (wv * xv * xv).sum(-1)
+    fused = fused_assign_available(xv, xv.shape[1])  # on a GPU: the fused nearest-codeword kernel, no [V, entries] matrices
+    if not fused:
+        cross = [(wv * xv) @ t.T for t in tables]
+        quad = [wv @ (t * t).T for t in tables]
+        x2 = (wv * xv * xv).sum(-1)
     best = torch.full((g,), float("inf"), device=xv.device)
     best_s = torch.zeros(g, dtype=torch.long, device=xv.device)
     best_i = torch.zeros((g, vpg), dtype=torch.long, device=xv.device)
     for s in range(16):
         b = int(bank_of[s])
-        sc = (anchors_v * float(lut[s]))[:, None]
-        val, idx = (sc * sc * quad[b] - 2.0 * sc * cross[b]).min(-1)
-        err = (val + x2).reshape(g, vpg).sum(-1)
+        if fused:
+            sc1 = (anchors_v * float(lut[s])).contiguous()
+            idx = assign_fused(xv, wv, tables[b], sc1)
+            diff = xv - sc1[:, None] * tables[b][idx]
+            err = (wv * diff * diff).sum(-1).reshape(g, vpg).sum(-1)
+        else:
+            sc = (anchors_v * float(lut[s]))[:, None]
+            val, idx = (sc * sc * quad[b] - 2.0 * sc * cross[b]).min(-1)
+            err = (val + x2).reshape(g, vpg).sum(-1)
         take = err < best
         best = torch.where(take, err, best)
         best_s = torch.where(take, torch.full_like(best_s, s), best_s)

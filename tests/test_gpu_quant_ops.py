@@ -40,3 +40,20 @@ def test_nvq_quantizer_on_the_gpu_matches_the_cpu_quality():
     e_cpu = float(((np.asarray(F.dequantize(cpu)) - w) ** 2).sum())
     e_gpu = float(((np.asarray(F.dequantize(gpu)) - w) ** 2).sum())
     assert e_gpu <= e_cpu * 1.02
+
+
+def test_jsc_quantizer_on_the_gpu_matches_the_cpu_quality():
+    """The state / entry assignment of the NVQ-JSC quantizer through the fused nearest-codeword kernel (one launch per
+    state, no vectors-by-entries matrices) reaches the error of the matrix form on the CPU; the MXFP4-SQ and NEPQ
+    encoders are device-agnostic torch / NumPy and need no kernel."""
+    require_gpu_lib()
+    from mfq_b200 import formats as F
+    from mfq_b200.quantize.nvq_jsc import quantize_nvq_jsc
+    w = (np.random.default_rng(1).standard_t(df=6, size=(96, 240)) * 0.03).astype(np.float32)
+    for grid, banks in (("e8_256", 2), ("d4_256", 1)):
+        cpu = quantize_nvq_jsc(w, grid, banks=banks, iterations=2, device="cpu")
+        gpu = quantize_nvq_jsc(w, grid, banks=banks, iterations=2, device="cuda")
+        e_cpu = float(((np.asarray(F.dequantize(cpu)) - w) ** 2).sum())
+        e_gpu = float(((np.asarray(F.dequantize(gpu)) - w) ** 2).sum())
+        assert e_gpu <= e_cpu * 1.03, (grid, e_cpu, e_gpu)
+        assert F.pack_tensor(F.unpack_tensor(*F.pack_tensor(gpu)))[1] == F.pack_tensor(gpu)[1]
