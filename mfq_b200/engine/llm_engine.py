@@ -432,6 +432,50 @@ class LLMEngine:
             c0 = c1
         return logits, (torch.cat(hidden_parts, 0) if want_hidden else None)
 
+    def score(self, row: int, token_ids, start: int) -> list[float]:
+        """Natural-log probabilities the model gives ``token_ids[start:]``, each conditioned on everything before it:
+        one chunked prefill on the free batch row ``row`` (released again afterwards; no sampling, no prefix or session
+        cache).  ``start >= 1``.  The evaluation the reference serves as probability scoring
+        (``mfq/server/api/routes/models.py:342-356``)."""
+        dev = self.device
+        self._bind_state()
+        ids = torch.as_tensor(token_ids, dtype=torch.int32)
+        n = int(ids.numel())
+        if not 1 <= start < n:
+            raise ValueError("score() needs at least one context token and one token to score")
+        if n > self.max_seq_len:
+            raise ValueError(f"{n} tokens exceed the engine's context of {self.max_seq_len}")
+        if row in self.row_seq:
+            raise ValueError(f"batch row {row} is in use")
+        seq_id = self._next_seq_id
+        self._next_seq_id += 1
+        self.row_seq[row] = seq_id
+        out: list[float] = []
+        try:
+            self.cache.assign(row, seq_id, n)
+            ids = ids.to(dev)
+            state_slots = None
+            if self.rec_state is not None:
+                self.rec_state.reset(row)
+                state_slots = self.row_ids[row : row + 1]
+            c0 = 0
+            while c0 < n - 1:
+                c1 = min(n, c0 + self.prefill_chunk)
+                m = c1 - c0
+                step = StepBuffers(input_ids=ids[c0:c1], positions=torch.arange(c0, c1, dtype=torch.int32, device=dev),
+                                   slots=self.cache.slots(seq_id, c0, m).to(dev), cu_seqlens=[0, m], state_slots=state_slots,
+                                   past_len=c0, block_table=self.cache.block_table[row : row + 1] if c0 else None)
+                lo, hi = max(start - 1, c0), min(n - 1, c1)          # positions whose NEXT token is scored, in this chunk
+                want = torch.arange(lo - c0, hi - c0, dtype=torch.int32, device=dev) if hi > lo else torch.zeros(1, dtype=torch.int32, device=dev)
+                logits = self.model.forward(step, self.cache, prefill=True, logits_rows=want)
+                if hi > lo:
+                    logp = torch.log_softmax(logits.float(), -1)
+                    out += logp.gather(1, ids[lo + 1 : hi + 1].long()[:, None])[:, 0].tolist()
+                c0 = c1
+        finally:
+            self.release(row)
+        return out
+
     def grow(self, row: int, tokens: int) -> None:
         self.cache.assign(row, self.row_seq[row], min(self.max_seq_len, tokens))
 

@@ -666,6 +666,47 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
     async def delete_session(sid: str):
         return {"deleted": store.delete(sid)}
 
+    @app.post("/api/v1/evaluations/probabilities")
+    async def evaluation_probabilities(request: HttpRequest):
+        """Log-probabilities of given continuations of a prompt under a loaded model (natural log, raw tokenization
+        without special tokens).  ``mode``: ``continuation`` scores every token of each continuation, ``next_token``
+        only its first.  Body: ``{"model"?, "prompt", "continuations": [...], "mode"?}``."""
+        body = await request.json()
+        prompt, conts, mode = body.get("prompt"), body.get("continuations"), body.get("mode", "continuation")
+        if not isinstance(prompt, str) or not prompt or not isinstance(conts, list) or not 1 <= len(conts) <= 64 \
+                or not all(isinstance(c, str) and c for c in conts) or mode not in ("continuation", "next_token"):
+            return error_response(400, "invalid_request", "need a prompt, 1..64 non-empty continuations and mode continuation | next_token")
+        try:
+            lm = service.resolve(body.get("model"))
+        except KeyError:
+            return error_response(404, "model_not_found", f"model {body.get('model')!r} is not loaded")
+        engine = lm.engine
+        if engine is None or not callable(getattr(engine, "score", None)):
+            return error_response(501, "probability_unavailable", "the loaded runtime does not support probability scoring")
+        head = [int(t) for t in lm.tokenizer.encode(prompt)]
+        tails = [[int(t) for t in lm.tokenizer.encode(c)] for c in conts]
+        if not head or any(not t for t in tails):
+            return error_response(400, "invalid_request", "prompt and continuations must tokenize to at least one token")
+
+        def run(model):
+            row = model.scheduler._free_row()
+            if row is None:
+                raise QueueFull("every batch row is busy")
+            out = []
+            for tail in tails:
+                use = tail[:1] if mode == "next_token" else tail
+                logp = engine.score(row, head + use, len(head))
+                out.append({"token_ids": use, "token_logprobs": [min(0.0, float(x)) for x in logp], "log_likelihood": float(sum(logp))})
+            return out
+
+        try:
+            scores = await asyncio.get_running_loop().run_in_executor(None, service.call, lm, run)
+        except QueueFull as exc:
+            return error_response(503, "server_busy", str(exc))
+        except ValueError as exc:
+            return error_response(400, "invalid_request", str(exc))
+        return {"prompt_tokens": len(head), "scores": scores, "log_base": "e", "tokenization": "raw-no-special-tokens"}
+
     @app.get("/api/v1/runtime/sampling-profile")
     async def sampling_profile(model: str | None = None):
         """Effective sampling defaults of a loaded model and where they come from."""

@@ -31,6 +31,8 @@ def required_scope(method: str, path: str) -> str | None:
         return "read" if method == "GET" else "inference"
     if path.startswith("/api/v1/auth"):
         return "admin"
+    if path.startswith("/api/v1/evaluations/"):
+        return "inference"  # runs the model on caller text, changes nothing
     if method in ("GET", "HEAD", "OPTIONS"):
         return "read"
     return "admin"

@@ -117,6 +117,18 @@ class ModelService:
             raise box["error"]
         return req, events
 
+    def call(self, model: LoadedModel, fn, timeout: float = 120.0):
+        """Run ``fn(model)`` on the serving thread, between scheduling steps (engine state has one owner), and return
+        its result or raise what it raised."""
+        box: dict = {}
+        done = threading.Event()
+        self._inbox.put(("call", model, fn, box, done))
+        if not done.wait(timeout):
+            raise TimeoutError("the serving thread did not get to the call in time")
+        if "error" in box:
+            raise box["error"]
+        return box.get("result")
+
     def cancel(self, model: LoadedModel, request_id: int) -> None:
         self._inbox.put(("cancel", model, request_id, None, None))
 
@@ -133,6 +145,12 @@ class ModelService:
                         done.set()
                     elif kind == "cancel":
                         model.scheduler.cancel(arg)
+                    elif kind == "call":
+                        try:
+                            box["result"] = arg(model)
+                        except Exception as exc:
+                            box["error"] = exc
+                        done.set()
             except queue.Empty:
                 pass
             busy = False
