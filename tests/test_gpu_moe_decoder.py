@@ -102,3 +102,26 @@ def test_expert_residency_under_graphs_replays_misses(slots):
     assert st["replays"] + st["fallbacks"] < st["steps"] * eng.residency_replays  # most steps ran once, from the graph
     res = eng.model.residencies()
     assert all(not r.optimistic for r in res) and sum(r.stats["uploads"] for r in res) >= slots
+
+
+def test_probability_scores_match_the_cpu_engine():
+    """`LLMEngine.score` (chunked prefill with logits at the scored positions only) on the GPU against the fp32 CPU path."""
+    import torch
+    from gpu_common import check_status, require_gpu_lib
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from mfq_b200.models.moe_lm import MoeConfig, init_weights
+    require_gpu_lib()
+    cfg = MoeDecoderConfig.tiny()
+    tensors = init_weights(MoeConfig(head_dim=128, hidden_size=256, moe_intermediate=128, shared_intermediate=128), seed=6, std=0.05)
+    ids = torch.randint(0, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(8)).tolist()
+    scores = {}
+    for dev in ("cpu", "cuda"):
+        eng = LLMEngine(MoeDecoderModel(cfg, MoeWeights.from_tensors(cfg, tensors, dev)), max_batch=2, max_seq_len=128, device=dev, use_graphs=False)
+        eng.prefill_chunk = 32                     # three chunks, the scored span starts inside the second
+        scores[dev] = torch.tensor(eng.score(1, ids, 40))
+        assert 1 not in eng.row_seq
+    check_status()
+    assert scores["cuda"].shape == (30,) and bool((scores["cuda"] <= 0).all())
+    # FP8 weights and activations on one side, fp32 on the other, at log-probabilities around -7
+    assert float((scores["cuda"] - scores["cpu"]).abs().max()) < 0.4 and float((scores["cuda"] - scores["cpu"]).abs().mean()) < 0.1
