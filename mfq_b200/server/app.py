@@ -22,6 +22,7 @@ import json
 import queue
 import time
 import uuid
+from pathlib import Path
 
 from fastapi import FastAPI, Request as HttpRequest, WebSocket, WebSocketDisconnect
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
@@ -122,6 +123,7 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
     from .jobs import JobManager
     from .policies import PolicyStore
     jobs = JobManager()
+    instance_id, started_at = uuid.uuid4().hex, time.time()
     policies = policies if policies is not None else PolicyStore()
     for _lm in service.models.values():
         policies.apply_concurrency(_lm.name, _lm.scheduler)
@@ -665,6 +667,67 @@ def create_app(service: ModelService, api_key=None, sessions=None, cluster=None,
     @app.delete("/api/v1/sessions/{sid}")
     async def delete_session(sid: str):
         return {"deleted": store.delete(sid)}
+
+    @app.get("/health/identity")
+    async def health_identity():
+        """Who answers here: package version, a process-lifetime instance id, the models it serves.  A cluster peer
+        list uses it to tell a restarted server from the one it knew."""
+        from .. import __version__
+        return {"service": "mfq_b200", "version": __version__, "instance_id": instance_id,
+                "started_at": started_at, "models": sorted(service.models)}
+
+    @app.get("/api/v1/models/{model}/cache-profile")
+    async def get_cache_profile(model: str):
+        """Per-expert heat of a model whose routed experts sit behind an HBM slot arena (what ``--moe-cache-profile``
+        saves and a later start warms the arena from)."""
+        from ..engine import moe_cache_profile as mcp
+        lm = service.models.get(model)
+        if lm is None:
+            return error_response(404, "model_not_found", f"model {model!r} is not loaded")
+        inner = getattr(getattr(lm, "engine", None), "model", None) or getattr(getattr(getattr(lm, "engine", None), "engine", None), "model", None)
+        if inner is None or not getattr(inner, "residencies", lambda: [])():
+            return error_response(409, "no_expert_cache", f"model {model!r} keeps every expert resident: there is no cache to profile")
+        return await asyncio.get_running_loop().run_in_executor(None, service.call, lm, lambda _m: mcp.collect(inner, model))
+
+    @app.post("/api/v1/models/{model}/cache-profile")
+    async def apply_cache_profile(model: str, request: HttpRequest):
+        """Warm the expert arena from a profile (the body is what the GET returns)."""
+        from ..engine import moe_cache_profile as mcp
+        lm = service.models.get(model)
+        if lm is None:
+            return error_response(404, "model_not_found", f"model {model!r} is not loaded")
+        inner = getattr(getattr(lm, "engine", None), "model", None)
+        if inner is None or not getattr(inner, "residencies", lambda: [])():
+            return error_response(409, "no_expert_cache", f"model {model!r} keeps every expert resident")
+        body = await request.json()
+        try:
+            warmed = await asyncio.get_running_loop().run_in_executor(None, service.call, lm, lambda _m: mcp.apply(inner, body))
+        except (ValueError, KeyError, TypeError) as exc:
+            return error_response(400, "invalid_request", f"not a usable cache profile: {exc}")
+        return {"model": model, "warmed_experts": warmed}
+
+    @app.get("/api/v1/datasets/catalog")
+    async def datasets_catalog():
+        """Calibration corpora (directories written by ``mfq calibrate data`` / ``trace-data``) under the catalog's
+        roots: name, path, format, sequences and tokens per split, tokenizer identity."""
+        roots = list(getattr(catalog, "roots", []) or [])
+        found = []
+        for root in roots:
+            base = Path(root)
+            if not base.is_dir():
+                continue
+            for manifest in sorted(base.glob("**/manifest.json")):
+                try:
+                    doc = json.loads(manifest.read_text(encoding="utf-8"))
+                except (OSError, ValueError):
+                    continue
+                if not str(doc.get("format", "")).startswith("mfq.calibration-corpus."):
+                    continue
+                found.append({"name": manifest.parent.name, "path": str(manifest.parent), "format": doc["format"],
+                              "sequence_length": doc.get("sequence_length"), "domains": doc.get("domains"),
+                              "tokens": doc.get("actual_tokens"), "scored_tokens": doc.get("scored_tokens"),
+                              "tokenizer": doc.get("tokenizer")})
+        return {"roots": roots, "datasets": found}
 
     @app.post("/api/v1/evaluations/probabilities")
     async def evaluation_probabilities(request: HttpRequest):

@@ -20,7 +20,7 @@ import time
 from pathlib import Path
 
 SCOPES = ("inference", "read", "admin")
-_OPEN_PATHS = ("/health",)
+_OPEN_PATHS = ("/health", "/health/identity")
 
 
 def required_scope(method: str, path: str) -> str | None:

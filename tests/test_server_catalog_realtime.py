@@ -190,3 +190,65 @@ def test_analysis_stats_and_purge_routes(tmp_path):
             assert c.delete("/api/v1/catalog/outside", params={"purge": "true"}).status_code == 403 and outside.exists()
         finally:
             outside.unlink(missing_ok=True)
+
+
+def test_identity_dataset_catalog_and_cache_profile_routes(tmp_path):
+    import json
+
+    from fastapi.testclient import TestClient
+
+    from mfq_b200.calibration.dataset import build_text_corpus
+    from mfq_b200.server import create_app
+    from mfq_b200.server.catalog import ModelCatalog
+    from mfq_b200.server.service import ModelService
+    from mfq_b200.server.tokenizer import ByteTokenizer
+    (tmp_path / "data").mkdir()
+    records = [{"text": f"paragraph {i} " + "lorem ipsum dolor sit amet " * 12} for i in range(60)]
+    build_text_corpus(ByteTokenizer(), tmp_path / "data" / "corpus-a", {"plain": records}, train_tokens=1024, validation_tokens=256,
+                      sequence_length=64)
+    (tmp_path / "data" / "other").mkdir()
+    (tmp_path / "data" / "other" / "manifest.json").write_text(json.dumps({"format": "something-else"}))
+    service = ModelService()
+    with TestClient(create_app(service, catalog=ModelCatalog(roots=[tmp_path / "data"]))) as c:
+        ident = c.get("/health/identity").json()
+        assert ident["service"] == "mfq_b200" and len(ident["instance_id"]) == 32 and ident["models"] == []
+        assert c.get("/health/identity").json()["instance_id"] == ident["instance_id"]
+        cat = c.get("/api/v1/datasets/catalog").json()
+        assert [d["name"] for d in cat["datasets"]] == ["corpus-a"]
+        d = cat["datasets"][0]
+        assert d["format"].startswith("mfq.calibration-corpus.") and d["sequence_length"] == 64 and d["tokens"]["train"] >= 1024
+        assert c.get("/api/v1/models/none/cache-profile").status_code == 404
+    service.shutdown()
+    from mfq_b200.server.auth import required_scope
+    assert required_scope("GET", "/health/identity") is None and required_scope("POST", "/api/v1/models/x/cache-profile") == "admin"
+
+
+def test_cache_profile_route_reads_and_warms_an_expert_arena():
+    import numpy as np
+    from fastapi.testclient import TestClient
+
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from mfq_b200.models.moe_lm import MoeConfig, init_weights
+    from mfq_b200.server import create_app
+    from mfq_b200.server.service import ModelService
+    from mfq_b200.server.tokenizer import ByteTokenizer
+    cfg = MoeDecoderConfig.tiny()
+    tensors = init_weights(MoeConfig(head_dim=128, hidden_size=256, moe_intermediate=128, shared_intermediate=128), seed=4, std=0.05)
+    model = MoeDecoderModel(cfg, MoeWeights.from_tensors(cfg, tensors, "cpu", expert_slots=3))
+    res = model.residencies()
+    assert res and all(r.slots == 3 for r in res)
+    service = ModelService()
+    service.add_model("moe", LLMEngine(model, max_batch=2, max_seq_len=64, device="cpu", use_graphs=False), ByteTokenizer())
+    with TestClient(create_app(service)) as c:
+        prof = c.get("/api/v1/models/moe/cache-profile").json()
+        assert prof["model"] == "moe" and len(prof["layers"]) == len(res) and all(v["slots"] == 3 for v in prof["layers"].values())
+        first = next(iter(prof["layers"]))
+        prof["layers"][first]["heat"] = [0.0, 5.0, 0.0, 9.0, 1.0, 0.0, 0.0, 0.0]
+        r = c.post("/api/v1/models/moe/cache-profile", json=prof).json()
+        assert r == {"model": "moe", "warmed_experts": 3}
+        assert sorted(int(e) for e in np.flatnonzero(res[0].slot_of >= 0)) == [1, 3, 4]
+        prof["layers"][first]["heat"] = [1.0]
+        assert c.post("/api/v1/models/moe/cache-profile", json=prof).json()["warmed_experts"] == 0   # a profile of another shape warms nothing
+        assert c.post("/api/v1/models/moe/cache-profile", json={"layers": 3}).status_code == 400
+    service.shutdown()
