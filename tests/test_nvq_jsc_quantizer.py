@@ -119,3 +119,19 @@ def test_tensor_local_codebook_for_plain_nvq(reference_pkg):
 
 def _rel_on(t, w):
     return float(((F.dequantize(t) - w) ** 2).sum() / (w ** 2).sum())
+
+
+def test_additive_and_product_vector_code_experiments():
+    """15 bits per 8-vector spent as two added codewords or as two half-vector codewords: the rounds only lower the error,
+    the tables are int8, and on a heavy-tailed matrix both land below plain NVQ2 (tables fitted to the matrix itself)."""
+    from mfq_b200.quantize.nvq_experiments import vector_code_experiment
+    w = _w(96, 192, seed=9)
+    for kind, shape in (("additive", (256, 8)), ("product", (256, 4))):
+        r = vector_code_experiment(w, kind, rounds=4)
+        assert r.first.shape == shape and r.second.shape == (128, shape[1]) and r.first.dtype == np.int8
+        assert all(b <= a * 1.002 for a, b in zip(r.history, r.history[1:])) and r.rel_error == r.history[-1]
+        assert r.rel_error < r.nvq2_rel_error and abs(r.bits_per_weight - (15 / 8 + 4 / 24 + 16 / 192)) < 1e-9
+    with pytest.raises(ValueError):
+        vector_code_experiment(w[:, :100], "additive")
+    with pytest.raises(ValueError):
+        vector_code_experiment(w, "lattice")
