@@ -569,9 +569,9 @@ class LLMEngine:
                 self._decode_step_once(b, stochastic, constrained, keep_head)
                 if int(self.moe_miss_count.item()) == 0:
                     return
-                verdicts = [r.settle() for r in res]
+                outcomes = [r.settle() for r in res]
                 restore()
-                if "fallback" in verdicts:
+                if "fallback" in outcomes:
                     break
                 self.residency_stats["replays"] += 1
         finally:
