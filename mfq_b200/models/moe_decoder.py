@@ -351,13 +351,15 @@ class MoeDecoderModel(LlamaModel):
         wt = wt * cfg.routed_scale
         out = torch.zeros_like(h, dtype=torch.float32)  # this rank's experts (+ its share of the shared expert)
         xd = xq.float() * xs[:, None]
-        for le in range(ffn.gate_up.shape[0]):
+        # with an expert arena the fp32 path reads the host tier directly: all experts are there, no slot bookkeeping
+        e_gu, e_gus, e_dn, e_dns = ffn.residency.host if ffn.residency is not None else (ffn.gate_up, ffn.gate_up_scale, ffn.down, ffn.down_scale)
+        for le in range(e_gu.shape[0]):
             tok, slot = (ids == ffn.e_lo + le).nonzero(as_tuple=True)
             if tok.numel() == 0:
                 continue
-            gu = (xd[tok] @ ref.dequant_block(ffn.gate_up[le], ffn.gate_up_scale[le]).T).to(torch.bfloat16)
+            gu = (xd[tok] @ ref.dequant_block(e_gu[le], e_gus[le]).T).to(torch.bfloat16)
             hq, hs = ref.silu_mul_quant(gu)
-            ye = ((hq.float() * hs[:, None]) @ ref.dequant_block(ffn.down[le], ffn.down_scale[le]).T).to(torch.bfloat16)
+            ye = ((hq.float() * hs[:, None]) @ ref.dequant_block(e_dn[le], e_dns[le]).T).to(torch.bfloat16)
             out.index_add_(0, tok, ye.float() * wt[tok, slot][:, None])
         if ffn.shared_gate_up is not None and not (ffn.shared_replicated and self.w.tp_rank != 0):
             sq, ss = ref.silu_mul_quant(ffn.shared_gate_up(xq, xs))

@@ -138,3 +138,20 @@ def test_optimistic_translate_counts_misses_and_settle_makes_the_step_whole():
     before = res.heat.copy()
     res.absorb_heat()
     assert res.heat[1] > before[1] * res.decay and int(res.heat_dev.sum()) == 0
+
+
+def test_cpu_decoder_with_an_arena_reads_the_host_tier():
+    """On the CPU the fp32 path has no arena to manage: a model built with ``expert_slots`` gives the logits of the same
+    model without it (the routed experts are read from the host tier, not from the uninitialised slot arena)."""
+    from mfq_b200.engine.llm_engine import LLMEngine
+    from mfq_b200.models.moe_decoder import MoeDecoderConfig, MoeDecoderModel, MoeWeights
+    from mfq_b200.models.moe_lm import MoeConfig, init_weights
+    cfg = MoeDecoderConfig.tiny()
+    tensors = init_weights(MoeConfig(head_dim=128, hidden_size=256, moe_intermediate=128, shared_intermediate=128), seed=4, std=0.05)
+    prompts = [torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(1))]
+    toks = []
+    for slots in (None, 3):
+        model = MoeDecoderModel(cfg, MoeWeights.from_tensors(cfg, tensors, "cpu", expert_slots=slots))
+        assert bool(model.residencies()) == (slots is not None)
+        toks.append(LLMEngine(model, max_batch=1, max_seq_len=48, device="cpu", use_graphs=False).generate(prompts, 6).tokens)
+    assert torch.equal(toks[0], toks[1])
